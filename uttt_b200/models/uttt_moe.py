@@ -1,0 +1,500 @@
+"""uTTT-MoE / TTT-MoE language model: sliding-window attention plus a routed pool of SwiGLU
+fast-weight experts that is read by every layer and written once per chunk.
+
+Behavioural reference: uttt_llm/flame/custom_models/uttt_moe/modeling_recurrent_lact.py
+(block ``:929-1017``, chunk loop ``:3490-3554``, aggregate write ``:2381-2546``, update rule
+``:754-825``, loss-free balancing ``:1593-1712``, cross-layer cut ``:1379-1529``) and, for the
+layer-local pools, uttt_llm/flame/custom_models/ttt_moe_lb/modeling_recurrent_lact.py:125-698.
+
+Design differences (same math):
+* chunk-major schedule with one recompute region per (chunk, layer) and one per chunk-boundary
+  write, but key/value history is carried as tensors (last ``window-1`` positions) instead of a
+  full-length in-place module buffer, and keys/values are projected once per chunk;
+* gate and up fast weights stay fused (``[B, E, 2I, D]``) for the whole sequence;
+* routing builds a tile-padded expert-major layout on the device without host syncs.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Dict, List, Optional, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+from torch.utils.checkpoint import checkpoint
+
+from .. import ops
+from ..config import LMConfig
+from . import fast_weights as fw
+from .common import (GatedMLP, LowRankFastWeight, RMSNorm, SlidingWindowAttention, init_linear_weights,
+                     inv_softplus, trim_history)
+
+
+@dataclass
+class CausalLMOutput:
+    loss: Optional[torch.Tensor] = None
+    logits: Optional[torch.Tensor] = None
+    ce_loss: Optional[torch.Tensor] = None
+    lb_loss: Optional[torch.Tensor] = None
+    hidden_states: Optional[torch.Tensor] = None
+    moe_stats: Optional[Dict[str, Any]] = None
+    past_key_values: Any = None
+
+
+class MoEBlock(nn.Module):
+    def __init__(self, config, layer_idx: int):
+        super().__init__()
+        self.config = config
+        self.layer_idx = layer_idx
+        d = config.hidden_size
+        self.attn_norm = RMSNorm(d, eps=config.norm_eps)
+        self.attn = SlidingWindowAttention(config, layer_idx)
+        if config.use_memory_block:
+            self.memory_norm = RMSNorm(d, eps=config.norm_eps) if config.residual_style == "sequential" else None
+            self.memory = fw.FastWeightMemory(config, layer_idx, momentum_out=1)
+            self.to_lr = nn.Linear(d, 3 * config.fw_heads if config.per_head_lr else 3)
+            self.base_lr_inv = inv_softplus(config.base_lr)
+        else:
+            self.memory_norm = None
+            self.memory = None
+        self.memory_output_proj = nn.Linear(d, d, bias=False) if config.enable_attention_memory_output_proj else None
+        self.mlp_norm = RMSNorm(d, eps=config.norm_eps)
+        self.mlp = GatedMLP(d, config.mlp_intermediate_size)
+
+    # -------------------------------------------------------------------------- read
+    def forward(self, h, k_hist, v_hist, w02, w1, router, bias, offset: int):
+        """One (chunk, layer) step.  Returns tensors only (it runs under activation recompute)."""
+        cfg = self.config
+        residual = h
+        x_attn_in = self.attn_norm(h)
+        attn_out, q_flat, k_flat, v_flat, k_rot, v_new = self.attn(x_attn_in, k_hist, v_hist, offset)
+        lb_probs = lb_counts = None
+        if self.memory is not None:
+            if cfg.residual_style == "sequential":
+                h = residual + attn_out
+                residual = h
+                x_mem_in = self.memory_norm(h)
+            else:
+                x_mem_in = x_attn_in
+            mem = self.memory
+            q_rows = mem.head_rows(mem.prep_query(q_flat, offset))
+            routing = fw.route_rows(q_rows, router, bias, cfg, getattr(cfg, "memory_bias_in_logits", False))
+            y = fw.pool_read(q_rows, w02, w1, routing)
+            mem_out = mem.finish_read(y, x_mem_in).to(attn_out.dtype)
+            lb_probs, lb_counts = routing.prob_sum, routing.counts
+            mixed = mem_out + attn_out if cfg.residual_style == "parallel" else mem_out
+        else:
+            mixed = attn_out
+        if self.memory_output_proj is not None:
+            mixed = self.memory_output_proj(mixed)
+        h = residual + mixed
+        h = h + self.mlp(self.mlp_norm(h))
+        if lb_probs is None:
+            lb_probs = h.new_zeros((h.shape[0], 1), dtype=torch.float32)
+            lb_counts = lb_probs
+        return h, x_attn_in, k_flat, v_flat, k_rot, v_new, lb_probs, lb_counts
+
+    # -------------------------------------------------------------------------- write
+    def raw_grad(self, x_in, k_flat, v_flat, w02, w1, router, bias, offset: int):
+        """This layer's lr-weighted inner gradient on the shared bank, plus momentum gate and lb sums."""
+        cfg = self.config
+        mem = self.memory
+        b, l, _ = x_in.shape
+        lr = F.softplus(self.to_lr(x_in).float() + self.base_lr_inv)          # [b, l, 3h] or [b, l, 3]
+        if lr.shape[-1] == 3:
+            lr_rows = lr.unsqueeze(2).expand(b, l, mem.fw_heads, 3).reshape(b, l * mem.fw_heads, 3)
+        else:
+            lr_rows = lr.reshape(b, l * mem.fw_heads, 3)
+        k_rows = mem.head_rows(mem.prep_key(k_flat, offset))
+        v_rows = mem.head_rows(mem.prep_value(v_flat))
+        route_in = v_rows if cfg.memory_router_from_v else k_rows
+        routing = fw.route_rows(route_in, router, bias, cfg, getattr(cfg, "memory_bias_in_logits", False))
+        g02, g1 = fw.pool_raw_grad(k_rows, v_rows, lr_rows, w02, w1, routing)
+        m = mem.momentum_coeff(x_in)
+        return g02, g1, m, routing.prob_sum, routing.counts
+
+
+class UTTTMoEModel(nn.Module):
+    """Backbone.  ``pool_mode='shared'``: one pool for the whole stack (uTTT-MoE);
+    ``'per_layer'``: each layer routes within its own pool (TTT-MoE)."""
+
+    def __init__(self, config):
+        super().__init__()
+        self.config = config
+        d = config.hidden_size
+        self.embeddings = nn.Embedding(config.vocab_size, d, config.pad_token_id)
+        self.layers = nn.ModuleList([MoEBlock(config, i) for i in range(config.num_hidden_layers)])
+        self.norm = RMSNorm(d, eps=config.norm_eps)
+        self.num_experts = config.memory_num_experts
+        self.per_layer_pool = config.memory_pool_mode != "shared"
+        write_layers = config.memory_write_layers
+        n_layers = config.num_hidden_layers
+        if write_layers == "all":
+            self.writer_layers = tuple(range(n_layers))
+        elif write_layers == "last":
+            self.writer_layers = (n_layers - 1,)
+        else:
+            self.writer_layers = tuple(sorted(int(i) for i in write_layers))
+        self.activation_checkpoint = True
+        if config.use_memory_block:
+            self._init_pool_parameters()
+            self._init_loss_free_buffers()
+        self.reset_parameters()
+
+    # ------------------------------------------------------------------ parameters
+    def _init_pool_parameters(self) -> None:
+        cfg = self.config
+        e, i_dim, d_dim = cfg.memory_num_experts, cfg.fw_inter_dim, cfg.fw_head_dim
+        n_pools = cfg.num_hidden_layers if self.per_layer_pool else 1
+        heads = e * n_pools
+        if cfg.w0_w2_low_rank > 0:
+            self.pool_w0 = LowRankFastWeight(heads, i_dim, d_dim, cfg.w0_w2_low_rank, cfg.fw_init_gain, True)
+            self.pool_w2 = LowRankFastWeight(heads, i_dim, d_dim, cfg.w0_w2_low_rank, cfg.fw_init_gain, True)
+        else:
+            self.pool_w0 = nn.Parameter(torch.empty(heads, i_dim, d_dim))
+            self.pool_w2 = nn.Parameter(torch.empty(heads, i_dim, d_dim))
+        self.pool_w1 = nn.Parameter(torch.empty(heads, d_dim, i_dim))
+        if cfg.memory_router_share_mode == "share_all" and not self.per_layer_pool:
+            self.shared_router_proj_weights = nn.Parameter(torch.empty(1, e, d_dim))
+            self.per_layer_router_proj_weights = None
+        else:
+            self.shared_router_proj_weights = None
+            self.per_layer_router_proj_weights = nn.Parameter(torch.empty(cfg.num_hidden_layers, 1, e, d_dim))
+
+    def _init_loss_free_buffers(self) -> None:
+        cfg = self.config
+        shape = (self.num_experts,) if (cfg.memory_lb_scope == "pool" and not self.per_layer_pool) \
+            else (cfg.num_hidden_layers, self.num_experts)
+        self.register_buffer("memory_loss_free_bias", torch.zeros(shape, dtype=torch.float32), persistent=True)
+        self.register_buffer("memory_loss_free_pending_counts", torch.zeros(shape, dtype=torch.float32),
+                             persistent=False)
+        self.register_buffer("memory_loss_free_steps", torch.zeros((), dtype=torch.long), persistent=True)
+        self.register_buffer("memory_loss_free_num_updates", torch.zeros((), dtype=torch.long), persistent=True)
+        # device-side flag: 1.0 once any count is pending (keeps the update free of host syncs)
+        self._host_steps = 0
+
+    def reset_parameters(self) -> None:
+        cfg = self.config
+        init_linear_weights(self, cfg.initializer_range)
+        for layer in self.layers:
+            if layer.memory is not None:
+                layer.memory.reset_parameters()
+        if not cfg.use_memory_block:
+            return
+        d_dim, i_dim = cfg.fw_head_dim, cfg.fw_inter_dim
+        if cfg.w0_w2_low_rank > 0:
+            self.pool_w0.reset_parameters()
+            self.pool_w2.reset_parameters()
+        else:
+            nn.init.normal_(self.pool_w0, std=d_dim ** -0.5)
+            nn.init.normal_(self.pool_w2, std=d_dim ** -0.5)
+        nn.init.normal_(self.pool_w1, std=i_dim ** -0.5)
+        router = self.shared_router_proj_weights if self.shared_router_proj_weights is not None \
+            else self.per_layer_router_proj_weights
+        nn.init.normal_(router, std=d_dim ** -0.5)
+
+    def _apply(self, fn, *args, **kwargs):
+        module = super()._apply(fn, *args, **kwargs)
+        for name in ("memory_loss_free_bias", "memory_loss_free_pending_counts"):
+            buf = self._buffers.get(name)
+            if buf is not None and buf.dtype != torch.float32:
+                self._buffers[name] = buf.float()
+        return module
+
+    # ------------------------------------------------------------------ helpers
+    def _router(self, layer_idx: int) -> torch.Tensor:
+        if self.shared_router_proj_weights is not None:
+            return self.shared_router_proj_weights[0]
+        return self.per_layer_router_proj_weights[layer_idx, 0]
+
+    def _loss_free_enabled(self) -> bool:
+        cfg = self.config
+        return cfg.memory_lb_mode == "loss_free" and cfg.memory_loss_free_update_rate > 0 and self.num_experts > 1
+
+    def _router_bias(self, layer_idx: int) -> Optional[torch.Tensor]:
+        if not self._loss_free_enabled():
+            return None
+        bias = self.memory_loss_free_bias
+        return bias if bias.dim() == 1 else bias[layer_idx]
+
+    def _pool_weights(self):
+        cfg = self.config
+        w0 = self.pool_w0() if cfg.w0_w2_low_rank > 0 else self.pool_w0
+        w2 = self.pool_w2() if cfg.w0_w2_low_rank > 0 else self.pool_w2
+        return w0, self.pool_w1, w2
+
+    def compute_dtype(self) -> torch.dtype:
+        return self.embeddings.weight.dtype if self.embeddings.weight.dtype != torch.float32 else (
+            torch.float32)
+
+    def init_states(self, batch: int) -> List[fw.PoolState]:
+        """One state for the shared pool, or one per layer for layer-local pools."""
+        cfg = self.config
+        w0, w1, w2 = self._pool_weights()
+        dt = self.compute_dtype()
+        e = self.num_experts
+        n_pools = cfg.num_hidden_layers if self.per_layer_pool else 1
+        return [fw.init_pool_state(w0[p * e:(p + 1) * e], w1[p * e:(p + 1) * e], w2[p * e:(p + 1) * e], batch,
+                                   cfg.use_momentum, dt) for p in range(n_pools)]
+
+    # ------------------------------------------------------------------ loss-free balancing
+    @torch.no_grad()
+    def _maybe_update_loss_free_bias(self) -> None:
+        """bias += u * sign(mean - count) once per update interval; no host sync
+        (modeling_recurrent_lact.py:1662-1693)."""
+        if not self.training or not self._loss_free_enabled():
+            return
+        cfg = self.config
+        steps = self._host_steps
+        counts = self.memory_loss_free_pending_counts
+        if steps == 0:
+            return
+        if steps <= cfg.memory_loss_free_warmup_steps:
+            counts.zero_()
+            return
+        if (steps - cfg.memory_loss_free_warmup_steps) % cfg.memory_loss_free_update_interval != 0:
+            return
+        bias = self.memory_loss_free_bias
+        active = (counts.sum() > 0).to(bias.dtype)
+        target = counts.mean() if counts.dim() == 1 else counts.mean(dim=-1, keepdim=True)
+        new_bias = bias + cfg.memory_loss_free_update_rate * torch.sign(target - counts)
+        new_bias = new_bias - (new_bias.mean() if bias.dim() == 1 else new_bias.mean(dim=-1, keepdim=True))
+        if cfg.memory_loss_free_bias_max >= 0:
+            new_bias = new_bias.clamp(-cfg.memory_loss_free_bias_max, cfg.memory_loss_free_bias_max)
+        bias.copy_(active * new_bias + (1 - active) * bias)
+        counts.zero_()
+        self.memory_loss_free_num_updates.add_(active.long())
+
+    @torch.no_grad()
+    def _store_loss_free_counts(self, apply_counts: torch.Tensor, update_counts: torch.Tensor) -> None:
+        if not self.training or not self._loss_free_enabled():
+            return
+        counts = apply_counts.sum(dim=1) + update_counts.sum(dim=1)   # [L, E]
+        if self.memory_loss_free_pending_counts.dim() == 1:
+            counts = counts.sum(dim=0)
+        counts = counts.float()
+        if torch.distributed.is_available() and torch.distributed.is_initialized():
+            torch.distributed.all_reduce(counts)
+        self.memory_loss_free_pending_counts.add_(counts)
+        self.memory_loss_free_steps.add_(1)
+        self._host_steps += 1
+
+    # ------------------------------------------------------------------ write
+    def _chunk_write(self, states: List[fw.PoolState], feats: List[Tuple[torch.Tensor, ...]], offset: int):
+        """Update the bank(s) from this chunk.  Returns (new_states, upd_probs [L,B,E], upd_counts [L,B,E])."""
+        cfg = self.config
+        mode = cfg.memory_update_backward_mode
+        n_layers = len(self.layers)
+        dt = states[0].w02.dtype
+
+        if self.per_layer_pool or not cfg.memory_update_aggregate_write:
+            # chained writes: every writer applies its own update (to its own pool, or to the shared bank in turn)
+            new_states = list(states)
+            probs, counts = [], []
+            for li, layer in enumerate(self.layers):
+                si = li if self.per_layer_pool else 0
+
+                def _one(x_in, k_flat, v_flat, *st, _layer=layer, _li=li):
+                    state = fw.PoolState.from_tensors(st)
+                    g02, g1, m, p, c = _layer.raw_grad(x_in, k_flat, v_flat, state.w02, state.w1,
+                                                       self._router(_li), self._router_bias(_li), offset)
+                    if mode in ("first_order_state", "stop_state"):
+                        g02, g1 = g02.detach(), g1.detach()
+                    if m is not None and (cfg.memory_detach_m_coeff or mode == "stop_state"):
+                        m = m.detach()
+                    mc = None if m is None else m.view(-1, 1, 1, 1)
+                    new = fw.apply_pool_update(g02, g1, state, mc, 1.0, cfg.use_moun, compute_dtype=dt)
+                    return (*[t for t in new.tensors() if t is not None], p, c)
+
+                st_in = [t for t in new_states[si].tensors() if t is not None]
+                out = self._ckpt(_one, *feats[li], *st_in) if mode != "stop_state" else _one(*feats[li], *st_in)
+                n_state = len(st_in)
+                vals = list(out[:n_state]) + [None] * (6 - n_state)
+                new = fw.PoolState.from_tensors(vals)
+                new_states[si] = new.detach() if mode == "stop_state" else new
+                probs.append(out[n_state])
+                counts.append(out[n_state + 1])
+            return new_states, torch.stack(probs), torch.stack(counts)
+
+        state = states[0]
+        writers = self.writer_layers
+        flat_feats = [t for li in writers for t in feats[li]]
+        st_in = [t for t in state.tensors() if t is not None]
+        n_state = len(st_in)
+        cut = mode == "cross_layer_cut" and self.training and torch.is_grad_enabled()
+
+        def _aggregate(*args):
+            f = args[:3 * len(writers)]
+            st = list(args[3 * len(writers):]) + [None] * (6 - n_state)
+            s = fw.PoolState.from_tensors(st)
+            a02 = torch.zeros_like(s.m02)
+            a1 = torch.zeros_like(s.m1)
+            ms, probs, counts = [], [], []
+            for wi, li in enumerate(writers):
+                g02, g1, m, p, c = self.layers[li].raw_grad(f[3 * wi], f[3 * wi + 1], f[3 * wi + 2], s.w02, s.w1,
+                                                             self._router(li), self._router_bias(li), offset)
+                if mode in ("first_order_state", "stop_state"):
+                    g02, g1 = g02.detach(), g1.detach()
+                a02 = a02 + g02
+                a1 = a1 + g1
+                if m is not None:
+                    ms.append(m.detach() if (cfg.memory_detach_m_coeff or mode == "stop_state") else m)
+                probs.append(p)
+                counts.append(c)
+            mc = None
+            if cfg.memory_aggregate_momentum_mode == "pool_mean" and ms:
+                mc = torch.stack(ms, dim=0).mean(dim=0).view(-1, 1, 1, 1)
+            new = fw.apply_pool_update(a02, a1, s, mc, cfg.memory_aggregate_lr_scale, cfg.use_moun, compute_dtype=dt)
+            return (*[t for t in new.tensors() if t is not None], torch.stack(probs), torch.stack(counts))
+
+        if cut:
+            from .cross_layer_cut import cross_layer_cut_write
+            return cross_layer_cut_write(self, states, feats, offset)
+        out = _aggregate(*flat_feats, *st_in) if mode == "stop_state" else self._ckpt(_aggregate, *flat_feats, *st_in)
+        vals = list(out[:n_state]) + [None] * (6 - n_state)
+        new = fw.PoolState.from_tensors(vals)
+        if mode == "stop_state":
+            new = new.detach()
+        e = self.num_experts
+        bsz = state.w02.shape[0]
+        probs = torch.zeros(n_layers, bsz, e, device=state.w02.device, dtype=torch.float32)
+        counts = torch.zeros_like(probs)
+        widx = torch.tensor(writers, device=probs.device)
+        probs = probs.index_copy(0, widx, out[n_state].float())
+        counts = counts.index_copy(0, widx, out[n_state + 1].float())
+        return [new], probs, counts
+
+    def _ckpt(self, fn, *args):
+        if self.activation_checkpoint and torch.is_grad_enabled():
+            return checkpoint(fn, *args, use_reentrant=False, preserve_rng_state=False)
+        return fn(*args)
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, input_ids: Optional[torch.Tensor] = None, inputs_embeds: Optional[torch.Tensor] = None,
+                past_key_values: Any = None, use_cache: bool = False):
+        cfg = self.config
+        if inputs_embeds is None:
+            inputs_embeds = self.embeddings(input_ids)
+        if cfg.use_memory_block:
+            self._maybe_update_loss_free_bias()
+        if use_cache and not self.training:
+            from .generation import forward_with_cache
+            return forward_with_cache(self, inputs_embeds, past_key_values)
+        bsz, seq_len, _ = inputs_embeds.shape
+        n_layers = len(self.layers)
+        chunk = cfg.chunk_size
+        e = max(self.num_experts, 1)
+        dev = inputs_embeds.device
+        states = self.init_states(bsz) if cfg.use_memory_block else []
+        hist: List[Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]] = [(None, None)] * n_layers
+        keep = self.layers[0].attn.history_len(chunk) if cfg.window_size is not None else None
+        apply_probs = torch.zeros(n_layers, bsz, e, device=dev, dtype=torch.float32)
+        apply_counts = torch.zeros_like(apply_probs)
+        update_probs = torch.zeros_like(apply_probs)
+        update_counts = torch.zeros_like(apply_probs)
+        cut = (cfg.use_memory_block and cfg.memory_update_backward_mode == "cross_layer_cut" and self.training
+               and torch.is_grad_enabled() and not self.per_layer_pool)
+        if cut:
+            # one aliased copy of the bank per reader layer: reader l's gradient reaches only writer l
+            from .cross_layer_cut import alias_streams
+            states = alias_streams(states[0], n_layers)
+        outputs = []
+        for start in range(0, seq_len, chunk):
+            end = min(start + chunk, seq_len)
+            h = inputs_embeds[:, start:end]
+            feats = []
+            layer_probs, layer_counts = [], []
+            for li, layer in enumerate(self.layers):
+                if cfg.use_memory_block:
+                    st = states[li] if (self.per_layer_pool or cut) else states[0]
+                    w02, w1 = st.w02, st.w1
+                    router, bias = self._router(li), self._router_bias(li)
+                else:
+                    w02 = w1 = router = bias = None
+                k_hist, v_hist = hist[li]
+                h, x_in, k_flat, v_flat, k_rot, v_new, p, c = self._ckpt(
+                    layer, h, k_hist, v_hist, w02, w1, router, bias, start)
+                hist[li] = trim_history(k_hist, v_hist, k_rot, v_new, keep)
+                feats.append((x_in, k_flat, v_flat))
+                layer_probs.append(p)
+                layer_counts.append(c)
+            outputs.append(h)
+            if cfg.use_memory_block:
+                apply_probs = apply_probs + torch.stack(layer_probs)
+                apply_counts = apply_counts + torch.stack(layer_counts)
+                if end < seq_len:   # apply-then-update; the last chunk never writes
+                    states, up, uc = self._chunk_write(states, feats, start)
+                    update_probs = update_probs + up
+                    update_counts = update_counts + uc
+        hidden = self.norm(torch.cat(outputs, dim=1))
+        lb_loss = hidden.new_zeros((), dtype=torch.float32)
+        stats = None
+        if cfg.use_memory_block and self.num_experts > 1:
+            scope = "layer" if self.per_layer_pool else cfg.memory_lb_scope
+            apply_lb = fw.lb_loss_for_scope(apply_probs, apply_counts, scope, self.num_experts)
+            update_lb = fw.lb_loss_for_scope(update_probs, update_counts, scope, self.num_experts)
+            if cfg.memory_lb_mode == "loss":
+                lb_loss = (apply_lb + update_lb) * cfg.memory_lb_loss_alpha
+            self._store_loss_free_counts(apply_counts, update_counts)
+            stats = {"apply_lb": apply_lb.detach(), "update_lb": update_lb.detach(),
+                     "apply_counts": apply_counts.detach(), "update_counts": update_counts.detach()}
+        return hidden, lb_loss, stats
+
+
+class UTTTMoEForCausalLM(nn.Module):
+    """Causal LM head over :class:`UTTTMoEModel`; ``forward(input_ids, labels)`` returns loss = CE + lb."""
+
+    config_class = None
+    model_cls = UTTTMoEModel
+
+    def __init__(self, config):
+        super().__init__()
+        self.config = config
+        self.model = self.model_cls(config)
+        self.vocab_size = config.vocab_size
+        self.lm_head = nn.Linear(config.hidden_size, config.vocab_size, bias=False)
+        nn.init.normal_(self.lm_head.weight, std=config.initializer_range)
+        if config.tie_word_embeddings:
+            self.lm_head.weight = self.model.embeddings.weight
+
+    def forward(self, input_ids=None, labels=None, inputs_embeds=None, past_key_values=None, use_cache=None,
+                logits_to_keep: int = 0, return_logits: Optional[bool] = None) -> CausalLMOutput:
+        use_cache = bool(use_cache) if use_cache is not None else (self.config.use_cache and not self.training
+                                                                   and past_key_values is not None)
+        out = self.model(input_ids=input_ids, inputs_embeds=inputs_embeds, past_key_values=past_key_values,
+                         use_cache=use_cache)
+        cache = None
+        if len(out) == 4:
+            hidden, lb_loss, stats, cache = out
+        else:
+            hidden, lb_loss, stats = out
+        want_logits = return_logits if return_logits is not None else labels is None
+        logits = None
+        if want_logits:
+            hs = hidden[:, -logits_to_keep:] if logits_to_keep else hidden
+            logits = self.lm_head(hs)
+        loss = ce = None
+        if labels is not None:
+            # next-token targets: shift inside, last position ignored
+            tgt = torch.cat([labels[:, 1:], torch.full_like(labels[:, :1], -100)], dim=1)
+            ce = ops.linear_cross_entropy(hidden.reshape(-1, hidden.shape[-1]), self.lm_head.weight,
+                                          tgt.reshape(-1), ignore_index=-100)
+            loss = ce + lb_loss.to(ce.dtype)
+        return CausalLMOutput(loss=loss, logits=logits, ce_loss=None if ce is None else ce.detach(),
+                              lb_loss=lb_loss.detach(), hidden_states=hidden, moe_stats=stats,
+                              past_key_values=cache)
+
+    # HF-flavoured conveniences -------------------------------------------------------
+    @classmethod
+    def from_config(cls, config):
+        return cls(config)
+
+    def num_parameters(self, exclude_embeddings: bool = False) -> int:
+        n = sum(p.numel() for p in self.parameters())
+        if exclude_embeddings:
+            n -= self.model.embeddings.weight.numel()
+        return n
+
+
+class TTTMoEForCausalLM(UTTTMoEForCausalLM):
+    """Layer-local routed pools (config.memory_pool_mode = 'per_layer')."""

@@ -1,0 +1,130 @@
+"""Training engine: model + sharded optimizer + step function (the public training API).
+
+``TrainEngine.train_step(batch)`` takes a batch in *host* memory (pinned when possible),
+copies it to the device on a side stream, runs forward/backward over its micro-batches,
+the fused gradient-reduce/clip/AdamW/redistribute step, and returns the loss as a device
+tensor (call ``.item()`` / ``float()`` to read it back).
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import Any, Dict, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..config import LMConfig
+from ..models import build_model
+from ..parallel.fsdp import AdamWConfig, ShardedTrainer, lm_fsdp_units
+from .lr import WarmupDecayLR
+
+
+@dataclass
+class EngineConfig:
+    micro_batch_size: int = 1          # sequences per forward/backward
+    lr: float = 1e-3
+    eps: float = 1e-15
+    beta1: float = 0.9
+    beta2: float = 0.95
+    weight_decay: float = 0.1
+    max_norm: float = 1.0
+    warmup_steps: int = 1024
+    total_steps: int = 40960
+    decay_type: str = "cosine"
+    lr_min: float = 0.1
+    skip_nan_inf: bool = True
+    seed: int = 42
+    activation_checkpoint: bool = True
+
+
+def init_distributed(backend: Optional[str] = None) -> tuple[int, int, int]:
+    """Join the torchrun rendezvous if there is one.  Returns (rank, world, local_rank)."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1 and not dist.is_initialized():
+        if backend is None:
+            backend = "nccl" if torch.cuda.is_available() else "gloo"
+        if backend == "nccl":
+            torch.cuda.set_device(local)
+            dist.init_process_group(backend, device_id=torch.device("cuda", local))
+        else:
+            dist.init_process_group(backend)
+    elif torch.cuda.is_available():
+        torch.cuda.set_device(local)
+    return rank, world, local
+
+
+class TrainEngine:
+    def __init__(self, model_config: LMConfig, cfg: Optional[EngineConfig] = None,
+                 device: Optional[torch.device] = None, model: Optional[nn.Module] = None):
+        self.cfg = cfg or EngineConfig()
+        self.model_config = model_config
+        if device is None:
+            device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() \
+                else torch.device("cpu")
+        self.device = device
+        torch.manual_seed(self.cfg.seed)   # same seed on every rank: identical initial weights
+        if model is None:
+            model = build_model(model_config)
+        self.model = model.to(device)
+        inner = getattr(self.model, "model", None)
+        if inner is not None and hasattr(inner, "activation_checkpoint"):
+            inner.activation_checkpoint = self.cfg.activation_checkpoint
+        opt = AdamWConfig(lr=self.cfg.lr, beta1=self.cfg.beta1, beta2=self.cfg.beta2, eps=self.cfg.eps,
+                          weight_decay=self.cfg.weight_decay, max_norm=self.cfg.max_norm,
+                          skip_nan_inf=self.cfg.skip_nan_inf)
+        self.trainer = ShardedTrainer(self.model, lm_fsdp_units(self.model), opt)
+        self.lr_sched = WarmupDecayLR(self.cfg.lr, self.cfg.total_steps, self.cfg.warmup_steps,
+                                      self.cfg.decay_type, self.cfg.lr_min)
+        self.copy_stream = torch.cuda.Stream(device) if device.type == "cuda" else None
+        self.step = 0
+        self.tokens_seen = 0
+        self.last_stats: Dict[str, Any] = {}
+
+    # ------------------------------------------------------------------ data movement
+    def to_device(self, batch: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        if self.copy_stream is None:
+            return {k: v.to(self.device) for k, v in batch.items()}
+        with torch.cuda.stream(self.copy_stream):
+            out = {k: v.to(self.device, non_blocking=True) for k, v in batch.items()}
+        torch.cuda.current_stream(self.device).wait_stream(self.copy_stream)
+        return out
+
+    # ------------------------------------------------------------------ one optimizer step
+    def train_step(self, batch: Dict[str, torch.Tensor]) -> torch.Tensor:
+        """batch: {'input_ids': [B, S], 'labels': [B, S]} (host or device).  Returns the mean loss (device)."""
+        self.model.train()
+        ids_all = batch["input_ids"]
+        if ids_all.device != self.device:
+            batch = self.to_device(batch)
+            ids_all = batch["input_ids"]
+        labels_all = batch.get("labels", ids_all)
+        bsz = ids_all.shape[0]
+        mb = min(self.cfg.micro_batch_size, bsz)
+        n_micro = (bsz + mb - 1) // mb
+        total = torch.zeros((), device=self.device, dtype=torch.float32)
+        for i in range(n_micro):
+            out = self.model(input_ids=ids_all[i * mb:(i + 1) * mb], labels=labels_all[i * mb:(i + 1) * mb])
+            (out.loss / n_micro).backward()
+            total += out.loss.detach().float() / n_micro
+            if n_micro > 1:
+                self.trainer.accumulate_micro_batch()
+            self.last_stats = {"ce": out.ce_loss, "lb": out.lb_loss}
+        lr = self.lr_sched.lr()
+        stats = self.trainer.step(lr=lr)
+        self.lr_sched.step()
+        self.step += 1
+        self.tokens_seen += ids_all.numel()
+        self.last_stats.update(stats)
+        self.last_stats["lr"] = lr
+        return total
+
+    @torch.no_grad()
+    def eval_loss(self, batch: Dict[str, torch.Tensor]) -> torch.Tensor:
+        self.model.eval()
+        batch = self.to_device(batch) if batch["input_ids"].device != self.device else batch
+        out = self.model(input_ids=batch["input_ids"], labels=batch.get("labels", batch["input_ids"]))
+        return out.loss
