@@ -1,0 +1,190 @@
+"""Headline benchmark: training tokens/s of the 760M uTTT-MoE language model at 32K context.
+
+    python bench.py --gpus N --steps K --warmup W          (N > 1: launched under torchrun)
+
+Every rank trains on its own synthetic Zipf(1.1) sequences (weak scaling: ``--per-gpu-batch``
+sequences of 32768 tokens per GPU and step, so 8 GPUs x 4 = the global batch of 32).  A step is
+forward + backward over the rank's sequences, the gradient reduction, clipping, AdamW and the
+parameter redistribution.  Two numbers are taken, both with CUDA events between
+barrier + synchronize fences, max over ranks:
+
+* ``value``: steps on batches already resident on the device (kernel-side throughput);
+* ``e2e``: steps through ``TrainEngine.train_step`` from pinned host memory with the loss read
+  back to the host every step.
+
+``--impl reference`` runs the unmodified reference implementation from ``baseline/_ref`` on the
+same metric and shape (see baseline/run_reference.py).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BASELINE_TOKENS_PER_S = None      # the reference publishes no throughput number
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of this rank's GPU with nvidia-smi while timing."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1])); power.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from uttt_b200 import ops
+    from uttt_b200.config import named_config
+    from uttt_b200.ops._ext import load
+    from uttt_b200.train.data import SyntheticZipfTokens
+    from uttt_b200.train.engine import EngineConfig, TrainEngine, init_distributed
+
+    rank, world, local = init_distributed()
+    assert torch.cuda.is_available(), "bench.py needs a GPU"
+    ext = load(required=True)
+    dev = torch.device("cuda", local)
+    cfg = named_config(args.model, memory_update_backward_mode=args.backward_mode)
+    seq = args.seq_len
+    eng = TrainEngine(cfg, EngineConfig(micro_batch_size=args.micro_batch, lr=1e-3, eps=1e-15, warmup_steps=1024,
+                                        total_steps=40960, seed=42), dev)
+    data = SyntheticZipfTokens(cfg.vocab_size, seq, args.per_gpu_batch, seed=1234, rank=rank, world=world)
+    n_params = eng.trainer.num_parameters()
+
+    def fence():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def timed(step_fn, batches):
+        fence()
+        sampler = ClockSampler(local)
+        sampler.start()
+        launches0 = ops.launch_count()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for b in batches:
+            step_fn(b)
+        end.record()
+        torch.cuda.synchronize(dev)
+        launches = ops.launch_count() - launches0
+        clocks = sampler.stop()
+        if world > 1:
+            dist.barrier()
+        ms = torch.tensor([start.elapsed_time(end) / len(batches)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()), launches, clocks
+
+    # warm-up (allocator, lazy tables, cuBLAS handles)
+    for _ in range(max(args.warmup, 3)):
+        float(eng.train_step(next(data)))
+    # (1) device-resident batches: distinct inputs every step, working set per step >> L2
+    dev_batches = [{k: v.to(dev) for k, v in next(data).items()} for _ in range(args.steps)]
+    ms, launches, clocks = timed(lambda b: eng.train_step(b), dev_batches)
+    # (2) end to end through the public API: pinned host batch -> device, loss -> host, every step
+    host_batches = [next(data) for _ in range(args.steps)]
+    losses = []
+    ms_e2e, _, clocks_e2e = timed(lambda b: losses.append(float(eng.train_step(b))), host_batches)
+    status = int(ext.gemm_status(torch.zeros(1, device=dev))[0])
+    tokens_per_step = args.per_gpu_batch * seq * world
+    h2d = host_batches[0]["input_ids"].numel() * host_batches[0]["input_ids"].element_size()
+    if rank == 0:
+        peak_gb = torch.cuda.max_memory_allocated(dev) / 2 ** 30
+        out = {
+            "metric": "train tokens/s, 760M uTTT-MoE 32K ctx", "value": tokens_per_step / (ms / 1e3),
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": (tokens_per_step / (ms / 1e3) / BASELINE_TOKENS_PER_S) if BASELINE_TOKENS_PER_S else None,
+            "dtype": "bf16", "data": "synthetic Zipf(1.1) token ids, random-init weights",
+            "impl": "uttt_b200",
+            "config": {"model": args.model, "params": n_params, "global_batch": args.per_gpu_batch * world,
+                       "per_gpu_batch": args.per_gpu_batch, "micro_batch": args.micro_batch, "seq_len": seq,
+                       "parallelism": f"fsdp{world}" if world > 1 else "single",
+                       "backward_mode": args.backward_mode,
+                       "cache": "inputs and per-step working set are far larger than L2 (no flush needed)"},
+            "clocks": clocks,
+            "e2e": {"value": tokens_per_step / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4, "clocks": clocks_e2e,
+                    "last_loss": losses[-1] if losses else None},
+            "gpu_launches": launches, "peak_mem_gib": round(peak_gb, 2), "kernel_status": status,
+        }
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="760M-uttt-moe")
+    ap.add_argument("--seq-len", type=int, default=32768)
+    ap.add_argument("--per-gpu-batch", type=int, default=4)
+    ap.add_argument("--micro-batch", type=int, default=int(os.environ.get("UTTT_BENCH_MICRO_BATCH", "2")))
+    ap.add_argument("--backward-mode", default="full")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        from baseline.run_reference import run_reference
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,322 @@
+"""Numerics of every sm_100a kernel against the plain PyTorch fp32 statement of the same op."""
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from uttt_b200 import ops
+from uttt_b200.ops import reference as ref
+from uttt_b200.ops import functional as fn
+from uttt_b200.ops._ext import load
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _ext():
+    ext = load(required=True)
+    return ext
+
+
+def _close(a, b, atol, rtol, msg=""):
+    torch.testing.assert_close(a.float(), b.float(), atol=atol, rtol=rtol, msg=lambda m: f"{msg}: {m}")
+
+
+def _status_ok():
+    st = _ext().gemm_status(torch.zeros(1, device=DEV))
+    assert int(st[0].item()) == 0, f"a tensor-core kernel reported a timed-out wait (code {int(st[0])})"
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("d", [384, 1536])
+def test_rms_norm(dtype, d):
+    _ext()
+    torch.manual_seed(0)
+    x = torch.randn(777, d, device=DEV, dtype=dtype, requires_grad=True)
+    w = (torch.randn(d, device=DEV, dtype=dtype) * 0.1 + 1).requires_grad_(True)
+    y = ops.rms_norm(x, w, 1e-6)
+    xr = x.detach().float().requires_grad_(True)
+    wr = w.detach().float().requires_grad_(True)
+    yr = ref.rms_norm(xr, wr, 1e-6)
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+    _close(y, yr, tol, tol)
+    g = torch.randn_like(y)
+    y.backward(g)
+    yr.backward(g.float())
+    _close(x.grad, xr.grad, tol, tol, "dx")
+    _close(w.grad, wr.grad, 0.5 if dtype == torch.bfloat16 else 1e-3, 3e-2 if dtype == torch.bfloat16 else 1e-4, "dw")
+
+
+@pytest.mark.parametrize("hd", [64, 96])
+def test_rope(hd):
+    _ext()
+    x = torch.randn(2, 300, 5, hd, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    y = ops.rope(x, 1000, 1e6)
+    yr = ref.rope(x.detach().float(), 1000, 1e6)
+    _close(y, yr, 2e-2, 2e-2)
+    g = torch.randn_like(y)
+    (gx,) = torch.autograd.grad(y, x, g)
+    _close(gx, ref.rope(g.float(), 1000, 1e6, inverse=True), 2e-2, 2e-2)
+
+
+@pytest.mark.parametrize("norm", ["l2", "rms", None])
+def test_fw_qk_prep(norm):
+    _ext()
+    torch.manual_seed(1)
+    b, l, heads, D, rope_dim = 2, 160, 4, 96, 32
+    d = heads * D
+    x = torch.randn(b, l, d, device=DEV, dtype=torch.float32, requires_grad=True)
+    sc = (torch.randn(d, device=DEV) * 0.1 + 1).requires_grad_(True)
+    sh = (torch.randn(d, device=DEV) * 0.1).requires_grad_(True)
+    y = ops.fw_qk_prep(x, sc, sh, heads, rope_dim, 1e6, 64, True, norm)
+    xr, scr, shr = [t.detach().clone().requires_grad_(True) for t in (x, sc, sh)]
+    yr = ref.fw_qk_prep(xr, scr, shr, heads, rope_dim, 1e6, 64, True, norm)
+    _close(y, yr, 1e-4, 1e-4)
+    g = torch.randn_like(y)
+    y.backward(g)
+    yr.backward(g)
+    _close(x.grad, xr.grad, 1e-4, 1e-3, "dx")
+    _close(sc.grad, scr.grad, 2e-3, 1e-3, "dscale")
+    _close(sh.grad, shr.grad, 2e-3, 1e-3, "dshift")
+    # bf16 path
+    xb = x.detach().bfloat16()
+    yb = ops.fw_qk_prep(xb, sc.detach().bfloat16(), sh.detach().bfloat16(), heads, rope_dim, 1e6, 64, True, norm)
+    _close(yb, yr, 3e-2, 3e-2)
+
+
+def test_swiglu_and_second_order():
+    _ext()
+    torch.manual_seed(2)
+    y02 = torch.randn(257, 2 * 192, device=DEV, requires_grad=True)
+    h = ops.swiglu(y02)
+    yr = y02.detach().clone().requires_grad_(True)
+    hr = ref.swiglu(yr)
+    _close(h, hr, 1e-5, 1e-5)
+    dh = torch.randn_like(h, requires_grad=True)
+    dhr = dh.detach().clone().requires_grad_(True)
+    (g1,) = torch.autograd.grad(h, y02, dh, create_graph=True)
+    (g1r,) = torch.autograd.grad(hr, yr, dhr, create_graph=True)
+    _close(g1, g1r, 1e-5, 1e-4)
+    c = torch.randn_like(g1)
+    gg = torch.autograd.grad(g1, [dh, y02], c)
+    ggr = torch.autograd.grad(g1r, [dhr, yr], c)
+    for a, b_ in zip(gg, ggr):
+        _close(a, b_, 1e-4, 1e-3)
+
+
+def test_fw_write_pointwise():
+    _ext()
+    torch.manual_seed(3)
+    r, inter = 300, 128
+    y02 = torch.randn(r, 2 * inter, device=DEV, requires_grad=True)
+    dh = torch.randn(r, inter, device=DEV, requires_grad=True)
+    lr = (torch.rand(r, 3, device=DEV) * 0.1).requires_grad_(True)
+    a, b_ = ops.fw_write_pointwise(y02, dh, lr)
+    ins_r = [t.detach().clone().requires_grad_(True) for t in (y02, dh, lr)]
+    ar, br = ref.fw_write_pointwise(*ins_r)
+    _close(a, ar, 1e-5, 1e-4)
+    _close(b_, br, 1e-5, 1e-4)
+    ca, cb = torch.randn_like(a), torch.randn_like(b_)
+    got = torch.autograd.grad([a, b_], [y02, dh, lr], [ca, cb])
+    want = torch.autograd.grad([ar, br], ins_r, [ca, cb])
+    for x, y in zip(got, want):
+        _close(x, y, 1e-4, 1e-3)
+
+
+def _plan(bsz=2, n=700, e=4, k=2, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    logits = torch.randn(bsz, n, e, generator=g)
+    idx = logits.topk(k, -1).indices.to(DEV)
+    return ops.build_group_plan(idx, e)
+
+
+def test_permute_unpermute():
+    _ext()
+    plan = _plan()
+    r, k = plan.dest.shape
+    x = torch.randn(r, 128, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    xp = ops.permute_rows(x, plan)
+    xpr = ref.permute_rows(x.detach().float(), plan.dest, plan.rows_padded)
+    _close(xp, xpr, 0, 0)
+    w = torch.rand(r, k, device=DEV, requires_grad=True)
+    yp = torch.randn(plan.rows_padded, 128, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    out = ops.unpermute_rows(yp, plan, w)
+    ypr = yp.detach().float().requires_grad_(True)
+    wr = w.detach().clone().requires_grad_(True)
+    outr = ref.unpermute_rows(ypr, plan.dest, wr)
+    _close(out, outr, 2e-2, 2e-2)
+    g = torch.randn_like(out)
+    gy, gw = torch.autograd.grad(out, [yp, w], g)
+    gyr, gwr = torch.autograd.grad(outr, [ypr, wr], g.float())
+    _close(gy, gyr, 2e-2, 2e-2)
+    _close(gw, gwr, 0.15, 3e-2)
+    (gx,) = torch.autograd.grad(xp, x, torch.ones_like(xp))
+    _close(gx, torch.full_like(gx, float(k)), 0, 0)
+
+
+@pytest.mark.parametrize("k,n", [(128, 256), (384, 3072), (64, 64)])
+def test_gg_nt(k, n):
+    _ext()
+    torch.manual_seed(4)
+    plan = _plan(seed=k)
+    g = plan.num_groups
+    x = torch.randn(plan.rows_padded, k, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(g, n, k, device=DEV) / math.sqrt(k)).bfloat16()
+    out = ops.gg_nt(x, w, plan)
+    want = ref.gg_nt(x.float(), w.float(), plan.tile_group)
+    torch.cuda.synchronize()
+    _status_ok()
+    # unused tiles are defined as zero by the kernel; the reference multiplies them by group 0
+    used = (plan.tile_group >= 0).repeat_interleave(128)
+    _close(out[used], want[used], 3e-2, 3e-2)
+    assert float(out[~used].abs().max() if (~used).any() else 0) == 0.0
+
+
+@pytest.mark.parametrize("k,n", [(128, 256), (384, 1536), (64, 64)])
+def test_gg_nn(k, n):
+    _ext()
+    torch.manual_seed(5)
+    plan = _plan(seed=k + 1)
+    g = plan.num_groups
+    x = torch.randn(plan.rows_padded, k, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(g, k, n, device=DEV) / math.sqrt(k)).bfloat16()
+    out = ops.gg_nn(x, w, plan)
+    want = ref.gg_nn(x.float(), w.float(), plan.tile_group)
+    torch.cuda.synchronize()
+    _status_ok()
+    used = (plan.tile_group >= 0).repeat_interleave(128)
+    _close(out[used], want[used], 3e-2, 3e-2)
+
+
+@pytest.mark.parametrize("m,n", [(128, 128), (384, 192), (256, 64)])
+def test_gg_tn(m, n):
+    _ext()
+    torch.manual_seed(6)
+    plan = _plan(seed=m)
+    used = (plan.tile_group >= 0).repeat_interleave(128).unsqueeze(1)
+    a = torch.randn(plan.rows_padded, m, device=DEV, dtype=torch.bfloat16) * used
+    b_ = torch.randn(plan.rows_padded, n, device=DEV, dtype=torch.bfloat16) * used
+    # zero the padding rows of every group (the layout contract)
+    real = torch.zeros(plan.rows_padded, 1, device=DEV, dtype=torch.bool)
+    real[plan.dest.reshape(-1)] = True
+    a = a * real
+    b_ = b_ * real
+    out = ops.gg_tn(a, b_, plan)
+    want = ref.gg_tn(a.float(), b_.float(), plan.tile_group, plan.num_groups)
+    torch.cuda.synchronize()
+    _status_ok()
+    _close(out, want, 0.3, 2e-2)
+
+
+def test_gg_autograd_matches_reference():
+    _ext()
+    torch.manual_seed(7)
+    plan = _plan(seed=11)
+    g, k, n = plan.num_groups, 128, 256
+    real = torch.zeros(plan.rows_padded, 1, device=DEV)
+    real[plan.dest.reshape(-1)] = 1
+    x = (torch.randn(plan.rows_padded, k, device=DEV) * real).bfloat16().requires_grad_(True)
+    w = (torch.randn(g, n, k, device=DEV) / math.sqrt(k)).bfloat16().requires_grad_(True)
+    out = ops.gg_nt(x, w, plan)
+    c = (torch.randn_like(out) * real.bfloat16())
+    gx, gw = torch.autograd.grad(out, [x, w], c)
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    outr = ref.gg_nt(xr, wr, plan.tile_group)
+    gxr, gwr = torch.autograd.grad(outr, [xr, wr], c.float())
+    used = (plan.tile_group >= 0).repeat_interleave(128)
+    _close(gx[used], gxr[used], 5e-2, 3e-2)
+    _close(gw, gwr, 0.5, 3e-2)
+    _status_ok()
+
+
+def test_bmm_nt_and_newton_schulz():
+    _ext()
+    torch.manual_seed(8)
+    a = torch.randn(6, 128, 256, device=DEV, dtype=torch.bfloat16)
+    b_ = torch.randn(6, 192, 256, device=DEV, dtype=torch.bfloat16)
+    d = torch.randn(6, 128, 192, device=DEV, dtype=torch.bfloat16)
+    out = ops.bmm_nt(a, b_, 0.5, d, 2.0)
+    want = 0.5 * a.float() @ b_.float().transpose(1, 2) + 2.0 * d.float()
+    torch.cuda.synchronize()
+    _status_ok()
+    _close(out, want, 0.15, 2e-2)
+    g = torch.randn(5, 384, 128, device=DEV)
+    x = ops.newton_schulz(g)
+    xr = ref.newton_schulz(g.cpu(), compute_dtype=torch.float32)
+    _close(x.cpu(), xr, 6e-2, 6e-2)
+    s = torch.linalg.svdvals(x.float())
+    assert s.max() < 1.3 and s.min() > 0.5
+
+
+def test_adamw_flat_matches_torch():
+    ext = _ext()
+    torch.manual_seed(9)
+    n = 8 * 1000
+    p = torch.randn(n, device=DEV)
+    ref_p = torch.nn.Parameter(p.clone())
+    opt = torch.optim.AdamW([ref_p], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    plow = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+    one = torch.ones(1, device=DEV)
+    for step in range(1, 4):
+        g = torch.randn(n, device=DEV)
+        ref_p.grad = g.clone()
+        opt.step()
+        ext.adamw_flat(p, g.bfloat16().float(), m, v, plow, 1e-2, 0.9, 0.95, 1e-8, 0.1, step, one, one, 1.0, n)
+    _close(p, ref_p.detach(), 2e-3, 2e-3)
+    _close(plow, p, 1e-2, 1e-2)
+    # apply == 0 leaves everything untouched
+    before = p.clone()
+    ext.adamw_flat(p, torch.randn(n, device=DEV), m, v, plow, 1e-2, 0.9, 0.95, 1e-8, 0.1, 5, one, one * 0, 1.0, n)
+    _close(p, before, 0, 0)
+    out = torch.zeros(1, device=DEV)
+    gg = torch.randn(n, device=DEV, dtype=torch.bfloat16)
+    ext.sumsq_accum(gg, 0.5, out)
+    _close(out[0], (gg.float() * 0.5).pow(2).sum(), 1e-1, 1e-3)
+
+
+def test_linear_cross_entropy():
+    _ext()
+    torch.manual_seed(10)
+    t, d, v = 1000, 128, 32000
+    h = (torch.randn(t, d, device=DEV) * 0.5).bfloat16().requires_grad_(True)
+    w = (torch.randn(v, d, device=DEV) * 0.05).bfloat16().requires_grad_(True)
+    labels = torch.randint(0, v, (t,), device=DEV)
+    labels[::7] = -100
+    loss = ops.linear_cross_entropy(h, w, labels, chunk=256)
+    hr, wr = h.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    lossr = F.cross_entropy(hr @ wr.t(), labels, ignore_index=-100)
+    _close(loss, lossr, 2e-2, 1e-2)
+    loss.backward()
+    lossr.backward()
+    _close(h.grad, hr.grad, 1e-4, 5e-2)
+    _close(w.grad, wr.grad, 1e-4, 5e-2)
+
+
+def test_tiny_lm_gpu_matches_cpu():
+    """Whole-model check: bf16 kernels on the GPU against the fp32 CPU path, same weights."""
+    _ext()
+    from uttt_b200.config import named_config
+    from uttt_b200.models import build_model
+    torch.manual_seed(0)
+    cfg = named_config("tiny-uttt-moe", hidden_size=256, num_heads=4, fw_num_heads=2, memory_num_experts=4,
+                       memory_num_active_experts=2, chunk_size=128, window_size=128, memory_lb_loss_alpha=0.0)
+    model = build_model(cfg)
+    ids = torch.randint(0, 1024, (2, 512))
+    out_cpu = model(input_ids=ids, labels=ids)
+    out_cpu.loss.backward()
+    gcpu = {n: p.grad.clone() for n, p in model.named_parameters()}
+    model.zero_grad()
+    gm = build_model(cfg)
+    gm.load_state_dict(model.state_dict())
+    gm = gm.to(DEV).to(torch.bfloat16)
+    out_gpu = gm(input_ids=ids.to(DEV), labels=ids.to(DEV))
+    out_gpu.loss.backward()
+    torch.cuda.synchronize()
+    _status_ok()
+    assert abs(out_gpu.loss.item() - out_cpu.loss.item()) < 0.05
+    for n, p in gm.named_parameters():
+        a, b_ = p.grad.float().cpu(), gcpu[n]
+        cos = F.cosine_similarity(a.flatten(), b_.flatten(), dim=0)
+        assert cos > 0.9 or b_.abs().max() < 1e-6, (n, float(cos))

@@ -97,9 +97,9 @@ def pool_read(q_rows: torch.Tensor, state_w02: torch.Tensor, state_w1: torch.Ten
     w02 = state_w02.reshape(g, state_w02.shape[2], d)
     w1 = state_w1.reshape(g, d, state_w1.shape[3])
     xp = ops.permute_rows(q_rows.reshape(bsz * n, d).to(w02.dtype), plan)
-    y02 = ops.gg_nt(xp, w02, plan.tile_group)
+    y02 = ops.gg_nt(xp, w02, plan)
     hid = ops.swiglu(y02)
-    yp = ops.gg_nt(hid, w1, plan.tile_group)
+    yp = ops.gg_nt(hid, w1, plan)
     y = ops.unpermute_rows(yp, plan, routing.weights)
     return y.view(bsz, n, d)
 
@@ -122,11 +122,11 @@ def pool_raw_grad(k_rows: torch.Tensor, v_rows: torch.Tensor, lr_rows: torch.Ten
     vw = (v_rows.reshape(bsz * n, 1, d).float() * routing.weights.unsqueeze(-1)).to(dt)
     vp = _permute_per_choice(vw, plan)
     lrp = _permute_per_choice(lr_rows.reshape(bsz * n, 1, 3).float().expand(-1, plan.topk, -1), plan)
-    y02 = ops.gg_nt(kp, w02, plan.tile_group)             # [R, 2I] gate|up pre-activations
-    dh = ops.gg_nn(vp, w1, plan.tile_group)               # [R, I]   = (p v) W1
+    y02 = ops.gg_nt(kp, w02, plan)             # [R, 2I] gate|up pre-activations
+    dh = ops.gg_nn(vp, w1, plan)               # [R, I]   = (p v) W1
     dy02_lr, h_lr = ops.fw_write_pointwise(y02, dh, lrp)
-    g02 = ops.gg_tn(dy02_lr, kp, plan.tile_group, g)      # [G, 2I, D]
-    g1 = ops.gg_tn(vp, h_lr, plan.tile_group, g)          # [G, D, I]
+    g02 = ops.gg_tn(dy02_lr, kp, plan)      # [G, 2I, D]
+    g1 = ops.gg_tn(vp, h_lr, plan)          # [G, D, I]
     e = g // bsz
     return g02.view(bsz, e, inter2, d), g1.view(bsz, e, d, inter2 // 2)
 

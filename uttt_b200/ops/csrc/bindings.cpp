@@ -1,0 +1,62 @@
+// Python bindings of the uttt_b200 sm_100a extension.
+#include <torch/extension.h>
+
+namespace uttt {
+std::vector<at::Tensor> rms_norm_fwd(at::Tensor x, c10::optional<at::Tensor> w, double eps);
+std::vector<at::Tensor> rms_norm_bwd(at::Tensor dy, at::Tensor x, c10::optional<at::Tensor> w, at::Tensor rstd);
+at::Tensor rope_fwd(at::Tensor x, at::Tensor table, int64_t offset, bool inverse);
+std::vector<at::Tensor> fw_qk_prep_fwd(at::Tensor x, c10::optional<at::Tensor> scale, c10::optional<at::Tensor> shift,
+                                       at::Tensor table, int64_t heads, int64_t rope_dim, int64_t offset, int64_t l,
+                                       bool silu, int64_t norm);
+std::vector<at::Tensor> fw_qk_prep_bwd(at::Tensor dy, at::Tensor x, c10::optional<at::Tensor> scale,
+                                       c10::optional<at::Tensor> shift, at::Tensor inv, at::Tensor table,
+                                       int64_t heads, int64_t rope_dim, int64_t offset, int64_t l, bool silu,
+                                       int64_t norm);
+at::Tensor swiglu_fwd(at::Tensor y02);
+at::Tensor swiglu_bwd(at::Tensor dh, at::Tensor y02);
+std::vector<at::Tensor> swiglu_bwd_bwd(at::Tensor G, at::Tensor dh, at::Tensor y02);
+std::vector<at::Tensor> fw_write_pw_fwd(at::Tensor y02, at::Tensor dh, at::Tensor lr);
+std::vector<at::Tensor> fw_write_pw_bwd(at::Tensor C, at::Tensor Ch, at::Tensor y02, at::Tensor dh, at::Tensor lr);
+at::Tensor permute_rows(at::Tensor x, at::Tensor dest, int64_t rows_padded);
+at::Tensor unpermute_rows(at::Tensor y, at::Tensor dest, c10::optional<at::Tensor> w);
+std::vector<at::Tensor> unpermute_rows_bwd(at::Tensor dout, at::Tensor y, at::Tensor dest, at::Tensor w);
+void sumsq_accum(at::Tensor g, double scale, at::Tensor out);
+void adamw_flat(at::Tensor p, at::Tensor g, at::Tensor m, at::Tensor v, c10::optional<at::Tensor> plow, double lr,
+                double b1, double b2, double eps, double wd, int64_t step, at::Tensor gscale, at::Tensor apply,
+                double gmul, int64_t decay_hi);
+void ce_fwd_bwd_(at::Tensor logits, at::Tensor labels, at::Tensor loss, int64_t ignore_index);
+int64_t launch_count();
+
+at::Tensor gg_nt(at::Tensor x, at::Tensor w, at::Tensor tile_group);
+at::Tensor gg_nn(at::Tensor x, at::Tensor w, at::Tensor tile_group);
+at::Tensor gg_tn_segments(at::Tensor a, at::Tensor b, at::Tensor offsets, int64_t num_groups, int64_t segments,
+                          at::ScalarType out_dtype, c10::optional<at::Tensor> accumulate_into);
+at::Tensor bmm_nt(at::Tensor a, at::Tensor b, double alpha, c10::optional<at::Tensor> d, double beta);
+at::Tensor gemm_status(at::Tensor like);
+}  // namespace uttt
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  using namespace uttt;
+  m.def("rms_norm_fwd", &rms_norm_fwd);
+  m.def("rms_norm_bwd", &rms_norm_bwd);
+  m.def("rope_fwd", &rope_fwd);
+  m.def("fw_qk_prep_fwd", &fw_qk_prep_fwd);
+  m.def("fw_qk_prep_bwd", &fw_qk_prep_bwd);
+  m.def("swiglu_fwd", &swiglu_fwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("swiglu_bwd_bwd", &swiglu_bwd_bwd);
+  m.def("fw_write_pw_fwd", &fw_write_pw_fwd);
+  m.def("fw_write_pw_bwd", &fw_write_pw_bwd);
+  m.def("permute_rows", &permute_rows);
+  m.def("unpermute_rows", &unpermute_rows);
+  m.def("unpermute_rows_bwd", &unpermute_rows_bwd);
+  m.def("sumsq_accum", &sumsq_accum);
+  m.def("adamw_flat", &adamw_flat);
+  m.def("ce_fwd_bwd_", &ce_fwd_bwd_);
+  m.def("launch_count", &launch_count);
+  m.def("gg_nt", &gg_nt);
+  m.def("gg_nn", &gg_nn);
+  m.def("gg_tn_segments", &gg_tn_segments);
+  m.def("bmm_nt", &bmm_nt);
+  m.def("gemm_status", &gemm_status);
+}

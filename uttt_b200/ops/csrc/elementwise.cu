@@ -1,0 +1,927 @@
+// Memory-bound fused kernels: RMSNorm, rotary, fast-weight q/k preprocessing, SwiGLU and the
+// write's inner-gradient pointwise block (with their backward passes), row permutation for
+// the expert-major layout, fused AdamW on flat shards, and in-place softmax cross-entropy.
+//
+// Conventions: rows are contiguous; one warp (or one CTA) owns a row; all reductions are fp32.
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "common.cuh"
+
+namespace uttt {
+
+unsigned long long g_launch_count = 0;
+
+#define UTTT_DISPATCH_FLOAT(TENSOR, ...)                                            \
+  if ((TENSOR).scalar_type() == at::kBFloat16) {                                    \
+    using T = __nv_bfloat16;                                                        \
+    __VA_ARGS__                                                                     \
+  } else if ((TENSOR).scalar_type() == at::kFloat) {                                \
+    using T = float;                                                                \
+    __VA_ARGS__                                                                     \
+  } else {                                                                          \
+    TORCH_CHECK(false, "expected a bfloat16 or float32 tensor");                    \
+  }
+
+template <typename T> static inline T* ptr(const at::Tensor& t) { return reinterpret_cast<T*>(t.data_ptr()); }
+template <typename T> static inline const T* optr(const c10::optional<at::Tensor>& t) {
+  return t.has_value() && t->defined() ? reinterpret_cast<const T*>(t->data_ptr()) : nullptr;
+}
+static inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+static inline int sm_count() { return at::cuda::getCurrentDeviceProperties()->multiProcessorCount; }
+
+// ------------------------------------------------------------------------------------ RMSNorm
+template <typename T>
+__global__ void rms_norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
+                                    float* __restrict__ rstd, int rows, int d, float eps) {
+  int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  int nwarps = (gridDim.x * blockDim.x) >> 5;
+  int nv = d >> 3;
+  for (int r = warp; r < rows; r += nwarps) {
+    const T* xr = x + (size_t)r * d;
+    float ss = 0.f;
+    for (int v = lane; v < nv; v += 32) {
+      float f[8];
+      Vec8<T>::load(xr + v * 8, f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+    }
+    ss = warp_sum(ss);
+    float rs = rsqrtf(ss / d + eps);
+    if (lane == 0) rstd[r] = rs;
+    T* yr = y + (size_t)r * d;
+    for (int v = lane; v < nv; v += 32) {
+      float f[8], g[8];
+      Vec8<T>::load(xr + v * 8, f);
+      if (w) {
+        Vec8<T>::load(w + v * 8, g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = f[i] * rs * g[i];
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] *= rs;
+      }
+      Vec8<T>::store(yr + v * 8, f);
+    }
+  }
+}
+
+// dx = rstd * (dy*w - xhat * mean(dy*w*xhat)); dw += dy * xhat.  A lane owns vectors lane, lane+32, ...
+// so it can keep its dw columns in registers across rows (d <= 8*32*MAXV).
+template <typename T, int MAXV>
+__global__ void rms_norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
+                                    const float* __restrict__ rstd, T* __restrict__ dx, float* __restrict__ dw,
+                                    int rows, int d) {
+  int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  int nwarps = (gridDim.x * blockDim.x) >> 5;
+  int nv = d >> 3;
+  float acc[MAXV][8];
+#pragma unroll
+  for (int j = 0; j < MAXV; ++j)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[j][i] = 0.f;
+  for (int r = warp; r < rows; r += nwarps) {
+    const T* xr = x + (size_t)r * d;
+    const T* gr = dy + (size_t)r * d;
+    float rs = rstd[r];
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j) {
+      int v = lane + 32 * j;
+      if (v < nv) {
+        float fx[8], fg[8], fw[8];
+        Vec8<T>::load(xr + v * 8, fx);
+        Vec8<T>::load(gr + v * 8, fg);
+        if (w) Vec8<T>::load(w + v * 8, fw);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float xh = fx[i] * rs;
+          float gw = w ? fg[i] * fw[i] : fg[i];
+          dot += gw * xh;
+          acc[j][i] += fg[i] * xh;
+        }
+      }
+    }
+    dot = warp_sum(dot) / d;
+    T* dxr = dx + (size_t)r * d;
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j) {
+      int v = lane + 32 * j;
+      if (v < nv) {
+        float fx[8], fg[8], fw[8], o[8];
+        Vec8<T>::load(xr + v * 8, fx);
+        Vec8<T>::load(gr + v * 8, fg);
+        if (w) Vec8<T>::load(w + v * 8, fw);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float gw = w ? fg[i] * fw[i] : fg[i];
+          o[i] = rs * (gw - fx[i] * rs * dot);
+        }
+        Vec8<T>::store(dxr + v * 8, o);
+      }
+    }
+  }
+  if (dw) {
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j) {
+      int v = lane + 32 * j;
+      if (v < nv) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) atomicAdd(dw + v * 8 + i, acc[j][i]);
+      }
+    }
+  }
+}
+
+std::vector<at::Tensor> rms_norm_fwd(at::Tensor x, c10::optional<at::Tensor> w, double eps) {
+  c10::cuda::CUDAGuard guard(x.device());
+  int rows = x.size(0), d = x.size(1);
+  TORCH_CHECK(x.is_contiguous() && d % 8 == 0);
+  auto y = at::empty_like(x);
+  auto rstd = at::empty({rows}, x.options().dtype(at::kFloat));
+  at::Tensor wc;
+  if (w.has_value() && w->defined()) wc = w->to(x.scalar_type()).contiguous();
+  int blocks = std::min((rows + 7) / 8, sm_count() * 8);
+  UTTT_DISPATCH_FLOAT(x, {
+    rms_norm_fwd_kernel<T><<<std::max(blocks, 1), 256, 0, cur_stream()>>>(
+        ptr<T>(x), wc.defined() ? ptr<T>(wc) : nullptr, ptr<T>(y), ptr<float>(rstd), rows, d, (float)eps);
+  });
+  count_launch();
+  return {y, rstd};
+}
+
+std::vector<at::Tensor> rms_norm_bwd(at::Tensor dy, at::Tensor x, c10::optional<at::Tensor> w, at::Tensor rstd) {
+  c10::cuda::CUDAGuard guard(x.device());
+  int rows = x.size(0), d = x.size(1);
+  TORCH_CHECK(d % 8 == 0 && d <= 8 * 32 * 16, "rms_norm_bwd: hidden size must be a multiple of 8 and <= 4096");
+  auto dx = at::empty_like(x);
+  at::Tensor wc, dw;
+  if (w.has_value() && w->defined()) {
+    wc = w->to(x.scalar_type()).contiguous();
+    dw = at::zeros({d}, x.options().dtype(at::kFloat));
+  } else {
+    dw = at::zeros({1}, x.options().dtype(at::kFloat));
+  }
+  int blocks = std::max(1, std::min((rows + 3) / 4, sm_count() * 4));
+  int nv = d / 8;
+  UTTT_DISPATCH_FLOAT(x, {
+    const T* wp = wc.defined() ? ptr<T>(wc) : nullptr;
+    float* dwp = wc.defined() ? ptr<float>(dw) : nullptr;
+    if (nv <= 32 * 2)
+      rms_norm_bwd_kernel<T, 2><<<blocks, 128, 0, cur_stream()>>>(ptr<T>(dy), ptr<T>(x), wp, ptr<float>(rstd),
+                                                                   ptr<T>(dx), dwp, rows, d);
+    else if (nv <= 32 * 8)
+      rms_norm_bwd_kernel<T, 8><<<blocks, 128, 0, cur_stream()>>>(ptr<T>(dy), ptr<T>(x), wp, ptr<float>(rstd),
+                                                                   ptr<T>(dx), dwp, rows, d);
+    else
+      rms_norm_bwd_kernel<T, 16><<<blocks, 128, 0, cur_stream()>>>(ptr<T>(dy), ptr<T>(x), wp, ptr<float>(rstd),
+                                                                    ptr<T>(dx), dwp, rows, d);
+  });
+  count_launch();
+  return {dx, dw};
+}
+
+// ------------------------------------------------------------------------------------ rotary
+// table: [max_pos, hd/2] float2 (cos, sin).  x: [b, l, nh, hd]; pair (i, i + hd/2).
+template <typename T>
+__global__ void rope_kernel(const T* __restrict__ x, T* __restrict__ y, const float2* __restrict__ table, int l,
+                            int nh, int hd, int offset, float sign, size_t total_pairs) {
+  int half = hd >> 1;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total_pairs;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    int i = idx % half;
+    size_t t = idx / half;      // (b*l + pos) * nh + head
+    int pos = (t / nh) % l;
+    float2 cs = table[(size_t)(offset + pos) * half + i];
+    size_t base = t * hd + i;
+    float a = to_f<T>(x[base]), b = to_f<T>(x[base + half]);
+    float s = cs.y * sign;
+    y[base] = from_f<T>(a * cs.x - b * s);
+    y[base + half] = from_f<T>(b * cs.x + a * s);
+  }
+}
+
+at::Tensor rope_fwd(at::Tensor x, at::Tensor table, int64_t offset, bool inverse) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 4 && x.is_contiguous());
+  int l = x.size(1), nh = x.size(2), hd = x.size(3);
+  TORCH_CHECK(table.scalar_type() == at::kFloat && table.size(0) >= offset + l && table.size(1) == hd / 2);
+  auto y = at::empty_like(x);
+  size_t pairs = x.numel() / 2;
+  int blocks = (int)std::min<size_t>((pairs + 255) / 256, (size_t)sm_count() * 16);
+  UTTT_DISPATCH_FLOAT(x, {
+    rope_kernel<T><<<std::max(blocks, 1), 256, 0, cur_stream()>>>(
+        ptr<T>(x), ptr<T>(y), reinterpret_cast<const float2*>(table.data_ptr()), l, nh, hd, (int)offset,
+        inverse ? -1.f : 1.f, pairs);
+  });
+  count_launch();
+  return y;
+}
+
+// ------------------------------------------------------------------------------------ fast-weight q/k prep
+// One CTA per token row of d = H * D elements:  a = x*scale+shift -> s = silu(a) -> n = s * inv (per head)
+// -> rotary on rope_dim-wide sub-heads.  norm: 0 none, 1 l2 (inv = 1/(||s||+1e-5)), 2 rms.
+template <typename T>
+__global__ void fw_qk_prep_fwd_kernel(const T* __restrict__ x, const T* __restrict__ scale,
+                                      const T* __restrict__ shift, const float2* __restrict__ table,
+                                      T* __restrict__ y, float* __restrict__ inv_out, int d, int heads, int rope_dim,
+                                      int offset, int l, int silu, int norm) {
+  extern __shared__ float sm[];
+  float* s = sm;            // [d]
+  float* invs = sm + d;     // [heads]
+  int row = blockIdx.x;
+  const T* xr = x + (size_t)row * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float a = to_f<T>(xr[i]);
+    if (scale) a = a * to_f<T>(scale[i]) + to_f<T>(shift[i]);
+    s[i] = silu ? siluf_(a) : a;
+  }
+  __syncthreads();
+  int D = d / heads;
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int h = warp; h < heads; h += nw) {
+    float inv = 1.f;
+    if (norm) {
+      float ss = 0.f;
+      for (int i = lane; i < D; i += 32) ss += s[h * D + i] * s[h * D + i];
+      ss = warp_sum(ss);
+      inv = norm == 1 ? 1.f / (sqrtf(ss) + 1e-5f) : rsqrtf(ss / D + 1e-5f);
+    }
+    if (lane == 0) {
+      invs[h] = inv;
+      inv_out[(size_t)row * heads + h] = inv;
+    }
+  }
+  __syncthreads();
+  T* yr = y + (size_t)row * d;
+  int pos = offset + row % l;
+  if (rope_dim > 0) {
+    int half = rope_dim >> 1;
+    for (int p = threadIdx.x; p < d / 2; p += blockDim.x) {
+      int sub = p / half, i = p % half;
+      int i0 = sub * rope_dim + i, i1 = i0 + half;
+      float a = s[i0] * invs[i0 / D], b = s[i1] * invs[i1 / D];
+      float2 cs = table[(size_t)pos * half + i];
+      yr[i0] = from_f<T>(a * cs.x - b * cs.y);
+      yr[i1] = from_f<T>(b * cs.x + a * cs.y);
+    }
+  } else {
+    for (int i = threadIdx.x; i < d; i += blockDim.x) yr[i] = from_f<T>(s[i] * invs[i / D]);
+  }
+}
+
+// Backward of the above.  CTAs stride over rows and keep d(scale), d(shift) partial sums for the
+// columns they own in registers (columns tid, tid+blockDim, ...: at most MAXC per thread).
+template <typename T, int MAXC>
+__global__ void fw_qk_prep_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                                      const T* __restrict__ scale, const T* __restrict__ shift,
+                                      const float* __restrict__ inv_in, const float2* __restrict__ table,
+                                      T* __restrict__ dx, float* __restrict__ dscale, float* __restrict__ dshift,
+                                      int rows, int d, int heads, int rope_dim, int offset, int l, int silu,
+                                      int norm) {
+  extern __shared__ float sm[];
+  float* dn = sm;            // [d] gradient wrt normalised vector
+  float* sv = sm + d;        // [d] silu output s
+  float* dots = sm + 2 * d;  // [heads]
+  int D = d / heads;
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  float acc_s[MAXC], acc_b[MAXC];
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c) acc_s[c] = acc_b[c] = 0.f;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* gr = dy + (size_t)row * d;
+    const T* xr = x + (size_t)row * d;
+    int pos = offset + row % l;
+    if (rope_dim > 0) {
+      int half = rope_dim >> 1;
+      for (int p = threadIdx.x; p < d / 2; p += blockDim.x) {
+        int sub = p / half, i = p % half;
+        int i0 = sub * rope_dim + i, i1 = i0 + half;
+        float ga = to_f<T>(gr[i0]), gb = to_f<T>(gr[i1]);
+        float2 cs = table[(size_t)pos * half + i];
+        dn[i0] = ga * cs.x + gb * cs.y;
+        dn[i1] = gb * cs.x - ga * cs.y;
+      }
+    } else {
+      for (int i = threadIdx.x; i < d; i += blockDim.x) dn[i] = to_f<T>(gr[i]);
+    }
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+      float a = to_f<T>(xr[i]);
+      if (scale) a = a * to_f<T>(scale[i]) + to_f<T>(shift[i]);
+      sv[i] = silu ? siluf_(a) : a;
+    }
+    __syncthreads();
+    if (norm) {
+      for (int h = warp; h < heads; h += nw) {
+        float dot = 0.f;
+        for (int i = lane; i < D; i += 32) dot += dn[h * D + i] * sv[h * D + i];
+        dot = warp_sum(dot);
+        if (lane == 0) dots[h] = dot;
+      }
+      __syncthreads();
+    }
+    T* dxr = dx + (size_t)row * d;
+#pragma unroll
+    for (int c = 0; c < MAXC; ++c) {
+      int i = threadIdx.x + c * blockDim.x;
+      if (i < d) {
+        int h = i / D;
+        float inv = inv_in[(size_t)row * heads + h];
+        float ds;
+        if (norm == 1) {
+          float r = 1.f / inv - 1e-5f;
+          ds = dn[i] * inv - sv[i] * dots[h] * inv * inv / fmaxf(r, 1e-20f);
+        } else if (norm == 2) {
+          ds = dn[i] * inv - sv[i] * dots[h] * inv * inv * inv / D;
+        } else {
+          ds = dn[i];
+        }
+        float xv = to_f<T>(xr[i]);
+        float a = xv;
+        float sc = 1.f;
+        if (scale) {
+          sc = to_f<T>(scale[i]);
+          a = a * sc + to_f<T>(shift[i]);
+        }
+        float da = silu ? ds * dsiluf_(a) : ds;
+        dxr[i] = from_f<T>(da * sc);
+        acc_s[c] += da * xv;
+        acc_b[c] += da;
+      }
+    }
+    __syncthreads();
+  }
+  if (dscale) {
+#pragma unroll
+    for (int c = 0; c < MAXC; ++c) {
+      int i = threadIdx.x + c * blockDim.x;
+      if (i < d) {
+        atomicAdd(dscale + i, acc_s[c]);
+        atomicAdd(dshift + i, acc_b[c]);
+      }
+    }
+  }
+}
+
+std::vector<at::Tensor> fw_qk_prep_fwd(at::Tensor x, c10::optional<at::Tensor> scale,
+                                       c10::optional<at::Tensor> shift, at::Tensor table, int64_t heads,
+                                       int64_t rope_dim, int64_t offset, int64_t l, bool silu, int64_t norm) {
+  c10::cuda::CUDAGuard guard(x.device());
+  int rows = x.size(0), d = x.size(1);
+  TORCH_CHECK(x.is_contiguous() && d % heads == 0);
+  auto y = at::empty_like(x);
+  auto inv = at::empty({rows, heads}, x.options().dtype(at::kFloat));
+  at::Tensor sc, sh;
+  if (scale.has_value() && scale->defined()) {
+    sc = scale->to(x.scalar_type()).contiguous();
+    sh = shift->to(x.scalar_type()).contiguous();
+  }
+  size_t smem = (d + heads) * sizeof(float);
+  UTTT_DISPATCH_FLOAT(x, {
+    fw_qk_prep_fwd_kernel<T><<<rows, 256, smem, cur_stream()>>>(
+        ptr<T>(x), sc.defined() ? ptr<T>(sc) : nullptr, sc.defined() ? ptr<T>(sh) : nullptr,
+        rope_dim > 0 ? reinterpret_cast<const float2*>(table.data_ptr()) : nullptr, ptr<T>(y), ptr<float>(inv), d,
+        (int)heads, (int)rope_dim, (int)offset, (int)l, silu ? 1 : 0, (int)norm);
+  });
+  count_launch();
+  return {y, inv};
+}
+
+std::vector<at::Tensor> fw_qk_prep_bwd(at::Tensor dy, at::Tensor x, c10::optional<at::Tensor> scale,
+                                       c10::optional<at::Tensor> shift, at::Tensor inv, at::Tensor table,
+                                       int64_t heads, int64_t rope_dim, int64_t offset, int64_t l, bool silu,
+                                       int64_t norm) {
+  c10::cuda::CUDAGuard guard(x.device());
+  int rows = x.size(0), d = x.size(1);
+  TORCH_CHECK(d <= 256 * 16, "fw_qk_prep_bwd: hidden size must be <= 4096");
+  auto dx = at::empty_like(x);
+  at::Tensor sc, sh;
+  bool has = scale.has_value() && scale->defined();
+  if (has) {
+    sc = scale->to(x.scalar_type()).contiguous();
+    sh = shift->to(x.scalar_type()).contiguous();
+  }
+  auto dscale = at::zeros({has ? d : 1}, x.options().dtype(at::kFloat));
+  auto dshift = at::zeros({has ? d : 1}, x.options().dtype(at::kFloat));
+  size_t smem = (2 * d + heads) * sizeof(float);
+  int blocks = std::max(1, std::min(rows, sm_count() * 4));
+  UTTT_DISPATCH_FLOAT(x, {
+    auto launch = [&](auto maxc) {
+      constexpr int MAXC = decltype(maxc)::value;
+      fw_qk_prep_bwd_kernel<T, MAXC><<<blocks, 256, smem, cur_stream()>>>(
+          ptr<T>(dy), ptr<T>(x), has ? ptr<T>(sc) : nullptr, has ? ptr<T>(sh) : nullptr, ptr<float>(inv),
+          rope_dim > 0 ? reinterpret_cast<const float2*>(table.data_ptr()) : nullptr, ptr<T>(dx),
+          has ? ptr<float>(dscale) : nullptr, has ? ptr<float>(dshift) : nullptr, rows, d, (int)heads,
+          (int)rope_dim, (int)offset, (int)l, silu ? 1 : 0, (int)norm);
+    };
+    if (d <= 256 * 4) launch(std::integral_constant<int, 4>{});
+    else if (d <= 256 * 8) launch(std::integral_constant<int, 8>{});
+    else launch(std::integral_constant<int, 16>{});
+  });
+  count_launch();
+  return {dx, dscale, dshift};
+}
+
+// ------------------------------------------------------------------------------------ SwiGLU family
+// y02 rows are [gate(I) | up(I)].
+template <typename T>
+__global__ void swiglu_fwd_kernel(const T* __restrict__ y02, T* __restrict__ h, size_t rows, int inter) {
+  size_t nvec = rows * (size_t)(inter >> 3);
+  int vpr = inter >> 3;
+  for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (size_t)gridDim.x * blockDim.x) {
+    size_t r = v / vpr;
+    int c = (v % vpr) * 8;
+    float g[8], u[8], o[8];
+    Vec8<T>::load(y02 + r * 2 * inter + c, g);
+    Vec8<T>::load(y02 + r * 2 * inter + inter + c, u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = siluf_(g[i]) * u[i];
+    Vec8<T>::store(h + r * inter + c, o);
+  }
+}
+
+template <typename T>
+__global__ void swiglu_bwd_kernel(const T* __restrict__ dh, const T* __restrict__ y02, T* __restrict__ dy02,
+                                  size_t rows, int inter) {
+  size_t nvec = rows * (size_t)(inter >> 3);
+  int vpr = inter >> 3;
+  for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (size_t)gridDim.x * blockDim.x) {
+    size_t r = v / vpr;
+    int c = (v % vpr) * 8;
+    float g[8], u[8], d[8], og[8], ou[8];
+    Vec8<T>::load(y02 + r * 2 * inter + c, g);
+    Vec8<T>::load(y02 + r * 2 * inter + inter + c, u);
+    Vec8<T>::load(dh + r * inter + c, d);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      og[i] = d[i] * u[i] * dsiluf_(g[i]);
+      ou[i] = d[i] * siluf_(g[i]);
+    }
+    Vec8<T>::store(dy02 + r * 2 * inter + c, og);
+    Vec8<T>::store(dy02 + r * 2 * inter + inter + c, ou);
+  }
+}
+
+// Gradient of (dh, y02) -> dy02 given cotangent G = [Gg | Gu].
+template <typename T>
+__global__ void swiglu_bwd_bwd_kernel(const T* __restrict__ G, const T* __restrict__ dh, const T* __restrict__ y02,
+                                      T* __restrict__ d_dh, T* __restrict__ d_y02, size_t rows, int inter) {
+  size_t nvec = rows * (size_t)(inter >> 3);
+  int vpr = inter >> 3;
+  for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (size_t)gridDim.x * blockDim.x) {
+    size_t r = v / vpr;
+    int c = (v % vpr) * 8;
+    float g[8], u[8], d[8], gg[8], gu[8], o_dh[8], o_g[8], o_u[8];
+    Vec8<T>::load(y02 + r * 2 * inter + c, g);
+    Vec8<T>::load(y02 + r * 2 * inter + inter + c, u);
+    Vec8<T>::load(dh + r * inter + c, d);
+    Vec8<T>::load(G + r * 2 * inter + c, gg);
+    Vec8<T>::load(G + r * 2 * inter + inter + c, gu);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float s1 = dsiluf_(g[i]), s0 = siluf_(g[i]), s2 = d2siluf_(g[i]);
+      o_dh[i] = gg[i] * u[i] * s1 + gu[i] * s0;
+      o_g[i] = gg[i] * d[i] * u[i] * s2 + gu[i] * d[i] * s1;
+      o_u[i] = gg[i] * d[i] * s1;
+    }
+    Vec8<T>::store(d_dh + r * inter + c, o_dh);
+    Vec8<T>::store(d_y02 + r * 2 * inter + c, o_g);
+    Vec8<T>::store(d_y02 + r * 2 * inter + inter + c, o_u);
+  }
+}
+
+static inline int ew_blocks(size_t n) {
+  return (int)std::max<size_t>(1, std::min<size_t>((n + 255) / 256, (size_t)sm_count() * 16));
+}
+
+at::Tensor swiglu_fwd(at::Tensor y02) {
+  c10::cuda::CUDAGuard guard(y02.device());
+  size_t rows = y02.size(0);
+  int inter = y02.size(1) / 2;
+  TORCH_CHECK(y02.is_contiguous() && inter % 8 == 0);
+  auto h = at::empty({(int64_t)rows, inter}, y02.options());
+  UTTT_DISPATCH_FLOAT(y02, {
+    swiglu_fwd_kernel<T><<<ew_blocks(rows * inter / 8), 256, 0, cur_stream()>>>(ptr<T>(y02), ptr<T>(h), rows, inter);
+  });
+  count_launch();
+  return h;
+}
+
+at::Tensor swiglu_bwd(at::Tensor dh, at::Tensor y02) {
+  c10::cuda::CUDAGuard guard(y02.device());
+  size_t rows = y02.size(0);
+  int inter = y02.size(1) / 2;
+  auto out = at::empty_like(y02);
+  UTTT_DISPATCH_FLOAT(y02, {
+    swiglu_bwd_kernel<T><<<ew_blocks(rows * inter / 8), 256, 0, cur_stream()>>>(ptr<T>(dh), ptr<T>(y02), ptr<T>(out),
+                                                                               rows, inter);
+  });
+  count_launch();
+  return out;
+}
+
+std::vector<at::Tensor> swiglu_bwd_bwd(at::Tensor G, at::Tensor dh, at::Tensor y02) {
+  c10::cuda::CUDAGuard guard(y02.device());
+  size_t rows = y02.size(0);
+  int inter = y02.size(1) / 2;
+  auto d_dh = at::empty_like(dh);
+  auto d_y02 = at::empty_like(y02);
+  UTTT_DISPATCH_FLOAT(y02, {
+    swiglu_bwd_bwd_kernel<T><<<ew_blocks(rows * inter / 8), 256, 0, cur_stream()>>>(
+        ptr<T>(G), ptr<T>(dh), ptr<T>(y02), ptr<T>(d_dh), ptr<T>(d_y02), rows, inter);
+  });
+  count_launch();
+  return {d_dh, d_y02};
+}
+
+// Write pointwise block.  Inputs y02 [R,2I], dh [R,I], lr [R,3] fp32.
+//   dy02_lr = [dh*u*silu'(g)*lr0 | dh*silu(g)*lr2],  h_lr = silu(g)*u*lr1
+template <typename T>
+__global__ void fw_write_pw_fwd_kernel(const T* __restrict__ y02, const T* __restrict__ dh,
+                                       const float* __restrict__ lr, T* __restrict__ dy02, T* __restrict__ hlr,
+                                       size_t rows, int inter) {
+  size_t nvec = rows * (size_t)(inter >> 3);
+  int vpr = inter >> 3;
+  for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (size_t)gridDim.x * blockDim.x) {
+    size_t r = v / vpr;
+    int c = (v % vpr) * 8;
+    float lr0 = lr[r * 3], lr1 = lr[r * 3 + 1], lr2 = lr[r * 3 + 2];
+    float g[8], u[8], d[8], og[8], ou[8], oh[8];
+    Vec8<T>::load(y02 + r * 2 * inter + c, g);
+    Vec8<T>::load(y02 + r * 2 * inter + inter + c, u);
+    Vec8<T>::load(dh + r * inter + c, d);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float s0 = siluf_(g[i]);
+      og[i] = d[i] * u[i] * dsiluf_(g[i]) * lr0;
+      ou[i] = d[i] * s0 * lr2;
+      oh[i] = s0 * u[i] * lr1;
+    }
+    Vec8<T>::store(dy02 + r * 2 * inter + c, og);
+    Vec8<T>::store(dy02 + r * 2 * inter + inter + c, ou);
+    Vec8<T>::store(hlr + r * inter + c, oh);
+  }
+}
+
+// Backward: cotangents Cg|Cu (for dy02_lr) and Ch (for h_lr).  One warp per row (row sums for d_lr).
+template <typename T>
+__global__ void fw_write_pw_bwd_kernel(const T* __restrict__ C, const T* __restrict__ Ch, const T* __restrict__ y02,
+                                       const T* __restrict__ dh, const float* __restrict__ lr,
+                                       T* __restrict__ d_y02, T* __restrict__ d_dh, float* __restrict__ d_lr,
+                                       size_t rows, int inter) {
+  size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  int lane = threadIdx.x & 31;
+  size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
+  int vpr = inter >> 3;
+  for (size_t r = warp; r < rows; r += nwarps) {
+    float lr0 = lr[r * 3], lr1 = lr[r * 3 + 1], lr2 = lr[r * 3 + 2];
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f;
+    for (int v = lane; v < vpr; v += 32) {
+      int c = v * 8;
+      float g[8], u[8], d[8], cg[8], cu[8], ch[8], o_g[8], o_u[8], o_d[8];
+      Vec8<T>::load(y02 + r * 2 * inter + c, g);
+      Vec8<T>::load(y02 + r * 2 * inter + inter + c, u);
+      Vec8<T>::load(dh + r * inter + c, d);
+      Vec8<T>::load(C + r * 2 * inter + c, cg);
+      Vec8<T>::load(C + r * 2 * inter + inter + c, cu);
+      Vec8<T>::load(Ch + r * inter + c, ch);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float s0 = siluf_(g[i]), s1 = dsiluf_(g[i]), s2 = d2siluf_(g[i]);
+        o_d[i] = cg[i] * lr0 * u[i] * s1 + cu[i] * lr2 * s0;
+        o_g[i] = cg[i] * lr0 * d[i] * u[i] * s2 + cu[i] * lr2 * d[i] * s1 + ch[i] * lr1 * u[i] * s1;
+        o_u[i] = cg[i] * lr0 * d[i] * s1 + ch[i] * lr1 * s0;
+        a0 += cg[i] * d[i] * u[i] * s1;
+        a2 += cu[i] * d[i] * s0;
+        a1 += ch[i] * s0 * u[i];
+      }
+      Vec8<T>::store(d_y02 + r * 2 * inter + c, o_g);
+      Vec8<T>::store(d_y02 + r * 2 * inter + inter + c, o_u);
+      Vec8<T>::store(d_dh + r * inter + c, o_d);
+    }
+    a0 = warp_sum(a0);
+    a1 = warp_sum(a1);
+    a2 = warp_sum(a2);
+    if (lane == 0) {
+      d_lr[r * 3] = a0;
+      d_lr[r * 3 + 1] = a1;
+      d_lr[r * 3 + 2] = a2;
+    }
+  }
+}
+
+std::vector<at::Tensor> fw_write_pw_fwd(at::Tensor y02, at::Tensor dh, at::Tensor lr) {
+  c10::cuda::CUDAGuard guard(y02.device());
+  size_t rows = y02.size(0);
+  int inter = y02.size(1) / 2;
+  TORCH_CHECK(lr.scalar_type() == at::kFloat && lr.size(0) == (int64_t)rows && lr.size(1) == 3 && inter % 8 == 0);
+  auto dy02 = at::empty_like(y02);
+  auto hlr = at::empty_like(dh);
+  UTTT_DISPATCH_FLOAT(y02, {
+    fw_write_pw_fwd_kernel<T><<<ew_blocks(rows * inter / 8), 256, 0, cur_stream()>>>(
+        ptr<T>(y02), ptr<T>(dh), ptr<float>(lr), ptr<T>(dy02), ptr<T>(hlr), rows, inter);
+  });
+  count_launch();
+  return {dy02, hlr};
+}
+
+std::vector<at::Tensor> fw_write_pw_bwd(at::Tensor C, at::Tensor Ch, at::Tensor y02, at::Tensor dh, at::Tensor lr) {
+  c10::cuda::CUDAGuard guard(y02.device());
+  size_t rows = y02.size(0);
+  int inter = y02.size(1) / 2;
+  auto d_y02 = at::empty_like(y02);
+  auto d_dh = at::empty_like(dh);
+  auto d_lr = at::empty_like(lr);
+  int blocks = (int)std::max<size_t>(1, std::min<size_t>((rows + 7) / 8, (size_t)sm_count() * 8));
+  UTTT_DISPATCH_FLOAT(y02, {
+    fw_write_pw_bwd_kernel<T><<<blocks, 256, 0, cur_stream()>>>(ptr<T>(C), ptr<T>(Ch), ptr<T>(y02), ptr<T>(dh),
+                                                               ptr<float>(lr), ptr<T>(d_y02), ptr<T>(d_dh),
+                                                               ptr<float>(d_lr), rows, inter);
+  });
+  count_launch();
+  return {d_y02, d_dh, d_lr};
+}
+
+// ------------------------------------------------------------------------------------ row permutation
+// out[dest[i, j]] = x[i] (one warp per (i, j)); out is zero-filled first so padding rows are zero.
+template <typename T>
+__global__ void permute_rows_kernel(const T* __restrict__ x, const int64_t* __restrict__ dest, T* __restrict__ out,
+                                    size_t n_copies, int k, int d) {
+  size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  int lane = threadIdx.x & 31;
+  size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
+  int nv = d >> 3;
+  for (size_t c = warp; c < n_copies; c += nwarps) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + (c / k) * d);
+    uint4* dst = reinterpret_cast<uint4*>(out + (size_t)dest[c] * d);
+    constexpr int per = 16 / sizeof(T);   // elements per uint4
+    for (int v = lane; v < d / per; v += 32) dst[v] = src[v];
+  }
+}
+
+// out[i] = sum_j w[i,j] * y[dest[i,j]]
+template <typename T>
+__global__ void unpermute_rows_kernel(const T* __restrict__ y, const int64_t* __restrict__ dest,
+                                      const float* __restrict__ w, T* __restrict__ out, size_t rows, int k, int d) {
+  size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  int lane = threadIdx.x & 31;
+  size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
+  int nv = d >> 3;
+  for (size_t r = warp; r < rows; r += nwarps) {
+    for (int v = lane; v < nv; v += 32) {
+      float acc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+      for (int j = 0; j < k; ++j) {
+        float f[8];
+        Vec8<T>::load(y + (size_t)dest[r * k + j] * d + v * 8, f);
+        float wj = w ? w[r * k + j] : 1.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += wj * f[i];
+      }
+      Vec8<T>::store(out + r * d + v * 8, acc);
+    }
+  }
+}
+
+// dy[dest[i,j]] = w[i,j] * dout[i];  dw[i,j] = <y[dest[i,j]], dout[i]>
+template <typename T>
+__global__ void unpermute_rows_bwd_kernel(const T* __restrict__ dout, const T* __restrict__ y,
+                                          const int64_t* __restrict__ dest, const float* __restrict__ w,
+                                          T* __restrict__ dy, float* __restrict__ dw, size_t n_copies, int k, int d) {
+  size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  int lane = threadIdx.x & 31;
+  size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
+  int nv = d >> 3;
+  for (size_t c = warp; c < n_copies; c += nwarps) {
+    size_t r = c / k;
+    size_t dr = (size_t)dest[c];
+    float wj = w[c];
+    float dot = 0.f;
+    for (int v = lane; v < nv; v += 32) {
+      float g[8], f[8], o[8];
+      Vec8<T>::load(dout + r * d + v * 8, g);
+      Vec8<T>::load(y + dr * d + v * 8, f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        dot += g[i] * f[i];
+        o[i] = wj * g[i];
+      }
+      Vec8<T>::store(dy + dr * d + v * 8, o);
+    }
+    dot = warp_sum(dot);
+    if (lane == 0) dw[c] = dot;
+  }
+}
+
+at::Tensor permute_rows(at::Tensor x, at::Tensor dest, int64_t rows_padded) {
+  c10::cuda::CUDAGuard guard(x.device());
+  int d = x.size(1);
+  int k = dest.size(1);
+  TORCH_CHECK(x.is_contiguous() && dest.is_contiguous() && dest.scalar_type() == at::kLong && d % 8 == 0);
+  auto out = at::zeros({rows_padded, d}, x.options());
+  size_t n = (size_t)dest.numel();
+  int blocks = (int)std::max<size_t>(1, std::min<size_t>((n + 7) / 8, (size_t)sm_count() * 16));
+  UTTT_DISPATCH_FLOAT(x, {
+    permute_rows_kernel<T><<<blocks, 256, 0, cur_stream()>>>(ptr<T>(x), ptr<int64_t>(dest), ptr<T>(out), n, k, d);
+  });
+  count_launch(2);
+  return out;
+}
+
+at::Tensor unpermute_rows(at::Tensor y, at::Tensor dest, c10::optional<at::Tensor> w) {
+  c10::cuda::CUDAGuard guard(y.device());
+  int d = y.size(1);
+  size_t rows = dest.size(0);
+  int k = dest.size(1);
+  TORCH_CHECK(y.is_contiguous() && d % 8 == 0);
+  at::Tensor wf;
+  if (w.has_value() && w->defined()) wf = w->to(at::kFloat).contiguous();
+  auto out = at::empty({(int64_t)rows, d}, y.options());
+  int blocks = (int)std::max<size_t>(1, std::min<size_t>((rows + 7) / 8, (size_t)sm_count() * 16));
+  UTTT_DISPATCH_FLOAT(y, {
+    unpermute_rows_kernel<T><<<blocks, 256, 0, cur_stream()>>>(ptr<T>(y), ptr<int64_t>(dest),
+                                                              wf.defined() ? ptr<float>(wf) : nullptr, ptr<T>(out),
+                                                              rows, k, d);
+  });
+  count_launch();
+  return out;
+}
+
+std::vector<at::Tensor> unpermute_rows_bwd(at::Tensor dout, at::Tensor y, at::Tensor dest, at::Tensor w) {
+  c10::cuda::CUDAGuard guard(y.device());
+  int d = y.size(1);
+  int k = dest.size(1);
+  size_t n = (size_t)dest.numel();
+  auto wf = w.to(at::kFloat).contiguous();
+  auto dy = at::zeros_like(y);
+  auto dw = at::empty({dest.size(0), k}, y.options().dtype(at::kFloat));
+  int blocks = (int)std::max<size_t>(1, std::min<size_t>((n + 7) / 8, (size_t)sm_count() * 16));
+  UTTT_DISPATCH_FLOAT(y, {
+    unpermute_rows_bwd_kernel<T><<<blocks, 256, 0, cur_stream()>>>(ptr<T>(dout), ptr<T>(y), ptr<int64_t>(dest),
+                                                                  ptr<float>(wf), ptr<T>(dy), ptr<float>(dw), n, k, d);
+  });
+  count_launch(2);
+  return {dy, dw};
+}
+
+// ------------------------------------------------------------------------------------ optimizer
+// sum of squares of (g * scale) accumulated into *out (fp32).
+template <typename T>
+__global__ void sumsq_kernel(const T* __restrict__ g, size_t n, float scale, float* __restrict__ out) {
+  float acc = 0.f;
+  size_t nv = n >> 3;
+  for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < nv; v += (size_t)gridDim.x * blockDim.x) {
+    float f[8];
+    Vec8<T>::load(g + v * 8, f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc += f[i] * f[i];
+  }
+  acc = warp_sum(acc);
+  __shared__ float red[32];
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) red[warp] = acc;
+  __syncthreads();
+  if (warp == 0) {
+    acc = lane < (blockDim.x >> 5) ? red[lane] : 0.f;
+    acc = warp_sum(acc);
+    if (lane == 0) atomicAdd(out, acc * scale * scale);
+  }
+}
+
+void sumsq_accum(at::Tensor g, double scale, at::Tensor out) {
+  c10::cuda::CUDAGuard guard(g.device());
+  TORCH_CHECK(g.is_contiguous() && g.numel() % 8 == 0 && out.scalar_type() == at::kFloat);
+  size_t n = g.numel();
+  UTTT_DISPATCH_FLOAT(g, {
+    sumsq_kernel<T><<<ew_blocks(n / 8), 256, 0, cur_stream()>>>(ptr<T>(g), n, (float)scale, ptr<float>(out));
+  });
+  count_launch();
+}
+
+// AdamW on a flat fp32 shard.  g may be bf16 or fp32; gscale[0] (device scalar) multiplies the gradient
+// (clip factor x 1/world); apply[0] == 0 turns the step into a no-op (non-finite gradient norm).
+// Elements [0, decay_hi) get weight decay.  Writes the low-precision compute copy when plow != nullptr.
+template <typename G, typename P>
+__global__ void adamw_flat_kernel(float* __restrict__ p, const G* __restrict__ g, float* __restrict__ m,
+                                  float* __restrict__ v, P* __restrict__ plow, size_t n, float lr, float b1,
+                                  float b2, float eps, float wd, float bc1, float bc2_sqrt,
+                                  const float* __restrict__ gscale, const float* __restrict__ apply, float gmul,
+                                  size_t decay_hi) {
+  if (apply[0] == 0.f) return;
+  float gs = gscale[0] * gmul;
+  size_t nv = n >> 3;
+  for (size_t vi = (size_t)blockIdx.x * blockDim.x + threadIdx.x; vi < nv; vi += (size_t)gridDim.x * blockDim.x) {
+    size_t base = vi * 8;
+    float fp[8], fg[8], fm[8], fv[8];
+    Vec8<float>::load(p + base, fp);
+    Vec8<G>::load(g + base, fg);
+    Vec8<float>::load(m + base, fm);
+    Vec8<float>::load(v + base, fv);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float gi = fg[i] * gs;
+      fm[i] = b1 * fm[i] + (1.f - b1) * gi;
+      fv[i] = b2 * fv[i] + (1.f - b2) * gi * gi;
+      float decay = (base + i) < decay_hi ? (1.f - lr * wd) : 1.f;
+      float denom = sqrtf(fv[i]) / bc2_sqrt + eps;
+      fp[i] = fp[i] * decay - (lr / bc1) * fm[i] / denom;
+    }
+    Vec8<float>::store(p + base, fp);
+    Vec8<float>::store(m + base, fm);
+    Vec8<float>::store(v + base, fv);
+    if (plow) Vec8<P>::store(plow + base, fp);
+  }
+}
+
+void adamw_flat(at::Tensor p, at::Tensor g, at::Tensor m, at::Tensor v, c10::optional<at::Tensor> plow, double lr,
+                double b1, double b2, double eps, double wd, int64_t step, at::Tensor gscale, at::Tensor apply,
+                double gmul, int64_t decay_hi) {
+  c10::cuda::CUDAGuard guard(p.device());
+  size_t n = p.numel();
+  TORCH_CHECK(n % 8 == 0 && p.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat);
+  TORCH_CHECK(gscale.scalar_type() == at::kFloat && apply.scalar_type() == at::kFloat);
+  float bc1 = 1.f - (float)std::pow(b1, (double)step);
+  float bc2s = (float)std::sqrt(1.0 - std::pow(b2, (double)step));
+  bool has_low = plow.has_value() && plow->defined();
+  auto launch = [&](auto gtag, auto ptag) {
+    using G = decltype(gtag);
+    using P = decltype(ptag);
+    adamw_flat_kernel<G, P><<<ew_blocks(n / 8), 256, 0, cur_stream()>>>(
+        ptr<float>(p), ptr<G>(g), ptr<float>(m), ptr<float>(v), has_low ? ptr<P>(*plow) : nullptr, n, (float)lr,
+        (float)b1, (float)b2, (float)eps, (float)wd, bc1, bc2s, ptr<float>(gscale), ptr<float>(apply), (float)gmul,
+        (size_t)decay_hi);
+  };
+  bool g16 = g.scalar_type() == at::kBFloat16;
+  bool p16 = has_low && plow->scalar_type() == at::kBFloat16;
+  if (g16 && p16) launch(__nv_bfloat16{}, __nv_bfloat16{});
+  else if (g16) launch(__nv_bfloat16{}, float{});
+  else if (p16) launch(float{}, __nv_bfloat16{});
+  else launch(float{}, float{});
+  count_launch();
+}
+
+// ------------------------------------------------------------------------------------ cross-entropy
+// In place on a chunk of logits [T, V]: logits <- softmax(logits) - onehot(label) (zero rows for ignored
+// labels); loss[0] += sum of -log softmax[label].  One CTA per row, online max/sum, two passes.
+template <typename T>
+__global__ void ce_fwd_bwd_kernel(T* __restrict__ logits, const int64_t* __restrict__ labels,
+                                  float* __restrict__ loss, int V, int64_t ignore_index) {
+  int row = blockIdx.x;
+  T* lr = logits + (size_t)row * V;
+  int64_t label = labels[row];
+  float mx = -INFINITY, sum = 0.f;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    float x = to_f<T>(lr[i]);
+    if (x > mx) {
+      sum = sum * __expf(mx - x) + 1.f;
+      mx = x;
+    } else {
+      sum += __expf(x - mx);
+    }
+  }
+  __shared__ float smx[32], ssum[32];
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float wm = warp_max(mx);
+  sum *= __expf(mx - wm);
+  sum = warp_sum(sum);
+  if (lane == 0) {
+    smx[warp] = wm;
+    ssum[warp] = sum;
+  }
+  __syncthreads();
+  int nw = blockDim.x >> 5;
+  float gm = -INFINITY;
+  for (int i = 0; i < nw; ++i) gm = fmaxf(gm, smx[i]);
+  float gs = 0.f;
+  for (int i = 0; i < nw; ++i) gs += ssum[i] * __expf(smx[i] - gm);
+  bool ignored = label == ignore_index;
+  if (threadIdx.x == 0 && !ignored) {
+    float xl = to_f<T>(lr[label]);
+    atomicAdd(loss, -(xl - gm - __logf(gs)));
+  }
+  __syncthreads();
+  float inv = 1.f / gs;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    float pr = ignored ? 0.f : __expf(to_f<T>(lr[i]) - gm) * inv - (i == label ? 1.f : 0.f);
+    lr[i] = from_f<T>(pr);
+  }
+}
+
+void ce_fwd_bwd_(at::Tensor logits, at::Tensor labels, at::Tensor loss, int64_t ignore_index) {
+  c10::cuda::CUDAGuard guard(logits.device());
+  TORCH_CHECK(logits.is_contiguous() && labels.scalar_type() == at::kLong && loss.scalar_type() == at::kFloat);
+  int rows = logits.size(0), V = logits.size(1);
+  if (rows == 0) return;
+  UTTT_DISPATCH_FLOAT(logits, {
+    ce_fwd_bwd_kernel<T><<<rows, 512, 0, cur_stream()>>>(ptr<T>(logits), ptr<int64_t>(labels), ptr<float>(loss), V,
+                                                        ignore_index);
+  });
+  count_launch();
+}
+
+int64_t launch_count() { return (int64_t)g_launch_count; }
+
+}  // namespace uttt

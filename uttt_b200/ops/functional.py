@@ -82,12 +82,29 @@ def layer_norm(x, weight, bias, eps: float = 1e-5):
 
 
 # =========================================================================== rotary
+_ROPE_TABLES = {}
+
+
+def rope_table(theta: float, dim: int, length: int, device) -> torch.Tensor:
+    """[max_len, dim/2, 2] fp32 (cos, sin) table, angles formed in fp64; cached per (theta, dim, device)."""
+    key = (float(theta), int(dim), str(device))
+    tab = _ROPE_TABLES.get(key)
+    if tab is None or tab.shape[0] < length:
+        n = max(length, 4096, 0 if tab is None else 2 * tab.shape[0])
+        inv = 1.0 / (float(theta) ** (torch.arange(0, dim, 2, dtype=torch.float64) / dim))
+        ang = torch.arange(n, dtype=torch.float64)[:, None] * inv[None, :]
+        tab = torch.stack([ang.cos(), ang.sin()], dim=-1).float().to(device).contiguous()
+        _ROPE_TABLES[key] = tab
+    return tab
+
+
 class _Rope(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, offset, theta, inverse):
         ext = cuda_ext(x)
         ctx.args = (offset, theta, inverse)
-        return ext.rope_fwd(x.contiguous(), int(offset), float(theta), bool(inverse))
+        table = rope_table(theta, x.shape[-1], offset + x.shape[1], x.device)
+        return ext.rope_fwd(x.contiguous(), table, int(offset), bool(inverse))
 
     @staticmethod
     def backward(ctx, dy):
@@ -108,7 +125,8 @@ class _FwQkPrep(torch.autograd.Function):
         ext = cuda_ext(x)
         b, l, d = x.shape
         xc = x.contiguous()
-        y, inv = ext.fw_qk_prep_fwd(xc.view(b * l, d), scale, shift, fw_heads, rope_dim, float(theta), int(offset),
+        table = rope_table(theta, rope_dim, offset + l, x.device) if rope_dim > 0 else x.new_zeros(1, dtype=torch.float32)
+        y, inv = ext.fw_qk_prep_fwd(xc.view(b * l, d), scale, shift, table, fw_heads, rope_dim, int(offset),
                                     int(l), bool(silu), {None: 0, "l2": 1, "rms": 2}[norm])
         ctx.save_for_backward(xc, scale, shift, inv)
         ctx.args = (fw_heads, rope_dim, theta, offset, silu, norm)
@@ -120,8 +138,9 @@ class _FwQkPrep(torch.autograd.Function):
         fw_heads, rope_dim, theta, offset, silu, norm = ctx.args
         ext = cuda_ext(xc)
         b, l, d = xc.shape
+        table = rope_table(theta, rope_dim, offset + l, xc.device) if rope_dim > 0 else xc.new_zeros(1, dtype=torch.float32)
         dx, dscale, dshift = ext.fw_qk_prep_bwd(dy.contiguous().view(b * l, d), xc.view(b * l, d), scale, shift, inv,
-                                                fw_heads, rope_dim, float(theta), int(offset), int(l), bool(silu),
+                                                table, fw_heads, rope_dim, int(offset), int(l), bool(silu),
                                                 {None: 0, "l2": 1, "rms": 2}[norm])
         ds = None if scale is None else dscale.to(scale.dtype)
         dsh = None if shift is None else dshift.to(shift.dtype)
@@ -264,22 +283,27 @@ def _gg_kernel_ok(*tensors) -> bool:
     return all(t.dtype == torch.bfloat16 for t in tensors) and _kernel("gg_nt", *tensors) is not None
 
 
+def _gg_dims_ok(k: int, n: int) -> bool:
+    return k % 64 == 0 and n % 64 == 0
+
+
 class _GGNT(torch.autograd.Function):
     """out[r] = x[r] @ w[g(r)]^T."""
 
     @staticmethod
-    def forward(ctx, x, w, tile_group):
-        ctx.save_for_backward(x, w, tile_group)
-        return cuda_ext(x).gg_nt(x.contiguous(), w.contiguous(), tile_group)
+    def forward(ctx, x, w, plan):
+        ctx.save_for_backward(x, w)
+        ctx.plan = plan
+        return cuda_ext(x).gg_nt(x.contiguous(), w.contiguous(), plan.tile_group)
 
     @staticmethod
     def backward(ctx, dy):
-        x, w, tile_group = ctx.saved_tensors
+        x, w = ctx.saved_tensors
         dx = dw = None
         if ctx.needs_input_grad[0]:
-            dx = gg_nn(dy, w, tile_group)
+            dx = gg_nn(dy, w, ctx.plan)
         if ctx.needs_input_grad[1]:
-            dw = gg_tn(dy, x, tile_group, w.shape[0], w.dtype)
+            dw = gg_tn(dy, x, ctx.plan, w.dtype)
         return dx, dw, None
 
 
@@ -287,18 +311,19 @@ class _GGNN(torch.autograd.Function):
     """out[r] = x[r] @ w[g(r)]."""
 
     @staticmethod
-    def forward(ctx, x, w, tile_group):
-        ctx.save_for_backward(x, w, tile_group)
-        return cuda_ext(x).gg_nn(x.contiguous(), w.contiguous(), tile_group)
+    def forward(ctx, x, w, plan):
+        ctx.save_for_backward(x, w)
+        ctx.plan = plan
+        return cuda_ext(x).gg_nn(x.contiguous(), w.contiguous(), plan.tile_group)
 
     @staticmethod
     def backward(ctx, dy):
-        x, w, tile_group = ctx.saved_tensors
+        x, w = ctx.saved_tensors
         dx = dw = None
         if ctx.needs_input_grad[0]:
-            dx = gg_nt(dy, w, tile_group)
+            dx = gg_nt(dy, w, ctx.plan)
         if ctx.needs_input_grad[1]:
-            dw = gg_tn(x, dy, tile_group, w.shape[0], w.dtype)
+            dw = gg_tn(x, dy, ctx.plan, w.dtype)
         return dx, dw, None
 
 
@@ -306,38 +331,43 @@ class _GGTN(torch.autograd.Function):
     """out[g] = sum over rows of group g of a[r]^T b[r]."""
 
     @staticmethod
-    def forward(ctx, a, b, tile_group, num_groups, out_dtype):
-        ctx.save_for_backward(a, b, tile_group)
-        return cuda_ext(a).gg_tn(a.contiguous(), b.contiguous(), tile_group, int(num_groups), out_dtype)
+    def forward(ctx, a, b, plan, out_dtype):
+        ctx.save_for_backward(a, b)
+        ctx.plan = plan
+        return cuda_ext(a).gg_tn_segments(a.contiguous(), b.contiguous(), plan.offsets, plan.num_groups, 1,
+                                          out_dtype, None)
 
     @staticmethod
     def backward(ctx, dg):
-        a, b, tile_group = ctx.saved_tensors
+        a, b = ctx.saved_tensors
         da = db = None
         dgl = dg.to(a.dtype).contiguous()
         if ctx.needs_input_grad[0]:
-            da = gg_nt(b, dgl, tile_group)
+            da = gg_nt(b, dgl, ctx.plan)
         if ctx.needs_input_grad[1]:
-            db = gg_nn(a, dgl, tile_group)
-        return da, db, None, None, None
+            db = gg_nn(a, dgl, ctx.plan)
+        return da, db, None, None
 
 
-def gg_nt(x, w, tile_group):
-    if _gg_kernel_ok(x, w):
-        return _GGNT.apply(x, w, tile_group)
-    return ref.gg_nt(x, w, tile_group)
+def gg_nt(x, w, plan: GroupPlan):
+    """out[r] = x[r] @ w[group(r)]^T;  x [R, K], w [G, N, K] -> [R, N]."""
+    if _gg_kernel_ok(x, w) and _gg_dims_ok(x.shape[1], w.shape[1]):
+        return _GGNT.apply(x, w, plan)
+    return ref.gg_nt(x, w, plan.tile_group)
 
 
-def gg_nn(x, w, tile_group):
-    if _gg_kernel_ok(x, w):
-        return _GGNN.apply(x, w, tile_group)
-    return ref.gg_nn(x, w, tile_group)
+def gg_nn(x, w, plan: GroupPlan):
+    """out[r] = x[r] @ w[group(r)];  x [R, K], w [G, K, N] -> [R, N]."""
+    if _gg_kernel_ok(x, w) and _gg_dims_ok(x.shape[1], w.shape[2]):
+        return _GGNN.apply(x, w, plan)
+    return ref.gg_nn(x, w, plan.tile_group)
 
 
-def gg_tn(a, b, tile_group, num_groups: int, out_dtype: torch.dtype = torch.float32):
-    if _gg_kernel_ok(a, b):
-        return _GGTN.apply(a, b, tile_group, num_groups, out_dtype)
-    return ref.gg_tn(a, b, tile_group, num_groups, out_dtype)
+def gg_tn(a, b, plan: GroupPlan, out_dtype: torch.dtype = torch.float32):
+    """out[g] = sum_{r in group g} a[r]^T b[r];  a [R, M], b [R, N] -> [G, M, N] (fp32 accumulation)."""
+    if _gg_kernel_ok(a, b) and a.shape[1] % 128 == 0 and b.shape[1] % 64 == 0:
+        return _GGTN.apply(a, b, plan, out_dtype)
+    return ref.gg_tn(a, b, plan.tile_group, plan.num_groups, out_dtype)
 
 
 # --------------------------------------------------------------------------- fast-weight pointwise
