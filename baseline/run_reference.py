@@ -1,8 +1,162 @@
-"""Reference arm of the benchmark: the unmodified reference code from ``baseline/_ref``."""
+"""Reference arm of the benchmark.
+
+Runs the *unmodified* reference implementation (a verbatim copy of the reference's
+``uttt_llm`` tree under ``baseline/_ref``; the reference ships no ``setup.py`` / ``pyproject.toml``,
+so ``pip install --target`` cannot install it and the tree is copied instead) on the same metric
+and shape as ``bench.py``: the reference's own ``RecurrentLactRefMoeGlobalV45ForCausalLM`` built
+from its shipped 760M JSON with the named-shape overrides, its own Triton / flash-attn / fla
+kernels, FSDP2 with the settings of its ``apply_fsdp`` (one unit per block plus the root, bf16
+parameters, fp32 reduction, no resharding after forward), fused AdamW and gradient clipping as in
+its job file.  None of this repository's models, kernels or engine is on that path.
+
+The reference trainer module itself (``flame.train``) cannot be imported on this image: it needs
+``torchtitan.config_manager`` from torchtitan 0.1.0, which the installed torchtitan does not have,
+and ``flame/custom_models/__init__.py`` needs fla >= 0.5.2.  The model package is therefore imported
+directly, with empty stand-in ``flame`` / ``flame.custom_models`` package objects so that only those
+two ``__init__`` files are skipped.
+"""
 from __future__ import annotations
 
 import json
+import os
+import sys
+import types
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REF_ROOT = os.path.join(HERE, "_ref", "uttt_llm")
+
+
+def _unavailable(why: str) -> None:
+    print(json.dumps({"impl": "reference", "unavailable": why.replace("\n", " ")[:300]}), flush=True)
+
+
+def _import_reference():
+    if not os.path.isdir(os.path.join(REF_ROOT, "flame", "custom_models", "uttt_moe")):
+        raise FileNotFoundError("baseline/_ref/uttt_llm is missing (copy the reference's uttt_llm tree there)")
+    sys.path.insert(0, REF_ROOT)
+    for name, path in (("flame", "flame"), ("flame.custom_models", "flame/custom_models")):
+        if name not in sys.modules:
+            mod = types.ModuleType(name)
+            mod.__path__ = [os.path.join(REF_ROOT, path)]
+            sys.modules[name] = mod
+    import flame.custom_models.uttt_moe as um
+    return um
 
 
 def run_reference(args) -> None:
-    print(json.dumps({"impl": "reference", "unavailable": "reference arm not wired yet"}), flush=True)
+    try:
+        _run(args)
+    except Exception as exc:  # the contract: say why on one line and exit 0
+        import traceback
+        traceback.print_exc(file=sys.stderr)
+        rank = int(os.environ.get("RANK", "0"))
+        if rank == 0:
+            _unavailable(f"{type(exc).__name__}: {exc}")
+
+
+def _run(args) -> None:
+    import torch
+    import torch.distributed as dist
+    from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
+
+    sys.path.insert(0, os.path.dirname(HERE))
+    from bench import ClockSampler  # timing helpers only
+    from uttt_b200.train.data import SyntheticZipfTokens  # synthetic ids only (same stream as the other arm)
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29531")
+    os.environ.setdefault("DISABLE_WANDB", "1")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if not dist.is_initialized():
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    um = _import_reference()
+    with open(os.path.join(REF_ROOT, "configs", "main", "760M", "uttt_moe.json")) as f:
+        cfgd = json.load(f)
+    cfgd.pop("model_type", None)
+    # the named benchmark shape (differs from the shipped JSON): 16 heads, 32 experts of hidden 1536, top-2,
+    # window = chunk = 2048
+    cfgd.update(num_heads=16, memory_num_experts=32, memory_num_active_experts=2, fw_inter_multi=4,
+                window_size=2048, chunk_size=2048, memory_update_backward_mode=args.backward_mode)
+    cfg = um.RecurrentLactRefMoeGlobalV45Config(**cfgd)
+    torch.manual_seed(42)
+    model = um.RecurrentLactRefMoeGlobalV45ForCausalLM(cfg).to(dev)
+    n_params = sum(p.numel() for p in model.parameters())
+    mesh = dist.device_mesh.init_device_mesh("cuda", (world,))
+    mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
+    for block in model.model.layers:
+        fully_shard(block, mesh=mesh, mp_policy=mp, reshard_after_forward=False)
+    fully_shard(model, mesh=mesh, mp_policy=mp, reshard_after_forward=False)
+    model.train()
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-3, betas=(0.9, 0.95), eps=1e-15, weight_decay=0.1, fused=True)
+    seq = args.seq_len
+    micro = int(os.environ.get("UTTT_REF_MICRO_BATCH", str(min(args.micro_batch, args.per_gpu_batch))))
+    data = SyntheticZipfTokens(cfg.vocab_size, seq, args.per_gpu_batch, seed=1234, rank=rank, world=world)
+
+    def step(batch):
+        ids = batch["input_ids"]
+        if ids.device != dev:
+            ids = ids.to(dev, non_blocking=True)
+        n_micro = (ids.shape[0] + micro - 1) // micro
+        total = torch.zeros((), device=dev)
+        for i in range(n_micro):
+            mb = ids[i * micro:(i + 1) * micro]
+            out = model(input_ids=mb, labels=mb)
+            (out.loss / n_micro).backward()
+            total += out.loss.detach().float() / n_micro
+        torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        return total
+
+    def fence():
+        torch.cuda.synchronize(dev)
+        dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def timed(fn, batches):
+        fence()
+        sampler = ClockSampler(local)
+        sampler.start()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for b in batches:
+            fn(b)
+        end.record()
+        torch.cuda.synchronize(dev)
+        clocks = sampler.stop()
+        dist.barrier()
+        ms = torch.tensor([start.elapsed_time(end) / len(batches)], device=dev)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()), clocks
+
+    for _ in range(max(args.warmup, 3)):          # also covers Triton autotuning
+        float(step(next(data)))
+    dev_batches = [{k: v.to(dev) for k, v in next(data).items()} for _ in range(args.steps)]
+    ms, clocks = timed(step, dev_batches)
+    host_batches = [next(data) for _ in range(args.steps)]
+    losses = []
+    ms_e2e, clocks_e2e = timed(lambda b: losses.append(float(step(b))), host_batches)
+    tokens = args.per_gpu_batch * seq * world
+    if rank == 0:
+        h2d = host_batches[0]["input_ids"].numel() * host_batches[0]["input_ids"].element_size()
+        print(json.dumps({
+            "metric": "train tokens/s, 760M uTTT-MoE 32K ctx", "value": tokens / (ms / 1e3), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic Zipf(1.1) token ids, random-init weights", "impl": "reference",
+            "config": {"model": "760M-uttt-moe (reference RecurrentLactRefMoeGlobalV45ForCausalLM)",
+                       "params": n_params, "global_batch": args.per_gpu_batch * world,
+                       "per_gpu_batch": args.per_gpu_batch, "micro_batch": micro, "seq_len": seq,
+                       "parallelism": f"fsdp{world}", "backward_mode": args.backward_mode},
+            "clocks": clocks,
+            "e2e": {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4, "clocks": clocks_e2e,
+                    "last_loss": losses[-1] if losses else None},
+            "peak_mem_gib": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 2),
+        }), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()

@@ -122,11 +122,7 @@ def pool_raw_grad(k_rows: torch.Tensor, v_rows: torch.Tensor, lr_rows: torch.Ten
     vw = (v_rows.reshape(bsz * n, 1, d).float() * routing.weights.unsqueeze(-1)).to(dt)
     vp = _permute_per_choice(vw, plan)
     lrp = _permute_per_choice(lr_rows.reshape(bsz * n, 1, 3).float().expand(-1, plan.topk, -1), plan)
-    y02 = ops.gg_nt(kp, w02, plan)             # [R, 2I] gate|up pre-activations
-    dh = ops.gg_nn(vp, w1, plan)               # [R, I]   = (p v) W1
-    dy02_lr, h_lr = ops.fw_write_pointwise(y02, dh, lrp)
-    g02 = ops.gg_tn(dy02_lr, kp, plan)      # [G, 2I, D]
-    g1 = ops.gg_tn(vp, h_lr, plan)          # [G, D, I]
+    g02, g1 = ops.fw_write_grad(kp, vp, lrp, w02, w1, plan)
     e = g // bsz
     return g02.view(bsz, e, inter2, d), g1.view(bsz, e, d, inter2 // 2)
 

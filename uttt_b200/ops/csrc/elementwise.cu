@@ -124,13 +124,24 @@ __global__ void rms_norm_bwd_kernel(const T* __restrict__ dy, const T* __restric
     }
   }
   if (dw) {
+    // per-CTA partial sums: the 4 warps of the CTA take turns adding into dw_partial[blockIdx.x, :]
+    float* dst = dw + (size_t)blockIdx.x * d;
+    int wid = threadIdx.x >> 5;
+    for (int turn = 0; turn < (int)(blockDim.x >> 5); ++turn) {
+      if (wid == turn) {
 #pragma unroll
-    for (int j = 0; j < MAXV; ++j) {
-      int v = lane + 32 * j;
-      if (v < nv) {
+        for (int j = 0; j < MAXV; ++j) {
+          int v = lane + 32 * j;
+          if (v < nv) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) atomicAdd(dw + v * 8 + i, acc[j][i]);
+            for (int i = 0; i < 8; ++i) {
+              if (turn == 0) dst[v * 8 + i] = acc[j][i];
+              else dst[v * 8 + i] += acc[j][i];
+            }
+          }
+        }
       }
+      __syncthreads();
     }
   }
 }
@@ -158,13 +169,13 @@ std::vector<at::Tensor> rms_norm_bwd(at::Tensor dy, at::Tensor x, c10::optional<
   TORCH_CHECK(d % 8 == 0 && d <= 8 * 32 * 16, "rms_norm_bwd: hidden size must be a multiple of 8 and <= 4096");
   auto dx = at::empty_like(x);
   at::Tensor wc, dw;
+  int blocks = std::max(1, std::min((rows + 3) / 4, sm_count() * 2));
   if (w.has_value() && w->defined()) {
     wc = w->to(x.scalar_type()).contiguous();
-    dw = at::zeros({d}, x.options().dtype(at::kFloat));
+    dw = at::empty({blocks, d}, x.options().dtype(at::kFloat));
   } else {
     dw = at::zeros({1}, x.options().dtype(at::kFloat));
   }
-  int blocks = std::max(1, std::min((rows + 3) / 4, sm_count() * 4));
   int nv = d / 8;
   UTTT_DISPATCH_FLOAT(x, {
     const T* wp = wc.defined() ? ptr<T>(wc) : nullptr;
@@ -180,6 +191,7 @@ std::vector<at::Tensor> rms_norm_bwd(at::Tensor dy, at::Tensor x, c10::optional<
                                                                     ptr<T>(dx), dwp, rows, d);
   });
   count_launch();
+  if (wc.defined()) dw = dw.sum(0);
   return {dx, dw};
 }
 

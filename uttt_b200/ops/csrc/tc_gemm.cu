@@ -287,6 +287,13 @@ static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
 // 2-D bf16 tensor map over a row-major [rows, cols] matrix; box = [box_rows, box_cols] with cols innermost.
 CUtensorMap make_tmap_2d_bf16(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t box_cols) {
   CUtensorMap m;
+  {
+    // autograd worker threads may not have the primary context current yet; the driver call needs it
+    int dev = 0;
+    C10_CUDA_CHECK(cudaGetDevice(&dev));
+    C10_CUDA_CHECK(cudaSetDevice(dev));
+    C10_CUDA_CHECK(cudaFree(nullptr));
+  }
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {cols * 2};
   cuuint32_t box[2] = {box_cols, box_rows};

@@ -34,9 +34,11 @@ def _count(n: int = 1) -> None:
 
 
 def launch_count() -> int:
-    ext = cuda_ext()
+    """Number of kernels of this extension launched so far in this process."""
+    from ._ext import load
+    ext = load()
     native = ext.launch_count() if (ext is not None and hasattr(ext, "launch_count")) else 0
-    return int(native) if native else _LAUNCHES
+    return int(native) + _LAUNCHES
 
 
 def _kernel(name: str, *tensors):
@@ -189,6 +191,9 @@ def swa_attention(q, k, v, window: Optional[int], causal: bool = True, scale: Op
     return ref.swa_attention(q, k, v, window, causal, scale)
 
 
+_MASKS = {}
+
+
 def _sdpa_attention(q, k, v, window, causal, scale):
     """Library stand-in used only where the hand-written kernel does not cover the shape."""
     b, lq, h, hd = q.shape
@@ -198,11 +203,15 @@ def _sdpa_attention(q, k, v, window, causal, scale):
         v = v.repeat_interleave(h // v.shape[2], dim=2)
     mask = None
     if causal:
-        qpos = torch.arange(lk - lq, lk, device=q.device)[:, None]
-        kpos = torch.arange(lk, device=q.device)[None, :]
-        mask = kpos <= qpos
-        if window is not None:
-            mask = mask & (kpos > qpos - window)
+        key = (lq, lk, window, str(q.device))
+        mask = _MASKS.get(key)
+        if mask is None:
+            qpos = torch.arange(lk - lq, lk, device=q.device)[:, None]
+            kpos = torch.arange(lk, device=q.device)[None, :]
+            mask = kpos <= qpos
+            if window is not None:
+                mask = mask & (kpos > qpos - window)
+            _MASKS[key] = mask
     o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), attn_mask=mask,
                                        scale=scale)
     return o.transpose(1, 2).contiguous()
@@ -422,6 +431,68 @@ def fw_write_pointwise(y02, dh, lr):
     if _kernel("fw_write_pw_fwd", y02) is not None and y02.shape[-1] % 16 == 0:
         return _FwWritePW.apply(y02, dh, lr.float())
     return ref.fw_write_pointwise(y02, dh, lr)
+
+
+class _FwWriteGrad(torch.autograd.Function):
+    """Inner gradient of the fast-weight write as one autograd node that keeps only its inputs.
+
+    forward : y02 = kp W02^T, dh = vp W1, (dy02*lr, h*lr1) = pointwise, G02 = (dy02*lr)^T kp, G1 = vp^T (h*lr1)
+    backward: recomputes y02 / dh, then runs the gradient-of-gradient chain with the same grouped GEMM
+    and pointwise kernels, so no [rows, 2I] intermediate outlives the call
+    (the reference does the same in FusedLactSwiGLUFFNBwd,
+    uttt_llm/flame/custom_models/uttt_moe/lact_moe_triton/lact_fw_grad.py:51-300).
+    """
+
+    @staticmethod
+    def forward(ctx, kp, vp, lrp, w02, w1, plan):
+        ctx.save_for_backward(kp, vp, lrp, w02, w1)
+        ctx.plan = plan
+        with torch.no_grad():
+            y02 = gg_nt(kp, w02, plan)
+            dh = gg_nn(vp, w1, plan)
+            dy02_lr, h_lr = fw_write_pointwise(y02, dh, lrp)
+            del y02, dh
+            g02 = gg_tn(dy02_lr, kp, plan)
+            g1 = gg_tn(vp, h_lr, plan)
+        return g02, g1
+
+    @staticmethod
+    def backward(ctx, c02, c1):
+        kp, vp, lrp, w02, w1 = ctx.saved_tensors
+        plan = ctx.plan
+        ext = cuda_ext(kp)
+        with torch.no_grad():
+            c02 = c02.to(kp.dtype).contiguous()
+            c1 = c1.to(kp.dtype).contiguous()
+            y02 = gg_nt(kp, w02, plan)
+            dh = gg_nn(vp, w1, plan)
+            dy02_lr, h_lr = ext.fw_write_pw_fwd(y02, dh, lrp)
+            d_dy02 = gg_nt(kp, c02, plan)            # [R, 2I]
+            d_kp = gg_nn(dy02_lr, c02, plan)         # [R, D]
+            d_vp = gg_nt(h_lr, c1, plan)             # [R, D]
+            d_hlr = gg_nn(vp, c1, plan)              # [R, I]
+            del dy02_lr, h_lr
+            d_y02, d_dh, d_lr = ext.fw_write_pw_bwd(d_dy02, d_hlr, y02, dh, lrp)
+            del d_dy02, d_hlr, y02, dh
+            d_kp += gg_nn(d_y02, w02, plan)
+            d_w02 = gg_tn(d_y02, kp, plan, w02.dtype)
+            d_vp += gg_nt(d_dh, w1, plan)
+            d_w1 = gg_tn(vp, d_dh, plan, w1.dtype)
+        return d_kp, d_vp, d_lr, d_w02, d_w1, None
+
+
+def fw_write_grad(kp, vp, lrp, w02, w1, plan: GroupPlan):
+    """(G02 [G, 2I, D], G1 [G, D, I]) fp32: lr-weighted inner gradients of the write, from permuted rows.
+
+    kp, vp: [R, D] expert-major keys and (prob-weighted) values; lrp: [R, 3] fp32; w02 [G, 2I, D]; w1 [G, D, I].
+    """
+    if (_gg_kernel_ok(kp, vp, w02, w1) and _gg_dims_ok(kp.shape[1], w02.shape[1]) and w02.shape[1] % 256 == 0
+            and kp.shape[1] % 128 == 0):
+        return _FwWriteGrad.apply(kp, vp, lrp.float().contiguous(), w02, w1, plan)
+    y02 = gg_nt(kp, w02, plan)
+    dh = gg_nn(vp, w1, plan)
+    dy02_lr, h_lr = fw_write_pointwise(y02, dh, lrp)
+    return gg_tn(dy02_lr, kp, plan), gg_tn(vp, h_lr, plan)
 
 
 # =========================================================================== Newton-Schulz

@@ -138,8 +138,13 @@ class ShardedTrainer:
         if use_symmetric_memory is None:
             use_symmetric_memory = first.is_cuda and self.world > 1
         if use_symmetric_memory:
-            from .symm import SymmetricHeap
-            self.symm = SymmetricHeap(self.device, self.group)
+            try:
+                from .symm import SymmetricHeap
+                self.symm = SymmetricHeap(self.device, self.group)
+            except Exception as exc:  # pragma: no cover - depends on the box
+                import warnings
+                warnings.warn(f"symmetric memory unavailable ({exc}); gradient path falls back to NCCL collectives")
+                self.symm = None
         # --- partition parameters into units: one per listed module, the remainder is the root unit
         seen = set()
         units: List[Tuple[str, List[Tuple[str, nn.Parameter]]]] = []
@@ -208,21 +213,30 @@ class ShardedTrainer:
         fused = self.symm is not None
         if fused:
             self.symm.barrier()          # every rank's backward has finished writing its gradient buffer
+        ext = cuda_ext(self.units[0].master) if self.units else None
+        native = ext is not None and hasattr(ext, "adamw_flat")
+        gmuls: List[float] = []
+        sq1 = sq.view(1)
         for u in self.units:
             u.rebind_grads()
             src = u.grad_accum if u.grad_accum is not None else u.grad
+            gmul = 1.0
             if fused:
-                g = self.symm.reduce_scatter_sumsq(u, src, scale, sq)
+                g = self.symm.reduce_scatter_sumsq(u, src, scale, sq1)
             elif self.world > 1:
                 g = torch.empty(u.shard_numel, dtype=torch.float32, device=self.device)
-                full = src.float()
-                dist.reduce_scatter_tensor(g, full, group=self.group)
+                dist.reduce_scatter_tensor(g, src.float(), group=self.group)
                 g.mul_(scale)
                 sq += g.pow(2).sum()
+            elif native:
+                # single rank: the optimizer kernel reads the gradient buffer in place
+                g, gmul = src, scale
+                ext.sumsq_accum(src, float(scale), sq1)
             else:
                 g = src.float() * scale if scale != 1.0 or src.dtype != torch.float32 else src
                 sq += g.pow(2).sum()
             shards.append(g)
+            gmuls.append(gmul)
         if self.world > 1:
             dist.all_reduce(sq, group=self.group)
         grad_norm = sq.sqrt()
@@ -233,8 +247,9 @@ class ShardedTrainer:
         # a non-finite norm turns the update into a no-op (skip_nan_inf) without branching on the host
         gscale = torch.where(finite, clip, torch.zeros_like(clip)) if opt.skip_nan_inf else clip
         apply = finite.float() if opt.skip_nan_inf else torch.ones_like(clip)
-        for u, g in zip(self.units, shards):
-            self._adamw_unit(u, g, lr, gscale, apply)
+        gscale1, apply1 = gscale.reshape(1).float(), apply.reshape(1).float()
+        for u, g, gmul in zip(self.units, shards, gmuls):
+            self._adamw_unit(u, g, lr, gscale1, apply1, gmul)
         if fused:
             self.symm.barrier()          # all peers' compute buffers now hold the new parameters
         for u in self.units:
@@ -244,7 +259,8 @@ class ShardedTrainer:
         self.micro_batches = 0
         return {"grad_norm": grad_norm, "skipped": ~finite}
 
-    def _adamw_unit(self, u: FlatUnit, g: torch.Tensor, lr: float, gscale: torch.Tensor, apply: torch.Tensor):
+    def _adamw_unit(self, u: FlatUnit, g: torch.Tensor, lr: float, gscale: torch.Tensor, apply: torch.Tensor,
+                    gmul: float = 1.0):
         opt = self.opt
         lo, hi = u.shard_range
         decay_hi = min(max(u.decay_end - lo, 0), u.shard_numel)   # elements [0, decay_hi) of the shard decay
@@ -254,7 +270,8 @@ class ShardedTrainer:
                 self.symm.adamw_scatter(u, g, lr, opt, self.step_count, gscale, apply, decay_hi)
                 return
             ext.adamw_flat(u.master, g, u.exp_avg, u.exp_avg_sq, u.compute[lo:hi], float(lr), opt.beta1, opt.beta2,
-                           opt.eps, opt.weight_decay, int(self.step_count), gscale, apply, int(decay_hi))
+                           opt.eps, opt.weight_decay, int(self.step_count), gscale, apply, float(gmul),
+                           int(decay_hi))
         else:
             self._adamw_torch(u, g, lr, gscale, apply, decay_hi)
             if self.world > 1:
