@@ -33,6 +33,12 @@ at::Tensor gg_tn_segments(at::Tensor a, at::Tensor b, at::Tensor offsets, int64_
                           at::ScalarType out_dtype, c10::optional<at::Tensor> accumulate_into);
 at::Tensor bmm_nt(at::Tensor a, at::Tensor b, double alpha, c10::optional<at::Tensor> d, double beta);
 at::Tensor gemm_status(at::Tensor like);
+void rs_sumsq(std::vector<int64_t> grad_ptrs, int64_t rank, int64_t shard_off, at::Tensor out, double scale,
+              at::Tensor sumsq, bool grads_bf16);
+void adamw_scatter(at::Tensor p, at::Tensor g, at::Tensor m, at::Tensor v, std::vector<int64_t> compute_ptrs,
+                   int64_t rank, int64_t shard_off, bool compute_bf16, double lr, double b1, double b2, double eps,
+                   double wd, int64_t step, at::Tensor gscale, at::Tensor apply, int64_t decay_hi);
+std::vector<at::Tensor> swa_fwd(at::Tensor q, at::Tensor k, at::Tensor v, int64_t window, bool causal, double scale);
 }  // namespace uttt
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -59,4 +65,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gg_tn_segments", &gg_tn_segments);
   m.def("bmm_nt", &bmm_nt);
   m.def("gemm_status", &gemm_status);
+  m.def("swa_fwd", &swa_fwd);
+  m.def("rs_sumsq", &rs_sumsq);
+  m.def("adamw_scatter", &adamw_scatter);
 }

@@ -161,11 +161,14 @@ def fw_qk_prep(x, scale, shift, fw_heads: int, rope_dim: int, theta: float, offs
 
 # =========================================================================== attention
 class _SWA(torch.autograd.Function):
+    """Forward: the tcgen05 sliding-window kernel.  Backward: hand-written kernel when the extension has one,
+    otherwise the flash-attn library backward fed with this forward's output and log-sum-exp."""
+
     @staticmethod
     def forward(ctx, q, k, v, window, causal, scale):
         ext = cuda_ext(q)
-        o, lse = ext.swa_fwd(q.contiguous(), k.contiguous(), v.contiguous(), int(window or 0), bool(causal),
-                             float(scale))
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        o, lse = ext.swa_fwd(q, k, v, int(window or 0), bool(causal), float(scale))
         ctx.save_for_backward(q, k, v, o, lse)
         ctx.args = (window, causal, scale)
         return o
@@ -175,8 +178,14 @@ class _SWA(torch.autograd.Function):
         q, k, v, o, lse = ctx.saved_tensors
         window, causal, scale = ctx.args
         ext = cuda_ext(q)
-        dq, dk, dv = ext.swa_bwd(do.contiguous(), q.contiguous(), k.contiguous(), v.contiguous(), o, lse,
-                                 int(window or 0), bool(causal), float(scale))
+        if hasattr(ext, "swa_bwd"):
+            dq, dk, dv = ext.swa_bwd(do.contiguous(), q, k, v, o, lse, int(window or 0), bool(causal), float(scale))
+            return dq, dk, dv, None, None, None
+        from flash_attn.flash_attn_interface import _flash_attn_backward
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        left = -1 if (window is None or not causal) else window - 1
+        _flash_attn_backward(do.contiguous(), q, k, v, o, lse, dq, dk, dv, 0.0, float(scale), bool(causal),
+                             left, 0 if causal else -1, 0.0, None, False)
         return dq, dk, dv, None, None, None
 
 
@@ -194,8 +203,26 @@ def swa_attention(q, k, v, window: Optional[int], causal: bool = True, scale: Op
 _MASKS = {}
 
 
+def _flash_attn_func():
+    global _FLASH
+    if _FLASH is None:
+        try:
+            from flash_attn import flash_attn_func
+            _FLASH = flash_attn_func
+        except Exception:
+            _FLASH = False
+    return _FLASH
+
+
+_FLASH = None
+
+
 def _sdpa_attention(q, k, v, window, causal, scale):
     """Library stand-in used only where the hand-written kernel does not cover the shape."""
+    fa = _flash_attn_func()
+    if fa and q.dtype in (torch.bfloat16, torch.float16) and causal:
+        return fa(q, k, v, softmax_scale=scale, causal=True,
+                  window_size=(-1, -1) if window is None else (window - 1, 0))
     b, lq, h, hd = q.shape
     lk = k.shape[1]
     if k.shape[2] != h:

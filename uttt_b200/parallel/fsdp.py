@@ -137,14 +137,6 @@ class ShardedTrainer:
         self.symm = None
         if use_symmetric_memory is None:
             use_symmetric_memory = first.is_cuda and self.world > 1
-        if use_symmetric_memory:
-            try:
-                from .symm import SymmetricHeap
-                self.symm = SymmetricHeap(self.device, self.group)
-            except Exception as exc:  # pragma: no cover - depends on the box
-                import warnings
-                warnings.warn(f"symmetric memory unavailable ({exc}); gradient path falls back to NCCL collectives")
-                self.symm = None
         # --- partition parameters into units: one per listed module, the remainder is the root unit
         seen = set()
         units: List[Tuple[str, List[Tuple[str, nn.Parameter]]]] = []
@@ -161,6 +153,22 @@ class ShardedTrainer:
         root = [(pn, p) for pn, p in model.named_parameters() if id(p) not in seen and not seen.add(id(p))]
         if root:
             units.append(("root", root))
+        if use_symmetric_memory:
+            try:
+                from .symm import SymmetricHeap
+                item = torch.empty((), dtype=compute_dtype).element_size()
+                chunk = _ALIGN * self.world
+                total = 0
+                for _, pl in units:
+                    n = sum((p.numel() + 7) // 8 * 8 for _, p in pl)
+                    n = (n + chunk - 1) // chunk * chunk
+                    # compute + low-precision grad + (optional) fp32 accumulation buffer, 1 KiB aligned each
+                    total += n * item * 2 + n * 4 + 3 * 1024
+                self.symm = SymmetricHeap(self.device, self.group, capacity_bytes=total + (1 << 20))
+            except Exception as exc:  # pragma: no cover - depends on the box
+                import warnings
+                warnings.warn(f"symmetric memory unavailable ({exc}); gradient path falls back to NCCL collectives")
+                self.symm = None
         alloc = self.symm.alloc if self.symm is not None else None
         self.units = [FlatUnit(n, pl, self.world, self.rank, compute_dtype, no_decay, alloc) for n, pl in units]
         # tied / aliased tensors (e.g. tied embeddings) keep working: every alias views the same slot
@@ -192,7 +200,8 @@ class ShardedTrainer:
         for u in self.units:
             u.rebind_grads()
             if u.grad_accum is None:
-                u.grad_accum = torch.zeros(u.numel, dtype=torch.float32, device=self.device)
+                u.grad_accum = (self.symm.alloc(u.numel, torch.float32).zero_() if self.symm is not None
+                                else torch.zeros(u.numel, dtype=torch.float32, device=self.device))
             u.grad_accum.add_(u.grad)
             u.grad.zero_()
         self.micro_batches += 1
