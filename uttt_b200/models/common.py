@@ -91,17 +91,21 @@ class SlidingWindowAttention(nn.Module):
             if config.enable_attention_output_proj else None
 
     def history_len(self, chunk: int) -> int:
-        return 0 if self.window_size is None else max(self.window_size - 1, 0)
+        """Keys carried between chunks.  A window of W needs W-1 predecessors; W are kept when that makes the
+        history a whole number of chunks (the kernel masks by position, so one spare key is harmless and the
+        history then needs no copy)."""
+        if self.window_size is None:
+            return 0
+        need = max(self.window_size - 1, 0)
+        if need > 0 and self.window_size % chunk == 0:
+            return self.window_size
+        return need
 
     def forward(self, x: torch.Tensor, k_hist: Optional[torch.Tensor], v_hist: Optional[torch.Tensor],
                 offset: int):
         b, l, _ = x.shape
-        if self.q_proj.bias is None:
-            w = torch.cat([self.q_proj.weight, self.k_proj.weight, self.v_proj.weight], dim=0)
-            qkv = F.linear(x, w)
-            q_flat, k_flat, v_flat = qkv.split([self.hidden_size, self.kv_dim, self.kv_dim], dim=-1)
-        else:
-            q_flat, k_flat, v_flat = self.q_proj(x), self.k_proj(x), self.v_proj(x)
+        # three GEMMs with contiguous outputs (a fused QKV GEMM would hand strided views to every consumer)
+        q_flat, k_flat, v_flat = self.q_proj(x), self.k_proj(x), self.v_proj(x)
         q = q_flat.reshape(b, l, self.num_heads, self.head_dim)
         k = k_flat.reshape(b, l, self.num_kv_heads, self.head_dim)
         v = v_flat.reshape(b, l, self.num_kv_heads, self.head_dim)
@@ -122,6 +126,13 @@ class SlidingWindowAttention(nn.Module):
 
 def trim_history(k_hist, v_hist, k_new, v_new, keep: Optional[int]):
     """Append this chunk's keys/values to the carried history and keep the last ``keep`` positions."""
+    if keep is not None and keep == 0:
+        return None, None
+    if keep is not None and k_new.shape[1] >= keep:
+        # the chunk alone covers the history: no concatenation, no copy when the lengths are equal
+        if k_new.shape[1] == keep:
+            return k_new, v_new
+        return k_new[:, k_new.shape[1] - keep:], v_new[:, v_new.shape[1] - keep:]
     if k_hist is not None and k_hist.shape[1] > 0:
         k_new = torch.cat([k_hist, k_new], dim=1)
         v_new = torch.cat([v_hist, v_new], dim=1)

@@ -105,10 +105,11 @@ def pool_read(q_rows: torch.Tensor, state_w02: torch.Tensor, state_w1: torch.Ten
 
 
 def pool_raw_grad(k_rows: torch.Tensor, v_rows: torch.Tensor, lr_rows: torch.Tensor, state_w02: torch.Tensor,
-                  state_w1: torch.Tensor, routing: Routing) -> Tuple[torch.Tensor, torch.Tensor]:
+                  state_w1: torch.Tensor, routing: Routing, acc=None) -> Tuple[torch.Tensor, torch.Tensor]:
     """Inner gradient (ascent direction) of <f_W(k), p*v> per (sequence, expert), lr-weighted per row.
 
     k_rows, v_rows: [B, N, D]; lr_rows: [B, N, 3] -> (G02 [B, E, 2I, D], G1 [B, E, D, I]) in fp32.
+    With ``acc = (A02, A1)`` the gradients are added to those running sums and the sums are returned.
     """
     bsz, n, d = k_rows.shape
     plan = routing.plan
@@ -122,6 +123,8 @@ def pool_raw_grad(k_rows: torch.Tensor, v_rows: torch.Tensor, lr_rows: torch.Ten
     vw = (v_rows.reshape(bsz * n, 1, d).float() * routing.weights.unsqueeze(-1)).to(dt)
     vp = _permute_per_choice(vw, plan)
     lrp = _permute_per_choice(lr_rows.reshape(bsz * n, 1, 3).float().expand(-1, plan.topk, -1), plan)
+    if acc is not None:
+        return ops.fw_write_grad_accumulate(kp, vp, lrp, w02, w1, plan, acc[0], acc[1])
     g02, g1 = ops.fw_write_grad(kp, vp, lrp, w02, w1, plan)
     e = g // bsz
     return g02.view(bsz, e, inter2, d), g1.view(bsz, e, d, inter2 // 2)

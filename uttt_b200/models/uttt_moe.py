@@ -95,8 +95,9 @@ class MoEBlock(nn.Module):
         return h, x_attn_in, k_flat, v_flat, k_rot, v_new, lb_probs, lb_counts
 
     # -------------------------------------------------------------------------- write
-    def raw_grad(self, x_in, k_flat, v_flat, w02, w1, router, bias, offset: int):
-        """This layer's lr-weighted inner gradient on the shared bank, plus momentum gate and lb sums."""
+    def raw_grad(self, x_in, k_flat, v_flat, w02, w1, router, bias, offset: int, acc=None):
+        """This layer's lr-weighted inner gradient on the shared bank (added to ``acc`` when given),
+        plus momentum gate and lb sums."""
         cfg = self.config
         mem = self.memory
         b, l, _ = x_in.shape
@@ -109,7 +110,7 @@ class MoEBlock(nn.Module):
         v_rows = mem.head_rows(mem.prep_value(v_flat))
         route_in = v_rows if cfg.memory_router_from_v else k_rows
         routing = fw.route_rows(route_in, router, bias, cfg, getattr(cfg, "memory_bias_in_logits", False))
-        g02, g1 = fw.pool_raw_grad(k_rows, v_rows, lr_rows, w02, w1, routing)
+        g02, g1 = fw.pool_raw_grad(k_rows, v_rows, lr_rows, w02, w1, routing, acc=acc)
         m = mem.momentum_coeff(x_in)
         return g02, g1, m, routing.prob_sum, routing.counts
 
@@ -330,13 +331,15 @@ class UTTTMoEModel(nn.Module):
             a02 = torch.zeros_like(s.m02)
             a1 = torch.zeros_like(s.m1)
             ms, probs, counts = [], [], []
+            detach_g = mode in ("first_order_state", "stop_state")
             for wi, li in enumerate(writers):
-                g02, g1, m, p, c = self.layers[li].raw_grad(f[3 * wi], f[3 * wi + 1], f[3 * wi + 2], s.w02, s.w1,
-                                                             self._router(li), self._router_bias(li), offset)
-                if mode in ("first_order_state", "stop_state"):
-                    g02, g1 = g02.detach(), g1.detach()
-                a02 = a02 + g02
-                a1 = a1 + g1
+                args_l = (f[3 * wi], f[3 * wi + 1], f[3 * wi + 2], s.w02, s.w1, self._router(li),
+                          self._router_bias(li), offset)
+                if detach_g:
+                    g02, g1, m, p, c = self.layers[li].raw_grad(*args_l)
+                    a02, a1 = a02 + g02.detach(), a1 + g1.detach()
+                else:
+                    a02, a1, m, p, c = self.layers[li].raw_grad(*args_l, acc=(a02, a1))
                 if m is not None:
                     ms.append(m.detach() if (cfg.memory_detach_m_coeff or mode == "stop_state") else m)
                 probs.append(p)
@@ -359,10 +362,17 @@ class UTTTMoEModel(nn.Module):
         bsz = state.w02.shape[0]
         probs = torch.zeros(n_layers, bsz, e, device=state.w02.device, dtype=torch.float32)
         counts = torch.zeros_like(probs)
-        widx = torch.tensor(writers, device=probs.device)
+        widx = self._writer_index(probs.device)
         probs = probs.index_copy(0, widx, out[n_state].float())
         counts = counts.index_copy(0, widx, out[n_state + 1].float())
         return [new], probs, counts
+
+    def _writer_index(self, device) -> torch.Tensor:
+        cached = getattr(self, "_writer_idx", None)
+        if cached is None or cached.device != device:
+            cached = torch.tensor(self.writer_layers, device=device)
+            self._writer_idx = cached
+        return cached
 
     def _ckpt(self, fn, *args):
         if self.activation_checkpoint and torch.is_grad_enabled():

@@ -508,18 +508,65 @@ class _FwWriteGrad(torch.autograd.Function):
         return d_kp, d_vp, d_lr, d_w02, d_w1, None
 
 
+def _gg_tn_acc_(a, b, plan: GroupPlan, acc: torch.Tensor) -> None:
+    """acc[g] += sum_{r in g} a[r]^T b[r] (fp32, in place; the add happens in the GEMM epilogue)."""
+    cuda_ext(a).gg_tn_segments(a.contiguous(), b.contiguous(), plan.offsets, plan.num_groups, 1, torch.float32,
+                               acc.view(plan.num_groups, a.shape[1], b.shape[1]))
+
+
+class _FwWriteGradAcc(torch.autograd.Function):
+    """:class:`_FwWriteGrad` that adds its result into running fp32 sums (the aggregate over writer layers)
+    inside the token-reduction GEMM's epilogue instead of materialising per-layer gradients."""
+
+    @staticmethod
+    def forward(ctx, kp, vp, lrp, w02, w1, plan, acc02, acc1):
+        ctx.save_for_backward(kp, vp, lrp, w02, w1)
+        ctx.plan = plan
+        with torch.no_grad():
+            y02 = gg_nt(kp, w02, plan)
+            dh = gg_nn(vp, w1, plan)
+            dy02_lr, h_lr = fw_write_pointwise(y02, dh, lrp)
+            del y02, dh
+            _gg_tn_acc_(dy02_lr, kp, plan, acc02)
+            _gg_tn_acc_(vp, h_lr, plan, acc1)
+        ctx.mark_dirty(acc02, acc1)
+        return acc02, acc1
+
+    @staticmethod
+    def backward(ctx, c02, c1):
+        grads = _FwWriteGrad.backward(ctx, c02.reshape(ctx.plan.num_groups, *c02.shape[-2:]),
+                                      c1.reshape(ctx.plan.num_groups, *c1.shape[-2:]))
+        return (*grads, c02, c1)
+
+
 def fw_write_grad(kp, vp, lrp, w02, w1, plan: GroupPlan):
     """(G02 [G, 2I, D], G1 [G, D, I]) fp32: lr-weighted inner gradients of the write, from permuted rows.
 
     kp, vp: [R, D] expert-major keys and (prob-weighted) values; lrp: [R, 3] fp32; w02 [G, 2I, D]; w1 [G, D, I].
     """
-    if (_gg_kernel_ok(kp, vp, w02, w1) and _gg_dims_ok(kp.shape[1], w02.shape[1]) and w02.shape[1] % 256 == 0
-            and kp.shape[1] % 128 == 0):
+    if _fw_write_kernel_ok(kp, vp, w02, w1):
         return _FwWriteGrad.apply(kp, vp, lrp.float().contiguous(), w02, w1, plan)
     y02 = gg_nt(kp, w02, plan)
     dh = gg_nn(vp, w1, plan)
     dy02_lr, h_lr = fw_write_pointwise(y02, dh, lrp)
     return gg_tn(dy02_lr, kp, plan), gg_tn(vp, h_lr, plan)
+
+
+def _fw_write_kernel_ok(kp, vp, w02, w1) -> bool:
+    return (_gg_kernel_ok(kp, vp, w02, w1) and _gg_dims_ok(kp.shape[1], w02.shape[1]) and w02.shape[1] % 256 == 0
+            and kp.shape[1] % 128 == 0)
+
+
+def fw_write_grad_accumulate(kp, vp, lrp, w02, w1, plan: GroupPlan, acc02: torch.Tensor, acc1: torch.Tensor):
+    """acc02 += G02, acc1 += G1 (see :func:`fw_write_grad`); returns the updated sums.
+
+    On the GPU the sums are updated in place by the GEMM epilogue; elsewhere new tensors are returned.
+    """
+    if _fw_write_kernel_ok(kp, vp, w02, w1) and acc02.dtype == torch.float32 and acc02.is_contiguous() \
+            and acc1.is_contiguous():
+        return _FwWriteGradAcc.apply(kp, vp, lrp.float().contiguous(), w02, w1, plan, acc02, acc1)
+    g02, g1 = fw_write_grad(kp, vp, lrp, w02, w1, plan)
+    return acc02 + g02.view_as(acc02), acc1 + g1.view_as(acc1)
 
 
 # =========================================================================== Newton-Schulz
