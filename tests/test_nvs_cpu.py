@@ -1,0 +1,209 @@
+"""View-synthesis half on CPU: model contract, schedules, data tools, checkpoint lifecycle, trainer step."""
+import os
+
+import pytest
+import torch
+
+from uttt_b200.nvs import checkpoint as ck
+from uttt_b200.nvs.data import (NVSDataset, ResumableDistributedSampler, SyntheticScenes, check_manifest,
+                                make_toy_dataset)
+from uttt_b200.nvs.metrics import bootstrap_ci, psnr, ssim
+from uttt_b200.nvs.model import LVSMModel
+from uttt_b200.nvs.schedule import inputs_then_targets_config, parallel_ttt_config
+from uttt_b200.nvs.trainer import NVSTrainer, apply_overrides, check_batch_arithmetic
+from uttt_b200.ops import reference as ref
+
+
+def _cfg(block="uttt_nvs.models.uttt_moe_block.MemoryModel", **params):
+    p = dict(attn_head_dim=32, fw_head_dim=32, inter_multi=2, fw_inter_multi=1, use_muon=False, num_experts=4,
+             num_active_experts=2, l2_norm=True, pool_mode="shared", router_share_mode="share_all",
+             aggregate_write=True, load_balancing_loss_alpha=1e-5)
+    p.update(params)
+    return {"exp_name": "t", "model": {"image_size": 32, "patch_size": 8, "dim": 64, "layers": 2,
+                                       "block_config": {"type": block, "params": p}},
+            "training": {"batch_size_per_gpu": 2, "total_batch_size": 2, "num_views": 4, "lr": 1e-3, "warmup": 0,
+                         "max_fwdbwd_passes": 4, "checkpoint_every": 2, "print_every": 100, "dataset": "synthetic"}}
+
+
+def _batch(b=2, v=4):
+    return next(SyntheticScenes(b, v, 32, pin=False))
+
+
+@pytest.mark.parametrize("block,params", [
+    ("uttt_nvs.models.uttt_moe_block.MemoryModel", {}),
+    ("uttt_nvs.models.uttt_moe_block.MemoryModel", dict(pool_mode="per_block", aggregate_write=False,
+                                                         router_share_mode="per_layer", use_muon=True)),
+    ("uttt_nvs.models.uttt_moe_block.MemoryModel", dict(aggregate_write=False)),
+    ("uttt_nvs.models.uttt_dense_block.MemoryModel", {}),
+    ("uttt_nvs.models.transformer_block.TransformerModel", {}),
+    ("uttt_nvs.models.deltanet_block.DeltaNetModel", {}),
+    ("uttt_nvs.models.gated_deltanet_block.GatedDeltaNetModel", {}),
+])
+def test_block_families_train(block, params):
+    torch.manual_seed(0)
+    model = LVSMModel(_cfg(block, **params))
+    out = model(_batch())
+    loss = out["loss_metrics"]["loss"]
+    assert torch.isfinite(loss) and out["rendering"].shape == (2, 3, 3, 32, 32)
+    loss.backward()
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in model.parameters())
+
+
+def test_state_dict_layout_and_aggregate_differs_from_chained():
+    torch.manual_seed(0)
+    agg = LVSMModel(_cfg())
+    keys = set(agg.state_dict())
+    for k in ("image_tokenizer.1.weight", "transformer_input_layernorm.weight", "transformer_blocks.pool_w0",
+              "transformer_blocks.shared_router_proj_weights", "transformer_blocks.blocks.0.ln_attn.weight",
+              "transformer_blocks.blocks.0.self_attention.to_qkv.weight",
+              "transformer_blocks.blocks.1.memory.k_input_proj.0.weight", "transformer_blocks.blocks.0.memory.to_lr.weight",
+              "transformer_blocks.blocks.0.mlp.gate.weight", "image_token_decoder.0.weight", "image_token_decoder.1.weight"):
+        assert k in keys, k
+    chained = LVSMModel(_cfg(aggregate_write=False))
+    chained.load_state_dict(agg.state_dict())
+    b = _batch()
+    with torch.no_grad():
+        a, c = agg(b)["rendering"], chained(b)["rendering"]
+    assert (a - c).abs().max() > 1e-7                 # one write from a shared snapshot != writes in turn
+    one = LVSMModel(dict(_cfg(), model=dict(_cfg()["model"], layers=1)))
+    one_c = LVSMModel(dict(_cfg(aggregate_write=False), model=dict(_cfg()["model"], layers=1)))
+    one_c.load_state_dict(one.state_dict())
+    with torch.no_grad():
+        torch.testing.assert_close(one(b)["rendering"], one_c(b)["rendering"])   # equal with a single layer
+
+
+def test_inputs_then_targets_layout():
+    cfg = _cfg()
+    cfg["model"].update(view_layout="inputs_then_targets", num_input_views=3)
+    model = LVSMModel(cfg)
+    out = model(_batch(v=5))
+    assert out["rendering"].shape[1] == 2
+    sched = inputs_then_targets_config(4, 2, 16)
+    assert [c.update for c in sched] == [True] * 4 + [False] * 2
+    par = parallel_ttt_config(16, 16, 96)
+    assert [c.update for c in par] == [True, False] * 3
+
+
+def test_plucker_rays_are_unit_and_orthogonal_moment():
+    b = _batch()
+    o, d = ref.plucker_rays(b["fxfycxcy"], b["c2w"], 32, 32)
+    torch.testing.assert_close(d.norm(dim=2), torch.ones_like(d[:, :, 0]), atol=1e-5, rtol=1e-5)
+    m = torch.cross(o, d, dim=2)
+    assert (m * d).sum(2).abs().max() < 1e-4          # o x d is perpendicular to d
+    # the central ray of a camera on the sphere looks at the origin
+    centre = d[..., 16, 16] + d[..., 15, 15]
+    eye = b["c2w"][..., :3, 3]
+    cos = torch.nn.functional.cosine_similarity(centre, -eye, dim=-1)
+    assert cos.min() > 0.999
+    tok = ref.plucker_embed(b["image"], b["fxfycxcy"], b["c2w"], torch.tensor([False, True, False, True]), 8)
+    assert tok.shape == (2, 4, 16, 8 * 8 * 12)
+    assert tok[:, 1].reshape(2, 16, 64, 12)[..., 9:].abs().max() == 0     # pose-only views carry zero RGB
+
+
+def test_toy_dataset_is_deterministic_and_right_handed(tmp_path):
+    m1 = make_toy_dataset(str(tmp_path / "a"), 2, 6, 32, seed=3)
+    m2 = make_toy_dataset(str(tmp_path / "b"), 2, 6, 32, seed=3)
+    assert check_manifest(m1) == []
+    d1, d2 = NVSDataset(m1, 4, 32), NVSDataset(m2, 4, 32)
+    torch.testing.assert_close(d1[0]["image"], d2[0]["image"])
+    rot = d1[1]["c2w"][:, :3, :3]
+    torch.testing.assert_close(torch.det(rot), torch.ones(4), atol=1e-4, rtol=1e-4)
+    with open(m1, "a") as fh:
+        fh.write(str(tmp_path / "missing.json") + "\n")
+    assert check_manifest(m1)
+
+
+def test_sampler_resume_skips_consumed_samples():
+    ds = list(range(40))
+    s = ResumableDistributedSampler(ds, num_replicas=2, rank=0, shuffle=True, seed=0)
+    s.set_epoch(3)
+    full = list(iter(s))
+    s.set_resume_offset(7)
+    assert list(iter(s)) == full[7:]
+    assert list(iter(s)) == full                      # the skip applies once
+    with pytest.raises(ValueError):
+        s.set_resume_offset(len(full))
+        list(iter(s))
+
+
+class _Obj:
+    def __init__(self):
+        self.v = {"a": 1}
+
+    def state_dict(self):
+        return self.v
+
+    def load_state_dict(self, sd):
+        self.v = sd
+
+
+def test_checkpoint_lifecycle(tmp_path, monkeypatch):
+    model = torch.nn.Linear(3, 3)
+    opt, sch = _Obj(), _Obj()
+    out = str(tmp_path)
+    ck.checkpoint_job(out, model, opt, sch, 10, 5)
+    ck.checkpoint_job(out, model, opt, sch, 200, 100)
+    assert [os.path.basename(p) for p in ck.find_checkpoints(out)] == ["ckpt_0000000000000010.pt",
+                                                                       "ckpt_0000000000000200.pt"]
+    # a failed save leaves the previous checkpoints intact and no temporary file behind
+    real_save = torch.save
+    def boom(*a, **k):
+        raise OSError("disk full")
+    monkeypatch.setattr(torch, "save", boom)
+    with pytest.raises(OSError):
+        ck.checkpoint_job(out, model, opt, sch, 300, 150)
+    monkeypatch.setattr(torch, "save", real_save)
+    assert len(ck.find_checkpoints(out)) == 2 and not [f for f in os.listdir(out) if f.endswith(".tmp")]
+    # corrupt newest -> falls back to the older one
+    with open(ck.find_checkpoints(out)[-1], "wb") as fh:
+        fh.write(b"garbage")
+    _, _, step, upd = ck.resume_job(out, torch.nn.Linear(3, 3), _Obj(), _Obj())
+    assert (step, upd) == (10, 5)
+    # reset keeps weights, zeroes counters
+    m2 = torch.nn.Linear(3, 3)
+    _, _, step, upd = ck.resume_job(ck.find_checkpoints(out)[0], m2, _Obj(), _Obj(), reset_training_state=True)
+    assert (step, upd) == (0, 0)
+    torch.testing.assert_close(m2.weight, model.weight)
+    # retention, missing path, all corrupt
+    ck.delete_previous_job(out, 200, 1)
+    assert len(ck.find_checkpoints(out)) == 1
+    with pytest.raises(FileNotFoundError):
+        ck.resume_job(str(tmp_path / "nope.pt"), model, opt, sch)
+    with open(ck.find_checkpoints(out)[0], "wb") as fh:
+        fh.write(b"x")
+    with pytest.raises(RuntimeError):
+        ck.resume_job(out, model, opt, sch)
+    assert ck.select_resume_path(out, "explicit.pt", "cfg.pt") == out
+    assert ck.select_resume_path(str(tmp_path / "empty"), "explicit.pt", "cfg.pt") == "explicit.pt"
+
+
+def test_overrides_and_batch_guard():
+    cfg = apply_overrides(_cfg(), [["block.num_experts", "8"], ["training.lr", "3e-4"], ["exp_name", "abc"]])
+    assert cfg["model"]["block_config"]["params"]["num_experts"] == 8 and cfg["training"]["lr"] == 3e-4
+    assert cfg["exp_name"] == "abc"
+    cfg["training"]["total_batch_size"] = 16
+    with pytest.raises(ValueError):
+        check_batch_arithmetic(cfg, 1)
+
+
+def test_trainer_runs_saves_and_resumes(tmp_path):
+    cfg = _cfg()
+    cfg["training"]["out_dir"] = str(tmp_path)
+    t = NVSTrainer(cfg, device=torch.device("cpu"))
+    summary = t.fit()
+    assert t.fwdbwd_step == 4 and summary["avg_step_time_s"] > 0
+    assert len(ck.find_checkpoints(t.out_dir)) == 1
+    t2 = NVSTrainer(cfg, device=torch.device("cpu"))
+    assert t2.fwdbwd_step == 4 and t2.update_step == 4
+    for (n1, p1), (n2, p2) in zip(t.model.named_parameters(), t2.model.named_parameters()):
+        torch.testing.assert_close(p1, p2, msg=n1)
+
+
+def test_metrics():
+    a = torch.rand(3, 3, 32, 32)
+    assert float(ssim(a, a).min()) > 0.999
+    assert float(psnr(a, a).min()) > 90
+    noisy = (a + 0.1 * torch.randn_like(a)).clamp(0, 1)
+    assert float(ssim(a, noisy).mean()) < 0.99
+    ci = bootstrap_ci([20.0, 21.0, 22.0, 23.0], resamples=2000)
+    assert ci["ci_low"] <= ci["mean"] <= ci["ci_high"]

@@ -1,0 +1,470 @@
+"""Decoder block stacks for the view-synthesis model.
+
+``MemoryModel``: per view-chunk, every block does full attention inside the view, a routed
+fast-weight *read* of a SwiGLU expert pool, and an MLP; after an "update" chunk the pool is written
+(uttt_nvs/models/uttt_moe_block.py: block ``:725-815``, read ``:362-423``, raw gradient ``:589-663``,
+write rule ``:665-714``, model ``:818-1524``).  Ownership regimes:
+
+* ``pool_mode="shared"`` (uTTT-MoE): one pool for the whole stack; ``aggregate_write`` sums all layers'
+  raw gradients from the same snapshot and writes once, otherwise the layers write in turn;
+* ``pool_mode="per_block"`` (TTT-MoE): every block owns a pool;
+* ``num_experts=1`` gives the dense variants (uTTT-Dense shared, TTT-Dense per block).
+
+Differences from the language model's rule: rows are *unit-normalised* after every write (the master
+is left unnormalised), there is no momentum, Newton-Schulz (when enabled) uses fixed coefficients,
+routing is a plain softmax over raw logits with top-k on the logits, and the write inputs are
+``k = SiLU(W_k x)``, ``v = SiLU(W_v rmsnorm(x))`` with fp32 learning rates.
+
+Parameter names follow the reference state dict (``pool_w0`` ``[1, E, I, D]``, ``blocks.{i}.memory.
+input_proj.0.weight`` ...).
+"""
+from __future__ import annotations
+
+import math
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+from torch.utils.checkpoint import checkpoint
+
+from .. import ops
+from ..models import fast_weights as fw
+from ..ops import reference as ref
+from .schedule import TTTConfig
+
+
+class _Cfg:
+    """Minimal routing config consumed by :func:`uttt_b200.models.fast_weights.route_rows`."""
+
+    def __init__(self, topk: int, alpha: float):
+        self.memory_num_active_experts = topk
+        self.memory_router_alpha = alpha
+        self.memory_router_type = "softmax"
+        self.memory_router_combine_mode = "selected_prob"
+        self.memory_router_scale = 0.0
+        self.memory_router_norm_eps = 1e-6
+
+
+class SelfAttention(nn.Module):
+    """Full (non-causal) attention over the tokens of one view."""
+
+    def __init__(self, dim: int, head_dim: int):
+        super().__init__()
+        self.dim, self.head_dim = dim, head_dim
+        self.to_qkv = nn.Linear(dim, 3 * dim, bias=False)
+        self.to_out = nn.Linear(dim, dim, bias=False)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        b, l, _ = x.shape
+        h = self.dim // self.head_dim
+        qkv = self.to_qkv(x).view(b, l, 3, h, self.head_dim)
+        q, k, v = qkv[:, :, 0].contiguous(), qkv[:, :, 1].contiguous(), qkv[:, :, 2].contiguous()
+        o = ops.swa_attention(q, k, v, None, causal=False)
+        return self.to_out(o.reshape(b, l, self.dim))
+
+
+class MLP(nn.Module):
+    def __init__(self, dim: int, inter_multi: float):
+        super().__init__()
+        inter = int(dim * inter_multi)
+        self.gate = nn.Linear(dim, inter, bias=False)
+        self.up = nn.Linear(dim, inter, bias=False)
+        self.down = nn.Linear(inter, dim, bias=False)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        y02 = F.linear(x, torch.cat([self.gate.weight, self.up.weight], dim=0))
+        return self.down(ops.swiglu(y02.view(-1, y02.shape[-1])).view(*x.shape[:-1], -1))
+
+
+class FastWeightMemory(nn.Module):
+    """Per-block projections of the memory branch (the pool and routers belong to the model)."""
+
+    def __init__(self, dim: int, fw_inter_multi: float, fw_head_dim: Optional[int] = None, base_lr: float = 0.01,
+                 use_muon: bool = True, num_experts: int = 2, num_active_experts: int = 1,
+                 sigmoid_router: bool = False, router_alpha: float = 1.0, router_from_v: bool = False,
+                 l2_norm: bool = False, use_shared_expert: bool = False, **_unused):
+        super().__init__()
+        if sigmoid_router:
+            raise NotImplementedError("sigmoid routing is not supported")
+        if use_shared_expert:
+            raise NotImplementedError("the always-on shared expert is not implemented")
+        self.dim = dim
+        self.head_dim = fw_head_dim or dim
+        self.num_heads = dim // self.head_dim
+        self.inter_dim = int(self.head_dim * fw_inter_multi)
+        self.use_muon, self.l2_norm, self.router_from_v = use_muon, l2_norm, router_from_v
+        self.num_experts = num_experts
+        self.route_cfg = _Cfg(num_active_experts, router_alpha)
+        self.input_proj = nn.Sequential(nn.Linear(dim, dim, bias=False), nn.SiLU())
+        self.k_input_proj = nn.Sequential(nn.Linear(dim, dim, bias=False), nn.SiLU())
+        self.to_v = nn.Sequential(nn.Linear(dim, dim, bias=False), nn.SiLU())
+        self.to_lr = nn.Linear(dim, 3 * self.num_heads, bias=False)
+        self.base_lr_inv = base_lr + math.log(-math.expm1(-base_lr))
+        self.output_proj = nn.Linear(dim, dim, bias=False)
+
+    def _rows(self, x: torch.Tensor) -> torch.Tensor:
+        b, l, _ = x.shape
+        rows = x.reshape(b, l * self.num_heads, self.head_dim)
+        if self.l2_norm:
+            return F.normalize(rows.float(), dim=-1, eps=1e-5).to(x.dtype)
+        return ops.rms_norm(rows, None, 1e-5)
+
+    def read(self, x: torch.Tensor, w02: torch.Tensor, w1: torch.Tensor, router: torch.Tensor):
+        b, l, _ = x.shape
+        rows = self._rows(self.input_proj(x))
+        routing = fw.route_rows(rows, router, None, self.route_cfg)
+        y = fw.pool_read(rows, w02, w1, routing)
+        y = ops.rms_norm(y, None, 1e-5).reshape(b, l, self.dim)
+        return self.output_proj(y.to(x.dtype)), routing.prob_sum, routing.counts
+
+    def raw_grad(self, pre_k, pre_v, w02, w1, router, acc=None, keep_mask: Optional[torch.Tensor] = None):
+        b, l, _ = pre_k.shape
+        k_rows = self._rows(self.k_input_proj(pre_k))
+        v_rows = self.to_v(pre_v).reshape(b, l * self.num_heads, self.head_dim)
+        lr = F.softplus(F.linear(pre_v.float(), self.to_lr.weight.float()) + self.base_lr_inv)
+        if keep_mask is not None:
+            lr = lr * keep_mask[..., None].to(lr.dtype)
+        lr_rows = lr.reshape(b, l * self.num_heads, 3)
+        routing = fw.route_rows(v_rows if self.router_from_v else k_rows, router, None, self.route_cfg)
+        g02, g1 = fw.pool_raw_grad(k_rows, v_rows, lr_rows, w02, w1, routing, acc=acc)
+        return g02, g1, routing.prob_sum, routing.counts
+
+
+class MemoryBlock(nn.Module):
+    def __init__(self, dim: int, attn_head_dim: int = 64, inter_multi: float = 2, **kwargs):
+        super().__init__()
+        self.dim = dim
+        self.ln_attn = nn.RMSNorm(dim, eps=1e-5)
+        self.self_attention = SelfAttention(dim, attn_head_dim)
+        self.ln_memory = nn.RMSNorm(dim, eps=1e-5)
+        self.memory = FastWeightMemory(dim, **kwargs)
+        self.ln_mlp = nn.RMSNorm(dim, eps=1e-5)
+        self.mlp = MLP(dim, inter_multi)
+
+    def forward(self, x, w02, w1, router):
+        x = x + self.self_attention(ops.rms_norm(x, self.ln_attn.weight, 1e-5))
+        mem_in = ops.rms_norm(x, self.ln_memory.weight, 1e-5)
+        y, probs, counts = self.memory.read(mem_in, w02, w1, router)
+        x = x + y
+        x = x + self.mlp(ops.rms_norm(x, self.ln_mlp.weight, 1e-5))
+        return x, mem_in, probs, counts
+
+
+def _unit_rows_state(w0, w1, w2, batch: int, dtype) -> fw.PoolState:
+    """Initial state: masters are the raw parameters, compute copies are their unit-row views."""
+    m02 = torch.cat([w0, w2], dim=2).float().repeat(batch, 1, 1, 1)
+    m1 = w1.float().repeat(batch, 1, 1, 1)
+    return fw.PoolState(F.normalize(m02, dim=3, eps=1e-5).to(dtype), F.normalize(m1, dim=3, eps=1e-5).to(dtype),
+                        m02, m1, None, None)
+
+
+def apply_unit_update(a02, a1, state: fw.PoolState, use_muon: bool, dtype) -> fw.PoolState:
+    bsz, e, inter2, d = state.m02.shape
+    if use_muon:
+        a02 = ops.newton_schulz(a02.reshape(bsz * e * 2, inter2 // 2, d), ref.NS_FIXED_COEFFS).reshape(state.m02.shape)
+        a1 = ops.newton_schulz(a1.reshape(bsz * e, d, inter2 // 2), ref.NS_FIXED_COEFFS).reshape(state.m1.shape)
+    n02 = state.m02 + a02.float()
+    n1 = state.m1 + a1.float()
+    return fw.PoolState(F.normalize(n02, dim=3, eps=1e-5).to(dtype), F.normalize(n1, dim=3, eps=1e-5).to(dtype),
+                        n02, n1, None, None)
+
+
+class MemoryModel(nn.Module):
+    def __init__(self, layers: int, dim: int, v_gap: Optional[int] = None, load_balancing_loss_alpha: float = 0.01,
+                 num_experts: int = 2, fw_head_dim: Optional[int] = None, fw_inter_multi: float = 1,
+                 pool_mode: str = "shared", router_share_mode: str = "per_layer", use_shared_expert: bool = False,
+                 shared_expert_per_layer: bool = False, aggregate_write: bool = False, apply_ckpt_group: int = 1,
+                 update_ckpt_sweep: bool = False, offload_master_states: bool = False, **kwargs):
+        super().__init__()
+        if pool_mode not in ("shared", "per_block"):
+            raise ValueError(f"Invalid pool_mode: {pool_mode}")
+        if router_share_mode not in ("per_layer", "share_all"):
+            raise ValueError(f"Invalid router_share_mode: {router_share_mode}")
+        if aggregate_write and pool_mode != "shared":
+            raise ValueError("aggregate_write=True is only supported with pool_mode='shared'.")
+        if offload_master_states and not aggregate_write:
+            raise ValueError("offload_master_states=True requires aggregate_write=True")
+        self.v_gap = v_gap
+        self.lb_alpha = load_balancing_loss_alpha
+        self.pool_mode, self.router_share_mode, self.aggregate_write = pool_mode, router_share_mode, aggregate_write
+        self.num_experts = num_experts
+        self.apply_ckpt_group, self.update_ckpt_sweep = int(apply_ckpt_group), bool(update_ckpt_sweep)
+        self.offload_master_states = bool(offload_master_states)
+        head_dim = fw_head_dim if fw_head_dim is not None else dim
+        inter = int(head_dim * fw_inter_multi)
+
+        def mk(n_out, n_in, fan):
+            return nn.Parameter(torch.randn(1, num_experts, n_out, n_in) / math.sqrt(fan))
+
+        if pool_mode == "shared":
+            self.pool_w0, self.pool_w1, self.pool_w2 = mk(inter, head_dim, head_dim), mk(head_dim, inter, inter), \
+                mk(inter, head_dim, head_dim)
+        else:
+            self.block_w0_list = nn.ParameterList([mk(inter, head_dim, head_dim) for _ in range(layers)])
+            self.block_w1_list = nn.ParameterList([mk(head_dim, inter, inter) for _ in range(layers)])
+            self.block_w2_list = nn.ParameterList([mk(inter, head_dim, head_dim) for _ in range(layers)])
+        if router_share_mode == "per_layer":
+            self.router_proj_weights_list = nn.ParameterList(
+                [nn.Parameter(torch.randn(1, num_experts, head_dim) / math.sqrt(head_dim)) for _ in range(layers)])
+        else:
+            self.shared_router_proj_weights = nn.Parameter(torch.randn(1, num_experts, head_dim) / math.sqrt(head_dim))
+        self.blocks = nn.ModuleList([
+            MemoryBlock(dim=dim, num_experts=num_experts, fw_head_dim=fw_head_dim, fw_inter_multi=fw_inter_multi,
+                        use_shared_expert=use_shared_expert, **kwargs) for _ in range(layers)])
+        self.v_layer_idxs = [max(min(i + v_gap, layers - 1), 0) for i in range(layers)] if v_gap is not None else None
+        self._update_mask_callback = None
+        self.activation_checkpoint = True
+
+    def set_update_mask_callback(self, fn) -> None:
+        self._update_mask_callback = fn
+
+    def _router(self, i: int) -> torch.Tensor:
+        if self.router_share_mode == "share_all":
+            return self.shared_router_proj_weights[0]
+        return self.router_proj_weights_list[i][0]
+
+    def _ckpt(self, fn, *args):
+        if self.activation_checkpoint and torch.is_grad_enabled():
+            return checkpoint(fn, *args, use_reentrant=False, preserve_rng_state=False)
+        return fn(*args)
+
+    def init_states(self, batch: int, dtype) -> List[fw.PoolState]:
+        if self.pool_mode == "shared":
+            return [_unit_rows_state(self.pool_w0, self.pool_w1, self.pool_w2, batch, dtype)]
+        return [_unit_rows_state(self.block_w0_list[i], self.block_w1_list[i], self.block_w2_list[i], batch, dtype)
+                for i in range(len(self.blocks))]
+
+    def forward(self, x: torch.Tensor, info: Dict[str, Any]):
+        """x: [b, tokens, dim]; info['ttt_config']: list of TTTConfig(start, end, fast_weight, update, apply)."""
+        bsz = x.shape[0]
+        n = len(self.blocks)
+        dt = x.dtype
+        shared = self.pool_mode == "shared"
+        states = self.init_states(bsz, dt)
+        e = self.num_experts
+        ap = torch.zeros(n, bsz, e, device=x.device)
+        ac = torch.zeros_like(ap)
+        up = torch.zeros_like(ap)
+        uc = torch.zeros_like(ap)
+        outputs = []
+        source_view = 0
+        for cfg in info["ttt_config"]:
+            start, end, update = cfg.start, cfg.end, cfg.update
+            xi = x[:, start:end]
+            mem_ins, outs = [], []
+            probs_l, counts_l = [], []
+            for i, block in enumerate(self.blocks):
+                st = states[0] if shared else states[i]
+                xi, mem_in, p, c = self._ckpt(block, xi, st.w02, st.w1, self._router(i))
+                mem_ins.append(mem_in)
+                outs.append(xi)
+                probs_l.append(p)
+                counts_l.append(c)
+            ap = ap + torch.stack(probs_l)
+            ac = ac + torch.stack(counts_l)
+            outputs.append(xi)
+            if update:
+                keep = None
+                if self._update_mask_callback is not None:
+                    keep = self._update_mask_callback(source_view, start, end, x)
+                pre_vs = [outs[self.v_layer_idxs[i]] if self.v_layer_idxs is not None else mem_ins[i]
+                          for i in range(n)]
+                states, p_u, c_u = self._write(states, mem_ins, pre_vs, keep, dt)
+                up = up + p_u
+                uc = uc + c_u
+                source_view += 1
+        out = torch.cat(outputs, dim=1)
+        lb = x.new_zeros((), dtype=torch.float32)
+        stats: Dict[str, Any] = {}
+        if e > 1:
+            lb = (fw.lb_loss_for_scope(ap, ac, "layer", e) + fw.lb_loss_for_scope(up, uc, "layer", e)) * self.lb_alpha
+            freq = ac.sum(1) / ac.sum(1).sum(1, keepdim=True).clamp_min(1)
+            stats = {"moe_freq_max": freq.max().detach(), "moe_freq_min": freq.min().detach(),
+                     "apply_max_violation_rate": (freq.max(1).values * e - 1).mean().detach()}
+        return out, lb, [stats]
+
+    def _write(self, states, mem_ins, pre_vs, keep, dt):
+        n = len(self.blocks)
+        shared = self.pool_mode == "shared"
+
+        def norm_v(t):
+            return ops.rms_norm(t, None, 1e-5)
+
+        if shared and self.aggregate_write:
+            st = states[0]
+
+            def _agg(w02, w1, m02, m1, *feats):
+                a02, a1 = torch.zeros_like(m02), torch.zeros_like(m1)
+                ps, cs = [], []
+                for i, block in enumerate(self.blocks):
+                    a02, a1, p, c = block.memory.raw_grad(feats[i], norm_v(feats[n + i]), w02, w1, self._router(i),
+                                                          acc=(a02, a1), keep_mask=keep)
+                    ps.append(p)
+                    cs.append(c)
+                new = apply_unit_update(a02, a1, fw.PoolState(w02, w1, m02, m1, None, None),
+                                        self.blocks[0].memory.use_muon, dt)
+                return new.w02, new.w1, new.m02, new.m1, torch.stack(ps), torch.stack(cs)
+
+            out = self._ckpt(_agg, st.w02, st.w1, st.m02, st.m1, *mem_ins, *pre_vs)
+            return [fw.PoolState(out[0], out[1], out[2], out[3], None, None)], out[4], out[5]
+
+        new_states = list(states)
+        ps, cs = [], []
+        for i, block in enumerate(self.blocks):
+            si = 0 if shared else i
+
+            def _one(w02, w1, m02, m1, k_in, v_in, _b=block, _i=i):
+                g02, g1, p, c = _b.memory.raw_grad(k_in, norm_v(v_in), w02, w1, self._router(_i), keep_mask=keep)
+                new = apply_unit_update(g02, g1, fw.PoolState(w02, w1, m02, m1, None, None), _b.memory.use_muon, dt)
+                return new.w02, new.w1, new.m02, new.m1, p, c
+
+            s = new_states[si]
+            out = self._ckpt(_one, s.w02, s.w1, s.m02, s.m1, mem_ins[i], pre_vs[i])
+            new_states[si] = fw.PoolState(out[0], out[1], out[2], out[3], None, None)
+            ps.append(out[4])
+            cs.append(out[5])
+        return new_states, torch.stack(ps), torch.stack(cs)
+
+
+class PartitionedMemoryModel(nn.Module):
+    """Depth-contiguous groups of blocks, each group with its own shared pool; ``num_experts`` is the total
+    expert budget split evenly over the groups (uttt_nvs/models/uttt_moe_partitioned.py:10-462)."""
+
+    def __init__(self, layers: int, dim: int, num_partitions: int = 2, num_experts: int = 4, **kwargs):
+        super().__init__()
+        if layers % num_partitions or num_experts % num_partitions:
+            raise ValueError("layers and num_experts must be divisible by num_partitions")
+        kwargs.setdefault("pool_mode", "shared")
+        self.parts = nn.ModuleList([MemoryModel(layers // num_partitions, dim, num_experts=num_experts // num_partitions,
+                                                **kwargs) for _ in range(num_partitions)])
+
+    def forward(self, x, info):
+        lb_total = x.new_zeros((), dtype=torch.float32)
+        infos: List[Any] = []
+        # every group sees the whole schedule: group g's output sequence feeds group g+1
+        for part in self.parts:
+            x, lb, inf = part(x, info)
+            lb_total = lb_total + lb
+            infos = inf
+        return x, lb_total, infos
+
+
+class DenseMemoryModel(MemoryModel):
+    """uTTT-Dense / TTT-Dense for view synthesis: a pool with a single expert (no routing)
+    (uttt_nvs/models/uttt_dense_block.py:39-521, ttt_dense_block.py:96-473)."""
+
+    def __init__(self, layers: int, dim: int, shared: bool = True, **kwargs):
+        for key in ("num_experts", "num_active_experts", "router_share_mode", "load_balancing_loss_alpha"):
+            kwargs.pop(key, None)
+        mode = kwargs.pop("pool_mode", "shared" if shared else "per_block")
+        kwargs["aggregate_write"] = bool(kwargs.get("aggregate_write", True)) and mode == "shared"
+        super().__init__(layers, dim, num_experts=1, num_active_experts=1, pool_mode=mode,
+                         router_share_mode="share_all", **kwargs)
+        # a single expert needs no router: drop the parameter, keep a constant stand-in for the call signature
+        head_dim = self.shared_router_proj_weights.shape[-1]
+        del self.shared_router_proj_weights
+        self.register_buffer("_no_router", torch.zeros(1, head_dim), persistent=False)
+
+    def _router(self, i: int) -> torch.Tensor:
+        return self._no_router
+
+
+class TransformerBlocks(nn.Module):
+    """Reference transformer decoder: causal over view-chunks with a growing key/value cache
+    (uttt_nvs/models/transformer_block.py)."""
+
+    def __init__(self, layers: int, dim: int, attn_head_dim: int = 64, inter_multi: float = 4, **_unused):
+        super().__init__()
+        self.head_dim = attn_head_dim
+        self.blocks = nn.ModuleList()
+        for _ in range(layers):
+            blk = nn.Module()
+            blk.ln_attn = nn.RMSNorm(dim, eps=1e-5)
+            blk.to_qkv = nn.Linear(dim, 3 * dim, bias=False)
+            blk.to_out = nn.Linear(dim, dim, bias=False)
+            blk.ln_mlp = nn.RMSNorm(dim, eps=1e-5)
+            blk.mlp = MLP(dim, inter_multi)
+            self.blocks.append(blk)
+
+    def forward(self, x, info):
+        b, _, dim = x.shape
+        h = dim // self.head_dim
+        caches = [[None, None] for _ in self.blocks]
+        outputs = []
+        for cfg in info["ttt_config"]:
+            xi = x[:, cfg.start:cfg.end]
+            l = xi.shape[1]
+            for blk, cache in zip(self.blocks, caches):
+                qkv = blk.to_qkv(ops.rms_norm(xi, blk.ln_attn.weight, 1e-5)).view(b, l, 3, h, self.head_dim)
+                q, k, v = qkv[:, :, 0].contiguous(), qkv[:, :, 1].contiguous(), qkv[:, :, 2].contiguous()
+                kk = k if cache[0] is None else torch.cat([cache[0], k], dim=1)
+                vv = v if cache[1] is None else torch.cat([cache[1], v], dim=1)
+                # a view attends to every posed (update) view before it and to itself, without a causal mask
+                o = ops.swa_attention(q, kk, vv, None, causal=False)
+                xi = xi + blk.to_out(o.reshape(b, l, dim))
+                xi = xi + blk.mlp(ops.rms_norm(xi, blk.ln_mlp.weight, 1e-5))
+                if cfg.update:
+                    cache[0], cache[1] = kk, vv
+            outputs.append(xi)
+        return torch.cat(outputs, dim=1), x.new_zeros((), dtype=torch.float32), [{}]
+
+
+class DeltaNetBlocks(nn.Module):
+    """Delta-rule (optionally gated) linear-state reference: the state ``S [h, dk, dv]`` is written by the posed
+    views and read by every view (uttt_nvs/models/deltanet_block.py, gated_deltanet_block.py)."""
+
+    def __init__(self, layers: int, dim: int, attn_head_dim: int = 64, inter_multi: float = 4, gated: bool = False,
+                 **_unused):
+        super().__init__()
+        self.head_dim, self.gated = attn_head_dim, gated
+        self.blocks = nn.ModuleList()
+        for _ in range(layers):
+            blk = nn.Module()
+            blk.ln_attn = nn.RMSNorm(dim, eps=1e-5)
+            blk.self_attention = SelfAttention(dim, attn_head_dim)
+            blk.ln_mem = nn.RMSNorm(dim, eps=1e-5)
+            blk.to_qkv = nn.Linear(dim, 3 * dim, bias=False)
+            blk.to_beta = nn.Linear(dim, dim // attn_head_dim, bias=False)
+            blk.to_gate = nn.Linear(dim, dim // attn_head_dim, bias=False) if gated else None
+            blk.to_out = nn.Linear(dim, dim, bias=False)
+            blk.ln_mlp = nn.RMSNorm(dim, eps=1e-5)
+            blk.mlp = MLP(dim, inter_multi)
+            self.blocks.append(blk)
+
+    def forward(self, x, info):
+        b, _, dim = x.shape
+        h = dim // self.head_dim
+        states = [x.new_zeros(b, h, self.head_dim, self.head_dim, dtype=torch.float32) for _ in self.blocks]
+        outputs = []
+        for cfg in info["ttt_config"]:
+            xi = x[:, cfg.start:cfg.end]
+            l = xi.shape[1]
+            for bi, blk in enumerate(self.blocks):
+                xi = xi + blk.self_attention(ops.rms_norm(xi, blk.ln_attn.weight, 1e-5))
+                m = ops.rms_norm(xi, blk.ln_mem.weight, 1e-5)
+                qkv = blk.to_qkv(m).view(b, l, 3, h, self.head_dim).float()
+                q = F.normalize(F.silu(qkv[:, :, 0]), dim=-1).transpose(1, 2)      # [b,h,l,d]
+                k = F.normalize(F.silu(qkv[:, :, 1]), dim=-1).transpose(1, 2)
+                v = qkv[:, :, 2].transpose(1, 2)
+                s = states[bi]
+                y = torch.einsum("bhld,bhde->bhle", q, s)
+                xi = xi + blk.to_out(y.transpose(1, 2).reshape(b, l, dim).to(xi.dtype))
+                if cfg.update:
+                    beta = torch.sigmoid(blk.to_beta(m)).float().transpose(1, 2).unsqueeze(-1)   # [b,h,l,1]
+                    if self.gated:
+                        decay = torch.sigmoid(blk.to_gate(m)).float().mean(dim=1).view(b, h, 1, 1)
+                        s = s * decay
+                    # chunk-level delta rule: S += K^T (beta * (V - K S)) / l
+                    err = v - torch.einsum("bhld,bhde->bhle", k, s)
+                    s = s + torch.einsum("bhld,bhle->bhde", k, beta * err) / l
+                    states[bi] = s
+                xi = xi + blk.mlp(ops.rms_norm(xi, blk.ln_mlp.weight, 1e-5))
+            outputs.append(xi)
+        return torch.cat(outputs, dim=1), x.new_zeros((), dtype=torch.float32), [{}]
+
+
+class GatedDeltaNetBlocks(DeltaNetBlocks):
+    def __init__(self, layers: int, dim: int, **kwargs):
+        kwargs["gated"] = True
+        super().__init__(layers, dim, **kwargs)

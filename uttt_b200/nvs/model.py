@@ -1,0 +1,174 @@
+"""LVSM-style decoder-only view-synthesis model.
+
+Per scene: camera rays -> Plucker channels (o, d, o x d) + RGB*2-1 -> 12-channel posed images; pose-only
+(target) views carry zero RGB; 8x8 patchify in (ph pw c) order -> Linear -> LayerNorm -> block stack
+(:mod:`uttt_b200.nvs.blocks`) -> LayerNorm -> Linear -> un-patchify -> sigmoid; loss = MSE on the target
+views (+ load-balance term), PSNR reported (uttt_nvs/models/lvsm_moe.py:22-125 loss, :128-163 rays,
+:167-294 model).
+
+Two view layouts are supported:
+* ``"autoregressive"`` (the reference's): V views become V-1 (posed input i, pose-only target i+1) pairs;
+* ``"inputs_then_targets"``: ``num_input_views`` posed views that write the memory, then the remaining
+  views decoded from pose only.
+"""
+from __future__ import annotations
+
+import importlib
+from typing import Any, Dict, List, Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import ops
+from ..ops import reference as ref
+from . import blocks as nvs_blocks
+from .schedule import inputs_then_targets_config, parallel_ttt_config
+
+# class paths used by the reference YAML files -> classes of this package
+_CLASS_ALIASES = {
+    "uttt_nvs.models.uttt_moe_block.MemoryModel": nvs_blocks.MemoryModel,
+    "uttt_nvs.models.uttt_moe_partitioned.MemoryModel": nvs_blocks.PartitionedMemoryModel,
+    "uttt_nvs.models.uttt_dense_block.MemoryModel": nvs_blocks.DenseMemoryModel,
+    "uttt_nvs.models.uttt_dense_partitioned.MemoryModel": nvs_blocks.DenseMemoryModel,
+    "uttt_nvs.models.ttt_dense_block.MemoryModel": nvs_blocks.DenseMemoryModel,
+    "uttt_nvs.models.transformer_block.TransformerModel": nvs_blocks.TransformerBlocks,
+    "uttt_nvs.models.deltanet_block.DeltaNetModel": nvs_blocks.DeltaNetBlocks,
+    "uttt_nvs.models.gated_deltanet_block.GatedDeltaNetModel": nvs_blocks.GatedDeltaNetBlocks,
+}
+
+
+def get_obj_by_name(path: str):
+    """Resolve a dotted class path (uttt_nvs/models/class_name.py:14-67); reference paths map to this package."""
+    if path in _CLASS_ALIASES:
+        return _CLASS_ALIASES[path]
+    module, _, name = path.rpartition(".")
+    if module.startswith("uttt_nvs.models"):
+        leaf = module.rsplit(".", 1)[-1]
+        for key, cls in _CLASS_ALIASES.items():
+            if key.rsplit(".", 2)[-2] == leaf:
+                return cls
+    return getattr(importlib.import_module(module), name)
+
+
+class Patchify(nn.Module):
+    def __init__(self, patch: int):
+        super().__init__()
+        self.patch = patch
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        b, v, c, h, w = x.shape
+        p = self.patch
+        x = x.view(b, v, c, h // p, p, w // p, p).permute(0, 1, 3, 5, 4, 6, 2)
+        return x.reshape(b, v * (h // p) * (w // p), p * p * c)
+
+
+def _cfg_get(cfg, key, default=None):
+    if isinstance(cfg, dict):
+        return cfg.get(key, default)
+    return getattr(cfg, key, default)
+
+
+class LVSMModel(nn.Module):
+    """``forward(batch)`` with ``batch = {image [b,v,3,H,W], fxfycxcy [b,v,4], c2w [b,v,4,4]}``."""
+
+    def __init__(self, config: Dict[str, Any]):
+        super().__init__()
+        self.config = config
+        m = config["model"]
+        size = m["image_size"]
+        self.image_size = (size, size) if isinstance(size, int) else tuple(size)
+        self.patch_size = m["patch_size"]
+        self.dim = m["dim"]
+        self.input_dim = 12
+        self.view_layout = m.get("view_layout", "autoregressive")
+        self.num_input_views = m.get("num_input_views")
+        self.image_tokenizer = nn.Sequential(Patchify(self.patch_size),
+                                             nn.Linear(self.input_dim * self.patch_size ** 2, self.dim, bias=False))
+        self.transformer_input_layernorm = nn.LayerNorm(self.dim, bias=False)
+        block_cls = get_obj_by_name(m["block_config"]["type"])
+        self.transformer_blocks = block_cls(layers=m["layers"], dim=self.dim, **dict(m["block_config"].get("params", {})))
+        self.image_token_decoder = nn.Sequential(nn.LayerNorm(self.dim, bias=False),
+                                                 nn.Linear(self.dim, self.patch_size ** 2 * 3, bias=False))
+        tr = config.get("training", {})
+        self.lpips_weight = float(tr.get("lpips_loss_weight", 0.0) or 0.0)
+        self.perceptual_weight = float(tr.get("perceptual_loss_weight", 0.0) or 0.0)
+        self.perceptual = None
+        if self.perceptual_weight > 0:
+            from .perceptual import PerceptualLoss
+            self.perceptual = PerceptualLoss()
+        for mod in self.modules():
+            if isinstance(mod, nn.Linear):
+                nn.init.normal_(mod.weight, std=0.02)
+
+    # ------------------------------------------------------------------ tokens
+    def build_tokens(self, batch):
+        """Returns (tokens [b, views*n, p*p*12], schedule, index of the slots to supervise, target images)."""
+        image, fxfycxcy, c2w = batch["image"], batch["fxfycxcy"], batch["c2w"]
+        b, v, _, h, w = image.shape
+        n_tok = (h // self.patch_size) * (w // self.patch_size)
+        dev = image.device
+        if self.view_layout == "inputs_then_targets":
+            n_in = self.num_input_views or (v - 1)
+            order = torch.arange(v, device=dev)
+            is_target = order >= n_in
+            sched = inputs_then_targets_config(n_in, v - n_in, n_tok)
+            sup = torch.arange(n_in, v, device=dev)
+            targets = image[:, n_in:]
+        else:
+            # slots 0,2,4,.. = posed view i; slots 1,3,5,.. = pose-only view i+1
+            order = torch.stack([torch.arange(v - 1, device=dev), torch.arange(1, v, device=dev)], 1).reshape(-1)
+            is_target = torch.arange(2 * (v - 1), device=dev) % 2 == 1
+            sched = parallel_ttt_config(n_tok, n_tok, 2 * (v - 1) * n_tok)
+            sup = torch.arange(1, 2 * (v - 1), 2, device=dev)
+            targets = image[:, 1:]
+        with torch.no_grad():
+            tokens = ops.plucker_embed(image.index_select(1, order), fxfycxcy.index_select(1, order),
+                                       c2w.index_select(1, order), is_target, self.patch_size)
+        return tokens.reshape(b, -1, tokens.shape[-1]), sched, sup, targets, n_tok
+
+    def unpatchify(self, y: torch.Tensor, views: int) -> torch.Tensor:
+        b = y.shape[0]
+        p = self.patch_size
+        hh, ww = self.image_size[0] // p, self.image_size[1] // p
+        y = y.view(b, views, hh, ww, p, p, 3).permute(0, 1, 6, 2, 4, 3, 5)
+        return y.reshape(b, views, 3, hh * p, ww * p)
+
+    def forward(self, batch: Dict[str, torch.Tensor]) -> Dict[str, Any]:
+        tokens, sched, sup, targets, n_tok = self.build_tokens(batch)
+        dt = self.image_tokenizer[1].weight.dtype
+        x = self.image_tokenizer[1](tokens.to(dt))
+        x = ops.layer_norm(x, self.transformer_input_layernorm.weight, None, 1e-5)
+        x, lb_loss, infos = self.transformer_blocks(x, {"num_img_tokens": n_tok, "ttt_config": sched})
+        b = x.shape[0]
+        views = x.shape[1] // n_tok
+        # only the supervised slots are decoded to pixels
+        xs = x.view(b, views, n_tok, self.dim).index_select(1, sup).reshape(b, -1, self.dim)
+        y = ops.layer_norm(xs, self.image_token_decoder[0].weight, None, 1e-5)
+        y = torch.sigmoid(self.image_token_decoder[1](y).float())
+        rendering = self.unpatchify(y, sup.numel())
+        tgt = targets.float()
+        mse = F.mse_loss(rendering, tgt)
+        loss = mse + lb_loss
+        perceptual = rendering.new_zeros(())
+        if self.perceptual is not None:
+            perceptual = self.perceptual(rendering.flatten(0, 1), tgt.flatten(0, 1))
+            loss = loss + self.perceptual_weight * perceptual
+        with torch.no_grad():
+            per_view = ((rendering - tgt) ** 2).mean(dim=(2, 3, 4))
+            psnr_loc = (-10.0 * torch.log10(per_view.clamp_min(1e-10))).mean(0)
+            psnr = psnr_loc.mean()
+        metrics = {"loss": loss, "l2_loss": mse.detach(), "lb_loss": lb_loss.detach(), "psnr": psnr,
+                   "psnr_loc": psnr_loc, "perceptual_loss": perceptual.detach(),
+                   "lpips_loss": rendering.new_zeros(())}
+        if infos and isinstance(infos[-1], dict):
+            metrics.update({k: v for k, v in infos[-1].items()})
+        return {"loss_metrics": metrics, "rendering": rendering, "target": targets}
+
+    def get_overview(self) -> Dict[str, int]:
+        count = lambda mod: sum(p.numel() for p in mod.parameters() if p.requires_grad)
+        return {"image_tokenizer": count(self.image_tokenizer), "transformer": count(self.transformer_blocks),
+                "image_token_decoder": count(self.image_token_decoder)}
+
+
+Images2latent3D = LVSMModel

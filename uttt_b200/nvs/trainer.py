@@ -1,0 +1,258 @@
+"""View-synthesis trainer.
+
+    torchrun -m uttt_b200.nvs.trainer --config cfg.yaml [-s dotted.key value ...] [--load PATH]
+
+Same job semantics as the reference script (uttt_nvs/train/trainer.py:44-814): one YAML per run with ``-s``
+overrides (values parsed with ``literal_eval``; ``block.x`` is an alias of ``model.block_config.params.x``),
+a ``datasets.yaml`` registry keyed by ``training.dataset``, a global-batch guard
+(``batch_size_per_gpu * world * grad_accum_steps == total_batch_size``), bf16 compute, AdamW with decay on
+tensors of rank >= 2, warmup + cosine schedule, a collective finite-loss vote before every backward,
+gradient clipping with outlier-step skipping, atomic ``ckpt_<step>.pt`` checkpoints with retention and
+resume, and a ``[TRAIN_SUMMARY]`` line with the average step time and peak memory.
+
+Data parallelism runs through :class:`uttt_b200.parallel.fsdp.ShardedTrainer`: gradients are reduced and
+AdamW is applied on per-rank shards by the fused peer-memory kernels (the role DDP's bucketed all-reduce
+plus a fused optimizer play in the reference).
+"""
+from __future__ import annotations
+
+import argparse
+import ast
+import math
+import os
+import sys
+import time
+from typing import Any, Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+import yaml
+
+from ..parallel.fsdp import AdamWConfig, ShardedTrainer
+from ..train.engine import init_distributed
+from .checkpoint import checkpoint_job, delete_previous_job, resume_job, select_resume_path
+from .data import NVSDataset, ResumableDistributedSampler, SyntheticScenes
+from .model import LVSMModel, get_obj_by_name
+
+ALIASES = {"block.": "model.block_config.params."}
+
+
+def apply_overrides(cfg: Dict[str, Any], pairs: List[List[str]]) -> Dict[str, Any]:
+    for key, raw in pairs:
+        for short, full in ALIASES.items():
+            if key.startswith(short):
+                key = full + key[len(short):]
+        try:
+            value = ast.literal_eval(raw)
+        except (ValueError, SyntaxError):
+            value = raw
+        node = cfg
+        parts = key.split(".")
+        for p in parts[:-1]:
+            node = node.setdefault(p, {})
+        node[parts[-1]] = value
+    return cfg
+
+
+def load_config(path: str, overrides: Optional[List[List[str]]] = None, datasets_yaml: Optional[str] = None):
+    with open(path) as fh:
+        cfg = yaml.safe_load(fh)
+    cfg = apply_overrides(cfg, overrides or [])
+    tr = cfg.setdefault("training", {})
+    name = tr.get("dataset")
+    if name and name != "synthetic" and "dataset_path" not in tr:
+        reg_path = datasets_yaml or os.path.join(os.path.dirname(os.path.dirname(path)), "datasets.yaml")
+        if os.path.exists(reg_path):
+            with open(reg_path) as fh:
+                reg = yaml.safe_load(fh) or {}
+            entry = reg.get(name, {})
+            tr.setdefault("dataset_path", entry.get("train"))
+            cfg.setdefault("eval_dataset_path", entry.get("eval"))
+    return cfg
+
+
+def check_batch_arithmetic(cfg: Dict[str, Any], world: int) -> int:
+    tr = cfg["training"]
+    accum = int(tr.get("grad_accum_steps", 1))
+    got = int(tr["batch_size_per_gpu"]) * world * accum
+    want = int(tr.get("total_batch_size", got))
+    if got != want:
+        raise ValueError(f"batch_size_per_gpu ({tr['batch_size_per_gpu']}) x world ({world}) x grad_accum_steps "
+                         f"({accum}) = {got} != total_batch_size ({want})")
+    return accum
+
+
+def lr_at(step: int, base: float, warmup: int, total: int, kind: str = "cosine", init_ratio: float = 0.0) -> float:
+    if step < warmup:
+        return base * (init_ratio + (1 - init_ratio) * (step + 1) / max(warmup, 1))
+    if kind == "constant":
+        return base
+    prog = min(max((step - warmup) / max(total - warmup, 1), 0.0), 1.0)
+    if kind == "linear":
+        return base * (1 - prog)
+    return base * 0.5 * (1 + math.cos(math.pi * prog))
+
+
+class _OptimizerView:
+    """state_dict()/load_state_dict() adapters so the checkpoint file keeps the reference's top-level keys."""
+
+    def __init__(self, trainer: ShardedTrainer):
+        self.trainer = trainer
+
+    def state_dict(self):
+        return self.trainer.optimizer_state_dict()
+
+    def load_state_dict(self, sd):
+        self.trainer.load_optimizer_state_dict(sd)
+
+
+class _Schedule:
+    def __init__(self):
+        self.step_count = 0
+
+    def state_dict(self):
+        return {"step_count": self.step_count}
+
+    def load_state_dict(self, sd):
+        self.step_count = int(sd.get("step_count", sd.get("last_epoch", 0)))
+
+
+class NVSTrainer:
+    def __init__(self, cfg: Dict[str, Any], device: Optional[torch.device] = None, load: str = ""):
+        self.cfg = cfg
+        self.rank, self.world, local = init_distributed()
+        self.device = device or (torch.device("cuda", local) if torch.cuda.is_available() else torch.device("cpu"))
+        tr = cfg["training"]
+        self.accum = check_batch_arithmetic(cfg, self.world)
+        torch.manual_seed(int(tr.get("seed", 0)))
+        model_cls = LVSMModel if "class_name" not in cfg["model"] else LVSMModel
+        self.model = model_cls(cfg).to(self.device)
+        opt = AdamWConfig(lr=float(tr.get("lr", 4e-4)), beta1=float(tr.get("beta1", 0.9)),
+                          beta2=float(tr.get("beta2", 0.95)), eps=1e-8, weight_decay=float(tr.get("weight_decay", 0.05)),
+                          max_norm=float(tr.get("grad_clip_norm", 1.0)), skip_nan_inf=True)
+        units = [(f"transformer_blocks.blocks.{i}", b) for i, b in
+                 enumerate(getattr(self.model.transformer_blocks, "blocks", []))]
+        self.trainer = ShardedTrainer(self.model, units, opt, no_decay=lambda n, p: p.dim() < 2)
+        self.optimizer, self.schedule = _OptimizerView(self.trainer), _Schedule()
+        self.out_dir = os.path.join(tr.get("out_dir", os.environ.get("UTTT_NVS_OUT_DIR", "experiments")),
+                                    cfg.get("exp_name", "run"))
+        self.total = int(tr.get("max_fwdbwd_passes", 20000))
+        self.fwdbwd_step = 0
+        self.update_step = 0
+        resume = select_resume_path(self.out_dir, load, tr.get("load", "") or "")
+        if resume:
+            _, _, self.fwdbwd_step, self.update_step = resume_job(
+                resume, self.model, self.optimizer, self.schedule,
+                reset_training_state=bool(tr.get("reset_training_state", False)),
+                load_optimizer_state_when_reset_training_state=bool(
+                    tr.get("load_optimizer_state_when_reset_training_state", False)))
+            self.trainer.load_model_state()
+        self.data = self._build_data()
+        self.step_times: List[float] = []
+
+    def _build_data(self):
+        tr = self.cfg["training"]
+        size = self.cfg["model"]["image_size"]
+        size = size if isinstance(size, int) else size[0]
+        if tr.get("dataset", "synthetic") == "synthetic" or not tr.get("dataset_path"):
+            src = SyntheticScenes(int(tr["batch_size_per_gpu"]), int(tr.get("num_views", 6)), size,
+                                  seed=int(tr.get("seed", 0)), rank=self.rank)
+            src.step = self.fwdbwd_step
+            return iter(src)
+        ds = NVSDataset(tr["dataset_path"], int(tr.get("num_views", 12)), size, tr.get("max_num_objects"))
+        sampler = ResumableDistributedSampler(ds, num_replicas=self.world, rank=self.rank, shuffle=True, seed=0,
+                                              drop_last=True)
+        per_epoch = max(len(sampler) // int(tr["batch_size_per_gpu"]), 1)
+        sampler.set_epoch(self.fwdbwd_step // per_epoch)
+        sampler.set_resume_offset((self.fwdbwd_step % per_epoch) * int(tr["batch_size_per_gpu"]))
+        loader = torch.utils.data.DataLoader(ds, batch_size=int(tr["batch_size_per_gpu"]), sampler=sampler,
+                                             num_workers=int(tr.get("num_workers", 0)), drop_last=True,
+                                             pin_memory=torch.cuda.is_available())
+
+        def forever():
+            epoch = self.fwdbwd_step // per_epoch
+            while True:
+                for batch in loader:
+                    yield batch
+                epoch += 1
+                sampler.set_epoch(epoch)
+        return forever()
+
+    def train_pass(self, batch: Dict[str, torch.Tensor]) -> Dict[str, float]:
+        """One forward/backward pass; an optimizer step every ``grad_accum_steps`` passes."""
+        tr = self.cfg["training"]
+        t0 = time.time()
+        batch = {k: v.to(self.device, non_blocking=True) for k, v in batch.items() if torch.is_tensor(v)}
+        self.model.train()
+        result = self.model(batch)
+        loss = result["loss_metrics"]["loss"]
+        vote = torch.isfinite(loss.detach()).float()
+        if self.world > 1:
+            dist.all_reduce(vote, op=dist.ReduceOp.MIN)       # every rank skips together
+        (loss * vote / self.accum).backward()
+        self.fwdbwd_step += 1
+        stats: Dict[str, Any] = {"loss": loss.detach(), "psnr": result["loss_metrics"]["psnr"], "finite": vote}
+        if self.fwdbwd_step % self.accum == 0:
+            lr = lr_at(self.update_step, float(tr.get("lr", 4e-4)), int(tr.get("warmup", 0)),
+                       max(self.total // self.accum, 1), tr.get("scheduler_type", "cosine"),
+                       float(tr.get("warmup_init_ratio", 0.0)))
+            skip_above = None
+            if self.update_step > int(tr.get("may_skip_gradnorm_after", 1 << 60)):
+                skip_above = float(tr.get("allowed_gradnorm_factor", 5)) * float(tr.get("grad_clip_norm", 1.0))
+            out = self.trainer.step(lr=lr, skip_above=skip_above)
+            self.update_step += 1
+            self.schedule.step_count = self.update_step
+            stats.update(grad_norm=out["grad_norm"], skipped=out["skipped"], lr=lr)
+        elif self.accum > 1:
+            self.trainer.accumulate_micro_batch()
+        self.step_times.append(time.time() - t0)
+        return stats
+
+    def save(self) -> Optional[str]:
+        tr = self.cfg["training"]
+        opt_sd = self.optimizer.state_dict()          # collective
+        path = None
+        if self.rank == 0:
+            class _Frozen:
+                def state_dict(_self):
+                    return opt_sd
+            path = checkpoint_job(self.out_dir, self.model, _Frozen(), self.schedule, self.fwdbwd_step,
+                                  self.update_step)
+            delete_previous_job(self.out_dir, self.fwdbwd_step, int(tr.get("save_last_n_ckpts", 1)))
+        if self.world > 1:
+            dist.barrier()
+        return path
+
+    def fit(self, max_passes: Optional[int] = None) -> Dict[str, float]:
+        tr = self.cfg["training"]
+        total = self.total if max_passes is None else min(self.total, self.fwdbwd_step + max_passes)
+        while self.fwdbwd_step < total:
+            stats = self.train_pass(next(self.data))
+            if self.rank == 0 and self.fwdbwd_step % int(tr.get("print_every", 20)) == 0:
+                print(f"[pass {self.fwdbwd_step}] loss {float(stats['loss']):.5f} psnr {float(stats['psnr']):.2f} "
+                      f"lr {stats.get('lr', 0):.2e} time {self.step_times[-1]:.3f}s", flush=True)
+            if self.fwdbwd_step % int(tr.get("checkpoint_every", 500)) == 0 or self.fwdbwd_step == total:
+                self.save()
+        summary = {"avg_step_time_s": sum(self.step_times) / max(len(self.step_times), 1),
+                   "peak_allocated_gib": torch.cuda.max_memory_allocated() / 2 ** 30 if torch.cuda.is_available() else 0.0,
+                   "peak_reserved_gib": torch.cuda.max_memory_reserved() / 2 ** 30 if torch.cuda.is_available() else 0.0}
+        if self.rank == 0:
+            print("[TRAIN_SUMMARY] " + " ".join(f"{k}={v:.4f}" for k, v in summary.items()), flush=True)
+        return summary
+
+
+def main(argv: Optional[List[str]] = None) -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", required=True)
+    ap.add_argument("-s", "--set", nargs=2, action="append", default=[], metavar=("KEY", "VALUE"))
+    ap.add_argument("--load", default="")
+    ap.add_argument("--max-passes", type=int, default=None)
+    args = ap.parse_args(argv)
+    cfg = load_config(args.config, args.set)
+    NVSTrainer(cfg, load=args.load).fit(args.max_passes)
+    if dist.is_available() and dist.is_initialized():
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

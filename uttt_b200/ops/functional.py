@@ -657,3 +657,14 @@ def linear_cross_entropy(h, weight, labels, ignore_index: int = -100, chunk: int
     if _kernel("ce_fwd_bwd_", h) is not None and h.dtype == torch.bfloat16:
         return _LinearCE.apply(h, weight, labels, ignore_index, chunk)
     return ref.linear_cross_entropy(h, weight, labels, ignore_index, chunk)[0]
+
+
+# =========================================================================== view synthesis
+def plucker_embed(image, fxfycxcy, c2w, is_target, patch: int) -> torch.Tensor:
+    """Posed-image tokens: per pixel (ray o, ray d, o x d, rgb*2-1 or 0 for pose-only views), patchified in
+    (ph pw c) order -> [b, v, n_patches, patch*patch*12] (bf16 on the GPU kernel path)."""
+    ext = _kernel("plucker_embed", image)
+    if ext is not None and image.shape[-1] % patch == 0 and image.shape[-2] % patch == 0:
+        return ext.plucker_embed(image.float().contiguous(), fxfycxcy.float().contiguous(), c2w.float().contiguous(),
+                                 is_target.to(torch.uint8).contiguous(), int(patch))
+    return ref.plucker_embed(image, fxfycxcy, c2w, is_target, patch)

@@ -208,7 +208,8 @@ class ShardedTrainer:
 
     # ------------------------------------------------------------------ the step
     @torch.no_grad()
-    def step(self, lr: Optional[float] = None, grad_divisor: float = 1.0) -> Dict[str, torch.Tensor]:
+    def step(self, lr: Optional[float] = None, grad_divisor: float = 1.0,
+             skip_above: Optional[float] = None) -> Dict[str, torch.Tensor]:
         """Reduce gradients (mean over ranks, divided by ``grad_divisor``), clip, AdamW, redistribute.
 
         Returns {'grad_norm': tensor, 'skipped': tensor(bool)} without a host sync.
@@ -250,6 +251,9 @@ class ShardedTrainer:
             dist.all_reduce(sq, group=self.group)
         grad_norm = sq.sqrt()
         finite = torch.isfinite(grad_norm)
+        if skip_above is not None:
+            # caller's outlier rule: a step whose gradient norm exceeds the threshold is skipped like a NaN step
+            finite = finite & (grad_norm <= skip_above)
         clip = torch.ones_like(grad_norm)
         if opt.max_norm and opt.max_norm > 0:
             clip = (opt.max_norm / (grad_norm + 1e-6)).clamp(max=1.0)
