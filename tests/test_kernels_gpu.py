@@ -318,6 +318,16 @@ def test_swa_attention_forward_backward(hd, lq, lk, window, causal):
     _close(gv, gvr, 5e-2, 5e-2, "dv")
 
 
+def test_plucker_embed():
+    _ext()
+    from uttt_b200.nvs.data import SyntheticScenes
+    batch = {k: v.to(DEV) for k, v in next(SyntheticScenes(2, 3, 64, pin=False)).items()}
+    tgt = torch.tensor([False, True, False], device=DEV)
+    got = ops.plucker_embed(batch["image"], batch["fxfycxcy"], batch["c2w"], tgt, 8)
+    want = ref.plucker_embed(batch["image"], batch["fxfycxcy"], batch["c2w"], tgt, 8)
+    _close(got, want, 1e-5, 1e-5)
+
+
 def test_tiny_lm_gpu_matches_cpu():
     """Whole-model check: bf16 kernels on the GPU against the fp32 CPU path, same weights."""
     _ext()

@@ -26,6 +26,7 @@ void adamw_flat(at::Tensor p, at::Tensor g, at::Tensor m, at::Tensor v, c10::opt
                 double gmul, int64_t decay_hi);
 void ce_fwd_bwd_(at::Tensor logits, at::Tensor labels, at::Tensor loss, int64_t ignore_index);
 int64_t launch_count();
+at::Tensor plucker_embed(at::Tensor image, at::Tensor fxfycxcy, at::Tensor c2w, at::Tensor is_target, int64_t patch);
 
 at::Tensor gg_nt(at::Tensor x, at::Tensor w, at::Tensor tile_group);
 at::Tensor gg_nn(at::Tensor x, at::Tensor w, at::Tensor tile_group);
@@ -60,6 +61,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("adamw_flat", &adamw_flat);
   m.def("ce_fwd_bwd_", &ce_fwd_bwd_);
   m.def("launch_count", &launch_count);
+  m.def("plucker_embed", &plucker_embed);
   m.def("gg_nt", &gg_nt);
   m.def("gg_nn", &gg_nn);
   m.def("gg_tn_segments", &gg_tn_segments);

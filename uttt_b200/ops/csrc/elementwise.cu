@@ -934,6 +934,63 @@ void ce_fwd_bwd_(at::Tensor logits, at::Tensor labels, at::Tensor loss, int64_t 
   count_launch();
 }
 
+// ------------------------------------------------------------------------------------ Plucker patch embed
+// image [b, v, 3, H, W] fp32 in [0,1]; fxfycxcy [b, v, 4]; c2w [b, v, 4, 4]; is_target [v] (uint8).
+// out [b, v, (H/p)*(W/p), p*p*12] with channel order (o, d, o x d, rgb*2-1) and (ph, pw, c) inside a patch.
+template <typename T>
+__global__ void plucker_embed_kernel(const float* __restrict__ image, const float* __restrict__ intr,
+                                     const float* __restrict__ c2w, const uint8_t* __restrict__ is_target,
+                                     T* __restrict__ out, int views, int H, int W, int p, size_t total_pixels) {
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total_pixels;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    int x = idx % W;
+    int y = (idx / W) % H;
+    size_t bv = idx / ((size_t)W * H);
+    int v = bv % views;
+    const float* K = intr + bv * 4;
+    const float* M = c2w + bv * 16;
+    float dx = (x + 0.5f - K[2]) / K[0], dy = (y + 0.5f - K[3]) / K[1], dz = 1.f;
+    float rx = M[0] * dx + M[1] * dy + M[2] * dz;
+    float ry = M[4] * dx + M[5] * dy + M[6] * dz;
+    float rz = M[8] * dx + M[9] * dy + M[10] * dz;
+    float inv = rsqrtf(rx * rx + ry * ry + rz * rz);
+    rx *= inv; ry *= inv; rz *= inv;
+    float ox = M[3], oy = M[7], oz = M[11];
+    float ch[12];
+    ch[0] = ox; ch[1] = oy; ch[2] = oz;
+    ch[3] = rx; ch[4] = ry; ch[5] = rz;
+    ch[6] = oy * rz - oz * ry;
+    ch[7] = oz * rx - ox * rz;
+    ch[8] = ox * ry - oy * rx;
+    bool tgt = is_target[v] != 0;
+    size_t plane = (size_t)H * W;
+    const float* img = image + bv * 3 * plane + (size_t)y * W + x;
+    ch[9] = tgt ? 0.f : img[0] * 2.f - 1.f;
+    ch[10] = tgt ? 0.f : img[plane] * 2.f - 1.f;
+    ch[11] = tgt ? 0.f : img[2 * plane] * 2.f - 1.f;
+    int ww = W / p;
+    size_t patch = (size_t)(y / p) * ww + (x / p);
+    size_t n_patch = (size_t)(H / p) * ww;
+    T* o = out + ((bv * n_patch + patch) * (size_t)(p * p) + (size_t)(y % p) * p + (x % p)) * 12;
+#pragma unroll
+    for (int c = 0; c < 12; ++c) o[c] = from_f<T>(ch[c]);
+  }
+}
+
+at::Tensor plucker_embed(at::Tensor image, at::Tensor fxfycxcy, at::Tensor c2w, at::Tensor is_target, int64_t patch) {
+  c10::cuda::CUDAGuard guard(image.device());
+  TORCH_CHECK(image.scalar_type() == at::kFloat && image.is_contiguous() && image.dim() == 5);
+  int b = image.size(0), v = image.size(1), H = image.size(3), W = image.size(4);
+  TORCH_CHECK(H % patch == 0 && W % patch == 0 && is_target.scalar_type() == at::kByte);
+  auto out = at::empty({b, v, (H / patch) * (W / patch), patch * patch * 12}, image.options().dtype(at::kFloat));
+  size_t total = (size_t)b * v * H * W;
+  plucker_embed_kernel<float><<<ew_blocks(total), 256, 0, cur_stream()>>>(
+      image.data_ptr<float>(), fxfycxcy.data_ptr<float>(), c2w.data_ptr<float>(), is_target.data_ptr<uint8_t>(),
+      out.data_ptr<float>(), v, H, W, (int)patch, total);
+  count_launch();
+  return out;
+}
+
 int64_t launch_count() { return (int64_t)g_launch_count; }
 
 }  // namespace uttt

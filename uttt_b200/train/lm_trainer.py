@@ -1,0 +1,174 @@
+"""Language-model training entry point:  ``torchrun -m uttt_b200.train.lm_trainer --job.config_file job.toml
+--model.config model.json [--section.key value ...]``.
+
+The loop follows the reference trainer (uttt_llm/flame/train.py:156-822): distributed init, data source,
+model build from the architecture JSON, sharding, optimizer + schedule, checkpoint resume, gradient
+accumulation, clipping with NaN/Inf step skipping, periodic metrics (loss average / max over ranks,
+tokens/s, MFU, memory), checkpointing, optional torch profiler traces.  Differences: the global-batch guard
+(``training.expected_global_batch_size``) is checked before anything is allocated; the loss-free balancing
+interval is multiplied by the accumulation factor as in the reference (:282-292); device timing uses CUDA
+events; the gradient path is the fused peer-memory reduce/AdamW/all-gather step.
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+import time
+from typing import Any, Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..config import load_config
+from ..config.job_config import JobConfig
+from ..utils.flops import get_nparams_and_flops, peak_flops
+from .checkpoint import CheckpointManager, TrainState
+from .data import build_dataloader
+from .engine import EngineConfig, TrainEngine, init_distributed
+
+
+def check_global_batch(job: JobConfig, world: int) -> int:
+    got = job.training.batch_size * world * job.training.gradient_accumulation_steps
+    want = job.training.expected_global_batch_size
+    if want is not None and int(want) != got:
+        raise ValueError(f"training.batch_size ({job.training.batch_size}) x data-parallel ranks ({world}) x "
+                         f"gradient_accumulation_steps ({job.training.gradient_accumulation_steps}) = {got}, "
+                         f"but training.expected_global_batch_size = {want}")
+    return got
+
+
+class Metrics:
+    """Loss history + throughput bookkeeping; prints, and writes TensorBoard / JSONL when enabled."""
+
+    def __init__(self, job: JobConfig, rank: int, flops_per_token: float, n_gpus: int):
+        self.rank, self.job = rank, job
+        self.flops_per_token, self.n_gpus = flops_per_token, n_gpus
+        self.t_last, self.tokens_since = time.perf_counter(), 0
+        self.path = os.path.join(job.job.dump_folder, "metrics.jsonl")
+        self.tb = None
+        if rank == 0:
+            os.makedirs(job.job.dump_folder, exist_ok=True)
+            if job.metrics.enable_tensorboard:
+                try:
+                    from torch.utils.tensorboard import SummaryWriter
+                    self.tb = SummaryWriter(os.path.join(job.job.dump_folder, job.metrics.save_tb_folder))
+                except Exception:
+                    self.tb = None
+
+    def log(self, step: int, loss: torch.Tensor, stats: Dict[str, Any], tokens: int, state: TrainState) -> None:
+        self.tokens_since += tokens
+        if step % self.job.metrics.log_freq != 0 and step != 1:
+            return
+        avg, mx = loss.detach().float().clone(), loss.detach().float().clone()
+        if dist.is_available() and dist.is_initialized():
+            dist.all_reduce(avg, op=dist.ReduceOp.AVG)
+            dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        now = time.perf_counter()
+        dt = max(now - self.t_last, 1e-9)
+        tps = self.tokens_since / dt                       # per rank
+        mfu = 100.0 * self.flops_per_token * tps / peak_flops()
+        self.t_last, self.tokens_since = now, 0
+        state.global_avg_losses.append(float(avg))
+        state.global_max_losses.append(float(mx))
+        state.log_steps.append(step)
+        if self.rank == 0:
+            mem = torch.cuda.max_memory_reserved() / 2 ** 30 if torch.cuda.is_available() else 0.0
+            rec = {"step": step, "loss": float(avg), "loss_max": float(mx), "tps_per_gpu": tps, "mfu": mfu,
+                   "memory_gib": mem, "lr": stats.get("lr"), "grad_norm": float(stats["grad_norm"]),
+                   "skipped_step": state.skipped_step}
+            for k in ("ce", "lb"):
+                if stats.get(k) is not None:
+                    rec[f"loss/{k}"] = float(stats[k])
+            print(f"step {step:6d}  loss {rec['loss']:.4f}  grad_norm {rec['grad_norm']:.3f}  lr {rec['lr']:.2e}  "
+                  f"tps/gpu {tps:,.0f}  mfu {mfu:.1f}%  mem {mem:.1f} GiB", flush=True)
+            with open(self.path, "a") as fh:
+                fh.write(json.dumps(rec) + "\n")
+            if self.tb is not None:
+                for k, v in rec.items():
+                    if isinstance(v, (int, float)) and k != "step":
+                        self.tb.add_scalar(k, v, step)
+
+
+def main(job: Optional[JobConfig] = None) -> TrainState:
+    job = job or JobConfig().parse_args()
+    rank, world, local = init_distributed()
+    check_global_batch(job, world)
+    if job.job.print_args and rank == 0:
+        print(json.dumps(job.to_dict(), indent=1, default=str))
+    model_cfg = load_config(job.model.config)
+    accum = job.training.gradient_accumulation_steps
+    if getattr(model_cfg, "memory_lb_mode", None) == "loss_free" and accum > 1:
+        # one bias update per optimizer step: the interval counts forwards
+        model_cfg = model_cfg.replace(
+            memory_loss_free_update_interval=model_cfg.memory_loss_free_update_interval * accum)
+    ecfg = EngineConfig(micro_batch_size=job.training.micro_batch_size or job.training.batch_size,
+                        lr=job.optimizer.lr, eps=job.optimizer.eps, beta1=job.optimizer.beta1, beta2=job.optimizer.beta2,
+                        weight_decay=job.optimizer.weight_decay, max_norm=job.training.max_norm,
+                        warmup_steps=job.lr_scheduler.warmup_steps, total_steps=job.training.steps,
+                        decay_type=job.lr_scheduler.decay_type, lr_min=job.lr_scheduler.lr_min,
+                        skip_nan_inf=job.training.skip_nan_inf, seed=job.training.seed,
+                        activation_checkpoint=job.activation_checkpoint.mode != "none" or True)
+    engine = TrainEngine(model_cfg, ecfg)
+    data = build_dataloader(job.training.dataset, vocab_size=model_cfg.vocab_size, seq_len=job.training.seq_len,
+                            batch_size=job.training.batch_size * accum, rank=rank, world=world,
+                            seed=job.training.seed, data_files=job.training.data_files)
+    state = TrainState()
+    ckpt = CheckpointManager(job.job.dump_folder, job.checkpoint.folder, job.checkpoint.interval,
+                             job.checkpoint.keep_latest_k, job.checkpoint.save_backend,
+                             job.checkpoint.model_weights_only, job.checkpoint.export_dtype,
+                             job.checkpoint.enable_checkpoint, job.checkpoint.initial_load_path,
+                             job.checkpoint.exclude_from_loading)
+    loaded = None
+    if job.checkpoint.enable_checkpoint:
+        loaded = ckpt.load(engine.model, engine.trainer, engine.lr_sched, data, state, step=job.checkpoint.load_step)
+    if os.environ.get("TRAIN_ATTEMPT_KIND") == "resume" and loaded is None:
+        raise RuntimeError("TRAIN_ATTEMPT_KIND=resume but no checkpoint could be loaded")
+    if loaded:
+        engine.step = state.step
+        engine.lr_sched.fast_forward(state.step)
+    if job.checkpoint.create_seed_checkpoint:
+        ckpt.save(0, engine.model, engine.trainer, engine.lr_sched, data, state, force=True)
+        return state
+    n_params, flops_tok = get_nparams_and_flops(engine.model, model_cfg, job.training.seq_len)
+    metrics = Metrics(job, rank, flops_tok, world)
+    if rank == 0:
+        print(f"model {model_cfg.model_type}: {n_params:,} parameters, {flops_tok / 1e9:.2f} GFLOP/token; "
+              f"world {world}, global batch {job.training.batch_size * world * accum}", flush=True)
+    prof = None
+    if job.profiling.enable_profiling:
+        from torch.profiler import ProfilerActivity, profile, schedule, tensorboard_trace_handler
+        folder = os.path.join(job.job.dump_folder, job.profiling.save_traces_folder)
+        prof = profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA],
+                       schedule=schedule(wait=max(job.profiling.profile_freq - 2, 0), warmup=1, active=1),
+                       on_trace_ready=tensorboard_trace_handler(folder))
+        prof.start()
+    t0 = time.perf_counter()
+    while state.step < job.training.steps:
+        os.environ["FLAME_TRAIN_STEP"] = str(state.step + 1)
+        batch = next(data)
+        loss = engine.train_step(batch)
+        state.step += 1
+        state.token += batch["input_ids"].numel() * world
+        if job.training.skip_nan_inf:
+            # read back lazily: only when logging
+            pass
+        stats = dict(engine.last_stats)
+        if state.step % job.metrics.log_freq == 0 or state.step == 1:
+            state.skipped_step += int(bool(stats["skipped"]))
+        metrics.log(state.step, loss, stats, batch["input_ids"].numel(), state)
+        state.elapsed = time.perf_counter() - t0
+        ckpt.save(state.step, engine.model, engine.trainer, engine.lr_sched, data, state,
+                  force=state.step == job.training.steps and job.checkpoint.enable_checkpoint)
+        if prof is not None:
+            prof.step()
+    if prof is not None:
+        prof.stop()
+    if dist.is_available() and dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+    return state
+
+
+if __name__ == "__main__":
+    main()
