@@ -1,0 +1,84 @@
+import math
+import os
+
+import torch
+
+from uttt_b200.config import named_config
+from uttt_b200.eval.ptl import PerPositionLossTracker, evaluate, per_token_loss, summarize
+from uttt_b200.eval.ruler import make_niah_sample, merge_shards, run_niah
+from uttt_b200.models import build_model
+from uttt_b200.train.checkpoint import CheckpointManager
+from uttt_b200.train.data import PackedTokenDataset, SyntheticZipfTokens
+from uttt_b200.utils.convert import dcp_to_hf, hf_to_dcp, preprocess
+from uttt_b200.utils.flops import get_nparams_and_flops
+
+
+def test_ptl_tracker_and_summary():
+    t = PerPositionLossTracker(8)
+    t.update(torch.ones(2, 8), torch.tensor([[1] * 6 + [0, 0]] * 2, dtype=torch.bool))
+    m = t.mean()
+    assert float(m[0]) == 1.0 and math.isnan(float(m[7]))
+    s = summarize([1.0, 2.0, None, float("nan"), 4.0], start=1)
+    assert s["ptl_tail_mean"] == 3.0 and s["tail_positions"] == 2
+
+
+def test_ptl_matches_model_loss():
+    torch.manual_seed(0)
+    model = build_model(named_config("tiny-uttt-moe", memory_lb_loss_alpha=0.0)).eval()
+    data = SyntheticZipfTokens(1024, 128, 2, seed=0)
+    tracker = evaluate(model, data, 128, max_batches=1)
+    data2 = SyntheticZipfTokens(1024, 128, 2, seed=0)
+    ids = next(data2)["input_ids"]
+    with torch.no_grad():
+        want = model(input_ids=ids, labels=ids).ce_loss
+    got = tracker.loss_sum.sum() / tracker.count.sum()
+    assert abs(float(got) - float(want)) < 1e-4
+
+
+def test_niah_sample_and_merge():
+    s = make_niah_sample(1024, 256, 4, 3, seed=1)
+    assert s["prompt"].shape == (256,) and int(s["prompt"][-3]) == 3
+    key = int(s["prompt"][-2])
+    pos = (s["prompt"][:-3] == key).nonzero()[0, 0]
+    assert torch.equal(s["prompt"][pos + 2:pos + 5], s["answer"])
+    model = build_model(named_config("tiny-uttt-moe")).eval()
+    r0 = run_niah(model, 1024, 128, num_samples=2, num_needles=2, value_len=2, shard=0, num_shards=2)
+    r1 = run_niah(model, 1024, 128, num_samples=2, num_needles=2, value_len=2, shard=1, num_shards=2)
+    assert merge_shards([r0, r1])["total"] == 2
+
+
+def test_convert_round_trip_and_preprocess(tmp_path):
+    torch.manual_seed(0)
+    cfg = named_config("tiny-uttt-moe")
+    model = build_model(cfg)
+    cfg_path = tmp_path / "cfg.json"
+    cfg_path.write_text(cfg.to_json_string())
+    mgr = CheckpointManager(str(tmp_path / "run"), interval=1)
+    ck = mgr.save(5, model, force=True)
+    hf = dcp_to_hf(ck, str(cfg_path), str(tmp_path / "hf"))
+    assert os.path.exists(os.path.join(hf, "config.json"))
+    back = hf_to_dcp(hf, str(tmp_path / "seed"))
+    m2 = build_model(cfg)
+    CheckpointManager(str(tmp_path / "seed")).load(m2)
+    for (n, a), (_, b) in zip(model.state_dict().items(), m2.state_dict().items()):
+        torch.testing.assert_close(a, b, msg=n)
+    txt = tmp_path / "docs.txt"
+    txt.write_text("\n".join(" ".join(str(i % 50) for i in range(j, j + 300)) for j in range(20)))
+    shards = preprocess([str(txt)], str(tmp_path / "arrow"), lambda s: [int(x) for x in s.split()], shard_docs=8,
+                        eos_token_id=2)
+    assert len(shards) == 3
+    ds = PackedTokenDataset(shards, seq_len=64, batch_size=2, pin=False)
+    b = next(ds)
+    assert b["input_ids"].shape == (2, 64)
+    st = ds.state_dict()
+    nxt = next(ds)["input_ids"]
+    ds.load_state_dict(st)
+    torch.testing.assert_close(next(ds)["input_ids"], nxt)
+
+
+def test_flop_model_subtracts_embeddings():
+    cfg = named_config("tiny-uttt-moe")
+    model = build_model(cfg)
+    n, flops = get_nparams_and_flops(model, cfg, 256)
+    assert n == sum(p.numel() for p in model.parameters())
+    assert flops < 6 * n + 12 * 2 * 4 * 16 * 256 + 1e9 and flops > 6 * (n - 1024 * 64 * 2)

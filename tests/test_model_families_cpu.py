@@ -48,9 +48,29 @@ def test_family_forward_backward(model_type, extra):
     assert all(torch.isfinite(p.grad).all() for p in model.parameters() if p.grad is not None)
 
 
+@pytest.mark.parametrize("mt", ["transformer", "deltanet_swa", "gated_deltanet_swa", "kda_swa", "mamba2_swa", "mom_swa"])
+def test_baseline_families(mt):
+    torch.manual_seed(0)
+    cfg = config_from_dict(dict(model_type=mt, hidden_size=64, num_hidden_layers=2, num_heads=4, vocab_size=128,
+                                window_size=16, mixer_head_dim=16, rope_theta=10000.0))
+    m = build_model(cfg)
+    ids = torch.randint(0, 128, (2, 40))
+    out = m(input_ids=ids, labels=ids)
+    out.loss.backward()
+    assert torch.isfinite(out.loss) and all(p.grad is not None for p in m.parameters())
+    # causality: a later token does not change earlier positions
+    m.eval()
+    ids2 = ids.clone()
+    ids2[:, 30] = (ids2[:, 30] + 1) % 128
+    with torch.no_grad():
+        h1, h2 = m(input_ids=ids).hidden_states, m(input_ids=ids2).hidden_states
+    torch.testing.assert_close(h1[:, :30], h2[:, :30], atol=1e-5, rtol=1e-5)
+
+
 def test_registry_covers_reference_model_types():
     have = set(registered_model_types())
-    for t in ("uttt_moe", "uttt_dense", "ttt_moe_lb", "ttt_moe_no_lb", "ttt_dense", "lact_swiglu"):
+    for t in ("uttt_moe", "uttt_dense", "ttt_moe_lb", "ttt_moe_no_lb", "ttt_dense", "lact_swiglu", "transformer",
+              "deltanet_swa", "gated_deltanet_swa", "kda_swa", "mamba2_swa", "mom_swa"):
         assert t in have
 
 
