@@ -49,14 +49,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr uint32_t kSpinLimit = 1u << 26;          // hard cap on polls
+constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s of wall clock per wait
 
-// Bounded wait.  On time-out writes `code` to *status (first writer wins) and returns false.
-// Also returns false early when another CTA has already reported a failure.
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Bounded wait.  Gives up after kWaitLimitNs (or kSpinLimit polls): writes `code` to *status (first writer
+// wins) and returns false.  Also returns false early when another CTA has already reported a failure.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
+  uint64_t t0 = 0;
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023u) == 1023u && status != nullptr && *(volatile int*)status != 0) return false;
+    if ((i & 255u) == 255u) {
+      if (status != nullptr && *(volatile int*)status != 0) return false;
+      uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitLimitNs) break;
+    }
   }
   if (status != nullptr) atomicCAS(status, 0, code);
   return false;

@@ -21,6 +21,9 @@
 #include <cudaTypedefs.h>
 #include <torch/extension.h>
 
+#include <cstdlib>
+#include <string>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -270,6 +273,266 @@ __global__ void __launch_bounds__(128) tc_gemm_kernel(const __grid_constant__ CU
   if (warp == 0) ptx::tmem_dealloc(tmem_acc, BN);
 }
 
+// ------------------------------------------------------------------------------------ persistent variant
+// One CTA per SM walks the output tiles (tile = blockIdx.x, += gridDim.x).  Six warps:
+//   warps 0-3 : epilogue   (TMEM -> registers -> global), one TMEM lane quarter each
+//   warp 4    : TMA producer (one lane), ring of STAGES shared-memory stages shared by all tiles
+//   warp 5    : MMA issuer   (one lane), two TMEM accumulator buffers so that tile i+1's main loop runs
+//               while tile i's epilogue drains
+template <int BN, int STAGES>
+struct PersistentSmem {
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarOffset = STAGES * kStageBytes;
+  static constexpr int kTotal = kBarOffset + (2 * STAGES + 4) * 8 + 16 + 1024;
+};
+
+struct TileCoord {
+  int g, a_row0, m0, n0, nkb;
+  size_t out_row0;
+  bool unused;
+};
+
+template <int MODE, int BN>
+__device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int id, int tiles_n, int tiles_m) {
+  TileCoord c{};
+  if (MODE == kNT || MODE == kNN) {
+    int t = id / tiles_n;
+    c.n0 = (id % tiles_n) * BN;
+    c.g = p.tile_group[t];
+    c.a_row0 = t * BM;
+    c.out_row0 = (size_t)t * BM;
+    c.unused = c.g < 0;
+    c.nkb = p.K / BK;
+  } else {
+    int per = tiles_m * tiles_n;
+    c.g = id / per;
+    int rem = id % per;
+    c.m0 = (rem / tiles_n) * BM;
+    c.n0 = (rem % tiles_n) * BN;
+    c.out_row0 = (size_t)c.g * p.M + c.m0;
+    c.a_row0 = c.g * p.M + c.m0;
+    c.unused = false;
+    if (MODE == kTN) {
+      int n = 0;
+      for (int s = 0; s < p.segments; ++s) {
+        const int* off = p.seg_offsets + (size_t)s * (p.groups + 1);
+        n += (off[c.g + 1] - off[c.g]) / BK;
+      }
+      c.nkb = n;
+    } else {
+      c.nkb = p.K / BK;
+    }
+  }
+  return c;
+}
+
+template <int MODE, int BN, int STAGES, typename OutT>
+__global__ void __launch_bounds__(192) tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tma_a,
+                                                                 const __grid_constant__ CUtensorMap tma_b,
+                                                                 GemmParams p, int total_tiles, int tiles_n,
+                                                                 int tiles_m) {
+  using L = PersistentSmem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+  const uint32_t bar_base = smem_base + L::kBarOffset;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto acc_full = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
+  auto acc_empty = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + L::kBarOffset + (2 * STAGES + 4) * 8);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  {
+    __shared__ int prior_failure;
+    if (threadIdx.x == 0) prior_failure = (p.status != nullptr) ? *(volatile int*)p.status : 0;
+    __syncthreads();
+    if (prior_failure != 0) return;
+  }
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(acc_full(b), 1);
+      ptx::mbar_init(acc_empty(b), 128);
+    }
+    ptx::mbar_fence_init();
+    ptx::tma_prefetch_desc(&tma_a);
+    ptx::tma_prefetch_desc(&tma_b);
+  }
+  constexpr uint32_t kTmemCols = 2 * BN;
+  if (warp == 4) {
+    ptx::tmem_alloc(ptx::smem_u32(tmem_slot), kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  OutT* out = reinterpret_cast<OutT*>(p.out);
+  const int ldo = p.N;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      // ================= TMA producer =================
+      uint32_t it = 0;
+      bool ok = true;
+      for (int id = blockIdx.x; id < total_tiles && ok; id += gridDim.x) {
+        TileCoord c = decode_tile<MODE, BN>(p, id, tiles_n, tiles_m);
+        if (c.unused || c.nkb == 0) continue;
+        int seg = 0, seg_row = 0, seg_end = 0;
+        if (MODE == kTN) {
+          seg_row = p.seg_offsets[c.g];
+          seg_end = p.seg_offsets[c.g + 1];
+        }
+        for (int kb = 0; kb < c.nkb; ++kb, ++it) {
+          int s = it % STAGES;
+          ok = ptx::mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1, p.status, 21);
+          if (!ok) break;
+          uint32_t sa = smem_base + s * L::kStageBytes;
+          uint32_t sb = sa + L::kABytes;
+          ptx::mbar_expect_tx(full_bar(s), L::kStageBytes);
+          if (MODE == kNT || MODE == kBMM) {
+            ptx::tma_load_2d(sa, &tma_a, full_bar(s), kb * BK, c.a_row0);
+            ptx::tma_load_2d(sb, &tma_b, full_bar(s), kb * BK, c.g * p.N + c.n0);
+          } else if (MODE == kNN) {
+            ptx::tma_load_2d(sa, &tma_a, full_bar(s), kb * BK, c.a_row0);
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              ptx::tma_load_2d(sb + j * (BK * 128), &tma_b, full_bar(s), c.n0 + 64 * j, c.g * p.K + kb * BK);
+          } else {
+            while (seg_row >= seg_end) {
+              ++seg;
+              const int* off = p.seg_offsets + (size_t)seg * (p.groups + 1);
+              seg_row = off[c.g];
+              seg_end = off[c.g + 1];
+            }
+            int row = seg * p.rows_per_segment + seg_row;
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              ptx::tma_load_2d(sa + j * (BK * 128), &tma_a, full_bar(s), c.m0 + 64 * j, row);
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              ptx::tma_load_2d(sb + j * (BK * 128), &tma_b, full_bar(s), c.n0 + 64 * j, row);
+            seg_row += BK;
+          }
+        }
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      // ================= MMA issuer =================
+      constexpr int a_mn = (MODE == kTN) ? 1 : 0;
+      constexpr int b_mn = (MODE == kNN || MODE == kTN) ? 1 : 0;
+      constexpr uint32_t idesc = ptx::make_instr_desc(BM, BN, a_mn, b_mn);
+      uint32_t it = 0, acc_it = 0;
+      bool ok = true;
+      for (int id = blockIdx.x; id < total_tiles && ok; id += gridDim.x) {
+        TileCoord c = decode_tile<MODE, BN>(p, id, tiles_n, tiles_m);
+        if (c.unused || c.nkb == 0) continue;
+        const int ab = acc_it & 1;
+        ok = ptx::mbar_wait(acc_empty(ab), ((acc_it >> 1) & 1) ^ 1, p.status, 22);
+        if (!ok) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t tmem_acc = tmem_base + ab * BN;
+        for (int kb = 0; kb < c.nkb; ++kb, ++it) {
+          int s = it % STAGES;
+          ok = ptx::mbar_wait(full_bar(s), (it / STAGES) & 1, p.status, 23);
+          if (!ok) break;
+          ptx::tc_fence_after_sync();
+          uint32_t sa = smem_base + s * L::kStageBytes;
+          uint32_t sb = sa + L::kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            uint64_t da = a_mn ? ptx::make_smem_desc(sa + k * 2048, BK * 128, 1024)
+                               : ptx::make_smem_desc(sa + k * 32, 16, 1024);
+            uint64_t db = b_mn ? ptx::make_smem_desc(sb + k * 2048, BK * 128, 1024)
+                               : ptx::make_smem_desc(sb + k * 32, 16, 1024);
+            ptx::mma_bf16_ss(tmem_acc, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          ptx::mma_commit(empty_bar(s));
+        }
+        if (!ok) break;
+        ptx::mma_commit(acc_full(ab));
+        ++acc_it;
+      }
+    }
+  } else {
+    // ================= epilogue (warps 0-3) =================
+    uint32_t acc_it = 0;
+    bool ok = true;
+    const int r = warp * 32 + lane;
+    for (int id = blockIdx.x; id < total_tiles && ok; id += gridDim.x) {
+      TileCoord c = decode_tile<MODE, BN>(p, id, tiles_n, tiles_m);
+      OutT* orow = out + (c.out_row0 + r) * ldo + c.n0;
+      const bool has_acc = !c.unused && c.nkb > 0;
+      if (!has_acc) {
+        if (!(MODE == kTN && p.accumulate)) {
+          for (int col = 0; col < BN; col += 16 / (int)sizeof(OutT))
+            *reinterpret_cast<uint4*>(orow + col) = make_uint4(0, 0, 0, 0);
+        }
+        continue;
+      }
+      const int ab = acc_it & 1;
+      ok = ptx::mbar_wait(acc_full(ab), (acc_it >> 1) & 1, p.status, 24);
+      if (!ok) break;
+      ptx::tc_fence_after_sync();
+      const uint32_t tmem_acc = tmem_base + ab * BN + ((uint32_t)(warp * 32) << 16);
+      const __nv_bfloat16* drow = (MODE == kBMM && p.addend != nullptr)
+          ? reinterpret_cast<const __nv_bfloat16*>(p.addend) + (c.out_row0 + r) * ldo + c.n0 : nullptr;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t raw[32];
+        ptx::tmem_ld_32x32(tmem_acc + c0, raw);
+        ptx::tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]);
+        if (MODE == kBMM) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] *= p.alpha;
+          if (drow != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              float d[8];
+              Vec8<__nv_bfloat16>::load(drow + c0 + i, d);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[i + j] += p.beta * d[j];
+            }
+          }
+        }
+        if (MODE == kTN && p.accumulate) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            float d[8];
+            Vec8<OutT>::load(orow + c0 + i, d);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[i + j] += d[j];
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          float o[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = v[i + j];
+          Vec8<OutT>::store(orow + c0 + i, o);
+        }
+      }
+      // this accumulator buffer may be overwritten by the MMA issuer once all 128 threads have drained it
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(acc_empty(ab));
+      ++acc_it;
+    }
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 4) ptx::tmem_dealloc(tmem_base, kTmemCols);
+}
+
 // ------------------------------------------------------------------------------------ host side
 static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
   static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
@@ -315,8 +578,42 @@ static at::Tensor& status_word(const at::Device& dev) {
 
 at::Tensor gemm_status(at::Tensor like) { return status_word(like.device()); }
 
+static bool use_persistent() {
+  static int mode = -1;
+  if (mode < 0) {
+    const char* e = std::getenv("UTTT_B200_GEMM");
+    mode = (e != nullptr && std::string(e) == "simple") ? 0 : 1;
+  }
+  return mode == 1;
+}
+
 template <int MODE, int BN, typename OutT>
 static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, dim3 grid) {
+  auto stream = at::cuda::getCurrentCUDAStream().stream();
+  if (use_persistent()) {
+    constexpr int STAGES = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
+    using L = PersistentSmem<BN, STAGES>;
+    auto kernel = tc_gemm_persistent_kernel<MODE, BN, STAGES, OutT>;
+    static bool configured = false;
+    if (!configured) {
+      C10_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+      configured = true;
+    }
+    int tiles_n, tiles_m, total;
+    if (MODE == kNT || MODE == kNN) {
+      tiles_n = grid.x; tiles_m = grid.y; total = grid.x * grid.y;
+    } else if (MODE == kTN) {
+      tiles_m = grid.x; tiles_n = grid.y; total = grid.x * grid.y * grid.z;
+    } else {
+      tiles_n = grid.x; tiles_m = grid.y; total = grid.x * grid.y * grid.z;
+    }
+    int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+    int ctas = std::min(total, sms);
+    kernel<<<ctas, 192, L::kTotal, stream>>>(ta, tb, p, total, tiles_n, tiles_m);
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+    count_launch();
+    return;
+  }
   constexpr int STAGES = (BN >= 256) ? 3 : (BN >= 128 ? 3 : 4);
   using L = SmemLayout<BN, STAGES>;
   auto kernel = tc_gemm_kernel<MODE, BN, STAGES, OutT>;
@@ -325,12 +622,12 @@ static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams
     C10_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
     configured = true;
   }
-  kernel<<<grid, 128, L::kTotal, at::cuda::getCurrentCUDAStream().stream()>>>(ta, tb, p);
+  kernel<<<grid, 128, L::kTotal, stream>>>(ta, tb, p);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   count_launch();
 }
 
-static int pick_bn(int n) { return (n % 128 == 0) ? 128 : 64; }
+static int pick_bn(int n) { return (n % 256 == 0) ? 256 : ((n % 128 == 0) ? 128 : 64); }
 
 at::Tensor gg_nt(at::Tensor x, at::Tensor w, at::Tensor tile_group) {
   c10::cuda::CUDAGuard guard(x.device());
@@ -344,13 +641,12 @@ at::Tensor gg_nt(at::Tensor x, at::Tensor w, at::Tensor tile_group) {
   p.tile_group = tile_group.data_ptr<int>();
   p.groups = G; p.N = N; p.K = K; p.out = out.data_ptr();
   p.status = status_word(x.device()).data_ptr<int>();
-  if (pick_bn(N) == 128) {
-    auto tb = make_tmap_2d_bf16(w.data_ptr(), (uint64_t)G * N, K, 128, BK);
-    launch_gemm<kNT, 128, __nv_bfloat16>(ta, tb, p, dim3(N / 128, R / BM));
-  } else {
-    auto tb = make_tmap_2d_bf16(w.data_ptr(), (uint64_t)G * N, K, 64, BK);
-    launch_gemm<kNT, 64, __nv_bfloat16>(ta, tb, p, dim3(N / 64, R / BM));
-  }
+  const int bn = pick_bn(N);
+  auto tb = make_tmap_2d_bf16(w.data_ptr(), (uint64_t)G * N, K, bn, BK);
+  dim3 grid(N / bn, R / BM);
+  if (bn == 256) launch_gemm<kNT, 256, __nv_bfloat16>(ta, tb, p, grid);
+  else if (bn == 128) launch_gemm<kNT, 128, __nv_bfloat16>(ta, tb, p, grid);
+  else launch_gemm<kNT, 64, __nv_bfloat16>(ta, tb, p, grid);
   return out;
 }
 
@@ -367,8 +663,11 @@ at::Tensor gg_nn(at::Tensor x, at::Tensor w, at::Tensor tile_group) {
   p.tile_group = tile_group.data_ptr<int>();
   p.groups = G; p.N = N; p.K = K; p.out = out.data_ptr();
   p.status = status_word(x.device()).data_ptr<int>();
-  if (pick_bn(N) == 128) launch_gemm<kNN, 128, __nv_bfloat16>(ta, tb, p, dim3(N / 128, R / BM));
-  else launch_gemm<kNN, 64, __nv_bfloat16>(ta, tb, p, dim3(N / 64, R / BM));
+  const int bn = pick_bn(N);
+  dim3 grid(N / bn, R / BM);
+  if (bn == 256) launch_gemm<kNN, 256, __nv_bfloat16>(ta, tb, p, grid);
+  else if (bn == 128) launch_gemm<kNN, 128, __nv_bfloat16>(ta, tb, p, grid);
+  else launch_gemm<kNN, 64, __nv_bfloat16>(ta, tb, p, grid);
   return out;
 }
 
@@ -400,12 +699,15 @@ at::Tensor gg_tn_segments(at::Tensor a, at::Tensor b, at::Tensor offsets, int64_
   p.accumulate = acc ? 1 : 0;
   p.status = status_word(a.device()).data_ptr<int>();
   bool f32 = out.scalar_type() == at::kFloat;
-  if (pick_bn(N) == 128) {
-    dim3 grid(M / BM, N / 128, G);
+  const int bn = pick_bn(N);
+  dim3 grid(M / BM, N / bn, G);
+  if (bn == 256) {
+    if (f32) launch_gemm<kTN, 256, float>(ta, tb, p, grid);
+    else launch_gemm<kTN, 256, __nv_bfloat16>(ta, tb, p, grid);
+  } else if (bn == 128) {
     if (f32) launch_gemm<kTN, 128, float>(ta, tb, p, grid);
     else launch_gemm<kTN, 128, __nv_bfloat16>(ta, tb, p, grid);
   } else {
-    dim3 grid(M / BM, N / 64, G);
     if (f32) launch_gemm<kTN, 64, float>(ta, tb, p, grid);
     else launch_gemm<kTN, 64, __nv_bfloat16>(ta, tb, p, grid);
   }
@@ -430,13 +732,12 @@ at::Tensor bmm_nt(at::Tensor a, at::Tensor b, double alpha, c10::optional<at::Te
     p.addend = dc.data_ptr();
   }
   p.status = status_word(a.device()).data_ptr<int>();
-  if (pick_bn(N) == 128) {
-    auto tb = make_tmap_2d_bf16(b.data_ptr(), (uint64_t)B * N, K, 128, BK);
-    launch_gemm<kBMM, 128, __nv_bfloat16>(ta, tb, p, dim3(N / 128, M / BM, B));
-  } else {
-    auto tb = make_tmap_2d_bf16(b.data_ptr(), (uint64_t)B * N, K, 64, BK);
-    launch_gemm<kBMM, 64, __nv_bfloat16>(ta, tb, p, dim3(N / 64, M / BM, B));
-  }
+  const int bn = pick_bn(N);
+  auto tb = make_tmap_2d_bf16(b.data_ptr(), (uint64_t)B * N, K, bn, BK);
+  dim3 grid(N / bn, M / BM, B);
+  if (bn == 256) launch_gemm<kBMM, 256, __nv_bfloat16>(ta, tb, p, grid);
+  else if (bn == 128) launch_gemm<kBMM, 128, __nv_bfloat16>(ta, tb, p, grid);
+  else launch_gemm<kBMM, 64, __nv_bfloat16>(ta, tb, p, grid);
   return out;
 }
 

@@ -1,0 +1,158 @@
+"""Kernel micro-benchmarks (CUDA-event timed, L2 flushed between iterations) and small cases for profilers.
+
+    python -m uttt_b200.ops.microbench [--kernel NAME] [--small] [--iters N]
+
+Kernels: gg_nt, gg_nn, gg_tn, bmm_nt, swa_fwd, rms_norm, fw_write_pw, adamw, ce.  ``--small`` runs one small case
+of the chosen kernel (inputs above L2 size, a few hundred MB on the device) three times, which is what the
+profile summaries under ``profiles/`` were captured from.  Prints one JSON line per case with the achieved
+TFLOP/s or GB/s and the fraction of the measured peaks in ``MEASURED_PEAKS.json`` when present.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+
+import torch
+
+from . import functional as F
+from ._ext import load
+
+
+def _peaks():
+    for cand in ("MEASURED_PEAKS.json", os.path.join(os.path.dirname(__file__), "..", "..", "MEASURED_PEAKS.json")):
+        try:
+            with open(cand) as fh:
+                d = json.load(fh)
+                return d["hbm_gbs"], d["bf16_tflops"]
+        except Exception:
+            continue
+    return 6650.0, 1590.0
+
+
+def _time(fn, iters: int, flush: torch.Tensor) -> float:
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        flush.zero_()                      # 256 MB write: evicts the 126 MB L2
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        total += s.elapsed_time(e)
+    return total / iters
+
+
+def _plan(bsz, tokens_heads, experts, topk, dev):
+    idx = torch.randint(0, experts, (bsz, tokens_heads, topk), device=dev)
+    if topk > 1:
+        idx[..., 1] = (idx[..., 0] + 1 + torch.randint(0, experts - 1, idx[..., 0].shape, device=dev)) % experts
+    return F.build_group_plan(idx, experts)
+
+
+def run(kernel: str, small: bool, iters: int):
+    dev = torch.device("cuda")
+    load(required=True)
+    hbm, tflops = _peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    bsz = 1 if small else 4
+    d, inter, experts = 384, 1536, 32
+    plan = _plan(bsz, 2048 * 4, experts, 2, dev)
+    rows, g = plan.rows_padded, plan.num_groups
+    real = int(plan.sizes.sum())
+    out = []
+
+    def rec(name, ms, flops=None, bytes_=None, **extra):
+        r = {"kernel": name, "ms": round(ms, 4), **extra}
+        if flops:
+            r["tflops"] = round(flops / ms / 1e9, 1)
+            r["frac_of_measured_bf16"] = round(flops / ms / 1e9 / tflops, 3)
+        if bytes_:
+            r["gbs"] = round(bytes_ / ms / 1e6, 1)
+            r["frac_of_measured_hbm"] = round(bytes_ / ms / 1e6 / hbm, 3)
+        print(json.dumps(r), flush=True)
+        out.append(r)
+
+    bf = dict(device=dev, dtype=torch.bfloat16)
+    if kernel in ("gg_nt", "all"):
+        x = torch.randn(rows, d, **bf)
+        w = torch.randn(g, 2 * inter, d, **bf) * 0.05
+        ms = _time(lambda: F.gg_nt(x, w, plan), iters, flush)
+        rec("gg_nt[read gate|up]", ms, flops=2.0 * real * d * 2 * inter, rows=rows, real_rows=real, K=d, N=2 * inter)
+        h = torch.randn(rows, inter, **bf)
+        w1 = torch.randn(g, d, inter, **bf) * 0.05
+        ms = _time(lambda: F.gg_nt(h, w1, plan), iters, flush)
+        rec("gg_nt[read down]", ms, flops=2.0 * real * d * inter, rows=rows, real_rows=real, K=inter, N=d)
+    if kernel in ("gg_nn", "all"):
+        v = torch.randn(rows, d, **bf)
+        w1 = torch.randn(g, d, inter, **bf) * 0.05
+        ms = _time(lambda: F.gg_nn(v, w1, plan), iters, flush)
+        rec("gg_nn[write dh]", ms, flops=2.0 * real * d * inter, K=d, N=inter)
+    if kernel in ("gg_tn", "all"):
+        a = torch.randn(rows, 2 * inter, **bf)
+        b = torch.randn(rows, d, **bf)
+        ms = _time(lambda: F.gg_tn(a, b, plan), iters, flush)
+        rec("gg_tn[G02]", ms, flops=2.0 * real * d * 2 * inter, M=2 * inter, N=d, groups=g)
+    if kernel in ("bmm_nt", "all"):
+        n = g * 2
+        x = torch.randn(n, d, inter, **bf)
+        ms = _time(lambda: F.bmm_nt(x, x), iters, flush)
+        rec("bmm_nt[NS X X^T]", ms, flops=2.0 * n * d * d * inter, batch=n)
+    if kernel in ("swa_fwd", "all"):
+        b_, lq, lk, h, hd, win = bsz, 2048, 4096, 16, 96, 2048
+        q = torch.randn(b_, lq, h, hd, **bf)
+        k = torch.randn(b_, lk, h, hd, **bf)
+        v = torch.randn(b_, lk, h, hd, **bf)
+        ms = _time(lambda: F.swa_attention(q, k, v, win, True), iters, flush)
+        band = win + 64          # average visible keys per query, rounded up to the tile edge
+        rec("swa_fwd[hd96 w2048]", ms, flops=4.0 * b_ * h * lq * band * hd, lq=lq, lk=lk)
+    if kernel in ("rms_norm", "all"):
+        x = torch.randn(bsz * 2048 * 8, 1536, **bf)
+        w = torch.ones(1536, **bf)
+        ms = _time(lambda: F.rms_norm(x, w, 1e-6), iters, flush)
+        rec("rms_norm_fwd", ms, bytes_=2.0 * x.numel() * 2)
+    if kernel in ("fw_write_pw", "all"):
+        ext = load()
+        y02 = torch.randn(rows, 2 * inter, **bf)
+        dh = torch.randn(rows, inter, **bf)
+        lr = torch.rand(rows, 3, device=dev)
+        ms = _time(lambda: ext.fw_write_pw_fwd(y02, dh, lr), iters, flush)
+        rec("fw_write_pw_fwd", ms, bytes_=2.0 * rows * inter * 6)
+    if kernel in ("adamw", "all"):
+        ext = load()
+        n = (32 if small else 256) << 20
+        p = torch.randn(n, device=dev)
+        gr = torch.randn(n, **bf)
+        m, v2 = torch.zeros_like(p), torch.zeros_like(p)
+        lo = torch.empty(n, **bf)
+        one = torch.ones(1, device=dev)
+        ms = _time(lambda: ext.adamw_flat(p, gr, m, v2, lo, 1e-3, 0.9, 0.95, 1e-8, 0.1, 1, one, one, 1.0, n), iters, flush)
+        rec("adamw_flat", ms, bytes_=float(n) * (4 * 3 * 2 + 2 + 2))
+    if kernel in ("ce", "all"):
+        ext = load()
+        t, vsz = (2048 if small else 8192), 32000
+        logits = torch.randn(t, vsz, **bf)
+        labels = torch.randint(0, vsz, (t,), device=dev)
+        loss = torch.zeros(1, device=dev)
+        ms = _time(lambda: ext.ce_fwd_bwd_(logits, labels, loss, -100), iters, flush)
+        rec("ce_fwd_bwd", ms, bytes_=float(t) * vsz * 2 * 3)
+    status = int(load().gemm_status(torch.zeros(1, device=dev))[0])
+    assert status == 0, f"kernel wait timed out (code {status})"
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", default="all")
+    ap.add_argument("--small", action="store_true")
+    ap.add_argument("--iters", type=int, default=10)
+    args = ap.parse_args()
+    run(args.kernel, args.small, 3 if args.small else args.iters)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,217 @@
+"""Writes the configuration tree under ``configs/``:  ``python -m uttt_b200.tools.make_configs``.
+
+* ``configs/lm/{124M,760M}/<model>.json`` - architecture files of every language-model family at the two paper
+  scales (the shapes shipped with the reference, uttt_llm/configs/main), plus ``configs/lm/named/*.json`` for the
+  benchmark-named shapes and ``configs/lm/balancing/*`` for the loss-free-rate / scope / router-alpha sweeps;
+* ``configs/lm/exp/train_{124M,760M}_32k.toml`` and ``eval_ptl.toml`` - job files (global batch 32 at 32K);
+* ``configs/nvs/<study>/<data>/<name>.yaml`` - view-synthesis runs (ownership ladder, capacity, width, topology,
+  dense widths, schedule, transformer and delta-rule references, 242M scale ladder).
+"""
+from __future__ import annotations
+
+import json
+import os
+from typing import Any, Dict
+
+import yaml
+
+from ..config.lm_config import _COMMON_UTTT, config_from_dict, named_config
+
+ROOT = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "configs")
+
+SCALES = {"124M": dict(hidden_size=768, num_hidden_layers=12, num_heads=12),
+          "760M": dict(hidden_size=1536, num_hidden_layers=24, num_heads=24)}
+MOE = dict(memory_router_share_mode="per_layer", memory_update_aggregate_write=True,
+           memory_aggregate_momentum_mode="pool_mean", memory_update_backward_mode="full",
+           memory_lb_mode="loss_free", memory_lb_scope="pool", fw_num_heads=4, fw_inter_multi=1, w0_w2_low_rank=32)
+
+
+def lm_shapes(scale: str) -> Dict[str, Dict[str, Any]]:
+    base = dict(_COMMON_UTTT, **SCALES[scale], window_size=4096, chunk_size=4096)
+    small = scale == "124M"
+    out = {
+        "uttt_moe": dict(base, **MOE, model_type="uttt_moe", memory_num_experts=48 if small else 96,
+                         memory_num_active_experts=1, memory_loss_free_update_rate=3e-5 if small else 1e-3),
+        "ttt_moe_lb": {**base, **MOE, **dict(model_type="ttt_moe_lb", memory_pool_mode="per_layer",
+                                             memory_update_aggregate_write=False,
+                                             memory_aggregate_momentum_mode="none", memory_num_experts=4,
+                                             memory_lb_scope="layer", memory_loss_free_update_rate=1e-3)},
+        "ttt_moe_no_lb": {**base, **MOE, **dict(model_type="ttt_moe_no_lb", memory_pool_mode="per_layer",
+                                                memory_update_aggregate_write=False,
+                                                memory_aggregate_momentum_mode="none", memory_num_experts=4,
+                                                memory_lb_scope="layer", memory_lb_mode="loss",
+                                                memory_lb_loss_alpha=0.01)},
+        "ttt_dense": dict(base, model_type="ttt_dense", fw_num_heads=4, fw_inter_multi=1, w0_w2_low_rank=0),
+        "lact": dict(base, model_type="lact_swiglu", num_lact_heads=4, inter_multi=1, lact_chunk_size=4096),
+        "transformer": dict(base, model_type="transformer", use_memory_block=False, window_size=None),
+        "transformer_swa": dict(base, model_type="transformer", use_memory_block=False),
+    }
+    for mixer in ("deltanet", "gated_deltanet", "kda", "mamba2", "mom"):
+        out[f"{mixer}_swa"] = dict(base, model_type=f"{mixer}_swa", use_memory_block=False, mixer_head_dim=64)
+    if small:
+        for r in (1, 2, 4, 6):
+            out[f"uttt_dense_r{r}"] = dict(base, model_type="uttt_dense", fw_num_heads=4, uttt_dense_r=r,
+                                           w0_w2_low_rank=0)
+    return out
+
+
+def job_toml(scale: str) -> str:
+    bs = {"124M": 4, "760M": 2}[scale]
+    steps = {"124M": 10240, "760M": 40960}[scale]
+    return f"""# {scale} @ 32K context: per-device batch {bs}; the global batch must be 32 sequences.
+[job]
+dump_folder = "runs"
+print_args = true
+
+[training]
+batch_size = {bs}
+seq_len = 32768
+context_len = 32768
+gradient_accumulation_steps = 1
+expected_global_batch_size = 32
+steps = {steps}
+max_norm = 1.0
+skip_nan_inf = true
+data_parallel_shard_degree = -1
+tensor_parallel_degree = 1
+dataset = "synthetic"
+seed = 42
+fsdp_reshard_after_forward = "never"
+
+[optimizer]
+name = "AdamW"
+eps = 1e-15
+lr = 1e-3
+
+[lr_scheduler]
+warmup_steps = 1024
+decay_type = "cosine"
+lr_min = 0.1
+
+[checkpoint]
+enable_checkpoint = true
+folder = "checkpoint"
+interval = 2048
+keep_latest_k = 2
+load_step = -1
+export_dtype = "float32"
+
+[profiling]
+enable_profiling = false
+profile_freq = 512
+
+[metrics]
+log_freq = 10
+
+[experimental]
+context_parallel_degree = 1
+pipeline_parallel_degree = 1
+"""
+
+
+def nvs_yaml(name: str, block_type: str, params: Dict[str, Any], dim=512, layers=8, size=256, batch=32,
+             views=12, total=128, **training) -> Dict[str, Any]:
+    tr = dict(total_batch_size=total, grad_accum_steps=1, grad_clip_norm=1.0, may_skip_gradnorm_after=1000,
+              allowed_gradnorm_factor=5, dataset="synthetic", num_views=views, eval_num_views=24,
+              batch_size_per_gpu=batch, num_workers=16, lpips_loss_weight=0.0, max_fwdbwd_passes=20000, lr=4e-4,
+              beta1=0.9, beta2=0.95, weight_decay=0.05, warmup=2500, print_every=20, checkpoint_every=500,
+              save_last_n_ckpts=1)
+    tr.update(training)
+    return {"exp_name": name, "model": {"class_name": "uttt_b200.nvs.model.LVSMModel", "image_size": size,
+                                        "patch_size": 8, "dim": dim, "layers": layers,
+                                        "block_config": {"type": block_type, "params": params}}, "training": tr}
+
+
+def nvs_configs() -> Dict[str, Dict[str, Any]]:
+    moe = "uttt_nvs.models.uttt_moe_block.MemoryModel"
+    dense = "uttt_nvs.models.uttt_dense_block.MemoryModel"
+    base = dict(attn_head_dim=64, fw_head_dim=64, inter_multi=3, fw_inter_multi=1, use_muon=False, num_experts=64,
+                num_active_experts=1, router_alpha=1.0, load_balancing_loss_alpha=1e-5, l2_norm=True,
+                pool_mode="shared", router_share_mode="share_all", aggregate_write=True)
+    out = {}
+    for data in ("obj", "dl3dv"):
+        out[f"ownership/{data}/uttt_moe_e64a1"] = nvs_yaml(f"uttt_moe_e64a1_{data}", moe, dict(base))
+        out[f"ownership/{data}/ttt_moe_e8a1"] = nvs_yaml(
+            f"ttt_moe_e8a1_{data}", moe, dict(base, num_experts=8, pool_mode="per_block", aggregate_write=False,
+                                              router_share_mode="per_layer"))
+        out[f"ownership/{data}/uttt_dense_r1"] = nvs_yaml(f"uttt_dense_r1_{data}", dense, dict(
+            attn_head_dim=64, fw_head_dim=64, inter_multi=3, fw_inter_multi=1, use_muon=False, l2_norm=True))
+        out[f"ownership/{data}/ttt_dense"] = nvs_yaml(f"ttt_dense_{data}", dense, dict(
+            attn_head_dim=64, fw_head_dim=64, inter_multi=3, fw_inter_multi=1, use_muon=False, l2_norm=True,
+            pool_mode="per_block"))
+        for e in (16, 32, 128, 256):
+            out[f"capacity/{data}/uttt_moe_e{e}a1"] = nvs_yaml(f"uttt_moe_e{e}a1_{data}", moe, dict(base, num_experts=e))
+        for k in (2, 4):
+            out[f"topology/{data}/uttt_moe_e64a{k}"] = nvs_yaml(f"uttt_moe_e64a{k}_{data}", moe,
+                                                               dict(base, num_active_experts=k))
+        out[f"topology/{data}/uttt_moe_e64a1_perlayer_router"] = nvs_yaml(
+            f"uttt_moe_e64a1_plr_{data}", moe, dict(base, router_share_mode="per_layer"))
+        out[f"topology/{data}/uttt_moe_e64a1_chained"] = nvs_yaml(
+            f"uttt_moe_e64a1_chained_{data}", moe, dict(base, aggregate_write=False))
+        out[f"topology/{data}/uttt_moe_e64a1_p2"] = nvs_yaml(
+            f"uttt_moe_e64a1_p2_{data}", "uttt_nvs.models.uttt_moe_partitioned.MemoryModel", dict(base, num_partitions=2))
+        for m in (2, 4):
+            out[f"width/{data}/uttt_moe_e64a1_w{m}"] = nvs_yaml(f"uttt_moe_e64a1_w{m}_{data}", moe,
+                                                               dict(base, fw_inter_multi=m))
+        for r in (2, 4, 8):
+            out[f"dense/{data}/uttt_dense_r{r}"] = nvs_yaml(f"uttt_dense_r{r}_{data}", dense, dict(
+                attn_head_dim=64, fw_head_dim=64, inter_multi=3, fw_inter_multi=r, use_muon=False, l2_norm=True))
+        out[f"schedule/{data}/uttt_moe_4in2out"] = nvs_yaml(f"uttt_moe_4in2out_{data}", moe, dict(base), views=6)
+        out[f"schedule/{data}/uttt_moe_4in2out"]["model"].update(view_layout="inputs_then_targets", num_input_views=4)
+        out[f"transformer/{data}/transformer"] = nvs_yaml(
+            f"transformer_{data}", "uttt_nvs.models.transformer_block.TransformerModel", dict(attn_head_dim=64, inter_multi=4))
+        out[f"reference/{data}/deltanet"] = nvs_yaml(
+            f"deltanet_{data}", "uttt_nvs.models.deltanet_block.DeltaNetModel", dict(attn_head_dim=64, inter_multi=3))
+        out[f"reference/{data}/gated_deltanet"] = nvs_yaml(
+            f"gated_deltanet_{data}", "uttt_nvs.models.gated_deltanet_block.GatedDeltaNetModel",
+            dict(attn_head_dim=64, inter_multi=3))
+    big = dict(base, num_experts=96, fw_head_dim=192, fw_inter_multi=2, attn_head_dim=64)
+    for size, batch, total in ((256, 8, 512), (512, 2, 128), (1024, 1, 64)):
+        out[f"scale/obj/uttt_moe_large_{size}"] = nvs_yaml(f"uttt_moe_large_{size}", moe, dict(big), dim=768, layers=24,
+                                                          size=size, batch=batch, total=total)
+    out["named/uttt_moe_256_4in2out"] = nvs_yaml(
+        "uttt_moe_256_4in2out", moe, dict(base, num_experts=16, num_active_experts=2, fw_head_dim=64), dim=768,
+        layers=24, size=256, batch=16, total=128, views=6)
+    out["named/uttt_moe_256_4in2out"]["model"].update(view_layout="inputs_then_targets", num_input_views=4)
+    return out
+
+
+def main() -> None:
+    for scale in SCALES:
+        for name, cfg in lm_shapes(scale).items():
+            path = os.path.join(ROOT, "lm", scale, f"{name}.json")
+            os.makedirs(os.path.dirname(path), exist_ok=True)
+            with open(path, "w") as fh:
+                fh.write(config_from_dict(cfg).to_json_string())
+        path = os.path.join(ROOT, "lm", "exp", f"train_{scale}_32k.toml")
+        os.makedirs(os.path.dirname(path), exist_ok=True)
+        with open(path, "w") as fh:
+            fh.write(job_toml(scale))
+    with open(os.path.join(ROOT, "lm", "exp", "eval_ptl.toml"), "w") as fh:
+        fh.write('[job]\ndump_folder = "runs/eval"\n\n[training]\nbatch_size = 1\nseq_len = 32768\ndataset = "synthetic"\n\n'
+                 '[eval]\nptl_start = 30000\nmax_batches = 64\n')
+    os.makedirs(os.path.join(ROOT, "lm", "named"), exist_ok=True)
+    for name in ("760M-uttt-moe", "124M-uttt-moe", "124M-uttt-dense", "tiny-uttt-moe"):
+        with open(os.path.join(ROOT, "lm", "named", f"{name}.json"), "w") as fh:
+            fh.write(named_config(name).to_json_string())
+    for scale in SCALES:
+        base = lm_shapes(scale)["uttt_moe"]
+        sweeps = {f"rate_{r:g}": dict(memory_loss_free_update_rate=r) for r in (1e-5, 1e-4, 1e-3, 1e-2)}
+        sweeps.update({"scope_layer": dict(memory_lb_scope="layer"), "aux_loss": dict(memory_lb_mode="loss", memory_lb_loss_alpha=0.01),
+                       "no_balancing": dict(memory_lb_mode="none"), "alpha_0.5": dict(memory_router_alpha=0.5),
+                       "alpha_2": dict(memory_router_alpha=2.0)})
+        for name, over in sweeps.items():
+            path = os.path.join(ROOT, "lm", "balancing", scale, f"uttt_moe_{name}.json")
+            os.makedirs(os.path.dirname(path), exist_ok=True)
+            with open(path, "w") as fh:
+                fh.write(config_from_dict(dict(base, **over)).to_json_string())
+    for rel, cfg in nvs_configs().items():
+        path = os.path.join(ROOT, "nvs", rel + ".yaml")
+        os.makedirs(os.path.dirname(path), exist_ok=True)
+        with open(path, "w") as fh:
+            yaml.safe_dump(cfg, fh, sort_keys=False)
+    print(f"wrote configs under {ROOT}")
+
+
+if __name__ == "__main__":
+    main()
