@@ -131,6 +131,19 @@ def _plan(bsz=2, n=700, e=4, k=2, seed=0):
     return ops.build_group_plan(idx, e)
 
 
+@pytest.mark.parametrize("bsz,n,e,k", [(2, 700, 4, 2), (3, 5000, 32, 2), (1, 64, 1, 1), (2, 2048, 96, 1)])
+def test_group_plan_kernel_matches_reference(bsz, n, e, k):
+    _ext()
+    g = torch.Generator().manual_seed(n)
+    idx = torch.randn(bsz, n, e, generator=g).topk(k, -1).indices.to(DEV)
+    plan = ops.build_group_plan(idx, e)
+    dest, offsets, sizes, tile_group, rows = ref.build_group_plan(idx, e)
+    assert plan.rows_padded == rows
+    assert torch.equal(plan.sizes.cpu(), sizes.cpu()) and torch.equal(plan.offsets.cpu(), offsets.cpu())
+    assert torch.equal(plan.tile_group.cpu(), tile_group.cpu())
+    assert torch.equal(plan.dest.cpu(), dest.cpu())          # same stable (token-major) order inside groups
+
+
 def test_permute_unpermute():
     _ext()
     plan = _plan()
@@ -153,6 +166,19 @@ def test_permute_unpermute():
     _close(gw, gwr, 0.15, 3e-2)
     (gx,) = torch.autograd.grad(xp, x, torch.ones_like(xp))
     _close(gx, torch.full_like(gx, float(k)), 0, 0)
+    # weighted scatter (value rows scaled by their combine weight) and its gradients
+    w2 = torch.rand(r, k, device=DEV, requires_grad=True)
+    xs = ops.permute_rows(x, plan, w2)
+    xr = x.detach().float().requires_grad_(True)
+    w2r = w2.detach().clone().requires_grad_(True)
+    scaled = (xr.unsqueeze(1) * w2r.unsqueeze(-1)).reshape(-1, 128)
+    xsr = torch.zeros(plan.rows_padded, 128, device=DEV).index_copy(0, plan.dest.reshape(-1), scaled)
+    _close(xs, xsr, 2e-2, 2e-2)
+    c = torch.randn_like(xs)
+    ga, gb = torch.autograd.grad(xs, [x, w2], c)
+    gar, gbr = torch.autograd.grad(xsr, [xr, w2r], c.float())
+    _close(ga, gar, 3e-2, 3e-2)
+    _close(gb, gbr, 0.2, 3e-2)
 
 
 @pytest.mark.parametrize("k,n", [(128, 256), (384, 3072), (64, 64)])
@@ -241,6 +267,28 @@ def test_bmm_nt_and_newton_schulz():
     torch.cuda.synchronize()
     _status_ok()
     _close(out, want, 0.15, 2e-2)
+    # transpose-free modes and their gradients
+    kn = torch.randn(6, 256, 192, device=DEV, dtype=torch.bfloat16, requires_grad=True)      # [B, K, N]
+    ar = a.detach().clone().requires_grad_(True)
+    c1 = ops.bmm(ar, kn, 1)
+    ar32, kn32 = ar.detach().float().requires_grad_(True), kn.detach().float().requires_grad_(True)
+    c1r = ar32 @ kn32
+    _close(c1, c1r, 0.3, 2e-2, "nn")
+    gc = torch.randn_like(c1)
+    g1, g2 = torch.autograd.grad(c1, [ar, kn], gc)
+    g1r, g2r = torch.autograd.grad(c1r, [ar32, kn32], gc.float())
+    _close(g1, g1r, 0.4, 3e-2, "nn dA")
+    _close(g2, g2r, 0.4, 3e-2, "nn dB")
+    km = torch.randn(6, 256, 128, device=DEV, dtype=torch.bfloat16)                           # [B, K, M]
+    c2 = ops.bmm(km, kn.detach(), 2)
+    _close(c2, km.float().transpose(1, 2) @ kn.detach().float(), 0.3, 2e-2, "tn")
+    torch.cuda.synchronize()
+    _status_ok()
+    for shape in ((5, 384, 128), (3, 128, 384)):
+        gg = torch.randn(*shape, device=DEV)
+        xx = ops.newton_schulz(gg)
+        xr_ = ref.newton_schulz(gg.cpu(), compute_dtype=torch.float32)
+        _close(xx.cpu(), xr_, 6e-2, 6e-2, f"ns {shape}")
     g = torch.randn(5, 384, 128, device=DEV)
     x = ops.newton_schulz(g)
     xr = ref.newton_schulz(g.cpu(), compute_dtype=torch.float32)

@@ -119,9 +119,8 @@ def pool_raw_grad(k_rows: torch.Tensor, v_rows: torch.Tensor, lr_rows: torch.Ten
     w1 = state_w1.reshape(g, d, inter2 // 2)
     dt = w02.dtype
     kp = ops.permute_rows(k_rows.reshape(bsz * n, d).to(dt), plan)
-    # v scaled by its combine weight per routed copy, then scattered
-    vw = (v_rows.reshape(bsz * n, 1, d).float() * routing.weights.unsqueeze(-1)).to(dt)
-    vp = _permute_per_choice(vw, plan)
+    # v scaled by its combine weight per routed copy while it is scattered
+    vp = ops.permute_rows(v_rows.reshape(bsz * n, d).to(dt), plan, routing.weights)
     lrp = _permute_per_choice(lr_rows.reshape(bsz * n, 1, 3).float().expand(-1, plan.topk, -1), plan)
     if acc is not None:
         return ops.fw_write_grad_accumulate(kp, vp, lrp, w02, w1, plan, acc[0], acc[1])

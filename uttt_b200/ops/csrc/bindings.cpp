@@ -17,7 +17,7 @@ at::Tensor swiglu_bwd(at::Tensor dh, at::Tensor y02);
 std::vector<at::Tensor> swiglu_bwd_bwd(at::Tensor G, at::Tensor dh, at::Tensor y02);
 std::vector<at::Tensor> fw_write_pw_fwd(at::Tensor y02, at::Tensor dh, at::Tensor lr);
 std::vector<at::Tensor> fw_write_pw_bwd(at::Tensor C, at::Tensor Ch, at::Tensor y02, at::Tensor dh, at::Tensor lr);
-at::Tensor permute_rows(at::Tensor x, at::Tensor dest, int64_t rows_padded);
+at::Tensor permute_rows(at::Tensor x, at::Tensor dest, int64_t rows_padded, c10::optional<at::Tensor> w);
 at::Tensor unpermute_rows(at::Tensor y, at::Tensor dest, c10::optional<at::Tensor> w);
 std::vector<at::Tensor> unpermute_rows_bwd(at::Tensor dout, at::Tensor y, at::Tensor dest, at::Tensor w);
 void sumsq_accum(at::Tensor g, double scale, at::Tensor out);
@@ -26,6 +26,7 @@ void adamw_flat(at::Tensor p, at::Tensor g, at::Tensor m, at::Tensor v, c10::opt
                 double gmul, int64_t decay_hi);
 void ce_fwd_bwd_(at::Tensor logits, at::Tensor labels, at::Tensor loss, int64_t ignore_index);
 int64_t launch_count();
+std::vector<at::Tensor> build_group_plan(at::Tensor expert_idx, int64_t num_experts);
 at::Tensor plucker_embed(at::Tensor image, at::Tensor fxfycxcy, at::Tensor c2w, at::Tensor is_target, int64_t patch);
 
 at::Tensor gg_nt(at::Tensor x, at::Tensor w, at::Tensor tile_group);
@@ -34,6 +35,7 @@ at::Tensor gg_tn_segments(at::Tensor a, at::Tensor b, at::Tensor offsets, int64_
                           at::ScalarType out_dtype, c10::optional<at::Tensor> accumulate_into);
 at::Tensor bmm_nt(at::Tensor a, at::Tensor b, double alpha, c10::optional<at::Tensor> d, double beta);
 at::Tensor gemm_status(at::Tensor like);
+at::Tensor bmm_general(at::Tensor a, at::Tensor b, int64_t mode, double alpha, c10::optional<at::Tensor> d, double beta);
 void rs_sumsq(std::vector<int64_t> grad_ptrs, int64_t rank, int64_t shard_off, at::Tensor out, double scale,
               at::Tensor sumsq, bool grads_bf16);
 void adamw_scatter(at::Tensor p, at::Tensor g, at::Tensor m, at::Tensor v, std::vector<int64_t> compute_ptrs,
@@ -61,12 +63,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("adamw_flat", &adamw_flat);
   m.def("ce_fwd_bwd_", &ce_fwd_bwd_);
   m.def("launch_count", &launch_count);
+  m.def("build_group_plan", &build_group_plan);
   m.def("plucker_embed", &plucker_embed);
   m.def("gg_nt", &gg_nt);
   m.def("gg_nn", &gg_nn);
   m.def("gg_tn_segments", &gg_tn_segments);
   m.def("bmm_nt", &bmm_nt);
   m.def("gemm_status", &gemm_status);
+  m.def("bmm_general", &bmm_general);
   m.def("swa_fwd", &swa_fwd);
   m.def("rs_sumsq", &rs_sumsq);
   m.def("adamw_scatter", &adamw_scatter);

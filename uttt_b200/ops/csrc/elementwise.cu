@@ -659,17 +659,30 @@ std::vector<at::Tensor> fw_write_pw_bwd(at::Tensor C, at::Tensor Ch, at::Tensor 
 // ------------------------------------------------------------------------------------ row permutation
 // out[dest[i, j]] = x[i] (one warp per (i, j)); out is zero-filled first so padding rows are zero.
 template <typename T>
-__global__ void permute_rows_kernel(const T* __restrict__ x, const int64_t* __restrict__ dest, T* __restrict__ out,
-                                    size_t n_copies, int k, int d) {
+__global__ void permute_rows_kernel(const T* __restrict__ x, const int64_t* __restrict__ dest,
+                                    const float* __restrict__ w, T* __restrict__ out, size_t n_copies, int k,
+                                    int d) {
   size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   int lane = threadIdx.x & 31;
   size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
-  int nv = d >> 3;
   for (size_t c = warp; c < n_copies; c += nwarps) {
-    const uint4* src = reinterpret_cast<const uint4*>(x + (c / k) * d);
-    uint4* dst = reinterpret_cast<uint4*>(out + (size_t)dest[c] * d);
-    constexpr int per = 16 / sizeof(T);   // elements per uint4
-    for (int v = lane; v < d / per; v += 32) dst[v] = src[v];
+    const T* src = x + (c / k) * d;
+    T* dst = out + (size_t)dest[c] * d;
+    if (w == nullptr) {
+      constexpr int per = 16 / sizeof(T);   // elements per uint4
+      const uint4* s4 = reinterpret_cast<const uint4*>(src);
+      uint4* d4 = reinterpret_cast<uint4*>(dst);
+      for (int v = lane; v < d / per; v += 32) d4[v] = s4[v];
+    } else {
+      float wj = w[c];
+      for (int v = lane; v < (d >> 3); v += 32) {
+        float f[8];
+        Vec8<T>::load(src + v * 8, f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] *= wj;
+        Vec8<T>::store(dst + v * 8, f);
+      }
+    }
   }
 }
 
@@ -728,16 +741,20 @@ __global__ void unpermute_rows_bwd_kernel(const T* __restrict__ dout, const T* _
   }
 }
 
-at::Tensor permute_rows(at::Tensor x, at::Tensor dest, int64_t rows_padded) {
+at::Tensor permute_rows(at::Tensor x, at::Tensor dest, int64_t rows_padded, c10::optional<at::Tensor> w) {
   c10::cuda::CUDAGuard guard(x.device());
   int d = x.size(1);
   int k = dest.size(1);
   TORCH_CHECK(x.is_contiguous() && dest.is_contiguous() && dest.scalar_type() == at::kLong && d % 8 == 0);
   auto out = at::zeros({rows_padded, d}, x.options());
   size_t n = (size_t)dest.numel();
+  at::Tensor wf;
+  if (w.has_value() && w->defined()) wf = w->to(at::kFloat).contiguous();
   int blocks = (int)std::max<size_t>(1, std::min<size_t>((n + 7) / 8, (size_t)sm_count() * 16));
   UTTT_DISPATCH_FLOAT(x, {
-    permute_rows_kernel<T><<<blocks, 256, 0, cur_stream()>>>(ptr<T>(x), ptr<int64_t>(dest), ptr<T>(out), n, k, d);
+    permute_rows_kernel<T><<<blocks, 256, 0, cur_stream()>>>(ptr<T>(x), ptr<int64_t>(dest),
+                                                            wf.defined() ? ptr<float>(wf) : nullptr, ptr<T>(out), n,
+                                                            k, d);
   });
   count_launch(2);
   return out;
@@ -777,6 +794,117 @@ std::vector<at::Tensor> unpermute_rows_bwd(at::Tensor dout, at::Tensor y, at::Te
   });
   count_launch(2);
   return {dy, dw};
+}
+
+// ------------------------------------------------------------------------------------ routing plan
+// expert_idx [B, NK] (NK = tokens*heads*topk entries per sequence, token-major) -> tile-padded expert-major layout.
+// Group g = b*E + e; every group starts on a multiple of 128 rows.  Three launches, no host sync, deterministic
+// (entries keep their token order inside a group).
+constexpr int kPlanBlock = 1024;
+
+__global__ void plan_count_kernel(const int* __restrict__ idx, int* __restrict__ blk_counts, int nk, int E,
+                                  int nblk) {
+  extern __shared__ int hist[];
+  int b = blockIdx.y, blk = blockIdx.x;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) hist[e] = 0;
+  __syncthreads();
+  int i = blk * kPlanBlock + threadIdx.x;
+  if (i < nk) atomicAdd(&hist[idx[(size_t)b * nk + i]], 1);
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) blk_counts[((size_t)b * nblk + blk) * E + e] = hist[e];
+}
+
+// single CTA: per-group sizes, per-block exclusive offsets inside each group, padded group offsets, tile table
+__global__ void plan_scan_kernel(int* __restrict__ blk_counts, int* __restrict__ sizes, int* __restrict__ offsets,
+                                 int* __restrict__ tile_group, int B, int E, int nblk, int t_max) {
+  int G = B * E;
+  __shared__ int carry;
+  for (int g = threadIdx.x; g < G; g += blockDim.x) {
+    int b = g / E, e = g % E;
+    int run = 0;
+    for (int blk = 0; blk < nblk; ++blk) {
+      size_t at = ((size_t)b * nblk + blk) * E + e;
+      int c = blk_counts[at];
+      blk_counts[at] = run;            // exclusive offset of this block inside the group
+      run += c;
+    }
+    sizes[g] = run;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int g = 0; g < G; ++g) {
+      offsets[g] = acc;
+      acc += (sizes[g] + 127) / 128 * 128;
+    }
+    offsets[G] = acc;
+    carry = acc;
+  }
+  __syncthreads();
+  for (int t = threadIdx.x; t < t_max; t += blockDim.x) tile_group[t] = -1;
+  __syncthreads();
+  for (int g = threadIdx.x; g < G; g += blockDim.x) {
+    for (int t = offsets[g] / 128; t < offsets[g + 1] / 128; ++t) tile_group[t] = g;
+  }
+}
+
+__global__ void plan_dest_kernel(const int* __restrict__ idx, const int* __restrict__ blk_offsets,
+                                 const int* __restrict__ offsets, int64_t* __restrict__ dest, int nk, int E,
+                                 int nblk) {
+  extern __shared__ int warp_hist[];          // [32 warps][E]
+  int b = blockIdx.y, blk = blockIdx.x;
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int t = threadIdx.x; t < 32 * E; t += blockDim.x) warp_hist[t] = 0;
+  __syncthreads();
+  int i = blk * kPlanBlock + threadIdx.x;
+  bool valid = i < nk;
+  int e = valid ? idx[(size_t)b * nk + i] : -1 - lane;      // invalid lanes never match anyone
+  unsigned peers = __match_any_sync(0xffffffffu, e);
+  int rank = __popc(peers & ((1u << lane) - 1u));
+  if (valid && rank == 0) warp_hist[warp * E + e] = __popc(peers);
+  __syncthreads();
+  for (int ee = threadIdx.x; ee < E; ee += blockDim.x) {     // exclusive scan over the 32 warps, per expert
+    int run = 0;
+    for (int w = 0; w < 32; ++w) {
+      int c = warp_hist[w * E + ee];
+      warp_hist[w * E + ee] = run;
+      run += c;
+    }
+  }
+  __syncthreads();
+  if (valid) {
+    int g = b * E + e;
+    dest[(size_t)b * nk + i] = (int64_t)offsets[g] + blk_offsets[((size_t)b * nblk + blk) * E + e] +
+                               warp_hist[warp * E + e] + rank;
+  }
+}
+
+std::vector<at::Tensor> build_group_plan(at::Tensor expert_idx, int64_t num_experts) {
+  c10::cuda::CUDAGuard guard(expert_idx.device());
+  TORCH_CHECK(expert_idx.scalar_type() == at::kInt && expert_idx.is_contiguous() && expert_idx.dim() == 3);
+  int B = expert_idx.size(0), n = expert_idx.size(1), k = expert_idx.size(2);
+  int E = (int)num_experts, nk = n * k, G = B * E;
+  TORCH_CHECK(E <= 256, "at most 256 experts");
+  int nblk = (nk + kPlanBlock - 1) / kPlanBlock;
+  int64_t total = (int64_t)B * nk;
+  int t_max = (int)((total + 127) / 128) + G;
+  auto iopt = expert_idx.options();
+  auto blk_counts = at::empty({B, nblk, E}, iopt);
+  auto sizes = at::empty({G}, iopt);
+  auto offsets = at::empty({G + 1}, iopt);
+  auto tile_group = at::empty({t_max}, iopt);
+  auto dest = at::empty({(int64_t)B * n, k}, iopt.dtype(at::kLong));
+  auto stream = cur_stream();
+  plan_count_kernel<<<dim3(nblk, B), kPlanBlock, E * sizeof(int), stream>>>(expert_idx.data_ptr<int>(),
+                                                                           blk_counts.data_ptr<int>(), nk, E, nblk);
+  plan_scan_kernel<<<1, 1024, 0, stream>>>(blk_counts.data_ptr<int>(), sizes.data_ptr<int>(),
+                                          offsets.data_ptr<int>(), tile_group.data_ptr<int>(), B, E, nblk, t_max);
+  plan_dest_kernel<<<dim3(nblk, B), kPlanBlock, 32 * E * sizeof(int), stream>>>(
+      expert_idx.data_ptr<int>(), blk_counts.data_ptr<int>(), offsets.data_ptr<int>(), dest.data_ptr<int64_t>(), nk,
+      E, nblk);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch(3);
+  return {dest, offsets, sizes, tile_group, at::scalar_tensor((int64_t)t_max * 128, iopt.dtype(at::kLong).device(at::kCPU))};
 }
 
 // ------------------------------------------------------------------------------------ optimizer

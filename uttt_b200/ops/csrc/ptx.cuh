@@ -173,6 +173,13 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
       : "r"(taddr)
       : "memory");
 }
+// 64 consecutive columns per thread (two back-to-back 32-column loads in flight, no wait in between).
+__device__ __forceinline__ void tmem_ld_32x64(uint32_t taddr, uint32_t (&r)[64]) {
+  uint32_t (&lo)[32] = *reinterpret_cast<uint32_t (*)[32]>(&r[0]);
+  uint32_t (&hi)[32] = *reinterpret_cast<uint32_t (*)[32]>(&r[32]);
+  tmem_ld_32x32(taddr, lo);
+  tmem_ld_32x32(taddr + 32, hi);
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // registers -> TMEM (32 lanes x 32 columns of 32-bit words)
 __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {

@@ -29,7 +29,8 @@
 
 namespace uttt {
 
-enum GemmMode { kNT = 0, kNN = 1, kTN = 2, kBMM = 3 };
+enum GemmMode { kNT = 0, kNN = 1, kTN = 2, kBMM = 3, kBNN = 4, kBTN = 5 };
+__host__ __device__ constexpr bool is_batched(int m) { return m == kBMM || m == kBNN || m == kBTN; }
 
 struct GemmParams {
   const int* tile_group;    // NT/NN: [tiles]
@@ -399,6 +400,18 @@ __global__ void __launch_bounds__(192) tc_gemm_persistent_kernel(const __grid_co
           if (MODE == kNT || MODE == kBMM) {
             ptx::tma_load_2d(sa, &tma_a, full_bar(s), kb * BK, c.a_row0);
             ptx::tma_load_2d(sb, &tma_b, full_bar(s), kb * BK, c.g * p.N + c.n0);
+          } else if (MODE == kBNN) {
+            ptx::tma_load_2d(sa, &tma_a, full_bar(s), kb * BK, c.a_row0);
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              ptx::tma_load_2d(sb + j * (BK * 128), &tma_b, full_bar(s), c.n0 + 64 * j, c.g * p.K + kb * BK);
+          } else if (MODE == kBTN) {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              ptx::tma_load_2d(sa + j * (BK * 128), &tma_a, full_bar(s), c.m0 + 64 * j, c.g * p.K + kb * BK);
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              ptx::tma_load_2d(sb + j * (BK * 128), &tma_b, full_bar(s), c.n0 + 64 * j, c.g * p.K + kb * BK);
           } else if (MODE == kNN) {
             ptx::tma_load_2d(sa, &tma_a, full_bar(s), kb * BK, c.a_row0);
 #pragma unroll
@@ -426,8 +439,8 @@ __global__ void __launch_bounds__(192) tc_gemm_persistent_kernel(const __grid_co
   } else if (warp == 5) {
     if (lane == 0) {
       // ================= MMA issuer =================
-      constexpr int a_mn = (MODE == kTN) ? 1 : 0;
-      constexpr int b_mn = (MODE == kNN || MODE == kTN) ? 1 : 0;
+      constexpr int a_mn = (MODE == kTN || MODE == kBTN) ? 1 : 0;
+      constexpr int b_mn = (MODE == kNN || MODE == kTN || MODE == kBNN || MODE == kBTN) ? 1 : 0;
       constexpr uint32_t idesc = ptx::make_instr_desc(BM, BN, a_mn, b_mn);
       uint32_t it = 0, acc_it = 0;
       bool ok = true;
@@ -482,45 +495,55 @@ __global__ void __launch_bounds__(192) tc_gemm_persistent_kernel(const __grid_co
       if (!ok) break;
       ptx::tc_fence_after_sync();
       const uint32_t tmem_acc = tmem_base + ab * BN + ((uint32_t)(warp * 32) << 16);
-      const __nv_bfloat16* drow = (MODE == kBMM && p.addend != nullptr)
+      const __nv_bfloat16* drow = (is_batched(MODE) && p.addend != nullptr)
           ? reinterpret_cast<const __nv_bfloat16*>(p.addend) + (c.out_row0 + r) * ldo + c.n0 : nullptr;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t raw[32];
-        ptx::tmem_ld_32x32(tmem_acc + c0, raw);
-        ptx::tmem_ld_wait();
-        float v[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]);
-        if (MODE == kBMM) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] *= p.alpha;
-          if (drow != nullptr) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              float d[8];
-              Vec8<__nv_bfloat16>::load(drow + c0 + i, d);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) v[i + j] += p.beta * d[j];
-            }
-          }
+      // software-pipelined drain: the TMEM load of chunk c+1 is in flight while chunk c is converted and stored
+      constexpr int CH = (BN >= 64) ? 64 : 32;
+      uint32_t raw[2][CH];
+      auto issue = [&](int buf, int c0) {
+        if (CH == 64) {
+          ptx::tmem_ld_32x64(tmem_acc + c0, *reinterpret_cast<uint32_t (*)[64]>(&raw[buf][0]));
+        } else {
+          ptx::tmem_ld_32x32(tmem_acc + c0, *reinterpret_cast<uint32_t (*)[32]>(&raw[buf][0]));
         }
+      };
+      issue(0, 0);
+      ptx::tmem_ld_wait();
+#pragma unroll
+      for (int ci = 0; ci < BN / CH; ++ci) {
+        const int c0 = ci * CH;
+        const int buf = ci & 1;
+        if (ci + 1 < BN / CH) issue(buf ^ 1, c0 + CH);
+        // read-modify-write operands of the whole chunk are fetched up front so their latencies overlap
+        float addv[CH];
+        const bool has_add = (MODE == kTN && p.accumulate) || (is_batched(MODE) && drow != nullptr);
         if (MODE == kTN && p.accumulate) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            float d[8];
-            Vec8<OutT>::load(orow + c0 + i, d);
+          for (int i = 0; i < CH; i += 8) Vec8<OutT>::load(orow + c0 + i, *reinterpret_cast<float (*)[8]>(&addv[i]));
+        } else if (is_batched(MODE) && drow != nullptr) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[i + j] += d[j];
-          }
+          for (int i = 0; i < CH; i += 8)
+            Vec8<__nv_bfloat16>::load(drow + c0 + i, *reinterpret_cast<float (*)[8]>(&addv[i]));
         }
 #pragma unroll
-        for (int i = 0; i < 32; i += 8) {
+        for (int i = 0; i < CH; i += 8) {
           float o[8];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] = v[i + j];
+          for (int j = 0; j < 8; ++j) o[j] = __uint_as_float(raw[buf][i + j]);
+          if (is_batched(MODE)) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] *= p.alpha;
+            if (has_add) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) o[j] += p.beta * addv[i + j];
+            }
+          } else if (has_add) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] += addv[i + j];
+          }
           Vec8<OutT>::store(orow + c0 + i, o);
         }
+        if (ci + 1 < BN / CH) ptx::tmem_ld_wait();
       }
       // this accumulator buffer may be overwritten by the MMA issuer once all 128 threads have drained it
       ptx::tc_fence_before_sync();
@@ -614,6 +637,9 @@ static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams
     count_launch();
     return;
   }
+  if constexpr (MODE == kBNN || MODE == kBTN) {
+    TORCH_CHECK(false, "the non-persistent GEMM has no batched NN / TN mode");
+  } else {
   constexpr int STAGES = (BN >= 256) ? 3 : (BN >= 128 ? 3 : 4);
   using L = SmemLayout<BN, STAGES>;
   auto kernel = tc_gemm_kernel<MODE, BN, STAGES, OutT>;
@@ -625,6 +651,7 @@ static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams
   kernel<<<grid, 128, L::kTotal, stream>>>(ta, tb, p);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   count_launch();
+  }
 }
 
 static int pick_bn(int n) { return (n % 256 == 0) ? 256 : ((n % 128 == 0) ? 128 : 64); }
@@ -714,7 +741,54 @@ at::Tensor gg_tn_segments(at::Tensor a, at::Tensor b, at::Tensor offsets, int64_
   return out;
 }
 
+// out[b] = alpha * op(A[b]) . op(B[b])^T-like products without materialised transposes:
+//   mode 0 (NT): A [B, M, K], Bm [B, N, K]  -> A . Bm^T
+//   mode 1 (NN): A [B, M, K], Bm [B, K, N]  -> A . Bm
+//   mode 2 (TN): A [B, K, M], Bm [B, K, N]  -> A^T . Bm
+at::Tensor bmm_general(at::Tensor a, at::Tensor b, int64_t mode, double alpha, c10::optional<at::Tensor> d,
+                       double beta) {
+  c10::cuda::CUDAGuard guard(a.device());
+  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && a.is_contiguous() &&
+              b.is_contiguous() && a.dim() == 3 && b.dim() == 3 && mode >= 0 && mode <= 2);
+  int B = a.size(0);
+  int M = mode == 2 ? a.size(2) : a.size(1);
+  int K = mode == 2 ? a.size(1) : a.size(2);
+  int N = mode == 0 ? b.size(1) : b.size(2);
+  int Kb = mode == 0 ? b.size(2) : b.size(1);
+  TORCH_CHECK(b.size(0) == B && Kb == K && M % BM == 0 && N % 64 == 0 && K % BK == 0);
+  auto out = at::empty({B, M, N}, a.options());
+  GemmParams p{};
+  p.groups = B; p.M = M; p.N = N; p.K = K; p.out = out.data_ptr();
+  p.alpha = (float)alpha; p.beta = (float)beta;
+  at::Tensor dc;
+  if (d.has_value() && d->defined()) {
+    dc = d->contiguous();
+    TORCH_CHECK(dc.scalar_type() == at::kBFloat16 && dc.numel() == out.numel());
+    p.addend = dc.data_ptr();
+  }
+  p.status = status_word(a.device()).data_ptr<int>();
+  const int bn = pick_bn(N);
+  dim3 grid(N / bn, M / BM, B);
+  CUtensorMap ta = mode == 2 ? make_tmap_2d_bf16(a.data_ptr(), (uint64_t)B * K, M, BK, 64)
+                             : make_tmap_2d_bf16(a.data_ptr(), (uint64_t)B * M, K, BM, BK);
+  CUtensorMap tb = mode == 0 ? make_tmap_2d_bf16(b.data_ptr(), (uint64_t)B * N, K, bn, BK)
+                             : make_tmap_2d_bf16(b.data_ptr(), (uint64_t)B * K, N, BK, 64);
+#define UTTT_BMM_DISPATCH(MODE_)                                                     \
+  if (bn == 256) launch_gemm<MODE_, 256, __nv_bfloat16>(ta, tb, p, grid);            \
+  else if (bn == 128) launch_gemm<MODE_, 128, __nv_bfloat16>(ta, tb, p, grid);       \
+  else launch_gemm<MODE_, 64, __nv_bfloat16>(ta, tb, p, grid);
+  if (mode == 0) { UTTT_BMM_DISPATCH(kBMM) }
+  else if (mode == 1) { UTTT_BMM_DISPATCH(kBNN) }
+  else { UTTT_BMM_DISPATCH(kBTN) }
+#undef UTTT_BMM_DISPATCH
+  return out;
+}
+
 at::Tensor bmm_nt(at::Tensor a, at::Tensor b, double alpha, c10::optional<at::Tensor> d, double beta) {
+  return bmm_general(a, b, 0, alpha, d, beta);
+}
+
+at::Tensor bmm_nt_legacy(at::Tensor a, at::Tensor b, double alpha, c10::optional<at::Tensor> d, double beta) {
   c10::cuda::CUDAGuard guard(a.device());
   TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && a.is_contiguous() &&
               b.is_contiguous() && a.dim() == 3 && b.dim() == 3);

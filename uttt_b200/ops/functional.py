@@ -260,10 +260,10 @@ class GroupPlan:
 def build_group_plan(expert_idx: torch.Tensor, num_experts: int) -> GroupPlan:
     bsz, n, k = expert_idx.shape
     ext = _kernel("build_group_plan", expert_idx)
-    if ext is not None:
-        _count(3)
-        dest, offsets, sizes, tile_group, rows_padded = ext.build_group_plan(
-            expert_idx.to(torch.int32).contiguous(), int(num_experts))
+    if ext is not None and num_experts <= 256:
+        dest, offsets, sizes, tile_group, _ = ext.build_group_plan(expert_idx.to(torch.int32).contiguous(),
+                                                                   int(num_experts))
+        rows_padded = ((bsz * n * k + TILE_ROWS - 1) // TILE_ROWS + bsz * num_experts) * TILE_ROWS
     else:
         dest, offsets, sizes, tile_group, rows_padded = ref.build_group_plan(expert_idx, num_experts)
     return GroupPlan(dest, offsets, sizes, tile_group, int(rows_padded), bsz * num_experts, k)
@@ -271,15 +271,23 @@ def build_group_plan(expert_idx: torch.Tensor, num_experts: int) -> GroupPlan:
 
 class _Permute(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, dest, rows_padded):
+    def forward(ctx, x, dest, rows_padded, weights):
         ext = cuda_ext(x)
-        ctx.save_for_backward(dest)
-        return ext.permute_rows(x.contiguous(), dest, int(rows_padded))
+        x = x.contiguous()
+        ctx.save_for_backward(dest, weights, x if weights is not None else None)
+        return ext.permute_rows(x, dest, int(rows_padded), weights)
 
     @staticmethod
     def backward(ctx, dout):
-        (dest,) = ctx.saved_tensors
-        return _Unpermute.apply(dout, dest, None), None, None
+        dest, weights, x = ctx.saved_tensors
+        if weights is None:
+            return _Unpermute.apply(dout, dest, None), None, None, None
+        ext = cuda_ext(dout)
+        dout = dout.contiguous()
+        dx = ext.unpermute_rows(dout, dest, weights)
+        # dw[i, j] = <x[i], dout[dest[i, j]]>
+        _, dw = ext.unpermute_rows_bwd(x, dout, dest, weights)
+        return dx, None, None, dw.to(weights.dtype)
 
 
 class _Unpermute(torch.autograd.Function):
@@ -294,17 +302,23 @@ class _Unpermute(torch.autograd.Function):
     def backward(ctx, dout):
         y, dest, weights = ctx.saved_tensors
         if weights is None:
-            return _Permute.apply(dout, dest, ctx.rows), None, None
+            return _Permute.apply(dout, dest, ctx.rows, None), None, None
         ext = cuda_ext(y)
         dy, dw = ext.unpermute_rows_bwd(dout.contiguous(), y, dest, weights)
         return dy, None, dw.to(weights.dtype)
 
 
-def permute_rows(x: torch.Tensor, plan: GroupPlan) -> torch.Tensor:
-    """[R, D] token-major rows -> [rows_padded, D] expert-major (each row copied to its top-k groups)."""
+def permute_rows(x: torch.Tensor, plan: GroupPlan, weights: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """[R, D] token-major rows -> [rows_padded, D] expert-major (each row copied to its top-k groups,
+    copy j scaled by ``weights[i, j]`` when given)."""
     if _kernel("permute_rows", x) is not None and x.shape[-1] % 8 == 0:
-        return _Permute.apply(x, plan.dest, plan.rows_padded)
-    return ref.permute_rows(x, plan.dest, plan.rows_padded)
+        return _Permute.apply(x, plan.dest, plan.rows_padded, weights)
+    if weights is None:
+        return ref.permute_rows(x, plan.dest, plan.rows_padded)
+    k = plan.dest.shape[1]
+    scaled = (x.unsqueeze(1).float() * weights.unsqueeze(-1).float()).to(x.dtype).reshape(-1, x.shape[-1])
+    out = scaled.new_zeros(plan.rows_padded, x.shape[-1])
+    return out.index_copy(0, plan.dest.reshape(-1), scaled)
 
 
 def unpermute_rows(y: torch.Tensor, plan: GroupPlan, weights: Optional[torch.Tensor]) -> torch.Tensor:
@@ -572,52 +586,89 @@ def fw_write_grad_accumulate(kp, vp, lrp, w02, w1, plan: GroupPlan, acc02: torch
 # =========================================================================== Newton-Schulz
 def newton_schulz(g: torch.Tensor, coeffs=ref.NS5_COEFFS) -> torch.Tensor:
     """Batched Newton-Schulz orthogonalisation (Muon).  g: [b, m, n] -> same shape, bf16 on GPU."""
-    ext = _kernel("bmm_nt", g)
-    if ext is None:
+    ext = _kernel("bmm_general", g)
+    if ext is None or g.shape[1] % 128 != 0 or g.shape[2] % 128 != 0:
         return ref.newton_schulz(g, coeffs)
     return _newton_schulz_kernels(g, coeffs)
 
 
-class _BmmNT(torch.autograd.Function):
-    """c = alpha * a @ b^T (+ beta * d); batched, bf16 in, fp32 accumulate, bf16 out (tcgen05 kernel)."""
+class _Bmm(torch.autograd.Function):
+    """Batched tcgen05 GEMM without materialised transposes.  mode 0: a @ b^T (a [B,M,K], b [B,N,K]);
+    mode 1: a @ b (b [B,K,N]); mode 2: a^T @ b (a [B,K,M], b [B,K,N]).  out = alpha * product + beta * d."""
 
     @staticmethod
-    def forward(ctx, a, b, alpha, d, beta):
+    def forward(ctx, a, b, mode, alpha, d, beta):
+        a, b = a.contiguous(), b.contiguous()
         ctx.save_for_backward(a, b)
-        ctx.alpha, ctx.beta, ctx.has_d = alpha, beta, d is not None
-        return cuda_ext(a).bmm_nt(a.contiguous(), b.contiguous(), float(alpha), d, float(beta))
+        ctx.mode, ctx.alpha, ctx.beta, ctx.has_d = mode, alpha, beta, d is not None
+        return cuda_ext(a).bmm_general(a, b, int(mode), float(alpha), d, float(beta))
 
     @staticmethod
     def backward(ctx, dc):
         a, b = ctx.saved_tensors
         dc = dc.contiguous()
-        da = _BmmNT.apply(dc, b.transpose(1, 2).contiguous(), ctx.alpha, None, 0.0) if ctx.needs_input_grad[0] else None
-        db = _BmmNT.apply(dc.transpose(1, 2).contiguous(), a.transpose(1, 2).contiguous(), ctx.alpha, None, 0.0) \
-            if ctx.needs_input_grad[1] else None
+        al = ctx.alpha
+        da = db = None
+        if ctx.mode == 0:
+            if ctx.needs_input_grad[0]:
+                da = _Bmm.apply(dc, b, 1, al, None, 0.0)
+            if ctx.needs_input_grad[1]:
+                db = _Bmm.apply(dc, a, 2, al, None, 0.0)
+        elif ctx.mode == 1:
+            if ctx.needs_input_grad[0]:
+                da = _Bmm.apply(dc, b, 0, al, None, 0.0)
+            if ctx.needs_input_grad[1]:
+                db = _Bmm.apply(a, dc, 2, al, None, 0.0)
+        else:
+            if ctx.needs_input_grad[0]:
+                da = _Bmm.apply(b, dc, 0, al, None, 0.0)
+            if ctx.needs_input_grad[1]:
+                db = _Bmm.apply(a, dc, 1, al, None, 0.0)
         dd = dc * ctx.beta if ctx.has_d else None
-        return da, db, None, dd, None
+        return da, db, None, None, dd, None
 
 
-def bmm_nt(a, b, alpha: float = 1.0, d=None, beta: float = 0.0):
-    if _kernel("bmm_nt", a) is not None and a.dtype == torch.bfloat16:
-        return _BmmNT.apply(a, b, alpha, d, beta)
-    out = alpha * torch.bmm(a, b.transpose(1, 2))
+def _bmm_shapes_ok(a, b, mode) -> bool:
+    m = a.shape[2] if mode == 2 else a.shape[1]
+    k = a.shape[1] if mode == 2 else a.shape[2]
+    n = b.shape[1] if mode == 0 else b.shape[2]
+    return m % 128 == 0 and n % 64 == 0 and k % 64 == 0
+
+
+def bmm(a, b, mode: int = 0, alpha: float = 1.0, d=None, beta: float = 0.0):
+    """alpha * (a @ b^T | a @ b | a^T @ b) + beta * d for mode 0 | 1 | 2, batched over the leading dim."""
+    if _kernel("bmm_general", a) is not None and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 \
+            and _bmm_shapes_ok(a, b, mode):
+        return _Bmm.apply(a, b, mode, alpha, d, beta)
+    if mode == 0:
+        out = torch.bmm(a, b.transpose(1, 2))
+    elif mode == 1:
+        out = torch.bmm(a, b)
+    else:
+        out = torch.bmm(a.transpose(1, 2), b)
+    out = alpha * out
     return out if d is None else out + beta * d
 
 
+def bmm_nt(a, b, alpha: float = 1.0, d=None, beta: float = 0.0):
+    return bmm(a, b, 0, alpha, d, beta)
+
+
 def _newton_schulz_kernels(g, coeffs):
+    """Newton-Schulz in the given orientation: wide X iterates with X X^T on the left, tall X with X^T X on the
+    right (X p(X^T X) = p(X X^T) X), so no transpose is ever materialised."""
     x = g.to(torch.bfloat16)
-    tall = g.size(1) > g.size(2)
-    if tall:
-        x = x.transpose(1, 2)
     x = (x / (x.float().norm(dim=(1, 2), keepdim=True) + 1e-7).to(torch.bfloat16)).contiguous()
+    tall = g.size(1) > g.size(2)
     for a, b, c in coeffs:
-        aa = bmm_nt(x, x)                                   # X X^T (symmetric)
-        bb = bmm_nt(aa, aa, c, aa, b)                        # c*A A^T + b*A  (A symmetric => A A^T = A^2)
-        xt = x.transpose(1, 2).contiguous()
-        x = bmm_nt(bb, xt, 1.0, x, a)                        # B X + a X
-    if tall:
-        x = x.transpose(1, 2)
+        if tall:
+            aa = bmm(x, x, 2)                       # X^T X   [n, n]
+            bb = bmm(aa, aa, 0, c, aa, b)           # c A A^T + b A (A symmetric)
+            x = bmm(x, bb, 1, 1.0, x, a)            # X B + a X
+        else:
+            aa = bmm(x, x, 0)                       # X X^T   [m, m]
+            bb = bmm(aa, aa, 0, c, aa, b)
+            x = bmm(bb, x, 1, 1.0, x, a)            # B X + a X
     return x
 
 
