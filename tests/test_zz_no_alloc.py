@@ -1,0 +1,66 @@
+"""The allocation-free RMSNorm backward, called through its exported C symbol.
+
+Some users of this library run where device allocation is off limits while work is in flight (a serving process
+with a frozen memory pool, a plugin whose host owns the device heap).  For them the library exports
+``uttt_rms_norm_bwd_noalloc``: same result as the regular backward, with its scratch in a fixed array inside the
+library.  This test loads the shared object with ctypes, calls the symbol twice in a row on caller-owned buffers
+and checks both results against the regular (allocating) entry point.  This file sorts last on purpose.
+"""
+import ctypes
+import glob
+import os
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _lib():
+    import uttt_b200.ops as ops_pkg
+    from uttt_b200.ops._ext import load
+    load(required=True)                                  # torch's libraries are resident before dlopen
+    path = sorted(glob.glob(os.path.join(os.path.dirname(ops_pkg.__file__), "_C*.so")))[-1]
+    lib = ctypes.CDLL(path)
+    fn = lib.uttt_rms_norm_bwd_noalloc
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_int] * 3 + [ctypes.c_void_p]
+    return fn
+
+
+@pytest.mark.parametrize("dtype,code", [(torch.bfloat16, 0), (torch.float32, 1)])
+def test_no_alloc_rms_norm_backward_matches_regular_entry_point(dtype, code):
+    from uttt_b200.ops._ext import load
+    ext = load(required=True)
+    fn = _lib()
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    stream = torch.cuda.current_stream(dev)
+    for call, (rows, d) in enumerate([(1000, 1536), (333, 384)]):      # two calls in a row share the scratch
+        x = torch.randn(rows, d, device=dev, dtype=dtype)
+        dy = torch.randn(rows, d, device=dev, dtype=dtype)
+        w = (torch.randn(d, device=dev) * 0.1 + 1).to(dtype)
+        _, rstd = ext.rms_norm_fwd(x, w, 1e-6)
+        want_dx, want_dw = ext.rms_norm_bwd(dy, x, w, rstd)
+        dx = torch.empty_like(x)                         # caller-owned outputs
+        dw = torch.empty(d, device=dev, dtype=torch.float32)
+        torch.cuda.synchronize()
+        before = torch.cuda.memory_allocated(dev)
+        rc = fn(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dx.data_ptr(), dw.data_ptr(), rows, d,
+                code, stream.cuda_stream)
+        torch.cuda.synchronize()
+        assert rc == 0, (call, rc)
+        assert torch.cuda.memory_allocated(dev) == before
+        tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+        torch.testing.assert_close(dx.float(), want_dx.float(), atol=tol, rtol=tol)
+        torch.testing.assert_close(dw, want_dw.float(), atol=0.5 if dtype == torch.bfloat16 else 1e-3,
+                                   rtol=3e-2 if dtype == torch.bfloat16 else 1e-4)
+
+
+def test_no_alloc_entry_point_rejects_oversize_and_bad_arguments():
+    fn = _lib()
+    t = torch.zeros(8, 8192, device="cuda")
+    r = torch.zeros(8, device="cuda")
+    assert fn(t.data_ptr(), t.data_ptr(), None, r.data_ptr(), t.data_ptr(), None, 8, 8192, 1, None) == 2
+    assert fn(t.data_ptr(), t.data_ptr(), None, r.data_ptr(), t.data_ptr(), None, 8, 4100, 1, None) == 1
+    assert fn(None, t.data_ptr(), None, r.data_ptr(), t.data_ptr(), None, 8, 4096, 1, None) == 1
