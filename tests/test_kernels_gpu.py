@@ -181,7 +181,7 @@ def test_permute_unpermute():
     _close(gb, gbr, 0.2, 3e-2)
 
 
-@pytest.mark.parametrize("k,n", [(128, 256), (384, 3072), (64, 64)])
+@pytest.mark.parametrize("k,n", [(128, 256), (384, 3072), (64, 64), (1536, 384), (128, 128)])
 def test_gg_nt(k, n):
     _ext()
     torch.manual_seed(4)
@@ -199,7 +199,7 @@ def test_gg_nt(k, n):
     assert float(out[~used].abs().max() if (~used).any() else 0) == 0.0
 
 
-@pytest.mark.parametrize("k,n", [(128, 256), (384, 1536), (64, 64)])
+@pytest.mark.parametrize("k,n", [(128, 256), (384, 1536), (64, 64), (128, 384)])
 def test_gg_nn(k, n):
     _ext()
     torch.manual_seed(5)
@@ -215,7 +215,7 @@ def test_gg_nn(k, n):
     _close(out[used], want[used], 3e-2, 3e-2)
 
 
-@pytest.mark.parametrize("m,n", [(128, 128), (384, 192), (256, 64)])
+@pytest.mark.parametrize("m,n", [(128, 128), (384, 192), (256, 64), (256, 384), (128, 512)])
 def test_gg_tn(m, n):
     _ext()
     torch.manual_seed(6)
@@ -233,6 +233,14 @@ def test_gg_tn(m, n):
     torch.cuda.synchronize()
     _status_ok()
     _close(out, want, 0.3, 2e-2)
+    # fp32 output accumulated in place over two launches (the memory-side reduce-add epilogue)
+    from uttt_b200.ops._ext import load
+    acc = torch.full((plan.num_groups, m, n), 0.25, device=DEV)
+    for _ in range(2):
+        load().gg_tn_segments(a, b_, plan.offsets, plan.num_groups, 1, torch.float32, acc)
+    torch.cuda.synchronize()
+    _status_ok()
+    _close(acc, 0.25 + 2 * want, 0.3, 2e-2)
 
 
 def test_gg_autograd_matches_reference():

@@ -25,6 +25,8 @@
 #include <string>
 
 #include "common.cuh"
+#include <type_traits>
+
 #include "ptx.cuh"
 
 namespace uttt {
@@ -40,6 +42,7 @@ struct GemmParams {
   int groups;
   int M, N, K;              // per-group problem dims (NT/NN: M unused)
   void* out;
+  long long out_rows;       // rows of the output seen as one [out_rows, N] matrix (all groups / batches stacked)
   const void* addend;       // BMM: D (bf16) or nullptr
   float alpha, beta;
   int accumulate;           // TN: out += result (fp32 output only)
@@ -285,8 +288,12 @@ struct PersistentSmem {
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kBarOffset = STAGES * kStageBytes;
+  static constexpr int kOutOffset = STAGES * kStageBytes;          // epilogue staging: 4 warps x 2 x (32 rows x 128 B)
+  static constexpr int kOutBytes = 4 * 2 * 4096;
+  static constexpr int kBarOffset = kOutOffset + kOutBytes;
   static constexpr int kTotal = kBarOffset + (2 * STAGES + 4) * 8 + 16 + 1024;
+  static constexpr int kAccStride = (BN == 192) ? 256 : BN;        // TMEM columns between the two accumulators
+  static constexpr int kTmemCols = (2 * kAccStride <= 128) ? 128 : ((2 * kAccStride <= 256) ? 256 : 512);
 };
 
 struct TileCoord {
@@ -332,6 +339,7 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int id, in
 template <int MODE, int BN, int STAGES, typename OutT>
 __global__ void __launch_bounds__(192) tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tma_a,
                                                                  const __grid_constant__ CUtensorMap tma_b,
+                                                                 const __grid_constant__ CUtensorMap tma_out,
                                                                  GemmParams p, int total_tiles, int tiles_n,
                                                                  int tiles_m) {
   using L = PersistentSmem<BN, STAGES>;
@@ -364,8 +372,9 @@ __global__ void __launch_bounds__(192) tc_gemm_persistent_kernel(const __grid_co
     ptx::mbar_fence_init();
     ptx::tma_prefetch_desc(&tma_a);
     ptx::tma_prefetch_desc(&tma_b);
+    ptx::tma_prefetch_desc(&tma_out);
   }
-  constexpr uint32_t kTmemCols = 2 * BN;
+  constexpr uint32_t kTmemCols = L::kTmemCols;
   if (warp == 4) {
     ptx::tmem_alloc(ptx::smem_u32(tmem_slot), kTmemCols);
     ptx::tmem_relinquish();
@@ -451,7 +460,7 @@ __global__ void __launch_bounds__(192) tc_gemm_persistent_kernel(const __grid_co
         ok = ptx::mbar_wait(acc_empty(ab), ((acc_it >> 1) & 1) ^ 1, p.status, 22);
         if (!ok) break;
         ptx::tc_fence_after_sync();
-        const uint32_t tmem_acc = tmem_base + ab * BN;
+        const uint32_t tmem_acc = tmem_base + ab * L::kAccStride;
         for (int kb = 0; kb < c.nkb; ++kb, ++it) {
           int s = it % STAGES;
           ok = ptx::mbar_wait(full_bar(s), (it / STAGES) & 1, p.status, 23);
@@ -476,9 +485,15 @@ __global__ void __launch_bounds__(192) tc_gemm_persistent_kernel(const __grid_co
     }
   } else {
     // ================= epilogue (warps 0-3) =================
-    uint32_t acc_it = 0;
+    // Each warp owns 32 accumulator rows.  A 64-column chunk is read from TMEM (one row per lane), converted, and
+    // written to a 128B-swizzled staging slab in shared memory; one lane then issues a TMA store (or, when the
+    // output is an fp32 accumulator, a TMA reduce-add) of the 32 x 128-byte slab, so global memory sees whole
+    // 128-byte row segments instead of 16-byte pieces at a row pitch.
+    uint32_t acc_it = 0, slab_it = 0;
     bool ok = true;
     const int r = warp * 32 + lane;
+    const uint32_t slab_base = smem_base + L::kOutOffset + warp * 8192;
+    constexpr int SUBW = 128 / (int)sizeof(OutT);      // output columns per 128-byte staging row
     for (int id = blockIdx.x; id < total_tiles && ok; id += gridDim.x) {
       TileCoord c = decode_tile<MODE, BN>(p, id, tiles_n, tiles_m);
       OutT* orow = out + (c.out_row0 + r) * ldo + c.n0;
@@ -494,18 +509,15 @@ __global__ void __launch_bounds__(192) tc_gemm_persistent_kernel(const __grid_co
       ok = ptx::mbar_wait(acc_full(ab), (acc_it >> 1) & 1, p.status, 24);
       if (!ok) break;
       ptx::tc_fence_after_sync();
-      const uint32_t tmem_acc = tmem_base + ab * BN + ((uint32_t)(warp * 32) << 16);
+      const uint32_t tmem_acc = tmem_base + ab * L::kAccStride + ((uint32_t)(warp * 32) << 16);
       const __nv_bfloat16* drow = (is_batched(MODE) && p.addend != nullptr)
           ? reinterpret_cast<const __nv_bfloat16*>(p.addend) + (c.out_row0 + r) * ldo + c.n0 : nullptr;
+      const bool reduce_add = (MODE == kTN) && p.accumulate;
       // software-pipelined drain: the TMEM load of chunk c+1 is in flight while chunk c is converted and stored
-      constexpr int CH = (BN >= 64) ? 64 : 32;
+      constexpr int CH = 64;
       uint32_t raw[2][CH];
       auto issue = [&](int buf, int c0) {
-        if (CH == 64) {
-          ptx::tmem_ld_32x64(tmem_acc + c0, *reinterpret_cast<uint32_t (*)[64]>(&raw[buf][0]));
-        } else {
-          ptx::tmem_ld_32x32(tmem_acc + c0, *reinterpret_cast<uint32_t (*)[32]>(&raw[buf][0]));
-        }
+        ptx::tmem_ld_32x64(tmem_acc + c0, *reinterpret_cast<uint32_t (*)[64]>(&raw[buf][0]));
       };
       issue(0, 0);
       ptx::tmem_ld_wait();
@@ -514,34 +526,62 @@ __global__ void __launch_bounds__(192) tc_gemm_persistent_kernel(const __grid_co
         const int c0 = ci * CH;
         const int buf = ci & 1;
         if (ci + 1 < BN / CH) issue(buf ^ 1, c0 + CH);
-        // read-modify-write operands of the whole chunk are fetched up front so their latencies overlap
+        // the addend of the whole chunk is fetched up front so the load latencies overlap
         float addv[CH];
-        const bool has_add = (MODE == kTN && p.accumulate) || (is_batched(MODE) && drow != nullptr);
-        if (MODE == kTN && p.accumulate) {
-#pragma unroll
-          for (int i = 0; i < CH; i += 8) Vec8<OutT>::load(orow + c0 + i, *reinterpret_cast<float (*)[8]>(&addv[i]));
-        } else if (is_batched(MODE) && drow != nullptr) {
+        const bool has_add = is_batched(MODE) && drow != nullptr;
+        if (has_add) {
 #pragma unroll
           for (int i = 0; i < CH; i += 8)
             Vec8<__nv_bfloat16>::load(drow + c0 + i, *reinterpret_cast<float (*)[8]>(&addv[i]));
         }
 #pragma unroll
-        for (int i = 0; i < CH; i += 8) {
-          float o[8];
+        for (int sub = 0; sub < CH / SUBW; ++sub) {
+          const uint32_t slab = slab_base + (slab_it & 1) * 4096;
+          // the store issued from this slab two steps ago must have finished reading it
+          if (lane == 0) ptx::tma_store_wait_read<1>();
+          __syncwarp();
 #pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] = __uint_as_float(raw[buf][i + j]);
-          if (is_batched(MODE)) {
+          for (int i = 0; i < SUBW; i += 8) {
+            float o[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) o[j] *= p.alpha;
-            if (has_add) {
+            for (int j = 0; j < 8; ++j) o[j] = __uint_as_float(raw[buf][sub * SUBW + i + j]);
+            if (is_batched(MODE)) {
 #pragma unroll
-              for (int j = 0; j < 8; ++j) o[j] += p.beta * addv[i + j];
+              for (int j = 0; j < 8; ++j) o[j] *= p.alpha;
+              if (has_add) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] += p.beta * addv[sub * SUBW + i + j];
+              }
             }
-          } else if (has_add) {
+            if (sizeof(OutT) == 2) {
+              uint32_t w[4];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) o[j] += addv[i + j];
+              for (int j = 0; j < 4; ++j) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(o[2 * j], o[2 * j + 1]);
+                w[j] = *reinterpret_cast<uint32_t*>(&h);
+              }
+              const int piece = i / 8;
+              ptx::st_shared_v4(slab + lane * 128 + ((piece ^ (lane & 7)) << 4), w[0], w[1], w[2], w[3]);
+            } else {
+#pragma unroll
+              for (int hlf = 0; hlf < 2; ++hlf) {
+                const int piece = i / 4 + hlf;
+                ptx::st_shared_v4(slab + lane * 128 + ((piece ^ (lane & 7)) << 4), __float_as_uint(o[4 * hlf]),
+                                  __float_as_uint(o[4 * hlf + 1]), __float_as_uint(o[4 * hlf + 2]),
+                                  __float_as_uint(o[4 * hlf + 3]));
+              }
+            }
           }
-          Vec8<OutT>::store(orow + c0 + i, o);
+          ptx::fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) {
+            const int x = c.n0 + c0 + sub * SUBW;
+            const int y = (int)c.out_row0 + warp * 32;
+            if (reduce_add) ptx::tma_reduce_add_2d(&tma_out, slab, x, y);
+            else ptx::tma_store_2d(&tma_out, slab, x, y);
+            ptx::tma_store_commit();
+          }
+          ++slab_it;
         }
         if (ci + 1 < BN / CH) ptx::tmem_ld_wait();
       }
@@ -550,6 +590,7 @@ __global__ void __launch_bounds__(192) tc_gemm_persistent_kernel(const __grid_co
       ptx::mbar_arrive(acc_empty(ab));
       ++acc_it;
     }
+    if (lane == 0) ptx::tma_store_wait_all();
   }
   ptx::tc_fence_before_sync();
   __syncthreads();
@@ -570,9 +611,16 @@ static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
   return fn;
 }
 
-// 2-D bf16 tensor map over a row-major [rows, cols] matrix; box = [box_rows, box_cols] with cols innermost.
+// 2-D tensor map (128B swizzle) over a row-major [rows, cols] matrix; box = [box_rows, box_cols], cols innermost.
+static CUtensorMap make_tmap_2d(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t box_cols,
+                                bool fp32);
 CUtensorMap make_tmap_2d_bf16(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t box_cols) {
+  return make_tmap_2d(base, rows, cols, box_rows, box_cols, false);
+}
+static CUtensorMap make_tmap_2d(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t box_cols,
+                                bool fp32) {
   CUtensorMap m;
+  const uint64_t esz = fp32 ? 4 : 2;
   {
     // autograd worker threads may not have the primary context current yet; the driver call needs it
     int dev = 0;
@@ -581,11 +629,12 @@ CUtensorMap make_tmap_2d_bf16(const void* base, uint64_t rows, uint64_t cols, ui
     C10_CUDA_CHECK(cudaFree(nullptr));
   }
   cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {cols * 2};
+  cuuint64_t strides[1] = {cols * esz};
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
-  TORCH_CHECK(((uintptr_t)base & 15) == 0 && (cols * 2) % 16 == 0, "TMA needs 16-byte aligned base and row pitch");
-  CUresult r = get_encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+  TORCH_CHECK(((uintptr_t)base & 15) == 0 && (cols * esz) % 16 == 0, "TMA needs 16-byte aligned base and row pitch");
+  CUresult r = get_encode_fn()(&m, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                               const_cast<void*>(base), dims, strides, box,
                                estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code ", (int)r);
@@ -614,8 +663,11 @@ template <int MODE, int BN, typename OutT>
 static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, dim3 grid) {
   auto stream = at::cuda::getCurrentCUDAStream().stream();
   if (use_persistent()) {
-    constexpr int STAGES = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
+    constexpr int STAGES = (BN >= 192) ? 4 : (BN >= 128 ? 6 : 8);
     using L = PersistentSmem<BN, STAGES>;
+    TORCH_CHECK(p.out_rows > 0 && p.out_rows % 32 == 0, "output rows must be a multiple of 32");
+    constexpr bool f32out = std::is_same<OutT, float>::value;
+    CUtensorMap tout = make_tmap_2d(p.out, (uint64_t)p.out_rows, (uint64_t)p.N, 32, f32out ? 32 : 64, f32out);
     auto kernel = tc_gemm_persistent_kernel<MODE, BN, STAGES, OutT>;
     static bool configured = false;
     if (!configured) {
@@ -632,13 +684,13 @@ static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams
     }
     int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
     int ctas = std::min(total, sms);
-    kernel<<<ctas, 192, L::kTotal, stream>>>(ta, tb, p, total, tiles_n, tiles_m);
+    kernel<<<ctas, 192, L::kTotal, stream>>>(ta, tb, tout, p, total, tiles_n, tiles_m);
     C10_CUDA_KERNEL_LAUNCH_CHECK();
     count_launch();
     return;
   }
-  if constexpr (MODE == kBNN || MODE == kBTN) {
-    TORCH_CHECK(false, "the non-persistent GEMM has no batched NN / TN mode");
+  if constexpr (MODE == kBNN || MODE == kBTN || BN == 192) {
+    TORCH_CHECK(false, "the non-persistent GEMM has no batched NN / TN mode and no 192-wide tile");
   } else {
   constexpr int STAGES = (BN >= 256) ? 3 : (BN >= 128 ? 3 : 4);
   using L = SmemLayout<BN, STAGES>;
@@ -654,7 +706,11 @@ static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams
   }
 }
 
-static int pick_bn(int n) { return (n % 256 == 0) ? 256 : ((n % 128 == 0) ? 128 : 64); }
+static int pick_bn(int n) {
+  if (n % 256 == 0) return 256;
+  if (n % 192 == 0 && use_persistent()) return 192;
+  return (n % 128 == 0) ? 128 : 64;
+}
 
 at::Tensor gg_nt(at::Tensor x, at::Tensor w, at::Tensor tile_group) {
   c10::cuda::CUDAGuard guard(x.device());
@@ -666,12 +722,13 @@ at::Tensor gg_nt(at::Tensor x, at::Tensor w, at::Tensor tile_group) {
   auto ta = make_tmap_2d_bf16(x.data_ptr(), R, K, BM, BK);
   GemmParams p{};
   p.tile_group = tile_group.data_ptr<int>();
-  p.groups = G; p.N = N; p.K = K; p.out = out.data_ptr();
+  p.groups = G; p.N = N; p.K = K; p.out = out.data_ptr(); p.out_rows = R;
   p.status = status_word(x.device()).data_ptr<int>();
   const int bn = pick_bn(N);
   auto tb = make_tmap_2d_bf16(w.data_ptr(), (uint64_t)G * N, K, bn, BK);
   dim3 grid(N / bn, R / BM);
   if (bn == 256) launch_gemm<kNT, 256, __nv_bfloat16>(ta, tb, p, grid);
+  else if (bn == 192) launch_gemm<kNT, 192, __nv_bfloat16>(ta, tb, p, grid);
   else if (bn == 128) launch_gemm<kNT, 128, __nv_bfloat16>(ta, tb, p, grid);
   else launch_gemm<kNT, 64, __nv_bfloat16>(ta, tb, p, grid);
   return out;
@@ -688,11 +745,12 @@ at::Tensor gg_nn(at::Tensor x, at::Tensor w, at::Tensor tile_group) {
   auto tb = make_tmap_2d_bf16(w.data_ptr(), (uint64_t)G * K, N, BK, 64);   // box: 64 k rows x 64 n
   GemmParams p{};
   p.tile_group = tile_group.data_ptr<int>();
-  p.groups = G; p.N = N; p.K = K; p.out = out.data_ptr();
+  p.groups = G; p.N = N; p.K = K; p.out = out.data_ptr(); p.out_rows = R;
   p.status = status_word(x.device()).data_ptr<int>();
   const int bn = pick_bn(N);
   dim3 grid(N / bn, R / BM);
   if (bn == 256) launch_gemm<kNN, 256, __nv_bfloat16>(ta, tb, p, grid);
+  else if (bn == 192) launch_gemm<kNN, 192, __nv_bfloat16>(ta, tb, p, grid);
   else if (bn == 128) launch_gemm<kNN, 128, __nv_bfloat16>(ta, tb, p, grid);
   else launch_gemm<kNN, 64, __nv_bfloat16>(ta, tb, p, grid);
   return out;
@@ -722,7 +780,7 @@ at::Tensor gg_tn_segments(at::Tensor a, at::Tensor b, at::Tensor offsets, int64_
   p.seg_offsets = offsets.data_ptr<int>();
   p.segments = (int)segments;
   p.rows_per_segment = (int)(rows / segments);
-  p.groups = G; p.M = M; p.N = N; p.out = out.data_ptr();
+  p.groups = G; p.M = M; p.N = N; p.out = out.data_ptr(); p.out_rows = (long long)G * M;
   p.accumulate = acc ? 1 : 0;
   p.status = status_word(a.device()).data_ptr<int>();
   bool f32 = out.scalar_type() == at::kFloat;
@@ -731,6 +789,9 @@ at::Tensor gg_tn_segments(at::Tensor a, at::Tensor b, at::Tensor offsets, int64_
   if (bn == 256) {
     if (f32) launch_gemm<kTN, 256, float>(ta, tb, p, grid);
     else launch_gemm<kTN, 256, __nv_bfloat16>(ta, tb, p, grid);
+  } else if (bn == 192) {
+    if (f32) launch_gemm<kTN, 192, float>(ta, tb, p, grid);
+    else launch_gemm<kTN, 192, __nv_bfloat16>(ta, tb, p, grid);
   } else if (bn == 128) {
     if (f32) launch_gemm<kTN, 128, float>(ta, tb, p, grid);
     else launch_gemm<kTN, 128, __nv_bfloat16>(ta, tb, p, grid);
@@ -758,7 +819,7 @@ at::Tensor bmm_general(at::Tensor a, at::Tensor b, int64_t mode, double alpha, c
   TORCH_CHECK(b.size(0) == B && Kb == K && M % BM == 0 && N % 64 == 0 && K % BK == 0);
   auto out = at::empty({B, M, N}, a.options());
   GemmParams p{};
-  p.groups = B; p.M = M; p.N = N; p.K = K; p.out = out.data_ptr();
+  p.groups = B; p.M = M; p.N = N; p.K = K; p.out = out.data_ptr(); p.out_rows = (long long)B * M;
   p.alpha = (float)alpha; p.beta = (float)beta;
   at::Tensor dc;
   if (d.has_value() && d->defined()) {
@@ -775,6 +836,7 @@ at::Tensor bmm_general(at::Tensor a, at::Tensor b, int64_t mode, double alpha, c
                              : make_tmap_2d_bf16(b.data_ptr(), (uint64_t)B * K, N, BK, 64);
 #define UTTT_BMM_DISPATCH(MODE_)                                                     \
   if (bn == 256) launch_gemm<MODE_, 256, __nv_bfloat16>(ta, tb, p, grid);            \
+  else if (bn == 192) launch_gemm<MODE_, 192, __nv_bfloat16>(ta, tb, p, grid);       \
   else if (bn == 128) launch_gemm<MODE_, 128, __nv_bfloat16>(ta, tb, p, grid);       \
   else launch_gemm<MODE_, 64, __nv_bfloat16>(ta, tb, p, grid);
   if (mode == 0) { UTTT_BMM_DISPATCH(kBMM) }
@@ -806,7 +868,9 @@ at::Tensor bmm_nt_legacy(at::Tensor a, at::Tensor b, double alpha, c10::optional
     p.addend = dc.data_ptr();
   }
   p.status = status_word(a.device()).data_ptr<int>();
-  const int bn = pick_bn(N);
+  p.out_rows = (long long)B * M;
+  int bn = pick_bn(N);
+  if (bn == 192) bn = 64;
   auto tb = make_tmap_2d_bf16(b.data_ptr(), (uint64_t)B * N, K, bn, BK);
   dim3 grid(N / bn, M / BM, B);
   if (bn == 256) launch_gemm<kBMM, 256, __nv_bfloat16>(ta, tb, p, grid);
