@@ -42,6 +42,8 @@ void adamw_scatter(at::Tensor p, at::Tensor g, at::Tensor m, at::Tensor v, std::
                    int64_t rank, int64_t shard_off, bool compute_bf16, double lr, double b1, double b2, double eps,
                    double wd, int64_t step, at::Tensor gscale, at::Tensor apply, int64_t decay_hi);
 std::vector<at::Tensor> swa_fwd(at::Tensor q, at::Tensor k, at::Tensor v, int64_t window, bool causal, double scale);
+std::vector<at::Tensor> swa_bwd(at::Tensor dout, at::Tensor q, at::Tensor k, at::Tensor v, at::Tensor o, at::Tensor lse,
+                                int64_t window, bool causal, double scale);
 }  // namespace uttt
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -72,6 +74,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_status", &gemm_status);
   m.def("bmm_general", &bmm_general);
   m.def("swa_fwd", &swa_fwd);
+  m.def("swa_bwd", &swa_bwd);
   m.def("rs_sumsq", &rs_sumsq);
   m.def("adamw_scatter", &adamw_scatter);
 }

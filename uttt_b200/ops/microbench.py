@@ -2,7 +2,7 @@
 
     python -m uttt_b200.ops.microbench [--kernel NAME] [--small] [--iters N]
 
-Kernels: gg_nt, gg_nn, gg_tn, bmm_nt, swa_fwd, rms_norm, fw_write_pw, adamw, ce.  ``--small`` runs one small case
+Kernels: gg_nt, gg_nn, gg_tn, bmm_nt, swa_fwd, swa_bwd, rms_norm, fw_write_pw, adamw, ce.  ``--small`` runs one small case
 of the chosen kernel (inputs above L2 size, a few hundred MB on the device) three times, which is what the
 profile summaries under ``profiles/`` were captured from.  Prints one JSON line per case with the achieved
 TFLOP/s or GB/s and the fraction of the measured peaks in ``MEASURED_PEAKS.json`` when present.
@@ -110,6 +110,18 @@ def run(kernel: str, small: bool, iters: int):
         ms = _time(lambda: F.swa_attention(q, k, v, win, True), iters, flush)
         band = win + 64          # average visible keys per query, rounded up to the tile edge
         rec("swa_fwd[hd96 w2048]", ms, flops=4.0 * b_ * h * lq * band * hd, lq=lq, lk=lk)
+    if kernel in ("swa_bwd", "all"):
+        ext = load()
+        b_, lq, lk, h, hd, win = bsz, 2048, 4096, 16, 96, 2048
+        q = torch.randn(b_, lq, h, hd, **bf)
+        k = torch.randn(b_, lk, h, hd, **bf)
+        v = torch.randn(b_, lk, h, hd, **bf)
+        o, lse = ext.swa_fwd(q, k, v, win, True, hd ** -0.5)
+        do = torch.randn_like(o)
+        ms = _time(lambda: ext.swa_bwd(do, q, k, v, o, lse, win, True, hd ** -0.5), iters, flush)
+        band = win + 64
+        # five products in the textbook backward (the two-kernel split recomputes S and dP once more)
+        rec("swa_bwd[hd96 w2048]", ms, flops=10.0 * b_ * h * lq * band * hd, lq=lq, lk=lk)
     if kernel in ("rms_norm", "all"):
         x = torch.randn(bsz * 2048 * 8, 1536, **bf)
         w = torch.ones(1536, **bf)
