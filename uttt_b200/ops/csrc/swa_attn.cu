@@ -5,11 +5,14 @@
 //   non-causal (window ignored): every key visible (full attention inside one view).
 //
 // One CTA = one (batch, head, 128-query tile).  It walks the 64-key tiles of its band:
-//   warp 4 / lane 0 : TMA producer   K_j, V_j -> 2-stage 128B-swizzled ring
-//   warp 5 / lane 0 : MMA issuer     S_j = Q K_j^T (double-buffered in TMEM), O_j = P_j V_j
-//   warps 0-3       : softmax        one thread per query row (its TMEM lane): online max / sum in
-//                                    registers, P_j written back to shared memory (reusing K_j's slot)
-//                                    as the bf16 A operand of the second MMA, O accumulated in registers
+//   warp 8 / lane 0 : TMA producer   K_j, V_j -> 2-stage 128B-swizzled ring
+//   warp 9 / lane 0 : MMA issuer     S_j = Q K_j^T (double-buffered in TMEM), O_j = P_j V_j
+//   warps 0-7       : softmax        two threads per query row (its TMEM lane), one per 32-column half of the
+//                                    tile: one TMEM read of S_j, row maximum exchanged through shared memory,
+//                                    P_j written back to shared memory (reusing K_j's slot) as the bf16 A
+//                                    operand of the second MMA.  O is accumulated in TMEM by the tensor core
+//                                    relative to a per-row reference maximum that moves only when the running
+//                                    maximum exceeds it by 8 (log2 units); only then O is rescaled in TMEM.
 // Two CTAs are resident per SM so one CTA's softmax overlaps the other's MMAs.
 #include <ATen/ATen.h>
 #include <ATen/cuda/CUDAContext.h>
@@ -39,10 +42,19 @@ constexpr int kQ = 128;   // queries per CTA
 constexpr int kKV = 64;   // keys per tile
 constexpr int kStageBytes = 32 * 1024;   // K slot (16 KB, later reused for P) + V slot (16 KB)
 constexpr int kQBytes = 32 * 1024;
-constexpr int kAttnSmem = kQBytes + 2 * kStageBytes + 128 + 1024;
+constexpr int kXchgBytes = 2 * 2 * kQ * 4;   // row maxima exchanged between the two column halves, double-buffered
+constexpr int kAttnSmem = kQBytes + 2 * kStageBytes + kXchgBytes + 160 + 1024;
+constexpr float kRescaleThreshold = 8.f;     // log2 units: P stays below 2^8 between rescales
+
+// Rendezvous of the two warps that share a TMEM lane quarter (one per column half): an mbarrier with 64 arrivals
+// per phase, waited on with the bounded wait so that a warp whose partner gave up cannot hang.
+__device__ __forceinline__ bool pair_sync(uint32_t bar, uint32_t use, int* status) {
+  ptx::mbar_arrive(bar);
+  return ptx::mbar_wait(bar, use & 1, status, 19);
+}
 
 template <int HD>
-__global__ void __launch_bounds__(192, (HD <= 96 ? 2 : 1)) swa_fwd_kernel(const __grid_constant__ CUtensorMap tq,
+__global__ void __launch_bounds__(320, 2) swa_fwd_kernel(const __grid_constant__ CUtensorMap tq,
                                                          const __grid_constant__ CUtensorMap tk,
                                                          const __grid_constant__ CUtensorMap tv, SwaParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -51,16 +63,18 @@ __global__ void __launch_bounds__(192, (HD <= 96 ? 2 : 1)) swa_fwd_kernel(const 
   const uint32_t q_smem = base;
   auto k_smem = [&](int s) { return base + kQBytes + s * kStageBytes; };
   auto v_smem = [&](int s) { return base + kQBytes + s * kStageBytes + 16 * 1024; };
-  const uint32_t bars = base + kQBytes + 2 * kStageBytes;
+  float* xchg = reinterpret_cast<float*>(gen + kQBytes + 2 * kStageBytes);      // [2 buffers][2 halves][128 rows]
+  const uint32_t bars = base + kQBytes + 2 * kStageBytes + kXchgBytes;
   // barrier slots
   const uint32_t q_full = bars;
   auto k_full = [&](int s) { return bars + 8 + 8 * s; };
   auto v_full = [&](int s) { return bars + 24 + 8 * s; };
   auto empty = [&](int s) { return bars + 40 + 8 * s; };
   auto s_done = [&](int s) { return bars + 56 + 8 * s; };
-  const uint32_t p_ready = bars + 72;
-  const uint32_t o_done = bars + 80;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + kQBytes + 2 * kStageBytes + 96);
+  auto p_ready = [&](int s) { return bars + 72 + 8 * s; };
+  const uint32_t o_done = bars + 88;
+  auto pair_bar = [&](int quarter) { return bars + 96 + 8 * quarter; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + kQBytes + 2 * kStageBytes + kXchgBytes + 128);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qt = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
@@ -88,15 +102,16 @@ __global__ void __launch_bounds__(192, (HD <= 96 ? 2 : 1)) swa_fwd_kernel(const 
       ptx::mbar_init(v_full(s), 1);
       ptx::mbar_init(empty(s), 1);
       ptx::mbar_init(s_done(s), 1);
+      ptx::mbar_init(p_ready(s), 256);
     }
-    ptx::mbar_init(p_ready, 128);
     ptx::mbar_init(o_done, 1);
+    for (int qd = 0; qd < 4; ++qd) ptx::mbar_init(pair_bar(qd), 64);
     ptx::mbar_fence_init();
     ptx::tma_prefetch_desc(&tq);
     ptx::tma_prefetch_desc(&tk);
     ptx::tma_prefetch_desc(&tv);
   }
-  if (warp == 4) {
+  if (warp == 8) {
     ptx::tmem_alloc(ptx::smem_u32(tmem_slot), 256);
     ptx::tmem_relinquish();
   }
@@ -105,14 +120,14 @@ __global__ void __launch_bounds__(192, (HD <= 96 ? 2 : 1)) swa_fwd_kernel(const 
   ptx::tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
   const uint32_t tmem_s0 = tmem;          // S buffers: columns [0,64) and [64,128)
-  const uint32_t tmem_o = tmem + 128;     // O_j: columns [128, 128 + HD)
+  const uint32_t tmem_o = tmem + 128;     // O: columns [128, 128 + HD), accumulated by the tensor core
 
   constexpr int KB = (HD + 63) / 64;      // 64-wide blocks along the head dimension
   constexpr uint32_t idesc_s = ptx::make_instr_desc(kQ, kKV, 0, 0);
   constexpr uint32_t idesc_o = ptx::make_instr_desc(kQ, HD, 0, 1);
   bool ok = true;
 
-  if (warp == 4 && lane == 0) {
+  if (warp == 8 && lane == 0) {
     // ================= producer =================
     ptx::mbar_expect_tx(q_full, KB * kQ * 128);
     for (int kb = 0; kb < KB; ++kb)
@@ -129,7 +144,7 @@ __global__ void __launch_bounds__(192, (HD <= 96 ? 2 : 1)) swa_fwd_kernel(const 
       for (int kb = 0; kb < KB; ++kb)
         ptx::tma_load_3d(v_smem(s) + kb * (kKV * 128), &tv, v_full(s), head * HD + kb * 64, key0, batch);
     }
-  } else if (warp == 5 && lane == 0) {
+  } else if (warp == 9 && lane == 0) {
     // ================= MMA issuer =================
     auto issue_s = [&](int j) -> bool {
       int s = j & 1;
@@ -152,7 +167,7 @@ __global__ void __launch_bounds__(192, (HD <= 96 ? 2 : 1)) swa_fwd_kernel(const 
       // drained before p_ready(j-1), and its K tile lands only after P_{j-1} V_{j-1} released the stage.
       if (j + 1 < nt) ok = issue_s(j + 1);
       if (!ok) break;
-      ok = ptx::mbar_wait(p_ready, j & 1, p.status, 14);
+      ok = ptx::mbar_wait(p_ready(s), (j >> 1) & 1, p.status, 14);
       if (!ok) break;
       ok = ptx::mbar_wait(v_full(s), (j >> 1) & 1, p.status, 15);
       if (!ok) break;
@@ -161,119 +176,142 @@ __global__ void __launch_bounds__(192, (HD <= 96 ? 2 : 1)) swa_fwd_kernel(const 
       for (int k = 0; k < kKV / 16; ++k) {
         uint64_t da = ptx::make_smem_desc(k_smem(s) + k * 32, 16, 1024);                 // P_j (K-major)
         uint64_t db = ptx::make_smem_desc(v_smem(s) + k * 2048, kKV * 128, 1024);        // V_j (N-major slabs)
-        ptx::mma_bf16_ss(tmem_o, da, db, idesc_o, k > 0 ? 1u : 0u);
+        ptx::mma_bf16_ss(tmem_o, da, db, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
       }
       ptx::mma_commit(o_done);
       ptx::mma_commit(empty(s));
     }
   }
 
-  // ================= softmax / accumulate (warps 0-3: one thread per query row) =================
-  if (warp < 4) {
-    const int r = warp * 32 + lane;               // query row inside the tile == TMEM lane
+  // ================= softmax (warps 0-7): thread = (query row, half of the 64 key columns) =================
+  // O stays in TMEM and is accumulated by the tensor core relative to a reference maximum m_ref per row; the
+  // reference moves (and O, l are rescaled) only when the running maximum exceeds it by kRescaleThreshold.
+  if (warp < 8) {
+    const int half = warp >> 2;
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;            // query row inside the tile == TMEM lane
     const int qpos = shift + q0 + r;              // absolute position
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-    float o_acc[HD];
-#pragma unroll
-    for (int i = 0; i < HD; ++i) o_acc[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    float m_ref = -INFINITY, l_part = 0.f;
 
     for (int j = 0; j < nt; ++j) {
       int s = j & 1;
       if (!ptx::mbar_wait(s_done(s), (j >> 1) & 1, p.status, 16)) { ok = false; break; }
       ptx::tc_fence_after_sync();
-      const int key0 = (t0 + j) * kKV;
-      bool need_mask = (key0 + kKV > p.lk);
+      const int key0 = (t0 + j) * kKV + half * 32;
+      bool need_mask = (key0 + 32 > p.lk);
       if (p.causal) {
-        need_mask = need_mask || (key0 + kKV - 1 > shift + q0);
+        need_mask = need_mask || (key0 + 31 > shift + q0);
         if (p.window > 0) need_mask = need_mask || (key0 <= shift + q0 + kQ - 1 - p.window);
       }
-      auto visible = [&](int kp) {
-        bool vis = kp < p.lk;
-        if (p.causal) {
-          vis = vis && (kp <= qpos);
-          if (p.window > 0) vis = vis && (kp > qpos - p.window);
-        }
-        return vis;
-      };
-      // pass 1: row maximum over the 64 scores of this tile
-      float mx = m_run;
+      uint32_t raw[32];
+      ptx::tmem_ld_32x32(tmem_s0 + s * 64 + lane_base + half * 32, raw);
+      ptx::tmem_ld_wait();
+      float x[32];
+      float mx = -INFINITY;
 #pragma unroll
-      for (int c0 = 0; c0 < kKV; c0 += 32) {
-        uint32_t raw[32];
-        ptx::tmem_ld_32x32(tmem_s0 + s * 64 + lane_base + c0, raw);
-        ptx::tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = __uint_as_float(raw[i]) * p.scale_log2;
-          if (need_mask && !visible(key0 + c0 + i)) x = -INFINITY;
-          mx = fmaxf(mx, x);
+      for (int i = 0; i < 32; ++i) {
+        x[i] = __uint_as_float(raw[i]) * p.scale_log2;
+        if (need_mask) {
+          const int kp = key0 + i;
+          bool vis = kp < p.lk;
+          if (p.causal) {
+            vis = vis && (kp <= qpos);
+            if (p.window > 0) vis = vis && (kp > qpos - p.window);
+          }
+          if (!vis) x[i] = -INFINITY;
         }
+        mx = fmaxf(mx, x[i]);
       }
-      const float m_use = (mx == -INFINITY) ? 0.f : mx;
-      const float alpha = exp2f(m_run - m_use);     // m_run = -inf -> 0
+      // row maximum over both halves
+      float* xb = xchg + (j & 1) * 2 * kQ;
+      xb[half * kQ + r] = mx;
+      if (!pair_sync(pair_bar(quarter), (uint32_t)j, p.status)) { ok = false; break; }
+      mx = fmaxf(mx, xb[(half ^ 1) * kQ + r]);
+      const bool move_ref = mx > m_ref + kRescaleThreshold;     // also true for the first visible key (m_ref = -inf)
+      const float new_ref = move_ref ? mx : m_ref;
+      const float factor = move_ref ? exp2f(m_ref - new_ref) : 1.f;    // m_ref = -inf -> 0
+      const float m_use = (new_ref == -INFINITY) ? 0.f : new_ref;
       float rs = 0.f;
-      // pass 2: P_j = exp2(s - m) -> shared memory (K-major, 128-byte rows, 16-byte chunks XOR-swizzled by
-      // row & 7), written into the slot that held K_j
       uint8_t* prow = gen + (k_smem(s) - base) + r * 128;
 #pragma unroll
-      for (int c0 = 0; c0 < kKV; c0 += 32) {
-        uint32_t raw[32];
-        ptx::tmem_ld_32x32(tmem_s0 + s * 64 + lane_base + c0, raw);
-        ptx::tmem_ld_wait();
+      for (int ch = 0; ch < 4; ++ch) {
+        float e[8];
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          float e[8];
+        for (int i = 0; i < 8; ++i) {
+          e[i] = exp2f(x[ch * 8 + i] - m_use);
+          rs += e[i];
+        }
+        uint4 u;
+        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&u);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            float x = __uint_as_float(raw[ch * 8 + i]) * p.scale_log2;
-            if (need_mask && !visible(key0 + c0 + ch * 8 + i)) x = -INFINITY;
-            e[i] = exp2f(x - m_use);
-            rs += e[i];
+        for (int i = 0; i < 4; ++i) h2[i] = __floats2bfloat162_rn(e[2 * i], e[2 * i + 1]);
+        const int chunk = half * 4 + ch;
+        *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = u;
+      }
+      l_part = l_part * factor + rs;
+      m_ref = new_ref;
+      // O may be touched only after P_{j-1} V_{j-1} has finished; P_j V_j starts after p_ready(j)
+      if (j > 0) {
+        if (!ptx::mbar_wait(o_done, (j - 1) & 1, p.status, 17)) { ok = false; break; }
+        if (__any_sync(0xffffffffu, move_ref)) {
+          ptx::tc_fence_after_sync();
+#pragma unroll
+          for (int c = 0; c < HD / 32; ++c) {
+            if ((c & 1) != half) continue;
+            uint32_t o[32];
+            ptx::tmem_ld_32x32(tmem_o + lane_base + c * 32, o);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+            ptx::tmem_st_32x32(tmem_o + lane_base + c * 32, o);
           }
-          uint4 u;
-          __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&u);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) h2[i] = __floats2bfloat162_rn(e[2 * i], e[2 * i + 1]);
-          const int chunk = (c0 >> 3) + ch;
-          *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = u;
+          ptx::tmem_st_wait();
         }
       }
-      l_run = l_run * alpha + rs;
-      m_run = mx;
       ptx::fence_proxy_async();          // make the generic-proxy writes of P visible to the tensor core
       ptx::tc_fence_before_sync();
-      ptx::mbar_arrive(p_ready);
-      if (!ptx::mbar_wait(o_done, j & 1, p.status, 17)) { ok = false; break; }
-      ptx::tc_fence_after_sync();
-#pragma unroll
-      for (int c0 = 0; c0 < HD; c0 += 32) {
-        uint32_t raw[32];
-        ptx::tmem_ld_32x32(tmem_o + lane_base + c0, raw);
-        ptx::tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o_acc[c0 + i] = o_acc[c0 + i] * alpha + __uint_as_float(raw[i]);
-      }
-      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(p_ready(s));
     }
 
-    if (ok && q0 + r < p.lq) {
+    if (ok) ok = ptx::mbar_wait(o_done, (nt - 1) & 1, p.status, 18);
+    if (ok) {
+      ptx::tc_fence_after_sync();
+      // total row sum: exchange the two halves' partial sums (buffer of parity nt is free: last used by tile nt-2)
+      float* xb = xchg + (nt & 1) * 2 * kQ;
+      xb[half * kQ + r] = l_part;
+      ok = pair_sync(pair_bar(quarter), (uint32_t)nt, p.status);
+    }
+    if (ok) {
+      const float* xb = xchg + (nt & 1) * 2 * kQ;
+      const float l_run = l_part + xb[(half ^ 1) * kQ + r];
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      __nv_bfloat16* orow = p.out + (((size_t)batch * p.lq + q0 + r) * p.heads + head) * HD;
+      const bool live = q0 + r < p.lq;
+      __nv_bfloat16* orow = p.out + (((size_t)batch * p.lq + (live ? q0 + r : 0)) * p.heads + head) * HD;
 #pragma unroll
-      for (int c = 0; c < HD; c += 8) {
-        float o[8];
+      for (int c = 0; c < HD / 32; ++c) {
+        if ((c & 1) != half) continue;
+        uint32_t o[32];
+        ptx::tmem_ld_32x32(tmem_o + lane_base + c * 32, o);
+        ptx::tmem_ld_wait();
+        if (live) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = o_acc[c + i] * inv;
-        Vec8<__nv_bfloat16>::store(orow + c, o);
+          for (int i = 0; i < 32; i += 8) {
+            float f[8];
+#pragma unroll
+            for (int t = 0; t < 8; ++t) f[t] = __uint_as_float(o[i + t]) * inv;
+            Vec8<__nv_bfloat16>::store(orow + c * 32 + i, f);
+          }
+        }
       }
-      p.lse[((size_t)batch * p.heads + head) * p.lq + q0 + r] =
-          l_run > 0.f ? (m_run * 0.6931471805599453f + __logf(l_run)) : -INFINITY;
+      if (live && half == 0)
+        p.lse[((size_t)batch * p.heads + head) * p.lq + q0 + r] =
+            l_run > 0.f ? (m_ref * 0.6931471805599453f + __logf(l_run)) : -INFINITY;
     }
   }
   ptx::tc_fence_before_sync();
   __syncthreads();
-  if (warp == 4) ptx::tmem_dealloc(tmem, 256);
+  if (warp == 8) ptx::tmem_dealloc(tmem, 256);
 }
 
 // ------------------------------------------------------------------------------------ host
@@ -337,7 +375,7 @@ std::vector<at::Tensor> swa_fwd(at::Tensor q, at::Tensor k, at::Tensor v, int64_
   auto stream = at::cuda::getCurrentCUDAStream().stream();
   auto launch = [&](auto kernel) {
     C10_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
-    kernel<<<grid, 192, kAttnSmem, stream>>>(tq, tk, tv, p);
+    kernel<<<grid, 320, kAttnSmem, stream>>>(tq, tk, tv, p);
     C10_CUDA_KERNEL_LAUNCH_CHECK();
   };
   if (hd == 64) launch(swa_fwd_kernel<64>);
