@@ -144,6 +144,76 @@ def test_group_plan_kernel_matches_reference(bsz, n, e, k):
     assert torch.equal(plan.dest.cpu(), dest.cpu())          # same stable (token-major) order inside groups
 
 
+@pytest.mark.parametrize("d,e,k,renorm,bias_in_logits,dtype", [(384, 32, 2, False, False, torch.bfloat16),
+                                                               (192, 64, 4, True, False, torch.bfloat16),
+                                                               (128, 8, 1, False, True, torch.float32),
+                                                               (512, 16, 2, True, False, torch.bfloat16)])
+def test_fused_router_matches_reference(d, e, k, renorm, bias_in_logits, dtype):
+    _ext()
+    torch.manual_seed(21)
+    bsz, n = 3, 1003
+    rows = torch.randn(bsz, n, d, device=DEV).to(dtype).requires_grad_(True)
+    router = (torch.randn(e, d, device=DEV) * 0.2).requires_grad_(True)
+    bias = torch.randn(e, device=DEV) * 0.05
+    idx, w, psum = ops.route_softmax_topk(rows, router, bias, k, 0.7, bias_in_logits, renorm)
+    rr = rows.detach().float().requires_grad_(True)
+    rt = router.detach().clone().requires_grad_(True)
+    logits = rr @ rt.t()
+    if bias_in_logits:
+        logits = logits + bias
+    probs = torch.softmax(logits, -1)
+    scores = logits.detach() if bias_in_logits else logits.detach() + bias
+    # selection must agree wherever the k-th and (k+1)-th scores are not nearly tied
+    top = torch.topk(scores, k + 1 if k < e else k, dim=-1)
+    clear = (top.values[..., k - 1] - top.values[..., -1]).abs() > 1e-3 if k < e else torch.ones_like(idx[..., 0]).bool()
+    want_idx = top.indices[..., :k]
+    assert bool((idx.long().sort(-1).values == want_idx.sort(-1).values)[clear].all())
+    picked = probs.gather(-1, idx.long())
+    if renorm:
+        picked = picked / picked.sum(-1, keepdim=True).clamp_min(1e-9)
+    wr = (picked * 0.7).view(bsz * n, k)
+    _close(w, wr, 1e-4, 1e-3, "weights")
+    _close(psum, probs.sum(1), 1e-2, 1e-3, "probs_sum")
+    gw = torch.randn_like(w)
+    gp = torch.randn_like(psum) * 0.1
+    g1, g2 = torch.autograd.grad([w, psum], [rows, router], [gw, gp])
+    g1r, g2r = torch.autograd.grad([wr, probs.sum(1)], [rr, rt], [gw, gp])
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
+    _close(g1, g1r, tol, tol, "drows")
+    _close(g2, g2r, 2e-3, 2e-3, "drouter")
+
+
+@pytest.mark.parametrize("renorm", ["restore", "unit", "none"])
+@pytest.mark.parametrize("d,ddtype", [(384, torch.bfloat16), (1536, torch.float32), (200, torch.bfloat16)])
+def test_pool_step_matches_reference(renorm, d, ddtype):
+    _ext()
+    torch.manual_seed(22)
+    m = torch.randn(3, 5, 70, d, device=DEV, requires_grad=True)
+    dd = torch.randn(3, 5, 70, d, device=DEV).to(ddtype).requires_grad_(True)
+    n, w = ops.pool_step(m, dd, 0.3, renorm)
+    assert w.dtype == torch.bfloat16 and n.dtype == torch.float32
+    mr = m.detach().clone().requires_grad_(True)
+    dr = dd.detach().float().requires_grad_(True)
+    u = mr + dr * 0.3
+    if renorm == "restore":
+        nr = u / (u.norm(dim=-1, keepdim=True) + 1e-5) * mr.norm(dim=-1, keepdim=True)
+    elif renorm == "unit":
+        nr = F.normalize(u, dim=-1)
+    else:
+        nr = u
+    _close(n, nr, 1e-5, 1e-5, "n")
+    _close(w, nr, 2e-2, 1e-2, "w")
+    gn = torch.randn_like(n)
+    gw = torch.randn_like(n).bfloat16()
+    g1, g2 = torch.autograd.grad([n, w], [m, dd], [gn, gw])
+    g1r, g2r = torch.autograd.grad(nr, [mr, dr], gn + gw.float())
+    _close(g1, g1r, 1e-4, 1e-4, "dm")
+    _close(g2, g2r, 3e-2 if ddtype == torch.bfloat16 else 1e-4, 1e-2 if ddtype == torch.bfloat16 else 1e-4, "dd")
+    (g3,) = torch.autograd.grad(w, m, gw)            # only the compute copy has a gradient
+    (g3r,) = torch.autograd.grad(nr, mr, gw.float())
+    _close(g3, g3r, 1e-4, 1e-4, "dm from w")
+
+
 def test_permute_unpermute():
     _ext()
     plan = _plan()

@@ -74,6 +74,11 @@ def route_rows(rows: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Te
         plan = ops.build_group_plan(idx, 1)
         ones = torch.ones(bsz * n, 1, device=rows.device, dtype=torch.float32)
         return Routing(plan, ones, ones.view(bsz, n).sum(1, keepdim=True), plan.sizes.view(bsz, 1).float())
+    if cfg.memory_router_type == "softmax":
+        idx, weights, psum = ops.route_softmax_topk(rows, router, bias, k, cfg.memory_router_alpha, bias_in_logits,
+                                                    cfg.memory_router_combine_mode == "topk_renorm")
+        plan = ops.build_group_plan(idx, e)
+        return Routing(plan, weights, psum, plan.sizes.view(bsz, e).float())
     logits = torch.matmul(rows.float(), router.float().t())
     if bias is not None and bias_in_logits:
         logits = logits + bias.view(1, 1, e)
@@ -149,23 +154,17 @@ def apply_pool_update(a02: torch.Tensor, a1: torch.Tensor, state: PoolState, m_c
     bsz, e, inter2, d = m02.shape
     z02, z1 = state.z02, state.z1
     if z02 is not None and m_coeff is not None:
-        a02 = a02 + z02 * m_coeff
-        a1 = a1 + z1 * m_coeff
+        a02 = torch.addcmul(a02, z02, m_coeff.to(a02.dtype))
+        a1 = torch.addcmul(a1, z1, m_coeff.to(a1.dtype))
         z02, z1 = a02, a1
     if use_muon:
         d02 = ops.newton_schulz(a02.reshape(bsz * e * 2, inter2 // 2, d), ns_coeffs).reshape(bsz, e, inter2, d)
         d1 = ops.newton_schulz(a1.reshape(bsz * e, d, inter2 // 2), ns_coeffs).reshape(bsz, e, d, inter2 // 2)
     else:
         d02, d1 = a02, a1
-    n02 = m02 + d02.float() * lr_scale
-    n1 = m1 + d1.float() * lr_scale
-    if renorm == "restore":
-        n02 = n02 / (n02.norm(dim=3, keepdim=True) + 1e-5) * m02.norm(dim=3, keepdim=True)
-        n1 = n1 / (n1.norm(dim=3, keepdim=True) + 1e-5) * m1.norm(dim=3, keepdim=True)
-    elif renorm == "unit":
-        n02 = F.normalize(n02, dim=3)
-        n1 = F.normalize(n1, dim=3)
-    return PoolState(n02.to(compute_dtype), n1.to(compute_dtype), n02, n1, z02, z1)
+    n02, w02 = ops.pool_step(m02, d02, lr_scale, renorm, compute_dtype)
+    n1, w1 = ops.pool_step(m1, d1, lr_scale, renorm, compute_dtype)
+    return PoolState(w02, w1, n02, n1, z02, z1)
 
 
 class FastWeightMemory(nn.Module):

@@ -42,6 +42,16 @@ void adamw_scatter(at::Tensor p, at::Tensor g, at::Tensor m, at::Tensor v, std::
                    int64_t rank, int64_t shard_off, bool compute_bf16, double lr, double b1, double b2, double eps,
                    double wd, int64_t step, at::Tensor gscale, at::Tensor apply, int64_t decay_hi);
 std::vector<at::Tensor> swa_fwd(at::Tensor q, at::Tensor k, at::Tensor v, int64_t window, bool causal, double scale);
+bool pool_step_supported(int64_t D);
+std::vector<at::Tensor> pool_step_fwd(at::Tensor m, at::Tensor d, double lr, int64_t mode);
+std::vector<at::Tensor> pool_step_bwd(at::Tensor m, at::Tensor d, c10::optional<at::Tensor> gn,
+                                      c10::optional<at::Tensor> gw, double lr, int64_t mode);
+bool router_supported(int64_t D, int64_t E, int64_t topk);
+std::vector<at::Tensor> router_fwd(at::Tensor rows, at::Tensor router, c10::optional<at::Tensor> bias, int64_t topk,
+                                   int64_t rows_per_batch, double alpha, bool bias_in_logits, bool renorm);
+std::vector<at::Tensor> router_bwd(at::Tensor rows, at::Tensor router, at::Tensor probs, at::Tensor idx,
+                                   c10::optional<at::Tensor> dweights, c10::optional<at::Tensor> dprobs_sum,
+                                   int64_t rows_per_batch, double alpha, bool renorm, bool need_drows);
 std::vector<at::Tensor> swa_bwd(at::Tensor dout, at::Tensor q, at::Tensor k, at::Tensor v, at::Tensor o, at::Tensor lse,
                                 int64_t window, bool causal, double scale);
 }  // namespace uttt
@@ -75,6 +85,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("bmm_general", &bmm_general);
   m.def("swa_fwd", &swa_fwd);
   m.def("swa_bwd", &swa_bwd);
+  m.def("pool_step_supported", &pool_step_supported);
+  m.def("pool_step_fwd", &pool_step_fwd);
+  m.def("pool_step_bwd", &pool_step_bwd);
+  m.def("router_supported", &router_supported);
+  m.def("router_fwd", &router_fwd);
+  m.def("router_bwd", &router_bwd);
   m.def("rs_sumsq", &rs_sumsq);
   m.def("adamw_scatter", &adamw_scatter);
 }

@@ -269,6 +269,92 @@ def build_group_plan(expert_idx: torch.Tensor, num_experts: int) -> GroupPlan:
     return GroupPlan(dest, offsets, sizes, tile_group, int(rows_padded), bsz * num_experts, k)
 
 
+_POOL_MODES = {"restore": 0, "unit": 1, "none": 2}
+
+
+class _PoolStep(torch.autograd.Function):
+    """n = renorm(m + lr * d), w = bf16(n) in one pass; first-order differentiable."""
+
+    @staticmethod
+    def forward(ctx, m, d, lr, mode):
+        m, d = m.contiguous(), d.contiguous()
+        n, w = cuda_ext(m).pool_step_fwd(m, d, float(lr), int(mode))
+        ctx.save_for_backward(m, d)
+        ctx.args = (float(lr), int(mode))
+        return n, w
+
+    @staticmethod
+    def backward(ctx, gn, gw):
+        m, d = ctx.saved_tensors
+        lr, mode = ctx.args
+        gm, gd = cuda_ext(m).pool_step_bwd(m, d, gn, gw, lr, mode)
+        return gm, gd, None, None
+
+
+def pool_step(m: torch.Tensor, d: torch.Tensor, lr: float, renorm: str = "restore",
+              compute_dtype: torch.dtype = torch.bfloat16):
+    """Master step of a fast-weight matrix stack: ``n = renorm(m + lr * d)`` over the last dim, plus the
+    compute-dtype copy.  m: fp32 [..., D]; d: same shape.  Returns (n fp32, w compute_dtype)."""
+    ext = _kernel("pool_step_fwd", m)
+    if ext is not None and m.dtype == torch.float32 and compute_dtype == torch.bfloat16 \
+            and d.dtype in (torch.bfloat16, torch.float32) and ext.pool_step_supported(m.shape[-1]):
+        return _PoolStep.apply(m, d, lr, _POOL_MODES[renorm])
+    n = m + d.float() * lr
+    if renorm == "restore":
+        n = n / (n.norm(dim=-1, keepdim=True) + 1e-5) * m.norm(dim=-1, keepdim=True)
+    elif renorm == "unit":
+        n = torch.nn.functional.normalize(n, dim=-1)
+    elif renorm != "none":
+        raise ValueError(f"unknown renorm {renorm!r}")
+    return n, n.to(compute_dtype)
+
+
+class _Router(torch.autograd.Function):
+    """Fused softmax router (logits, softmax, top-k, combine weights, per-sequence probability sums)."""
+
+    @staticmethod
+    def forward(ctx, rows, router, bias, topk, rows_per_batch, alpha, bias_in_logits, renorm):
+        ext = cuda_ext(rows)
+        idx, w, probs, psum = ext.router_fwd(rows, router, bias, int(topk), int(rows_per_batch), float(alpha),
+                                             bool(bias_in_logits), bool(renorm))
+        ctx.save_for_backward(rows, router, probs, idx)
+        ctx.args = (int(rows_per_batch), float(alpha), bool(renorm))
+        ctx.mark_non_differentiable(idx)
+        return idx, w, psum
+
+    @staticmethod
+    def backward(ctx, _gidx, gw, gpsum):
+        rows, router, probs, idx = ctx.saved_tensors
+        rpb, alpha, renorm = ctx.args
+        ext = cuda_ext(rows)
+        drows, drouter = ext.router_bwd(rows, router, probs, idx, gw, gpsum, rpb, alpha, renorm,
+                                        bool(ctx.needs_input_grad[0]))
+        return (drows if ctx.needs_input_grad[0] else None), drouter, None, None, None, None, None, None
+
+
+def route_softmax_topk(rows, router, bias, topk: int, alpha: float = 1.0, bias_in_logits: bool = False,
+                       renorm: bool = False):
+    """rows [B, N, D], router [E, D], bias [E] or None -> (idx [B, N, k] int, weights [B*N, k] fp32,
+    probs_sum [B, E] fp32) of a softmax router; the bias shifts selection only unless ``bias_in_logits``."""
+    bsz, n, d = rows.shape
+    e = router.shape[0]
+    ext = _kernel("router_fwd", rows)
+    if ext is not None and ext.router_supported(d, e, topk) and rows.dtype in (torch.bfloat16, torch.float32):
+        idx, w, psum = _Router.apply(rows.reshape(bsz * n, d).contiguous(), router.float().contiguous(),
+                                     None if bias is None else bias.detach(), topk, n, alpha, bias_in_logits, renorm)
+        return idx.view(bsz, n, topk), w, psum
+    logits = torch.matmul(rows.float(), router.float().t())
+    if bias is not None and bias_in_logits:
+        logits = logits + bias.view(1, 1, e)
+    probs = torch.softmax(logits, dim=-1)
+    scores = logits if (bias is None or bias_in_logits) else logits + bias.view(1, 1, e)
+    idx = torch.topk(scores.detach(), k=topk, dim=-1).indices
+    picked = probs.gather(-1, idx)
+    if renorm:
+        picked = picked / picked.sum(dim=-1, keepdim=True).clamp_min(1e-9)
+    return idx, (picked * alpha).view(bsz * n, topk), probs.sum(dim=1)
+
+
 class _Permute(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, dest, rows_padded, weights):
