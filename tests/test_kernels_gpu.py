@@ -205,8 +205,8 @@ def test_pool_step_matches_reference(renorm, d, ddtype):
     _close(w, nr, 2e-2, 1e-2, "w")
     gn = torch.randn_like(n)
     gw = torch.randn_like(n).bfloat16()
-    g1, g2 = torch.autograd.grad([n, w], [m, dd], [gn, gw])
-    g1r, g2r = torch.autograd.grad(nr, [mr, dr], gn + gw.float())
+    g1, g2 = torch.autograd.grad([n, w], [m, dd], [gn, gw], retain_graph=True)
+    g1r, g2r = torch.autograd.grad(nr, [mr, dr], gn + gw.float(), retain_graph=True)
     _close(g1, g1r, 1e-4, 1e-4, "dm")
     _close(g2, g2r, 3e-2 if ddtype == torch.bfloat16 else 1e-4, 1e-2 if ddtype == torch.bfloat16 else 1e-4, "dd")
     (g3,) = torch.autograd.grad(w, m, gw)            # only the compute copy has a gradient

@@ -61,10 +61,9 @@ class GatedMLP(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         # one GEMM for gate|up, fused SwiGLU kernel, one GEMM down
-        w = torch.cat([self.gate_proj.weight, self.up_proj.weight], dim=0)
-        y02 = F.linear(x, w)
+        y02 = ops.stacked_linear(x, self.gate_proj.weight, self.up_proj.weight)
         h = ops.swiglu(y02.view(-1, y02.shape[-1])).view(*x.shape[:-1], -1)
-        return self.down_proj(h)
+        return ops.linear(h, self.down_proj.weight)
 
 
 class SlidingWindowAttention(nn.Module):
@@ -105,7 +104,9 @@ class SlidingWindowAttention(nn.Module):
                 offset: int):
         b, l, _ = x.shape
         # three GEMMs with contiguous outputs (a fused QKV GEMM would hand strided views to every consumer)
-        q_flat, k_flat, v_flat = self.q_proj(x), self.k_proj(x), self.v_proj(x)
+        q_flat, k_flat, v_flat = ops.fanout_linear(
+            x, [self.q_proj.weight, self.k_proj.weight, self.v_proj.weight],
+            [self.q_proj.bias, self.k_proj.bias, self.v_proj.bias])
         q = q_flat.reshape(b, l, self.num_heads, self.head_dim)
         k = k_flat.reshape(b, l, self.num_kv_heads, self.head_dim)
         v = v_flat.reshape(b, l, self.num_kv_heads, self.head_dim)
@@ -120,7 +121,7 @@ class SlidingWindowAttention(nn.Module):
         o = ops.swa_attention(q, full_k, full_v, self.window_size, causal=True)
         o = o.reshape(b, l, self.hidden_size)
         if self.o_proj is not None:
-            o = self.o_proj(o)
+            o = ops.linear(o, self.o_proj.weight)
         return o, q_flat, k_flat, v_flat, k, v
 
 

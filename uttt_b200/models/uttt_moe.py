@@ -86,7 +86,7 @@ class MoEBlock(nn.Module):
         else:
             mixed = attn_out
         if self.memory_output_proj is not None:
-            mixed = self.memory_output_proj(mixed)
+            mixed = ops.linear(mixed, self.memory_output_proj.weight)
         h = residual + mixed
         h = h + self.mlp(self.mlp_norm(h))
         if lb_probs is None:

@@ -7,10 +7,11 @@
 //   weight = alpha * probs[idx]   or   alpha * probs[idx] / sum_sel probs[idx]
 //   probs_sum[b, e] += probs[r, e]                            (load-balance statistics per sequence)
 //
-// Forward: one warp per 8 rows, lane = expert (two experts per lane when E = 64); the router matrix sits
-// transposed in shared memory, the rows are read once from global memory with warp-uniform 16-byte loads.
+// Forward: a block stages 64 rows in shared memory, each warp multiplies 8 of them with lane = expert (two
+// experts per lane when E = 64) against the transposed router matrix in shared memory, then does the softmax
+// and the top-k with warp shuffles.
 // Backward: one kernel turns (d weight, d probs_sum) into d logits and d rows (lane = slice of D), a second one
-// reduces d router = d logits^T . rows over row chunks with per-thread register tiles and fp32 atomics.
+// reduces d router = d logits^T . rows over row chunks with per-thread register tiles into per-block partials.
 // Reference behaviour: flame/custom_models/uttt_moe/moe_routing.py:7-75 (softmax router, selected_prob /
 // topk_renorm combine modes).
 #include <ATen/ATen.h>
@@ -22,31 +23,37 @@
 
 namespace uttt {
 
-constexpr int kRowsPerWarp = 8;
 constexpr int kMaxTopK = 4;
 
 template <typename T>
 __device__ __forceinline__ void load8(const T* p, float (&f)[8]) { Vec8<T>::load(p, f); }
 
 // ------------------------------------------------------------------------------------ forward
-template <typename T, int EPL>
+// Block = 8 warps.  Per step the block stages 8 * RPW rows in shared memory with coalesced 16-byte loads (all
+// in flight at once), then warp w multiplies its RPW rows: lane = expert, the row values are warp-uniform
+// shared-memory reads, the router matrix sits transposed ([D][32 * EPL + 1], padded against bank conflicts).
+template <typename T, int EPL, int RPW>
 __global__ void __launch_bounds__(256) router_fwd_kernel(const T* __restrict__ rows, const float* __restrict__ router,
                                                          const float* __restrict__ bias, int R, int D, int E, int topk,
                                                          int rows_per_batch, float alpha, int bias_in_logits,
                                                          int renorm, int* __restrict__ idx_out,
                                                          float* __restrict__ w_out, float* __restrict__ probs_out,
                                                          float* __restrict__ probs_sum) {
-  extern __shared__ float wt[];                 // [D][32 * EPL] transposed router matrix (zero for e >= E)
-  constexpr int EP = 32 * EPL;
-  for (int i = threadIdx.x; i < D * EP; i += blockDim.x) {
-    int d = i / EP, e = i % EP;
-    wt[i] = (e < E) ? router[(size_t)e * D + d] : 0.f;
+  constexpr int EP = 32 * EPL + 1;
+  constexpr int VEC = 16 / (int)sizeof(T);           // elements per 16-byte piece
+  constexpr int BR = 8 * RPW;                        // rows per block step
+  extern __shared__ __align__(16) uint8_t smem_r[];
+  float* wt = reinterpret_cast<float*>(smem_r);                        // [D][EP]
+  T* xs = reinterpret_cast<T*>(smem_r + (((size_t)D * EP * 4 + 15) & ~(size_t)15));   // [BR][D]
+  for (int i = threadIdx.x; i < E * D; i += blockDim.x) {
+    int e = i / D, d = i - e * D;
+    wt[d * EP + e] = router[i];
   }
-  __syncthreads();
-  const int lane = threadIdx.x & 31;
-  const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int nwarps = (gridDim.x * blockDim.x) >> 5;
-  const int groups = (R + kRowsPerWarp - 1) / kRowsPerWarp;
+  for (int i = threadIdx.x; i < D * (32 * EPL - E); i += blockDim.x) {
+    int d = i / (32 * EPL - E), e = E + i % (32 * EPL - E);
+    wt[d * EP + e] = 0.f;
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float bsel[EPL], blog[EPL];
 #pragma unroll
   for (int q = 0; q < EPL; ++q) {
@@ -69,33 +76,44 @@ __global__ void __launch_bounds__(256) router_fwd_kernel(const T* __restrict__ r
       }
     }
   };
-  for (int g = warp_global; g < groups; g += nwarps) {
-    const int r0 = g * kRowsPerWarp;
-    float acc[kRowsPerWarp][EPL];
+  const int steps = (R + BR - 1) / BR;
+  const int vec_per_row = D / VEC;
+  for (int step = blockIdx.x; step < steps; step += gridDim.x) {
+    const int rb = step * BR;
+    __syncthreads();                                 // previous step's readers are done (and wt is written)
+    for (int i = threadIdx.x; i < BR * vec_per_row; i += blockDim.x) {
+      int r = i / vec_per_row, v = i - r * vec_per_row;
+      int rr = min(rb + r, R - 1);
+      *reinterpret_cast<uint4*>(xs + (size_t)r * D + v * VEC) =
+          *reinterpret_cast<const uint4*>(rows + (size_t)rr * D + v * VEC);
+    }
+    __syncthreads();
+    const int r0 = rb + warp * RPW;
+    float acc[RPW][EPL];
 #pragma unroll
-    for (int r = 0; r < kRowsPerWarp; ++r)
+    for (int r = 0; r < RPW; ++r)
 #pragma unroll
       for (int q = 0; q < EPL; ++q) acc[r][q] = 0.f;
+    const T* xw = xs + (size_t)warp * RPW * D;
+#pragma unroll 2
     for (int d0 = 0; d0 < D; d0 += 8) {
-      float x[kRowsPerWarp][8];
+      float w[8][EPL];
 #pragma unroll
-      for (int r = 0; r < kRowsPerWarp; ++r) {
-        int rr = min(r0 + r, R - 1);
-        load8(rows + (size_t)rr * D + d0, x[r]);
-      }
+      for (int dd = 0; dd < 8; ++dd)
 #pragma unroll
-      for (int dd = 0; dd < 8; ++dd) {
-        float w[EPL];
+        for (int q = 0; q < EPL; ++q) w[dd][q] = wt[(d0 + dd) * EP + lane + 32 * q];
 #pragma unroll
-        for (int q = 0; q < EPL; ++q) w[q] = wt[(d0 + dd) * EP + lane + 32 * q];
+      for (int r = 0; r < RPW; ++r) {
+        float x[8];
+        load8(xw + (size_t)r * D + d0, x);
 #pragma unroll
-        for (int r = 0; r < kRowsPerWarp; ++r)
+        for (int dd = 0; dd < 8; ++dd)
 #pragma unroll
-          for (int q = 0; q < EPL; ++q) acc[r][q] = fmaf(x[r][dd], w[q], acc[r][q]);
+          for (int q = 0; q < EPL; ++q) acc[r][q] = fmaf(x[dd], w[dd][q], acc[r][q]);
       }
     }
 #pragma unroll
-    for (int r = 0; r < kRowsPerWarp; ++r) {
+    for (int r = 0; r < RPW; ++r) {
       const int row = r0 + r;
       if (row >= R) break;                       // warp-uniform
       float lg[EPL], mx = -INFINITY;
@@ -266,17 +284,20 @@ __global__ void __launch_bounds__(256) router_bwd_rows_kernel(
 }
 
 // ------------------------------------------------------------------------------------ backward: d router
-// block = 256 threads = 8 expert groups x 32 lanes; thread tile = EG experts x DPL slices of D.
+// block = 256 threads = 8 expert groups x 32 lanes; thread tile = EG experts x DPL slices of D.  Every block
+// reduces `chunk` rows and writes its [E, D] partial to scratch; the partials are summed afterwards.
 template <typename T, int EG, int DPL>
 __global__ void __launch_bounds__(256) router_bwd_weight_kernel(const T* __restrict__ rows,
                                                                 const float* __restrict__ dlogits, int R, int D,
-                                                                int E, int chunk, float* __restrict__ drouter) {
+                                                                int E, int chunk, float* __restrict__ partial) {
   constexpr int SUB = 32;                         // rows staged per step
-  extern __shared__ uint8_t smem_w[];
+  constexpr int VEC = 16 / (int)sizeof(T);
+  extern __shared__ __align__(16) uint8_t smem_w[];
   float* xs = reinterpret_cast<float*>(smem_w);                   // [SUB][D]
   float* ds = xs + SUB * D;                                       // [SUB][E]
   const int lane = threadIdx.x & 31, eg = threadIdx.x >> 5;
   const int r_begin = blockIdx.x * chunk, r_end = min(R, r_begin + chunk);
+  const int vec_per_row = D / VEC;
   float acc[EG][DPL];
 #pragma unroll
   for (int a = 0; a < EG; ++a)
@@ -285,9 +306,22 @@ __global__ void __launch_bounds__(256) router_bwd_weight_kernel(const T* __restr
   for (int rs = r_begin; rs < r_end; rs += SUB) {
     const int nr = min(SUB, r_end - rs);
     __syncthreads();
-    for (int i = threadIdx.x; i < SUB * D; i += blockDim.x) {
-      int r = i / D, d = i % D;
-      xs[i] = (r < nr) ? static_cast<float>(rows[(size_t)(rs + r) * D + d]) : 0.f;
+    for (int i = threadIdx.x; i < SUB * vec_per_row; i += blockDim.x) {
+      int r = i / vec_per_row, v = i - r * vec_per_row;
+      float f[VEC];
+      if (r < nr) {
+        if (VEC == 8) load8(rows + (size_t)(rs + r) * D + v * VEC, *reinterpret_cast<float (*)[8]>(&f[0]));
+        else {
+          float4 t = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(rows) + (size_t)(rs + r) * D + v * 4);
+          f[0] = t.x; f[1] = t.y; f[2] = t.z; f[3] = t.w;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) f[j] = 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < VEC; j += 4)
+        *reinterpret_cast<float4*>(xs + r * D + v * VEC + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
     }
     for (int i = threadIdx.x; i < SUB * E; i += blockDim.x) {
       int r = i / E;
@@ -310,12 +344,13 @@ __global__ void __launch_bounds__(256) router_bwd_weight_kernel(const T* __restr
         for (int i = 0; i < DPL; ++i) acc[a][i] = fmaf(g[a], x[i], acc[a][i]);
     }
   }
+  float* out = partial + (size_t)blockIdx.x * E * D;
 #pragma unroll
   for (int a = 0; a < EG; ++a)
 #pragma unroll
     for (int i = 0; i < DPL; ++i) {
       int d = lane + 32 * i;
-      if (d < D) atomicAdd(drouter + (size_t)(eg * EG + a) * D + d, acc[a][i]);
+      if (d < D) out[(size_t)(eg * EG + a) * D + d] = acc[a][i];
     }
 }
 
@@ -347,9 +382,11 @@ std::vector<at::Tensor> router_fwd(at::Tensor rows, at::Tensor router, c10::opti
   auto probs = at::empty({R, E}, opts.dtype(at::kFloat));
   auto psum = at::zeros({R / rows_per_batch, E}, opts.dtype(at::kFloat));
   const int epl = E > 32 ? 2 : 1;
-  const size_t smem = (size_t)D * 32 * epl * sizeof(float);
-  const int groups = (R + kRowsPerWarp - 1) / kRowsPerWarp;
-  const int blocks = std::max(1, std::min((groups + 7) / 8, 2 * sm_count()));
+  const bool bf = rows.scalar_type() == at::kBFloat16;
+  const int rpw = bf ? 8 : 4;
+  const size_t smem = (((size_t)D * (32 * epl + 1) * 4 + 15) & ~(size_t)15) + (size_t)8 * rpw * D * (bf ? 2 : 4);
+  const int steps = (R + 8 * rpw - 1) / (8 * rpw);
+  const int blocks = std::max(1, std::min(steps, 2 * sm_count()));
   auto stream = at::cuda::getCurrentCUDAStream().stream();
   auto launch = [&](auto kernel, auto* rp) {
     C10_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -360,13 +397,13 @@ std::vector<at::Tensor> router_fwd(at::Tensor rows, at::Tensor router, c10::opti
   };
   if (rows.scalar_type() == at::kBFloat16) {
     auto* rp = reinterpret_cast<const __nv_bfloat16*>(rows.data_ptr());
-    if (epl == 1) launch(router_fwd_kernel<__nv_bfloat16, 1>, rp);
-    else launch(router_fwd_kernel<__nv_bfloat16, 2>, rp);
+    if (epl == 1) launch(router_fwd_kernel<__nv_bfloat16, 1, 8>, rp);
+    else launch(router_fwd_kernel<__nv_bfloat16, 2, 8>, rp);
   } else {
     TORCH_CHECK(rows.scalar_type() == at::kFloat);
     auto* rp = rows.data_ptr<float>();
-    if (epl == 1) launch(router_fwd_kernel<float, 1>, rp);
-    else launch(router_fwd_kernel<float, 2>, rp);
+    if (epl == 1) launch(router_fwd_kernel<float, 1, 4>, rp);
+    else launch(router_fwd_kernel<float, 2, 4>, rp);
   }
   count_launch();
   return {idx, w, probs, psum};
@@ -392,14 +429,13 @@ static void launch_bwd_rows(int dpl, const float* router, const float* probs, co
 }
 
 template <typename T, int EG>
-static void launch_bwd_weight(int dpl, const T* rows, const float* dlogits, int R, int D, int E, float* drouter,
-                              cudaStream_t stream) {
-  const int chunk = 256;
+static void launch_bwd_weight(int dpl, const T* rows, const float* dlogits, int R, int D, int E, float* partial,
+                              int chunk, cudaStream_t stream) {
   const int blocks = (R + chunk - 1) / chunk;
   const size_t smem = (size_t)32 * (D + E) * sizeof(float);
   auto go = [&](auto kernel) {
     C10_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kernel<<<blocks, 256, smem, stream>>>(rows, dlogits, R, D, E, chunk, drouter);
+    kernel<<<blocks, 256, smem, stream>>>(rows, dlogits, R, D, E, chunk, partial);
     C10_CUDA_KERNEL_LAUNCH_CHECK();
   };
   if (dpl <= 4) go(router_bwd_weight_kernel<T, EG, 4>);
@@ -427,7 +463,8 @@ std::vector<at::Tensor> router_bwd(at::Tensor rows, at::Tensor router, at::Tenso
   }
   auto dlogits = at::empty({R, E}, probs.options());
   auto drows = need_drows ? at::empty_like(rows) : at::Tensor();
-  auto drouter = at::zeros({E, D}, router.options());
+  const int wchunk = 128;
+  auto partial = at::empty({(R + wchunk - 1) / wchunk, E, D}, router.options());
   auto stream = at::cuda::getCurrentCUDAStream().stream();
   const int dpl = (D + 31) / 32;
   const bool bf = rows.scalar_type() == at::kBFloat16;
@@ -449,22 +486,23 @@ std::vector<at::Tensor> router_bwd(at::Tensor rows, at::Tensor router, at::Tenso
 #define UTTT_ROUTER_BWD_W(T_)                                                                                  \
   do {                                                                                                         \
     auto* rp = reinterpret_cast<const T_*>(rows.data_ptr());                                                   \
-    float* dr = drouter.data_ptr<float>();                                                                     \
+    float* dr = partial.data_ptr<float>();                                                                     \
     switch (E / 8) {                                                                                           \
-      case 1: launch_bwd_weight<T_, 1>(dpl, rp, dl, R, D, E, dr, stream); break;                               \
-      case 2: launch_bwd_weight<T_, 2>(dpl, rp, dl, R, D, E, dr, stream); break;                               \
-      case 3: launch_bwd_weight<T_, 3>(dpl, rp, dl, R, D, E, dr, stream); break;                               \
-      case 4: launch_bwd_weight<T_, 4>(dpl, rp, dl, R, D, E, dr, stream); break;                               \
-      case 5: launch_bwd_weight<T_, 5>(dpl, rp, dl, R, D, E, dr, stream); break;                               \
-      case 6: launch_bwd_weight<T_, 6>(dpl, rp, dl, R, D, E, dr, stream); break;                               \
-      case 7: launch_bwd_weight<T_, 7>(dpl, rp, dl, R, D, E, dr, stream); break;                               \
-      default: launch_bwd_weight<T_, 8>(dpl, rp, dl, R, D, E, dr, stream); break;                              \
+      case 1: launch_bwd_weight<T_, 1>(dpl, rp, dl, R, D, E, dr, wchunk, stream); break;                               \
+      case 2: launch_bwd_weight<T_, 2>(dpl, rp, dl, R, D, E, dr, wchunk, stream); break;                               \
+      case 3: launch_bwd_weight<T_, 3>(dpl, rp, dl, R, D, E, dr, wchunk, stream); break;                               \
+      case 4: launch_bwd_weight<T_, 4>(dpl, rp, dl, R, D, E, dr, wchunk, stream); break;                               \
+      case 5: launch_bwd_weight<T_, 5>(dpl, rp, dl, R, D, E, dr, wchunk, stream); break;                               \
+      case 6: launch_bwd_weight<T_, 6>(dpl, rp, dl, R, D, E, dr, wchunk, stream); break;                               \
+      case 7: launch_bwd_weight<T_, 7>(dpl, rp, dl, R, D, E, dr, wchunk, stream); break;                               \
+      default: launch_bwd_weight<T_, 8>(dpl, rp, dl, R, D, E, dr, wchunk, stream); break;                              \
     }                                                                                                          \
   } while (0)
   if (bf) UTTT_ROUTER_BWD_W(__nv_bfloat16); else UTTT_ROUTER_BWD_W(float);
 #undef UTTT_ROUTER_BWD_W
   count_launch();
   count_launch();
+  auto drouter = partial.sum(0);
   if (!need_drows) drows = at::empty({0}, rows.options());
   return {drows, drouter};
 }

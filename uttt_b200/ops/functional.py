@@ -269,6 +269,135 @@ def build_group_plan(expert_idx: torch.Tensor, num_experts: int) -> GroupPlan:
     return GroupPlan(dest, offsets, sizes, tile_group, int(rows_padded), bsz * num_experts, k)
 
 
+# =========================================================================== dense projections
+_FUSED_WGRAD = False
+
+
+def set_fused_weight_grad(flag: bool) -> None:
+    """Let dense projections add their weight gradient into an existing ``.grad`` buffer inside the GEMM
+    (and report no gradient to autograd).  Meant for trainers that own persistent ``.grad`` buffers and call
+    ``backward()``; leave it off when gradients of weights are requested through ``torch.autograd.grad``."""
+    global _FUSED_WGRAD
+    _FUSED_WGRAD = bool(flag)
+
+
+def _fuse_wgrad(w: torch.Tensor, g2: torch.Tensor) -> bool:
+    """True when the weight gradient can be accumulated by the GEMM itself into the existing ``.grad`` buffer."""
+    return (_FUSED_WGRAD and w.grad is not None and w.grad.dtype == g2.dtype and w.grad.is_contiguous() and w.is_cuda
+            and not torch.is_grad_enabled())
+
+
+class _FanoutLinear(torch.autograd.Function):
+    """``y_i = x @ W_i^T (+ b_i)`` for several weights reading the same input.
+
+    Backward adds every ``dY_i @ W_i`` into one input-gradient buffer inside the GEMM (beta = 1) instead of
+    leaving n - 1 elementwise adds to autograd, and adds ``dY_i^T @ x`` straight into ``W_i.grad`` when that
+    buffer already exists (flat gradient buffers of the sharded trainer), returning no weight gradient then."""
+
+    @staticmethod
+    def forward(ctx, x, n, *wb):
+        ws, bs = wb[:n], wb[n:]
+        ctx.save_for_backward(x, *ws)
+        ctx.n = n
+        ctx.has_bias = [b is not None for b in bs]
+        outs = tuple(torch.nn.functional.linear(x, w, b) for w, b in zip(ws, bs))
+        return outs
+
+    @staticmethod
+    def backward(ctx, *gys):
+        x, *ws = ctx.saved_tensors
+        n = ctx.n
+        x2 = x.reshape(-1, x.shape[-1])
+        dx = None
+        gws, gbs = [], []
+        for i, (w, gy) in enumerate(zip(ws, gys)):
+            if gy is None:
+                gws.append(None)
+                gbs.append(None)
+                continue
+            g2 = gy.reshape(-1, gy.shape[-1])
+            if ctx.needs_input_grad[0]:
+                if dx is None:
+                    dx = torch.mm(g2, w)
+                else:
+                    dx.addmm_(g2, w)
+            if ctx.needs_input_grad[2 + i]:
+                if _fuse_wgrad(w, g2):
+                    w.grad.addmm_(g2.t(), x2)
+                    gws.append(None)
+                else:
+                    gws.append(torch.mm(g2.t(), x2))
+            else:
+                gws.append(None)
+            gbs.append(g2.sum(0) if (ctx.has_bias[i] and ctx.needs_input_grad[2 + n + i]) else None)
+        return (None if dx is None else dx.view_as(x), None, *gws, *gbs)
+
+
+def fanout_linear(x: torch.Tensor, weights, biases=None):
+    """Several linear maps of one input; see ``_FanoutLinear``.  Returns a tuple of outputs."""
+    weights = list(weights)
+    biases = [None] * len(weights) if biases is None else list(biases)
+    if not x.is_cuda:
+        return tuple(torch.nn.functional.linear(x, w, b) for w, b in zip(weights, biases))
+    return _FanoutLinear.apply(x, len(weights), *weights, *biases)
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x @ W^T (+ b)`` with the weight gradient accumulated in the GEMM when ``W.grad`` exists."""
+    return fanout_linear(x, [weight], [bias])[0]
+
+
+def _stacked_view(a: torch.Tensor, b: torch.Tensor):
+    """[a; b] as one matrix without a copy when ``b`` directly follows ``a`` in the same storage, else None."""
+    if (a.dim() == 2 and b.dim() == 2 and a.shape[1] == b.shape[1] and a.is_contiguous() and b.is_contiguous()
+            and a.dtype == b.dtype and a.device == b.device
+            and a.untyped_storage().data_ptr() == b.untyped_storage().data_ptr()
+            and b.storage_offset() == a.storage_offset() + a.numel()):
+        return torch.as_strided(a.detach(), (a.shape[0] + b.shape[0], a.shape[1]), (a.shape[1], 1), a.storage_offset())
+    return None
+
+
+class _StackedLinear(torch.autograd.Function):
+    """``x @ [W_a; W_b]^T`` as ONE GEMM.  When the two weights (and their ``.grad`` buffers) are neighbours in a
+    flat buffer the stacked operand is a view; otherwise it is concatenated."""
+
+    @staticmethod
+    def forward(ctx, x, wa, wb):
+        wc = _stacked_view(wa, wb)
+        if wc is None:
+            wc = torch.cat([wa.detach(), wb.detach()], dim=0)
+        ctx.save_for_backward(x, wa, wb)
+        return torch.nn.functional.linear(x, wc)
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, wa, wb = ctx.saved_tensors
+        wc = _stacked_view(wa, wb)
+        if wc is None:
+            wc = torch.cat([wa.detach(), wb.detach()], dim=0)
+        g2 = gy.reshape(-1, gy.shape[-1])
+        x2 = x.reshape(-1, x.shape[-1])
+        dx = torch.mm(g2, wc).view_as(x) if ctx.needs_input_grad[0] else None
+        ga = gb = None
+        if ctx.needs_input_grad[1] or ctx.needs_input_grad[2]:
+            gc = None
+            if wa.grad is not None and wb.grad is not None and _fuse_wgrad(wa, g2) and _fuse_wgrad(wb, g2):
+                gc = _stacked_view(wa.grad, wb.grad)
+            if gc is not None:
+                gc.addmm_(g2.t(), x2)
+            else:
+                full = torch.mm(g2.t(), x2)
+                ga, gb = full[:wa.shape[0]], full[wa.shape[0]:]
+        return dx, ga, gb
+
+
+def stacked_linear(x: torch.Tensor, wa: torch.Tensor, wb: torch.Tensor) -> torch.Tensor:
+    """``cat(x @ W_a^T, x @ W_b^T)`` along the last dim, one GEMM."""
+    if not x.is_cuda:
+        return torch.nn.functional.linear(x, torch.cat([wa, wb], dim=0))
+    return _StackedLinear.apply(x, wa, wb)
+
+
 _POOL_MODES = {"restore": 0, "unit": 1, "none": 2}
 
 

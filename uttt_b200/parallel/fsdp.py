@@ -178,6 +178,11 @@ class ShardedTrainer:
         self._norm_buf = torch.zeros(2, dtype=torch.float32, device=self.device)
         if self.symm is not None:
             self.symm.finalize()
+        if self.device.type == "cuda":
+            # the .grad tensors are persistent views of the flat buffers: dense projections may add their weight
+            # gradients into them inside the GEMM
+            from ..ops import set_fused_weight_grad
+            set_fused_weight_grad(True)
 
     # ------------------------------------------------------------------ bookkeeping
     def num_parameters(self) -> int:
