@@ -176,7 +176,7 @@ def main():
     ap.add_argument("--model", default="760M-uttt-moe")
     ap.add_argument("--seq-len", type=int, default=32768)
     ap.add_argument("--per-gpu-batch", type=int, default=4)
-    ap.add_argument("--micro-batch", type=int, default=int(os.environ.get("UTTT_BENCH_MICRO_BATCH", "2")))
+    ap.add_argument("--micro-batch", type=int, default=int(os.environ.get("UTTT_BENCH_MICRO_BATCH", "4")))
     ap.add_argument("--backward-mode", default="full")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -61,11 +61,24 @@ class Routing:
     weights: torch.Tensor       # [B*N, k] combine weights (differentiable)
     prob_sum: torch.Tensor      # [B, E] sum of balance probabilities over tokens
     counts: torch.Tensor        # [B, E] tokens routed to each expert
+    ep: object = None           # expert-parallel handle (parallel/expert_parallel.py) and its plan, when sharded
+    ep_plan: object = None
+    idx: Optional[torch.Tensor] = None   # [B, N, k] selected experts
 
 
 def route_rows(rows: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Tensor], cfg,
-               bias_in_logits: bool = False) -> Routing:
-    """rows: [B, N, D]; router: [E, D] (fp32 logits outside autocast; moe_routing.py:7-75)."""
+               bias_in_logits: bool = False, ep=None) -> Routing:
+    """rows: [B, N, D]; router: [E, D] (fp32 logits outside autocast; moe_routing.py:7-75).
+    With an expert-parallel handle the routing also carries the cross-rank plan."""
+    routing = _route_rows_local(rows, router, bias, cfg, bias_in_logits)
+    if ep is not None and ep.P > 1:
+        routing.ep = ep
+        routing.ep_plan = ep.plan(routing.plan, routing.idx)
+    return routing
+
+
+def _route_rows_local(rows: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Tensor], cfg,
+                      bias_in_logits: bool = False) -> Routing:
     bsz, n, _ = rows.shape
     e = router.shape[0]
     k = cfg.memory_num_active_experts
@@ -73,12 +86,12 @@ def route_rows(rows: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Te
         idx = torch.zeros(bsz, n, 1, dtype=torch.long, device=rows.device)
         plan = ops.build_group_plan(idx, 1)
         ones = torch.ones(bsz * n, 1, device=rows.device, dtype=torch.float32)
-        return Routing(plan, ones, ones.view(bsz, n).sum(1, keepdim=True), plan.sizes.view(bsz, 1).float())
+        return Routing(plan, ones, ones.view(bsz, n).sum(1, keepdim=True), plan.sizes.view(bsz, 1).float(), idx=idx)
     if cfg.memory_router_type == "softmax":
         idx, weights, psum = ops.route_softmax_topk(rows, router, bias, k, cfg.memory_router_alpha, bias_in_logits,
                                                     cfg.memory_router_combine_mode == "topk_renorm")
         plan = ops.build_group_plan(idx, e)
-        return Routing(plan, weights, psum, plan.sizes.view(bsz, e).float())
+        return Routing(plan, weights, psum, plan.sizes.view(bsz, e).float(), idx=idx)
     logits = torch.matmul(rows.float(), router.float().t())
     if bias is not None and bias_in_logits:
         logits = logits + bias.view(1, 1, e)
@@ -91,12 +104,24 @@ def route_rows(rows: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Te
         picked = picked / picked.sum(dim=-1, keepdim=True).clamp_min(1e-9)
     weights = (picked * cfg.memory_router_alpha).view(bsz * n, k)
     plan = ops.build_group_plan(idx, e)
-    return Routing(plan, weights, probs.sum(dim=1), plan.sizes.view(bsz, e).float())
+    return Routing(plan, weights, probs.sum(dim=1), plan.sizes.view(bsz, e).float(), idx=idx)
 
 
 def pool_read(q_rows: torch.Tensor, state_w02: torch.Tensor, state_w1: torch.Tensor, routing: Routing) -> torch.Tensor:
     """y = sum_{e in top-k} p_e * W1_e (silu(W0_e q) * W2_e q).  q_rows: [B, N, D] -> [B, N, D]."""
     bsz, n, d = q_rows.shape
+    if routing.ep is not None:
+        # expert-parallel: rows travel to the owners of their experts; the state holds (source, sequence, local expert)
+        ep, eplan = routing.ep, routing.ep_plan
+        plan = eplan.owner
+        g = plan.num_groups
+        w02 = state_w02.reshape(g, state_w02.shape[2], d)
+        w1 = state_w1.reshape(g, d, state_w1.shape[3])
+        xp = ep.dispatch(q_rows.reshape(bsz * n, d).to(w02.dtype), None, eplan)
+        y02 = ops.gg_nt(xp, w02, plan)
+        hid = ops.swiglu(y02)
+        yp = ops.gg_nt(hid, w1, plan)
+        return ep.combine(yp, routing.weights, eplan).view(bsz, n, d)
     plan = routing.plan
     g = plan.num_groups
     w02 = state_w02.reshape(g, state_w02.shape[2], d)
@@ -117,21 +142,28 @@ def pool_raw_grad(k_rows: torch.Tensor, v_rows: torch.Tensor, lr_rows: torch.Ten
     With ``acc = (A02, A1)`` the gradients are added to those running sums and the sums are returned.
     """
     bsz, n, d = k_rows.shape
-    plan = routing.plan
-    g = plan.num_groups
     inter2 = state_w02.shape[2]
+    dt = state_w02.dtype
+    if routing.ep is not None:
+        ep, eplan = routing.ep, routing.ep_plan
+        plan = eplan.owner
+        kp = ep.dispatch(k_rows.reshape(bsz * n, d).to(dt), None, eplan)
+        vp = ep.dispatch(v_rows.reshape(bsz * n, d).to(dt), routing.weights, eplan)
+        lr8 = F.pad(lr_rows.reshape(bsz * n, 3).float(), (0, 5))          # 32-byte rows for the transport
+        lrp = ep.dispatch(lr8, None, eplan)[:, :3].contiguous()
+    else:
+        plan = routing.plan
+        kp = ops.permute_rows(k_rows.reshape(bsz * n, d).to(dt), plan)
+        # v scaled by its combine weight per routed copy while it is scattered
+        vp = ops.permute_rows(v_rows.reshape(bsz * n, d).to(dt), plan, routing.weights)
+        lrp = _permute_per_choice(lr_rows.reshape(bsz * n, 1, 3).float().expand(-1, plan.topk, -1), plan)
+    g = plan.num_groups
     w02 = state_w02.reshape(g, inter2, d)
     w1 = state_w1.reshape(g, d, inter2 // 2)
-    dt = w02.dtype
-    kp = ops.permute_rows(k_rows.reshape(bsz * n, d).to(dt), plan)
-    # v scaled by its combine weight per routed copy while it is scattered
-    vp = ops.permute_rows(v_rows.reshape(bsz * n, d).to(dt), plan, routing.weights)
-    lrp = _permute_per_choice(lr_rows.reshape(bsz * n, 1, 3).float().expand(-1, plan.topk, -1), plan)
     if acc is not None:
         return ops.fw_write_grad_accumulate(kp, vp, lrp, w02, w1, plan, acc[0], acc[1])
     g02, g1 = ops.fw_write_grad(kp, vp, lrp, w02, w1, plan)
-    e = g // bsz
-    return g02.view(bsz, e, inter2, d), g1.view(bsz, e, d, inter2 // 2)
+    return g02.view(*state_w02.shape[:2], inter2, d), g1.view(*state_w02.shape[:2], d, inter2 // 2)
 
 
 def _permute_per_choice(x: torch.Tensor, plan: ops.GroupPlan) -> torch.Tensor:

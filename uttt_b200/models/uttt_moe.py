@@ -60,6 +60,7 @@ class MoEBlock(nn.Module):
         self.memory_output_proj = nn.Linear(d, d, bias=False) if config.enable_attention_memory_output_proj else None
         self.mlp_norm = RMSNorm(d, eps=config.norm_eps)
         self.mlp = GatedMLP(d, config.mlp_intermediate_size)
+        self.ep = None            # expert-parallel handle, set by the model
 
     # -------------------------------------------------------------------------- read
     def forward(self, h, k_hist, v_hist, w02, w1, router, bias, offset: int):
@@ -78,7 +79,7 @@ class MoEBlock(nn.Module):
                 x_mem_in = x_attn_in
             mem = self.memory
             q_rows = mem.head_rows(mem.prep_query(q_flat, offset))
-            routing = fw.route_rows(q_rows, router, bias, cfg, getattr(cfg, "memory_bias_in_logits", False))
+            routing = fw.route_rows(q_rows, router, bias, cfg, getattr(cfg, "memory_bias_in_logits", False), self.ep)
             y = fw.pool_read(q_rows, w02, w1, routing)
             mem_out = mem.finish_read(y, x_mem_in).to(attn_out.dtype)
             lb_probs, lb_counts = routing.prob_sum, routing.counts
@@ -109,7 +110,7 @@ class MoEBlock(nn.Module):
         k_rows = mem.head_rows(mem.prep_key(k_flat, offset))
         v_rows = mem.head_rows(mem.prep_value(v_flat))
         route_in = v_rows if cfg.memory_router_from_v else k_rows
-        routing = fw.route_rows(route_in, router, bias, cfg, getattr(cfg, "memory_bias_in_logits", False))
+        routing = fw.route_rows(route_in, router, bias, cfg, getattr(cfg, "memory_bias_in_logits", False), self.ep)
         g02, g1 = fw.pool_raw_grad(k_rows, v_rows, lr_rows, w02, w1, routing, acc=acc)
         m = mem.momentum_coeff(x_in)
         return g02, g1, m, routing.prob_sum, routing.counts
@@ -137,6 +138,7 @@ class UTTTMoEModel(nn.Module):
         else:
             self.writer_layers = tuple(sorted(int(i) for i in write_layers))
         self.activation_checkpoint = True
+        self.ep = None
         if config.use_memory_block:
             self._init_pool_parameters()
             self._init_loss_free_buffers()
@@ -228,12 +230,29 @@ class UTTTMoEModel(nn.Module):
         return self.embeddings.weight.dtype if self.embeddings.weight.dtype != torch.float32 else (
             torch.float32)
 
+    def set_expert_parallel(self, ep) -> None:
+        """Shard the experts of the pool over the ranks of ``ep`` (parallel/expert_parallel.py): this rank then
+        keeps the state of every sequence of the group for its own experts only."""
+        if ep is not None and ep.P > 1:
+            if self.per_layer_pool or not self.config.memory_update_aggregate_write:
+                raise NotImplementedError("expert parallelism covers the shared pool with aggregated writes")
+            if self.config.memory_update_backward_mode == "cross_layer_cut":
+                raise NotImplementedError("expert parallelism with cross_layer_cut is not implemented")
+        else:
+            ep = None
+        self.ep = ep
+        for layer in self.layers:
+            layer.ep = ep
+
     def init_states(self, batch: int) -> List[fw.PoolState]:
         """One state for the shared pool, or one per layer for layer-local pools."""
         cfg = self.config
         w0, w1, w2 = self._pool_weights()
         dt = self.compute_dtype()
         e = self.num_experts
+        if self.ep is not None:
+            mine = self.ep.local_experts()
+            return [fw.init_pool_state(w0[mine], w1[mine], w2[mine], batch * self.ep.P, cfg.use_momentum, dt)]
         n_pools = cfg.num_hidden_layers if self.per_layer_pool else 1
         return [fw.init_pool_state(w0[p * e:(p + 1) * e], w1[p * e:(p + 1) * e], w2[p * e:(p + 1) * e], batch,
                                    cfg.use_momentum, dt) for p in range(n_pools)]
@@ -346,7 +365,10 @@ class UTTTMoEModel(nn.Module):
                 counts.append(c)
             mc = None
             if cfg.memory_aggregate_momentum_mode == "pool_mean" and ms:
-                mc = torch.stack(ms, dim=0).mean(dim=0).view(-1, 1, 1, 1)
+                mc = torch.stack(ms, dim=0).mean(dim=0)
+                if self.ep is not None:
+                    mc = self.ep.gather_sequences(mc.reshape(-1))        # the owner updates every sequence of the group
+                mc = mc.view(-1, 1, 1, 1)
             new = fw.apply_pool_update(a02, a1, s, mc, cfg.memory_aggregate_lr_scale, cfg.use_moun, compute_dtype=dt)
             return (*[t for t in new.tensors() if t is not None], torch.stack(probs), torch.stack(counts))
 
@@ -359,7 +381,7 @@ class UTTTMoEModel(nn.Module):
         if mode == "stop_state":
             new = new.detach()
         e = self.num_experts
-        bsz = state.w02.shape[0]
+        bsz = out[n_state].shape[1]
         probs = torch.zeros(n_layers, bsz, e, device=state.w02.device, dtype=torch.float32)
         counts = torch.zeros_like(probs)
         widx = self._writer_index(probs.device)

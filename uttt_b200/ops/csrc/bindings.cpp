@@ -42,6 +42,15 @@ void adamw_scatter(at::Tensor p, at::Tensor g, at::Tensor m, at::Tensor v, std::
                    int64_t rank, int64_t shard_off, bool compute_bf16, double lr, double b1, double b2, double eps,
                    double wd, int64_t step, at::Tensor gscale, at::Tensor apply, int64_t decay_hi);
 std::vector<at::Tensor> swa_fwd(at::Tensor q, at::Tensor k, at::Tensor v, int64_t window, bool causal, double scale);
+std::vector<at::Tensor> ep_plan(at::Tensor sizes_all, int64_t rank, int64_t B, int64_t E, int64_t tiles_cap);
+void ep_push(at::Tensor src, c10::optional<at::Tensor> weights, at::Tensor idx, at::Tensor dest, at::Tensor offsets_local,
+             at::Tensor sizes_local, at::Tensor remote_start, std::vector<int64_t> peer_ptrs, int64_t E,
+             int64_t rows_per_batch);
+at::Tensor ep_pull(std::vector<int64_t> peer_ptrs, c10::optional<at::Tensor> weights, at::Tensor idx, at::Tensor dest,
+                   at::Tensor offsets_local, at::Tensor remote_start, int64_t E, int64_t rows_per_batch, int64_t D,
+                   at::ScalarType dtype);
+at::Tensor ep_pull_dot(at::Tensor local, std::vector<int64_t> peer_ptrs, at::Tensor idx, at::Tensor dest,
+                       at::Tensor offsets_local, at::Tensor remote_start, int64_t E, int64_t rows_per_batch);
 bool pool_step_supported(int64_t D);
 std::vector<at::Tensor> pool_step_fwd(at::Tensor m, at::Tensor d, double lr, int64_t mode);
 std::vector<at::Tensor> pool_step_bwd(at::Tensor m, at::Tensor d, c10::optional<at::Tensor> gn,
@@ -85,6 +94,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("bmm_general", &bmm_general);
   m.def("swa_fwd", &swa_fwd);
   m.def("swa_bwd", &swa_bwd);
+  m.def("ep_plan", &ep_plan);
+  m.def("ep_push", &ep_push);
+  m.def("ep_pull", &ep_pull);
+  m.def("ep_pull_dot", &ep_pull_dot);
   m.def("pool_step_supported", &pool_step_supported);
   m.def("pool_step_fwd", &pool_step_fwd);
   m.def("pool_step_bwd", &pool_step_bwd);

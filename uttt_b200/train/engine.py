@@ -73,6 +73,22 @@ class TrainEngine:
         inner = getattr(self.model, "model", None)
         if inner is not None and hasattr(inner, "activation_checkpoint"):
             inner.activation_checkpoint = self.cfg.activation_checkpoint
+        self.expert_parallel = None
+        ep_size = int(getattr(model_config, "memory_expert_parallel", 1) or 1)
+        if ep_size > 1:
+            import torch.distributed as dist
+            from ..parallel.expert_parallel import ExpertParallel
+            if not dist.is_initialized() or dist.get_world_size() % ep_size != 0:
+                raise ValueError(f"memory_expert_parallel={ep_size} needs a job whose size is a multiple of it")
+            world, rank = dist.get_world_size(), dist.get_rank()
+            mine = None
+            for start in range(0, world, ep_size):           # consecutive ranks share an NVLink domain
+                grp = dist.new_group(list(range(start, start + ep_size)))
+                if start <= rank < start + ep_size:
+                    mine = grp
+            self.expert_parallel = ExpertParallel(mine, device, model_config.memory_num_experts,
+                                                  max_row_bytes=4 * model_config.fw_head_dim)
+            inner.set_expert_parallel(self.expert_parallel)
         opt = AdamWConfig(lr=self.cfg.lr, beta1=self.cfg.beta1, beta2=self.cfg.beta2, eps=self.cfg.eps,
                           weight_decay=self.cfg.weight_decay, max_norm=self.cfg.max_norm,
                           skip_nan_inf=self.cfg.skip_nan_inf)
