@@ -93,7 +93,8 @@ def _run(args) -> None:
     model.train()
     opt = torch.optim.AdamW(model.parameters(), lr=1e-3, betas=(0.9, 0.95), eps=1e-15, weight_decay=0.1, fused=True)
     seq = args.seq_len
-    micro = int(os.environ.get("UTTT_REF_MICRO_BATCH", str(min(args.micro_batch, args.per_gpu_batch))))
+    # two sequences of 32K per micro-batch is what fits comfortably with the reference's activation footprint
+    micro = int(os.environ.get("UTTT_REF_MICRO_BATCH", str(min(2, args.per_gpu_batch))))
     data = SyntheticZipfTokens(cfg.vocab_size, seq, args.per_gpu_batch, seed=1234, rank=rank, world=world)
 
     def step(batch):

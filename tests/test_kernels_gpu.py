@@ -221,7 +221,9 @@ def test_permute_unpermute():
     x = torch.randn(r, 128, device=DEV, dtype=torch.bfloat16, requires_grad=True)
     xp = ops.permute_rows(x, plan)
     xpr = ref.permute_rows(x.detach().float(), plan.dest, plan.rows_padded)
-    _close(xp, xpr, 0, 0)
+    # rows of groups (their zero padding included) are defined; tiles past the last group are never read
+    live = int(plan.offsets[-1])
+    _close(xp[:live], xpr[:live], 0, 0)
     w = torch.rand(r, k, device=DEV, requires_grad=True)
     yp = torch.randn(plan.rows_padded, 128, device=DEV, dtype=torch.bfloat16, requires_grad=True)
     out = ops.unpermute_rows(yp, plan, w)
@@ -232,7 +234,7 @@ def test_permute_unpermute():
     g = torch.randn_like(out)
     gy, gw = torch.autograd.grad(out, [yp, w], g)
     gyr, gwr = torch.autograd.grad(outr, [ypr, wr], g.float())
-    _close(gy, gyr, 2e-2, 2e-2)
+    _close(gy[:live], gyr[:live], 2e-2, 2e-2)
     _close(gw, gwr, 0.15, 3e-2)
     (gx,) = torch.autograd.grad(xp, x, torch.ones_like(xp))
     _close(gx, torch.full_like(gx, float(k)), 0, 0)
@@ -243,7 +245,7 @@ def test_permute_unpermute():
     w2r = w2.detach().clone().requires_grad_(True)
     scaled = (xr.unsqueeze(1) * w2r.unsqueeze(-1)).reshape(-1, 128)
     xsr = torch.zeros(plan.rows_padded, 128, device=DEV).index_copy(0, plan.dest.reshape(-1), scaled)
-    _close(xs, xsr, 2e-2, 2e-2)
+    _close(xs[:live], xsr[:live], 2e-2, 2e-2)
     c = torch.randn_like(xs)
     ga, gb = torch.autograd.grad(xs, [x, w2], c)
     gar, gbr = torch.autograd.grad(xsr, [xr, w2r], c.float())

@@ -17,9 +17,11 @@ at::Tensor swiglu_bwd(at::Tensor dh, at::Tensor y02);
 std::vector<at::Tensor> swiglu_bwd_bwd(at::Tensor G, at::Tensor dh, at::Tensor y02);
 std::vector<at::Tensor> fw_write_pw_fwd(at::Tensor y02, at::Tensor dh, at::Tensor lr);
 std::vector<at::Tensor> fw_write_pw_bwd(at::Tensor C, at::Tensor Ch, at::Tensor y02, at::Tensor dh, at::Tensor lr);
-at::Tensor permute_rows(at::Tensor x, at::Tensor dest, int64_t rows_padded, c10::optional<at::Tensor> w);
+at::Tensor permute_rows(at::Tensor x, at::Tensor dest, int64_t rows_padded, c10::optional<at::Tensor> w,
+                        c10::optional<at::Tensor> offsets, c10::optional<at::Tensor> sizes);
 at::Tensor unpermute_rows(at::Tensor y, at::Tensor dest, c10::optional<at::Tensor> w);
-std::vector<at::Tensor> unpermute_rows_bwd(at::Tensor dout, at::Tensor y, at::Tensor dest, at::Tensor w);
+std::vector<at::Tensor> unpermute_rows_bwd(at::Tensor dout, at::Tensor y, at::Tensor dest, at::Tensor w,
+                                           c10::optional<at::Tensor> offsets, c10::optional<at::Tensor> sizes);
 void sumsq_accum(at::Tensor g, double scale, at::Tensor out);
 void adamw_flat(at::Tensor p, at::Tensor g, at::Tensor m, at::Tensor v, c10::optional<at::Tensor> plow, double lr,
                 double b1, double b2, double eps, double wd, int64_t step, at::Tensor gscale, at::Tensor apply,
@@ -77,9 +79,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("swiglu_bwd_bwd", &swiglu_bwd_bwd);
   m.def("fw_write_pw_fwd", &fw_write_pw_fwd);
   m.def("fw_write_pw_bwd", &fw_write_pw_bwd);
-  m.def("permute_rows", &permute_rows);
+  m.def("permute_rows", &permute_rows, py::arg("x"), py::arg("dest"), py::arg("rows_padded"), py::arg("w"),
+        py::arg("offsets") = py::none(), py::arg("sizes") = py::none());
   m.def("unpermute_rows", &unpermute_rows);
-  m.def("unpermute_rows_bwd", &unpermute_rows_bwd);
+  m.def("unpermute_rows_bwd", &unpermute_rows_bwd, py::arg("dout"), py::arg("y"), py::arg("dest"), py::arg("w"),
+        py::arg("offsets") = py::none(), py::arg("sizes") = py::none());
   m.def("sumsq_accum", &sumsq_accum);
   m.def("adamw_flat", &adamw_flat);
   m.def("ce_fwd_bwd_", &ce_fwd_bwd_);

@@ -741,12 +741,44 @@ __global__ void unpermute_rows_bwd_kernel(const T* __restrict__ dout, const T* _
   }
 }
 
-at::Tensor permute_rows(at::Tensor x, at::Tensor dest, int64_t rows_padded, c10::optional<at::Tensor> w) {
+// Zero rows [offsets[g] + sizes[g], offsets[g + 1]) of every group: the tile padding that token reductions read.
+__global__ void zero_pad_rows_kernel(uint4* __restrict__ out, const int* __restrict__ offsets,
+                                     const int* __restrict__ sizes, int groups, int vec_per_row) {
+  const int lane = threadIdx.x & 31;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  for (int g = warp; g < groups; g += nwarps) {
+    const int begin = offsets[g] + sizes[g], end = offsets[g + 1];
+    for (int r = begin; r < end; ++r)
+      for (int v = lane; v < vec_per_row; v += 32) out[(size_t)r * vec_per_row + v] = make_uint4(0, 0, 0, 0);
+  }
+}
+
+// A [rows_padded, d] buffer for a scatter into the tile-padded layout.  With the layout's offsets / sizes only
+// the padding rows inside groups are cleared (rows of tiles past the last group are never read); without them the
+// whole buffer is zero-filled.
+static at::Tensor padded_buffer(int64_t rows_padded, int d, const at::TensorOptions& opt,
+                                const c10::optional<at::Tensor>& offsets, const c10::optional<at::Tensor>& sizes) {
+  if (!(offsets.has_value() && offsets->defined() && sizes.has_value() && sizes->defined()))
+    return at::zeros({rows_padded, d}, opt);
+  auto out = at::empty({rows_padded, d}, opt);
+  TORCH_CHECK(offsets->scalar_type() == at::kInt && sizes->scalar_type() == at::kInt &&
+              offsets->numel() == sizes->numel() + 1 && (d * out.element_size()) % 16 == 0);
+  int groups = sizes->numel();
+  zero_pad_rows_kernel<<<std::max(1, (groups + 7) / 8), 256, 0, cur_stream()>>>(
+      reinterpret_cast<uint4*>(out.data_ptr()), offsets->data_ptr<int>(), sizes->data_ptr<int>(), groups,
+      (int)(d * out.element_size() / 16));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return out;
+}
+
+at::Tensor permute_rows(at::Tensor x, at::Tensor dest, int64_t rows_padded, c10::optional<at::Tensor> w,
+                        c10::optional<at::Tensor> offsets, c10::optional<at::Tensor> sizes) {
   c10::cuda::CUDAGuard guard(x.device());
   int d = x.size(1);
   int k = dest.size(1);
   TORCH_CHECK(x.is_contiguous() && dest.is_contiguous() && dest.scalar_type() == at::kLong && d % 8 == 0);
-  auto out = at::zeros({rows_padded, d}, x.options());
+  auto out = padded_buffer(rows_padded, d, x.options(), offsets, sizes);
   size_t n = (size_t)dest.numel();
   at::Tensor wf;
   if (w.has_value() && w->defined()) wf = w->to(at::kFloat).contiguous();
@@ -779,13 +811,14 @@ at::Tensor unpermute_rows(at::Tensor y, at::Tensor dest, c10::optional<at::Tenso
   return out;
 }
 
-std::vector<at::Tensor> unpermute_rows_bwd(at::Tensor dout, at::Tensor y, at::Tensor dest, at::Tensor w) {
+std::vector<at::Tensor> unpermute_rows_bwd(at::Tensor dout, at::Tensor y, at::Tensor dest, at::Tensor w,
+                                           c10::optional<at::Tensor> offsets, c10::optional<at::Tensor> sizes) {
   c10::cuda::CUDAGuard guard(y.device());
   int d = y.size(1);
   int k = dest.size(1);
   size_t n = (size_t)dest.numel();
   auto wf = w.to(at::kFloat).contiguous();
-  auto dy = at::zeros_like(y);
+  auto dy = padded_buffer(y.size(0), d, y.options(), offsets, sizes);
   auto dw = at::empty({dest.size(0), k}, y.options().dtype(at::kFloat));
   int blocks = (int)std::max<size_t>(1, std::min<size_t>((n + 7) / 8, (size_t)sm_count() * 16));
   UTTT_DISPATCH_FLOAT(y, {

@@ -484,50 +484,59 @@ def route_softmax_topk(rows, router, bias, topk: int, alpha: float = 1.0, bias_i
     return idx, (picked * alpha).view(bsz * n, topk), probs.sum(dim=1)
 
 
+def _pad_layout(offsets, sizes):
+    """(offsets, sizes) as the int32 pair the scatter kernels use to clear only the padding rows, or (None, None)."""
+    if offsets is None or sizes is None or offsets.dtype != torch.int32 or not offsets.is_cuda:
+        return None, None
+    return offsets, (sizes if sizes.dtype == torch.int32 else sizes.to(torch.int32))
+
+
 class _Permute(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, dest, rows_padded, weights):
+    def forward(ctx, x, dest, rows_padded, weights, offsets=None, sizes=None):
         ext = cuda_ext(x)
         x = x.contiguous()
-        ctx.save_for_backward(dest, weights, x if weights is not None else None)
-        return ext.permute_rows(x, dest, int(rows_padded), weights)
+        offsets, sizes = _pad_layout(offsets, sizes)
+        ctx.save_for_backward(dest, weights, x if weights is not None else None, offsets, sizes)
+        return ext.permute_rows(x, dest, int(rows_padded), weights, offsets, sizes)
 
     @staticmethod
     def backward(ctx, dout):
-        dest, weights, x = ctx.saved_tensors
+        dest, weights, x, offsets, sizes = ctx.saved_tensors
         if weights is None:
-            return _Unpermute.apply(dout, dest, None), None, None, None
+            return _Unpermute.apply(dout, dest, None, offsets, sizes), None, None, None, None, None
         ext = cuda_ext(dout)
         dout = dout.contiguous()
         dx = ext.unpermute_rows(dout, dest, weights)
-        # dw[i, j] = <x[i], dout[dest[i, j]]>
-        _, dw = ext.unpermute_rows_bwd(x, dout, dest, weights)
-        return dx, None, None, dw.to(weights.dtype)
+        # dw[i, j] = <x[i], dout[dest[i, j]]>  (the scattered gradient this call also produces is not needed)
+        _, dw = ext.unpermute_rows_bwd(x, dout, dest, weights, offsets, sizes)
+        return dx, None, None, dw.to(weights.dtype), None, None
 
 
 class _Unpermute(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, y, dest, weights):
+    def forward(ctx, y, dest, weights, offsets=None, sizes=None):
         ext = cuda_ext(y)
-        ctx.save_for_backward(y, dest, weights)
+        offsets, sizes = _pad_layout(offsets, sizes)
+        ctx.save_for_backward(y, dest, weights, offsets, sizes)
         ctx.rows = y.shape[0]
         return ext.unpermute_rows(y.contiguous(), dest, weights)
 
     @staticmethod
     def backward(ctx, dout):
-        y, dest, weights = ctx.saved_tensors
+        y, dest, weights, offsets, sizes = ctx.saved_tensors
         if weights is None:
-            return _Permute.apply(dout, dest, ctx.rows, None), None, None
+            return _Permute.apply(dout, dest, ctx.rows, None, offsets, sizes), None, None, None, None
         ext = cuda_ext(y)
-        dy, dw = ext.unpermute_rows_bwd(dout.contiguous(), y, dest, weights)
-        return dy, None, dw.to(weights.dtype)
+        dy, dw = ext.unpermute_rows_bwd(dout.contiguous(), y, dest, weights, offsets, sizes)
+        return dy, None, dw.to(weights.dtype), None, None
 
 
 def permute_rows(x: torch.Tensor, plan: GroupPlan, weights: Optional[torch.Tensor] = None) -> torch.Tensor:
     """[R, D] token-major rows -> [rows_padded, D] expert-major (each row copied to its top-k groups,
     copy j scaled by ``weights[i, j]`` when given)."""
     if _kernel("permute_rows", x) is not None and x.shape[-1] % 8 == 0:
-        return _Permute.apply(x, plan.dest, plan.rows_padded, weights)
+        return _Permute.apply(x, plan.dest, plan.rows_padded, weights, plan.offsets, plan.sizes)
     if weights is None:
         return ref.permute_rows(x, plan.dest, plan.rows_padded)
     k = plan.dest.shape[1]
@@ -539,7 +548,7 @@ def permute_rows(x: torch.Tensor, plan: GroupPlan, weights: Optional[torch.Tenso
 def unpermute_rows(y: torch.Tensor, plan: GroupPlan, weights: Optional[torch.Tensor]) -> torch.Tensor:
     """Expert-major rows back to token-major, summing the top-k copies with ``weights`` [R, k]."""
     if _kernel("unpermute_rows", y) is not None and y.shape[-1] % 8 == 0:
-        return _Unpermute.apply(y, plan.dest, weights)
+        return _Unpermute.apply(y, plan.dest, weights, plan.offsets, plan.sizes)
     return ref.unpermute_rows(y, plan.dest, weights)
 
 

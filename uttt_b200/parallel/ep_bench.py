@@ -1,0 +1,87 @@
+"""Expert-parallel dispatch / combine micro-benchmark (one process per GPU).
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        -m uttt_b200.parallel.ep_bench [--batch 4] [--rows 8192] [--dim 384] [--experts 32] [--topk 2]
+
+Times, with CUDA events on the device and the maximum over ranks: the fused peer-memory path (``ep_push`` /
+``ep_pull`` kernels, including their ordering collectives and staging copies) and the all-to-all baseline (local
+permute + ``all_to_all_single`` + local un-permute) on the same routing.  Prints one JSON line on rank 0 with the
+bytes that cross NVLink per rank and the fraction of the measured 770 GB/s per-direction peer copy bandwidth.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+from ..ops import functional as F_ops
+from .expert_parallel import ExpertParallel
+
+
+def _time(fn, iters, flush):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        flush.zero_()
+        dist.barrier()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        total += s.elapsed_time(e)
+    t = torch.tensor([total / iters], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--batch", type=int, default=4)
+    ap.add_argument("--rows", type=int, default=8192, help="rows per sequence (tokens x fast-weight heads)")
+    ap.add_argument("--dim", type=int, default=384)
+    ap.add_argument("--experts", type=int, default=32)
+    ap.add_argument("--topk", type=int, default=2)
+    ap.add_argument("--iters", type=int, default=10)
+    args = ap.parse_args()
+    rank = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", device_id=dev)
+    world = dist.get_world_size()
+    torch.manual_seed(7 + dist.get_rank())
+    b, n, d, e, k = args.batch, args.rows, args.dim, args.experts, args.topk
+    idx = torch.rand(b, n, e, device=dev).topk(k, dim=-1).indices
+    plan = F_ops.build_group_plan(idx, e)
+    rows = torch.randn(b * n, d, device=dev, dtype=torch.bfloat16)
+    w = torch.rand(b * n, k, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    out = {"n_gpus": world, "rows_per_rank": b * n, "dim": d, "experts": e, "topk": k}
+    remote_frac = (world - 1) / world
+    nvlink_bytes = b * n * k * d * 2 * remote_frac
+    for name in ("peer", "a2a"):
+        ep = ExpertParallel(None, dev, e, transport=name, max_row_bytes=4 * d)
+        eplan = ep.plan(plan, idx)
+        with torch.no_grad():
+            xp = ep.dispatch(rows, None, eplan)
+            t_plan = _time(lambda: ep.plan(plan, idx), args.iters, flush)
+            t_disp = _time(lambda: ep.dispatch(rows, None, eplan), args.iters, flush)
+            t_comb = _time(lambda: ep.combine(xp, w, eplan), args.iters, flush)
+        out[name] = {"plan_ms": round(t_plan, 4), "dispatch_ms": round(t_disp, 4), "combine_ms": round(t_comb, 4),
+                     "dispatch_gbs_per_rank": round(nvlink_bytes / t_disp / 1e6, 1),
+                     "combine_gbs_per_rank": round(nvlink_bytes / t_comb / 1e6, 1),
+                     "dispatch_frac_of_measured_peer_copy": round(nvlink_bytes / t_disp / 1e6 / 770.0, 3),
+                     "combine_frac_of_measured_peer_copy": round(nvlink_bytes / t_comb / 1e6 / 770.0, 3)}
+    if dist.get_rank() == 0:
+        print(json.dumps(out), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

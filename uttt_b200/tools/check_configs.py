@@ -92,9 +92,22 @@ def check_all(root: str = ROOT) -> Tuple[int, List[str]]:
         errs += check_job_toml(path)
         n += 1
     for path in sorted(glob.glob(os.path.join(root, "nvs", "**", "*.yaml"), recursive=True)):
-        errs += check_nvs_yaml(path)
+        if os.sep + "eval" + os.sep in path:
+            errs += check_eval_registry(path)
+        else:
+            errs += check_nvs_yaml(path)
         n += 1
     return n, errs
+
+
+def check_eval_registry(path: str) -> List[str]:
+    """Every entry of an evaluation registry names a known dataset and a configuration file that exists."""
+    from ..nvs.eval.registry import load_registry
+    try:
+        reg = load_registry(path)
+    except Exception as exc:
+        return [f"{path}: {exc}"]
+    return [f"{path}: {e.name}: config {e.config} not found" for e in reg.values() if not e.config.is_file()]
 
 
 def catalog(root: str = ROOT) -> str:
@@ -105,6 +118,10 @@ def catalog(root: str = ROOT) -> str:
             c = load_config(path)
             extra = f", E={c.memory_num_experts} top-{c.memory_num_active_experts}" if hasattr(c, "memory_num_experts") else ""
             lines.append(f"| {rel} | lm:{c.model_type} | d={c.hidden_size} L={c.num_hidden_layers} chunk={c.chunk_size}{extra} |")
+        elif path.endswith(".yaml") and os.sep + "eval" + os.sep in path:
+            with open(path) as fh:
+                c = yaml.safe_load(fh)
+            lines.append(f"| {rel} | nvs-eval | registry of {len(c.get('experiments', []))} evaluations |")
         elif path.endswith(".yaml"):
             with open(path) as fh:
                 c = yaml.safe_load(fh)

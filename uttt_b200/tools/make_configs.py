@@ -210,6 +210,31 @@ def main() -> None:
         os.makedirs(os.path.dirname(path), exist_ok=True)
         with open(path, "w") as fh:
             yaml.safe_dump(cfg, fh, sort_keys=False)
+    # evaluation registries: one entry per released view-synthesis configuration and test domain
+    domains = {"obj": "gso", "dl3dv": "dl3dv"}
+    steps = {"gso": 24476, "dl3dv": 20046}
+    datasets = {"gso": {"manifest": "/PATH/TO/MANIFESTS/gso_v0.1_instant3d_test_localssd.txt",
+                        "view_manifest": "/PATH/TO/MANIFESTS/gso_views_24_seed9595.json", "image_size": 256,
+                        "num_scenes": 1019},
+                "dl3dv": {"manifest": "/PATH/TO/MANIFESTS/dl3dv10k_benchmark_local.txt",
+                          "view_manifest": "/PATH/TO/MANIFESTS/dl3dv_views_24_seed9595.json", "image_size": 256,
+                          "num_scenes": 140}}
+    main_entries, tr_entries = [], []
+    for rel, cfg in sorted(nvs_configs().items()):
+        parts = rel.split("/")
+        if len(parts) != 3 or parts[1] not in domains or parts[0] in ("scale", "schedule"):
+            continue
+        ds = domains[parts[1]]
+        entry = {"name": f"{ds}/{parts[2]}", "dataset": ds, "config": f"configs/nvs/{rel}.yaml",
+                 "checkpoint": f"{ds}/{parts[2]}/ckpt_{steps[ds]:016d}.pt", "paper_model": parts[2],
+                 "display_name": parts[2].replace("_", "-"), "checkpoint_impl": parts[2].split("_e")[0], "v_gap": None}
+        (tr_entries if parts[0] == "transformer" else main_entries).append(entry)
+    defaults = {"checkpoint_root": "/PATH/TO/CHECKPOINTS", "output_root": "eval_outputs", "num_views": 24,
+                "view_seed": 9595}
+    os.makedirs(os.path.join(ROOT, "nvs", "eval"), exist_ok=True)
+    for fname, entries in (("experiments.yaml", main_entries), ("experiments_transformer.yaml", tr_entries)):
+        with open(os.path.join(ROOT, "nvs", "eval", fname), "w") as fh:
+            yaml.safe_dump({"defaults": defaults, "datasets": datasets, "experiments": entries}, fh, sort_keys=False)
     print(f"wrote configs under {ROOT}")
 
 
