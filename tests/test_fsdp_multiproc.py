@@ -93,3 +93,53 @@ def test_two_gpu_ranks_fused_kernels_match_single_gpu(tmp_path):
             worst = max(worst, err)
             assert err < 3e-2, (k, err)      # bf16 parameters after two lr=1e-2 steps
     assert all(l == l for l in got["losses"])
+
+
+def _ag_worker(rank: int, world: int, port: int, out_path: str):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from uttt_b200.ops._ext import load
+    from uttt_b200.parallel.ag_linear import ShardedWeightLinear
+    from uttt_b200.parallel.symm import SymmetricHeap
+    n, k, m = 1024, 384, 512
+    heap = SymmetricHeap(dev, None, capacity_bytes=n * k * 2 + (1 << 20))
+    layer = ShardedWeightLinear(heap, k, n, gather_ctas=8)
+    g = torch.Generator(device="cpu").manual_seed(5)
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).to(dev)
+    layer.load_full_weight(w)
+    torch.manual_seed(10 + rank)
+    x = torch.randn(m, k, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    ok = True
+    for _ in range(2):                                   # the second call re-gathers over the first call's copies
+        y = layer(x)
+        want = x.detach().float() @ w.bfloat16().float().t()
+        ok = ok and bool(torch.allclose(y.float(), want, atol=3e-2, rtol=3e-2))
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    dx_want = gy.float() @ w.bfloat16().float()
+    ok = ok and bool(torch.allclose(x.grad.float(), dx_want, atol=5e-2, rtol=5e-2))
+    dw = gy.float().t() @ x.detach().float()
+    dist.all_reduce(dw)
+    rows = n // world
+    ok = ok and bool(torch.allclose(layer.shard.grad.float(), dw[rank * rows:(rank + 1) * rows], atol=0.3, rtol=5e-2))
+    status = int(load().gemm_status(x)[0])
+    flag = torch.tensor([1.0 if (ok and status == 0) else 0.0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        torch.save({"ok": bool(flag.item() == 1.0), "status": status}, out_path)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+def test_two_gpu_all_gather_fused_gemm(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    out = str(tmp_path / "ag.pt")
+    mp.spawn(_ag_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    got = torch.load(out, weights_only=False)
+    assert got["status"] == 0 and got["ok"]

@@ -82,3 +82,53 @@ def summarize(per_position: List[Optional[float]], start: int = 30000) -> Dict[s
     allv = [v for v in per_position if v is not None and not math.isnan(v)]
     return {"ptl_tail_mean": sum(vals) / len(vals) if vals else float("nan"), "tail_positions": len(vals),
             "mean_all": sum(allv) / len(allv) if allv else float("nan"), "start": start}
+
+
+def main(argv=None):
+    """``python -m uttt_b200.eval.ptl --config CFG.json [--checkpoint HF_DIR] [--seq-len 32768] [--batch-size 1]
+    [--max-batches 64] [--ptl-start 30000] [--data-files F ...] [--output out.json]``"""
+    import argparse
+    import json
+    from ..config import load_config
+    from ..models import build_model
+    from ..train.data import build_dataloader
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", required=True)
+    ap.add_argument("--checkpoint", default="", help="HF-style folder written by export_hf / dcp-to-hf")
+    ap.add_argument("--seq-len", type=int, default=32768)
+    ap.add_argument("--batch-size", type=int, default=1)
+    ap.add_argument("--max-batches", type=int, default=64)
+    ap.add_argument("--ptl-start", type=int, default=30000)
+    ap.add_argument("--data-files", nargs="*", default=None)
+    ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
+    ap.add_argument("--output", default="")
+    args = ap.parse_args(argv)
+    cfg = load_config(args.checkpoint if args.checkpoint else args.config)
+    model = build_model(cfg)
+    if args.checkpoint:
+        import os
+        st = os.path.join(args.checkpoint, "model.safetensors")
+        if os.path.exists(st):
+            from safetensors.torch import load_file
+            sd = load_file(st)
+        else:
+            sd = torch.load(os.path.join(args.checkpoint, "pytorch_model.bin"), map_location="cpu")
+        model.load_state_dict(sd, strict=False)
+    model = model.to(args.device)
+    if args.device.startswith("cuda"):
+        model = model.bfloat16()
+    loader = build_dataloader("synthetic" if not args.data_files else "files", vocab_size=cfg.vocab_size,
+                              seq_len=args.seq_len, batch_size=args.batch_size, rank=0, world=1, seed=0,
+                              data_files=args.data_files)
+    tracker = evaluate(model, loader, args.seq_len, args.max_batches, torch.device(args.device))
+    mean = tracker.mean().tolist()
+    per_position = [None if math.isnan(x) else x for x in mean]
+    summary = summarize(per_position, min(args.ptl_start, max(args.seq_len - 1, 0)))
+    print(json.dumps(summary, sort_keys=True))
+    if args.output:
+        with open(args.output, "w") as fh:
+            fh.write(tracker.to_json())
+
+
+if __name__ == "__main__":
+    main()

@@ -56,3 +56,51 @@ def merge_shards(results: List[Dict[str, float]]) -> Dict[str, float]:
     hits, total = sum(r["hits"] for r in results), sum(r["total"] for r in results)
     return {"task": results[0]["task"], "length": results[0]["length"], "hits": hits, "total": total,
             "accuracy": hits / max(total, 1), "shards": len(results)}
+
+
+def main(argv=None):
+    """``python -m uttt_b200.eval.ruler --config CFG.json [--checkpoint HF_DIR] [--length 4096] [--num-samples 8]
+    [--shard I --num-shards S] [--output shard.json]`` or ``--merge a.json b.json ...``"""
+    import argparse
+    import json
+    import os
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", default="")
+    ap.add_argument("--checkpoint", default="")
+    ap.add_argument("--length", type=int, default=4096)
+    ap.add_argument("--num-samples", type=int, default=8)
+    ap.add_argument("--num-needles", type=int, default=4)
+    ap.add_argument("--value-len", type=int, default=4)
+    ap.add_argument("--shard", type=int, default=0)
+    ap.add_argument("--num-shards", type=int, default=1)
+    ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
+    ap.add_argument("--output", default="")
+    ap.add_argument("--merge", nargs="*", default=None, help="merge shard result files instead of running")
+    args = ap.parse_args(argv)
+    if args.merge:
+        results = [json.load(open(f)) for f in args.merge]
+        print(json.dumps(merge_shards(results), sort_keys=True))
+        return
+    from ..config import load_config
+    from ..models import build_model
+    cfg = load_config(args.checkpoint if args.checkpoint else args.config)
+    model = build_model(cfg)
+    if args.checkpoint:
+        st = os.path.join(args.checkpoint, "model.safetensors")
+        if os.path.exists(st):
+            from safetensors.torch import load_file
+            sd = load_file(st)
+        else:
+            sd = torch.load(os.path.join(args.checkpoint, "pytorch_model.bin"), map_location="cpu")
+        model.load_state_dict(sd, strict=False)
+    model = model.to(args.device).eval()
+    res = run_niah(model, cfg.vocab_size, args.length, args.num_samples, args.num_needles, args.value_len, args.shard,
+                   args.num_shards, torch.device(args.device))
+    print(json.dumps(res, sort_keys=True))
+    if args.output:
+        with open(args.output, "w") as fh:
+            json.dump(res, fh)
+
+
+if __name__ == "__main__":
+    main()

@@ -229,3 +229,52 @@ class ResumableDistributedSampler(DistributedSampler):
 
     def __len__(self) -> int:
         return max(self.num_samples - self._skip, 0)
+
+
+def main(argv=None):
+    """``python -m uttt_b200.nvs.data make-toy --output DIR [--num-scenes 4] [--num-frames 16] [--image-size 64]``
+    ``python -m uttt_b200.nvs.data check-manifest MANIFEST``
+    ``python -m uttt_b200.nvs.data build-manifest --root DIR --output manifest.txt [--pattern "**/cameras.json"]``"""
+    import argparse
+    import glob
+    import sys
+    ap = argparse.ArgumentParser()
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    a = sub.add_parser("make-toy")
+    a.add_argument("--output", required=True)
+    a.add_argument("--num-scenes", type=int, default=4)
+    a.add_argument("--num-frames", type=int, default=16)
+    a.add_argument("--image-size", type=int, default=64)
+    a.add_argument("--seed", type=int, default=0)
+    b = sub.add_parser("check-manifest")
+    b.add_argument("manifest")
+    c = sub.add_parser("build-manifest")
+    c.add_argument("--root", required=True)
+    c.add_argument("--output", required=True)
+    c.add_argument("--pattern", default="**/*.json")
+    args = ap.parse_args(argv)
+    if args.cmd == "make-toy":
+        print(make_toy_dataset(args.output, args.num_scenes, args.num_frames, args.image_size, args.seed))
+    elif args.cmd == "check-manifest":
+        problems = check_manifest(args.manifest)
+        for p in problems:
+            print("ERROR", p)
+        print(f"{len(problems)} problem(s)")
+        sys.exit(1 if problems else 0)
+    else:
+        paths = sorted(os.path.abspath(p) for p in glob.glob(os.path.join(args.root, args.pattern), recursive=True))
+        keep = []
+        for p in paths:
+            try:
+                with open(p) as fh:
+                    if "frames" in json.load(fh):
+                        keep.append(p)
+            except Exception:
+                continue
+        with open(args.output, "w") as fh:
+            fh.write("\n".join(keep) + "\n")
+        print(f"{len(keep)} scenes -> {args.output}")
+
+
+if __name__ == "__main__":
+    main()

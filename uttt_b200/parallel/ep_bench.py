@@ -1,4 +1,5 @@
-"""Expert-parallel dispatch / combine micro-benchmark (one process per GPU).
+"""Micro-benchmark of the fused compute + collective kernels (one process per GPU): expert-parallel dispatch /
+combine and the all-gather-fused GEMM.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
         -m uttt_b200.parallel.ep_bench [--batch 4] [--rows 8192] [--dim 384] [--experts 32] [--topk 2]
@@ -48,6 +49,7 @@ def main():
     ap.add_argument("--experts", type=int, default=32)
     ap.add_argument("--topk", type=int, default=2)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--gather-ctas", type=int, default=24)
     args = ap.parse_args()
     rank = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(rank)
@@ -77,6 +79,31 @@ def main():
                      "combine_gbs_per_rank": round(nvlink_bytes / t_comb / 1e6, 1),
                      "dispatch_frac_of_measured_peer_copy": round(nvlink_bytes / t_disp / 1e6 / 770.0, 3),
                      "combine_frac_of_measured_peer_copy": round(nvlink_bytes / t_comb / 1e6 / 770.0, 3)}
+    # all-gather fused into the GEMM (weight rows sharded over the ranks) against all-gather + library GEMM
+    from .ag_linear import ShardedWeightLinear
+    from .symm import SymmetricHeap
+    m_rows, k_in, n_out = 8192, 1536, 4096
+    if n_out % (256 * world) == 0:
+        heap = SymmetricHeap(dev, None, capacity_bytes=n_out * k_in * 2 + (1 << 20))
+        layer = ShardedWeightLinear(heap, k_in, n_out, gather_ctas=args.gather_ctas)
+        layer.load_full_weight(torch.randn(n_out, k_in, device=dev) / k_in ** 0.5)
+        x = torch.randn(m_rows, k_in, device=dev, dtype=torch.bfloat16)
+        full = torch.empty(n_out, k_in, device=dev, dtype=torch.bfloat16)
+        shard = layer.shard.detach().clone()
+
+        def baseline():
+            dist.all_gather_into_tensor(full, shard)
+            return x @ full.t()
+
+        with torch.no_grad():
+            t_fused = _time(lambda: layer(x), args.iters, flush)
+            t_base = _time(baseline, args.iters, flush)
+            t_gemm = _time(lambda: x @ full.t(), args.iters, flush)
+        flops = 2.0 * m_rows * k_in * n_out
+        out["ag_gemm"] = {"M": m_rows, "K": k_in, "N": n_out, "fused_ms": round(t_fused, 4),
+                          "allgather_then_gemm_ms": round(t_base, 4), "library_gemm_only_ms": round(t_gemm, 4),
+                          "fused_tflops": round(flops / t_fused / 1e9, 1),
+                          "remote_bytes": int(n_out * k_in * 2 * remote_frac)}
     if dist.get_rank() == 0:
         print(json.dumps(out), flush=True)
     dist.barrier()

@@ -83,3 +83,42 @@ def preprocess(files: Iterable[str], out_dir: str, tokenize: Callable[[str], Lis
                     flush()
     flush()
     return shards
+
+
+def main(argv=None):
+    """``python -m uttt_b200.utils.convert dcp-to-hf --checkpoint DIR --config CFG.json --output OUT``
+    ``python -m uttt_b200.utils.convert hf-to-dcp --hf-dir DIR --dump-folder RUN``
+    ``python -m uttt_b200.utils.convert preprocess --files a.txt b.jsonl --output DIR --tokenizer TOK_DIR``"""
+    import argparse
+    ap = argparse.ArgumentParser()
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    a = sub.add_parser("dcp-to-hf")
+    a.add_argument("--checkpoint", required=True)
+    a.add_argument("--config", required=True)
+    a.add_argument("--output", required=True)
+    a.add_argument("--tokenizer", default=None)
+    b = sub.add_parser("hf-to-dcp")
+    b.add_argument("--hf-dir", required=True)
+    b.add_argument("--dump-folder", required=True)
+    c = sub.add_parser("preprocess")
+    c.add_argument("--files", nargs="+", required=True)
+    c.add_argument("--output", required=True)
+    c.add_argument("--tokenizer", default="", help="folder of a HF tokenizer; bytes are used when empty")
+    c.add_argument("--shard-docs", type=int, default=1000)
+    args = ap.parse_args(argv)
+    if args.cmd == "dcp-to-hf":
+        print(dcp_to_hf(args.checkpoint, args.config, args.output, args.tokenizer))
+    elif args.cmd == "hf-to-dcp":
+        print(hf_to_dcp(args.hf_dir, args.dump_folder))
+    else:
+        if args.tokenizer:
+            from transformers import AutoTokenizer
+            tok = AutoTokenizer.from_pretrained(args.tokenizer)
+            tokenize, eos = (lambda t: tok(t)["input_ids"]), tok.eos_token_id
+        else:
+            tokenize, eos = (lambda t: list(t.encode("utf-8"))), 0
+        print("\n".join(preprocess(args.files, args.output, tokenize, args.shard_docs, eos)))
+
+
+if __name__ == "__main__":
+    main()
