@@ -446,6 +446,28 @@ def test_swa_attention_forward_backward(hd, lq, lk, window, causal):
     _close(gv, gvr, 5e-2, 5e-2, "dv")
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_patch_decode_matches_reference(dtype):
+    _ext()
+    torch.manual_seed(23)
+    b, v, h, w, p = 2, 3, 32, 48, 8
+    t = (h // p) * (w // p)
+    y = torch.randn(b, v * t, p * p * 3, device=DEV).to(dtype).requires_grad_(True)
+    target = torch.rand(b, v, 3, h, w, device=DEV)
+    r, sse = ops.patch_decode(y, target, v, h, w, p)
+    yr = y.detach().float().requires_grad_(True)
+    rr = torch.sigmoid(yr).view(b, v, h // p, w // p, p, p, 3).permute(0, 1, 6, 2, 4, 3, 5).reshape(b, v, 3, h, w)
+    sser = ((rr - target) ** 2).sum(dim=(2, 3, 4))
+    _close(r, rr, 1e-5, 1e-5, "rendering")
+    _close(sse, sser, 1e-2, 1e-4, "sse")
+    gr = torch.randn_like(r)
+    gs = torch.randn_like(sse)
+    (g,) = torch.autograd.grad([r, sse], y, [gr, gs])
+    (gref,) = torch.autograd.grad([rr, sser], yr, [gr, gs])
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+    _close(g, gref, tol, tol, "dy")
+
+
 def test_plucker_embed():
     _ext()
     from uttt_b200.nvs.data import SyntheticScenes

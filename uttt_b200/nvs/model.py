@@ -145,17 +145,20 @@ class LVSMModel(nn.Module):
         # only the supervised slots are decoded to pixels
         xs = x.view(b, views, n_tok, self.dim).index_select(1, sup).reshape(b, -1, self.dim)
         y = ops.layer_norm(xs, self.image_token_decoder[0].weight, None, 1e-5)
-        y = torch.sigmoid(self.image_token_decoder[1](y).float())
-        rendering = self.unpatchify(y, sup.numel())
+        logits = self.image_token_decoder[1](y)
         tgt = targets.float()
-        mse = F.mse_loss(rendering, tgt)
+        # un-patchify + sigmoid + squared-error sums per view in one pass
+        rendering, sse = ops.patch_decode(logits, tgt, sup.numel(), self.image_size[0], self.image_size[1],
+                                          self.patch_size)
+        pixels = 3 * self.image_size[0] * self.image_size[1]
+        mse = sse.sum() / (sse.numel() * pixels)
         loss = mse + lb_loss
         perceptual = rendering.new_zeros(())
         if self.perceptual is not None:
             perceptual = self.perceptual(rendering.flatten(0, 1), tgt.flatten(0, 1))
             loss = loss + self.perceptual_weight * perceptual
         with torch.no_grad():
-            per_view = ((rendering - tgt) ** 2).mean(dim=(2, 3, 4))
+            per_view = sse.detach() / pixels
             psnr_loc = (-10.0 * torch.log10(per_view.clamp_min(1e-10))).mean(0)
             psnr = psnr_loc.mean()
         metrics = {"loss": loss, "l2_loss": mse.detach(), "lb_loss": lb_loss.detach(), "psnr": psnr,

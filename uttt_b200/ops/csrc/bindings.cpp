@@ -44,6 +44,10 @@ void adamw_scatter(at::Tensor p, at::Tensor g, at::Tensor m, at::Tensor v, std::
                    int64_t rank, int64_t shard_off, bool compute_bf16, double lr, double b1, double b2, double eps,
                    double wd, int64_t step, at::Tensor gscale, at::Tensor apply, int64_t decay_hi);
 std::vector<at::Tensor> swa_fwd(at::Tensor q, at::Tensor k, at::Tensor v, int64_t window, bool causal, double scale);
+std::vector<at::Tensor> patch_decode_fwd(at::Tensor y, c10::optional<at::Tensor> target, int64_t views, int64_t height,
+                                         int64_t width, int64_t patch);
+at::Tensor patch_decode_bwd(at::Tensor rendering, c10::optional<at::Tensor> target, c10::optional<at::Tensor> g_render,
+                            c10::optional<at::Tensor> g_sse, int64_t patch, at::ScalarType dtype);
 at::Tensor ag_linear(at::Tensor x, std::vector<int64_t> shard_ptrs, int64_t rank, at::Tensor w_full, at::Tensor ready,
                      int64_t gather_ctas);
 std::vector<at::Tensor> ep_plan(at::Tensor sizes_all, int64_t rank, int64_t B, int64_t E, int64_t tiles_cap);
@@ -100,6 +104,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("bmm_general", &bmm_general);
   m.def("swa_fwd", &swa_fwd);
   m.def("swa_bwd", &swa_bwd);
+  m.def("patch_decode_fwd", &patch_decode_fwd);
+  m.def("patch_decode_bwd", &patch_decode_bwd);
   m.def("ag_linear", &ag_linear);
   m.def("ep_plan", &ep_plan);
   m.def("ep_push", &ep_push);

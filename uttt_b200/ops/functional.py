@@ -398,6 +398,37 @@ def stacked_linear(x: torch.Tensor, wa: torch.Tensor, wb: torch.Tensor) -> torch
     return _StackedLinear.apply(x, wa, wb)
 
 
+# =========================================================================== view-synthesis decoder tail
+class _PatchDecode(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, y, target, views, height, width, patch):
+        y = y.contiguous()
+        rendering, sse = cuda_ext(y).patch_decode_fwd(y, target, int(views), int(height), int(width), int(patch))
+        ctx.save_for_backward(rendering, target)
+        ctx.patch, ctx.dtype = int(patch), y.dtype
+        return rendering, sse
+
+    @staticmethod
+    def backward(ctx, g_render, g_sse):
+        rendering, target = ctx.saved_tensors
+        dy = cuda_ext(rendering).patch_decode_bwd(rendering, target, g_render, g_sse, ctx.patch, ctx.dtype)
+        return dy, None, None, None, None, None
+
+
+def patch_decode(y: torch.Tensor, target: Optional[torch.Tensor], views: int, height: int, width: int, patch: int):
+    """Decoder logits [B, V*T, P*P*3] -> (sigmoid image [B, V, 3, H, W] fp32, squared error per view [B, V]).
+    Channel order inside a token is (ph, pw, c); ``target`` may be None (then the error sums are zero)."""
+    if _kernel("patch_decode_fwd", y) is not None and y.dtype in (torch.bfloat16, torch.float32):
+        return _PatchDecode.apply(y, None if target is None else target.float().contiguous(), views, height, width,
+                                  patch)
+    b = y.shape[0]
+    hh, ww = height // patch, width // patch
+    r = torch.sigmoid(y.float()).view(b, views, hh, ww, patch, patch, 3).permute(0, 1, 6, 2, 4, 3, 5)
+    r = r.reshape(b, views, 3, height, width)
+    sse = ((r - target.float()) ** 2).sum(dim=(2, 3, 4)) if target is not None else r.new_zeros(b, views)
+    return r, sse
+
+
 _POOL_MODES = {"restore": 0, "unit": 1, "none": 2}
 
 
