@@ -95,7 +95,8 @@ def run_ours(args):
     assert torch.cuda.is_available(), "bench.py needs a GPU"
     ext = load(required=True)
     dev = torch.device("cuda", local)
-    cfg = named_config(args.model, memory_update_backward_mode=args.backward_mode)
+    cfg = named_config(args.model, memory_update_backward_mode=args.backward_mode,
+                       memory_expert_parallel=max(1, args.expert_parallel))
     seq = args.seq_len
     eng = TrainEngine(cfg, EngineConfig(micro_batch_size=args.micro_batch, lr=1e-3, eps=1e-15, warmup_steps=1024,
                                         total_steps=40960, seed=42), dev)
@@ -152,7 +153,8 @@ def run_ours(args):
             "impl": "uttt_b200",
             "config": {"model": args.model, "params": n_params, "global_batch": args.per_gpu_batch * world,
                        "per_gpu_batch": args.per_gpu_batch, "micro_batch": args.micro_batch, "seq_len": seq,
-                       "parallelism": f"fsdp{world}" if world > 1 else "single",
+                       "parallelism": (f"fsdp{world}" if world > 1 else "single")
+                       + (f"+ep{args.expert_parallel}" if args.expert_parallel > 1 else ""),
                        "backward_mode": args.backward_mode,
                        "cache": "inputs and per-step working set are far larger than L2 (no flush needed)"},
             "clocks": clocks,
@@ -178,6 +180,9 @@ def main():
     ap.add_argument("--per-gpu-batch", type=int, default=4)
     ap.add_argument("--micro-batch", type=int, default=int(os.environ.get("UTTT_BENCH_MICRO_BATCH", "4")))
     ap.add_argument("--backward-mode", default="full")
+    ap.add_argument("--expert-parallel", type=int, default=1,
+                    help="shard the experts of the pool over this many ranks (default: pool state stays with its "
+                         "sequence's rank, as in the reference)")
     args = ap.parse_args()
     if args.impl == "reference":
         from baseline.run_reference import run_reference

@@ -53,12 +53,13 @@ at::Tensor ag_linear(at::Tensor x, std::vector<int64_t> shard_ptrs, int64_t rank
 std::vector<at::Tensor> ep_plan(at::Tensor sizes_all, int64_t rank, int64_t B, int64_t E, int64_t tiles_cap);
 void ep_push(at::Tensor src, c10::optional<at::Tensor> weights, at::Tensor idx, at::Tensor dest, at::Tensor offsets_local,
              at::Tensor sizes_local, at::Tensor remote_start, std::vector<int64_t> peer_ptrs, int64_t E,
-             int64_t rows_per_batch);
+             int64_t rows_per_batch, int64_t cap_rows);
 at::Tensor ep_pull(std::vector<int64_t> peer_ptrs, c10::optional<at::Tensor> weights, at::Tensor idx, at::Tensor dest,
                    at::Tensor offsets_local, at::Tensor remote_start, int64_t E, int64_t rows_per_batch, int64_t D,
-                   at::ScalarType dtype);
+                   at::ScalarType dtype, int64_t cap_rows);
 at::Tensor ep_pull_dot(at::Tensor local, std::vector<int64_t> peer_ptrs, at::Tensor idx, at::Tensor dest,
-                       at::Tensor offsets_local, at::Tensor remote_start, int64_t E, int64_t rows_per_batch);
+                       at::Tensor offsets_local, at::Tensor remote_start, int64_t E, int64_t rows_per_batch,
+                       int64_t cap_rows);
 bool pool_step_supported(int64_t D);
 std::vector<at::Tensor> pool_step_fwd(at::Tensor m, at::Tensor d, double lr, int64_t mode);
 std::vector<at::Tensor> pool_step_bwd(at::Tensor m, at::Tensor d, c10::optional<at::Tensor> gn,

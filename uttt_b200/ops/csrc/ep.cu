@@ -26,6 +26,8 @@
 
 namespace uttt {
 
+at::Tensor gemm_status(at::Tensor like);
+
 constexpr int kEpMaxRanks = 16;
 struct EpPeers {
   void* p[kEpMaxRanks];
@@ -37,7 +39,7 @@ constexpr int kTile = 128;
 __global__ void __launch_bounds__(1024) ep_plan_kernel(const int* __restrict__ sizes_all, int P, int B, int E, int rank,
                                                        int tiles_cap, int* __restrict__ remote_start,
                                                        int* __restrict__ tile_group, int* __restrict__ offsets,
-                                                       int* __restrict__ sizes_owner) {
+                                                       int* __restrict__ sizes_owner, int* __restrict__ status) {
   const int El = E / P;
   const int G = P * B * El;                  // groups per owner
   __shared__ int warp_tot[32];
@@ -93,6 +95,8 @@ __global__ void __launch_bounds__(1024) ep_plan_kernel(const int* __restrict__ s
       __syncthreads();
     }
     if (owner == rank && threadIdx.x == 0) offsets[G] = carry;
+    // a routing more skewed than the staging capacity allows is reported, never silently truncated
+    if (threadIdx.x == 0 && carry > tiles_cap * kTile && status != nullptr) atomicCAS(status, 0, 61);
     __syncthreads();
   }
 }
@@ -103,6 +107,7 @@ struct EpMap {
   const int* offsets_local;  // [B * E + 1] local padded group starts
   const int* remote_start;   // [B * E] start of the sender's group in its owner's buffer
   int k, E, El, rows_per_batch;
+  long long cap_rows;        // rows of a staging buffer; positions past it are dropped (and reported by the plan)
 };
 
 __device__ __forceinline__ void ep_locate(const EpMap& m, long long copy, int& peer, long long& pos) {
@@ -128,6 +133,7 @@ __global__ void __launch_bounds__(256) ep_push_kernel(const T* __restrict__ src,
     int peer;
     long long pos;
     ep_locate(m, c, peer, pos);
+    if (pos >= m.cap_rows) continue;
     const T* s = src + (c / m.k) * D;
     T* d = reinterpret_cast<T*>(peers.p[peer]) + pos * D;
     if (weights == nullptr) {
@@ -156,6 +162,7 @@ __global__ void __launch_bounds__(256) ep_push_kernel(const T* __restrict__ src,
     const int e = (int)(g % m.E);
     T* base = reinterpret_cast<T*>(peers.p[e / m.El]) + (long long)m.remote_start[g] * D;
     for (int row = sz; row < padded; ++row)
+      if ((long long)m.remote_start[g] + row < m.cap_rows)
       for (int v = lane; v < nv; v += 32) reinterpret_cast<uint4*>(base + (long long)row * D)[v] = make_uint4(0, 0, 0, 0);
   }
 }
@@ -177,6 +184,7 @@ __global__ void __launch_bounds__(256) ep_pull_kernel(T* __restrict__ out, const
         int peer;
         long long pos;
         ep_locate(m, r * m.k + j, peer, pos);
+        if (pos >= m.cap_rows) continue;
         float f[8];
         Vec8<T>::load(reinterpret_cast<const T*>(peers.p[peer]) + pos * D + v * 8, f);
         const float wgt = weights ? weights[r * m.k + j] : 1.f;
@@ -202,6 +210,7 @@ __global__ void __launch_bounds__(256) ep_pull_dot_kernel(const T* __restrict__ 
     const T* a = local + (c / m.k) * D;
     const T* b = reinterpret_cast<const T*>(peers.p[peer]) + pos * D;
     float acc = 0.f;
+    if (pos < m.cap_rows)
     for (int v = lane; v < nv; v += 32) {
       float x[8], y[8];
       Vec8<T>::load(a + v * 8, x);
@@ -223,7 +232,7 @@ static EpPeers make_peers(const std::vector<int64_t>& ptrs) {
 }
 
 static EpMap make_map(const at::Tensor& idx, const at::Tensor& dest, const at::Tensor& offsets_local,
-                      const at::Tensor& remote_start, int64_t E, int64_t P, int64_t rows_per_batch) {
+                      const at::Tensor& remote_start, int64_t E, int64_t P, int64_t rows_per_batch, int64_t cap_rows) {
   TORCH_CHECK(idx.scalar_type() == at::kInt && idx.is_contiguous() && dest.scalar_type() == at::kLong &&
               dest.is_contiguous() && offsets_local.scalar_type() == at::kInt && remote_start.scalar_type() == at::kInt);
   TORCH_CHECK(idx.dim() == 2 && dest.numel() == idx.numel() && E % P == 0);
@@ -236,6 +245,7 @@ static EpMap make_map(const at::Tensor& idx, const at::Tensor& dest, const at::T
   m.E = (int)E;
   m.El = (int)(E / P);
   m.rows_per_batch = (int)rows_per_batch;
+  m.cap_rows = cap_rows;
   return m;
 }
 
@@ -258,7 +268,8 @@ std::vector<at::Tensor> ep_plan(at::Tensor sizes_all, int64_t rank, int64_t B, i
   auto sizes = at::empty({G}, opts);
   ep_plan_kernel<<<1, 1024, 0, at::cuda::getCurrentCUDAStream().stream()>>>(
       sizes_all.data_ptr<int>(), P, (int)B, (int)E, (int)rank, (int)tiles_cap, remote_start.data_ptr<int>(),
-      tile_group.data_ptr<int>(), offsets.data_ptr<int>(), sizes.data_ptr<int>());
+      tile_group.data_ptr<int>(), offsets.data_ptr<int>(), sizes.data_ptr<int>(),
+      gemm_status(sizes_all).data_ptr<int>());
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   count_launch();
   return {remote_start, tile_group, offsets, sizes};
@@ -266,13 +277,13 @@ std::vector<at::Tensor> ep_plan(at::Tensor sizes_all, int64_t rank, int64_t B, i
 
 void ep_push(at::Tensor src, c10::optional<at::Tensor> weights, at::Tensor idx, at::Tensor dest, at::Tensor offsets_local,
              at::Tensor sizes_local, at::Tensor remote_start, std::vector<int64_t> peer_ptrs, int64_t E,
-             int64_t rows_per_batch) {
+             int64_t rows_per_batch, int64_t cap_rows) {
   c10::cuda::CUDAGuard guard(src.device());
   TORCH_CHECK(src.dim() == 2 && src.is_contiguous() && src.size(0) == idx.size(0));
   const int D = src.size(1);
   TORCH_CHECK((D * src.element_size()) % 16 == 0, "expert-parallel rows must be a multiple of 16 bytes");
   const int P = peer_ptrs.size();
-  EpMap m = make_map(idx, dest, offsets_local, remote_start, E, P, rows_per_batch);
+  EpMap m = make_map(idx, dest, offsets_local, remote_start, E, P, rows_per_batch, cap_rows);
   EpPeers peers = make_peers(peer_ptrs);
   const float* wp = nullptr;
   at::Tensor wc;
@@ -299,11 +310,11 @@ void ep_push(at::Tensor src, c10::optional<at::Tensor> weights, at::Tensor idx, 
 
 at::Tensor ep_pull(std::vector<int64_t> peer_ptrs, c10::optional<at::Tensor> weights, at::Tensor idx, at::Tensor dest,
                    at::Tensor offsets_local, at::Tensor remote_start, int64_t E, int64_t rows_per_batch, int64_t D,
-                   at::ScalarType dtype) {
+                   at::ScalarType dtype, int64_t cap_rows) {
   c10::cuda::CUDAGuard guard(idx.device());
   TORCH_CHECK(D % 8 == 0);
   const int P = peer_ptrs.size();
-  EpMap m = make_map(idx, dest, offsets_local, remote_start, E, P, rows_per_batch);
+  EpMap m = make_map(idx, dest, offsets_local, remote_start, E, P, rows_per_batch, cap_rows);
   EpPeers peers = make_peers(peer_ptrs);
   const float* wp = nullptr;
   at::Tensor wc;
@@ -328,11 +339,12 @@ at::Tensor ep_pull(std::vector<int64_t> peer_ptrs, c10::optional<at::Tensor> wei
 }
 
 at::Tensor ep_pull_dot(at::Tensor local, std::vector<int64_t> peer_ptrs, at::Tensor idx, at::Tensor dest,
-                       at::Tensor offsets_local, at::Tensor remote_start, int64_t E, int64_t rows_per_batch) {
+                       at::Tensor offsets_local, at::Tensor remote_start, int64_t E, int64_t rows_per_batch,
+                       int64_t cap_rows) {
   c10::cuda::CUDAGuard guard(local.device());
   TORCH_CHECK(local.dim() == 2 && local.is_contiguous() && local.size(1) % 8 == 0 && local.size(0) == idx.size(0));
   const int P = peer_ptrs.size();
-  EpMap m = make_map(idx, dest, offsets_local, remote_start, E, P, rows_per_batch);
+  EpMap m = make_map(idx, dest, offsets_local, remote_start, E, P, rows_per_batch, cap_rows);
   EpPeers peers = make_peers(peer_ptrs);
   auto out = at::empty({idx.size(0), idx.size(1)}, local.options().dtype(at::kFloat));
   const long long copies = idx.numel();

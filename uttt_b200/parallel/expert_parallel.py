@@ -51,7 +51,7 @@ class EPPlan:
 
 class ExpertParallel:
     def __init__(self, group, device: torch.device, num_experts: int, transport: str = "auto",
-                 max_row_bytes: int = 4096):
+                 max_row_bytes: int = 4096, capacity_factor: float = 2.0):
         self.group = group if group is not None else dist.group.WORLD
         self.P = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
@@ -64,6 +64,9 @@ class ExpertParallel:
             transport = "peer" if device.type == "cuda" else "a2a"
         self.transport = transport
         self.max_row_bytes = max_row_bytes
+        # staging rows per rank = capacity_factor x the balanced load (0 = size for the worst case, P x); a routing
+        # that needs more is reported through the kernel status word (code 61), never truncated silently
+        self.capacity_factor = float(capacity_factor)
         self.heap = None
         self._recv: List[torch.Tensor] = []
         self._send: List[torch.Tensor] = []
@@ -117,7 +120,9 @@ class ExpertParallel:
         g_owner = p * bsz * el
         idx32 = idx.reshape(bsz * n, k).to(torch.int32).contiguous()
         if self.transport == "peer":
-            cap_rows = ((p * bsz * n * k + TILE - 1) // TILE + g_owner) * TILE
+            worst = p * bsz * n * k
+            want = worst if self.capacity_factor <= 0 else min(worst, int(self.capacity_factor * bsz * n * k))
+            cap_rows = ((want + TILE - 1) // TILE + g_owner) * TILE
             self._ensure_heap(cap_rows)
             remote_start, tile_group, offsets, sizes = load(required=True).ep_plan(sizes_all, self.rank, bsz, e,
                                                                                    cap_rows // TILE)
@@ -191,7 +196,7 @@ class _PeerDispatch(torch.autograd.Function):
         rows = rows.contiguous()
         slot = ep._slot(ep._recv, "recv", plan.owner.rows_padded, rows.shape[1], rows.dtype)
         ext.ep_push(rows, weights, *_map_args(plan)[:3], plan.sizes32, plan.remote_start, ep.heap.peer_ptrs(slot),
-                    ep.E, plan.rows_per_batch)
+                    ep.E, plan.rows_per_batch, plan.owner.rows_padded)
         ep.barrier()
         out = slot.clone()
         ctx.ep, ctx.plan = ep, plan
@@ -210,9 +215,11 @@ class _PeerDispatch(torch.autograd.Function):
         ptrs = ep.heap.peer_ptrs(slot)
         drows = dweights = None
         if ctx.needs_input_grad[0]:
-            drows = ext.ep_pull(ptrs, weights, *_map_args(plan), ep.E, plan.rows_per_batch, rows.shape[1], rows.dtype)
+            drows = ext.ep_pull(ptrs, weights, *_map_args(plan), ep.E, plan.rows_per_batch, rows.shape[1], rows.dtype,
+                                plan.owner.rows_padded)
         if weights is not None and ctx.needs_input_grad[1]:
-            dweights = ext.ep_pull_dot(rows, ptrs, *_map_args(plan), ep.E, plan.rows_per_batch).to(weights.dtype)
+            dweights = ext.ep_pull_dot(rows, ptrs, *_map_args(plan), ep.E, plan.rows_per_batch,
+                                       plan.owner.rows_padded).to(weights.dtype)
         return drows, dweights, None, None
 
 
@@ -225,7 +232,7 @@ class _PeerCombine(torch.autograd.Function):
         slot.copy_(yp)
         ep.barrier()
         out = ext.ep_pull(ep.heap.peer_ptrs(slot), weights, *_map_args(plan), ep.E, plan.rows_per_batch, yp.shape[1],
-                          yp.dtype)
+                          yp.dtype, plan.owner.rows_padded)
         ctx.ep, ctx.plan = ep, plan
         ctx.save_for_backward(yp, weights)
         return out
@@ -242,11 +249,11 @@ class _PeerCombine(torch.autograd.Function):
             slot.copy_(yp)
             ep.barrier()
             dweights = ext.ep_pull_dot(dy, ep.heap.peer_ptrs(slot), *_map_args(plan), ep.E,
-                                       plan.rows_per_batch).to(weights.dtype)
+                                       plan.rows_per_batch, plan.owner.rows_padded).to(weights.dtype)
         if ctx.needs_input_grad[0]:
             slot = ep._slot(ep._recv, "recv", plan.owner.rows_padded, yp.shape[1], yp.dtype)
             ext.ep_push(dy, weights, *_map_args(plan)[:3], plan.sizes32, plan.remote_start, ep.heap.peer_ptrs(slot),
-                        ep.E, plan.rows_per_batch)
+                        ep.E, plan.rows_per_batch, plan.owner.rows_padded)
             ep.barrier()
             dyp = slot.clone()
         return dyp, dweights, None, None
