@@ -468,6 +468,66 @@ def test_patch_decode_matches_reference(dtype):
     _close(g, gref, tol, tol, "dy")
 
 
+def test_fanout_and_stacked_linear_accumulate_gradients_in_the_gemm():
+    _ext()
+    torch.manual_seed(24)
+    x = torch.randn(4, 64, 128, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    flat = (torch.randn(3 * 256 * 128, device=DEV) * 0.05).bfloat16()
+    gflat = torch.zeros_like(flat)
+    ws = []
+    for i in range(3):                                   # three neighbours in one flat buffer, like the trainer's
+        w = flat[i * 256 * 128:(i + 1) * 256 * 128].view(256, 128).requires_grad_(True)
+        w.grad = gflat[i * 256 * 128:(i + 1) * 256 * 128].view(256, 128)
+        w.grad.fill_(0.5)
+        ws.append(w)
+    ops.set_fused_weight_grad(True)
+    try:
+        a, b = ops.fanout_linear(x, ws[:2])
+        c = ops.stacked_linear(x, ws[1], ws[2])
+        ga, gb, gc = torch.randn_like(a), torch.randn_like(b), torch.randn_like(c)
+        (a * ga).sum().add((b * gb).sum()).add((c * gc).sum()).backward()
+    finally:
+        ops.set_fused_weight_grad(False)
+    xr = x.detach().float().requires_grad_(True)
+    wr = [w.detach().float().requires_grad_(True) for w in ws]
+    ar, br = xr @ wr[0].t(), xr @ wr[1].t()
+    cr = xr @ torch.cat([wr[1], wr[2]]).t()
+    _close(a, ar, 3e-2, 3e-2, "a")
+    _close(c, cr, 3e-2, 3e-2, "c")
+    (ar * ga.float()).sum().add((br * gb.float()).sum()).add((cr * gc.float()).sum()).backward()
+    _close(x.grad, xr.grad, 0.15, 3e-2, "dx")
+    for i in range(3):
+        _close(ws[i].grad, 0.5 + wr[i].grad, 0.6, 3e-2, f"dw{i}")        # added onto the existing 0.5
+    assert gflat.view(3, 256, 128)[0].data_ptr() == ws[0].grad.data_ptr()  # still the flat buffer's view
+
+
+def test_grad_sink_matches_autograd_accumulation():
+    _ext()
+    torch.manual_seed(25)
+    plan = _plan(seed=3)
+    g, k, n = plan.num_groups, 128, 256
+    real = torch.zeros(plan.rows_padded, 1, device=DEV)
+    real[plan.dest.reshape(-1)] = 1
+    xs = [(torch.randn(plan.rows_padded, k, device=DEV) * real).bfloat16() for _ in range(3)]
+    cs = [(torch.randn(plan.rows_padded, n, device=DEV) * real).bfloat16() for _ in range(3)]
+
+    def run(use_sink):
+        w = (torch.randn(g, n, k, device=DEV, generator=torch.Generator(DEV).manual_seed(1)) / 11).bfloat16()
+        w.requires_grad_(True)
+        ws = ops.grad_sink(w * 1.0) if use_sink else w * 1.0     # a non-leaf, like a chunk's state
+        total = 0
+        for x, c in zip(xs, cs):
+            total = total + (ops.gg_nt(x, ws, plan).float() * c.float()).sum()
+        # one consumer that knows nothing about sinks contributes through autograd as usual
+        total = total + (ws.float() ** 2).sum() * 0.01
+        total.backward()
+        return w.grad.float()
+
+    a, b = run(False), run(True)
+    _close(b, a, 0.3, 2e-2, "sink")
+    assert not fn._GRAD_SINKS
+
+
 def test_plucker_embed():
     _ext()
     from uttt_b200.nvs.data import SyntheticScenes

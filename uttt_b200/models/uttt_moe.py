@@ -431,9 +431,17 @@ class UTTTMoEModel(nn.Module):
             from .cross_layer_cut import alias_streams
             states = alias_streams(states[0], n_layers)
         outputs = []
+        sink = (cfg.use_memory_block and not self.per_layer_pool and not cut and self.ep is None and self.training
+                and torch.is_grad_enabled())
+        if sink:
+            ops.reset_grad_sinks()
         for start in range(0, seq_len, chunk):
             end = min(start + chunk, seq_len)
             h = inputs_embeds[:, start:end]
+            if sink:
+                # all readers and writers of this chunk add their bank gradients into one buffer (see ops.grad_sink)
+                s0 = states[0]
+                states = [fw.PoolState(ops.grad_sink(s0.w02), ops.grad_sink(s0.w1), s0.m02, s0.m1, s0.z02, s0.z1)]
             feats = []
             layer_probs, layer_counts = [], []
             for li, layer in enumerate(self.layers):

@@ -592,6 +592,63 @@ def _gg_dims_ok(k: int, n: int) -> bool:
     return k % 64 == 0 and n % 64 == 0
 
 
+# --------------------------------------------------------------------------- gradient sinks for shared weights
+# A fast-weight bank is read by every layer of a chunk and by every writer of the chunk boundary, so ~2 L weight
+# gradients of the full bank size meet at one tensor.  Left to autograd that is ~2 L bank-sized adds per chunk.
+# With a sink, every consumer's token-reduction GEMM adds its contribution into ONE fp32 buffer inside the GEMM
+# epilogue and reports no gradient; the sink node hands the buffer to the producer of the bank.
+_GRAD_SINKS = {}
+
+
+class _GradSink(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, w):
+        ctx.key = w.data_ptr()
+        ctx.meta = (w.shape, w.dtype)
+        ctx.set_materialize_grads(False)
+        _GRAD_SINKS[ctx.key] = [None]
+        return w.view_as(w)
+
+    @staticmethod
+    def backward(ctx, g):
+        entry = _GRAD_SINKS.pop(ctx.key, None)
+        buf = None if entry is None else entry[0]
+        if buf is None:
+            return g
+        shape, dtype = ctx.meta
+        total = buf.view(shape)
+        if g is not None:
+            total = total + g.float()
+        return total.to(dtype)
+
+
+def grad_sink(w: torch.Tensor) -> torch.Tensor:
+    """Mark ``w`` (a tensor consumed by many grouped GEMMs) so that its consumers accumulate their weight
+    gradients in one fp32 buffer inside their GEMMs.  Identity in value; a no-op off the kernel path."""
+    if w.is_cuda and w.requires_grad and torch.is_grad_enabled() and w.dtype == torch.bfloat16 \
+            and w.is_contiguous() and _kernel("gg_tn_segments", w) is not None:
+        return _GradSink.apply(w)
+    return w
+
+
+def reset_grad_sinks() -> None:
+    """Forget sinks whose backward never ran (e.g. a forward pass that was not differentiated)."""
+    _GRAD_SINKS.clear()
+
+
+def _sink_add(w: torch.Tensor, a: torch.Tensor, b: torch.Tensor, plan) -> bool:
+    """If ``w`` has a sink: sink[g] += sum_{r in g} a[r]^T b[r] and True; otherwise False."""
+    if torch.is_grad_enabled() or not _GRAD_SINKS:
+        return False
+    entry = _GRAD_SINKS.get(w.data_ptr())
+    if entry is None or not _gg_kernel_ok(a, b) or a.shape[1] % 128 != 0 or b.shape[1] % 64 != 0:
+        return False
+    if entry[0] is None:
+        entry[0] = torch.zeros(plan.num_groups, a.shape[1], b.shape[1], device=a.device, dtype=torch.float32)
+    _gg_tn_acc_(a, b, plan, entry[0])
+    return True
+
+
 class _GGNT(torch.autograd.Function):
     """out[r] = x[r] @ w[g(r)]^T."""
 
@@ -607,7 +664,7 @@ class _GGNT(torch.autograd.Function):
         dx = dw = None
         if ctx.needs_input_grad[0]:
             dx = gg_nn(dy, w, ctx.plan)
-        if ctx.needs_input_grad[1]:
+        if ctx.needs_input_grad[1] and not _sink_add(w, dy, x, ctx.plan):
             dw = gg_tn(dy, x, ctx.plan, w.dtype)
         return dx, dw, None
 
@@ -627,7 +684,7 @@ class _GGNN(torch.autograd.Function):
         dx = dw = None
         if ctx.needs_input_grad[0]:
             dx = gg_nt(dy, w, ctx.plan)
-        if ctx.needs_input_grad[1]:
+        if ctx.needs_input_grad[1] and not _sink_add(w, x, dy, ctx.plan):
             dw = gg_tn(x, dy, ctx.plan, w.dtype)
         return dx, dw, None
 
@@ -771,9 +828,9 @@ class _FwWriteGrad(torch.autograd.Function):
             d_y02, d_dh, d_lr = ext.fw_write_pw_bwd(d_dy02, d_hlr, y02, dh, lrp)
             del d_dy02, d_hlr, y02, dh
             d_kp += gg_nn(d_y02, w02, plan)
-            d_w02 = gg_tn(d_y02, kp, plan, w02.dtype)
+            d_w02 = None if _sink_add(w02, d_y02, kp, plan) else gg_tn(d_y02, kp, plan, w02.dtype)
             d_vp += gg_nt(d_dh, w1, plan)
-            d_w1 = gg_tn(vp, d_dh, plan, w1.dtype)
+            d_w1 = None if _sink_add(w1, vp, d_dh, plan) else gg_tn(vp, d_dh, plan, w1.dtype)
         return d_kp, d_vp, d_lr, d_w02, d_w1, None
 
 

@@ -2,7 +2,8 @@
 
     python -m uttt_b200.ops.microbench [--kernel NAME] [--small] [--iters N]
 
-Kernels: gg_nt, gg_nn, gg_tn, bmm_nt, swa_fwd, swa_bwd, rms_norm, fw_write_pw, adamw, ce.  ``--small`` runs one small case
+Kernels: gg_nt, gg_nn, gg_tn, bmm_nt, swa_fwd, swa_bwd, rms_norm, rope, fw_qk_prep, router, pool_step, plucker,
+fw_write_pw, adamw, ce.  ``--small`` runs one small case
 of the chosen kernel (inputs above L2 size, a few hundred MB on the device) three times, which is what the
 profile summaries under ``profiles/`` were captured from.  Prints one JSON line per case with the achieved
 TFLOP/s or GB/s and the fraction of the measured peaks in ``MEASURED_PEAKS.json`` when present.
@@ -127,6 +128,35 @@ def run(kernel: str, small: bool, iters: int):
         w = torch.ones(1536, **bf)
         ms = _time(lambda: F.rms_norm(x, w, 1e-6), iters, flush)
         rec("rms_norm_fwd", ms, bytes_=2.0 * x.numel() * 2)
+    if kernel in ("rope", "all"):
+        q = torch.randn(bsz, 2048, 16, 96, **bf)
+        ms = _time(lambda: F.rope(q, 0, 10000.0), iters, flush)
+        rec("rope[hd96]", ms, bytes_=2.0 * q.numel() * 2)
+    if kernel in ("fw_qk_prep", "all"):
+        x = torch.randn(bsz, 2048, 1536, **bf)
+        sc = torch.ones(1536, **bf)
+        sh = torch.zeros(1536, **bf)
+        ms = _time(lambda: F.fw_qk_prep(x, sc, sh, 4, 96, 10000.0, 0, True, "l2"), iters, flush)
+        rec("fw_qk_prep_fwd", ms, bytes_=2.0 * x.numel() * 2)
+    if kernel in ("router", "all"):
+        rows_r = torch.randn(bsz, 8192, d, **bf)
+        rt = torch.randn(experts, d, device=dev) * 0.1
+        ms = _time(lambda: F.route_softmax_topk(rows_r, rt, None, 2), iters, flush)
+        rec("router_fwd[E32 top2]", ms, bytes_=rows_r.numel() * 2.0 + bsz * 8192 * (experts * 4 + 16),
+            flops=2.0 * bsz * 8192 * d * experts)
+    if kernel in ("pool_step", "all"):
+        m = torch.randn(bsz, experts, 2 * inter, d, device=dev)
+        dd = torch.randn(bsz, experts, 2 * inter, d, **bf)
+        ms = _time(lambda: F.pool_step(m, dd, 0.1, "restore"), iters, flush)
+        rec("pool_step_fwd[restore]", ms, bytes_=float(m.numel()) * (4 + 2 + 4 + 2))
+    if kernel in ("plucker", "all"):
+        v_, hw = 6, 256
+        img = torch.rand(bsz, v_, 3, hw, hw, device=dev)
+        fx = torch.tensor([300.0, 300.0, 128.0, 128.0], device=dev).expand(bsz, v_, 4).contiguous()
+        c2w = torch.eye(4, device=dev).expand(bsz, v_, 4, 4).contiguous()
+        tgt = torch.zeros(v_, dtype=torch.bool, device=dev)
+        ms = _time(lambda: F.plucker_embed(img, fx, c2w, tgt, 8), iters, flush)
+        rec("plucker_embed[256px]", ms, bytes_=float(img.numel()) * 4 + bsz * v_ * hw * hw * 12 * 4.0)
     if kernel in ("fw_write_pw", "all"):
         ext = load()
         y02 = torch.randn(rows, 2 * inter, **bf)
