@@ -528,6 +528,21 @@ def test_grad_sink_matches_autograd_accumulation():
     assert not fn._GRAD_SINKS
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_frobenius_normalize_forward_backward(dtype):
+    ext = _ext()
+    torch.manual_seed(26)
+    g = (torch.randn(5, 384, 128, device=DEV) * 3).to(dtype).requires_grad_(True)
+    x = fn._FrobNormalize.apply(g, 1e-7)
+    gr = g.detach().float().requires_grad_(True)
+    xr = gr / (gr.norm(dim=(1, 2), keepdim=True) + 1e-7)
+    _close(x, xr, 1e-3, 1e-2, "x")
+    c = torch.randn_like(xr).bfloat16()
+    (d,) = torch.autograd.grad(x, g, c)
+    (dr,) = torch.autograd.grad(xr, gr, c.float())
+    _close(d, dr, 2e-3 if dtype == torch.float32 else 2e-2, 2e-2, "dg")
+
+
 def test_plucker_embed():
     _ext()
     from uttt_b200.nvs.data import SyntheticScenes

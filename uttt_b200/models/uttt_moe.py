@@ -50,6 +50,15 @@ class MoEBlock(nn.Module):
         self.attn_norm = RMSNorm(d, eps=config.norm_eps)
         self.attn = SlidingWindowAttention(config, layer_idx)
         if config.use_memory_block:
+            # every released configuration feeds the memory from the attention's own q / k / v projections
+            # ("reuse_kv"); the other sources the schema can name (separate projections, gapped layers) are rejected
+            # instead of being silently replaced
+            unsupported = [n for n in ("memory_k_gap", "memory_v_gap", "memory_k_compose_mode", "memory_v_compose_mode")
+                           if getattr(config, n, None) is not None]
+            if getattr(config, "memory_kv_mode", "reuse_kv") != "reuse_kv" or unsupported:
+                raise NotImplementedError(
+                    "the memory branch implements memory_kv_mode='reuse_kv' without k/v gaps or compose modes; got "
+                    f"memory_kv_mode={getattr(config, 'memory_kv_mode', None)!r}, {unsupported}")
             self.memory_norm = RMSNorm(d, eps=config.norm_eps) if config.residual_style == "sequential" else None
             self.memory = fw.FastWeightMemory(config, layer_idx, momentum_out=1)
             self.to_lr = nn.Linear(d, 3 * config.fw_heads if config.per_head_lr else 3)

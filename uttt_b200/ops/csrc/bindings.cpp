@@ -60,6 +60,8 @@ at::Tensor ep_pull(std::vector<int64_t> peer_ptrs, c10::optional<at::Tensor> wei
 at::Tensor ep_pull_dot(at::Tensor local, std::vector<int64_t> peer_ptrs, at::Tensor idx, at::Tensor dest,
                        at::Tensor offsets_local, at::Tensor remote_start, int64_t E, int64_t rows_per_batch,
                        int64_t cap_rows);
+std::vector<at::Tensor> frob_normalize_fwd(at::Tensor g, double eps);
+at::Tensor frob_normalize_bwd(at::Tensor g, at::Tensor sumsq, at::Tensor dx, double eps);
 bool pool_step_supported(int64_t D);
 std::vector<at::Tensor> pool_step_fwd(at::Tensor m, at::Tensor d, double lr, int64_t mode);
 std::vector<at::Tensor> pool_step_bwd(at::Tensor m, at::Tensor d, c10::optional<at::Tensor> gn,
@@ -112,6 +114,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ep_push", &ep_push);
   m.def("ep_pull", &ep_pull);
   m.def("ep_pull_dot", &ep_pull_dot);
+  m.def("frob_normalize_fwd", &frob_normalize_fwd);
+  m.def("frob_normalize_bwd", &frob_normalize_bwd);
   m.def("pool_step_supported", &pool_step_supported);
   m.def("pool_step_fwd", &pool_step_fwd);
   m.def("pool_step_bwd", &pool_step_bwd);

@@ -254,3 +254,141 @@ std::vector<at::Tensor> pool_step_bwd(at::Tensor m, at::Tensor d, c10::optional<
 }
 
 }  // namespace uttt
+
+// ------------------------------------------------------------------------------------ Newton-Schulz input
+// X[b] = G[b] / (|G[b]|_F + eps) cast to bf16, per matrix of a batch, in two passes (sum of squares, scale + cast)
+// instead of cast / cast back / norm / add / cast / divide; and its VJP
+//   dG = dX / (r + eps) - G <dX, G> / (r (r + eps)^2),   r = |G|_F.
+namespace uttt {
+
+template <typename T>
+__global__ void __launch_bounds__(256) frob_partial_kernel(const T* __restrict__ g, const __nv_bfloat16* __restrict__ dx,
+                                                           float* __restrict__ out, long long per_matrix) {
+  // grid (chunks, matrices); out[b] += sum g^2 (dx == nullptr) or sum dx * g
+  const long long b = blockIdx.y;
+  const T* gp = g + b * per_matrix;
+  const __nv_bfloat16* dp = dx ? dx + b * per_matrix : nullptr;
+  float acc = 0.f;
+  const long long nv = per_matrix >> 2;
+  for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nv; v += (long long)gridDim.x * blockDim.x) {
+    float a[4];
+    load4(gp + v * 4, a);
+    if (dp) {
+      float d[4];
+      load4(dp + v * 4, d);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc = fmaf(a[i], d[i], acc);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc = fmaf(a[i], a[i], acc);
+    }
+  }
+  acc = warp_sum(acc);
+  __shared__ float red[8];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  if (lane == 0) red[wid] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = 0.f;
+    for (int i = 0; i < 8; ++i) s += red[i];
+    atomicAdd(out + b, s);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) frob_scale_kernel(const T* __restrict__ g, const float* __restrict__ sumsq,
+                                                         float eps, __nv_bfloat16* __restrict__ x,
+                                                         long long per_matrix) {
+  const long long b = blockIdx.y;
+  const float inv = 1.f / (sqrtf(sumsq[b]) + eps);
+  const long long nv = per_matrix >> 2;
+  for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nv; v += (long long)gridDim.x * blockDim.x) {
+    float a[4];
+    load4(g + b * per_matrix + v * 4, a);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) a[i] *= inv;
+    store4(x + b * per_matrix + v * 4, a);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) frob_scale_bwd_kernel(const T* __restrict__ g, const __nv_bfloat16* __restrict__ dx,
+                                                             const float* __restrict__ sumsq,
+                                                             const float* __restrict__ dot, float eps,
+                                                             T* __restrict__ dg, long long per_matrix) {
+  const long long b = blockIdx.y;
+  const float r = sqrtf(sumsq[b]);
+  const float inv = 1.f / (r + eps);
+  const float coef = r > 0.f ? dot[b] * inv * inv / r : 0.f;
+  const long long nv = per_matrix >> 2;
+  for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nv; v += (long long)gridDim.x * blockDim.x) {
+    float a[4], d[4], o[4];
+    load4(g + b * per_matrix + v * 4, a);
+    load4(dx + b * per_matrix + v * 4, d);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[i] = d[i] * inv - a[i] * coef;
+    store4(dg + b * per_matrix + v * 4, o);
+  }
+}
+
+static dim3 frob_grid(long long per_matrix, int batch) {
+  int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  long long want = (per_matrix / 4 + 255) / 256;
+  int per = (int)std::max<long long>(1, std::min<long long>(want, std::max(1, sms * 4 / std::max(batch, 1))));
+  return dim3(per, batch);
+}
+
+// g [B, M, N] (fp32 or bf16) -> (x bf16 [B, M, N], sumsq [B] fp32)
+std::vector<at::Tensor> frob_normalize_fwd(at::Tensor g, double eps) {
+  c10::cuda::CUDAGuard guard(g.device());
+  TORCH_CHECK(g.dim() == 3 && g.is_contiguous() && (g.size(1) * g.size(2)) % 4 == 0);
+  const int batch = g.size(0);
+  const long long per = (long long)g.size(1) * g.size(2);
+  auto sumsq = at::zeros({batch}, g.options().dtype(at::kFloat));
+  auto x = at::empty(g.sizes(), g.options().dtype(at::kBFloat16));
+  auto stream = at::cuda::getCurrentCUDAStream().stream();
+  dim3 grid = frob_grid(per, batch);
+  auto* xp = reinterpret_cast<__nv_bfloat16*>(x.data_ptr());
+  if (g.scalar_type() == at::kFloat) {
+    frob_partial_kernel<float><<<grid, 256, 0, stream>>>(g.data_ptr<float>(), nullptr, sumsq.data_ptr<float>(), per);
+    frob_scale_kernel<float><<<grid, 256, 0, stream>>>(g.data_ptr<float>(), sumsq.data_ptr<float>(), (float)eps, xp, per);
+  } else {
+    TORCH_CHECK(g.scalar_type() == at::kBFloat16);
+    auto* gp = reinterpret_cast<const __nv_bfloat16*>(g.data_ptr());
+    frob_partial_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(gp, nullptr, sumsq.data_ptr<float>(), per);
+    frob_scale_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(gp, sumsq.data_ptr<float>(), (float)eps, xp, per);
+  }
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch(2);
+  return {x, sumsq};
+}
+
+at::Tensor frob_normalize_bwd(at::Tensor g, at::Tensor sumsq, at::Tensor dx, double eps) {
+  c10::cuda::CUDAGuard guard(g.device());
+  TORCH_CHECK(g.dim() == 3 && g.is_contiguous() && sumsq.scalar_type() == at::kFloat);
+  auto dxc = dx.to(at::kBFloat16).contiguous();
+  const int batch = g.size(0);
+  const long long per = (long long)g.size(1) * g.size(2);
+  auto dot = at::zeros({batch}, sumsq.options());
+  auto dg = at::empty_like(g);
+  auto stream = at::cuda::getCurrentCUDAStream().stream();
+  dim3 grid = frob_grid(per, batch);
+  auto* dp = reinterpret_cast<const __nv_bfloat16*>(dxc.data_ptr());
+  if (g.scalar_type() == at::kFloat) {
+    frob_partial_kernel<float><<<grid, 256, 0, stream>>>(g.data_ptr<float>(), dp, dot.data_ptr<float>(), per);
+    frob_scale_bwd_kernel<float><<<grid, 256, 0, stream>>>(g.data_ptr<float>(), dp, sumsq.data_ptr<float>(),
+                                                          dot.data_ptr<float>(), (float)eps, dg.data_ptr<float>(), per);
+  } else {
+    TORCH_CHECK(g.scalar_type() == at::kBFloat16);
+    auto* gp = reinterpret_cast<const __nv_bfloat16*>(g.data_ptr());
+    frob_partial_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(gp, dp, dot.data_ptr<float>(), per);
+    frob_scale_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
+        gp, dp, sumsq.data_ptr<float>(), dot.data_ptr<float>(), (float)eps,
+        reinterpret_cast<__nv_bfloat16*>(dg.data_ptr()), per);
+  }
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch(2);
+  return dg;
+}
+
+}  // namespace uttt

@@ -632,8 +632,10 @@ def grad_sink(w: torch.Tensor) -> torch.Tensor:
 
 
 def reset_grad_sinks() -> None:
-    """Forget sinks whose backward never ran (e.g. a forward pass that was not differentiated)."""
+    """Forget sinks whose backward never ran (e.g. a forward pass that was not differentiated) and the cached
+    cotangent conversions of the previous step."""
     _GRAD_SINKS.clear()
+    _CAST_CACHE.clear()
 
 
 def _sink_add(w: torch.Tensor, a: torch.Tensor, b: torch.Tensor, plan) -> bool:
@@ -815,8 +817,8 @@ class _FwWriteGrad(torch.autograd.Function):
         plan = ctx.plan
         ext = cuda_ext(kp)
         with torch.no_grad():
-            c02 = c02.to(kp.dtype).contiguous()
-            c1 = c1.to(kp.dtype).contiguous()
+            c02 = _cached_cast("c02", c02, kp.dtype)
+            c1 = _cached_cast("c1", c1, kp.dtype)
             y02 = gg_nt(kp, w02, plan)
             dh = gg_nn(vp, w1, plan)
             dy02_lr, h_lr = ext.fw_write_pw_fwd(y02, dh, lrp)
@@ -832,6 +834,22 @@ class _FwWriteGrad(torch.autograd.Function):
             d_vp += gg_nt(d_dh, w1, plan)
             d_w1 = None if _sink_add(w1, vp, d_dh, plan) else gg_tn(vp, d_dh, plan, w1.dtype)
         return d_kp, d_vp, d_lr, d_w02, d_w1, None
+
+
+_CAST_CACHE = {}
+
+
+def _cached_cast(slot: str, t: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """``t.to(dtype)`` remembered per slot: the writer layers of one chunk boundary all receive the SAME
+    bank-sized cotangent (it passes through the accumulating nodes unchanged), so it is converted once, not L times.
+    The source is kept referenced, so an equal address and version mean the same contents."""
+    ent = _CAST_CACHE.get(slot)
+    if ent is not None and ent[0].data_ptr() == t.data_ptr() and ent[0].shape == t.shape \
+            and ent[0]._version == t._version and ent[1].dtype == dtype:
+        return ent[1]
+    out = t.to(dtype).contiguous()
+    _CAST_CACHE[slot] = (t, out)
+    return out
 
 
 def _gg_tn_acc_(a, b, plan: GroupPlan, acc: torch.Tensor) -> None:
@@ -966,11 +984,32 @@ def bmm_nt(a, b, alpha: float = 1.0, d=None, beta: float = 0.0):
     return bmm(a, b, 0, alpha, d, beta)
 
 
+class _FrobNormalize(torch.autograd.Function):
+    """x[b] = g[b] / (|g[b]|_F + eps) in bf16: two kernels (sum of squares; scale + cast) and a two-kernel VJP."""
+
+    @staticmethod
+    def forward(ctx, g, eps):
+        g = g.contiguous()
+        x, sumsq = cuda_ext(g).frob_normalize_fwd(g, float(eps))
+        ctx.save_for_backward(g, sumsq)
+        ctx.eps = float(eps)
+        return x
+
+    @staticmethod
+    def backward(ctx, dx):
+        g, sumsq = ctx.saved_tensors
+        return cuda_ext(g).frob_normalize_bwd(g, sumsq, dx, ctx.eps), None
+
+
 def _newton_schulz_kernels(g, coeffs):
     """Newton-Schulz in the given orientation: wide X iterates with X X^T on the left, tall X with X^T X on the
     right (X p(X^T X) = p(X X^T) X), so no transpose is ever materialised."""
-    x = g.to(torch.bfloat16)
-    x = (x / (x.float().norm(dim=(1, 2), keepdim=True) + 1e-7).to(torch.bfloat16)).contiguous()
+    if _kernel("frob_normalize_fwd", g) is not None and g.dtype in (torch.float32, torch.bfloat16) \
+            and (g.size(1) * g.size(2)) % 4 == 0:
+        x = _FrobNormalize.apply(g, 1e-7)
+    else:
+        x = g.to(torch.bfloat16)
+        x = (x / (x.float().norm(dim=(1, 2), keepdim=True) + 1e-7).to(torch.bfloat16)).contiguous()
     tall = g.size(1) > g.size(2)
     for a, b, c in coeffs:
         if tall:

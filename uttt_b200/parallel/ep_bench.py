@@ -74,7 +74,23 @@ def main():
             t_plan = _time(lambda: ep.plan(plan, idx), args.iters, flush)
             t_disp = _time(lambda: ep.dispatch(rows, None, eplan), args.iters, flush)
             t_comb = _time(lambda: ep.combine(xp, w, eplan), args.iters, flush)
-        out[name] = {"plan_ms": round(t_plan, 4), "dispatch_ms": round(t_disp, 4), "combine_ms": round(t_comb, 4),
+        extra = {}
+        if name == "peer":
+            # the NVLink kernels alone (no ordering collective, no staging copy): what the link sees
+            from ..ops._ext import load
+            ext = load(required=True)
+            from .expert_parallel import _map_args
+            cap = eplan.owner.rows_padded
+            slot = ep._slot(ep._recv, "recv", cap, d, rows.dtype)
+            ptrs = ep.heap.peer_ptrs(slot)
+            t_push = _time(lambda: ext.ep_push(rows, None, *_map_args(eplan)[:3], eplan.sizes32, eplan.remote_start,
+                                               ptrs, e, n, cap), args.iters, flush)
+            t_pull = _time(lambda: ext.ep_pull(ptrs, w, *_map_args(eplan), e, n, d, rows.dtype, cap), args.iters,
+                           flush)
+            extra = {"push_kernel_ms": round(t_push, 4), "pull_kernel_ms": round(t_pull, 4),
+                     "push_kernel_frac_of_measured_peer_copy": round(nvlink_bytes / t_push / 1e6 / 770.0, 3),
+                     "pull_kernel_frac_of_measured_peer_copy": round(nvlink_bytes / t_pull / 1e6 / 770.0, 3)}
+        out[name] = {**extra, "plan_ms": round(t_plan, 4), "dispatch_ms": round(t_disp, 4), "combine_ms": round(t_comb, 4),
                      "dispatch_gbs_per_rank": round(nvlink_bytes / t_disp / 1e6, 1),
                      "combine_gbs_per_rank": round(nvlink_bytes / t_comb / 1e6, 1),
                      "dispatch_frac_of_measured_peer_copy": round(nvlink_bytes / t_disp / 1e6 / 770.0, 3),

@@ -198,7 +198,9 @@ class _PeerDispatch(torch.autograd.Function):
         ext.ep_push(rows, weights, *_map_args(plan)[:3], plan.sizes32, plan.remote_start, ep.heap.peer_ptrs(slot),
                     ep.E, plan.rows_per_batch, plan.owner.rows_padded)
         ep.barrier()
-        out = slot.clone()
+        # Outside autograd nothing keeps the rows beyond their immediate consumers, which are enqueued before this
+        # rank joins the ordering collective of the dispatch that reuses the slot: the slot itself can be returned.
+        out = slot.clone() if any(ctx.needs_input_grad[:2]) else slot
         ctx.ep, ctx.plan = ep, plan
         ctx.save_for_backward(rows, weights)
         return out
