@@ -82,3 +82,23 @@ def test_flop_model_subtracts_embeddings():
     n, flops = get_nparams_and_flops(model, cfg, 256)
     assert n == sum(p.numel() for p in model.parameters())
     assert flops < 6 * n + 12 * 2 * 4 * 16 * 256 + 1e9 and flops > 6 * (n - 1024 * 64 * 2)
+
+
+def test_validation_loss_and_offload_context_cpu():
+    import torch
+    from uttt_b200.config import named_config
+    from uttt_b200.eval.validate import validation_loss
+    from uttt_b200.models import build_model
+    from uttt_b200.train.data import SyntheticZipfTokens
+    from uttt_b200.utils.activation_offload import offload_activations
+    cfg = named_config("tiny-uttt-moe")
+    model = build_model(cfg)
+    out = validation_loss(model, SyntheticZipfTokens(cfg.vocab_size, 128, 2, seed=3), max_batches=2)
+    assert out["tokens"] == 2 * 2 * 127 and 0 < out["loss"] < 20 and out["perplexity"] > 1
+    # on CPU tensors the offloading context changes nothing
+    lin = torch.nn.Linear(8, 8)
+    x = torch.randn(4, 8, requires_grad=True)
+    with offload_activations(min_bytes=0) as off:
+        y = lin(x).relu().sum()
+    y.backward()
+    assert off.tensors_offloaded == 0 and x.grad is not None

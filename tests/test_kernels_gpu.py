@@ -544,6 +544,21 @@ def test_frobenius_normalize_forward_backward(dtype):
     _close(d, dr, 2e-3 if dtype == torch.float32 else 2e-2, 2e-2, "dg")
 
 
+def test_activation_offload_round_trip():
+    _ext()
+    from uttt_b200.utils.activation_offload import offload_activations
+    torch.manual_seed(27)
+    lin = torch.nn.Linear(256, 256).to(DEV)
+    x = torch.randn(512, 256, device=DEV, requires_grad=True)
+    ref_out = (lin(x).relu() ** 2).sum()
+    (gref,) = torch.autograd.grad(ref_out, x)
+    with offload_activations(min_bytes=1024) as off:
+        out = (lin(x).relu() ** 2).sum()
+    (g,) = torch.autograd.grad(out, x)
+    assert off.tensors_offloaded > 0 and off.bytes_offloaded >= 512 * 256 * 4
+    _close(g, gref, 0, 0, "grad through offloaded activations")
+
+
 def test_plucker_embed():
     _ext()
     from uttt_b200.nvs.data import SyntheticScenes
