@@ -744,14 +744,12 @@ __global__ void unpermute_rows_bwd_kernel(const T* __restrict__ dout, const T* _
 // Zero rows [offsets[g] + sizes[g], offsets[g + 1]) of every group: the tile padding that token reductions read.
 __global__ void zero_pad_rows_kernel(uint4* __restrict__ out, const int* __restrict__ offsets,
                                      const int* __restrict__ sizes, int groups, int vec_per_row) {
-  const int lane = threadIdx.x & 31;
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int nwarps = (gridDim.x * blockDim.x) >> 5;
-  for (int g = warp; g < groups; g += nwarps) {
-    const int begin = offsets[g] + sizes[g], end = offsets[g + 1];
-    for (int r = begin; r < end; ++r)
-      for (int v = lane; v < vec_per_row; v += 32) out[(size_t)r * vec_per_row + v] = make_uint4(0, 0, 0, 0);
-  }
+  // one block per group: its (< 128) padding rows are cleared by all threads together
+  const int g = blockIdx.x;
+  if (g >= groups) return;
+  const int begin = offsets[g] + sizes[g], end = offsets[g + 1];
+  const long long first = (long long)begin * vec_per_row, n = (long long)(end - begin) * vec_per_row;
+  for (long long i = threadIdx.x; i < n; i += blockDim.x) out[first + i] = make_uint4(0, 0, 0, 0);
 }
 
 // A [rows_padded, d] buffer for a scatter into the tile-padded layout.  With the layout's offsets / sizes only
@@ -765,7 +763,7 @@ static at::Tensor padded_buffer(int64_t rows_padded, int d, const at::TensorOpti
   TORCH_CHECK(offsets->scalar_type() == at::kInt && sizes->scalar_type() == at::kInt &&
               offsets->numel() == sizes->numel() + 1 && (d * out.element_size()) % 16 == 0);
   int groups = sizes->numel();
-  zero_pad_rows_kernel<<<std::max(1, (groups + 7) / 8), 256, 0, cur_stream()>>>(
+  zero_pad_rows_kernel<<<std::max(1, groups), 256, 0, cur_stream()>>>(
       reinterpret_cast<uint4*>(out.data_ptr()), offsets->data_ptr<int>(), sizes->data_ptr<int>(), groups,
       (int)(d * out.element_size() / 16));
   C10_CUDA_KERNEL_LAUNCH_CHECK();

@@ -78,16 +78,35 @@ __global__ void __launch_bounds__(256) router_fwd_kernel(const T* __restrict__ r
   };
   const int steps = (R + BR - 1) / BR;
   const int vec_per_row = D / VEC;
+  // the next step's rows are fetched into registers while this step is being multiplied
+  constexpr int MAXP = 16;                           // 16-byte pieces per thread and step (D <= 512)
+  uint4 pre[MAXP];
+  auto fetch = [&](int step) {
+    const int rb = step * BR;
+#pragma unroll
+    for (int j = 0; j < MAXP; ++j) {
+      const int i = threadIdx.x + j * 256;
+      if (i < BR * vec_per_row) {
+        const int r = i / vec_per_row, v = i - r * vec_per_row;
+        const int rr = min(rb + r, R - 1);
+        pre[j] = *reinterpret_cast<const uint4*>(rows + (size_t)rr * D + v * VEC);
+      }
+    }
+  };
+  if ((int)blockIdx.x < steps) fetch(blockIdx.x);
   for (int step = blockIdx.x; step < steps; step += gridDim.x) {
     const int rb = step * BR;
     __syncthreads();                                 // previous step's readers are done (and wt is written)
-    for (int i = threadIdx.x; i < BR * vec_per_row; i += blockDim.x) {
-      int r = i / vec_per_row, v = i - r * vec_per_row;
-      int rr = min(rb + r, R - 1);
-      *reinterpret_cast<uint4*>(xs + (size_t)r * D + v * VEC) =
-          *reinterpret_cast<const uint4*>(rows + (size_t)rr * D + v * VEC);
+#pragma unroll
+    for (int j = 0; j < MAXP; ++j) {
+      const int i = threadIdx.x + j * 256;
+      if (i < BR * vec_per_row) {
+        const int r = i / vec_per_row, v = i - r * vec_per_row;
+        *reinterpret_cast<uint4*>(xs + (size_t)r * D + v * VEC) = pre[j];
+      }
     }
     __syncthreads();
+    if (step + (int)gridDim.x < steps) fetch(step + gridDim.x);
     const int r0 = rb + warp * RPW;
     float acc[RPW][EPL];
 #pragma unroll

@@ -770,7 +770,8 @@ at::Tensor gg_tn_segments(at::Tensor a, at::Tensor b, at::Tensor offsets, int64_
   bool acc = accumulate_into.has_value() && accumulate_into->defined();
   if (acc) {
     out = *accumulate_into;
-    TORCH_CHECK(out.scalar_type() == at::kFloat && out.is_contiguous() && out.numel() == (int64_t)G * M * N);
+    TORCH_CHECK((out.scalar_type() == at::kFloat || out.scalar_type() == at::kBFloat16) && out.is_contiguous() &&
+                out.numel() == (int64_t)G * M * N);
   } else {
     out = at::empty({G, M, N}, a.options().dtype(out_dtype));
   }

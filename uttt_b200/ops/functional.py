@@ -595,7 +595,7 @@ def _gg_dims_ok(k: int, n: int) -> bool:
 # --------------------------------------------------------------------------- gradient sinks for shared weights
 # A fast-weight bank is read by every layer of a chunk and by every writer of the chunk boundary, so ~2 L weight
 # gradients of the full bank size meet at one tensor.  Left to autograd that is ~2 L bank-sized adds per chunk.
-# With a sink, every consumer's token-reduction GEMM adds its contribution into ONE fp32 buffer inside the GEMM
+# With a sink, every consumer's token-reduction GEMM adds its contribution into ONE buffer inside the GEMM
 # epilogue and reports no gradient; the sink node hands the buffer to the producer of the bank.
 _GRAD_SINKS = {}
 
@@ -624,7 +624,7 @@ class _GradSink(torch.autograd.Function):
 
 def grad_sink(w: torch.Tensor) -> torch.Tensor:
     """Mark ``w`` (a tensor consumed by many grouped GEMMs) so that its consumers accumulate their weight
-    gradients in one fp32 buffer inside their GEMMs.  Identity in value; a no-op off the kernel path."""
+    gradients in one buffer inside their GEMMs.  Identity in value; a no-op off the kernel path."""
     if w.is_cuda and w.requires_grad and torch.is_grad_enabled() and w.dtype == torch.bfloat16 \
             and w.is_contiguous() and _kernel("gg_tn_segments", w) is not None:
         return _GradSink.apply(w)
@@ -646,8 +646,10 @@ def _sink_add(w: torch.Tensor, a: torch.Tensor, b: torch.Tensor, plan) -> bool:
     if entry is None or not _gg_kernel_ok(a, b) or a.shape[1] % 128 != 0 or b.shape[1] % 64 != 0:
         return False
     if entry[0] is None:
-        entry[0] = torch.zeros(plan.num_groups, a.shape[1], b.shape[1], device=a.device, dtype=torch.float32)
-    _gg_tn_acc_(a, b, plan, entry[0])
+        # accumulated in the dtype of the bank (what autograd's own summation would use), at half the traffic of fp32
+        entry[0] = torch.zeros(plan.num_groups, a.shape[1], b.shape[1], device=a.device, dtype=w.dtype)
+    cuda_ext(a).gg_tn_segments(a.contiguous(), b.contiguous(), plan.offsets, plan.num_groups, 1, entry[0].dtype,
+                               entry[0])
     return True
 
 
