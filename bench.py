@@ -98,8 +98,13 @@ def run_ours(args):
     cfg = named_config(args.model, memory_update_backward_mode=args.backward_mode,
                        memory_expert_parallel=max(1, args.expert_parallel))
     seq = args.seq_len
+    keep_arg = args.keep_activation_layers
+    if keep_arg == "auto":
+        # two of the 24 layers keep their activations (about 18 GB each at 4 x 32K tokens): 140 GB peak on a 180 GB part
+        keep_arg = "0,12" if (args.model == "760M-uttt-moe" and args.micro_batch * args.seq_len <= 4 * 32768) else ""
+    keep = tuple(int(i) for i in keep_arg.split(",") if i.strip())
     eng = TrainEngine(cfg, EngineConfig(micro_batch_size=args.micro_batch, lr=1e-3, eps=1e-15, warmup_steps=1024,
-                                        total_steps=40960, seed=42), dev)
+                                        total_steps=40960, seed=42, keep_activation_layers=keep), dev)
     data = SyntheticZipfTokens(cfg.vocab_size, seq, args.per_gpu_batch, seed=1234, rank=rank, world=world)
     n_params = eng.trainer.num_parameters()
 
@@ -156,6 +161,8 @@ def run_ours(args):
                        "parallelism": (f"fsdp{world}" if world > 1 else "single")
                        + (f"+ep{args.expert_parallel}" if args.expert_parallel > 1 else ""),
                        "backward_mode": args.backward_mode,
+                       "activation_recompute": "per (chunk, layer) and per chunk write" + (
+                           f"; layers {list(keep)} keep their activations" if keep else ""),
                        "cache": "inputs and per-step working set are far larger than L2 (no flush needed)"},
             "clocks": clocks,
             "e2e": {"value": tokens_per_step / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
@@ -180,6 +187,8 @@ def main():
     ap.add_argument("--per-gpu-batch", type=int, default=4)
     ap.add_argument("--micro-batch", type=int, default=int(os.environ.get("UTTT_BENCH_MICRO_BATCH", "4")))
     ap.add_argument("--backward-mode", default="full")
+    ap.add_argument("--keep-activation-layers", default=os.environ.get("UTTT_BENCH_KEEP_LAYERS", "auto"),
+                    help="comma-separated layer indices whose activations are kept instead of recomputed")
     ap.add_argument("--expert-parallel", type=int, default=1,
                     help="shard the experts of the pool over this many ranks (default: pool state stays with its "
                          "sequence's rank, as in the reference)")

@@ -147,6 +147,9 @@ class UTTTMoEModel(nn.Module):
         else:
             self.writer_layers = tuple(sorted(int(i) for i in write_layers))
         self.activation_checkpoint = True
+        # layers whose (chunk, layer) regions keep their activations instead of recomputing them in backward:
+        # trades spare HBM for one forward pass of those layers
+        self.keep_activation_layers = frozenset()
         self.ep = None
         if config.use_memory_block:
             self._init_pool_parameters()
@@ -461,8 +464,9 @@ class UTTTMoEModel(nn.Module):
                 else:
                     w02 = w1 = router = bias = None
                 k_hist, v_hist = hist[li]
-                h, x_in, k_flat, v_flat, k_rot, v_new, p, c = self._ckpt(
-                    layer, h, k_hist, v_hist, w02, w1, router, bias, start)
+                run = layer.__call__ if li in self.keep_activation_layers else (
+                    lambda *a, _layer=layer: self._ckpt(_layer, *a))
+                h, x_in, k_flat, v_flat, k_rot, v_new, p, c = run(h, k_hist, v_hist, w02, w1, router, bias, start)
                 hist[li] = trim_history(k_hist, v_hist, k_rot, v_new, keep)
                 feats.append((x_in, k_flat, v_flat))
                 layer_probs.append(p)

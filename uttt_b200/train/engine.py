@@ -37,6 +37,7 @@ class EngineConfig:
     skip_nan_inf: bool = True
     seed: int = 42
     activation_checkpoint: bool = True
+    keep_activation_layers: tuple = ()     # layer indices that skip recomputation (needs spare device memory)
 
 
 def init_distributed(backend: Optional[str] = None) -> tuple[int, int, int]:
@@ -73,6 +74,8 @@ class TrainEngine:
         inner = getattr(self.model, "model", None)
         if inner is not None and hasattr(inner, "activation_checkpoint"):
             inner.activation_checkpoint = self.cfg.activation_checkpoint
+            if hasattr(inner, "keep_activation_layers"):
+                inner.keep_activation_layers = frozenset(int(i) for i in self.cfg.keep_activation_layers)
         self.expert_parallel = None
         ep_size = int(getattr(model_config, "memory_expert_parallel", 1) or 1)
         if ep_size > 1:
