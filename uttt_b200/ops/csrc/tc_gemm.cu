@@ -597,231 +597,6 @@ __global__ void __launch_bounds__(192) tc_gemm_persistent_kernel(const __grid_co
   if (warp == 4) ptx::tmem_dealloc(tmem_base, kTmemCols);
 }
 
-// ------------------------------------------------------------------------------------ resident-A variant
-// For the grouped NT / NN products with a short reduction (K <= 384, i.e. at most six 64-wide k blocks) the A tile
-// of a 128-row tile (<= 96 KB) is kept in shared memory while the CTA sweeps several 256-wide N tiles, so only B
-// streams through the ring: per output tile the operand traffic from L2 drops from (128 + 256) K to
-// (128 / sweep + 256) K elements.  A work unit is (row tile, part of the N range); units are dealt round-robin to the
-// persistent CTAs.  Each k block of A has its own full / empty barrier pair, so the next unit's A block is reloaded
-// as soon as the last N tile of the current unit has consumed it.
-constexpr int kResaMaxKb = 6;
-constexpr int kResaBN = 256;
-constexpr int kResaStages = 3;
-struct ResaSmem {
-  static constexpr int kABytes = BM * BK * 2;                       // one k block of A
-  static constexpr int kBBytes = kResaBN * BK * 2;
-  static constexpr int kBOffset = kResaMaxKb * kABytes;
-  static constexpr int kOutOffset = kBOffset + kResaStages * kBBytes;
-  static constexpr int kOutBytes = 4 * 2 * 4096;
-  static constexpr int kBarOffset = kOutOffset + kOutBytes;
-  static constexpr int kNumBars = 2 * kResaStages + 2 * kResaMaxKb + 4;
-  static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16 + 1024;
-};
-
-template <int MODE, typename OutT>
-__global__ void __launch_bounds__(192) tc_gemm_resa_kernel(const __grid_constant__ CUtensorMap tma_a,
-                                                           const __grid_constant__ CUtensorMap tma_b,
-                                                           const __grid_constant__ CUtensorMap tma_out, GemmParams p,
-                                                           int row_tiles, int tiles_n, int nsplit) {
-  static_assert(MODE == kNT || MODE == kNN, "resident-A variant serves the grouped NT / NN products");
-  using L = ResaSmem;
-  constexpr int BN = kResaBN;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
-  const uint32_t bar_base = smem_base + L::kBarOffset;
-  auto b_full = [&](int s) { return bar_base + 8u * s; };
-  auto b_empty = [&](int s) { return bar_base + 8u * (kResaStages + s); };
-  auto a_full = [&](int k) { return bar_base + 8u * (2 * kResaStages + k); };
-  auto a_empty = [&](int k) { return bar_base + 8u * (2 * kResaStages + kResaMaxKb + k); };
-  auto acc_full = [&](int b) { return bar_base + 8u * (2 * kResaStages + 2 * kResaMaxKb + b); };
-  auto acc_empty = [&](int b) { return bar_base + 8u * (2 * kResaStages + 2 * kResaMaxKb + 2 + b); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + L::kBarOffset + L::kNumBars * 8);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  {
-    __shared__ int prior_failure;
-    if (threadIdx.x == 0) prior_failure = (p.status != nullptr) ? *(volatile int*)p.status : 0;
-    __syncthreads();
-    if (prior_failure != 0) return;
-  }
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kResaStages; ++s) {
-      ptx::mbar_init(b_full(s), 1);
-      ptx::mbar_init(b_empty(s), 1);
-    }
-    for (int k = 0; k < kResaMaxKb; ++k) {
-      ptx::mbar_init(a_full(k), 1);
-      ptx::mbar_init(a_empty(k), 1);
-    }
-    for (int b = 0; b < 2; ++b) {
-      ptx::mbar_init(acc_full(b), 1);
-      ptx::mbar_init(acc_empty(b), 128);
-    }
-    ptx::mbar_fence_init();
-    ptx::tma_prefetch_desc(&tma_a);
-    ptx::tma_prefetch_desc(&tma_b);
-    ptx::tma_prefetch_desc(&tma_out);
-  }
-  constexpr uint32_t kTmemCols = 2 * BN;
-  if (warp == 4) {
-    ptx::tmem_alloc(ptx::smem_u32(tmem_slot), kTmemCols);
-    ptx::tmem_relinquish();
-  }
-  ptx::tc_fence_before_sync();
-  __syncthreads();
-  ptx::tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_slot;
-  OutT* out = reinterpret_cast<OutT*>(p.out);
-  const int ldo = p.N;
-  const int nkb = p.K / BK;
-  const int per = tiles_n / nsplit;                 // N tiles per unit
-  const int total_units = row_tiles * nsplit;
-
-  if (warp == 4) {
-    if (lane == 0) {
-      // ================= TMA producer =================
-      uint32_t bit = 0, a_use = 0;
-      bool ok = true;
-      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
-        const int t = u / nsplit, part = u - t * nsplit;
-        const int g = p.tile_group[t];
-        if (g < 0) continue;
-        for (int j = 0; j < per && ok; ++j) {
-          const int n0 = (part * per + j) * BN;
-          for (int kb = 0; kb < nkb; ++kb, ++bit) {
-            if (j == 0) {
-              // this k block of A was last read by the final N tile of the previous unit
-              ok = ptx::mbar_wait(a_empty(kb), (a_use & 1) ^ 1, p.status, 25);
-              if (!ok) break;
-              ptx::mbar_expect_tx(a_full(kb), L::kABytes);
-              ptx::tma_load_2d(smem_base + kb * L::kABytes, &tma_a, a_full(kb), kb * BK, t * BM);
-            }
-            const int s = bit % kResaStages;
-            ok = ptx::mbar_wait(b_empty(s), ((bit / kResaStages) & 1) ^ 1, p.status, 26);
-            if (!ok) break;
-            const uint32_t sb = smem_base + L::kBOffset + s * L::kBBytes;
-            ptx::mbar_expect_tx(b_full(s), L::kBBytes);
-            if (MODE == kNT) {
-              ptx::tma_load_2d(sb, &tma_b, b_full(s), kb * BK, g * p.N + n0);
-            } else {
-#pragma unroll
-              for (int q = 0; q < BN / 64; ++q)
-                ptx::tma_load_2d(sb + q * (BK * 128), &tma_b, b_full(s), n0 + 64 * q, g * p.K + kb * BK);
-            }
-          }
-        }
-        ++a_use;
-      }
-    }
-  } else if (warp == 5) {
-    if (lane == 0) {
-      // ================= MMA issuer =================
-      constexpr int b_mn = (MODE == kNN) ? 1 : 0;
-      constexpr uint32_t idesc = ptx::make_instr_desc(BM, BN, 0, b_mn);
-      uint32_t bit = 0, a_use = 0, acc_it = 0;
-      bool ok = true;
-      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
-        const int t = u / nsplit;
-        if (p.tile_group[t] < 0) continue;
-        for (int j = 0; j < per && ok; ++j) {
-          const int ab = acc_it & 1;
-          ok = ptx::mbar_wait(acc_empty(ab), ((acc_it >> 1) & 1) ^ 1, p.status, 27);
-          if (!ok) break;
-          ptx::tc_fence_after_sync();
-          const uint32_t tmem_acc = tmem_base + ab * BN;
-          for (int kb = 0; kb < nkb; ++kb, ++bit) {
-            if (j == 0) {
-              ok = ptx::mbar_wait(a_full(kb), a_use & 1, p.status, 28);
-              if (!ok) break;
-            }
-            const int s = bit % kResaStages;
-            ok = ptx::mbar_wait(b_full(s), (bit / kResaStages) & 1, p.status, 29);
-            if (!ok) break;
-            ptx::tc_fence_after_sync();
-            const uint32_t sa = smem_base + kb * L::kABytes;
-            const uint32_t sb = smem_base + L::kBOffset + s * L::kBBytes;
-#pragma unroll
-            for (int k = 0; k < BK / 16; ++k) {
-              uint64_t da = ptx::make_smem_desc(sa + k * 32, 16, 1024);
-              uint64_t db = b_mn ? ptx::make_smem_desc(sb + k * 2048, BK * 128, 1024)
-                                 : ptx::make_smem_desc(sb + k * 32, 16, 1024);
-              ptx::mma_bf16_ss(tmem_acc, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-            }
-            ptx::mma_commit(b_empty(s));
-            if (j == per - 1) ptx::mma_commit(a_empty(kb));
-          }
-          if (!ok) break;
-          ptx::mma_commit(acc_full(ab));
-          ++acc_it;
-        }
-        ++a_use;
-      }
-    }
-  } else {
-    // ================= epilogue (warps 0-3): TMEM -> swizzled staging slab -> TMA store =================
-    uint32_t acc_it = 0, slab_it = 0;
-    bool ok = true;
-    const int r = warp * 32 + lane;
-    const uint32_t slab_base = smem_base + L::kOutOffset + warp * 8192;
-    static_assert(sizeof(OutT) == 2, "the resident-A variant writes bf16");
-    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
-      const int t = u / nsplit, part = u - t * nsplit;
-      const bool unused = p.tile_group[t] < 0;
-      for (int j = 0; j < per && ok; ++j) {
-        const int n0 = (part * per + j) * BN;
-        if (unused) {
-          OutT* orow = out + ((size_t)t * BM + r) * ldo + n0;
-          for (int col = 0; col < BN; col += 8) *reinterpret_cast<uint4*>(orow + col) = make_uint4(0, 0, 0, 0);
-          continue;
-        }
-        const int ab = acc_it & 1;
-        ok = ptx::mbar_wait(acc_full(ab), (acc_it >> 1) & 1, p.status, 30);
-        if (!ok) break;
-        ptx::tc_fence_after_sync();
-        const uint32_t tmem_acc = tmem_base + ab * BN + ((uint32_t)(warp * 32) << 16);
-        uint32_t raw[2][64];
-        ptx::tmem_ld_32x64(tmem_acc, *reinterpret_cast<uint32_t (*)[64]>(&raw[0][0]));
-        ptx::tmem_ld_wait();
-#pragma unroll
-        for (int ci = 0; ci < BN / 64; ++ci) {
-          const int buf = ci & 1;
-          if (ci + 1 < BN / 64)
-            ptx::tmem_ld_32x64(tmem_acc + (ci + 1) * 64, *reinterpret_cast<uint32_t (*)[64]>(&raw[buf ^ 1][0]));
-          const uint32_t slab = slab_base + (slab_it & 1) * 4096;
-          if (lane == 0) ptx::tma_store_wait_read<1>();
-          __syncwarp();
-#pragma unroll
-          for (int i = 0; i < 64; i += 8) {
-            uint32_t w[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(raw[buf][i + 2 * q]),
-                                                       __uint_as_float(raw[buf][i + 2 * q + 1]));
-              w[q] = *reinterpret_cast<uint32_t*>(&h);
-            }
-            ptx::st_shared_v4(slab + lane * 128 + (((i / 8) ^ (lane & 7)) << 4), w[0], w[1], w[2], w[3]);
-          }
-          ptx::fence_proxy_async();
-          __syncwarp();
-          if (lane == 0) {
-            ptx::tma_store_2d(&tma_out, slab, n0 + ci * 64, t * BM + warp * 32);
-            ptx::tma_store_commit();
-          }
-          ++slab_it;
-          if (ci + 1 < BN / 64) ptx::tmem_ld_wait();
-        }
-        ptx::tc_fence_before_sync();
-        ptx::mbar_arrive(acc_empty(ab));
-        ++acc_it;
-      }
-    }
-    if (lane == 0) ptx::tma_store_wait_all();
-  }
-  ptx::tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 4) ptx::tmem_dealloc(tmem_base, kTmemCols);
-}
-
 // ------------------------------------------------------------------------------------ host side
 static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
   static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
@@ -931,38 +706,6 @@ static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams
   }
 }
 
-// Resident-A launch for the grouped NT / NN products (see tc_gemm_resa_kernel); returns false when it does not apply.
-template <int MODE>
-static bool launch_resa(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, int R) {
-  static int enabled = -1;
-  if (enabled < 0) {
-    const char* e = std::getenv("UTTT_B200_GEMM_RESIDENT_A");
-    enabled = (e != nullptr && std::string(e) == "0") ? 0 : 1;
-  }
-  if (!enabled || !use_persistent() || p.K > kResaMaxKb * BK || p.N % kResaBN != 0) return false;
-  const int row_tiles = R / BM, tiles_n = p.N / kResaBN;
-  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
-  // split the N range of a row tile just enough to give every CTA several units
-  int nsplit = tiles_n;
-  for (int d = 1; d <= tiles_n; ++d) {
-    if (tiles_n % d == 0 && (long long)row_tiles * d >= 6LL * sms) { nsplit = d; break; }
-  }
-  auto kernel = tc_gemm_resa_kernel<MODE, __nv_bfloat16>;
-  static bool configured = false;
-  if (!configured) {
-    C10_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ResaSmem::kTotal));
-    configured = true;
-  }
-  p.out_rows = R;
-  CUtensorMap tout = make_tmap_2d(p.out, (uint64_t)R, (uint64_t)p.N, 32, 64, false);
-  const int ctas = std::min(row_tiles * nsplit, sms);
-  kernel<<<ctas, 192, ResaSmem::kTotal, at::cuda::getCurrentCUDAStream().stream()>>>(ta, tb, tout, p, row_tiles,
-                                                                                   tiles_n, nsplit);
-  C10_CUDA_KERNEL_LAUNCH_CHECK();
-  count_launch();
-  return true;
-}
-
 static int pick_bn(int n) {
   if (n % 256 == 0) return 256;
   if (n % 192 == 0 && use_persistent()) return 192;
@@ -983,7 +726,6 @@ at::Tensor gg_nt(at::Tensor x, at::Tensor w, at::Tensor tile_group) {
   p.status = status_word(x.device()).data_ptr<int>();
   const int bn = pick_bn(N);
   auto tb = make_tmap_2d_bf16(w.data_ptr(), (uint64_t)G * N, K, bn, BK);
-  if (bn == 256 && launch_resa<kNT>(ta, tb, p, R)) return out;
   dim3 grid(N / bn, R / BM);
   if (bn == 256) launch_gemm<kNT, 256, __nv_bfloat16>(ta, tb, p, grid);
   else if (bn == 192) launch_gemm<kNT, 192, __nv_bfloat16>(ta, tb, p, grid);
@@ -1006,7 +748,6 @@ at::Tensor gg_nn(at::Tensor x, at::Tensor w, at::Tensor tile_group) {
   p.groups = G; p.N = N; p.K = K; p.out = out.data_ptr(); p.out_rows = R;
   p.status = status_word(x.device()).data_ptr<int>();
   const int bn = pick_bn(N);
-  if (bn == 256 && launch_resa<kNN>(ta, tb, p, R)) return out;
   dim3 grid(N / bn, R / BM);
   if (bn == 256) launch_gemm<kNN, 256, __nv_bfloat16>(ta, tb, p, grid);
   else if (bn == 192) launch_gemm<kNN, 192, __nv_bfloat16>(ta, tb, p, grid);
