@@ -733,6 +733,9 @@ def gg_tn(a, b, plan: GroupPlan, out_dtype: torch.dtype = torch.float32):
     """out[g] = sum_{r in group g} a[r]^T b[r];  a [R, M], b [R, N] -> [G, M, N] (fp32 accumulation)."""
     if _gg_kernel_ok(a, b) and a.shape[1] % 128 == 0 and b.shape[1] % 64 == 0:
         return _GGTN.apply(a, b, plan, out_dtype)
+    if _gg_kernel_ok(a, b) and b.shape[1] % 128 == 0 and a.shape[1] % 64 == 0:
+        # the kernel wants 128 rows of output per tile: compute the transposed product and view it back
+        return _GGTN.apply(b, a, plan, out_dtype).transpose(1, 2)
     return ref.gg_tn(a, b, plan.tile_group, plan.num_groups, out_dtype)
 
 

@@ -203,6 +203,8 @@ def gg_tn(a: torch.Tensor, b: torch.Tensor, tile_group: torch.Tensor, num_groups
     """out[g] = sum_{r in g} a[r]^T b[r] ; a: [R, M], b: [R, N] -> [G, M, N] (fp32 accumulation)."""
     t = a.shape[0] // TILE_ROWS
     part = torch.bmm(a.view(t, TILE_ROWS, -1).transpose(1, 2), b.view(t, TILE_ROWS, -1)).float()
+    # rows of tiles that belong to no group are undefined on the kernel path: select them away (not multiply)
+    part = torch.where((tile_group[:t] >= 0).view(-1, 1, 1), part, torch.zeros((), dtype=part.dtype, device=part.device))
     out = torch.zeros(num_groups, a.shape[1], b.shape[1], device=a.device, dtype=torch.float32)
     out.index_add_(0, _tile_groups(tile_group)[:t], part)
     return out.to(out_dtype)
