@@ -680,3 +680,45 @@ def test_lvsm_gpu_matches_cpu():
             continue
         cos.append(float(F.cosine_similarity(a.grad.float().cpu().flatten(), b_.grad.flatten(), dim=0)))
     assert sum(c > 0.9 for c in cos) >= 0.75 * len(cos), sorted(cos)[:8]
+
+
+def test_cached_generation_on_gpu_matches_one_shot_forward():
+    """Incremental decoding through the kernels (single-token attention calls, routing of one row per head)."""
+    _ext()
+    from uttt_b200.config import named_config
+    from uttt_b200.models import build_model
+    from uttt_b200.models.generation import generate
+    torch.manual_seed(0)
+    cfg = named_config("tiny-uttt-moe", hidden_size=256, num_heads=4, fw_num_heads=2, memory_num_experts=4,
+                       memory_num_active_experts=2, chunk_size=64, window_size=64)
+    model = build_model(cfg).to(DEV).to(torch.bfloat16).eval()
+    ids = torch.randint(0, cfg.vocab_size, (1, 160), device=DEV)
+    with torch.no_grad():
+        full = model(input_ids=ids).logits.float()
+        out = model(input_ids=ids[:, :100], use_cache=True)
+        parts = [out.logits.float()]
+        cache = out.past_key_values
+        for t in range(100, 160):
+            out = model(input_ids=ids[:, t:t + 1], past_key_values=cache, use_cache=True)
+            cache = out.past_key_values
+            parts.append(out.logits.float())
+    got = torch.cat(parts, dim=1)
+    torch.cuda.synchronize()
+    _status_ok()
+    assert torch.isfinite(got).all()
+    # bf16 end to end: compare the distributions, not the raw logits
+    agree = (got.argmax(-1) == full.argmax(-1)).float().mean().item()
+    assert agree > 0.9, agree
+    _close(torch.log_softmax(got, -1), torch.log_softmax(full, -1), 0.25, 0.0, "log-probs")
+    toks = generate(model, ids[:, :10], max_new_tokens=5)
+    assert toks.shape == (1, 15)
+
+
+@pytest.mark.parametrize("mode", ["cross_layer_cut", "first_order_state", "stop_state"])
+def test_backward_modes_gpu_match_cpu(mode):
+    _ext()
+    from uttt_b200.config import named_config
+    cfg = named_config("tiny-uttt-moe", hidden_size=256, num_heads=4, fw_num_heads=2, memory_num_experts=4,
+                       memory_num_active_experts=2, chunk_size=128, window_size=128, memory_lb_loss_alpha=0.0,
+                       memory_update_backward_mode=mode)
+    _gpu_vs_cpu_lm(cfg, seq=384, frac=0.75)
