@@ -207,3 +207,24 @@ def test_metrics():
     assert float(ssim(a, noisy).mean()) < 0.99
     ci = bootstrap_ci([20.0, 21.0, 22.0, 23.0], resamples=2000)
     assert ci["ci_low"] <= ci["mean"] <= ci["ci_high"]
+
+
+def test_debug_helpers_and_trace_ranges():
+    from uttt_b200.nvs.debug import RouterTrace, log_status, sketch_tensor
+    from uttt_b200.utils import trace
+    t = torch.tensor([[1.0, 2.0], [float("nan"), 4.0]])
+    s = sketch_tensor(t, "x")
+    assert s["non_finite"] == 1 and s["shape"] == [2, 2] and abs(s["max"] - 4.0) < 1e-6
+    lines = []
+    rows = log_status({"a": torch.ones(3), "b": torch.zeros(0)}, lines.append)
+    assert len(rows) == 2 and len(lines) == 1 and lines[0].startswith("a")
+    tr = RouterTrace()
+    tr(0, "read", torch.tensor([[3.0, 1.0]]), torch.tensor([[2.0, 2.0]]))
+    assert tr.summary()["freq_max"] == 0.75
+    trace.enable(True)
+    try:
+        with trace.trace_range("unit-test"):
+            pass
+    finally:
+        trace.enable(False)
+    assert not trace.enabled()

@@ -26,6 +26,7 @@ from torch.utils.checkpoint import checkpoint
 from .. import ops
 from ..config import LMConfig
 from . import fast_weights as fw
+from ..utils.trace import trace_range
 from .common import (GatedMLP, LowRankFastWeight, RMSNorm, SlidingWindowAttention, init_linear_weights,
                      inv_softplus, trim_history)
 
@@ -466,7 +467,8 @@ class UTTTMoEModel(nn.Module):
                 k_hist, v_hist = hist[li]
                 run = layer.__call__ if li in self.keep_activation_layers else (
                     lambda *a, _layer=layer: self._ckpt(_layer, *a))
-                h, x_in, k_flat, v_flat, k_rot, v_new, p, c = run(h, k_hist, v_hist, w02, w1, router, bias, start)
+                with trace_range(f"chunk{start // chunk}.layer{li}.read"):
+                    h, x_in, k_flat, v_flat, k_rot, v_new, p, c = run(h, k_hist, v_hist, w02, w1, router, bias, start)
                 hist[li] = trim_history(k_hist, v_hist, k_rot, v_new, keep)
                 feats.append((x_in, k_flat, v_flat))
                 layer_probs.append(p)
@@ -476,7 +478,8 @@ class UTTTMoEModel(nn.Module):
                 apply_probs = apply_probs + torch.stack(layer_probs)
                 apply_counts = apply_counts + torch.stack(layer_counts)
                 if end < seq_len:   # apply-then-update; the last chunk never writes
-                    states, up, uc = self._chunk_write(states, feats, start)
+                    with trace_range(f"chunk{start // chunk}.write"):
+                        states, up, uc = self._chunk_write(states, feats, start)
                     update_probs = update_probs + up
                     update_counts = update_counts + uc
         hidden = self.norm(torch.cat(outputs, dim=1))

@@ -30,6 +30,7 @@ import torch.distributed as dist
 from ..ops import functional as F_ops
 from ..ops import reference as ref
 from ..ops._ext import load
+from ..utils.trace import trace_range
 
 TILE = ref.TILE_ROWS
 
@@ -157,7 +158,8 @@ class ExpertParallel:
     def dispatch(self, rows: torch.Tensor, weights: Optional[torch.Tensor], plan: EPPlan) -> torch.Tensor:
         """rows [R, D] (optionally scaled per routed copy by weights [R, k]) -> owner layout [rows_owner, D]."""
         if self.transport == "peer":
-            return _PeerDispatch.apply(rows, weights, self, plan)
+            with trace_range("ep.dispatch"):
+                return _PeerDispatch.apply(rows, weights, self, plan)
         import torch.distributed.nn.functional as dnn
         r, d = rows.shape
         k = plan.idx.shape[1]
@@ -171,7 +173,8 @@ class ExpertParallel:
     def combine(self, yp: torch.Tensor, weights: Optional[torch.Tensor], plan: EPPlan) -> torch.Tensor:
         """Owner layout [rows_owner, D] -> [R, D]: y[r] = sum_j weights[r, j] * (row of copy (r, j))."""
         if self.transport == "peer":
-            return _PeerCombine.apply(yp, weights, self, plan)
+            with trace_range("ep.combine"):
+                return _PeerCombine.apply(yp, weights, self, plan)
         import torch.distributed.nn.functional as dnn
         d = yp.shape[1]
         back = yp.new_empty(plan.send_rows, d)

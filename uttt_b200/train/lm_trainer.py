@@ -143,6 +143,11 @@ def main(job: Optional[JobConfig] = None) -> TrainState:
                        schedule=schedule(wait=max(job.profiling.profile_freq - 2, 0), warmup=1, active=1),
                        on_trace_ready=tensorboard_trace_handler(folder))
         prof.start()
+        from ..utils import trace
+        trace.enable(True)            # named ranges per chunk / layer / write show up in the trace
+    snapshot = bool(job.profiling.enable_memory_snapshot) and torch.cuda.is_available()
+    if snapshot:
+        torch.cuda.memory._record_memory_history(max_entries=100000)
     t0 = time.perf_counter()
     while state.step < job.training.steps:
         os.environ["FLAME_TRAIN_STEP"] = str(state.step + 1)
@@ -164,6 +169,11 @@ def main(job: Optional[JobConfig] = None) -> TrainState:
             prof.step()
     if prof is not None:
         prof.stop()
+    if snapshot:
+        folder = os.path.join(job.job.dump_folder, job.profiling.save_memory_snapshot_folder)
+        os.makedirs(folder, exist_ok=True)
+        torch.cuda.memory._dump_snapshot(os.path.join(folder, f"rank{rank}_memory_snapshot.pickle"))
+        torch.cuda.memory._record_memory_history(enabled=None)
     if dist.is_available() and dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()
