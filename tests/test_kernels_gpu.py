@@ -131,7 +131,9 @@ def _plan(bsz=2, n=700, e=4, k=2, seed=0):
     return ops.build_group_plan(idx, e)
 
 
-@pytest.mark.parametrize("bsz,n,e,k", [(2, 700, 4, 2), (3, 5000, 32, 2), (1, 64, 1, 1), (2, 2048, 96, 1)])
+@pytest.mark.parametrize("bsz,n,e,k", [(2, 700, 4, 2), (3, 5000, 32, 2), (1, 64, 1, 1), (2, 2048, 96, 1),
+                                       # small exhaustive shapes: empty groups, groups of one row, odd expert counts
+                                       (1, 3, 5, 2), (2, 1, 3, 1), (4, 129, 2, 2), (1, 128, 5, 1), (3, 2, 2, 2)])
 def test_group_plan_kernel_matches_reference(bsz, n, e, k):
     _ext()
     g = torch.Generator().manual_seed(n)

@@ -48,12 +48,18 @@ def build(verbose: bool = False, force: bool = False) -> str:
     inc, torch_lib = _include_flags()
     abi = f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"
     flags = [f for f in NVCC_FLAGS if not f.startswith("-D_GLIBCXX")] + [abi]
+    build_dir = BUILD
+    if os.environ.get("UTTT_B200_BOUNDS_CHECK", "0") == "1":
+        # checked build: index tables are validated against buffer extents, violations go to the status word
+        flags.append("-DUTTT_BOUNDS_CHECK")
+        build_dir = BUILD + "_checked"
+        os.makedirs(build_dir, exist_ok=True)
     headers = glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(CSRC, "*.h")) + [__file__]
     sources = sorted(glob.glob(os.path.join(CSRC, "*.cu")) + glob.glob(os.path.join(CSRC, "*.cpp")))
     jobs = []
     objs = []
     for src in sources:
-        obj = os.path.join(BUILD, os.path.basename(src) + ".o")
+        obj = os.path.join(build_dir, os.path.basename(src) + ".o")
         objs.append(obj)
         if force or _stale(obj, [src] + headers):
             cmd = [nvcc, "-c", src, "-o", obj] + flags + inc
@@ -64,7 +70,7 @@ def build(verbose: bool = False, force: bool = False) -> str:
     def run(job):
         src, cmd = job
         res = subprocess.run(cmd, capture_output=True, text=True)
-        log = os.path.join(BUILD, os.path.basename(src) + ".log")
+        log = os.path.join(build_dir, os.path.basename(src) + ".log")
         with open(log, "w") as f:
             f.write(" ".join(cmd) + "\n" + res.stdout + res.stderr)
         if res.returncode != 0:
@@ -76,13 +82,23 @@ def build(verbose: bool = False, force: bool = False) -> str:
     if jobs:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             list(ex.map(run, jobs))
-    if jobs or force or _stale(TARGET, objs):
+    # the shared object remembers which flavour it was linked from, so switching flavours relinks
+    marker = TARGET + ".flavour"
+    flavour = "checked" if build_dir != BUILD else "regular"
+    try:
+        with open(marker) as fh:
+            linked = fh.read().strip()
+    except OSError:
+        linked = "regular"
+    if jobs or force or linked != flavour or _stale(TARGET, objs):
         cmd = [nvcc, "-shared", "-o", TARGET] + objs + [
             "-L" + torch_lib, "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python",
             "-lcudart", "-Xlinker", "-rpath", "-Xlinker", torch_lib]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stderr[-4000:]}")
+        with open(marker, "w") as fh:
+            fh.write(flavour)
     return TARGET
 
 

@@ -74,3 +74,15 @@ __device__ __forceinline__ float d2siluf_(float x) {
 }
 
 }  // namespace uttt
+
+// Checked build (-DUTTT_BOUNDS_CHECK, `UTTT_B200_BOUNDS_CHECK=1 python -m uttt_b200.ops.build`): kernels that follow
+// index tables compare every index with the extent of the buffer they address; a violation writes `code` to the
+// status word (first writer wins) and the access is skipped - nothing traps.  In the regular build the macro
+// evaluates to `true` and the compiler removes it.
+#ifdef UTTT_BOUNDS_CHECK
+#define UTTT_INDEX_OK(idx, limit, status, code) \
+  (((long long)(idx) >= 0 && (long long)(idx) < (long long)(limit)) ? true \
+       : (((status) != nullptr ? (void)atomicCAS((status), 0, (code)) : (void)0), false))
+#else
+#define UTTT_INDEX_OK(idx, limit, status, code) (true)
+#endif

@@ -12,6 +12,8 @@
 
 namespace uttt {
 
+at::Tensor gemm_status(at::Tensor like);
+
 unsigned long long g_launch_count = 0;
 
 #define UTTT_DISPATCH_FLOAT(TENSOR, ...)                                            \
@@ -661,11 +663,12 @@ std::vector<at::Tensor> fw_write_pw_bwd(at::Tensor C, at::Tensor Ch, at::Tensor 
 template <typename T>
 __global__ void permute_rows_kernel(const T* __restrict__ x, const int64_t* __restrict__ dest,
                                     const float* __restrict__ w, T* __restrict__ out, size_t n_copies, int k,
-                                    int d) {
+                                    int d, long long rows_out, int* __restrict__ status) {
   size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   int lane = threadIdx.x & 31;
   size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
   for (size_t c = warp; c < n_copies; c += nwarps) {
+    if (!UTTT_INDEX_OK(dest[c], rows_out, status, 71)) continue;
     const T* src = x + (c / k) * d;
     T* dst = out + (size_t)dest[c] * d;
     if (w == nullptr) {
@@ -689,12 +692,18 @@ __global__ void permute_rows_kernel(const T* __restrict__ x, const int64_t* __re
 // out[i] = sum_j w[i,j] * y[dest[i,j]]
 template <typename T>
 __global__ void unpermute_rows_kernel(const T* __restrict__ y, const int64_t* __restrict__ dest,
-                                      const float* __restrict__ w, T* __restrict__ out, size_t rows, int k, int d) {
+                                      const float* __restrict__ w, T* __restrict__ out, size_t rows, int k, int d,
+                                      long long rows_in, int* __restrict__ status) {
   size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   int lane = threadIdx.x & 31;
   size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
   int nv = d >> 3;
   for (size_t r = warp; r < rows; r += nwarps) {
+#ifdef UTTT_BOUNDS_CHECK
+    bool in_range = true;
+    for (int j = 0; j < k; ++j) in_range = UTTT_INDEX_OK(dest[r * k + j], rows_in, status, 72) && in_range;
+    if (!in_range) continue;
+#endif
     for (int v = lane; v < nv; v += 32) {
       float acc[8];
 #pragma unroll
@@ -784,7 +793,8 @@ at::Tensor permute_rows(at::Tensor x, at::Tensor dest, int64_t rows_padded, c10:
   UTTT_DISPATCH_FLOAT(x, {
     permute_rows_kernel<T><<<blocks, 256, 0, cur_stream()>>>(ptr<T>(x), ptr<int64_t>(dest),
                                                             wf.defined() ? ptr<float>(wf) : nullptr, ptr<T>(out), n,
-                                                            k, d);
+                                                            k, d, (long long)rows_padded,
+                                                            gemm_status(x).data_ptr<int>());
   });
   count_launch(2);
   return out;
@@ -803,7 +813,8 @@ at::Tensor unpermute_rows(at::Tensor y, at::Tensor dest, c10::optional<at::Tenso
   UTTT_DISPATCH_FLOAT(y, {
     unpermute_rows_kernel<T><<<blocks, 256, 0, cur_stream()>>>(ptr<T>(y), ptr<int64_t>(dest),
                                                               wf.defined() ? ptr<float>(wf) : nullptr, ptr<T>(out),
-                                                              rows, k, d);
+                                                              rows, k, d, (long long)y.size(0),
+                                                              gemm_status(y).data_ptr<int>());
   });
   count_launch();
   return out;
