@@ -3,7 +3,7 @@
     python -m uttt_b200.ops.microbench [--kernel NAME] [--small] [--iters N]
 
 Kernels: gg_nt, gg_nn, gg_tn, bmm_nt, swa_fwd, swa_bwd, rms_norm, rope, fw_qk_prep, router, pool_step, plucker,
-fw_write_pw, adamw, ce.  ``--small`` runs one small case
+swiglu, permute, patch_decode, frob, fw_write_pw, adamw, ce.  ``--small`` runs one small case
 of the chosen kernel (inputs above L2 size, a few hundred MB on the device) three times, which is what the
 profile summaries under ``profiles/`` were captured from.  Prints one JSON line per case with the achieved
 TFLOP/s or GB/s and the fraction of the measured peaks in ``MEASURED_PEAKS.json`` when present.
@@ -157,6 +157,28 @@ def run(kernel: str, small: bool, iters: int):
         tgt = torch.zeros(v_, dtype=torch.bool, device=dev)
         ms = _time(lambda: F.plucker_embed(img, fx, c2w, tgt, 8), iters, flush)
         rec("plucker_embed[256px]", ms, bytes_=float(img.numel()) * 4 + bsz * v_ * hw * hw * 12 * 4.0)
+    if kernel in ("swiglu", "all"):
+        y02 = torch.randn(rows, 2 * inter, **bf)
+        ms = _time(lambda: F.swiglu(y02), iters, flush)
+        rec("swiglu_fwd", ms, bytes_=2.0 * rows * inter * 3)
+    if kernel in ("permute", "all"):
+        xr = torch.randn(bsz * 8192, d, **bf)
+        ms = _time(lambda: F.permute_rows(xr, plan), iters, flush)
+        rec("permute_rows[top2]", ms, bytes_=2.0 * xr.numel() * 3)
+        yp = torch.randn(rows, d, **bf)
+        wts = torch.rand(bsz * 8192, 2, device=dev)
+        ms = _time(lambda: F.unpermute_rows(yp, plan, wts), iters, flush)
+        rec("unpermute_rows[top2]", ms, bytes_=2.0 * xr.numel() * 3)
+    if kernel in ("patch_decode", "all"):
+        v_, hw = 4, 256
+        yl = torch.randn(bsz, v_ * (hw // 8) ** 2, 192, **bf)
+        tg = torch.rand(bsz, v_, 3, hw, hw, device=dev)
+        ms = _time(lambda: F.patch_decode(yl, tg, v_, hw, hw, 8), iters, flush)
+        rec("patch_decode_fwd[256px]", ms, bytes_=float(yl.numel()) * 2 + tg.numel() * 8.0)
+    if kernel in ("frob", "all"):
+        gmat = torch.randn(bsz * experts * 2, inter, d, device=dev)
+        ms = _time(lambda: F._FrobNormalize.apply(gmat, 1e-7), iters, flush)
+        rec("frob_normalize_fwd", ms, bytes_=float(gmat.numel()) * (4 + 4 + 2))
     if kernel in ("fw_write_pw", "all"):
         ext = load()
         y02 = torch.randn(rows, 2 * inter, **bf)
