@@ -143,3 +143,88 @@ def test_two_gpu_all_gather_fused_gemm(tmp_path):
     mp.spawn(_ag_worker, args=(2, _free_port(), out), nprocs=2, join=True)
     got = torch.load(out, weights_only=False)
     assert got["status"] == 0 and got["ok"]
+
+
+def _multimem_worker(rank: int, world: int, port: int, out_path: str):
+    """Switch-side reduction / broadcast forms of the optimizer-step kernels against the peer-pointer forms."""
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from uttt_b200.parallel.symm import SymmetricHeap
+    n = 1 << 24                                           # elements per buffer, shard = n / world
+    heap = SymmetricHeap(dev, None, capacity_bytes=n * (2 + 4 + 2 + 4) + (1 << 20), use_multimem=True)
+    result = {"supported": heap.use_multimem}
+    if heap.use_multimem:                                 # same answer on every rank: one fabric
+        ext = heap.ext
+        shard = n // world
+        lo = rank * shard
+        ok = True
+        times = {}
+        for dtype in (torch.bfloat16, torch.float32):
+            grad = heap.alloc(n, dtype)
+            comp = heap.alloc(n, dtype)
+            torch.manual_seed(3 + rank)
+            grad.copy_(torch.randint(-8, 9, (n,), device=dev).to(dtype) * 0.25)   # sums are exact in bf16
+            comp.zero_()
+            heap.barrier()
+            outs = []
+            for mc in (0, heap.multicast_addr(grad)):
+                out = torch.empty(shard, dtype=torch.float32, device=dev)
+                sq = torch.zeros(1, device=dev)
+                ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+                for it in range(4):
+                    if it == 3:
+                        ev[0].record()
+                    sq.zero_()
+                    ext.rs_sumsq(heap.peer_ptrs(grad), rank, lo, out, 0.5, sq, dtype == torch.bfloat16, mc)
+                ev[1].record()
+                torch.cuda.synchronize()
+                times[f"rs_{'mc' if mc else 'peer'}_{str(dtype)[6:]}"] = ev[0].elapsed_time(ev[1])
+                outs.append((out, sq.clone()))
+            ok = ok and bool(torch.equal(outs[0][0], outs[1][0])) and bool(
+                torch.allclose(outs[0][1], outs[1][1], rtol=1e-5))
+            heap.barrier()
+            # optimizer step + broadcast: the two forms must leave identical buffers on every rank
+            g = outs[0][0]
+            one = torch.ones(1, device=dev)
+            got = []
+            for mc in (0, heap.multicast_addr(comp)):
+                p = torch.full((shard,), 0.5, device=dev)
+                m = torch.zeros_like(p)
+                v = torch.zeros_like(p)
+                comp.zero_()
+                heap.barrier()
+                ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+                ev[0].record()
+                ext.adamw_scatter(p, g, m, v, heap.peer_ptrs(comp), rank, lo, dtype == torch.bfloat16, 1e-2, 0.9, 0.95,
+                                  1e-8, 0.1, 1, one, one, shard, mc)
+                ev[1].record()
+                heap.barrier()
+                torch.cuda.synchronize()
+                times[f"adamw_{'mc' if mc else 'peer'}_{str(dtype)[6:]}"] = ev[0].elapsed_time(ev[1])
+                got.append(comp.clone())
+                heap.barrier()
+            ok = ok and bool(torch.equal(got[0], got[1])) and bool((got[0] != 0).all())
+        flag = torch.tensor([1.0 if ok else 0.0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        result.update(ok=bool(flag.item() == 1.0), times=times)
+    if rank == 0:
+        torch.save(result, out_path)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+def test_two_gpu_multimem_forms_match_peer_forms(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    out = str(tmp_path / "mm.pt")
+    mp.spawn(_multimem_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    got = torch.load(out, weights_only=False)
+    if not got["supported"]:
+        pytest.skip("the symmetric allocation has no multicast mapping on this box")
+    print("multimem timings (ms):", got["times"])
+    assert got["ok"]

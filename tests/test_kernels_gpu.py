@@ -48,6 +48,68 @@ def test_rms_norm(dtype, d):
     _close(w.grad, wr.grad, 0.5 if dtype == torch.bfloat16 else 1e-3, 3e-2 if dtype == torch.bfloat16 else 1e-4, "dw")
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("d", [384, 1536])
+def test_add_rms_norm(dtype, d):
+    """Residual addition fused with the norm: both outputs and all three gradients against fp32 PyTorch."""
+    _ext()
+    torch.manual_seed(1)
+    x = torch.randn(515, d, device=DEV, dtype=dtype, requires_grad=True)
+    delta = torch.randn(515, d, device=DEV, dtype=dtype, requires_grad=True)
+    w = (torch.randn(d, device=DEV, dtype=dtype) * 0.1 + 1).requires_grad_(True)
+    s, y = ops.add_rms_norm(x, delta, w, 1e-6)
+    gs, gy = torch.randn_like(s), torch.randn_like(y)
+    (s.float() * gs.float()).sum().add((y.float() * gy.float()).sum()).backward()
+    xr, dr, wr = (t.detach().float().requires_grad_(True) for t in (x, delta, w))
+    sr = (xr + dr).to(dtype).float() if dtype == torch.bfloat16 else xr + dr
+    sr_live = xr + dr
+    yr = ref.rms_norm(sr_live, wr, 1e-6)
+    ((sr_live * gs.float()).sum() + (yr * gy.float()).sum()).backward()
+    tol = dict(atol=3e-2, rtol=3e-2) if dtype == torch.bfloat16 else dict(atol=1e-5, rtol=1e-5)
+    _close(s, sr, 1e-6 if dtype == torch.float32 else 0.0, 0.0, "sum")       # the rounded sum itself is exact
+    _close(y, yr, **tol, msg="y")
+    _close(x.grad, xr.grad, **tol, msg="dx")
+    _close(delta.grad, dr.grad, **tol, msg="ddelta")
+    wtol = dict(atol=0.5, rtol=5e-2) if dtype == torch.bfloat16 else dict(atol=1e-3, rtol=1e-4)
+    _close(w.grad, wr.grad, **wtol, msg="dw")
+    # only the norm output used downstream: the gradient of the sum is absent
+    x2 = x.detach().clone().requires_grad_(True)
+    _, y2 = ops.add_rms_norm(x2, delta.detach(), w.detach(), 1e-6)
+    y2.float().mul(gy.float()).sum().backward()
+    xr2 = x.detach().float().requires_grad_(True)
+    ref.rms_norm(xr2 + delta.detach().float(), w.detach().float(), 1e-6).mul(gy.float()).sum().backward()
+    _close(x2.grad, xr2.grad, **tol, msg="dx (norm output only)")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_embedding_gather_and_scatter_add(dtype):
+    """Embedding lookup and its table gradient (fp32 vector reductions) against torch, with a skewed id
+    distribution, a padding row and an out-of-range id (skipped, status 73, no fault)."""
+    ext = _ext()
+    torch.manual_seed(2)
+    vocab, d = 1000, 384
+    table = torch.randn(vocab, d, device=DEV, dtype=dtype, requires_grad=True)
+    ids = (torch.rand(4, 2048, device=DEV) ** 4 * vocab).long().clamp_(0, vocab - 1)      # many repeats of low ids
+    ids[0, :7] = 5                                                                        # padding rows
+    out = ops.embedding(ids, table, padding_idx=5)
+    assert torch.equal(out, table.detach()[ids])
+    gy = torch.randn_like(out)
+    out.backward(gy)
+    tr = table.detach().float().requires_grad_(True)
+    F.embedding(ids, tr, padding_idx=5).backward(gy.float())
+    tol = dict(atol=0.25, rtol=2e-2) if dtype == torch.bfloat16 else dict(atol=1e-3, rtol=1e-4)
+    _close(table.grad, tr.grad, **tol, msg="dtable")
+    assert float(table.grad[5].abs().max()) == 0.0
+    _status_ok()
+    bad = ids.clone()
+    bad[1, 3] = vocab + 17
+    o2 = ext.embedding_fwd(table.detach(), bad)
+    assert float(o2[1, 3].abs().max()) == 0.0 and torch.equal(o2[0], out[0])
+    st = ext.gemm_status(torch.zeros(1, device=DEV))
+    assert int(st[0].item()) == 73
+    st.zero_()
+
+
 @pytest.mark.parametrize("hd", [64, 96])
 def test_rope(hd):
     _ext()
@@ -183,6 +245,40 @@ def test_fused_router_matches_reference(d, e, k, renorm, bias_in_logits, dtype):
     tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
     _close(g1, g1r, tol, tol, "drows")
     _close(g2, g2r, 2e-3, 2e-3, "drouter")
+
+
+@pytest.mark.parametrize("router_type,scale", [("norm_softmax", 0.0), ("norm_relu", 0.0), ("norm_relu", 3.0)])
+@pytest.mark.parametrize("d,e,k,renorm,dtype", [(384, 32, 2, False, torch.bfloat16), (192, 64, 4, True, torch.float32)])
+def test_fused_router_normalised_modes(router_type, scale, d, e, k, renorm, dtype):
+    """The L2-normalised router variants (scores = scale * logits / |logits|, softmax or rectified) in the fused
+    kernel: selection, weights, probability sums and both gradients against the fp32 PyTorch statement."""
+    _ext()
+    torch.manual_seed(22)
+    bsz, n = 2, 777
+    rows = torch.randn(bsz, n, d, device=DEV).to(dtype).requires_grad_(True)
+    router = (torch.randn(e, d, device=DEV) * 0.2).requires_grad_(True)
+    bias = torch.randn(e, device=DEV) * 0.02
+    idx, w, psum = ops.route_topk(rows, router, bias, k, 0.7, False, renorm, router_type, scale, 1e-6)
+    rr = rows.detach().float().requires_grad_(True)
+    rt = router.detach().clone().requires_grad_(True)
+    sel, probs = ref.route_scores(rr @ rt.t(), router_type, scale, 1e-6)
+    scores = sel.detach() + bias
+    top = torch.topk(scores, k + 1, dim=-1)
+    clear = (top.values[..., k - 1] - top.values[..., -1]).abs() > 1e-3
+    assert bool((idx.long().sort(-1).values == top.indices[..., :k].sort(-1).values)[clear].all())
+    picked = probs.gather(-1, idx.long())
+    if renorm:
+        picked = picked / picked.sum(-1, keepdim=True).clamp_min(1e-9)
+    wr = (picked * 0.7).view(bsz * n, k)
+    _close(w, wr, 1e-4, 1e-3, "weights")
+    _close(psum, probs.sum(1), 1e-2, 1e-3, "probs_sum")
+    gw = torch.randn_like(w)
+    gp = torch.randn_like(psum) * 0.1
+    g1, g2 = torch.autograd.grad([w, psum], [rows, router], [gw, gp])
+    g1r, g2r = torch.autograd.grad([wr, probs.sum(1)], [rr, rt], [gw, gp])
+    tol = 2e-2 if dtype == torch.bfloat16 else 2e-4
+    _close(g1, g1r, tol, tol, "drows")
+    _close(g2, g2r, 3e-3, 3e-3, "drouter")
 
 
 @pytest.mark.parametrize("renorm", ["restore", "unit", "none"])

@@ -18,7 +18,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .. import ops
-from .common import GatedMLP, RMSNorm, SlidingWindowAttention, init_linear_weights
+from .common import GatedMLP, RMSNorm, SlidingWindowAttention, TokenEmbedding, init_linear_weights
 from .uttt_moe import UTTTMoEForCausalLM
 
 
@@ -169,7 +169,7 @@ class _StackModel(nn.Module):
     def __init__(self, config):
         super().__init__()
         self.config = config
-        self.embeddings = nn.Embedding(config.vocab_size, config.hidden_size, config.pad_token_id)
+        self.embeddings = TokenEmbedding(config.vocab_size, config.hidden_size, config.pad_token_id)
         self.layers = nn.ModuleList([self.block_cls(config, i) for i in range(config.num_hidden_layers)])
         self.norm = RMSNorm(config.hidden_size, eps=config.norm_eps)
         self.activation_checkpoint = True

@@ -25,6 +25,19 @@ class RMSNorm(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return ops.rms_norm(x, self.weight, self.eps)
 
+    def add_forward(self, x: torch.Tensor, delta: torch.Tensor):
+        """(x + delta, norm(x + delta)): the residual addition runs inside the norm kernel."""
+        return ops.add_rms_norm(x, delta, self.weight, self.eps)
+
+
+class TokenEmbedding(nn.Embedding):
+    """``nn.Embedding`` whose lookup and table gradient run on the gather / scatter-add kernels."""
+
+    def forward(self, input_ids: torch.Tensor) -> torch.Tensor:
+        if self.max_norm is not None or self.sparse:
+            return super().forward(input_ids)
+        return ops.embedding(input_ids, self.weight, self.padding_idx)
+
 
 class LowRankFastWeight(nn.Module):
     """``W = w_left @ w_right (+ 0.5 * I)``: low-rank parameterisation of the initial fast weights."""

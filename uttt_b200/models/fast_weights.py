@@ -87,24 +87,11 @@ def _route_rows_local(rows: torch.Tensor, router: torch.Tensor, bias: Optional[t
         plan = ops.build_group_plan(idx, 1)
         ones = torch.ones(bsz * n, 1, device=rows.device, dtype=torch.float32)
         return Routing(plan, ones, ones.view(bsz, n).sum(1, keepdim=True), plan.sizes.view(bsz, 1).float(), idx=idx)
-    if cfg.memory_router_type == "softmax":
-        idx, weights, psum = ops.route_softmax_topk(rows, router, bias, k, cfg.memory_router_alpha, bias_in_logits,
-                                                    cfg.memory_router_combine_mode == "topk_renorm")
-        plan = ops.build_group_plan(idx, e)
-        return Routing(plan, weights, psum, plan.sizes.view(bsz, e).float(), idx=idx)
-    logits = torch.matmul(rows.float(), router.float().t())
-    if bias is not None and bias_in_logits:
-        logits = logits + bias.view(1, 1, e)
-    sel, probs = ref.route_scores(logits, cfg.memory_router_type, cfg.memory_router_scale,
-                                  cfg.memory_router_norm_eps)
-    scores = sel if (bias is None or bias_in_logits) else sel + bias.view(1, 1, e)
-    idx = torch.topk(scores.detach(), k=k, dim=-1).indices
-    picked = probs.gather(-1, idx)
-    if cfg.memory_router_combine_mode == "topk_renorm":
-        picked = picked / picked.sum(dim=-1, keepdim=True).clamp_min(1e-9)
-    weights = (picked * cfg.memory_router_alpha).view(bsz * n, k)
+    idx, weights, psum = ops.route_topk(rows, router, bias, k, cfg.memory_router_alpha, bias_in_logits,
+                                        cfg.memory_router_combine_mode == "topk_renorm", cfg.memory_router_type,
+                                        cfg.memory_router_scale, cfg.memory_router_norm_eps)
     plan = ops.build_group_plan(idx, e)
-    return Routing(plan, weights, probs.sum(dim=1), plan.sizes.view(bsz, e).float(), idx=idx)
+    return Routing(plan, weights, psum, plan.sizes.view(bsz, e).float(), idx=idx)
 
 
 def pool_read(q_rows: torch.Tensor, state_w02: torch.Tensor, state_w1: torch.Tensor, routing: Routing) -> torch.Tensor:

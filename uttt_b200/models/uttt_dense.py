@@ -23,7 +23,8 @@ import torch.nn.functional as F
 from .. import ops
 from ..ops import reference as ref
 from . import fast_weights as fw
-from .common import GatedMLP, RMSNorm, SlidingWindowAttention, init_linear_weights, inv_softplus, trim_history
+from .common import (GatedMLP, RMSNorm, SlidingWindowAttention, TokenEmbedding, init_linear_weights, inv_softplus,
+                     trim_history)
 from .uttt_moe import UTTTMoEForCausalLM
 
 
@@ -100,9 +101,8 @@ class DenseBlock(nn.Module):
         attn_out, q_flat, k_flat, v_flat, k_rot, v_new = self.attn(x_in, k_hist, v_hist, offset)
         mem = self.memory
         if cfg.residual_style == "sequential":
-            h = residual + attn_out
+            h, x_mem = self.memory_norm.add_forward(residual, attn_out)
             residual = h
-            x_mem = self.memory_norm(h)
         else:
             x_mem = x_in
         q_rows = mem.head_rows(mem.prep_query(q_flat, offset))
@@ -112,8 +112,8 @@ class DenseBlock(nn.Module):
         mixed = mem_out + attn_out if cfg.residual_style == "parallel" else mem_out
         if self.memory_output_proj is not None:
             mixed = self.memory_output_proj(mixed)
-        h = residual + mixed
-        h = h + self.mlp(self.mlp_norm(h))
+        h, x_mlp_in = self.mlp_norm.add_forward(residual, mixed)
+        h = h + self.mlp(x_mlp_in)
         return h, x_in, k_flat, v_flat, k_rot, v_new
 
     def raw_grad(self, x_in, k_flat, v_flat, w02, w1, offset: int, acc=None):
@@ -141,7 +141,7 @@ class DenseFWModel(nn.Module):
         super().__init__()
         self.config = config
         d = config.hidden_size
-        self.embeddings = nn.Embedding(config.vocab_size, d, config.pad_token_id)
+        self.embeddings = TokenEmbedding(config.vocab_size, d, config.pad_token_id)
         self.layers = nn.ModuleList([DenseBlock(config, i, private_weights=not self.shared)
                                      for i in range(config.num_hidden_layers)])
         self.norm = RMSNorm(d, eps=config.norm_eps)

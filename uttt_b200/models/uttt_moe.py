@@ -27,7 +27,7 @@ from .. import ops
 from ..config import LMConfig
 from . import fast_weights as fw
 from ..utils.trace import trace_range
-from .common import (GatedMLP, LowRankFastWeight, RMSNorm, SlidingWindowAttention, init_linear_weights,
+from .common import (GatedMLP, LowRankFastWeight, RMSNorm, SlidingWindowAttention, TokenEmbedding, init_linear_weights,
                      inv_softplus, trim_history)
 
 
@@ -82,9 +82,8 @@ class MoEBlock(nn.Module):
         lb_probs = lb_counts = None
         if self.memory is not None:
             if cfg.residual_style == "sequential":
-                h = residual + attn_out
+                h, x_mem_in = self.memory_norm.add_forward(residual, attn_out)
                 residual = h
-                x_mem_in = self.memory_norm(h)
             else:
                 x_mem_in = x_attn_in
             mem = self.memory
@@ -98,8 +97,8 @@ class MoEBlock(nn.Module):
             mixed = attn_out
         if self.memory_output_proj is not None:
             mixed = ops.linear(mixed, self.memory_output_proj.weight)
-        h = residual + mixed
-        h = h + self.mlp(self.mlp_norm(h))
+        h, x_mlp_in = self.mlp_norm.add_forward(residual, mixed)
+        h = h + self.mlp(x_mlp_in)
         if lb_probs is None:
             lb_probs = h.new_zeros((h.shape[0], 1), dtype=torch.float32)
             lb_counts = lb_probs
@@ -134,7 +133,7 @@ class UTTTMoEModel(nn.Module):
         super().__init__()
         self.config = config
         d = config.hidden_size
-        self.embeddings = nn.Embedding(config.vocab_size, d, config.pad_token_id)
+        self.embeddings = TokenEmbedding(config.vocab_size, d, config.pad_token_id)
         self.layers = nn.ModuleList([MoEBlock(config, i) for i in range(config.num_hidden_layers)])
         self.norm = RMSNorm(d, eps=config.norm_eps)
         self.num_experts = config.memory_num_experts

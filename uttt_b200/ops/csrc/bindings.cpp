@@ -4,6 +4,11 @@
 namespace uttt {
 std::vector<at::Tensor> rms_norm_fwd(at::Tensor x, c10::optional<at::Tensor> w, double eps);
 std::vector<at::Tensor> rms_norm_bwd(at::Tensor dy, at::Tensor x, c10::optional<at::Tensor> w, at::Tensor rstd);
+at::Tensor embedding_fwd(at::Tensor table, at::Tensor ids);
+at::Tensor embedding_bwd(at::Tensor dy, at::Tensor ids, int64_t vocab);
+std::vector<at::Tensor> add_rms_norm_fwd(at::Tensor x, at::Tensor delta, c10::optional<at::Tensor> w, double eps);
+std::vector<at::Tensor> add_rms_norm_bwd(at::Tensor dy, c10::optional<at::Tensor> ds, at::Tensor s,
+                                         c10::optional<at::Tensor> w, at::Tensor rstd);
 at::Tensor rope_fwd(at::Tensor x, at::Tensor table, int64_t offset, bool inverse);
 std::vector<at::Tensor> fw_qk_prep_fwd(at::Tensor x, c10::optional<at::Tensor> scale, c10::optional<at::Tensor> shift,
                                        at::Tensor table, int64_t heads, int64_t rope_dim, int64_t offset, int64_t l,
@@ -39,10 +44,10 @@ at::Tensor bmm_nt(at::Tensor a, at::Tensor b, double alpha, c10::optional<at::Te
 at::Tensor gemm_status(at::Tensor like);
 at::Tensor bmm_general(at::Tensor a, at::Tensor b, int64_t mode, double alpha, c10::optional<at::Tensor> d, double beta);
 void rs_sumsq(std::vector<int64_t> grad_ptrs, int64_t rank, int64_t shard_off, at::Tensor out, double scale,
-              at::Tensor sumsq, bool grads_bf16);
+              at::Tensor sumsq, bool grads_bf16, int64_t mc_ptr);
 void adamw_scatter(at::Tensor p, at::Tensor g, at::Tensor m, at::Tensor v, std::vector<int64_t> compute_ptrs,
                    int64_t rank, int64_t shard_off, bool compute_bf16, double lr, double b1, double b2, double eps,
-                   double wd, int64_t step, at::Tensor gscale, at::Tensor apply, int64_t decay_hi);
+                   double wd, int64_t step, at::Tensor gscale, at::Tensor apply, int64_t decay_hi, int64_t mc_ptr);
 std::vector<at::Tensor> swa_fwd(at::Tensor q, at::Tensor k, at::Tensor v, int64_t window, bool causal, double scale);
 std::vector<at::Tensor> patch_decode_fwd(at::Tensor y, c10::optional<at::Tensor> target, int64_t views, int64_t height,
                                          int64_t width, int64_t patch);
@@ -68,10 +73,12 @@ std::vector<at::Tensor> pool_step_bwd(at::Tensor m, at::Tensor d, c10::optional<
                                       c10::optional<at::Tensor> gw, double lr, int64_t mode);
 bool router_supported(int64_t D, int64_t E, int64_t topk);
 std::vector<at::Tensor> router_fwd(at::Tensor rows, at::Tensor router, c10::optional<at::Tensor> bias, int64_t topk,
-                                   int64_t rows_per_batch, double alpha, bool bias_in_logits, bool renorm);
+                                   int64_t rows_per_batch, double alpha, bool bias_in_logits, bool renorm,
+                                   int64_t mode, double rscale, double norm_eps);
 std::vector<at::Tensor> router_bwd(at::Tensor rows, at::Tensor router, at::Tensor probs, at::Tensor idx,
                                    c10::optional<at::Tensor> dweights, c10::optional<at::Tensor> dprobs_sum,
-                                   int64_t rows_per_batch, double alpha, bool renorm, bool need_drows);
+                                   int64_t rows_per_batch, double alpha, bool renorm, bool need_drows, int64_t mode,
+                                   double rscale, double norm_eps, c10::optional<at::Tensor> logits);
 std::vector<at::Tensor> swa_bwd(at::Tensor dout, at::Tensor q, at::Tensor k, at::Tensor v, at::Tensor o, at::Tensor lse,
                                 int64_t window, bool causal, double scale);
 }  // namespace uttt
@@ -80,6 +87,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   using namespace uttt;
   m.def("rms_norm_fwd", &rms_norm_fwd);
   m.def("rms_norm_bwd", &rms_norm_bwd);
+  m.def("embedding_fwd", &embedding_fwd);
+  m.def("embedding_bwd", &embedding_bwd);
+  m.def("add_rms_norm_fwd", &add_rms_norm_fwd);
+  m.def("add_rms_norm_bwd", &add_rms_norm_bwd);
   m.def("rope_fwd", &rope_fwd);
   m.def("fw_qk_prep_fwd", &fw_qk_prep_fwd);
   m.def("fw_qk_prep_bwd", &fw_qk_prep_bwd);

@@ -35,20 +35,40 @@ static inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream(
 static inline int sm_count() { return at::cuda::getCurrentDeviceProperties()->multiProcessorCount; }
 
 // ------------------------------------------------------------------------------------ RMSNorm
+// With `add` the kernel first forms the residual sum s = x + add (rounded to T, as the separate addition
+// would), writes it to `sum_out` and normalises s: residual addition and the following norm in one pass.
 template <typename T>
 __global__ void rms_norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
-                                    float* __restrict__ rstd, int rows, int d, float eps) {
+                                    float* __restrict__ rstd, int rows, int d, float eps,
+                                    const T* __restrict__ add = nullptr, T* __restrict__ sum_out = nullptr) {
   int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   int nwarps = (gridDim.x * blockDim.x) >> 5;
   int nv = d >> 3;
   for (int r = warp; r < rows; r += nwarps) {
     const T* xr = x + (size_t)r * d;
     float ss = 0.f;
-    for (int v = lane; v < nv; v += 32) {
-      float f[8];
-      Vec8<T>::load(xr + v * 8, f);
+    if (add != nullptr) {
+      const T* ar = add + (size_t)r * d;
+      T* sr = sum_out + (size_t)r * d;
+      for (int v = lane; v < nv; v += 32) {
+        float f[8], a[8];
+        Vec8<T>::load(xr + v * 8, f);
+        Vec8<T>::load(ar + v * 8, a);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+        for (int i = 0; i < 8; ++i) {
+          f[i] = static_cast<float>(static_cast<T>(f[i] + a[i]));
+          ss += f[i] * f[i];
+        }
+        Vec8<T>::store(sr + v * 8, f);
+      }
+      xr = sr;                                   // the second pass re-reads what this lane just wrote
+    } else {
+      for (int v = lane; v < nv; v += 32) {
+        float f[8];
+        Vec8<T>::load(xr + v * 8, f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+      }
     }
     ss = warp_sum(ss);
     float rs = rsqrtf(ss / d + eps);
@@ -75,7 +95,7 @@ __global__ void rms_norm_fwd_kernel(const T* __restrict__ x, const T* __restrict
 template <typename T, int MAXV>
 __global__ void rms_norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
                                     const float* __restrict__ rstd, T* __restrict__ dx, float* __restrict__ dw,
-                                    int rows, int d) {
+                                    int rows, int d, const T* __restrict__ dres = nullptr) {
   int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   int nwarps = (gridDim.x * blockDim.x) >> 5;
   int nv = d >> 3;
@@ -121,6 +141,12 @@ __global__ void rms_norm_bwd_kernel(const T* __restrict__ dy, const T* __restric
           float gw = w ? fg[i] * fw[i] : fg[i];
           o[i] = rs * (gw - fx[i] * rs * dot);
         }
+        if (dres != nullptr) {                   // gradient that reached the residual sum directly
+          float fr[8];
+          Vec8<T>::load(dres + (size_t)r * d + v * 8, fr);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] += fr[i];
+        }
         Vec8<T>::store(dxr + v * 8, o);
       }
     }
@@ -148,25 +174,47 @@ __global__ void rms_norm_bwd_kernel(const T* __restrict__ dy, const T* __restric
   }
 }
 
-std::vector<at::Tensor> rms_norm_fwd(at::Tensor x, c10::optional<at::Tensor> w, double eps) {
+static std::vector<at::Tensor> rms_norm_fwd_impl(at::Tensor x, c10::optional<at::Tensor> w, double eps,
+                                                 c10::optional<at::Tensor> add) {
   c10::cuda::CUDAGuard guard(x.device());
   int rows = x.size(0), d = x.size(1);
   TORCH_CHECK(x.is_contiguous() && d % 8 == 0);
   auto y = at::empty_like(x);
+  at::Tensor addc, sum;
+  if (add.has_value() && add->defined()) {
+    TORCH_CHECK(add->sizes() == x.sizes() && add->scalar_type() == x.scalar_type() && add->is_contiguous());
+    addc = *add;
+    sum = at::empty_like(x);
+  }
   auto rstd = at::empty({rows}, x.options().dtype(at::kFloat));
   at::Tensor wc;
   if (w.has_value() && w->defined()) wc = w->to(x.scalar_type()).contiguous();
   int blocks = std::min((rows + 7) / 8, sm_count() * 8);
   UTTT_DISPATCH_FLOAT(x, {
     rms_norm_fwd_kernel<T><<<std::max(blocks, 1), 256, 0, cur_stream()>>>(
-        ptr<T>(x), wc.defined() ? ptr<T>(wc) : nullptr, ptr<T>(y), ptr<float>(rstd), rows, d, (float)eps);
+        ptr<T>(x), wc.defined() ? ptr<T>(wc) : nullptr, ptr<T>(y), ptr<float>(rstd), rows, d, (float)eps,
+        addc.defined() ? ptr<T>(addc) : nullptr, addc.defined() ? ptr<T>(sum) : nullptr);
   });
   count_launch();
+  if (addc.defined()) return {sum, y, rstd};
   return {y, rstd};
 }
+std::vector<at::Tensor> rms_norm_fwd(at::Tensor x, c10::optional<at::Tensor> w, double eps) {
+  return rms_norm_fwd_impl(x, w, eps, c10::nullopt);
+}
+// s = x + delta, y = rms_norm(s) * w  ->  {s, y, rstd}
+std::vector<at::Tensor> add_rms_norm_fwd(at::Tensor x, at::Tensor delta, c10::optional<at::Tensor> w, double eps) {
+  return rms_norm_fwd_impl(x, w, eps, delta);
+}
 
-std::vector<at::Tensor> rms_norm_bwd(at::Tensor dy, at::Tensor x, c10::optional<at::Tensor> w, at::Tensor rstd) {
+static std::vector<at::Tensor> rms_norm_bwd_impl(at::Tensor dy, at::Tensor x, c10::optional<at::Tensor> w,
+                                                 at::Tensor rstd, c10::optional<at::Tensor> dres) {
   c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor dresc;
+  if (dres.has_value() && dres->defined()) {
+    TORCH_CHECK(dres->sizes() == x.sizes() && dres->scalar_type() == x.scalar_type() && dres->is_contiguous());
+    dresc = *dres;
+  }
   int rows = x.size(0), d = x.size(1);
   TORCH_CHECK(d % 8 == 0 && d <= 8 * 32 * 16, "rms_norm_bwd: hidden size must be a multiple of 8 and <= 4096");
   auto dx = at::empty_like(x);
@@ -182,19 +230,28 @@ std::vector<at::Tensor> rms_norm_bwd(at::Tensor dy, at::Tensor x, c10::optional<
   UTTT_DISPATCH_FLOAT(x, {
     const T* wp = wc.defined() ? ptr<T>(wc) : nullptr;
     float* dwp = wc.defined() ? ptr<float>(dw) : nullptr;
+    const T* rp = dresc.defined() ? ptr<T>(dresc) : nullptr;
     if (nv <= 32 * 2)
       rms_norm_bwd_kernel<T, 2><<<blocks, 128, 0, cur_stream()>>>(ptr<T>(dy), ptr<T>(x), wp, ptr<float>(rstd),
-                                                                   ptr<T>(dx), dwp, rows, d);
+                                                                   ptr<T>(dx), dwp, rows, d, rp);
     else if (nv <= 32 * 8)
       rms_norm_bwd_kernel<T, 8><<<blocks, 128, 0, cur_stream()>>>(ptr<T>(dy), ptr<T>(x), wp, ptr<float>(rstd),
-                                                                   ptr<T>(dx), dwp, rows, d);
+                                                                   ptr<T>(dx), dwp, rows, d, rp);
     else
       rms_norm_bwd_kernel<T, 16><<<blocks, 128, 0, cur_stream()>>>(ptr<T>(dy), ptr<T>(x), wp, ptr<float>(rstd),
-                                                                    ptr<T>(dx), dwp, rows, d);
+                                                                    ptr<T>(dx), dwp, rows, d, rp);
   });
   count_launch();
   if (wc.defined()) dw = dw.sum(0);
   return {dx, dw};
+}
+std::vector<at::Tensor> rms_norm_bwd(at::Tensor dy, at::Tensor x, c10::optional<at::Tensor> w, at::Tensor rstd) {
+  return rms_norm_bwd_impl(dy, x, w, rstd, c10::nullopt);
+}
+// backward of add_rms_norm_fwd: d(x) = d(delta) = ds + rms_norm_bwd(dy, s)  ->  {dsum, dw}
+std::vector<at::Tensor> add_rms_norm_bwd(at::Tensor dy, c10::optional<at::Tensor> ds, at::Tensor s,
+                                         c10::optional<at::Tensor> w, at::Tensor rstd) {
+  return rms_norm_bwd_impl(dy, s, w, rstd, ds);
 }
 
 // ------------------------------------------------------------------------------------ rotary

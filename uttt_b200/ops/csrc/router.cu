@@ -1,7 +1,10 @@
-// Fused softmax router of the fast-weight expert pool.
+// Fused router of the fast-weight expert pool.
 //
 //   logits = rows . router^T (+ bias)   fp32, rows [R, D] bf16 / fp32, router [E, D] fp32
-//   probs  = softmax(logits)
+//   probs  = softmax(logits)                                              mode 0 (softmax)
+//            softmax(s * z),  z = logits / max(|logits|_2, eps)           mode 1 (norm_softmax)
+//            relu(z) s / sum relu(z) s  (uniform when the sum is 0)       mode 2 (norm_relu)
+//   (modes 1 and 2 select on the rescaled scores and keep the raw logits for the backward)
 //   idx    = top-k of (logits + selection bias)               (the bias moves selection only, unless it is
 //                                                              declared part of the logits)
 //   weight = alpha * probs[idx]   or   alpha * probs[idx] / sum_sel probs[idx]
@@ -38,7 +41,8 @@ __global__ void __launch_bounds__(256) router_fwd_kernel(const T* __restrict__ r
                                                          int rows_per_batch, float alpha, int bias_in_logits,
                                                          int renorm, int* __restrict__ idx_out,
                                                          float* __restrict__ w_out, float* __restrict__ probs_out,
-                                                         float* __restrict__ probs_sum) {
+                                                         float* __restrict__ probs_sum, int mode, float rscale,
+                                                         float norm_eps, float* __restrict__ logits_out) {
   constexpr int EP = 32 * EPL + 1;
   constexpr int VEC = 16 / (int)sizeof(T);           // elements per 16-byte piece
   constexpr int BR = 8 * RPW;                        // rows per block step
@@ -142,19 +146,44 @@ __global__ void __launch_bounds__(256) router_fwd_kernel(const T* __restrict__ r
         lg[q] = (e < E) ? acc[r][q] + blog[q] : -INFINITY;
         mx = fmaxf(mx, lg[q]);
       }
+      if (mode != 0) {
+        // normalised variants: keep the raw logits for the backward, continue with the rescaled scores
+        float ss = 0.f;
+#pragma unroll
+        for (int q = 0; q < EPL; ++q)
+          if (lane + 32 * q < E) ss += lg[q] * lg[q];
+        ss = warp_sum(ss);
+        const float inv_n = 1.f / fmaxf(sqrtf(ss), norm_eps);
+        mx = -INFINITY;
+#pragma unroll
+        for (int q = 0; q < EPL; ++q) {
+          int e = lane + 32 * q;
+          if (e < E) {
+            logits_out[(size_t)row * E + e] = lg[q];
+            float z = lg[q] * inv_n;
+            lg[q] = (mode == 1 ? z : fmaxf(z, 0.f)) * rscale;
+            mx = fmaxf(mx, lg[q]);
+          }
+        }
+      }
       mx = warp_max(mx);
       float pr[EPL], sum = 0.f;
 #pragma unroll
       for (int q = 0; q < EPL; ++q) {
-        pr[q] = (lane + 32 * q < E) ? __expf(lg[q] - mx) : 0.f;
+        if (mode == 2) pr[q] = (lane + 32 * q < E) ? lg[q] : 0.f;
+        else pr[q] = (lane + 32 * q < E) ? __expf(lg[q] - mx) : 0.f;
         sum += pr[q];
       }
       sum = warp_sum(sum);
-      const float inv = 1.f / sum;
+      float inv = 1.f / sum, uniform = 0.f;
+      if (mode == 2) {
+        if (sum > 0.f) inv = 1.f / fmaxf(sum, 1e-9f);
+        else { inv = 0.f; uniform = 1.f / (float)E; }
+      }
 #pragma unroll
       for (int q = 0; q < EPL; ++q) {
-        pr[q] *= inv;
         int e = lane + 32 * q;
+        pr[q] = (e < E) ? pr[q] * inv + uniform : 0.f;
         if (e < E) probs_out[(size_t)row * E + e] = pr[q];
       }
       const int b = row / rows_per_batch;
@@ -212,7 +241,8 @@ template <typename T, int EPL, int DPL, int RPW>
 __global__ void __launch_bounds__(256) router_bwd_rows_kernel(
     const float* __restrict__ router, const float* __restrict__ probs, const int* __restrict__ idx,
     const float* __restrict__ dw, const float* __restrict__ dpsum, int R, int D, int E, int topk, int rows_per_batch,
-    float alpha, int renorm, float* __restrict__ dlogits, T* __restrict__ drows) {
+    float alpha, int renorm, float* __restrict__ dlogits, T* __restrict__ drows, int mode, float rscale,
+    float norm_eps, const float* __restrict__ logits) {
   extern __shared__ float ws[];                 // [E][D] router matrix
   for (int i = threadIdx.x; i < E * D; i += blockDim.x) ws[i] = router[i];
   __syncthreads();
@@ -263,9 +293,45 @@ __global__ void __launch_bounds__(256) router_bwd_rows_kernel(
 #pragma unroll
       for (int q = 0; q < EPL; ++q) inner += dp[q] * pr[q];
       inner = warp_sum(inner);
+      if (mode == 0) {
+#pragma unroll
+        for (int q = 0; q < EPL; ++q) dl[r][q] = pr[q] * (dp[q] - inner);
+      } else {
+        // z = l / max(|l|, eps); scores = z s (mode 1) or relu(z) s (mode 2)
+        float lr_[EPL], z[EPL], ss = 0.f;
+#pragma unroll
+        for (int q = 0; q < EPL; ++q) {
+          int e = lane + 32 * q;
+          lr_[q] = (e < E) ? logits[(size_t)row * E + e] : 0.f;
+          ss += lr_[q] * lr_[q];
+        }
+        ss = warp_sum(ss);
+        const float nr = sqrtf(ss), inv_n = 1.f / fmaxf(nr, norm_eps);
+        float ssum = 0.f;
+#pragma unroll
+        for (int q = 0; q < EPL; ++q) {
+          z[q] = lr_[q] * inv_n;
+          ssum += fmaxf(z[q], 0.f) * rscale;
+        }
+        float dz[EPL], zdot = 0.f;
+        if (mode == 2) ssum = warp_sum(ssum);
+#pragma unroll
+        for (int q = 0; q < EPL; ++q) {
+          float dsel;
+          if (mode == 1) dsel = pr[q] * (dp[q] - inner);
+          else if (ssum >= 1e-9f) dsel = (dp[q] - inner) / ssum;
+          else dsel = ssum > 0.f ? dp[q] * 1e9f : 0.f;
+          dz[q] = (mode == 2 && z[q] <= 0.f) ? 0.f : dsel * rscale;
+          if (lane + 32 * q >= E) dz[q] = 0.f;
+          zdot += dz[q] * z[q];
+        }
+        zdot = warp_sum(zdot);
+        const bool clamped = nr <= norm_eps;       // the clamp cuts the gradient through the norm
+#pragma unroll
+        for (int q = 0; q < EPL; ++q) dl[r][q] = (clamped ? dz[q] : dz[q] - z[q] * zdot) * inv_n;
+      }
 #pragma unroll
       for (int q = 0; q < EPL; ++q) {
-        dl[r][q] = pr[q] * (dp[q] - inner);
         int e = lane + 32 * q;
         if (e < E && r0 + r < R) dlogits[(size_t)row * E + e] = dl[r][q];
       }
@@ -381,9 +447,11 @@ bool router_supported(int64_t D, int64_t E, int64_t topk) {
   return D % 8 == 0 && D <= 512 && E % 8 == 0 && E <= 64 && topk >= 1 && topk <= kMaxTopK && topk <= E;
 }
 
-// returns (idx [R, k] int32, weights [R, k] fp32, probs [R, E] fp32, probs_sum [B, E] fp32)
+// returns (idx [R, k] int32, weights [R, k] fp32, probs [R, E] fp32, probs_sum [B, E] fp32,
+//          raw logits [R, E] fp32 for modes 1 and 2, empty for mode 0)
 std::vector<at::Tensor> router_fwd(at::Tensor rows, at::Tensor router, c10::optional<at::Tensor> bias, int64_t topk,
-                                   int64_t rows_per_batch, double alpha, bool bias_in_logits, bool renorm) {
+                                   int64_t rows_per_batch, double alpha, bool bias_in_logits, bool renorm,
+                                   int64_t mode, double rscale, double norm_eps) {
   c10::cuda::CUDAGuard guard(rows.device());
   TORCH_CHECK(rows.dim() == 2 && rows.is_contiguous() && router.is_contiguous() && router.scalar_type() == at::kFloat);
   const int R = rows.size(0), D = rows.size(1), E = router.size(0);
@@ -400,6 +468,8 @@ std::vector<at::Tensor> router_fwd(at::Tensor rows, at::Tensor router, c10::opti
   auto w = at::empty({R, topk}, opts.dtype(at::kFloat));
   auto probs = at::empty({R, E}, opts.dtype(at::kFloat));
   auto psum = at::zeros({R / rows_per_batch, E}, opts.dtype(at::kFloat));
+  TORCH_CHECK(mode >= 0 && mode <= 2, "router mode: 0 softmax, 1 norm_softmax, 2 norm_relu");
+  auto logits = mode != 0 ? at::empty({R, E}, opts.dtype(at::kFloat)) : at::empty({0}, opts.dtype(at::kFloat));
   const int epl = E > 32 ? 2 : 1;
   const bool bf = rows.scalar_type() == at::kBFloat16;
   const int rpw = bf ? 8 : 4;
@@ -411,7 +481,8 @@ std::vector<at::Tensor> router_fwd(at::Tensor rows, at::Tensor router, c10::opti
     C10_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kernel<<<blocks, 256, smem, stream>>>(rp, router.data_ptr<float>(), bp, R, D, E, (int)topk, (int)rows_per_batch,
                                           (float)alpha, bias_in_logits ? 1 : 0, renorm ? 1 : 0, idx.data_ptr<int>(),
-                                          w.data_ptr<float>(), probs.data_ptr<float>(), psum.data_ptr<float>());
+                                          w.data_ptr<float>(), probs.data_ptr<float>(), psum.data_ptr<float>(),
+                                          (int)mode, (float)rscale, (float)norm_eps, logits.data_ptr<float>());
     C10_CUDA_KERNEL_LAUNCH_CHECK();
   };
   if (rows.scalar_type() == at::kBFloat16) {
@@ -425,20 +496,21 @@ std::vector<at::Tensor> router_fwd(at::Tensor rows, at::Tensor router, c10::opti
     else launch(router_fwd_kernel<float, 2, 4>, rp);
   }
   count_launch();
-  return {idx, w, probs, psum};
+  return {idx, w, probs, psum, logits};
 }
 
 template <typename T, int EPL>
 static void launch_bwd_rows(int dpl, const float* router, const float* probs, const int* idx, const float* dw,
                             const float* dpsum, int R, int D, int E, int topk, int rpb, float alpha, int renorm,
-                            float* dlogits, T* drows, cudaStream_t stream) {
+                            float* dlogits, T* drows, cudaStream_t stream, int mode, float rscale, float norm_eps,
+                            const float* logits) {
   const size_t smem = (size_t)E * D * sizeof(float);
   auto go = [&](auto kernel, int rpw) {
     C10_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const int groups = (R + rpw - 1) / rpw;
     const int blocks = std::max(1, std::min((groups + 7) / 8, 2 * sm_count()));
     kernel<<<blocks, 256, smem, stream>>>(router, probs, idx, dw, dpsum, R, D, E, topk, rpb, alpha, renorm, dlogits,
-                                          drows);
+                                          drows, mode, rscale, norm_eps, logits);
     C10_CUDA_KERNEL_LAUNCH_CHECK();
   };
   if (dpl <= 4) go(router_bwd_rows_kernel<T, EPL, 4, 8>, 8);
@@ -466,7 +538,8 @@ static void launch_bwd_weight(int dpl, const T* rows, const float* dlogits, int 
 // returns (d rows [R, D] in the dtype of rows, d router [E, D] fp32)
 std::vector<at::Tensor> router_bwd(at::Tensor rows, at::Tensor router, at::Tensor probs, at::Tensor idx,
                                    c10::optional<at::Tensor> dweights, c10::optional<at::Tensor> dprobs_sum,
-                                   int64_t rows_per_batch, double alpha, bool renorm, bool need_drows) {
+                                   int64_t rows_per_batch, double alpha, bool renorm, bool need_drows, int64_t mode,
+                                   double rscale, double norm_eps, c10::optional<at::Tensor> logits) {
   c10::cuda::CUDAGuard guard(rows.device());
   const int R = rows.size(0), D = rows.size(1), E = router.size(0), topk = idx.size(1);
   TORCH_CHECK(router_supported(D, E, topk) && probs.is_contiguous() && idx.is_contiguous() && rows.is_contiguous());
@@ -479,6 +552,12 @@ std::vector<at::Tensor> router_bwd(at::Tensor rows, at::Tensor router, at::Tenso
   if (dprobs_sum.has_value() && dprobs_sum->defined()) {
     dpc = dprobs_sum->to(at::kFloat).contiguous();
     dpp = dpc.data_ptr<float>();
+  }
+  const float* lgp = nullptr;
+  if (mode != 0) {
+    TORCH_CHECK(logits.has_value() && logits->defined() && logits->is_contiguous() && logits->numel() == (int64_t)R * E,
+                "the normalised router modes need the raw logits of the forward");
+    lgp = logits->data_ptr<float>();
   }
   auto dlogits = at::empty({R, E}, probs.options());
   auto drows = need_drows ? at::empty_like(rows) : at::Tensor();
@@ -495,7 +574,7 @@ std::vector<at::Tensor> router_bwd(at::Tensor rows, at::Tensor router, at::Tenso
 #define UTTT_ROUTER_BWD(T_, EPL_)                                                                              \
   launch_bwd_rows<T_, EPL_>(dpl, rt, pp, ip, dwp, dpp, R, D, E, topk, (int)rows_per_batch, (float)alpha,       \
                             renorm ? 1 : 0, dl, need_drows ? reinterpret_cast<T_*>(drows.data_ptr()) : nullptr, \
-                            stream)
+                            stream, (int)mode, (float)rscale, (float)norm_eps, lgp)
   if (bf) {
     if (E > 32) UTTT_ROUTER_BWD(__nv_bfloat16, 2); else UTTT_ROUTER_BWD(__nv_bfloat16, 1);
   } else {

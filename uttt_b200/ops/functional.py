@@ -75,8 +75,73 @@ def rms_norm(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float = 1e-6)
     return ref.rms_norm(x, weight, eps)
 
 
+class _AddRMSNorm(torch.autograd.Function):
+    """s = x + delta; y = rms_norm(s) * weight in one kernel; the backward adds the gradient that reached s
+    directly inside the norm's backward kernel."""
+
+    @staticmethod
+    def forward(ctx, x, delta, weight, eps):
+        ext = cuda_ext(x)
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        d2 = delta.reshape(x2.shape).to(x2.dtype).contiguous()
+        s, y, rstd = ext.add_rms_norm_fwd(x2, d2, weight, float(eps))
+        ctx.save_for_backward(s, weight, rstd)
+        ctx.shape = x.shape
+        ctx.delta_dtype = delta.dtype
+        return s.view(x.shape), y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, ds, dy):
+        s, weight, rstd = ctx.saved_tensors
+        ext = cuda_ext(s)
+        if dy is None:
+            return ds, (None if ds is None else ds.to(ctx.delta_dtype)), None, None
+        ds2 = None if ds is None else ds.reshape(s.shape).to(s.dtype).contiguous()
+        g, dw = ext.add_rms_norm_bwd(dy.reshape(s.shape).contiguous(), ds2, s, weight, rstd)
+        g = g.view(ctx.shape)
+        dwo = None if weight is None else dw.to(weight.dtype)
+        return g, g.to(ctx.delta_dtype), dwo, None
+
+
+def add_rms_norm(x: torch.Tensor, delta: torch.Tensor, weight: Optional[torch.Tensor], eps: float = 1e-6):
+    """Residual addition fused with the norm that follows it: returns (x + delta, rms_norm(x + delta) * weight)."""
+    if _kernel("add_rms_norm_fwd", x) is not None and x.shape[-1] % 8 == 0 and x.shape[-1] <= 4096:
+        return _AddRMSNorm.apply(x, delta, weight, eps)
+    s = x + delta
+    return s, ref.rms_norm(s, weight, eps)
+
+
 def l2_norm(x: torch.Tensor) -> torch.Tensor:
     return ref.l2_norm(x)
+
+
+# =========================================================================== embedding
+class _Embedding(torch.autograd.Function):
+    """Row gather; the backward scatter-adds the output gradient into an fp32 table with vector reductions."""
+
+    @staticmethod
+    def forward(ctx, ids, table, padding_idx):
+        ext = cuda_ext(table)
+        ctx.save_for_backward(ids)
+        ctx.vocab, ctx.dtype, ctx.padding_idx = table.shape[0], table.dtype, padding_idx
+        return ext.embedding_fwd(table.contiguous(), ids)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (ids,) = ctx.saved_tensors
+        ext = cuda_ext(dy)
+        g = ext.embedding_bwd(dy, ids, ctx.vocab)
+        if ctx.padding_idx is not None:
+            g[ctx.padding_idx].zero_()                   # the padding row never trains
+        return None, g.to(ctx.dtype), None
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, padding_idx: Optional[int] = None) -> torch.Tensor:
+    """table[ids] with the gather / scatter-add kernels on a GPU (ids: integer tensor of any shape)."""
+    if _kernel("embedding_fwd", table) is not None and ids.is_cuda and table.shape[1] % 8 == 0 \
+            and table.dtype in (torch.bfloat16, torch.float32):
+        return _Embedding.apply(ids.long(), table, padding_idx)
+    return torch.nn.functional.embedding(ids, table, padding_idx)
 
 
 def layer_norm(x, weight, bias, eps: float = 1e-5):
@@ -469,50 +534,65 @@ def pool_step(m: torch.Tensor, d: torch.Tensor, lr: float, renorm: str = "restor
     return n, n.to(compute_dtype)
 
 
+_ROUTER_MODES = {"softmax": 0, "norm_softmax": 1, "norm_relu": 2}
+
+
 class _Router(torch.autograd.Function):
-    """Fused softmax router (logits, softmax, top-k, combine weights, per-sequence probability sums)."""
+    """Fused router (logits, softmax or normalised variant, top-k, combine weights, per-sequence probability sums)."""
 
     @staticmethod
-    def forward(ctx, rows, router, bias, topk, rows_per_batch, alpha, bias_in_logits, renorm):
+    def forward(ctx, rows, router, bias, topk, rows_per_batch, alpha, bias_in_logits, renorm, mode, rscale, eps):
         ext = cuda_ext(rows)
-        idx, w, probs, psum = ext.router_fwd(rows, router, bias, int(topk), int(rows_per_batch), float(alpha),
-                                             bool(bias_in_logits), bool(renorm))
-        ctx.save_for_backward(rows, router, probs, idx)
-        ctx.args = (int(rows_per_batch), float(alpha), bool(renorm))
+        idx, w, probs, psum, logits = ext.router_fwd(rows, router, bias, int(topk), int(rows_per_batch), float(alpha),
+                                                     bool(bias_in_logits), bool(renorm), int(mode), float(rscale),
+                                                     float(eps))
+        ctx.save_for_backward(rows, router, probs, idx, logits)
+        ctx.args = (int(rows_per_batch), float(alpha), bool(renorm), int(mode), float(rscale), float(eps))
         ctx.mark_non_differentiable(idx)
         return idx, w, psum
 
     @staticmethod
     def backward(ctx, _gidx, gw, gpsum):
-        rows, router, probs, idx = ctx.saved_tensors
-        rpb, alpha, renorm = ctx.args
+        rows, router, probs, idx, logits = ctx.saved_tensors
+        rpb, alpha, renorm, mode, rscale, eps = ctx.args
         ext = cuda_ext(rows)
         drows, drouter = ext.router_bwd(rows, router, probs, idx, gw, gpsum, rpb, alpha, renorm,
-                                        bool(ctx.needs_input_grad[0]))
-        return (drows if ctx.needs_input_grad[0] else None), drouter, None, None, None, None, None, None
+                                        bool(ctx.needs_input_grad[0]), mode, rscale, eps, logits if mode else None)
+        return (drows if ctx.needs_input_grad[0] else None), drouter, None, None, None, None, None, None, None, None, None
 
 
-def route_softmax_topk(rows, router, bias, topk: int, alpha: float = 1.0, bias_in_logits: bool = False,
-                       renorm: bool = False):
+def route_topk(rows, router, bias, topk: int, alpha: float = 1.0, bias_in_logits: bool = False,
+               renorm: bool = False, router_type: str = "softmax", router_scale: float = 0.0,
+               norm_eps: float = 1e-6):
     """rows [B, N, D], router [E, D], bias [E] or None -> (idx [B, N, k] int, weights [B*N, k] fp32,
-    probs_sum [B, E] fp32) of a softmax router; the bias shifts selection only unless ``bias_in_logits``."""
+    probs_sum [B, E] fp32).  ``router_type``: 'softmax', 'norm_softmax' (softmax of the L2-normalised logits times
+    ``router_scale``, sqrt(E) when 0) or 'norm_relu' (their rectified values, normalised to sum 1).  The bias shifts
+    selection only unless ``bias_in_logits``."""
     bsz, n, d = rows.shape
     e = router.shape[0]
+    rscale = router_scale if router_scale > 0 else math.sqrt(float(e))
     ext = _kernel("router_fwd", rows)
     if ext is not None and ext.router_supported(d, e, topk) and rows.dtype in (torch.bfloat16, torch.float32):
         idx, w, psum = _Router.apply(rows.reshape(bsz * n, d).contiguous(), router.float().contiguous(),
-                                     None if bias is None else bias.detach(), topk, n, alpha, bias_in_logits, renorm)
+                                     None if bias is None else bias.detach(), topk, n, alpha, bias_in_logits, renorm,
+                                     _ROUTER_MODES[router_type], rscale, norm_eps)
         return idx.view(bsz, n, topk), w, psum
     logits = torch.matmul(rows.float(), router.float().t())
     if bias is not None and bias_in_logits:
         logits = logits + bias.view(1, 1, e)
-    probs = torch.softmax(logits, dim=-1)
-    scores = logits if (bias is None or bias_in_logits) else logits + bias.view(1, 1, e)
+    sel, probs = ref.route_scores(logits, router_type, router_scale, norm_eps)
+    scores = sel if (bias is None or bias_in_logits) else sel + bias.view(1, 1, e)
     idx = torch.topk(scores.detach(), k=topk, dim=-1).indices
     picked = probs.gather(-1, idx)
     if renorm:
         picked = picked / picked.sum(dim=-1, keepdim=True).clamp_min(1e-9)
     return idx, (picked * alpha).view(bsz * n, topk), probs.sum(dim=1)
+
+
+def route_softmax_topk(rows, router, bias, topk: int, alpha: float = 1.0, bias_in_logits: bool = False,
+                       renorm: bool = False):
+    """The softmax case of :func:`route_topk`."""
+    return route_topk(rows, router, bias, topk, alpha, bias_in_logits, renorm)
 
 
 def _pad_layout(offsets, sizes):
