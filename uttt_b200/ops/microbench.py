@@ -2,7 +2,7 @@
 
     python -m uttt_b200.ops.microbench [--kernel NAME] [--small] [--iters N]
 
-Kernels: gg_nt, gg_nn, gg_tn, bmm_nt, swa_fwd, swa_bwd, rms_norm, rope, fw_qk_prep, router, pool_step, plucker,
+Kernels: gg_nt, gg_nn, gg_tn, bmm_nt, swa_fwd, swa_bwd, rms_norm, add_rms_norm, embedding, rope, fw_qk_prep, router, pool_step, plucker,
 swiglu, permute, patch_decode, frob, fw_write_pw, adamw, ce.  ``--small`` runs one small case
 of the chosen kernel (inputs above L2 size, a few hundred MB on the device) three times, which is what the
 profile summaries under ``profiles/`` were captured from.  Prints one JSON line per case with the achieved
@@ -128,6 +128,22 @@ def run(kernel: str, small: bool, iters: int):
         w = torch.ones(1536, **bf)
         ms = _time(lambda: F.rms_norm(x, w, 1e-6), iters, flush)
         rec("rms_norm_fwd", ms, bytes_=2.0 * x.numel() * 2)
+    if kernel in ("add_rms_norm", "all"):
+        x = torch.randn(bsz * 2048 * 8, 1536, **bf)
+        dl = torch.randn_like(x)
+        w = torch.ones(1536, **bf)
+        ms = _time(lambda: F.add_rms_norm(x, dl, w, 1e-6), iters, flush)
+        rec("add_rms_norm_fwd", ms, bytes_=4.0 * x.numel() * 2)          # two reads, two writes
+    if kernel in ("embedding", "all"):
+        table = torch.randn(32000, 1536, **bf)
+        ids = (torch.rand(bsz, 32768 if not small else 8192, device=dev) ** 3 * 32000).long().clamp_(0, 31999)
+        ms = _time(lambda: F.embedding(ids, table), iters, flush)
+        rec("embedding_fwd", ms, bytes_=2.0 * ids.numel() * 1536 * 2)
+        gy = torch.randn(*ids.shape, 1536, **bf)
+        ext = load()
+        ms = _time(lambda: ext.embedding_bwd(gy, ids, 32000), iters, flush)
+        # read dy once, zero and reduce into the fp32 table
+        rec("embedding_bwd[fp32 reductions]", ms, bytes_=ids.numel() * 1536 * 2.0 + 2.0 * 32000 * 1536 * 4)
     if kernel in ("rope", "all"):
         q = torch.randn(bsz, 2048, 16, 96, **bf)
         ms = _time(lambda: F.rope(q, 0, 10000.0), iters, flush)
