@@ -508,6 +508,30 @@ def test_adamw_flat_matches_torch():
     _close(out[0], (gg.float() * 0.5).pow(2).sum(), 1e-1, 1e-3)
 
 
+@pytest.mark.parametrize("v", [1000, 12000, 32000, 50264, 33001])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_cross_entropy_in_place_kernel(v, dtype):
+    """softmax(logits) - onehot in place and the summed loss, for row lengths that take the register-resident
+    kernel (2, 4 or 8 vectors per thread) and the streaming kernel (rows too long or not a multiple of 8)."""
+    ext = _ext()
+    torch.manual_seed(12)
+    t = 37
+    logits = (torch.randn(t, v, device=DEV) * 3).to(dtype)
+    labels = torch.randint(0, v, (t,), device=DEV)
+    labels[5] = -100
+    labels[6] = v - 1
+    want = torch.softmax(logits.float(), -1)
+    keep = labels != -100
+    want[keep, labels[keep]] -= 1
+    want[~keep] = 0
+    want_loss = F.cross_entropy(logits.float(), labels, ignore_index=-100, reduction="sum")
+    loss = torch.zeros(1, device=DEV)
+    work = logits.clone()
+    ext.ce_fwd_bwd_(work, labels, loss, -100)
+    _close(work, want, 4e-3 if dtype == torch.bfloat16 else 1e-6, 1e-2 if dtype == torch.bfloat16 else 1e-4, "grad")
+    _close(loss[0], want_loss, 1e-2, 1e-4, "loss")
+
+
 def test_linear_cross_entropy():
     _ext()
     torch.manual_seed(10)

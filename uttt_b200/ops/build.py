@@ -10,6 +10,7 @@ from __future__ import annotations
 import glob
 import os
 import subprocess
+import time
 import sys
 import sysconfig
 from concurrent.futures import ThreadPoolExecutor
@@ -69,6 +70,7 @@ def build(verbose: bool = False, force: bool = False) -> str:
 
     def run(job):
         src, cmd = job
+        started = time.time()
         res = subprocess.run(cmd, capture_output=True, text=True)
         log = os.path.join(build_dir, os.path.basename(src) + ".log")
         with open(log, "w") as f:
@@ -77,6 +79,9 @@ def build(verbose: bool = False, force: bool = False) -> str:
             raise RuntimeError(f"nvcc failed for {src}:\n{res.stderr[-6000:]}")
         if verbose:
             print(res.stderr)
+        # date the object at the start of its compilation: a source edited while nvcc ran stays newer than it
+        obj = cmd[cmd.index("-o") + 1]
+        os.utime(obj, (started, started))
         return src
 
     if jobs:
@@ -99,7 +104,19 @@ def build(verbose: bool = False, force: bool = False) -> str:
             raise RuntimeError(f"link failed:\n{res.stderr[-4000:]}")
         with open(marker, "w") as fh:
             fh.write(flavour)
+        _check_symbols(TARGET)
     return TARGET
+
+
+def _check_symbols(path: str) -> None:
+    """Load the shared object with immediate binding: a declaration in the bindings that no object defines
+    (a stale object, a changed signature) fails here instead of at the first import on a GPU machine."""
+    import ctypes
+    import torch  # noqa: F401  (the extension links against torch's libraries)
+    try:
+        ctypes.CDLL(path, mode=os.RTLD_NOW)
+    except OSError as exc:
+        raise RuntimeError(f"{path} does not load: {exc}") from exc
 
 
 if __name__ == "__main__":

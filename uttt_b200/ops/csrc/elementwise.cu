@@ -1149,14 +1149,90 @@ __global__ void ce_fwd_bwd_kernel(T* __restrict__ logits, const int64_t* __restr
   }
 }
 
+// Same contract with the whole row held in registers (NV vectors of 8 values per thread, 512 threads): the row is
+// read once with 16-byte loads and written once, which is the algorithmic minimum of traffic.
+template <typename T, int NV>
+__global__ void __launch_bounds__(512) ce_fwd_bwd_reg_kernel(T* __restrict__ logits, const int64_t* __restrict__ labels,
+                                                             float* __restrict__ loss, int V, int64_t ignore_index) {
+  const int row = blockIdx.x;
+  T* lr = logits + (size_t)row * V;
+  const int64_t label = labels[row];
+  const int nvec = V >> 3;
+  float f[NV][8];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int v = threadIdx.x + j * 512;
+    if (v < nvec) {
+      Vec8<T>::load(lr + (size_t)v * 8, f[j]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mx = fmaxf(mx, f[j][i]);
+    }
+  }
+  __shared__ float smx[16], ssum[16];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  mx = warp_max(mx);
+  if (lane == 0) smx[warp] = mx;
+  __syncthreads();
+  float gm = smx[0];
+#pragma unroll
+  for (int i = 1; i < 16; ++i) gm = fmaxf(gm, smx[i]);
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int v = threadIdx.x + j * 512;
+    if (v < nvec) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        f[j][i] = __expf(f[j][i] - gm);
+        sum += f[j][i];
+      }
+    }
+  }
+  sum = warp_sum(sum);
+  if (lane == 0) ssum[warp] = sum;
+  const bool ignored = label == ignore_index;
+  float xl = 0.f;
+  if (threadIdx.x == 0 && !ignored) xl = to_f<T>(lr[label]);      // read before anybody overwrites the row
+  __syncthreads();
+  float gs = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) gs += ssum[i];
+  if (threadIdx.x == 0 && !ignored) atomicAdd(loss, -(xl - gm - __logf(gs)));
+  const float inv = ignored ? 0.f : 1.f / gs;
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int v = threadIdx.x + j * 512;
+    if (v < nvec) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        f[j][i] *= inv;
+        if (!ignored && (int64_t)v * 8 + i == label) f[j][i] -= 1.f;
+      }
+      Vec8<T>::store(lr + (size_t)v * 8, f[j]);
+    }
+  }
+}
+
 void ce_fwd_bwd_(at::Tensor logits, at::Tensor labels, at::Tensor loss, int64_t ignore_index) {
   c10::cuda::CUDAGuard guard(logits.device());
   TORCH_CHECK(logits.is_contiguous() && labels.scalar_type() == at::kLong && loss.scalar_type() == at::kFloat);
   int rows = logits.size(0), V = logits.size(1);
   if (rows == 0) return;
+  const int nvec = V / 8;
   UTTT_DISPATCH_FLOAT(logits, {
-    ce_fwd_bwd_kernel<T><<<rows, 512, 0, cur_stream()>>>(ptr<T>(logits), ptr<int64_t>(labels), ptr<float>(loss), V,
-                                                        ignore_index);
+    if (V % 8 == 0 && nvec <= 512 * 2)
+      ce_fwd_bwd_reg_kernel<T, 2><<<rows, 512, 0, cur_stream()>>>(ptr<T>(logits), ptr<int64_t>(labels),
+                                                                   ptr<float>(loss), V, ignore_index);
+    else if (V % 8 == 0 && nvec <= 512 * 4)
+      ce_fwd_bwd_reg_kernel<T, 4><<<rows, 512, 0, cur_stream()>>>(ptr<T>(logits), ptr<int64_t>(labels),
+                                                                   ptr<float>(loss), V, ignore_index);
+    else if (V % 8 == 0 && nvec <= 512 * 8)
+      ce_fwd_bwd_reg_kernel<T, 8><<<rows, 512, 0, cur_stream()>>>(ptr<T>(logits), ptr<int64_t>(labels),
+                                                                   ptr<float>(loss), V, ignore_index);
+    else
+      ce_fwd_bwd_kernel<T><<<rows, 512, 0, cur_stream()>>>(ptr<T>(logits), ptr<int64_t>(labels), ptr<float>(loss), V,
+                                                          ignore_index);
   });
   count_launch();
 }
