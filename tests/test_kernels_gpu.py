@@ -123,10 +123,14 @@ def test_rope(hd):
 
 
 @pytest.mark.parametrize("norm", ["l2", "rms", None])
-def test_fw_qk_prep(norm):
+@pytest.mark.parametrize("heads,D,rope_dim", [(4, 96, 32),      # warp form, 6 vector pairs per head
+                                              (4, 384, 96),     # warp form, the 760M shape (24 pairs, 96-wide sub-heads)
+                                              (2, 768, 256),    # warp form, two pairs per lane
+                                              (3, 72, 24)])     # block form (odd number of vectors per head)
+def test_fw_qk_prep(norm, heads, D, rope_dim):
     _ext()
     torch.manual_seed(1)
-    b, l, heads, D, rope_dim = 2, 160, 4, 96, 32
+    b, l = 2, 160
     d = heads * D
     x = torch.randn(b, l, d, device=DEV, dtype=torch.float32, requires_grad=True)
     sc = (torch.randn(d, device=DEV) * 0.1 + 1).requires_grad_(True)

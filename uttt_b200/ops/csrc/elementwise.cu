@@ -274,6 +274,36 @@ __global__ void rope_kernel(const T* __restrict__ x, T* __restrict__ y, const fl
   }
 }
 
+// Same rotation with eight pairs per thread: two 16-byte loads of x, four of the table, two 16-byte stores
+// (half a head must be a multiple of 8 elements).
+template <typename T>
+__global__ void rope_vec_kernel(const T* __restrict__ x, T* __restrict__ y, const float2* __restrict__ table, int l,
+                                int nh, int hd, int offset, float sign, size_t total_vecs) {
+  const int half = hd >> 1, hv = half >> 3;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total_vecs;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const int i = (int)(idx % hv) * 8;
+    const size_t t = idx / hv;      // (b*l + pos) * nh + head
+    const int pos = (int)((t / nh) % l);
+    const float4* tp = reinterpret_cast<const float4*>(table + (size_t)(offset + pos) * half + i);
+    const size_t base = t * hd + i;
+    float a[8], b[8], oa[8], ob[8];
+    Vec8<T>::load(x + base, a);
+    Vec8<T>::load(x + base + half, b);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float4 cs = __ldg(tp + k);
+      const float s0 = cs.y * sign, s1 = cs.w * sign;
+      oa[2 * k] = a[2 * k] * cs.x - b[2 * k] * s0;
+      ob[2 * k] = b[2 * k] * cs.x + a[2 * k] * s0;
+      oa[2 * k + 1] = a[2 * k + 1] * cs.z - b[2 * k + 1] * s1;
+      ob[2 * k + 1] = b[2 * k + 1] * cs.z + a[2 * k + 1] * s1;
+    }
+    Vec8<T>::store(y + base, oa);
+    Vec8<T>::store(y + base + half, ob);
+  }
+}
+
 at::Tensor rope_fwd(at::Tensor x, at::Tensor table, int64_t offset, bool inverse) {
   c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(x.dim() == 4 && x.is_contiguous());
@@ -282,6 +312,17 @@ at::Tensor rope_fwd(at::Tensor x, at::Tensor table, int64_t offset, bool inverse
   auto y = at::empty_like(x);
   size_t pairs = x.numel() / 2;
   int blocks = (int)std::min<size_t>((pairs + 255) / 256, (size_t)sm_count() * 16);
+  if ((hd / 2) % 8 == 0 && table.is_contiguous()) {
+    const size_t vecs = pairs / 8;
+    const int vblocks = (int)std::max<size_t>(1, std::min<size_t>((vecs + 255) / 256, (size_t)sm_count() * 16));
+    UTTT_DISPATCH_FLOAT(x, {
+      rope_vec_kernel<T><<<vblocks, 256, 0, cur_stream()>>>(
+          ptr<T>(x), ptr<T>(y), reinterpret_cast<const float2*>(table.data_ptr()), l, nh, hd, (int)offset,
+          inverse ? -1.f : 1.f, vecs);
+    });
+    count_launch();
+    return y;
+  }
   UTTT_DISPATCH_FLOAT(x, {
     rope_kernel<T><<<std::max(blocks, 1), 256, 0, cur_stream()>>>(
         ptr<T>(x), ptr<T>(y), reinterpret_cast<const float2*>(table.data_ptr()), l, nh, hd, (int)offset,
@@ -436,6 +477,245 @@ __global__ void fw_qk_prep_bwd_kernel(const T* __restrict__ dy, const T* __restr
   }
 }
 
+// Warp-per-(row, head) forms of the two kernels above, used when a head is at most 64 * MAXP 16-byte vectors wide
+// and half a rotary sub-head is a multiple of 8 elements.  A lane owns pairs of vectors that are half a sub-head
+// apart, i.e. both members of eight rotary pairs: every access is a 16-byte vector, the head's values stay in
+// registers, the rotation needs no exchange, and the forward has no shared memory or block barrier.
+struct QkPairMap {
+  int nv, npairs, px, vps;
+  __device__ __forceinline__ QkPairMap(int D, int rope_dim) {
+    nv = D >> 3;
+    npairs = nv >> 1;
+    px = rope_dim > 0 ? (rope_dim >> 4) : npairs;      // vectors in half a sub-head
+    vps = 2 * px;
+  }
+  __device__ __forceinline__ int first_vec(int p) const { return (p / px) * vps + (p % px); }
+};
+
+template <typename T, int MAXP>
+__global__ void __launch_bounds__(256) fw_qk_prep_fwd_warp_kernel(
+    const T* __restrict__ x, const T* __restrict__ scale, const T* __restrict__ shift,
+    const float2* __restrict__ table, T* __restrict__ y, float* __restrict__ inv_out, size_t rows, int d, int heads,
+    int rope_dim, int offset, int l, int silu, int norm) {
+  const int D = d / heads;
+  const QkPairMap map(D, rope_dim);
+  const int lane = threadIdx.x & 31;
+  const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
+  const size_t units = rows * (size_t)heads;
+  const int half = rope_dim >> 1;
+  for (size_t u = warp; u < units; u += nwarps) {
+    const size_t row = u / heads;
+    const int h = (int)(u - row * heads);
+    const size_t base = row * d + (size_t)h * D;
+    float s[MAXP][2][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < MAXP; ++j) {
+      const int p = lane + 32 * j;
+      if (p < map.npairs) {
+        const int v0 = map.first_vec(p);
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+          const int v = v0 + m * map.px;
+          Vec8<T>::load(x + base + v * 8, s[j][m]);
+          if (scale != nullptr) {
+            float sc[8], sh[8];
+            Vec8<T>::load(scale + h * D + v * 8, sc);
+            Vec8<T>::load(shift + h * D + v * 8, sh);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) s[j][m][i] = s[j][m][i] * sc[i] + sh[i];
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            if (silu) s[j][m][i] = siluf_(s[j][m][i]);
+            ss += s[j][m][i] * s[j][m][i];
+          }
+        }
+      }
+    }
+    float inv = 1.f;
+    if (norm) {
+      ss = warp_sum(ss);
+      inv = norm == 1 ? 1.f / (sqrtf(ss) + 1e-5f) : rsqrtf(ss / D + 1e-5f);
+    }
+    if (lane == 0) inv_out[u] = inv;
+    const int pos = offset + (int)(row % l);
+#pragma unroll
+    for (int j = 0; j < MAXP; ++j) {
+      const int p = lane + 32 * j;
+      if (p < map.npairs) {
+        const int v0 = map.first_vec(p);
+        float oa[8], ob[8];
+        if (rope_dim > 0) {
+          const float4* tp = reinterpret_cast<const float4*>(table + (size_t)pos * half + (p % map.px) * 8);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float4 cs = __ldg(tp + i);                     // (cos, sin) of two consecutive pairs
+            const float a0 = s[j][0][2 * i] * inv, b0 = s[j][1][2 * i] * inv;
+            const float a1 = s[j][0][2 * i + 1] * inv, b1 = s[j][1][2 * i + 1] * inv;
+            oa[2 * i] = a0 * cs.x - b0 * cs.y;
+            ob[2 * i] = b0 * cs.x + a0 * cs.y;
+            oa[2 * i + 1] = a1 * cs.z - b1 * cs.w;
+            ob[2 * i + 1] = b1 * cs.z + a1 * cs.w;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            oa[i] = s[j][0][i] * inv;
+            ob[i] = s[j][1][i] * inv;
+          }
+        }
+        Vec8<T>::store(y + base + v0 * 8, oa);
+        Vec8<T>::store(y + base + (v0 + map.px) * 8, ob);
+      }
+    }
+  }
+}
+
+// A warp keeps one head (warp index modulo heads) and strides over the rows, so its lanes own fixed columns and
+// carry the d(scale) / d(shift) partial sums in registers; they are merged per block in shared memory and added
+// to the result with one atomic per column and block.
+template <typename T, int MAXP>
+__global__ void __launch_bounds__(256) fw_qk_prep_bwd_warp_kernel(
+    const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ scale, const T* __restrict__ shift,
+    const float* __restrict__ inv_in, const float2* __restrict__ table, T* __restrict__ dx,
+    float* __restrict__ dscale, float* __restrict__ dshift, size_t rows, int d, int heads, int rope_dim, int offset,
+    int l, int silu, int norm) {
+  extern __shared__ float red[];                 // [2][d] block sums of d(scale), d(shift)
+  const int D = d / heads;
+  const QkPairMap map(D, rope_dim);
+  const int lane = threadIdx.x & 31;
+  const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;      // a multiple of heads (host)
+  const int h = (int)(warp % heads);
+  const int half = rope_dim >> 1;
+  if (dscale != nullptr) {
+    for (int i = threadIdx.x; i < 2 * d; i += blockDim.x) red[i] = 0.f;
+    __syncthreads();
+  }
+  float sc[MAXP][2][8], sh[MAXP][2][8], acc_s[MAXP][2][8], acc_b[MAXP][2][8];
+#pragma unroll
+  for (int j = 0; j < MAXP; ++j) {
+    const int p = lane + 32 * j;
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        sc[j][m][i] = 1.f;
+        sh[j][m][i] = 0.f;
+        acc_s[j][m][i] = acc_b[j][m][i] = 0.f;
+      }
+      if (scale != nullptr && p < map.npairs) {
+        const int v = map.first_vec(p) + m * map.px;
+        Vec8<T>::load(scale + h * D + v * 8, sc[j][m]);
+        Vec8<T>::load(shift + h * D + v * 8, sh[j][m]);
+      }
+    }
+  }
+  for (size_t row = warp / heads; row < rows; row += nwarps / heads) {
+    const size_t base = row * d + (size_t)h * D;
+    const int pos = offset + (int)(row % l);
+    float dn[MAXP][2][8], xv[MAXP][2][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < MAXP; ++j) {
+      const int p = lane + 32 * j;
+      if (p < map.npairs) {
+        const int v0 = map.first_vec(p);
+        float ga[8], gb[8];
+        Vec8<T>::load(dy + base + v0 * 8, ga);
+        Vec8<T>::load(dy + base + (v0 + map.px) * 8, gb);
+        Vec8<T>::load(x + base + v0 * 8, xv[j][0]);
+        Vec8<T>::load(x + base + (v0 + map.px) * 8, xv[j][1]);
+        if (rope_dim > 0) {
+          const float4* tp = reinterpret_cast<const float4*>(table + (size_t)pos * half + (p % map.px) * 8);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float4 cs = __ldg(tp + i);
+            dn[j][0][2 * i] = ga[2 * i] * cs.x + gb[2 * i] * cs.y;
+            dn[j][1][2 * i] = gb[2 * i] * cs.x - ga[2 * i] * cs.y;
+            dn[j][0][2 * i + 1] = ga[2 * i + 1] * cs.z + gb[2 * i + 1] * cs.w;
+            dn[j][1][2 * i + 1] = gb[2 * i + 1] * cs.z - ga[2 * i + 1] * cs.w;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            dn[j][0][i] = ga[i];
+            dn[j][1][i] = gb[i];
+          }
+        }
+#pragma unroll
+        for (int m = 0; m < 2; ++m)
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float a = xv[j][m][i] * sc[j][m][i] + sh[j][m][i];
+            dot += dn[j][m][i] * (silu ? siluf_(a) : a);
+          }
+      }
+    }
+    const float inv = inv_in[row * heads + h];
+    float c1 = 0.f;                              // coefficient of s in d(s)
+    if (norm) {
+      dot = warp_sum(dot);
+      if (norm == 1) c1 = dot * inv * inv / fmaxf(1.f / inv - 1e-5f, 1e-20f);
+      else c1 = dot * inv * inv * inv / D;
+    }
+#pragma unroll
+    for (int j = 0; j < MAXP; ++j) {
+      const int p = lane + 32 * j;
+      if (p < map.npairs) {
+        const int v0 = map.first_vec(p);
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+          float o[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float a = xv[j][m][i] * sc[j][m][i] + sh[j][m][i];
+            const float s = silu ? siluf_(a) : a;
+            const float ds = norm ? dn[j][m][i] * inv - s * c1 : dn[j][m][i];
+            const float da = silu ? ds * dsiluf_(a) : ds;
+            o[i] = da * sc[j][m][i];
+            acc_s[j][m][i] += da * xv[j][m][i];
+            acc_b[j][m][i] += da;
+          }
+          Vec8<T>::store(dx + base + (v0 + m * map.px) * 8, o);
+        }
+      }
+    }
+  }
+  if (dscale != nullptr) {
+#pragma unroll
+    for (int j = 0; j < MAXP; ++j) {
+      const int p = lane + 32 * j;
+      if (p < map.npairs) {
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+          const int c0 = h * D + (map.first_vec(p) + m * map.px) * 8;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            atomicAdd(red + c0 + i, acc_s[j][m][i]);
+            atomicAdd(red + d + c0 + i, acc_b[j][m][i]);
+          }
+        }
+      }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+      atomicAdd(dscale + i, red[i]);
+      atomicAdd(dshift + i, red[d + i]);
+    }
+  }
+}
+
+static inline bool qk_warp_form_ok(int d, int heads, int rope_dim) {
+  if (d % heads != 0) return false;
+  const int D = d / heads;
+  if (D % 16 != 0 || D > 16 * 32 * 2) return false;          // an even number of vectors, at most 64 pairs
+  if (rope_dim == 0) return true;
+  return rope_dim % 16 == 0 && D % rope_dim == 0;
+}
+
 std::vector<at::Tensor> fw_qk_prep_fwd(at::Tensor x, c10::optional<at::Tensor> scale,
                                        c10::optional<at::Tensor> shift, at::Tensor table, int64_t heads,
                                        int64_t rope_dim, int64_t offset, int64_t l, bool silu, int64_t norm) {
@@ -450,6 +730,22 @@ std::vector<at::Tensor> fw_qk_prep_fwd(at::Tensor x, c10::optional<at::Tensor> s
     sh = shift->to(x.scalar_type()).contiguous();
   }
   size_t smem = (d + heads) * sizeof(float);
+  if (qk_warp_form_ok(d, (int)heads, (int)rope_dim) && rows > 0) {
+    const size_t units = (size_t)rows * heads;
+    const int blocks = (int)std::max<size_t>(1, std::min<size_t>((units + 7) / 8, (size_t)sm_count() * 8));
+    UTTT_DISPATCH_FLOAT(x, {
+      auto go = [&](auto kernel) {
+        kernel<<<blocks, 256, 0, cur_stream()>>>(
+            ptr<T>(x), sc.defined() ? ptr<T>(sc) : nullptr, sc.defined() ? ptr<T>(sh) : nullptr,
+            rope_dim > 0 ? reinterpret_cast<const float2*>(table.data_ptr()) : nullptr, ptr<T>(y), ptr<float>(inv),
+            (size_t)rows, d, (int)heads, (int)rope_dim, (int)offset, (int)l, silu ? 1 : 0, (int)norm);
+      };
+      if (d / heads <= 512) go(fw_qk_prep_fwd_warp_kernel<T, 1>);
+      else go(fw_qk_prep_fwd_warp_kernel<T, 2>);
+    });
+    count_launch();
+    return {y, inv};
+  }
   UTTT_DISPATCH_FLOAT(x, {
     fw_qk_prep_fwd_kernel<T><<<rows, 256, smem, cur_stream()>>>(
         ptr<T>(x), sc.defined() ? ptr<T>(sc) : nullptr, sc.defined() ? ptr<T>(sh) : nullptr,
@@ -478,6 +774,25 @@ std::vector<at::Tensor> fw_qk_prep_bwd(at::Tensor dy, at::Tensor x, c10::optiona
   auto dshift = at::zeros({has ? d : 1}, x.options().dtype(at::kFloat));
   size_t smem = (2 * d + heads) * sizeof(float);
   int blocks = std::max(1, std::min(rows, sm_count() * 4));
+  if (qk_warp_form_ok(d, (int)heads, (int)rope_dim) && rows > 0 && heads <= 8 * 4) {
+    // 8 warps per block; the warp count must be a multiple of the head count (a warp keeps its head)
+    int wblocks = std::max(1, std::min((int)(((size_t)rows * heads + 7) / 8), sm_count() * 4));
+    while (((size_t)wblocks * 8) % heads != 0) ++wblocks;
+    const size_t wsmem = (size_t)2 * d * sizeof(float);
+    UTTT_DISPATCH_FLOAT(x, {
+      auto go = [&](auto kernel) {
+        kernel<<<wblocks, 256, has ? wsmem : 0, cur_stream()>>>(
+            ptr<T>(dy), ptr<T>(x), has ? ptr<T>(sc) : nullptr, has ? ptr<T>(sh) : nullptr, ptr<float>(inv),
+            rope_dim > 0 ? reinterpret_cast<const float2*>(table.data_ptr()) : nullptr, ptr<T>(dx),
+            has ? ptr<float>(dscale) : nullptr, has ? ptr<float>(dshift) : nullptr, (size_t)rows, d, (int)heads,
+            (int)rope_dim, (int)offset, (int)l, silu ? 1 : 0, (int)norm);
+      };
+      if (d / heads <= 512) go(fw_qk_prep_bwd_warp_kernel<T, 1>);
+      else go(fw_qk_prep_bwd_warp_kernel<T, 2>);
+    });
+    count_launch();
+    return {dx, dscale, dshift};
+  }
   UTTT_DISPATCH_FLOAT(x, {
     auto launch = [&](auto maxc) {
       constexpr int MAXC = decltype(maxc)::value;
