@@ -133,3 +133,30 @@ def test_newton_schulz_orthogonalises():
     x = ops.newton_schulz(g)
     s = torch.linalg.svdvals(x.float())
     assert s.max() < 1.3 and s.min() > 0.5
+
+
+def test_router_types_and_small_ops_on_cpu():
+    """The portable statements behind the fused kernels: normalised router types, residual add + norm, embedding."""
+    torch.manual_seed(3)
+    rows = torch.randn(2, 50, 16)
+    router = torch.randn(8, 16)
+    bias = torch.randn(8) * 0.01
+    for rtype in ("softmax", "norm_softmax", "norm_relu"):
+        idx, w, psum = ops.route_topk(rows, router, bias, 2, 0.5, False, True, rtype, 0.0, 1e-6)
+        sel, probs = ref.route_scores(rows @ router.t(), rtype, 0.0, 1e-6)
+        assert torch.equal(idx, (sel + bias).topk(2, -1).indices)
+        picked = probs.gather(-1, idx)
+        torch.testing.assert_close(w, (picked / picked.sum(-1, keepdim=True) * 0.5).view(-1, 2))
+        torch.testing.assert_close(psum, probs.sum(1))
+        torch.testing.assert_close(psum.sum(-1), torch.full((2,), 50.0))      # every variant yields a distribution
+    x, delta, wgt = torch.randn(7, 16), torch.randn(7, 16), torch.rand(16) + 0.5
+    s, y = ops.add_rms_norm(x, delta, wgt, 1e-6)
+    torch.testing.assert_close(s, x + delta)
+    torch.testing.assert_close(y, ops.rms_norm(x + delta, wgt, 1e-6))
+    from uttt_b200.models.common import TokenEmbedding
+    emb = TokenEmbedding(11, 8, padding_idx=3)
+    ids = torch.tensor([[1, 3, 3, 10], [0, 1, 1, 1]])
+    out = emb(ids)
+    assert torch.equal(out, emb.weight[ids])
+    out.sum().backward()
+    assert float(emb.weight.grad[3].abs().sum()) == 0.0 and float(emb.weight.grad[1].sum()) == 4 * 8

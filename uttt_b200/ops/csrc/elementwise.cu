@@ -1032,13 +1032,36 @@ std::vector<at::Tensor> fw_write_pw_bwd(at::Tensor C, at::Tensor Ch, at::Tensor 
 
 // ------------------------------------------------------------------------------------ row permutation
 // out[dest[i, j]] = x[i] (one warp per (i, j)); out is zero-filled first so padding rows are zero.
+// Padding rows of the tile-padded layout, cleared by extra blocks of the scatter kernel itself: blocks
+// [copy_blocks, copy_blocks + 2 * groups) zero rows [offsets[g] + sizes[g], offsets[g + 1]) of group g (two blocks
+// per group).  Returns true in those blocks.
+struct PadLayout {
+  const int* offsets;
+  const int* sizes;
+  int groups;
+  int copy_blocks;       // blocks that scatter; the grid holds 2 * groups more when offsets != nullptr
+};
+__device__ __forceinline__ bool zero_pad_block(void* out, int vec_per_row, const PadLayout& pad) {
+  if (pad.offsets == nullptr || (int)blockIdx.x < pad.copy_blocks) return false;
+  const int pb = blockIdx.x - pad.copy_blocks, g = pb >> 1, part = pb & 1;
+  if (g < pad.groups) {
+    const int begin = pad.offsets[g] + pad.sizes[g], end = pad.offsets[g + 1];
+    const long long first = (long long)begin * vec_per_row, n = (long long)(end - begin) * vec_per_row;
+    uint4* o = reinterpret_cast<uint4*>(out);
+    for (long long i = (long long)part * blockDim.x + threadIdx.x; i < n; i += 2 * blockDim.x)
+      o[first + i] = make_uint4(0, 0, 0, 0);
+  }
+  return true;
+}
+
 template <typename T>
 __global__ void permute_rows_kernel(const T* __restrict__ x, const int64_t* __restrict__ dest,
                                     const float* __restrict__ w, T* __restrict__ out, size_t n_copies, int k,
-                                    int d, long long rows_out, int* __restrict__ status) {
+                                    int d, long long rows_out, int* __restrict__ status, PadLayout pad) {
+  if (zero_pad_block(out, d * (int)sizeof(T) / 16, pad)) return;
   size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   int lane = threadIdx.x & 31;
-  size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
+  size_t nwarps = ((size_t)pad.copy_blocks * blockDim.x) >> 5;
   for (size_t c = warp; c < n_copies; c += nwarps) {
     if (!UTTT_INDEX_OK(dest[c], rows_out, status, 71)) continue;
     const T* src = x + (c / k) * d;
@@ -1096,10 +1119,12 @@ __global__ void unpermute_rows_kernel(const T* __restrict__ y, const int64_t* __
 template <typename T>
 __global__ void unpermute_rows_bwd_kernel(const T* __restrict__ dout, const T* __restrict__ y,
                                           const int64_t* __restrict__ dest, const float* __restrict__ w,
-                                          T* __restrict__ dy, float* __restrict__ dw, size_t n_copies, int k, int d) {
+                                          T* __restrict__ dy, float* __restrict__ dw, size_t n_copies, int k, int d,
+                                          PadLayout pad) {
+  if (zero_pad_block(dy, d * (int)sizeof(T) / 16, pad)) return;
   size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   int lane = threadIdx.x & 31;
-  size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
+  size_t nwarps = ((size_t)pad.copy_blocks * blockDim.x) >> 5;
   int nv = d >> 3;
   for (size_t c = warp; c < n_copies; c += nwarps) {
     size_t r = c / k;
@@ -1122,32 +1147,19 @@ __global__ void unpermute_rows_bwd_kernel(const T* __restrict__ dout, const T* _
   }
 }
 
-// Zero rows [offsets[g] + sizes[g], offsets[g + 1]) of every group: the tile padding that token reductions read.
-__global__ void zero_pad_rows_kernel(uint4* __restrict__ out, const int* __restrict__ offsets,
-                                     const int* __restrict__ sizes, int groups, int vec_per_row) {
-  // one block per group: its (< 128) padding rows are cleared by all threads together
-  const int g = blockIdx.x;
-  if (g >= groups) return;
-  const int begin = offsets[g] + sizes[g], end = offsets[g + 1];
-  const long long first = (long long)begin * vec_per_row, n = (long long)(end - begin) * vec_per_row;
-  for (long long i = threadIdx.x; i < n; i += blockDim.x) out[first + i] = make_uint4(0, 0, 0, 0);
-}
-
 // A [rows_padded, d] buffer for a scatter into the tile-padded layout.  With the layout's offsets / sizes only
-// the padding rows inside groups are cleared (rows of tiles past the last group are never read); without them the
-// whole buffer is zero-filled.
+// the padding rows inside groups are cleared, by extra blocks of the scatter kernel (rows of tiles past the last
+// group are never read); without them the whole buffer is zero-filled here.
 static at::Tensor padded_buffer(int64_t rows_padded, int d, const at::TensorOptions& opt,
-                                const c10::optional<at::Tensor>& offsets, const c10::optional<at::Tensor>& sizes) {
+                                const c10::optional<at::Tensor>& offsets, const c10::optional<at::Tensor>& sizes,
+                                int copy_blocks, PadLayout* pad) {
+  *pad = PadLayout{nullptr, nullptr, 0, copy_blocks};
   if (!(offsets.has_value() && offsets->defined() && sizes.has_value() && sizes->defined()))
     return at::zeros({rows_padded, d}, opt);
   auto out = at::empty({rows_padded, d}, opt);
   TORCH_CHECK(offsets->scalar_type() == at::kInt && sizes->scalar_type() == at::kInt &&
               offsets->numel() == sizes->numel() + 1 && (d * out.element_size()) % 16 == 0);
-  int groups = sizes->numel();
-  zero_pad_rows_kernel<<<std::max(1, groups), 256, 0, cur_stream()>>>(
-      reinterpret_cast<uint4*>(out.data_ptr()), offsets->data_ptr<int>(), sizes->data_ptr<int>(), groups,
-      (int)(d * out.element_size() / 16));
-  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  *pad = PadLayout{offsets->data_ptr<int>(), sizes->data_ptr<int>(), (int)sizes->numel(), copy_blocks};
   return out;
 }
 
@@ -1157,18 +1169,18 @@ at::Tensor permute_rows(at::Tensor x, at::Tensor dest, int64_t rows_padded, c10:
   int d = x.size(1);
   int k = dest.size(1);
   TORCH_CHECK(x.is_contiguous() && dest.is_contiguous() && dest.scalar_type() == at::kLong && d % 8 == 0);
-  auto out = padded_buffer(rows_padded, d, x.options(), offsets, sizes);
   size_t n = (size_t)dest.numel();
+  int blocks = (int)std::max<size_t>(1, std::min<size_t>((n + 7) / 8, (size_t)sm_count() * 16));
+  PadLayout pad;
+  auto out = padded_buffer(rows_padded, d, x.options(), offsets, sizes, blocks, &pad);
   at::Tensor wf;
   if (w.has_value() && w->defined()) wf = w->to(at::kFloat).contiguous();
-  int blocks = (int)std::max<size_t>(1, std::min<size_t>((n + 7) / 8, (size_t)sm_count() * 16));
   UTTT_DISPATCH_FLOAT(x, {
-    permute_rows_kernel<T><<<blocks, 256, 0, cur_stream()>>>(ptr<T>(x), ptr<int64_t>(dest),
-                                                            wf.defined() ? ptr<float>(wf) : nullptr, ptr<T>(out), n,
-                                                            k, d, (long long)rows_padded,
-                                                            gemm_status(x).data_ptr<int>());
+    permute_rows_kernel<T><<<blocks + 2 * pad.groups, 256, 0, cur_stream()>>>(
+        ptr<T>(x), ptr<int64_t>(dest), wf.defined() ? ptr<float>(wf) : nullptr, ptr<T>(out), n, k, d,
+        (long long)rows_padded, gemm_status(x).data_ptr<int>(), pad);
   });
-  count_launch(2);
+  count_launch();
   return out;
 }
 
@@ -1199,14 +1211,15 @@ std::vector<at::Tensor> unpermute_rows_bwd(at::Tensor dout, at::Tensor y, at::Te
   int k = dest.size(1);
   size_t n = (size_t)dest.numel();
   auto wf = w.to(at::kFloat).contiguous();
-  auto dy = padded_buffer(y.size(0), d, y.options(), offsets, sizes);
-  auto dw = at::empty({dest.size(0), k}, y.options().dtype(at::kFloat));
   int blocks = (int)std::max<size_t>(1, std::min<size_t>((n + 7) / 8, (size_t)sm_count() * 16));
+  PadLayout pad;
+  auto dy = padded_buffer(y.size(0), d, y.options(), offsets, sizes, blocks, &pad);
+  auto dw = at::empty({dest.size(0), k}, y.options().dtype(at::kFloat));
   UTTT_DISPATCH_FLOAT(y, {
-    unpermute_rows_bwd_kernel<T><<<blocks, 256, 0, cur_stream()>>>(ptr<T>(dout), ptr<T>(y), ptr<int64_t>(dest),
-                                                                  ptr<float>(wf), ptr<T>(dy), ptr<float>(dw), n, k, d);
+    unpermute_rows_bwd_kernel<T><<<blocks + 2 * pad.groups, 256, 0, cur_stream()>>>(
+        ptr<T>(dout), ptr<T>(y), ptr<int64_t>(dest), ptr<float>(wf), ptr<T>(dy), ptr<float>(dw), n, k, d, pad);
   });
-  count_launch(2);
+  count_launch();
   return {dy, dw};
 }
 
