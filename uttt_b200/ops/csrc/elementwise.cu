@@ -594,25 +594,27 @@ __global__ void __launch_bounds__(256) fw_qk_prep_bwd_warp_kernel(
     for (int i = threadIdx.x; i < 2 * d; i += blockDim.x) red[i] = 0.f;
     __syncthreads();
   }
-  float sc[MAXP][2][8], sh[MAXP][2][8], acc_s[MAXP][2][8], acc_b[MAXP][2][8];
+  // scale / shift of this warp's columns are re-read per row (they stay in L1): keeping them in registers next
+  // to the partial sums would halve the resident warps
+  float acc_s[MAXP][2][8], acc_b[MAXP][2][8];
 #pragma unroll
-  for (int j = 0; j < MAXP; ++j) {
-    const int p = lane + 32 * j;
+  for (int j = 0; j < MAXP; ++j)
 #pragma unroll
-    for (int m = 0; m < 2; ++m) {
+    for (int m = 0; m < 2; ++m)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc_s[j][m][i] = acc_b[j][m][i] = 0.f;
+  auto affine = [&](int v, float (&sc)[8], float (&sh)[8]) {
+    if (scale != nullptr) {
+      Vec8<T>::load(scale + h * D + v * 8, sc);
+      Vec8<T>::load(shift + h * D + v * 8, sh);
+    } else {
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        sc[j][m][i] = 1.f;
-        sh[j][m][i] = 0.f;
-        acc_s[j][m][i] = acc_b[j][m][i] = 0.f;
-      }
-      if (scale != nullptr && p < map.npairs) {
-        const int v = map.first_vec(p) + m * map.px;
-        Vec8<T>::load(scale + h * D + v * 8, sc[j][m]);
-        Vec8<T>::load(shift + h * D + v * 8, sh[j][m]);
+        sc[i] = 1.f;
+        sh[i] = 0.f;
       }
     }
-  }
+  };
   for (size_t row = warp / heads; row < rows; row += nwarps / heads) {
     const size_t base = row * d + (size_t)h * D;
     const int pos = offset + (int)(row % l);
@@ -646,12 +648,15 @@ __global__ void __launch_bounds__(256) fw_qk_prep_bwd_warp_kernel(
           }
         }
 #pragma unroll
-        for (int m = 0; m < 2; ++m)
+        for (int m = 0; m < 2; ++m) {
+          float sc[8], sh[8];
+          affine(v0 + m * map.px, sc, sh);
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            const float a = xv[j][m][i] * sc[j][m][i] + sh[j][m][i];
+            const float a = xv[j][m][i] * sc[i] + sh[i];
             dot += dn[j][m][i] * (silu ? siluf_(a) : a);
           }
+        }
       }
     }
     const float inv = inv_in[row * heads + h];
@@ -668,14 +673,15 @@ __global__ void __launch_bounds__(256) fw_qk_prep_bwd_warp_kernel(
         const int v0 = map.first_vec(p);
 #pragma unroll
         for (int m = 0; m < 2; ++m) {
-          float o[8];
+          float o[8], sc[8], sh[8];
+          affine(v0 + m * map.px, sc, sh);
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            const float a = xv[j][m][i] * sc[j][m][i] + sh[j][m][i];
+            const float a = xv[j][m][i] * sc[i] + sh[i];
             const float s = silu ? siluf_(a) : a;
             const float ds = norm ? dn[j][m][i] * inv - s * c1 : dn[j][m][i];
             const float da = silu ? ds * dsiluf_(a) : ds;
-            o[i] = da * sc[j][m][i];
+            o[i] = da * sc[i];
             acc_s[j][m][i] += da * xv[j][m][i];
             acc_b[j][m][i] += da;
           }
