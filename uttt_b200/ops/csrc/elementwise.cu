@@ -504,6 +504,13 @@ __global__ void __launch_bounds__(256) fw_qk_prep_fwd_warp_kernel(
   const size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
   const size_t units = rows * (size_t)heads;
   const int half = rope_dim >> 1;
+  int v0s[MAXP], toff[MAXP];                      // per lane: first vector of each owned pair, its table offset
+#pragma unroll
+  for (int j = 0; j < MAXP; ++j) {
+    const int p = lane + 32 * j;
+    v0s[j] = p < map.npairs ? map.first_vec(p) : -1;
+    toff[j] = (p % map.px) * 8;
+  }
   for (size_t u = warp; u < units; u += nwarps) {
     const size_t row = u / heads;
     const int h = (int)(u - row * heads);
@@ -512,9 +519,8 @@ __global__ void __launch_bounds__(256) fw_qk_prep_fwd_warp_kernel(
     float ss = 0.f;
 #pragma unroll
     for (int j = 0; j < MAXP; ++j) {
-      const int p = lane + 32 * j;
-      if (p < map.npairs) {
-        const int v0 = map.first_vec(p);
+      if (v0s[j] >= 0) {
+        const int v0 = v0s[j];
 #pragma unroll
         for (int m = 0; m < 2; ++m) {
           const int v = v0 + m * map.px;
@@ -543,12 +549,11 @@ __global__ void __launch_bounds__(256) fw_qk_prep_fwd_warp_kernel(
     const int pos = offset + (int)(row % l);
 #pragma unroll
     for (int j = 0; j < MAXP; ++j) {
-      const int p = lane + 32 * j;
-      if (p < map.npairs) {
-        const int v0 = map.first_vec(p);
+      if (v0s[j] >= 0) {
+        const int v0 = v0s[j];
         float oa[8], ob[8];
         if (rope_dim > 0) {
-          const float4* tp = reinterpret_cast<const float4*>(table + (size_t)pos * half + (p % map.px) * 8);
+          const float4* tp = reinterpret_cast<const float4*>(table + (size_t)pos * half + toff[j]);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const float4 cs = __ldg(tp + i);                     // (cos, sin) of two consecutive pairs
@@ -590,6 +595,13 @@ __global__ void __launch_bounds__(256) fw_qk_prep_bwd_warp_kernel(
   const size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;      // a multiple of heads (host)
   const int h = (int)(warp % heads);
   const int half = rope_dim >> 1;
+  int v0s[MAXP], toff[MAXP];                      // per lane: first vector of each owned pair, its table offset
+#pragma unroll
+  for (int j = 0; j < MAXP; ++j) {
+    const int p = lane + 32 * j;
+    v0s[j] = p < map.npairs ? map.first_vec(p) : -1;
+    toff[j] = (p % map.px) * 8;
+  }
   if (dscale != nullptr) {
     for (int i = threadIdx.x; i < 2 * d; i += blockDim.x) red[i] = 0.f;
     __syncthreads();
@@ -622,16 +634,15 @@ __global__ void __launch_bounds__(256) fw_qk_prep_bwd_warp_kernel(
     float dot = 0.f;
 #pragma unroll
     for (int j = 0; j < MAXP; ++j) {
-      const int p = lane + 32 * j;
-      if (p < map.npairs) {
-        const int v0 = map.first_vec(p);
+      if (v0s[j] >= 0) {
+        const int v0 = v0s[j];
         float ga[8], gb[8];
         Vec8<T>::load(dy + base + v0 * 8, ga);
         Vec8<T>::load(dy + base + (v0 + map.px) * 8, gb);
         Vec8<T>::load(x + base + v0 * 8, xv[j][0]);
         Vec8<T>::load(x + base + (v0 + map.px) * 8, xv[j][1]);
         if (rope_dim > 0) {
-          const float4* tp = reinterpret_cast<const float4*>(table + (size_t)pos * half + (p % map.px) * 8);
+          const float4* tp = reinterpret_cast<const float4*>(table + (size_t)pos * half + toff[j]);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const float4 cs = __ldg(tp + i);
@@ -668,9 +679,8 @@ __global__ void __launch_bounds__(256) fw_qk_prep_bwd_warp_kernel(
     }
 #pragma unroll
     for (int j = 0; j < MAXP; ++j) {
-      const int p = lane + 32 * j;
-      if (p < map.npairs) {
-        const int v0 = map.first_vec(p);
+      if (v0s[j] >= 0) {
+        const int v0 = v0s[j];
 #pragma unroll
         for (int m = 0; m < 2; ++m) {
           float o[8], sc[8], sh[8];
@@ -693,11 +703,10 @@ __global__ void __launch_bounds__(256) fw_qk_prep_bwd_warp_kernel(
   if (dscale != nullptr) {
 #pragma unroll
     for (int j = 0; j < MAXP; ++j) {
-      const int p = lane + 32 * j;
-      if (p < map.npairs) {
+      if (v0s[j] >= 0) {
 #pragma unroll
         for (int m = 0; m < 2; ++m) {
-          const int c0 = h * D + (map.first_vec(p) + m * map.px) * 8;
+          const int c0 = h * D + (v0s[j] + m * map.px) * 8;
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             atomicAdd(red + c0 + i, acc_s[j][m][i]);
