@@ -219,7 +219,7 @@ static std::vector<at::Tensor> rms_norm_bwd_impl(at::Tensor dy, at::Tensor x, c1
   TORCH_CHECK(d % 8 == 0 && d <= 8 * 32 * 16, "rms_norm_bwd: hidden size must be a multiple of 8 and <= 4096");
   auto dx = at::empty_like(x);
   at::Tensor wc, dw;
-  int blocks = std::max(1, std::min((rows + 3) / 4, sm_count() * 2));
+  int blocks = std::max(1, std::min((rows + 3) / 4, sm_count() * 4));
   if (w.has_value() && w->defined()) {
     wc = w->to(x.scalar_type()).contiguous();
     dw = at::empty({blocks, d}, x.options().dtype(at::kFloat));
