@@ -511,11 +511,32 @@ __global__ void __launch_bounds__(256) fw_qk_prep_fwd_warp_kernel(
     v0s[j] = p < map.npairs ? map.first_vec(p) : -1;
     toff[j] = (p % map.px) * 8;
   }
+  // the next unit's values are requested before this unit's arithmetic and reduction, so that a warp always has
+  // loads in flight
+  float nx[MAXP][2][8];
+  auto fetch = [&](size_t uu) {
+    const size_t r = uu / heads;
+    const size_t b = r * d + (uu - r * heads) * (size_t)D;
+#pragma unroll
+    for (int j = 0; j < MAXP; ++j)
+      if (v0s[j] >= 0) {
+#pragma unroll
+        for (int m = 0; m < 2; ++m) Vec8<T>::load(x + b + (v0s[j] + m * map.px) * 8, nx[j][m]);
+      }
+  };
+  if (warp < units) fetch(warp);
   for (size_t u = warp; u < units; u += nwarps) {
     const size_t row = u / heads;
     const int h = (int)(u - row * heads);
     const size_t base = row * d + (size_t)h * D;
     float s[MAXP][2][8];
+#pragma unroll
+    for (int j = 0; j < MAXP; ++j)
+#pragma unroll
+      for (int m = 0; m < 2; ++m)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s[j][m][i] = nx[j][m][i];
+    if (u + nwarps < units) fetch(u + nwarps);
     float ss = 0.f;
 #pragma unroll
     for (int j = 0; j < MAXP; ++j) {
@@ -524,7 +545,6 @@ __global__ void __launch_bounds__(256) fw_qk_prep_fwd_warp_kernel(
 #pragma unroll
         for (int m = 0; m < 2; ++m) {
           const int v = v0 + m * map.px;
-          Vec8<T>::load(x + base + v * 8, s[j][m]);
           if (scale != nullptr) {
             float sc[8], sh[8];
             Vec8<T>::load(scale + h * D + v * 8, sc);
