@@ -199,6 +199,34 @@ def test_trainer_runs_saves_and_resumes(tmp_path):
         torch.testing.assert_close(p1, p2, msg=n1)
 
 
+def test_grad_accumulation_keeps_every_micro_batch(tmp_path):
+    """Two passes of b scenes with grad_accum_steps=2 give the same update as one pass of 2b scenes."""
+    big = _batch(b=4)
+
+    def run(accum):
+        cfg = _cfg(block="uttt_nvs.models.transformer_block.TransformerModel")
+        tr = cfg["training"]
+        tr.update(out_dir=str(tmp_path / f"a{accum}"), grad_accum_steps=accum, batch_size_per_gpu=4 // accum,
+                  total_batch_size=4, grad_clip_norm=0.0, weight_decay=0.0)
+        t = NVSTrainer(cfg, device=torch.device("cpu"))
+        per = 4 // accum
+        for i in range(accum):
+            t.train_pass({k: v[i * per:(i + 1) * per] for k, v in big.items() if torch.is_tensor(v)})
+        assert t.update_step == 1
+        return {n: p.detach().clone() for n, p in t.model.named_parameters()}
+
+    one, two = run(1), run(2)
+    moved = 0
+    for n in one:
+        torch.testing.assert_close(two[n], one[n], rtol=1e-4, atol=2e-5, msg=n)
+    # dropping the last micro-batch changes the update by far more than the tolerance above
+    ref0 = {n: p.detach().clone() for n, p in NVSTrainer(
+        {**_cfg(block="uttt_nvs.models.transformer_block.TransformerModel"),
+         "training": {**_cfg()["training"], "out_dir": str(tmp_path / "z")}},
+        device=torch.device("cpu")).model.named_parameters()}
+    assert any((one[n] - ref0[n]).abs().max() > 1e-4 for n in one)
+
+
 def test_metrics():
     a = torch.rand(3, 3, 32, 32)
     assert float(ssim(a, a).min()) > 0.999

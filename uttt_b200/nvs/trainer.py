@@ -98,12 +98,14 @@ class _OptimizerView:
 
     def __init__(self, trainer: ShardedTrainer):
         self.trainer = trainer
+        self.loaded = False          # True once fp32 masters and moments came from a checkpoint
 
     def state_dict(self):
         return self.trainer.optimizer_state_dict()
 
     def load_state_dict(self, sd):
         self.trainer.load_optimizer_state_dict(sd)
+        self.loaded = True
 
 
 class _Schedule:
@@ -146,7 +148,11 @@ class NVSTrainer:
                 reset_training_state=bool(tr.get("reset_training_state", False)),
                 load_optimizer_state_when_reset_training_state=bool(
                     tr.get("load_optimizer_state_when_reset_training_state", False)))
-            self.trainer.load_model_state()
+            if not self.optimizer.loaded:
+                # only the model came back (a reset of the training state): rebuild the fp32 masters from it.
+                # With optimizer state loaded the masters are already exact; re-reading the bf16 compute copy
+                # would round them.
+                self.trainer.load_model_state()
         self.data = self._build_data()
         self.step_times: List[float] = []
 
@@ -192,6 +198,8 @@ class NVSTrainer:
         (loss * vote / self.accum).backward()
         self.fwdbwd_step += 1
         stats: Dict[str, Any] = {"loss": loss.detach(), "psnr": result["loss_metrics"]["psnr"], "finite": vote}
+        if self.accum > 1:
+            self.trainer.accumulate_micro_batch()             # every pass, the last one included
         if self.fwdbwd_step % self.accum == 0:
             lr = lr_at(self.update_step, float(tr.get("lr", 4e-4)), int(tr.get("warmup", 0)),
                        max(self.total // self.accum, 1), tr.get("scheduler_type", "cosine"),
@@ -203,8 +211,6 @@ class NVSTrainer:
             self.update_step += 1
             self.schedule.step_count = self.update_step
             stats.update(grad_norm=out["grad_norm"], skipped=out["skipped"], lr=lr)
-        elif self.accum > 1:
-            self.trainer.accumulate_micro_batch()
         self.step_times.append(time.time() - t0)
         return stats
 

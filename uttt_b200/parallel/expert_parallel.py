@@ -201,9 +201,10 @@ class _PeerDispatch(torch.autograd.Function):
         ext.ep_push(rows, weights, *_map_args(plan)[:3], plan.sizes32, plan.remote_start, ep.heap.peer_ptrs(slot),
                     ep.E, plan.rows_per_batch, plan.owner.rows_padded)
         ep.barrier()
-        # Outside autograd nothing keeps the rows beyond their immediate consumers, which are enqueued before this
-        # rank joins the ordering collective of the dispatch that reuses the slot: the slot itself can be returned.
-        out = slot.clone() if any(ctx.needs_input_grad[:2]) else slot
+        # The staging slot is reused by the dispatch after next, and callers issue several dispatches in a row
+        # before consuming any of them (the write path sends keys, values and learning rates back to back), so the
+        # rows always leave the slot, with or without autograd.
+        out = slot.clone()
         ctx.ep, ctx.plan = ep, plan
         ctx.save_for_backward(rows, weights)
         return out

@@ -35,6 +35,10 @@ import torch.distributed as dist
 _STEP_RE = re.compile(r"^step-(\d+)$")
 
 
+class MissingRankState(KeyError):
+    """The checkpoint is readable but has no entry for this rank (not a corrupt file: never fall back silently)."""
+
+
 @dataclass
 class TrainState:
     """Counters and loss histories that survive a restart (components/checkpoint.py:16-59)."""
@@ -141,6 +145,16 @@ class CheckpointManager:
                 for name, st in opt_sd["state"].items():
                     if name in model_sd and model_sd[name].is_floating_point():
                         model_sd[name] = st["master"].to(self.export_dtype).view(model_sd[name].shape)
+        # every rank's data position goes into the checkpoint (collective; rank 0 writes all of them)
+        loader_blobs: Optional[List[bytes]] = None
+        if dataloader is not None and self.save_backend == "dcp":
+            blob = io.BytesIO()
+            torch.save(dataloader.state_dict(), blob)
+            loader_blobs = [blob.getvalue()]
+            if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+                gathered: List[Any] = [None] * dist.get_world_size()
+                dist.all_gather_object(gathered, loader_blobs[0])
+                loader_blobs = gathered
         final = self.path(step)
         if _rank() == 0:
             tmp = final + ".tmp"
@@ -162,11 +176,9 @@ class CheckpointManager:
                     if lr_scheduler is not None:
                         states["lr_scheduler"] = {k: torch.tensor(v) if isinstance(v, (int, float)) else v
                                                   for k, v in lr_scheduler.state_dict().items()}
-                    if dataloader is not None:
-                        blob = io.BytesIO()
-                        torch.save(dataloader.state_dict(), blob)
-                        states["dataloader"] = {f"rank_{_rank()}": torch.frombuffer(
-                            bytearray(blob.getvalue()), dtype=torch.uint8).clone()}
+                    if loader_blobs is not None:
+                        states["dataloader"] = {f"rank_{r}": torch.frombuffer(bytearray(b), dtype=torch.uint8).clone()
+                                                for r, b in enumerate(loader_blobs)}
                     if train_state is not None:
                         states["train_state"] = train_state.state_dict()
                     flat: Dict[str, Any] = {}
@@ -223,7 +235,7 @@ class CheckpointManager:
             try:
                 loaded = self._load_path(path, model, trainer, lr_scheduler, dataloader, train_state)
                 return loaded
-            except FileNotFoundError:
+            except (FileNotFoundError, MissingRankState):
                 raise
             except Exception as exc:  # corrupt newest -> fall back to the previous one
                 last_err = exc
@@ -259,9 +271,13 @@ class CheckpointManager:
                                           for k, v in states["lr_scheduler"].items()})
         if dataloader is not None and "dataloader" in states and "dataloader" not in self.exclude_from_loading:
             key = f"rank_{_rank()}"
-            if key in states["dataloader"]:
-                dataloader.load_state_dict(torch.load(io.BytesIO(states["dataloader"][key].numpy().tobytes()),
-                                                      weights_only=False))
+            if key not in states["dataloader"]:
+                # resuming on more ranks than the checkpoint was written with: replaying data silently is worse
+                # than stopping (exclude "dataloader" from loading to start the data over on purpose)
+                raise MissingRankState(f"checkpoint {path} holds no data position for {key} "
+                               f"(it has {sorted(states['dataloader'])})")
+            dataloader.load_state_dict(torch.load(io.BytesIO(states["dataloader"][key].numpy().tobytes()),
+                                                  weights_only=False))
         step = 0
         if train_state is not None and "train_state" in states:
             train_state.load_state_dict(states["train_state"])
