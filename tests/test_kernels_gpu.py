@@ -423,6 +423,203 @@ def test_gg_tn(m, n):
     _close(acc, 0.25 + 2 * want, 0.3, 2e-2)
 
 
+def _rel_fro(a, b):
+    a, b = a.float(), b.float()
+    return float((a - b).norm() / b.norm().clamp_min(1e-12))
+
+
+@pytest.mark.parametrize("k,inter", [(128, 128), (384, 1536), (64, 256)])
+def test_gg_swiglu_fused_epilogue(k, inter):
+    """SwiGLU applied in the grouped GEMM's epilogue = silu(x W0^T) * (x W2^T) in fp32, forward and gradients."""
+    _ext()
+    torch.manual_seed(14)
+    plan = _plan(seed=k + inter)
+    g = plan.num_groups
+    real = torch.zeros(plan.rows_padded, 1, device=DEV)
+    real[plan.dest.reshape(-1)] = 1
+    used = (plan.tile_group >= 0).repeat_interleave(128)
+    x = (torch.randn(plan.rows_padded, k, device=DEV) * real).bfloat16().requires_grad_(True)
+    w = (torch.randn(g, 2 * inter, k, device=DEV) / math.sqrt(k)).bfloat16().requires_grad_(True)
+    hid = ops.gg_swiglu(x, w, plan)
+    assert hid.shape == (plan.rows_padded, inter)
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    y = ref.gg_nt(xr, wr, plan.tile_group)
+    want = F.silu(y[:, :inter]) * y[:, inter:]
+    torch.cuda.synchronize()
+    _status_ok()
+    _close(hid[used], want[used], 3e-2, 3e-2, "hidden")
+    assert _rel_fro(hid[used], want[used]) < 1e-2
+    assert float(hid[~used].abs().max() if (~used).any() else 0) == 0.0
+    c = torch.randn_like(hid) * real.bfloat16()
+    gx, gw = torch.autograd.grad(hid, [x, w], c)
+    gxr, gwr = torch.autograd.grad(want, [xr, wr], c.float())
+    torch.cuda.synchronize()
+    _status_ok()
+    _close(gx[used], gxr[used], 8e-2, 3e-2, "dx")
+    assert _rel_fro(gx[used], gxr[used]) < 1.5e-2
+    _close(gw, gwr, 0.5, 3e-2, "dw")
+    assert _rel_fro(gw, gwr) < 1.5e-2
+
+
+@pytest.mark.parametrize("with_lr,want_y", [(True, False), (True, True), (False, False)])
+def test_gg_swiglu_write_epilogue(with_lr, want_y):
+    """The write's point-wise block in the GEMM epilogue: dy02 * lr, hidden * lr1 and (optionally) y02."""
+    ext = _ext()
+    torch.manual_seed(15)
+    k, inter = 128, 256
+    plan = _plan(seed=77)
+    g = plan.num_groups
+    real = torch.zeros(plan.rows_padded, 1, device=DEV)
+    real[plan.dest.reshape(-1)] = 1
+    used = (plan.tile_group >= 0).repeat_interleave(128)
+    x = (torch.randn(plan.rows_padded, k, device=DEV) * real).bfloat16()
+    w = (torch.randn(g, 2 * inter, k, device=DEV) / math.sqrt(k)).bfloat16()
+    dh = (torch.randn(plan.rows_padded, inter, device=DEV) * real).bfloat16()
+    lr = (torch.rand(plan.rows_padded, 3, device=DEV) + 0.5) if with_lr else None
+    dy02, hlr, y02 = ext.gg_nt_swiglu_bwd(x, w, dh, lr, plan.tile_group, True, want_y)
+    torch.cuda.synchronize()
+    _status_ok()
+    y = ref.gg_nt(x.float(), w.float(), plan.tile_group)
+    y0, y2, d = y[:, :inter], y[:, inter:], dh.float()
+    sg = torch.sigmoid(y0)
+    l = lr if with_lr else torch.ones(plan.rows_padded, 3, device=DEV)
+    want_g = d * y2 * (sg * (1 + y0 * (1 - sg))) * l[:, 0:1]
+    want_u = d * F.silu(y0) * l[:, 2:3]
+    want_h = F.silu(y0) * y2 * l[:, 1:2]
+    for name, got, want in (("dy0", dy02[:, :inter], want_g), ("dy2", dy02[:, inter:], want_u), ("hlr", hlr, want_h)):
+        _close(got[used], want[used], 4e-2, 3e-2, name)
+        assert _rel_fro(got[used], want[used]) < 1e-2, name
+        assert float(got[~used].abs().max() if (~used).any() else 0) == 0.0
+    if want_y:
+        _close(y02[used], y[used], 3e-2, 2e-2, "y02")
+    # same numbers as the unfused sequence within bf16 rounding of the intermediate
+    y02_ref = ops.gg_nt(x, w, plan)
+    a, b_ = ext.fw_write_pw_fwd(y02_ref, dh, l.contiguous())
+    assert _rel_fro(dy02[used], a[used]) < 1.5e-2 and _rel_fro(hlr[used], b_[used]) < 1.5e-2
+
+
+def test_fw_write_grad_uses_fused_epilogue_and_matches_reference():
+    """Inner gradient of the write and its gradient-of-gradient through the fused kernels vs fp32 autograd."""
+    _ext()
+    torch.manual_seed(16)
+    k, inter = 128, 128
+    plan = _plan(bsz=2, n=300, e=4, k=2, seed=5)
+    g = plan.num_groups
+    real = torch.zeros(plan.rows_padded, 1, device=DEV)
+    real[plan.dest.reshape(-1)] = 1
+    kp = (torch.randn(plan.rows_padded, k, device=DEV) * real).bfloat16().requires_grad_(True)
+    vp = (torch.randn(plan.rows_padded, k, device=DEV) * real).bfloat16().requires_grad_(True)
+    lrp = ((torch.rand(plan.rows_padded, 3, device=DEV) * 0.5 + 0.5) * real).requires_grad_(True)
+    w02 = (torch.randn(g, 2 * inter, k, device=DEV) / math.sqrt(k)).bfloat16().requires_grad_(True)
+    w1 = (torch.randn(g, k, inter, device=DEV) / math.sqrt(inter)).bfloat16().requires_grad_(True)
+    g02, g1 = ops.fw_write_grad(kp, vp, lrp, w02, w1, plan)
+    c02, c1 = torch.randn_like(g02) * 0.1, torch.randn_like(g1) * 0.1
+    grads = torch.autograd.grad([g02, g1], [kp, vp, lrp, w02, w1], [c02, c1])
+    f = [t.detach().float().requires_grad_(True) for t in (kp, vp, lrp, w02, w1)]
+    y = ref.gg_nt(f[0], f[3], plan.tile_group)
+    dhr = ref.gg_nn(f[1], f[4], plan.tile_group)
+    a, b_ = ref.fw_write_pointwise(y, dhr, f[2])
+    g02r = ref.gg_tn(a, f[0], plan.tile_group, g)
+    g1r = ref.gg_tn(f[1], b_, plan.tile_group, g)
+    gradsr = torch.autograd.grad([g02r, g1r], f, [c02.float(), c1.float()])
+    torch.cuda.synchronize()
+    _status_ok()
+    assert _rel_fro(g02, g02r) < 1.5e-2 and _rel_fro(g1, g1r) < 1.5e-2
+    for name, got, want in zip(("d_kp", "d_vp", "d_lr", "d_w02", "d_w1"), grads, gradsr):
+        assert _rel_fro(got, want) < 3e-2, (name, _rel_fro(got, want))
+
+
+def _pair_plan_reference(tile_group, offsets, tiles):
+    out = []
+    tg = tile_group.tolist()
+    off = offsets.tolist()
+    for t in range(tiles):
+        g = tg[t]
+        if g < 0:
+            out.append((-t - 2, -1))
+        elif (t - off[g] // 128) % 2 == 0:
+            out.append((t, t + 1 if t + 1 < tiles and tg[t + 1] == g else -1))
+    return out
+
+
+@pytest.mark.parametrize("bsz,n,e,k", [(2, 700, 4, 2), (3, 5000, 32, 2), (1, 3, 5, 2), (4, 129, 2, 2), (2, 2048, 96, 1)])
+def test_pair_plan(bsz, n, e, k):
+    ext = _ext()
+    plan = _plan(bsz, n, e, k, seed=n)
+    tiles = plan.rows_padded // 128
+    entries, count = ext.pair_plan(plan.tile_group, plan.offsets, tiles)
+    want = _pair_plan_reference(plan.tile_group.cpu(), plan.offsets.cpu(), tiles)
+    assert int(count[0]) == len(want)
+    assert entries[:len(want)].cpu().tolist() == [list(w) for w in want]
+
+
+@pytest.fixture
+def one_cta_then_pairs():
+    """Yields a function that runs ``f`` with the one-CTA kernels and then with CTA pairs."""
+    def run(f):
+        try:
+            fn.set_cta_pairs(False)
+            a = f()
+            fn.set_cta_pairs(True)
+            b_ = f()
+        finally:
+            fn.set_cta_pairs(True)
+        return a, b_
+    return run
+
+
+@pytest.mark.parametrize("mode,k,n", [("nt", 384, 3072), ("nt", 1536, 384), ("nt", 64, 128), ("nt", 128, 256),
+                                      ("nn", 384, 1536), ("nn", 3072, 384), ("nn", 64, 128), ("nn", 128, 640)])
+def test_gg_pair_kernels(mode, k, n, one_cta_then_pairs):
+    """Two-CTA (cta_group::2) NT / NN products: equal to the one-CTA kernels and to fp32, unused tiles zero."""
+    _ext()
+    torch.manual_seed(21)
+    # 3 experts x 2 sequences with ~230 routed rows each: groups of one and two tiles, odd and even counts
+    plan = _plan(bsz=2, n=350, e=3, k=2, seed=k + n)
+    g = plan.num_groups
+    x = torch.randn(plan.rows_padded, k, device=DEV, dtype=torch.bfloat16)
+    shape = (g, n, k) if mode == "nt" else (g, k, n)
+    w = (torch.randn(*shape, device=DEV) / math.sqrt(k)).bfloat16()
+    op = ops.gg_nt if mode == "nt" else ops.gg_nn
+    one, two = one_cta_then_pairs(lambda: op(x, w, plan))
+    torch.cuda.synchronize()
+    _status_ok()
+    want = (ref.gg_nt if mode == "nt" else ref.gg_nn)(x.float(), w.float(), plan.tile_group)
+    used = (plan.tile_group >= 0).repeat_interleave(128)
+    _close(two[used], want[used], 3e-2, 3e-2, "pairs vs fp32")
+    assert _rel_fro(two[used], want[used]) < 1e-2
+    _close(two[used], one[used], 1e-2, 1e-2, "pairs vs one CTA")
+    assert float(two[~used].abs().max() if (~used).any() else 0) == 0.0
+
+
+def test_gg_pair_fused_epilogues(one_cta_then_pairs):
+    ext = _ext()
+    torch.manual_seed(22)
+    k, inter = 384, 256
+    plan = _plan(bsz=2, n=350, e=3, k=2, seed=9)
+    g = plan.num_groups
+    real = torch.zeros(plan.rows_padded, 1, device=DEV)
+    real[plan.dest.reshape(-1)] = 1
+    used = (plan.tile_group >= 0).repeat_interleave(128)
+    x = (torch.randn(plan.rows_padded, k, device=DEV) * real).bfloat16()
+    w = (torch.randn(g, 2 * inter, k, device=DEV) / math.sqrt(k)).bfloat16()
+    dh = (torch.randn(plan.rows_padded, inter, device=DEV) * real).bfloat16()
+    lr = torch.rand(plan.rows_padded, 3, device=DEV) + 0.5
+    one, two = one_cta_then_pairs(lambda: ops.gg_swiglu(x, w, plan))
+    y = ref.gg_nt(x.float(), w.float(), plan.tile_group)
+    want = F.silu(y[:, :inter]) * y[:, inter:]
+    torch.cuda.synchronize()
+    _status_ok()
+    assert _rel_fro(two[used], want[used]) < 1e-2 and _rel_fro(two[used], one[used]) < 1e-3
+    assert float(two[~used].abs().max() if (~used).any() else 0) == 0.0
+    one, two = one_cta_then_pairs(lambda: fn._swiglu_bwd_kernel(x, w, dh, lr, plan, True, True))
+    torch.cuda.synchronize()
+    _status_ok()
+    for a, b_ in zip(one, two):
+        assert _rel_fro(b_[used], a[used]) < 1e-3
+        assert float(b_[~used].abs().max() if (~used).any() else 0) == 0.0
+
+
 def test_gg_autograd_matches_reference():
     _ext()
     torch.manual_seed(7)

@@ -105,8 +105,7 @@ def pool_read(q_rows: torch.Tensor, state_w02: torch.Tensor, state_w1: torch.Ten
         w02 = state_w02.reshape(g, state_w02.shape[2], d)
         w1 = state_w1.reshape(g, d, state_w1.shape[3])
         xp = ep.dispatch(q_rows.reshape(bsz * n, d).to(w02.dtype), None, eplan)
-        y02 = ops.gg_nt(xp, w02, plan)
-        hid = ops.swiglu(y02)
+        hid = ops.gg_swiglu(xp, w02, plan)
         yp = ops.gg_nt(hid, w1, plan)
         return ep.combine(yp, routing.weights, eplan).view(bsz, n, d)
     plan = routing.plan
@@ -114,8 +113,7 @@ def pool_read(q_rows: torch.Tensor, state_w02: torch.Tensor, state_w1: torch.Ten
     w02 = state_w02.reshape(g, state_w02.shape[2], d)
     w1 = state_w1.reshape(g, d, state_w1.shape[3])
     xp = ops.permute_rows(q_rows.reshape(bsz * n, d).to(w02.dtype), plan)
-    y02 = ops.gg_nt(xp, w02, plan)
-    hid = ops.swiglu(y02)
+    hid = ops.gg_swiglu(xp, w02, plan)
     yp = ops.gg_nt(hid, w1, plan)
     y = ops.unpermute_rows(yp, plan, routing.weights)
     return y.view(bsz, n, d)

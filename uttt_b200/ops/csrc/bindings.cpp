@@ -38,6 +38,17 @@ at::Tensor plucker_embed(at::Tensor image, at::Tensor fxfycxcy, at::Tensor c2w, 
 
 at::Tensor gg_nt(at::Tensor x, at::Tensor w, at::Tensor tile_group);
 at::Tensor gg_nn(at::Tensor x, at::Tensor w, at::Tensor tile_group);
+at::Tensor gg_nt_swiglu(at::Tensor x, at::Tensor w02, at::Tensor tile_group);
+std::vector<at::Tensor> gg_nt_swiglu_bwd(at::Tensor x, at::Tensor w02, at::Tensor dh, c10::optional<at::Tensor> lr,
+                                         at::Tensor tile_group, bool want_h, bool want_y);
+std::vector<at::Tensor> pair_plan(at::Tensor tile_group, at::Tensor offsets, int64_t tiles);
+at::Tensor gg_nt_pair(at::Tensor x, at::Tensor w, at::Tensor tile_group, at::Tensor entries, at::Tensor count);
+at::Tensor gg_nn_pair(at::Tensor x, at::Tensor w, at::Tensor tile_group, at::Tensor entries, at::Tensor count);
+at::Tensor gg_nt_swiglu_pair(at::Tensor x, at::Tensor w02, at::Tensor tile_group, at::Tensor entries,
+                             at::Tensor count);
+std::vector<at::Tensor> gg_nt_swiglu_bwd_pair(at::Tensor x, at::Tensor w02, at::Tensor dh, c10::optional<at::Tensor> lr,
+                                              at::Tensor tile_group, at::Tensor entries, at::Tensor count, bool want_h,
+                                              bool want_y);
 at::Tensor gg_tn_segments(at::Tensor a, at::Tensor b, at::Tensor offsets, int64_t num_groups, int64_t segments,
                           at::ScalarType out_dtype, c10::optional<at::Tensor> accumulate_into);
 at::Tensor bmm_nt(at::Tensor a, at::Tensor b, double alpha, c10::optional<at::Tensor> d, double beta);
@@ -112,6 +123,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("plucker_embed", &plucker_embed);
   m.def("gg_nt", &gg_nt);
   m.def("gg_nn", &gg_nn);
+  m.def("gg_nt_swiglu", &gg_nt_swiglu);
+  m.def("gg_nt_swiglu_bwd", &gg_nt_swiglu_bwd);
+  m.def("pair_plan", &pair_plan);
+  m.def("gg_nt_pair", &gg_nt_pair);
+  m.def("gg_nn_pair", &gg_nn_pair);
+  m.def("gg_nt_swiglu_pair", &gg_nt_swiglu_pair);
+  m.def("gg_nt_swiglu_bwd_pair", &gg_nt_swiglu_bwd_pair);
   m.def("gg_tn_segments", &gg_tn_segments);
   m.def("bmm_nt", &bmm_nt);
   m.def("gemm_status", &gemm_status);

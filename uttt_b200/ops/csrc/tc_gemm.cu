@@ -10,11 +10,9 @@
 // and is zero padded), so a 128-row tile belongs to exactly one group (`tile_group[t]`, -1 = unused)
 // and token reductions need no masking.
 //
-// One CTA computes one 128 x BN output tile:
-//   warp 0 / one lane : TMA producer  (cp.async.bulk.tensor into a STAGES-deep 128B-swizzled ring)
-//   warp 1 / one lane : MMA issuer    (tcgen05.mma, accumulator in TMEM, tcgen05.commit frees stages)
-//   warps 0-3         : epilogue      (tcgen05.ld -> registers -> global)
-// Two CTAs fit per SM, so one CTA's epilogue overlaps the other's main loop.
+// One persistent CTA per SM walks the 128 x BN output tiles (see tc_gemm_persistent_kernel); the NT product against
+// the stacked gate|up weights can apply the SwiGLU, or the SwiGLU derivative with per-row learning rates, in its
+// epilogue (GemmEpilogue).  The two-CTA (cta_group::2) variant of the NT / NN modes lives in tc_gemm_pair.cu.
 #include <ATen/ATen.h>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
@@ -28,268 +26,23 @@
 #include <type_traits>
 
 #include "ptx.cuh"
+#include "tc_gemm.cuh"
 
 namespace uttt {
 
-enum GemmMode { kNT = 0, kNN = 1, kTN = 2, kBMM = 3, kBNN = 4, kBTN = 5 };
-__host__ __device__ constexpr bool is_batched(int m) { return m == kBMM || m == kBNN || m == kBTN; }
-
-struct GemmParams {
-  const int* tile_group;    // NT/NN: [tiles]
-  const int* seg_offsets;   // TN: [segments, G + 1] padded row offsets of every group in every segment
-  int segments;             // TN: number of stacked row buffers reduced together
-  int rows_per_segment;     // TN: row stride between stacked buffers
-  int groups;
-  int M, N, K;              // per-group problem dims (NT/NN: M unused)
-  void* out;
-  long long out_rows;       // rows of the output seen as one [out_rows, N] matrix (all groups / batches stacked)
-  const void* addend;       // BMM: D (bf16) or nullptr
-  float alpha, beta;
-  int accumulate;           // TN: out += result (fp32 output only)
-  int* status;              // error word (0 = ok)
-};
-
-constexpr int BM = 128;
-constexpr int BK = 64;      // bf16 elements per k block = one 128-byte swizzle row
-
-template <int BN, int STAGES>
-struct SmemLayout {
-  static constexpr int kABytes = BM * BK * 2;
-  static constexpr int kBBytes = BN * BK * 2;
-  static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kBarOffset = STAGES * kStageBytes;
-  static constexpr int kTotal = kBarOffset + (2 * STAGES + 1) * 8 + 16 + 1024;  // + alignment slack
-};
-
-template <int MODE, int BN, int STAGES, typename OutT>
-__global__ void __launch_bounds__(128) tc_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
-                                                      const __grid_constant__ CUtensorMap tma_b, GemmParams p) {
-  using L = SmemLayout<BN, STAGES>;
-  extern __shared__ uint8_t smem_raw[];
-  // 128B-swizzled tiles need 1024-byte alignment
-  uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
-  const uint32_t bar_base = smem_base + L::kBarOffset;
-  auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
-  const uint32_t accum_bar = bar_base + 8u * (2 * STAGES);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + L::kBarOffset + (2 * STAGES + 1) * 8);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-  // ---- tile coordinates ---------------------------------------------------------------
-  int g = 0, a_row0 = 0, m0 = 0, n0 = 0;
-  size_t out_row0 = 0;
-  if (MODE == kNT || MODE == kNN) {
-    n0 = blockIdx.x * BN;
-    int t = blockIdx.y;
-    g = p.tile_group[t];
-    a_row0 = t * BM;
-    out_row0 = (size_t)t * BM;
-  } else if (MODE == kTN) {
-    m0 = blockIdx.x * BM;
-    n0 = blockIdx.y * BN;
-    g = blockIdx.z;
-    out_row0 = (size_t)g * p.M + m0;
-  } else {
-    n0 = blockIdx.x * BN;
-    m0 = blockIdx.y * BM;
-    g = blockIdx.z;
-    a_row0 = g * p.M + m0;
-    out_row0 = (size_t)g * p.M + m0;
-  }
-  OutT* out = reinterpret_cast<OutT*>(p.out);
-  const int ldo = p.N;
-
-  if ((MODE == kNT || MODE == kNN) && g < 0) {
-    // unused tile of the padded layout: define its rows as zero
-    OutT* o = out + (out_row0 + threadIdx.x) * ldo + n0;
-    for (int c = 0; c < BN; c += 16 / (int)sizeof(OutT)) *reinterpret_cast<uint4*>(o + c) = make_uint4(0, 0, 0, 0);
-    return;
-  }
-  {
-    // bail out (uniformly) when an earlier CTA of this process reported a failed wait
-    __shared__ int prior_failure;
-    if (threadIdx.x == 0) prior_failure = (p.status != nullptr) ? *(volatile int*)p.status : 0;
-    __syncthreads();
-    if (prior_failure != 0) return;
-  }
-
-  // number of 64-wide k blocks
-  int nkb = 0;
-  if (MODE == kTN) {
-    for (int s = 0; s < p.segments; ++s) {
-      const int* off = p.seg_offsets + (size_t)s * (p.groups + 1);
-      nkb += (off[g + 1] - off[g]) / BK;
-    }
-  } else {
-    nkb = p.K / BK;
-  }
-
-  // ---- setup: barriers, TMEM ----------------------------------------------------------
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      ptx::mbar_init(full_bar(s), 1);
-      ptx::mbar_init(empty_bar(s), 1);
-    }
-    ptx::mbar_init(accum_bar, 1);
-    ptx::mbar_fence_init();
-    ptx::tma_prefetch_desc(&tma_a);
-    ptx::tma_prefetch_desc(&tma_b);
-  }
-  if (warp == 0) {
-    ptx::tmem_alloc(ptx::smem_u32(tmem_slot), BN);
-    ptx::tmem_relinquish();
-  }
-  ptx::tc_fence_before_sync();
-  __syncthreads();
-  ptx::tc_fence_after_sync();
-  const uint32_t tmem_acc = *tmem_slot;
-  bool ok = true;
-
-  if (nkb > 0) {
-    if (warp == 0 && lane == 0) {
-      // ================= TMA producer =================
-      int seg = 0, seg_row = 0, seg_end = 0;
-      if (MODE == kTN) {
-        const int* off = p.seg_offsets;
-        seg_row = off[g];
-        seg_end = off[g + 1];
-      }
-      for (int kb = 0; kb < nkb && ok; ++kb) {
-        int s = kb % STAGES;
-        if (kb >= STAGES) ok = ptx::mbar_wait(empty_bar(s), ((kb / STAGES) - 1) & 1, p.status, 1);
-        if (!ok) break;
-        uint32_t sa = smem_base + s * L::kStageBytes;
-        uint32_t sb = sa + L::kABytes;
-        ptx::mbar_expect_tx(full_bar(s), L::kStageBytes);
-        if (MODE == kNT || MODE == kBMM) {
-          ptx::tma_load_2d(sa, &tma_a, full_bar(s), kb * BK, a_row0);
-          int brow = (MODE == kNT ? g * p.N : g * p.N) + n0;
-          ptx::tma_load_2d(sb, &tma_b, full_bar(s), kb * BK, brow);
-        } else if (MODE == kNN) {
-          ptx::tma_load_2d(sa, &tma_a, full_bar(s), kb * BK, a_row0);
-#pragma unroll
-          for (int j = 0; j < BN / 64; ++j)
-            ptx::tma_load_2d(sb + j * (BK * 128), &tma_b, full_bar(s), n0 + 64 * j, g * p.K + kb * BK);
-        } else {
-          while (seg_row >= seg_end) {   // advance to the next stacked buffer that has rows for this group
-            ++seg;
-            const int* off = p.seg_offsets + (size_t)seg * (p.groups + 1);
-            seg_row = off[g];
-            seg_end = off[g + 1];
-          }
-          int row = seg * p.rows_per_segment + seg_row;
-#pragma unroll
-          for (int j = 0; j < BM / 64; ++j)
-            ptx::tma_load_2d(sa + j * (BK * 128), &tma_a, full_bar(s), m0 + 64 * j, row);
-#pragma unroll
-          for (int j = 0; j < BN / 64; ++j)
-            ptx::tma_load_2d(sb + j * (BK * 128), &tma_b, full_bar(s), n0 + 64 * j, row);
-          seg_row += BK;
-        }
-      }
-    } else if (warp == 1 && lane == 0) {
-      // ================= MMA issuer =================
-      constexpr int a_mn = (MODE == kTN) ? 1 : 0;
-      constexpr int b_mn = (MODE == kNN || MODE == kTN) ? 1 : 0;
-      constexpr uint32_t idesc = ptx::make_instr_desc(BM, BN, a_mn, b_mn);
-      for (int kb = 0; kb < nkb && ok; ++kb) {
-        int s = kb % STAGES;
-        ok = ptx::mbar_wait(full_bar(s), (kb / STAGES) & 1, p.status, 2);
-        if (!ok) break;
-        ptx::tc_fence_after_sync();
-        uint32_t sa = smem_base + s * L::kStageBytes;
-        uint32_t sb = sa + L::kABytes;
-#pragma unroll
-        for (int k = 0; k < BK / 16; ++k) {
-          // K-major: advance 16 elements = 32 B inside the swizzle row; MN-major: advance 16 k rows = 2048 B
-          uint64_t da = a_mn ? ptx::make_smem_desc(sa + k * 2048, BK * 128, 1024)
-                             : ptx::make_smem_desc(sa + k * 32, 16, 1024);
-          uint64_t db = b_mn ? ptx::make_smem_desc(sb + k * 2048, BK * 128, 1024)
-                             : ptx::make_smem_desc(sb + k * 32, 16, 1024);
-          ptx::mma_bf16_ss(tmem_acc, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-        }
-        ptx::mma_commit(empty_bar(s));   // stage reusable once these MMAs have read it
-      }
-      if (ok) ptx::mma_commit(accum_bar);
-    }
-    __syncwarp();
-    // ================= epilogue =================
-    if (!ptx::mbar_wait(accum_bar, 0, p.status, 3)) ok = false;
-    ptx::tc_fence_after_sync();
-  }
-  // a failed wait anywhere in the CTA is visible through the status word
-  if (p.status != nullptr && *(volatile int*)p.status != 0) ok = false;
-
-  if (ok) {
-    const int r = warp * 32 + lane;   // TMEM lane == output row inside the tile
-    OutT* orow = out + (out_row0 + r) * ldo + n0;
-    const __nv_bfloat16* drow =
-        (MODE == kBMM && p.addend != nullptr)
-            ? reinterpret_cast<const __nv_bfloat16*>(p.addend) + (out_row0 + r) * ldo + n0 : nullptr;
-#pragma unroll 1
-    for (int c0 = 0; c0 < BN; c0 += 32) {
-      float v[32];
-      if (nkb > 0) {
-        uint32_t raw[32];
-        ptx::tmem_ld_32x32(tmem_acc + ((uint32_t)(warp * 32) << 16) + c0, raw);
-        ptx::tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]);
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = 0.f;
-      }
-      if (MODE == kBMM) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] *= p.alpha;
-        if (drow != nullptr) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            float d[8];
-            Vec8<__nv_bfloat16>::load(drow + c0 + i, d);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[i + j] += p.beta * d[j];
-          }
-        }
-      }
-      if (MODE == kTN && p.accumulate) {
-#pragma unroll
-        for (int i = 0; i < 32; i += 8) {
-          float d[8];
-          Vec8<OutT>::load(orow + c0 + i, d);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) v[i + j] += d[j];
-        }
-      }
-#pragma unroll
-      for (int i = 0; i < 32; i += 8) {
-        float o[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = v[i + j];
-        Vec8<OutT>::store(orow + c0 + i, o);
-      }
-    }
-  }
-  ptx::tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 0) ptx::tmem_dealloc(tmem_acc, BN);
-}
-
-// ------------------------------------------------------------------------------------ persistent variant
+// ------------------------------------------------------------------------------------ persistent kernel
 // One CTA per SM walks the output tiles (tile = blockIdx.x, += gridDim.x).  Six warps:
 //   warps 0-3 : epilogue   (TMEM -> registers -> global), one TMEM lane quarter each
 //   warp 4    : TMA producer (one lane), ring of STAGES shared-memory stages shared by all tiles
 //   warp 5    : MMA issuer   (one lane), two TMEM accumulator buffers so that tile i+1's main loop runs
 //               while tile i's epilogue drains
-template <int BN, int STAGES>
+template <int BN, int STAGES, int OUT_BYTES = 4 * 2 * 4096>
 struct PersistentSmem {
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kOutOffset = STAGES * kStageBytes;          // epilogue staging: 4 warps x 2 x (32 rows x 128 B)
-  static constexpr int kOutBytes = 4 * 2 * 4096;
+  static constexpr int kOutBytes = OUT_BYTES;                      // (fused epilogues: 8 warps x their slabs)
   static constexpr int kBarOffset = kOutOffset + kOutBytes;
   static constexpr int kTotal = kBarOffset + (2 * STAGES + 4) * 8 + 16 + 1024;
   static constexpr int kAccStride = (BN == 192) ? 256 : BN;        // TMEM columns between the two accumulators
@@ -336,13 +89,20 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int id, in
   return c;
 }
 
-template <int MODE, int BN, int STAGES, typename OutT>
-__global__ void __launch_bounds__(192) tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tma_a,
+template <int MODE, int BN, int STAGES, typename OutT, int EPI = kEpiNone>
+__global__ void __launch_bounds__((EPI != kEpiNone ? kFusedWarps : 4) * 32 + 64) tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tma_a,
                                                                  const __grid_constant__ CUtensorMap tma_b,
                                                                  const __grid_constant__ CUtensorMap tma_out,
+                                                                 const __grid_constant__ CUtensorMap tma_out_h,
+                                                                 const __grid_constant__ CUtensorMap tma_out_y,
                                                                  GemmParams p, int total_tiles, int tiles_n,
                                                                  int tiles_m) {
-  using L = PersistentSmem<BN, STAGES>;
+  static_assert(EPI == kEpiNone || (MODE == kNT && BN == 256 && sizeof(OutT) == 2),
+                "fused SwiGLU epilogues run on 256-wide NT tiles (128 gate + 128 up columns) with bf16 output");
+  constexpr int TW = (EPI != kEpiNone) ? 128 : BN;      // output columns that a tile index advances by
+  // warps [0, EW): epilogue; warp EW: TMA producer (and owner of the tensor-memory allocation); warp EW + 1: MMA issuer
+  constexpr int EW = (EPI != kEpiNone) ? kFusedWarps : 4;
+  using L = PersistentSmem<BN, STAGES, (EPI != kEpiNone) ? kFusedWarps * fused_warp_smem(EPI) : 4 * 2 * 4096>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
@@ -367,15 +127,19 @@ __global__ void __launch_bounds__(192) tc_gemm_persistent_kernel(const __grid_co
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(acc_full(b), 1);
-      ptx::mbar_init(acc_empty(b), 128);
+      ptx::mbar_init(acc_empty(b), EW * 32);
     }
     ptx::mbar_fence_init();
     ptx::tma_prefetch_desc(&tma_a);
     ptx::tma_prefetch_desc(&tma_b);
     ptx::tma_prefetch_desc(&tma_out);
+    if (EPI == kEpiWrite) {
+      if (p.out_h != nullptr) ptx::tma_prefetch_desc(&tma_out_h);
+      if (p.out_y != nullptr) ptx::tma_prefetch_desc(&tma_out_y);
+    }
   }
   constexpr uint32_t kTmemCols = L::kTmemCols;
-  if (warp == 4) {
+  if (warp == EW) {
     ptx::tmem_alloc(ptx::smem_u32(tmem_slot), kTmemCols);
     ptx::tmem_relinquish();
   }
@@ -386,13 +150,13 @@ __global__ void __launch_bounds__(192) tc_gemm_persistent_kernel(const __grid_co
   OutT* out = reinterpret_cast<OutT*>(p.out);
   const int ldo = p.N;
 
-  if (warp == 4) {
+  if (warp == EW) {
     if (lane == 0) {
       // ================= TMA producer =================
       uint32_t it = 0;
       bool ok = true;
       for (int id = blockIdx.x; id < total_tiles && ok; id += gridDim.x) {
-        TileCoord c = decode_tile<MODE, BN>(p, id, tiles_n, tiles_m);
+        TileCoord c = decode_tile<MODE, TW>(p, id, tiles_n, tiles_m);
         if (c.unused || c.nkb == 0) continue;
         int seg = 0, seg_row = 0, seg_end = 0;
         if (MODE == kTN) {
@@ -406,7 +170,12 @@ __global__ void __launch_bounds__(192) tc_gemm_persistent_kernel(const __grid_co
           uint32_t sa = smem_base + s * L::kStageBytes;
           uint32_t sb = sa + L::kABytes;
           ptx::mbar_expect_tx(full_bar(s), L::kStageBytes);
-          if (MODE == kNT || MODE == kBMM) {
+          if (EPI != kEpiNone) {
+            // 128 gate rows and the 128 up rows of the same hidden columns: accumulator columns 0-127 | 128-255
+            ptx::tma_load_2d(sa, &tma_a, full_bar(s), kb * BK, c.a_row0);
+            ptx::tma_load_2d(sb, &tma_b, full_bar(s), kb * BK, c.g * p.N + c.n0);
+            ptx::tma_load_2d(sb + 128 * BK * 2, &tma_b, full_bar(s), kb * BK, c.g * p.N + p.inter + c.n0);
+          } else if (MODE == kNT || MODE == kBMM) {
             ptx::tma_load_2d(sa, &tma_a, full_bar(s), kb * BK, c.a_row0);
             ptx::tma_load_2d(sb, &tma_b, full_bar(s), kb * BK, c.g * p.N + c.n0);
           } else if (MODE == kBNN) {
@@ -445,7 +214,7 @@ __global__ void __launch_bounds__(192) tc_gemm_persistent_kernel(const __grid_co
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == EW + 1) {
     if (lane == 0) {
       // ================= MMA issuer =================
       constexpr int a_mn = (MODE == kTN || MODE == kBTN) ? 1 : 0;
@@ -454,7 +223,7 @@ __global__ void __launch_bounds__(192) tc_gemm_persistent_kernel(const __grid_co
       uint32_t it = 0, acc_it = 0;
       bool ok = true;
       for (int id = blockIdx.x; id < total_tiles && ok; id += gridDim.x) {
-        TileCoord c = decode_tile<MODE, BN>(p, id, tiles_n, tiles_m);
+        TileCoord c = decode_tile<MODE, TW>(p, id, tiles_n, tiles_m);
         if (c.unused || c.nkb == 0) continue;
         const int ab = acc_it & 1;
         ok = ptx::mbar_wait(acc_empty(ab), ((acc_it >> 1) & 1) ^ 1, p.status, 22);
@@ -495,7 +264,37 @@ __global__ void __launch_bounds__(192) tc_gemm_persistent_kernel(const __grid_co
     const uint32_t slab_base = smem_base + L::kOutOffset + warp * 8192;
     constexpr int SUBW = 128 / (int)sizeof(OutT);      // output columns per 128-byte staging row
     for (int id = blockIdx.x; id < total_tiles && ok; id += gridDim.x) {
-      TileCoord c = decode_tile<MODE, BN>(p, id, tiles_n, tiles_m);
+      TileCoord c = decode_tile<MODE, TW>(p, id, tiles_n, tiles_m);
+      if constexpr (EPI != kEpiNone) {
+        // ---- fused SwiGLU epilogues: accumulator columns [0, 128) = y0 (gate), [128, 256) = y2 (up) ----
+        const int quarter = warp & 3, half = warp >> 2;       // TMEM lane quarter; which 64 hidden columns
+        const size_t grow = c.out_row0 + quarter * 32 + lane;
+        if (c.unused || c.nkb == 0) {
+          zero_fused_tile<EPI>(p, grow, c.n0 + half * 64);
+          continue;
+        }
+        if (EPI == kEpiWrite && id + (int)gridDim.x < total_tiles) {
+          const TileCoord nx = decode_tile<MODE, TW>(p, id + gridDim.x, tiles_n, tiles_m);
+          if (!nx.unused) prefetch_dh_line(p, nx.out_row0 + quarter * 32 + lane, nx.n0, half);
+        }
+        const int ab = acc_it & 1;
+        const uint32_t tmem_acc = tmem_base + ab * L::kAccStride + ((uint32_t)(quarter * 32) << 16);
+        const uint32_t warp_smem = smem_base + L::kOutOffset + warp * fused_warp_smem(EPI);
+        ok = fused_swiglu_epilogue<EPI>(
+            p, &tma_out, tmem_acc, warp_smem, slab_it, grow, (int)c.out_row0 + quarter * 32, c.n0, half, lane,
+            [&]() {
+              bool got = ptx::mbar_wait(acc_full(ab), (acc_it >> 1) & 1, p.status, 24);
+              ptx::tc_fence_after_sync();
+              return got;
+            },
+            [&]() {
+              ptx::tc_fence_before_sync();
+              ptx::mbar_arrive(acc_empty(ab));
+            });
+        if (!ok) break;
+        ++acc_it;
+        continue;
+      }
       OutT* orow = out + (c.out_row0 + r) * ldo + c.n0;
       const bool has_acc = !c.unused && c.nkb > 0;
       if (!has_acc) {
@@ -594,7 +393,7 @@ __global__ void __launch_bounds__(192) tc_gemm_persistent_kernel(const __grid_co
   }
   ptx::tc_fence_before_sync();
   __syncthreads();
-  if (warp == 4) ptx::tmem_dealloc(tmem_base, kTmemCols);
+  if (warp == EW) ptx::tmem_dealloc(tmem_base, kTmemCols);
 }
 
 // ------------------------------------------------------------------------------------ host side
@@ -612,13 +411,11 @@ static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
 }
 
 // 2-D tensor map (128B swizzle) over a row-major [rows, cols] matrix; box = [box_rows, box_cols], cols innermost.
-static CUtensorMap make_tmap_2d(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t box_cols,
-                                bool fp32);
 CUtensorMap make_tmap_2d_bf16(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t box_cols) {
   return make_tmap_2d(base, rows, cols, box_rows, box_cols, false);
 }
-static CUtensorMap make_tmap_2d(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t box_cols,
-                                bool fp32) {
+CUtensorMap make_tmap_2d(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t box_cols,
+                         bool fp32, bool swizzle64) {
   CUtensorMap m;
   const uint64_t esz = fp32 ? 4 : 2;
   {
@@ -635,13 +432,14 @@ static CUtensorMap make_tmap_2d(const void* base, uint64_t rows, uint64_t cols, 
   TORCH_CHECK(((uintptr_t)base & 15) == 0 && (cols * esz) % 16 == 0, "TMA needs 16-byte aligned base and row pitch");
   CUresult r = get_encode_fn()(&m, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                                const_cast<void*>(base), dims, strides, box,
-                               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                               swizzle64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
                                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code ", (int)r);
   return m;
 }
 
-static at::Tensor& status_word(const at::Device& dev) {
+at::Tensor& status_word(const at::Device& dev) {
   static std::vector<at::Tensor> words(64);
   int idx = dev.index() < 0 ? 0 : dev.index();
   if (!words[idx].defined()) words[idx] = at::zeros({4}, at::TensorOptions().device(dev).dtype(at::kInt));
@@ -650,25 +448,27 @@ static at::Tensor& status_word(const at::Device& dev) {
 
 at::Tensor gemm_status(at::Tensor like) { return status_word(like.device()); }
 
-static bool use_persistent() {
-  static int mode = -1;
-  if (mode < 0) {
-    const char* e = std::getenv("UTTT_B200_GEMM");
-    mode = (e != nullptr && std::string(e) == "simple") ? 0 : 1;
-  }
-  return mode == 1;
-}
-
-template <int MODE, int BN, typename OutT>
+template <int MODE, int BN, typename OutT, int EPI = kEpiNone>
 static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, dim3 grid) {
   auto stream = at::cuda::getCurrentCUDAStream().stream();
-  if (use_persistent()) {
-    constexpr int STAGES = (BN >= 192) ? 4 : (BN >= 128 ? 6 : 8);
-    using L = PersistentSmem<BN, STAGES>;
+  {
+    // the write epilogue stages four slabs per warp (64 KB) and is bound by its epilogue: three stages suffice
+    constexpr int STAGES = (EPI == kEpiWrite) ? 3 : ((BN >= 192) ? 4 : (BN >= 128 ? 6 : 8));
+    using L = PersistentSmem<BN, STAGES, (EPI != kEpiNone) ? kFusedWarps * fused_warp_smem(EPI) : 4 * 2 * 4096>;
     TORCH_CHECK(p.out_rows > 0 && p.out_rows % 32 == 0, "output rows must be a multiple of 32");
     constexpr bool f32out = std::is_same<OutT, float>::value;
-    CUtensorMap tout = make_tmap_2d(p.out, (uint64_t)p.out_rows, (uint64_t)p.N, 32, f32out ? 32 : 64, f32out);
-    auto kernel = tc_gemm_persistent_kernel<MODE, BN, STAGES, OutT>;
+    CUtensorMap tout, tout_h, tout_y;
+    if (EPI == kEpiNone) {
+      tout = make_tmap_2d(p.out, (uint64_t)p.out_rows, (uint64_t)p.N, 32, f32out ? 32 : 64, f32out);
+      tout_h = tout_y = tout;
+    } else {
+      // fused epilogues store 32 x 32 bf16 boxes (64-byte rows, 64-byte swizzle) into one to three outputs
+      const uint64_t I = (uint64_t)p.inter, R = (uint64_t)p.out_rows;
+      tout = make_tmap_2d(p.out, R, EPI == kEpiSwiGLU ? I : 2 * I, 32, 32, false, true);
+      tout_h = p.out_h != nullptr ? make_tmap_2d(p.out_h, R, I, 32, 32, false, true) : tout;
+      tout_y = p.out_y != nullptr ? make_tmap_2d(p.out_y, R, 2 * I, 32, 32, false, true) : tout;
+    }
+    auto kernel = tc_gemm_persistent_kernel<MODE, BN, STAGES, OutT, EPI>;
     static bool configured = false;
     if (!configured) {
       C10_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
@@ -684,31 +484,17 @@ static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams
     }
     int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
     int ctas = std::min(total, sms);
-    kernel<<<ctas, 192, L::kTotal, stream>>>(ta, tb, tout, p, total, tiles_n, tiles_m);
+    constexpr int kThreads = (EPI != kEpiNone ? kFusedWarps : 4) * 32 + 64;
+    kernel<<<ctas, kThreads, L::kTotal, stream>>>(ta, tb, tout, tout_h, tout_y, p, total, tiles_n, tiles_m);
     C10_CUDA_KERNEL_LAUNCH_CHECK();
     count_launch();
     return;
-  }
-  if constexpr (MODE == kBNN || MODE == kBTN || BN == 192) {
-    TORCH_CHECK(false, "the non-persistent GEMM has no batched NN / TN mode and no 192-wide tile");
-  } else {
-  constexpr int STAGES = (BN >= 256) ? 3 : (BN >= 128 ? 3 : 4);
-  using L = SmemLayout<BN, STAGES>;
-  auto kernel = tc_gemm_kernel<MODE, BN, STAGES, OutT>;
-  static bool configured = false;
-  if (!configured) {
-    C10_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
-    configured = true;
-  }
-  kernel<<<grid, 128, L::kTotal, stream>>>(ta, tb, p);
-  C10_CUDA_KERNEL_LAUNCH_CHECK();
-  count_launch();
   }
 }
 
 static int pick_bn(int n) {
   if (n % 256 == 0) return 256;
-  if (n % 192 == 0 && use_persistent()) return 192;
+  if (n % 192 == 0) return 192;
   return (n % 128 == 0) ? 128 : 64;
 }
 
@@ -732,6 +518,60 @@ at::Tensor gg_nt(at::Tensor x, at::Tensor w, at::Tensor tile_group) {
   else if (bn == 128) launch_gemm<kNT, 128, __nv_bfloat16>(ta, tb, p, grid);
   else launch_gemm<kNT, 64, __nv_bfloat16>(ta, tb, p, grid);
   return out;
+}
+
+// hid[r, :] = silu(x[r] . W0[g(r)]^T) * (x[r] . W2[g(r)]^T) with W02 = [W0; W2] stacked on the row axis:
+// x [R, K], w02 [G, 2I, K] -> [R, I].  The pre-activations stay in tensor memory.
+at::Tensor gg_nt_swiglu(at::Tensor x, at::Tensor w02, at::Tensor tile_group) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w02.scalar_type() == at::kBFloat16 && x.is_contiguous() &&
+              w02.is_contiguous() && tile_group.scalar_type() == at::kInt);
+  int R = x.size(0), K = x.size(1), G = w02.size(0), N = w02.size(1), I = N / 2;
+  TORCH_CHECK(w02.size(2) == K && R % BM == 0 && K % BK == 0 && I % 128 == 0 && tile_group.numel() >= R / BM,
+              "gg_nt_swiglu: the hidden width must be a multiple of 128 and K a multiple of 64");
+  auto out = at::empty({R, I}, x.options());
+  auto ta = make_tmap_2d_bf16(x.data_ptr(), R, K, BM, BK);
+  auto tb = make_tmap_2d_bf16(w02.data_ptr(), (uint64_t)G * N, K, 128, BK);
+  GemmParams p{};
+  p.tile_group = tile_group.data_ptr<int>();
+  p.groups = G; p.N = N; p.K = K; p.out = out.data_ptr(); p.out_rows = R; p.inter = I;
+  p.status = status_word(x.device()).data_ptr<int>();
+  launch_gemm<kNT, 256, __nv_bfloat16, kEpiSwiGLU>(ta, tb, p, dim3(I / 128, R / BM));
+  return out;
+}
+
+// One pass over y0|y2 = x . W02[g]^T that emits the SwiGLU derivative products instead of the pre-activations:
+//   dy02 [R, 2I] = [dh * y2 * silu'(y0) * lr0 | dh * silu(y0) * lr2],  hlr [R, I] = silu(y0) * y2 * lr1 (want_h),
+//   y02 [R, 2I] (want_y).  lr: [R, 3] fp32 or absent (ones).  Returns {dy02, hlr or empty, y02 or empty}.
+std::vector<at::Tensor> gg_nt_swiglu_bwd(at::Tensor x, at::Tensor w02, at::Tensor dh, c10::optional<at::Tensor> lr,
+                                         at::Tensor tile_group, bool want_h, bool want_y) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w02.scalar_type() == at::kBFloat16 && x.is_contiguous() &&
+              w02.is_contiguous() && dh.scalar_type() == at::kBFloat16 && dh.is_contiguous() &&
+              tile_group.scalar_type() == at::kInt);
+  int R = x.size(0), K = x.size(1), G = w02.size(0), N = w02.size(1), I = N / 2;
+  TORCH_CHECK(w02.size(2) == K && R % BM == 0 && K % BK == 0 && I % 128 == 0 && tile_group.numel() >= R / BM &&
+              dh.size(0) == R && dh.size(1) == I, "gg_nt_swiglu_bwd: shape mismatch");
+  auto dy02 = at::empty({R, N}, x.options());
+  at::Tensor hlr = want_h ? at::empty({R, I}, x.options()) : at::Tensor();
+  at::Tensor y02 = want_y ? at::empty({R, N}, x.options()) : at::Tensor();
+  auto ta = make_tmap_2d_bf16(x.data_ptr(), R, K, BM, BK);
+  auto tb = make_tmap_2d_bf16(w02.data_ptr(), (uint64_t)G * N, K, 128, BK);
+  GemmParams p{};
+  p.tile_group = tile_group.data_ptr<int>();
+  p.groups = G; p.N = N; p.K = K; p.out = dy02.data_ptr(); p.out_rows = R; p.inter = I;
+  p.dh = dh.data_ptr();
+  at::Tensor lrc;
+  if (lr.has_value() && lr->defined()) {
+    lrc = lr->contiguous();
+    TORCH_CHECK(lrc.scalar_type() == at::kFloat && lrc.numel() == (int64_t)R * 3, "lr must be [R, 3] fp32");
+    p.lr = lrc.data_ptr<float>();
+  }
+  p.out_h = want_h ? hlr.data_ptr() : nullptr;
+  p.out_y = want_y ? y02.data_ptr() : nullptr;
+  p.status = status_word(x.device()).data_ptr<int>();
+  launch_gemm<kNT, 256, __nv_bfloat16, kEpiWrite>(ta, tb, p, dim3(I / 128, R / BM));
+  return {dy02, want_h ? hlr : at::empty({0}, x.options()), want_y ? y02 : at::empty({0}, x.options())};
 }
 
 at::Tensor gg_nn(at::Tensor x, at::Tensor w, at::Tensor tile_group) {
@@ -849,35 +689,6 @@ at::Tensor bmm_general(at::Tensor a, at::Tensor b, int64_t mode, double alpha, c
 
 at::Tensor bmm_nt(at::Tensor a, at::Tensor b, double alpha, c10::optional<at::Tensor> d, double beta) {
   return bmm_general(a, b, 0, alpha, d, beta);
-}
-
-at::Tensor bmm_nt_legacy(at::Tensor a, at::Tensor b, double alpha, c10::optional<at::Tensor> d, double beta) {
-  c10::cuda::CUDAGuard guard(a.device());
-  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && a.is_contiguous() &&
-              b.is_contiguous() && a.dim() == 3 && b.dim() == 3);
-  int B = a.size(0), M = a.size(1), K = a.size(2), N = b.size(1);
-  TORCH_CHECK(b.size(0) == B && b.size(2) == K && M % BM == 0 && N % 64 == 0 && K % BK == 0);
-  auto out = at::empty({B, M, N}, a.options());
-  auto ta = make_tmap_2d_bf16(a.data_ptr(), (uint64_t)B * M, K, BM, BK);
-  GemmParams p{};
-  p.groups = B; p.M = M; p.N = N; p.K = K; p.out = out.data_ptr();
-  p.alpha = (float)alpha; p.beta = (float)beta;
-  at::Tensor dc;
-  if (d.has_value() && d->defined()) {
-    dc = d->contiguous();
-    TORCH_CHECK(dc.scalar_type() == at::kBFloat16 && dc.numel() == out.numel());
-    p.addend = dc.data_ptr();
-  }
-  p.status = status_word(a.device()).data_ptr<int>();
-  p.out_rows = (long long)B * M;
-  int bn = pick_bn(N);
-  if (bn == 192) bn = 64;
-  auto tb = make_tmap_2d_bf16(b.data_ptr(), (uint64_t)B * N, K, bn, BK);
-  dim3 grid(N / bn, M / BM, B);
-  if (bn == 256) launch_gemm<kBMM, 256, __nv_bfloat16>(ta, tb, p, grid);
-  else if (bn == 128) launch_gemm<kBMM, 128, __nv_bfloat16>(ta, tb, p, grid);
-  else launch_gemm<kBMM, 64, __nv_bfloat16>(ta, tb, p, grid);
-  return out;
 }
 
 }  // namespace uttt

@@ -13,6 +13,7 @@ straddles two groups and token reductions need no masking.
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 from typing import Optional, Tuple
 
@@ -320,6 +321,7 @@ class GroupPlan:
     rows_padded: int            # static upper bound on padded rows (multiple of 128)
     num_groups: int
     topk: int
+    pairs: Optional[tuple] = None   # (entries [tiles, 2], count [1]) of the two-CTA GEMMs, built on first use
 
 
 def build_group_plan(expert_idx: torch.Tensor, num_experts: int) -> GroupPlan:
@@ -332,6 +334,31 @@ def build_group_plan(expert_idx: torch.Tensor, num_experts: int) -> GroupPlan:
     else:
         dest, offsets, sizes, tile_group, rows_padded = ref.build_group_plan(expert_idx, num_experts)
     return GroupPlan(dest, offsets, sizes, tile_group, int(rows_padded), bsz * num_experts, k)
+
+
+# Two-CTA (cta_group::2) variants of the grouped NT / NN products: pairs of 128-row tiles of one group share one
+# 256 x 256 MMA with a third less operand traffic per FLOP.  Measured at the benchmark's shapes they do not beat the
+# one-CTA kernels (odd tile counts leave a quarter of the pair slots half empty), so they are opt-in:
+# ``UTTT_B200_PAIR=1``.
+_USE_PAIRS = os.environ.get("UTTT_B200_PAIR", "0") == "1"
+
+
+def set_cta_pairs(flag: bool) -> None:
+    """Switch the grouped NT / NN products between the two-CTA and the one-CTA kernels (both are tested)."""
+    global _USE_PAIRS
+    _USE_PAIRS = bool(flag)
+
+
+def _pairs(plan: GroupPlan):
+    """Pair plan of ``plan`` (built by one small kernel the first time a GEMM asks for it; no host sync)."""
+    if plan.pairs is None:
+        ext = cuda_ext(plan.tile_group)
+        plan.pairs = tuple(ext.pair_plan(plan.tile_group, plan.offsets, plan.rows_padded // TILE_ROWS))
+    return plan.pairs
+
+
+def _pair_ok(n: int, plan: GroupPlan) -> bool:
+    return _USE_PAIRS and n % 128 == 0 and plan.offsets is not None and plan.tile_group.is_cuda
 
 
 # =========================================================================== dense projections
@@ -740,6 +767,8 @@ class _GGNT(torch.autograd.Function):
     def forward(ctx, x, w, plan):
         ctx.save_for_backward(x, w)
         ctx.plan = plan
+        if _pair_ok(w.shape[1], plan):
+            return cuda_ext(x).gg_nt_pair(x.contiguous(), w.contiguous(), plan.tile_group, *_pairs(plan))
         return cuda_ext(x).gg_nt(x.contiguous(), w.contiguous(), plan.tile_group)
 
     @staticmethod
@@ -760,6 +789,8 @@ class _GGNN(torch.autograd.Function):
     def forward(ctx, x, w, plan):
         ctx.save_for_backward(x, w)
         ctx.plan = plan
+        if _pair_ok(w.shape[2], plan):
+            return cuda_ext(x).gg_nn_pair(x.contiguous(), w.contiguous(), plan.tile_group, *_pairs(plan))
         return cuda_ext(x).gg_nn(x.contiguous(), w.contiguous(), plan.tile_group)
 
     @staticmethod
@@ -853,6 +884,54 @@ def swiglu(y02: torch.Tensor) -> torch.Tensor:
     return ref.swiglu(y02)
 
 
+class _GGSwiGLU(torch.autograd.Function):
+    """hid[r] = silu(x[r] W0[g]^T) * (x[r] W2[g]^T) in one grouped GEMM whose epilogue applies the gate, so the
+    [rows, 2I] pre-activations never reach memory (the reference's fused read kernel,
+    uttt_llm/flame/custom_models/uttt_moe/lact_moe_triton/triton_grouped_swiglu_kernels.py:83-270).  The backward
+    recomputes them in tensor memory and emits dh * d swiglu directly (triton_grouped_swiglu_bwd_kernels.py:49-227)."""
+
+    @staticmethod
+    def forward(ctx, x, w02, plan):
+        x, w02 = x.contiguous(), w02.contiguous()
+        ctx.save_for_backward(x, w02)
+        ctx.plan = plan
+        if _pair_ok(w02.shape[1], plan):
+            return cuda_ext(x).gg_nt_swiglu_pair(x, w02, plan.tile_group, *_pairs(plan))
+        return cuda_ext(x).gg_nt_swiglu(x, w02, plan.tile_group)
+
+    @staticmethod
+    def backward(ctx, dh):
+        x, w02 = ctx.saved_tensors
+        plan = ctx.plan
+        dy02 = _swiglu_bwd_kernel(x, w02, dh.contiguous(), None, plan, False, False)[0]
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gg_nn(dy02, w02, plan)
+        if ctx.needs_input_grad[1] and not _sink_add(w02, dy02, x, plan):
+            dw = gg_tn(dy02, x, plan, w02.dtype)
+        return dx, dw, None
+
+
+def _swiglu_bwd_kernel(x, w02, dh, lr, plan: GroupPlan, want_h: bool, want_y: bool):
+    """(dy02 [* lr], hidden [* lr1] or empty, y02 or empty): the SwiGLU derivative applied in the GEMM epilogue."""
+    ext = cuda_ext(x)
+    if _pair_ok(w02.shape[1], plan):
+        return ext.gg_nt_swiglu_bwd_pair(x, w02, dh, lr, plan.tile_group, *_pairs(plan), want_h, want_y)
+    return ext.gg_nt_swiglu_bwd(x, w02, dh, lr, plan.tile_group, want_h, want_y)
+
+
+def _gg_swiglu_ok(x, w02) -> bool:
+    return (_gg_kernel_ok(x, w02) and _kernel("gg_nt_swiglu", x) is not None and x.shape[1] % 64 == 0
+            and w02.shape[1] % 256 == 0)
+
+
+def gg_swiglu(x, w02, plan: GroupPlan):
+    """Grouped SwiGLU hidden activation: x [R, K], w02 [G, 2I, K] (gate rows, then up rows) -> [R, I]."""
+    if _gg_swiglu_ok(x, w02):
+        return _GGSwiGLU.apply(x, w02, plan)
+    return swiglu(gg_nt(x, w02, plan))
+
+
 class _FwWritePW(torch.autograd.Function):
     @staticmethod
     def forward(ctx, y02, dh, lr):
@@ -873,6 +952,23 @@ def fw_write_pointwise(y02, dh, lr):
     return ref.fw_write_pointwise(y02, dh, lr)
 
 
+def _write_inner(kp, vp, lrp, w02, w1, plan, keep_pre: bool):
+    """(dy02 * lr, hidden * lr1, y02 or None[, dh]) of the write from permuted keys / values (kernel path only).
+
+    dh = vp W1 is one grouped GEMM; the product kp W02^T stays in tensor memory and its epilogue applies the
+    SwiGLU derivative and the per-row learning rates (the reference's three-GEMM kernel with learning rates,
+    lact_moe_triton/triton_grouped_swiglu_bwd_with_lr_kernels.py:49-252).  ``keep_pre`` also writes the
+    pre-activations, which the gradient-of-gradient pass needs."""
+    dh = gg_nn(vp, w1, plan)
+    ext = cuda_ext(kp)
+    if _gg_swiglu_ok(kp, w02):
+        dy02_lr, h_lr, y02 = _swiglu_bwd_kernel(kp.contiguous(), w02.contiguous(), dh, lrp, plan, True, keep_pre)
+    else:
+        y02 = gg_nt(kp, w02, plan)
+        dy02_lr, h_lr = ext.fw_write_pw_fwd(y02, dh, lrp)
+    return (dy02_lr, h_lr, y02, dh) if keep_pre else (dy02_lr, h_lr, None)
+
+
 class _FwWriteGrad(torch.autograd.Function):
     """Inner gradient of the fast-weight write as one autograd node that keeps only its inputs.
 
@@ -888,10 +984,7 @@ class _FwWriteGrad(torch.autograd.Function):
         ctx.save_for_backward(kp, vp, lrp, w02, w1)
         ctx.plan = plan
         with torch.no_grad():
-            y02 = gg_nt(kp, w02, plan)
-            dh = gg_nn(vp, w1, plan)
-            dy02_lr, h_lr = fw_write_pointwise(y02, dh, lrp)
-            del y02, dh
+            dy02_lr, h_lr, _ = _write_inner(kp, vp, lrp, w02, w1, plan, False)
             g02 = gg_tn(dy02_lr, kp, plan)
             g1 = gg_tn(vp, h_lr, plan)
         return g02, g1
@@ -904,9 +997,7 @@ class _FwWriteGrad(torch.autograd.Function):
         with torch.no_grad():
             c02 = _cached_cast("c02", c02, kp.dtype)
             c1 = _cached_cast("c1", c1, kp.dtype)
-            y02 = gg_nt(kp, w02, plan)
-            dh = gg_nn(vp, w1, plan)
-            dy02_lr, h_lr = ext.fw_write_pw_fwd(y02, dh, lrp)
+            dy02_lr, h_lr, y02, dh = _write_inner(kp, vp, lrp, w02, w1, plan, True)
             d_dy02 = gg_nt(kp, c02, plan)            # [R, 2I]
             d_kp = gg_nn(dy02_lr, c02, plan)         # [R, D]
             d_vp = gg_nt(h_lr, c1, plan)             # [R, D]
@@ -952,10 +1043,7 @@ class _FwWriteGradAcc(torch.autograd.Function):
         ctx.save_for_backward(kp, vp, lrp, w02, w1)
         ctx.plan = plan
         with torch.no_grad():
-            y02 = gg_nt(kp, w02, plan)
-            dh = gg_nn(vp, w1, plan)
-            dy02_lr, h_lr = fw_write_pointwise(y02, dh, lrp)
-            del y02, dh
+            dy02_lr, h_lr, _ = _write_inner(kp, vp, lrp, w02, w1, plan, False)
             _gg_tn_acc_(dy02_lr, kp, plan, acc02)
             _gg_tn_acc_(vp, h_lr, plan, acc1)
         ctx.mark_dirty(acc02, acc1)

@@ -2,11 +2,12 @@
 
     python -m uttt_b200.ops.microbench [--kernel NAME] [--small] [--iters N]
 
-Kernels: gg_nt, gg_nn, gg_tn, bmm_nt, swa_fwd, swa_bwd, rms_norm, add_rms_norm, embedding, rope, fw_qk_prep, router, pool_step, plucker,
+Kernels: gg_nt, gg_swiglu, gg_write, gg_nn, gg_tn, bmm_nt, swa_fwd, swa_bwd, rms_norm, add_rms_norm, embedding, rope, fw_qk_prep, router, pool_step, plucker,
 swiglu, permute, patch_decode, frob, fw_write_pw, adamw, ce.  ``--small`` runs one small case
 of the chosen kernel (inputs above L2 size, a few hundred MB on the device) three times, which is what the
 profile summaries under ``profiles/`` were captured from.  Prints one JSON line per case with the achieved
-TFLOP/s or GB/s and the fraction of the measured peaks in ``MEASURED_PEAKS.json`` when present.
+TFLOP/s or GB/s and the fraction of the measured peaks in ``MEASURED_PEAKS.json`` when present, and a last line
+with the SM clock (median, maximum) and the throttle reasons sampled while the cases ran.
 """
 from __future__ import annotations
 
@@ -17,6 +18,7 @@ import os
 
 import torch
 
+from ..utils.clocks import ClockSampler
 from . import functional as F
 from ._ext import load
 
@@ -79,20 +81,53 @@ def run(kernel: str, small: bool, iters: int):
         out.append(r)
 
     bf = dict(device=dev, dtype=torch.bfloat16)
-    if kernel in ("gg_nt", "all"):
-        x = torch.randn(rows, d, **bf)
-        w = torch.randn(g, 2 * inter, d, **bf) * 0.05
-        ms = _time(lambda: F.gg_nt(x, w, plan), iters, flush)
-        rec("gg_nt[read gate|up]", ms, flops=2.0 * real * d * 2 * inter, rows=rows, real_rows=real, K=d, N=2 * inter)
-        h = torch.randn(rows, inter, **bf)
-        w1 = torch.randn(g, d, inter, **bf) * 0.05
-        ms = _time(lambda: F.gg_nt(h, w1, plan), iters, flush)
-        rec("gg_nt[read down]", ms, flops=2.0 * real * d * inter, rows=rows, real_rows=real, K=inter, N=d)
-    if kernel in ("gg_nn", "all"):
-        v = torch.randn(rows, d, **bf)
-        w1 = torch.randn(g, d, inter, **bf) * 0.05
-        ms = _time(lambda: F.gg_nn(v, w1, plan), iters, flush)
-        rec("gg_nn[write dh]", ms, flops=2.0 * real * d * inter, K=d, N=inter)
+    for pairs in (False, True):
+        # the grouped NT / NN products as one-CTA kernels and as CTA pairs (cta_group::2)
+        F.set_cta_pairs(pairs)
+        tag = " 2cta" if pairs else " 1cta"
+        if kernel in ("gg_nt", "all"):
+            x = torch.randn(rows, d, **bf)
+            w = torch.randn(g, 2 * inter, d, **bf) * 0.05
+            ms = _time(lambda: F.gg_nt(x, w, plan), iters, flush)
+            rec("gg_nt[read gate|up]" + tag, ms, flops=2.0 * real * d * 2 * inter, rows=rows, real_rows=real, K=d,
+                N=2 * inter)
+            h = torch.randn(rows, inter, **bf)
+            w1 = torch.randn(g, d, inter, **bf) * 0.05
+            ms = _time(lambda: F.gg_nt(h, w1, plan), iters, flush)
+            rec("gg_nt[read down]" + tag, ms, flops=2.0 * real * d * inter, rows=rows, real_rows=real, K=inter, N=d)
+        if kernel in ("gg_swiglu", "all"):
+            x = torch.randn(rows, d, **bf)
+            w = torch.randn(g, 2 * inter, d, **bf) * 0.05
+            ms = _time(lambda: F.gg_swiglu(x, w, plan), iters, flush)
+            rec("gg_swiglu[read gate|up + SwiGLU epilogue]" + tag, ms, flops=2.0 * real * d * 2 * inter, rows=rows,
+                real_rows=real, K=d, N=2 * inter)
+            if not pairs:
+                ms = _time(lambda: F.swiglu(F.gg_nt(x, w, plan)), iters, flush)
+                rec("gg_nt + swiglu_fwd [unfused pair of kernels]", ms, flops=2.0 * real * d * 2 * inter)
+        if kernel in ("gg_write", "all"):
+            ext = load()
+            x = torch.randn(rows, d, **bf)
+            w = torch.randn(g, 2 * inter, d, **bf) * 0.05
+            dh = torch.randn(rows, inter, **bf)
+            lr = torch.rand(rows, 3, device=dev)
+            ms = _time(lambda: F._swiglu_bwd_kernel(x, w, dh, lr, plan, True, False), iters, flush)
+            rec("gg_nt_swiglu_bwd[write: dy02*lr, h*lr1]" + tag, ms, flops=2.0 * real * d * 2 * inter, rows=rows,
+                real_rows=real)
+            ms = _time(lambda: F._swiglu_bwd_kernel(x, w, dh, None, plan, False, False), iters, flush)
+            rec("gg_nt_swiglu_bwd[read backward: dy02]" + tag, ms, flops=2.0 * real * d * 2 * inter)
+            if not pairs:
+                ms = _time(lambda: ext.fw_write_pw_fwd(F.gg_nt(x, w, plan), dh, lr), iters, flush)
+                rec("gg_nt + fw_write_pw_fwd [unfused pair of kernels]", ms, flops=2.0 * real * d * 2 * inter)
+        if kernel in ("gg_nn", "all"):
+            v = torch.randn(rows, d, **bf)
+            w1 = torch.randn(g, d, inter, **bf) * 0.05
+            ms = _time(lambda: F.gg_nn(v, w1, plan), iters, flush)
+            rec("gg_nn[write dh]" + tag, ms, flops=2.0 * real * d * inter, K=d, N=inter)
+            a2 = torch.randn(rows, 2 * inter, **bf)
+            w02 = torch.randn(g, 2 * inter, d, **bf) * 0.05
+            ms = _time(lambda: F.gg_nn(a2, w02, plan), iters, flush)
+            rec("gg_nn[d rows: K 3072, N 384]" + tag, ms, flops=2.0 * real * d * 2 * inter, K=2 * inter, N=d)
+    F.set_cta_pairs(True)
     if kernel in ("gg_tn", "all"):
         a = torch.randn(rows, 2 * inter, **bf)
         b = torch.randn(rows, d, **bf)
@@ -231,7 +266,12 @@ def main():
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--iters", type=int, default=10)
     args = ap.parse_args()
-    run(args.kernel, args.small, 3 if args.small else args.iters)
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
+    try:
+        run(args.kernel, args.small, 3 if args.small else args.iters)
+    finally:
+        print(json.dumps({"clocks": sampler.stop()}), flush=True)
 
 
 if __name__ == "__main__":

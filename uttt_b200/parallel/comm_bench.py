@@ -24,6 +24,8 @@ import os
 import torch
 import torch.distributed as dist
 
+from ..utils.clocks import ClockSampler
+
 from .symm import SymmetricHeap
 
 PEER_GBS = 770.0
@@ -56,6 +58,8 @@ def main():
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", device_id=dev)
     world = dist.get_world_size()
+    sampler = ClockSampler(rank)          # SM clock and throttle reasons of this rank's GPU during the timings
+    sampler.start()
     chunk = 1024 * world
     n = (args.numel + chunk - 1) // chunk * chunk
     shard = n // world
@@ -103,6 +107,7 @@ def main():
     res["nvlink_bytes_per_gpu"] = link_bytes
     for key in ("rs_peer_ms", "adamw_gather_peer_ms"):
         res[key.replace("_ms", "_frac_of_770GBs")] = round(link_bytes / (res[key] * 1e-3) / 1e9 / PEER_GBS, 3)
+    res["clocks"] = sampler.stop()          # every rank ends its own sampler
     if rank == 0:
         print(json.dumps(res))
     heap.barrier()

@@ -18,6 +18,8 @@ import os
 import torch
 import torch.distributed as dist
 
+from ..utils.clocks import ClockSampler
+
 from ..ops import functional as F_ops
 from .expert_parallel import ExpertParallel
 
@@ -56,6 +58,8 @@ def main():
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", device_id=dev)
     world = dist.get_world_size()
+    sampler = ClockSampler(rank)          # SM clock and throttle reasons of this rank's GPU during the timings
+    sampler.start()
     torch.manual_seed(7 + dist.get_rank())
     b, n, d, e, k = args.batch, args.rows, args.dim, args.experts, args.topk
     idx = torch.rand(b, n, e, device=dev).topk(k, dim=-1).indices
@@ -120,6 +124,7 @@ def main():
                           "allgather_then_gemm_ms": round(t_base, 4), "library_gemm_only_ms": round(t_gemm, 4),
                           "fused_tflops": round(flops / t_fused / 1e9, 1),
                           "remote_bytes": int(n_out * k_in * 2 * remote_frac)}
+    out["clocks"] = sampler.stop()          # every rank ends its own sampler
     if dist.get_rank() == 0:
         print(json.dumps(out), flush=True)
     dist.barrier()
