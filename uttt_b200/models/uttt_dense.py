@@ -41,13 +41,21 @@ def apply_dense_update(a02, a1, state: fw.PoolState, m_coeff, lr_scale: float, u
                        master_renorm: bool, compute_dtype) -> fw.PoolState:
     """Dense write: momentum on the raw aggregate, Newton-Schulz per square D x D slice (``slices`` = r) or
     per whole matrix (``slices`` = 0), master += delta, fast copy = master rescaled row-wise to the *previous
-    fast* row norms (the master itself is renormalised only with ``master_renorm``)."""
+    fast* row norms (the master itself is renormalised only with ``master_renorm``).
+
+    With slices, a "row" is a row of one D x D slice: for the down matrix ``w1`` [D, r*D] every row is r segments of
+    D entries with their own norms (uttt_llm/flame/custom_models/uttt_dense/modeling_recurrent_lact.py:1068-1085,
+    1166-1216 renormalise the slices, not the wide matrices)."""
     m02, m1 = state.m02, state.m1
     bsz, h, inter2, d = m02.shape
     inter = inter2 // 2
     src02, src1 = (m02, m1) if master_renorm else (state.w02, state.w1)
+    seg = (inter // d) if (slices and slices > 0) else 1       # norm segments per row of w1
+
+    def rows1(t):                                              # [b, h, d, inter] -> [b, h, d, seg, inter / seg]
+        return t.reshape(bsz, h, d, seg, inter // seg)
     old02 = src02.float().norm(dim=3, keepdim=True)
-    old1 = src1.float().norm(dim=3, keepdim=True)
+    old1 = rows1(src1.float()).norm(dim=4, keepdim=True)
     z02, z1 = state.z02, state.z1
     if z02 is not None and m_coeff is not None:
         a02 = a02 + z02 * m_coeff
@@ -68,7 +76,7 @@ def apply_dense_update(a02, a1, state: fw.PoolState, m_coeff, lr_scale: float, u
     n02 = m02 + d02.float() * lr_scale
     n1 = m1 + d1.float() * lr_scale
     p02 = n02 / (n02.norm(dim=3, keepdim=True) + 1e-5) * old02
-    p1 = n1 / (n1.norm(dim=3, keepdim=True) + 1e-5) * old1
+    p1 = (rows1(n1) / (rows1(n1).norm(dim=4, keepdim=True) + 1e-5) * old1).reshape(bsz, h, d, inter)
     if master_renorm:
         n02, n1 = p02, p1
     return fw.PoolState(p02.to(compute_dtype), p1.to(compute_dtype), n02, n1, z02, z1)

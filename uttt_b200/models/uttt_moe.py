@@ -154,7 +154,46 @@ class UTTTMoEModel(nn.Module):
         if config.use_memory_block:
             self._init_pool_parameters()
             self._init_loss_free_buffers()
+            if self.per_layer_pool:
+                # layer-local pools are kept as one stacked tensor here (one grouped launch serves every layer's
+                # state), but a checkpoint holds them under the owning layer, as the reference's does
+                self._register_state_dict_hook(UTTTMoEModel._split_pools_for_state_dict)
+                self._register_load_state_dict_pre_hook(self._merge_pools_from_state_dict)
         self.reset_parameters()
+
+    # ------------------------------------------------------------------ checkpoint layout of layer-local pools
+    # Reference layout (uttt_llm/flame/custom_models/ttt_moe_lb/modeling_recurrent_lact.py:137-158):
+    #   layers.{l}.memory.w0 / w2 [E, I, D] (or .w0.w_left [E, I, r], .w0.w_right [E, r, D]), layers.{l}.memory.w1
+    #   [E, D, I], layers.{l}.memory.router_proj_weights [1, E, D].
+    _POOL_KEYS = (("pool_w0", "w0"), ("pool_w2", "w2"), ("pool_w1", "w1"), ("pool_w0.w_left", "w0.w_left"),
+                  ("pool_w0.w_right", "w0.w_right"), ("pool_w2.w_left", "w2.w_left"),
+                  ("pool_w2.w_right", "w2.w_right"))
+
+    @staticmethod
+    def _split_pools_for_state_dict(module, state_dict, prefix, local_metadata):
+        n_layers, e = module.config.num_hidden_layers, module.num_experts
+        for ours, theirs in UTTTMoEModel._POOL_KEYS:
+            t = state_dict.pop(prefix + ours, None)
+            if t is None:
+                continue
+            for l in range(n_layers):
+                state_dict[f"{prefix}layers.{l}.memory.{theirs}"] = t[l * e:(l + 1) * e]
+        r = state_dict.pop(prefix + "per_layer_router_proj_weights", None)
+        if r is not None:
+            for l in range(n_layers):
+                state_dict[f"{prefix}layers.{l}.memory.router_proj_weights"] = r[l]
+        return state_dict
+
+    def _merge_pools_from_state_dict(self, state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys,
+                                     error_msgs):
+        n_layers = self.config.num_hidden_layers
+        for ours, theirs in UTTTMoEModel._POOL_KEYS:
+            keys = [f"{prefix}layers.{l}.memory.{theirs}" for l in range(n_layers)]
+            if all(k in state_dict for k in keys):
+                state_dict[prefix + ours] = torch.cat([state_dict.pop(k) for k in keys], dim=0)
+        keys = [f"{prefix}layers.{l}.memory.router_proj_weights" for l in range(n_layers)]
+        if all(k in state_dict for k in keys):
+            state_dict[prefix + "per_layer_router_proj_weights"] = torch.stack([state_dict.pop(k) for k in keys], dim=0)
 
     # ------------------------------------------------------------------ parameters
     def _init_pool_parameters(self) -> None:
@@ -180,11 +219,14 @@ class UTTTMoEModel(nn.Module):
         cfg = self.config
         shape = (self.num_experts,) if (cfg.memory_lb_scope == "pool" and not self.per_layer_pool) \
             else (cfg.num_hidden_layers, self.num_experts)
-        self.register_buffer("memory_loss_free_bias", torch.zeros(shape, dtype=torch.float32), persistent=True)
+        # the auxiliary-loss-only family has no balancing state in its checkpoints
+        # (uttt_llm/flame/custom_models/ttt_moe_no_lb/modeling_recurrent_lact.py registers none)
+        keep = getattr(cfg, "model_type", "") != "ttt_moe_no_lb"
+        self.register_buffer("memory_loss_free_bias", torch.zeros(shape, dtype=torch.float32), persistent=keep)
         self.register_buffer("memory_loss_free_pending_counts", torch.zeros(shape, dtype=torch.float32),
                              persistent=False)
-        self.register_buffer("memory_loss_free_steps", torch.zeros((), dtype=torch.long), persistent=True)
-        self.register_buffer("memory_loss_free_num_updates", torch.zeros((), dtype=torch.long), persistent=True)
+        self.register_buffer("memory_loss_free_steps", torch.zeros((), dtype=torch.long), persistent=keep)
+        self.register_buffer("memory_loss_free_num_updates", torch.zeros((), dtype=torch.long), persistent=keep)
         # device-side flag: 1.0 once any count is pending (keeps the update free of host syncs)
         self._host_steps = 0
 
