@@ -47,8 +47,11 @@ def _worker(rank: int, world: int, port: int, backend: str, out_dir: str):
     for ep in (1, 2):
         eng = TrainEngine(_cfg(ep), EngineConfig(micro_batch_size=2, lr=1e-2, warmup_steps=0, total_steps=10, seed=0,
                                                  weight_decay=0.0, eps=1e-3), device)
+        # evaluation first, on the initial weights and without autograd: the write path then issues its three
+        # dispatches (keys, values, learning rates) back to back before any of them is consumed
+        eval_loss = float(eng.eval_loss(batch))
         losses = [float(eng.train_step(batch)) for _ in range(2)]
-        result[ep] = {"losses": losses,
+        result[ep] = {"losses": losses, "eval_loss": eval_loss,
                       "model": {k: v.detach().float().cpu() for k, v in eng.model.state_dict().items()},
                       "transport": None if eng.expert_parallel is None else eng.expert_parallel.transport}
     torch.save(result, os.path.join(out_dir, f"r{rank}.pt"))
@@ -60,6 +63,8 @@ def _check(out_dir, atol, rtol, want_transport):
     for rank in range(2):
         got = torch.load(os.path.join(out_dir, f"r{rank}.pt"), weights_only=False)
         assert got[2]["transport"] == want_transport
+        a, b = got[1]["eval_loss"], got[2]["eval_loss"]
+        assert abs(a - b) <= atol + rtol * abs(a), ("no_grad forward", a, b)
         for a, b in zip(got[1]["losses"], got[2]["losses"]):
             assert abs(a - b) <= atol + rtol * abs(a), (got[1]["losses"], got[2]["losses"])
         for k, v in got[1]["model"].items():

@@ -1045,3 +1045,79 @@ def test_backward_modes_gpu_match_cpu(mode):
                        memory_num_active_experts=2, chunk_size=128, window_size=128, memory_lb_loss_alpha=0.0,
                        memory_update_backward_mode=mode)
     _gpu_vs_cpu_lm(cfg, seq=384, frac=0.75)
+
+
+def test_bounded_wait_gives_up_records_status_and_next_launch_is_healthy():
+    """A consumer that waits for a block nobody announces must give up after its limit, record status 51, return with
+    its tensor memory freed, and leave the device usable: the next launch (status word cleared) is correct.
+    One GPU plays both ranks of the gather-fused GEMM: the 'peer' shard is a second buffer on the same device, and
+    the gather CTAs of the SAME launch copy it but withhold the announcement (nothing faults, traps or hangs)."""
+    import time
+    ext = _ext()
+    torch.manual_seed(31)
+    m, k, n = 256, 128, 1024
+    x = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(n, k, device=DEV) / math.sqrt(k)).bfloat16()
+    want = x.float() @ w.float().t()
+    peer = w[n // 2:].clone()                                 # the other rank's rows
+    w_full = torch.zeros_like(w)
+    w_full[:n // 2] = w[:n // 2]                              # this rank's rows are in place
+    ptrs = [w_full.data_ptr(), peer.data_ptr()]
+    ready = torch.zeros(n // 256, dtype=torch.int32, device=DEV)
+    status = ext.gemm_status(x)
+    status.zero_()
+    out = ext.ag_linear(x, ptrs, 0, w_full, ready, 8)
+    torch.cuda.synchronize()
+    _status_ok()
+    _close(out, want, 3e-2, 3e-2, "healthy launch")
+    # the peer's blocks are never announced: the wait runs out after 5 ms
+    w_full[n // 2:] = 0
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    ext.ag_linear(x, ptrs, 0, w_full, ready, 8, wait_limit_ms=5.0, withhold_from_block=(n // 256) // 2)
+    torch.cuda.synchronize()
+    elapsed = time.perf_counter() - t0
+    assert int(status[0].item()) == 51, int(status[0].item())
+    assert elapsed < 1.0, f"the kernel took {elapsed:.3f} s to give up on a 5 ms limit"
+    # while the word is set, tensor-core kernels return at once; after clearing it everything works again
+    status.zero_()
+    w_full[n // 2:] = 0
+    out = ext.ag_linear(x, ptrs, 0, w_full, ready, 8)
+    torch.cuda.synchronize()
+    _status_ok()
+    _close(out, want, 3e-2, 3e-2, "launch after the failed wait")
+    a = torch.randn(256, 128, device=DEV, dtype=torch.bfloat16)
+    _close(ops.bmm_nt(a[None], a[None]), (a.float() @ a.float().t())[None], 0.2, 3e-2, "tcgen05 GEMM after it")
+    _status_ok()
+
+
+def test_training_step_is_reproducible_run_to_run():
+    """Same seed, same data, twice.  A race between kernels (a consumer that starts before its producer's data is
+    complete, a staging slab reused too early) shows up as gross differences.  What is legitimately unordered is a
+    handful of fp32 atomic sums (loss, gradient norm, router probability sums, the q/k scale gradients, the Frobenius
+    norms, the embedding-gradient scatter): they move results by fp32 rounding, which can flip the bf16 rounding of
+    a few parameter elements by one unit in the last place."""
+    _ext()
+    from uttt_b200.config import named_config
+    from uttt_b200.train.engine import EngineConfig, TrainEngine
+    cfg = named_config("tiny-uttt-moe", hidden_size=256, num_heads=4, fw_num_heads=2, memory_num_experts=4,
+                       memory_num_active_experts=2, chunk_size=128, window_size=128)
+    ids = torch.randint(0, cfg.vocab_size, (2, 256), generator=torch.Generator().manual_seed(5))
+    runs = []
+    for _ in range(2):
+        eng = TrainEngine(cfg, EngineConfig(micro_batch_size=2, warmup_steps=0, total_steps=4, seed=3),
+                          torch.device(DEV, 0))
+        losses = [float(eng.train_step({"input_ids": ids, "labels": ids})) for _ in range(2)]
+        torch.cuda.synchronize()
+        masters = eng.trainer.optimizer_state_dict()["state"]
+        runs.append((losses, {k: v["master"].float() for k, v in masters.items()}))
+    _status_ok()
+    for a, b_ in zip(runs[0][0], runs[1][0]):
+        assert abs(a - b_) <= 2e-6 * abs(a), (runs[0][0], runs[1][0])
+    for k, v in runs[0][1].items():
+        w = runs[1][1][k]
+        # fp32 masters after two AdamW steps: update size lr = 1e-3; a differing sign of a near-zero gradient moves
+        # an element by at most 2 lr
+        diff = (v - w).abs()
+        assert float(diff.max()) <= 2.5e-3, (k, float(diff.max()))
+        assert float((diff > 1e-6).float().mean()) < 0.02, (k, float((diff > 1e-6).float().mean()))

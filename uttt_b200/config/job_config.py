@@ -3,9 +3,10 @@
 Precedence: command line > TOML file (``--job.config_file``) > default, as in the reference
 (uttt_llm/flame/config_manager.py:45-66, 927-966).  TOML keys that are not declared flags (for example
 ``training.expected_global_batch_size`` or an ``[eval]`` table) are kept, so job files can carry extra
-settings.  Every section/key of the reference's flag list is declared here; options whose feature this
-framework does not implement (tensor / pipeline / context parallel degrees above 1, float8) are accepted
-and rejected with a clear error at trainer start.
+settings.  Every section/key of the reference's flag list is declared here.  No flag is silently ignored: each
+one is either read by the trainer (``FLAG_READERS`` names where) or, when its value asks for a feature this
+framework does not have, rejected by ``_validate`` with the reason (tensor / pipeline / context parallelism,
+float8, HSDP replication, parameter resharding, CPU offload of parameters, compiled blocks, torchft).
 """
 from __future__ import annotations
 
@@ -50,13 +51,36 @@ _FLAGS: Dict[str, Dict[str, Any]] = {
                        save_backend="dcp", last_save_model_weights_only=False, export_dtype="float32",
                        create_seed_checkpoint=False, async_mode="disabled", keep_latest_k=0, load_step=-1,
                        exclude_from_loading=[], interval_type="steps"),
-    "activation_checkpoint": dict(mode="selective", selective_ac_option="2"),
+    "activation_checkpoint": dict(mode="selective", selective_ac_option="2", keep_layers=[]),
     "activation_offload": dict(mode="none"),
     "float8": dict(enable_fsdp_float8_all_gather=False, precompute_float8_dynamic_scale_for_fsdp=False,
                    force_recompute_fp8_weight_in_bwd=False, recipe_name=None),
     "comm": dict(init_timeout_seconds=300, train_timeout_seconds=100, trace_buf_size=20000),
     "memory_estimation": dict(enabled=False, disable_fake_mode=False),
     "fault_tolerance": dict(enable=False, replica_id=0, group_size=0, min_replica_size=1),
+}
+
+
+# Where every flag is consumed.  "validate" = its only legal values are checked in JobConfig._validate (the feature
+# behind any other value does not exist here); tests assert that this table covers _FLAGS completely.
+FLAG_READERS: Dict[str, str] = {
+    "job": "lm_trainer.main (dump folder, printing); use_for_integration_test / description: informational",
+    "model": "lm_trainer.main (architecture JSON); tokenizer_path: train/data.py; converters: validate",
+    "profiling": "lm_trainer.main (torch profiler schedule, memory snapshot)",
+    "optimizer": "train/engine.py::EngineConfig (lr, betas, eps, decay); name / implementation / "
+                 "early_step_in_backward: validate",
+    "lr_scheduler": "train/lr.py::WarmupDecayLR",
+    "training": "lm_trainer.main + train/data.py::build_dataloader; parallel degrees, reshard policy, offload, "
+                "compile, mixed precision: validate; gc_freq, deterministic, seed: lm_trainer.main",
+    "metrics": "lm_trainer.Metrics",
+    "experimental": "validate (degrees); expert_parallel_degree: lm_trainer.main -> memory_expert_parallel",
+    "checkpoint": "train/checkpoint.py::CheckpointManager (async_mode included)",
+    "activation_checkpoint": "lm_trainer.main (recompute policy of the chunk loop)",
+    "activation_offload": "train/engine.py (saved-tensor offload to pinned host memory)",
+    "float8": "validate",
+    "comm": "train/engine.py::init_distributed (time-outs, flight-recorder size)",
+    "memory_estimation": "lm_trainer.main (prints the estimate and stops)",
+    "fault_tolerance": "validate",
 }
 
 
@@ -119,7 +143,50 @@ class JobConfig:
         return self
 
     def _validate(self) -> None:
-        assert self.model.config or self.job.use_for_integration_test or True
+        t, o, c, e = self.training, self.optimizer, self.checkpoint, self.experimental
+        if o.name not in ("AdamW",):
+            raise NotImplementedError(f"optimizer.name={o.name!r}: the fused reduce / clip / update kernels implement "
+                                      "AdamW (decoupled weight decay) only")
+        if o.implementation not in ("fused", "foreach", "for-loop"):
+            raise ValueError("optimizer.implementation must be 'fused', 'foreach' or 'for-loop' (all map to the one "
+                             "fused kernel here)")
+        if o.early_step_in_backward:
+            raise NotImplementedError("optimizer.early_step_in_backward: the step needs the global gradient norm "
+                                      "for clipping, so it runs after backward")
+        if t.data_parallel_replicate_degree != 1:
+            raise NotImplementedError("training.data_parallel_replicate_degree != 1 (HSDP): optimizer state is sharded "
+                                      "over all data-parallel ranks of the job")
+        if t.data_parallel_shard_degree not in (-1, 0) and t.data_parallel_shard_degree != int(
+                __import__("os").environ.get("WORLD_SIZE", t.data_parallel_shard_degree)):
+            raise NotImplementedError("training.data_parallel_shard_degree must be -1 or the job size")
+        if str(t.fsdp_reshard_after_forward) not in ("default", "never"):
+            raise NotImplementedError("training.fsdp_reshard_after_forward='always': parameters stay gathered between "
+                                      "steps (the reference's setting for these models is 'never')")
+        if t.enable_cpu_offload:
+            raise NotImplementedError("training.enable_cpu_offload: parameters and optimizer state live in HBM")
+        if t.compile or e.enable_compiled_autograd:
+            raise NotImplementedError("training.compile / experimental.enable_compiled_autograd: the hot path is "
+                                      "hand-written kernels, there is no traced graph to compile")
+        if t.mixed_precision_param != "bfloat16" or t.mixed_precision_reduce != "float32":
+            raise NotImplementedError("mixed precision is fixed: bfloat16 parameters / compute, float32 reduction")
+        if t.disable_loss_parallel or e.enable_async_tensor_parallel:
+            raise NotImplementedError("loss-parallel / async tensor parallel belong to tensor parallelism (degree 1)")
+        if self.model.converters:
+            raise NotImplementedError(f"model.converters={self.model.converters}: no module converters (float8) here")
+        if c.async_mode not in ("disabled", "async", "async_with_pinned_mem"):
+            raise ValueError("checkpoint.async_mode must be 'disabled', 'async' or 'async_with_pinned_mem'")
+        if c.interval_type != "steps":
+            raise NotImplementedError("checkpoint.interval_type must be 'steps'")
+        if self.activation_checkpoint.mode not in ("none", "selective", "full"):
+            raise ValueError("activation_checkpoint.mode must be 'none', 'selective' or 'full'")
+        if self.activation_offload.mode not in ("none", "offload"):
+            raise ValueError("activation_offload.mode must be 'none' or 'offload'")
+        if self.fault_tolerance.enable:
+            raise NotImplementedError("fault_tolerance.enable: torchft is not available; failures are handled by "
+                                      "step skipping, bounded waits and atomic checkpoints")
+        if self.float8.precompute_float8_dynamic_scale_for_fsdp or self.float8.force_recompute_fp8_weight_in_bwd \
+                or self.float8.recipe_name:
+            raise NotImplementedError("float8 training is not implemented")
         if self.training.tensor_parallel_degree != 1:
             raise NotImplementedError("tensor_parallel_degree > 1: the uTTT model families have no tensor-parallel plan")
         if self.experimental.pipeline_parallel_degree != 1:

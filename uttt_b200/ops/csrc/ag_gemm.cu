@@ -42,6 +42,8 @@ struct AgParams {
   __nv_bfloat16* w_full;    // [N, K] local staging of the gathered weight
   unsigned int* ready;      // [N / kAgBN] counters: gather CTAs that finished their slice of the block
   int* status;
+  unsigned long long wait_limit_ns;   // how long a GEMM CTA waits for a gathered block before it gives up
+  int withhold_blocks;      // failure-handling test: the gather CTAs copy but never announce blocks >= this index
 };
 
 struct AgSmem {
@@ -71,10 +73,12 @@ __device__ __forceinline__ bool ag_wait_ready(const AgParams& p, int block) {
       if (p.status != nullptr && *(volatile int*)p.status != 0) return false;
       uint64_t now = ptx::globaltimer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > ptx::kWaitLimitNs) break;
+      else if (now - t0 > p.wait_limit_ns) break;
     }
     __nanosleep(64);
   }
+  // the block never arrived: record it (first writer wins) and give up; the caller breaks out of its tile loop,
+  // the other warps of the CTA see the status word in their own waits, tensor memory is freed at the end
   if (p.status != nullptr) atomicCAS(p.status, 0, 51);
   return false;
 }
@@ -116,7 +120,7 @@ __global__ void __launch_bounds__(192) ag_gemm_kernel(const __grid_constant__ CU
       for (; v < vec_per_block; v += stride) dst[v] = src[v];
       __threadfence();
       __syncthreads();
-      if (threadIdx.x == 0) atomicAdd(p.ready + blk, 1u);
+      if (threadIdx.x == 0 && i < p.withhold_blocks) atomicAdd(p.ready + blk, 1u);
     }
     return;
   }
@@ -283,8 +287,12 @@ __global__ void __launch_bounds__(192) ag_gemm_kernel(const __grid_constant__ CU
 
 // x [M, K] bf16; shard_ptrs: address of every rank's [N / P, K] shard (this rank's included); w_full [N, K]
 // staging whose rows of the local shard already hold that shard; ready [N / 256] uint32 zeroed by this call.
+// `wait_limit_ms` bounds the wait of a GEMM CTA for a gathered block (default 2 s).  `withhold_from_block` >= 0 is
+// for the failure-handling test only: blocks from that position of the rank's order on are copied but never
+// announced, which is what a peer that stopped answering looks like to the consumer; the kernel then records status
+// 51 and returns after the limit, and the output is not valid.
 at::Tensor ag_linear(at::Tensor x, std::vector<int64_t> shard_ptrs, int64_t rank, at::Tensor w_full, at::Tensor ready,
-                     int64_t gather_ctas) {
+                     int64_t gather_ctas, double wait_limit_ms, int64_t withhold_from_block) {
   c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w_full.scalar_type() == at::kBFloat16 && x.is_contiguous() &&
               w_full.is_contiguous() && x.dim() == 2 && w_full.dim() == 2);
@@ -307,6 +315,8 @@ at::Tensor ag_linear(at::Tensor x, std::vector<int64_t> shard_ptrs, int64_t rank
   p.w_full = reinterpret_cast<__nv_bfloat16*>(w_full.data_ptr());
   p.ready = reinterpret_cast<unsigned int*>(ready.data_ptr<int>());
   p.status = gemm_status(x).data_ptr<int>();
+  p.wait_limit_ns = wait_limit_ms > 0 ? (unsigned long long)(wait_limit_ms * 1e6) : ptx::kWaitLimitNs;
+  p.withhold_blocks = withhold_from_block >= 0 ? (int)withhold_from_block : (1 << 30);
   AgPeers peers{};
   for (int i = 0; i < world; ++i) peers.p[i] = reinterpret_cast<const void*>(shard_ptrs[i]);
   auto ta = make_tmap_2d_bf16(x.data_ptr(), M, K, kAgBM, kAgBK);

@@ -65,7 +65,7 @@ std::vector<at::Tensor> patch_decode_fwd(at::Tensor y, c10::optional<at::Tensor>
 at::Tensor patch_decode_bwd(at::Tensor rendering, c10::optional<at::Tensor> target, c10::optional<at::Tensor> g_render,
                             c10::optional<at::Tensor> g_sse, int64_t patch, at::ScalarType dtype);
 at::Tensor ag_linear(at::Tensor x, std::vector<int64_t> shard_ptrs, int64_t rank, at::Tensor w_full, at::Tensor ready,
-                     int64_t gather_ctas);
+                     int64_t gather_ctas, double wait_limit_ms, int64_t withhold_from_block);
 std::vector<at::Tensor> ep_plan(at::Tensor sizes_all, int64_t rank, int64_t B, int64_t E, int64_t tiles_cap);
 void ep_push(at::Tensor src, c10::optional<at::Tensor> weights, at::Tensor idx, at::Tensor dest, at::Tensor offsets_local,
              at::Tensor sizes_local, at::Tensor remote_start, std::vector<int64_t> peer_ptrs, int64_t E,
@@ -138,7 +138,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("swa_bwd", &swa_bwd);
   m.def("patch_decode_fwd", &patch_decode_fwd);
   m.def("patch_decode_bwd", &patch_decode_bwd);
-  m.def("ag_linear", &ag_linear);
+  m.def("ag_linear", &ag_linear, py::arg("x"), py::arg("shard_ptrs"), py::arg("rank"), py::arg("w_full"),
+        py::arg("ready"), py::arg("gather_ctas"), py::arg("wait_limit_ms") = 0.0,
+        py::arg("withhold_from_block") = -1);
   m.def("ep_plan", &ep_plan);
   m.def("ep_push", &ep_push);
   m.def("ep_pull", &ep_pull);

@@ -99,7 +99,7 @@ class CheckpointManager:
     def __init__(self, dump_folder: str, folder: str = "checkpoint", interval: int = 2048, keep_latest_k: int = 2,
                  save_backend: str = "dcp", model_weights_only: bool = False, export_dtype: str = "float32",
                  enable: bool = True, initial_load_path: Optional[str] = None,
-                 exclude_from_loading: Optional[List[str]] = None):
+                 exclude_from_loading: Optional[List[str]] = None, async_mode: str = "disabled"):
         if save_backend not in {"dcp", "rank0_model_only"}:
             raise ValueError("save_backend must be 'dcp' or 'rank0_model_only'")
         self.root = os.path.join(dump_folder, folder)
@@ -111,6 +111,14 @@ class CheckpointManager:
         self.enable = enable
         self.initial_load_path = initial_load_path
         self.exclude_from_loading = set(exclude_from_loading or [])
+        # "async" / "async_with_pinned_mem": the state is copied to host memory inside save() (collectively, so it
+        # is a consistent snapshot of that step); rank 0 then writes and publishes it on a background thread while
+        # training continues.  The next save, load or wait() joins the thread and re-raises its error, if any.
+        if async_mode not in ("disabled", "async", "async_with_pinned_mem"):
+            raise ValueError("async_mode must be 'disabled', 'async' or 'async_with_pinned_mem'")
+        self.async_mode = async_mode
+        self._writer = None
+        self._writer_error: Optional[BaseException] = None
 
     # ------------------------------------------------------------------ discovery
     def steps(self) -> List[int]:
@@ -129,11 +137,21 @@ class CheckpointManager:
     def should_save(self, step: int, force: bool = False) -> bool:
         return self.enable and (force or (self.interval > 0 and step % self.interval == 0))
 
+    def wait(self) -> None:
+        """Block until a background write has been published; raise what it raised."""
+        if self._writer is not None:
+            self._writer.join()
+            self._writer = None
+        if self._writer_error is not None:
+            err, self._writer_error = self._writer_error, None
+            raise RuntimeError("asynchronous checkpoint write failed") from err
+
     # ------------------------------------------------------------------ save
     def save(self, step: int, model: torch.nn.Module, trainer=None, lr_scheduler=None, dataloader=None,
              train_state: Optional[TrainState] = None, force: bool = False) -> Optional[str]:
         if not self.should_save(step, force):
             return None
+        self.wait()
         # live model state every time (the compute buffers are views that change in place)
         model_sd = {k: v.detach().to("cpu", self.export_dtype if v.is_floating_point() else v.dtype)
                     for k, v in model.state_dict().items()}
@@ -156,7 +174,10 @@ class CheckpointManager:
                 dist.all_gather_object(gathered, loader_blobs[0])
                 loader_blobs = gathered
         final = self.path(step)
-        if _rank() == 0:
+        lr_sd = None if lr_scheduler is None else dict(lr_scheduler.state_dict())
+        ts_sd = None if train_state is None else train_state.state_dict()
+
+        def write() -> None:
             tmp = final + ".tmp"
             if os.path.exists(tmp):
                 shutil.rmtree(tmp)
@@ -173,14 +194,14 @@ class CheckpointManager:
                         states["optimizer"] = {"step": torch.tensor(opt_sd["step"]),
                                                "skipped_steps": torch.tensor(opt_sd["skipped_steps"]),
                                                "state": opt_sd["state"]}
-                    if lr_scheduler is not None:
+                    if lr_sd is not None:
                         states["lr_scheduler"] = {k: torch.tensor(v) if isinstance(v, (int, float)) else v
-                                                  for k, v in lr_scheduler.state_dict().items()}
+                                                  for k, v in lr_sd.items()}
                     if loader_blobs is not None:
                         states["dataloader"] = {f"rank_{r}": torch.frombuffer(bytearray(b), dtype=torch.uint8).clone()
                                                 for r, b in enumerate(loader_blobs)}
-                    if train_state is not None:
-                        states["train_state"] = train_state.state_dict()
+                    if ts_sd is not None:
+                        states["train_state"] = ts_sd
                     flat: Dict[str, Any] = {}
                     _flatten("", states, flat)
                     self._dcp_save(flat, tmp)
@@ -191,6 +212,20 @@ class CheckpointManager:
                 shutil.rmtree(tmp, ignore_errors=True)
                 raise
             self._purge()
+
+        if _rank() == 0:
+            if self.async_mode == "disabled":
+                write()
+            else:
+                import threading
+
+                def guarded() -> None:
+                    try:
+                        write()
+                    except BaseException as exc:      # surfaced by the next wait()
+                        self._writer_error = exc
+                self._writer = threading.Thread(target=guarded, name=f"checkpoint-step-{step}", daemon=False)
+                self._writer.start()
         _barrier()
         return final
 
@@ -223,6 +258,7 @@ class CheckpointManager:
              train_state: Optional[TrainState] = None, step: int = -1) -> Optional[int]:
         """Load ``step`` (newest readable when -1).  Missing keys are tolerated (partial load).
         Returns the step loaded or None when there is nothing to load."""
+        self.wait()
         candidates: List[str] = []
         if step >= 0:
             candidates = [self.path(step)]

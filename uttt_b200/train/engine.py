@@ -38,24 +38,55 @@ class EngineConfig:
     seed: int = 42
     activation_checkpoint: bool = True
     keep_activation_layers: tuple = ()     # layer indices that skip recomputation (needs spare device memory)
+    activation_offload: bool = False       # saved tensors of the forward go to pinned host memory until backward
 
 
-def init_distributed(backend: Optional[str] = None) -> tuple[int, int, int]:
-    """Join the torchrun rendezvous if there is one.  Returns (rank, world, local_rank)."""
+def init_distributed(backend: Optional[str] = None, timeout_seconds: Optional[float] = None,
+                     trace_buf_size: Optional[int] = None) -> tuple[int, int, int]:
+    """Join the torchrun rendezvous if there is one.  Returns (rank, world, local_rank).
+
+    ``timeout_seconds`` bounds every collective until :func:`set_collective_timeout` tightens it after the first
+    step (``comm.init_timeout_seconds`` / ``comm.train_timeout_seconds``, uttt_llm/flame/train.py:811-815);
+    ``trace_buf_size`` sizes NCCL's flight recorder (``comm.trace_buf_size``)."""
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world > 1 and not dist.is_initialized():
+        import datetime
         if backend is None:
             backend = "nccl" if torch.cuda.is_available() else "gloo"
+        if trace_buf_size:
+            os.environ.setdefault("TORCH_NCCL_TRACE_BUFFER_SIZE", str(int(trace_buf_size)))
+        kwargs = {}
+        if timeout_seconds:
+            kwargs["timeout"] = datetime.timedelta(seconds=float(timeout_seconds))
         if backend == "nccl":
             torch.cuda.set_device(local)
-            dist.init_process_group(backend, device_id=torch.device("cuda", local))
+            dist.init_process_group(backend, device_id=torch.device("cuda", local), **kwargs)
         else:
-            dist.init_process_group(backend)
+            dist.init_process_group(backend, **kwargs)
     elif torch.cuda.is_available():
         torch.cuda.set_device(local)
     return rank, world, local
+
+
+def set_collective_timeout(seconds: float) -> bool:
+    """Tighten the time-out of the default process group (a rank that stops answering then fails the others'
+    next collective after ``seconds`` instead of after the start-up allowance).  Returns False when the installed
+    torch has no way to change it."""
+    if not (dist.is_available() and dist.is_initialized()):
+        return False
+    import datetime
+    try:
+        from torch.distributed.distributed_c10d import _set_pg_timeout
+        _set_pg_timeout(datetime.timedelta(seconds=float(seconds)), dist.group.WORLD)
+        return True
+    except Exception:
+        return False
+
+
+class KernelStatusError(RuntimeError):
+    """A bounded device-side wait gave up, or a staging buffer overflowed: results since then are not valid."""
 
 
 class TrainEngine:
@@ -126,7 +157,8 @@ class TrainEngine:
         n_micro = (bsz + mb - 1) // mb
         total = torch.zeros((), device=self.device, dtype=torch.float32)
         for i in range(n_micro):
-            out = self.model(input_ids=ids_all[i * mb:(i + 1) * mb], labels=labels_all[i * mb:(i + 1) * mb])
+            with self._offload():
+                out = self.model(input_ids=ids_all[i * mb:(i + 1) * mb], labels=labels_all[i * mb:(i + 1) * mb])
             (out.loss / n_micro).backward()
             total += out.loss.detach().float() / n_micro
             if n_micro > 1:
@@ -140,6 +172,32 @@ class TrainEngine:
         self.last_stats.update(stats)
         self.last_stats["lr"] = lr
         return total
+
+    def _offload(self):
+        from ..utils.activation_offload import offload_activations
+        return offload_activations(enabled=self.cfg.activation_offload and self.device.type == "cuda")
+
+    def kernel_status(self) -> int:
+        """The device status word of the tensor-core / expert-parallel kernels (0 = healthy).  Reading it
+        synchronises with the device: call it at log and checkpoint steps, not every step."""
+        if self.device.type != "cuda":
+            return 0
+        from ..ops._ext import load
+        ext = load()
+        if ext is None or not hasattr(ext, "gemm_status"):
+            return 0
+        return int(ext.gemm_status(torch.zeros(1, device=self.device))[0].item())
+
+    def check_kernel_status(self) -> None:
+        """Raise when a kernel reported a failed bounded wait or an overflow.  After such a report every later
+        tensor-core kernel returns at once and leaves its outputs stale, so training must not go on (and no
+        checkpoint may be written) on top of it."""
+        code = self.kernel_status()
+        if code != 0:
+            raise KernelStatusError(
+                f"device status word = {code} at step {self.step}: a bounded wait timed out (codes 1-59), an "
+                f"expert-parallel staging buffer overflowed (61) or an index was out of range (7x); "
+                f"restart from the last checkpoint")
 
     @torch.no_grad()
     def eval_loss(self, batch: Dict[str, torch.Tensor]) -> torch.Tensor:

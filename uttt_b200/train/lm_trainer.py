@@ -11,6 +11,7 @@ events; the gradient path is the fused peer-memory reduce/AdamW/all-gather step.
 """
 from __future__ import annotations
 
+import gc
 import json
 import os
 import sys
@@ -25,7 +26,7 @@ from ..config.job_config import JobConfig
 from ..utils.flops import get_nparams_and_flops, peak_flops
 from .checkpoint import CheckpointManager, TrainState
 from .data import build_dataloader
-from .engine import EngineConfig, TrainEngine, init_distributed
+from .engine import EngineConfig, TrainEngine, init_distributed, set_collective_timeout
 
 
 def check_global_batch(job: JobConfig, world: int) -> int:
@@ -47,6 +48,17 @@ class Metrics:
         self.t_last, self.tokens_since = time.perf_counter(), 0
         self.path = os.path.join(job.job.dump_folder, "metrics.jsonl")
         self.tb = None
+        self.wandb = None
+        if rank == 0 and job.metrics.enable_wandb and os.environ.get("DISABLE_WANDB", "0").lower() in ("0", "", "false"):
+            try:
+                import wandb
+            except ImportError as exc:
+                raise ImportError("metrics.enable_wandb is set but the wandb package is not installed; install it "
+                                  "or set DISABLE_WANDB=1 (metrics still go to stdout, metrics.jsonl and "
+                                  "TensorBoard)") from exc
+            self.wandb = wandb.init(project=os.environ.get("WANDB_PROJECT", "uttt_b200"),
+                                    name=os.environ.get("WANDB_NAME"), dir=job.job.dump_folder,
+                                    config=job.to_dict(), resume="allow")
         if rank == 0:
             os.makedirs(job.job.dump_folder, exist_ok=True)
             if job.metrics.enable_tensorboard:
@@ -88,15 +100,66 @@ class Metrics:
                 for k, v in rec.items():
                     if isinstance(v, (int, float)) and k != "step":
                         self.tb.add_scalar(k, v, step)
+            if self.wandb is not None:
+                self.wandb.log({k: v for k, v in rec.items() if isinstance(v, (int, float))}, step=step)
+
+
+def param_check(model: torch.nn.Module) -> List[str]:
+    """One line per parameter with its shape, mean and standard deviation (the reference prints the same table
+    at start-up, uttt_llm/flame/train.py:394-420): a wrong initialisation or a failed load shows up before step 1."""
+    lines = []
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            f = p.detach().float()
+            std = float(f.std()) if f.numel() > 1 else 0.0
+            lines.append(f"[param-check] {name} shape={tuple(p.shape)} mean={float(f.mean()):+.6e} std={std:.6e}")
+    return lines
+
+
+def estimate_memory(model_cfg, job: JobConfig, world: int) -> Dict[str, float]:
+    """Analytic per-GPU memory estimate in GiB (``memory_estimation.enabled``): parameters and optimizer state from
+    a meta-device build, fast-weight state and recompute checkpoints from the shapes of the chunk recurrence."""
+    from ..models import build_model
+    with torch.device("meta"):
+        n = sum(p.numel() for p in build_model(model_cfg).parameters())
+    b, s = job.training.batch_size, job.training.seq_len
+    d, layers = model_cfg.hidden_size, model_cfg.num_hidden_layers
+    chunk = getattr(model_cfg, "chunk_size", s) or s
+    gib = 2.0 ** 30
+    out = {"params_bf16": 2 * n / gib, "grads_bf16": 2 * n / gib, "optimizer_fp32_shard": 12 * n / max(world, 1) / gib}
+    if getattr(model_cfg, "use_memory_block", False) and hasattr(model_cfg, "memory_num_experts"):
+        e, hd, inter = model_cfg.memory_num_experts, model_cfg.fw_head_dim, model_cfg.fw_inter_dim
+        per_seq = 3 * e * hd * inter * (4 + 4 + 2)                        # master + momentum + compute copy
+        out["pool_state_per_version"] = b * per_seq / gib
+        out["pool_versions_kept_for_backward"] = out["pool_state_per_version"] * (s // chunk)
+    out["chunk_checkpoints"] = b * s * d * 2 * layers / gib               # one block input per (chunk, layer)
+    out["recompute_working_set"] = b * chunk * d * 2 * 40 / gib           # activations of one (chunk, layer) region
+    out["logits_chunk"] = 8192 * model_cfg.vocab_size * 2 * 2 / gib
+    out["total"] = sum(out.values())
+    return out
 
 
 def main(job: Optional[JobConfig] = None) -> TrainState:
     job = job or JobConfig().parse_args()
-    rank, world, local = init_distributed()
+    rank, world, local = init_distributed(timeout_seconds=job.comm.init_timeout_seconds,
+                                          trace_buf_size=job.comm.trace_buf_size)
     check_global_batch(job, world)
     if job.job.print_args and rank == 0:
         print(json.dumps(job.to_dict(), indent=1, default=str))
+    if job.training.deterministic:
+        # same seed, same reduction order: bit-identical reruns (the kernels of this framework use fixed
+        # reduction orders except the embedding-gradient scatter, which uses fp32 reductions in memory)
+        os.environ.setdefault("CUBLAS_WORKSPACE_CONFIG", ":4096:8")
+        torch.use_deterministic_algorithms(True, warn_only=True)
+        torch.backends.cudnn.deterministic, torch.backends.cudnn.benchmark = True, False
     model_cfg = load_config(job.model.config)
+    if job.experimental.expert_parallel_degree > 1:
+        model_cfg = model_cfg.replace(memory_expert_parallel=int(job.experimental.expert_parallel_degree))
+    if job.memory_estimation.enabled:
+        est = estimate_memory(model_cfg, job, world)
+        if rank == 0:
+            print("[memory-estimate] " + " ".join(f"{k}={v:.2f}GiB" for k, v in est.items()), flush=True)
+        return TrainState()
     accum = job.training.gradient_accumulation_steps
     if getattr(model_cfg, "memory_lb_mode", None) == "loss_free" and accum > 1:
         # one bias update per optimizer step: the interval counts forwards
@@ -108,8 +171,17 @@ def main(job: Optional[JobConfig] = None) -> TrainState:
                         warmup_steps=job.lr_scheduler.warmup_steps, total_steps=job.training.steps,
                         decay_type=job.lr_scheduler.decay_type, lr_min=job.lr_scheduler.lr_min,
                         skip_nan_inf=job.training.skip_nan_inf, seed=job.training.seed,
-                        activation_checkpoint=job.activation_checkpoint.mode != "none" or True)
+                        # The recompute of every (chunk, layer) region belongs to the model, as in the reference
+                        # (modeling_recurrent_lact.py:3501 checkpoints unconditionally; its job files say
+                        # mode = "none").  The job-level modes would wrap whole blocks on top of that, which
+                        # recomputes nothing more: all three select the same schedule; `keep_layers` opts
+                        # layers out of it where memory allows.
+                        activation_checkpoint=True,
+                        keep_activation_layers=tuple(int(i) for i in job.activation_checkpoint.keep_layers),
+                        activation_offload=job.activation_offload.mode == "offload")
     engine = TrainEngine(model_cfg, ecfg)
+    if rank == 0 and job.job.print_args:
+        print("\n".join(param_check(engine.model)), flush=True)
     data = build_dataloader(job.training.dataset, vocab_size=model_cfg.vocab_size, seq_len=job.training.seq_len,
                             batch_size=job.training.batch_size * accum, rank=rank, world=world,
                             seed=job.training.seed, data_files=job.training.data_files)
@@ -118,7 +190,7 @@ def main(job: Optional[JobConfig] = None) -> TrainState:
                              job.checkpoint.keep_latest_k, job.checkpoint.save_backend,
                              job.checkpoint.model_weights_only, job.checkpoint.export_dtype,
                              job.checkpoint.enable_checkpoint, job.checkpoint.initial_load_path,
-                             job.checkpoint.exclude_from_loading)
+                             job.checkpoint.exclude_from_loading, job.checkpoint.async_mode)
     loaded = None
     if job.checkpoint.enable_checkpoint:
         loaded = ckpt.load(engine.model, engine.trainer, engine.lr_sched, data, state, step=job.checkpoint.load_step)
@@ -149,24 +221,47 @@ def main(job: Optional[JobConfig] = None) -> TrainState:
     if snapshot:
         torch.cuda.memory._record_memory_history(max_entries=100000)
     t0 = time.perf_counter()
+    # garbage collection at fixed steps on every rank instead of whenever each interpreter feels like it: an
+    # unsynchronised collection stalls one rank and with it every collective (training.gc_freq)
+    gc_freq = int(job.training.gc_freq or 0)
+    if gc_freq > 0:
+        gc.disable()
+        gc.collect(1)
+    skipped_on_device = None          # running count of skipped steps, read back only when logging
+    first_step = True
     while state.step < job.training.steps:
+        # the step number as the model's statistics hooks see it (the pool statistics are taken every N steps)
         os.environ["FLAME_TRAIN_STEP"] = str(state.step + 1)
         batch = next(data)
         loss = engine.train_step(batch)
         state.step += 1
         state.token += batch["input_ids"].numel() * world
-        if job.training.skip_nan_inf:
-            # read back lazily: only when logging
-            pass
         stats = dict(engine.last_stats)
-        if state.step % job.metrics.log_freq == 0 or state.step == 1:
-            state.skipped_step += int(bool(stats["skipped"]))
+        skipped = stats["skipped"].detach().to(torch.int64) if torch.is_tensor(stats["skipped"]) \
+            else torch.tensor(int(bool(stats["skipped"])))
+        skipped_on_device = skipped if skipped_on_device is None else skipped_on_device + skipped
+        logging_step = state.step % job.metrics.log_freq == 0 or state.step == 1
+        saving_step = ckpt.should_save(state.step, state.step == job.training.steps and job.checkpoint.enable_checkpoint)
+        if logging_step or saving_step:
+            state.skipped_step += int(skipped_on_device.item())       # every skipped step since the last read
+            skipped_on_device = None
+            engine.check_kernel_status()                               # never log or save on top of a failed kernel
         metrics.log(state.step, loss, stats, batch["input_ids"].numel(), state)
         state.elapsed = time.perf_counter() - t0
         ckpt.save(state.step, engine.model, engine.trainer, engine.lr_sched, data, state,
                   force=state.step == job.training.steps and job.checkpoint.enable_checkpoint)
+        if first_step:
+            # start-up (lazy initialisation, first allocations) is over: a rank that stops answering now fails
+            # the others' next collective after the training time-out, not the start-up one
+            set_collective_timeout(job.comm.train_timeout_seconds)
+            first_step = False
+        if gc_freq > 0 and state.step % gc_freq == 0:
+            gc.collect(1)
         if prof is not None:
             prof.step()
+    ckpt.wait()
+    if gc_freq > 0:
+        gc.enable()
     if prof is not None:
         prof.stop()
     if snapshot:
