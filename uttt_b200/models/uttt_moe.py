@@ -405,6 +405,8 @@ class UTTTMoEModel(nn.Module):
             a1 = torch.zeros_like(s.m1)
             ms, probs, counts = [], [], []
             detach_g = mode in ("first_order_state", "stop_state")
+            # the writers' token reductions are added to the aggregate several layers per launch
+            stash = None if detach_g else ops.write_stash_for(a02)
             for wi, li in enumerate(writers):
                 args_l = (f[3 * wi], f[3 * wi + 1], f[3 * wi + 2], s.w02, s.w1, self._router(li),
                           self._router_bias(li), offset)
@@ -412,7 +414,8 @@ class UTTTMoEModel(nn.Module):
                     g02, g1, m, p, c = self.layers[li].raw_grad(*args_l)
                     a02, a1 = a02 + g02.detach(), a1 + g1.detach()
                 else:
-                    a02, a1, m, p, c = self.layers[li].raw_grad(*args_l, acc=(a02, a1))
+                    a02, a1, m, p, c = self.layers[li].raw_grad(
+                        *args_l, acc=(a02, a1, stash, wi == len(writers) - 1))
                 if m is not None:
                     ms.append(m.detach() if (cfg.memory_detach_m_coeff or mode == "stop_state") else m)
                 probs.append(p)

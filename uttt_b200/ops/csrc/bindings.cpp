@@ -49,6 +49,8 @@ at::Tensor gg_nt_swiglu_pair(at::Tensor x, at::Tensor w02, at::Tensor tile_group
 std::vector<at::Tensor> gg_nt_swiglu_bwd_pair(at::Tensor x, at::Tensor w02, at::Tensor dh, c10::optional<at::Tensor> lr,
                                               at::Tensor tile_group, at::Tensor entries, at::Tensor count, bool want_h,
                                               bool want_y);
+at::Tensor gg_tn_multi(std::vector<at::Tensor> as, std::vector<at::Tensor> bs, std::vector<at::Tensor> offsets,
+                       int64_t num_groups, at::ScalarType out_dtype, c10::optional<at::Tensor> accumulate_into);
 at::Tensor gg_tn_segments(at::Tensor a, at::Tensor b, at::Tensor offsets, int64_t num_groups, int64_t segments,
                           at::ScalarType out_dtype, c10::optional<at::Tensor> accumulate_into);
 at::Tensor bmm_nt(at::Tensor a, at::Tensor b, double alpha, c10::optional<at::Tensor> d, double beta);
@@ -131,6 +133,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gg_nt_swiglu_pair", &gg_nt_swiglu_pair);
   m.def("gg_nt_swiglu_bwd_pair", &gg_nt_swiglu_bwd_pair);
   m.def("gg_tn_segments", &gg_tn_segments);
+  m.def("gg_tn_multi", &gg_tn_multi);
   m.def("bmm_nt", &bmm_nt);
   m.def("gemm_status", &gemm_status);
   m.def("bmm_general", &bmm_general);

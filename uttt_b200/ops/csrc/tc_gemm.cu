@@ -56,7 +56,8 @@ struct TileCoord {
 };
 
 template <int MODE, int BN>
-__device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int id, int tiles_n, int tiles_m) {
+__device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, const TnSegments& segs, int id, int tiles_n,
+                                                 int tiles_m) {
   TileCoord c{};
   if (MODE == kNT || MODE == kNN) {
     int t = id / tiles_n;
@@ -77,10 +78,7 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int id, in
     c.unused = false;
     if (MODE == kTN) {
       int n = 0;
-      for (int s = 0; s < p.segments; ++s) {
-        const int* off = p.seg_offsets + (size_t)s * (p.groups + 1);
-        n += (off[c.g + 1] - off[c.g]) / BK;
-      }
+      for (int s = 0; s < p.segments; ++s) n += (segs.offsets[s][c.g + 1] - segs.offsets[s][c.g]) / BK;
       c.nkb = n;
     } else {
       c.nkb = p.K / BK;
@@ -95,6 +93,7 @@ __global__ void __launch_bounds__((EPI != kEpiNone ? kFusedWarps : 4) * 32 + 64)
                                                                  const __grid_constant__ CUtensorMap tma_out,
                                                                  const __grid_constant__ CUtensorMap tma_out_h,
                                                                  const __grid_constant__ CUtensorMap tma_out_y,
+                                                                 const __grid_constant__ TnSegments segs,
                                                                  GemmParams p, int total_tiles, int tiles_n,
                                                                  int tiles_m) {
   static_assert(EPI == kEpiNone || (MODE == kNT && BN == 256 && sizeof(OutT) == 2),
@@ -156,12 +155,12 @@ __global__ void __launch_bounds__((EPI != kEpiNone ? kFusedWarps : 4) * 32 + 64)
       uint32_t it = 0;
       bool ok = true;
       for (int id = blockIdx.x; id < total_tiles && ok; id += gridDim.x) {
-        TileCoord c = decode_tile<MODE, TW>(p, id, tiles_n, tiles_m);
+        TileCoord c = decode_tile<MODE, TW>(p, segs, id, tiles_n, tiles_m);
         if (c.unused || c.nkb == 0) continue;
         int seg = 0, seg_row = 0, seg_end = 0;
         if (MODE == kTN) {
-          seg_row = p.seg_offsets[c.g];
-          seg_end = p.seg_offsets[c.g + 1];
+          seg_row = segs.offsets[0][c.g];
+          seg_end = segs.offsets[0][c.g + 1];
         }
         for (int kb = 0; kb < c.nkb; ++kb, ++it) {
           int s = it % STAGES;
@@ -196,19 +195,19 @@ __global__ void __launch_bounds__((EPI != kEpiNone ? kFusedWarps : 4) * 32 + 64)
             for (int j = 0; j < BN / 64; ++j)
               ptx::tma_load_2d(sb + j * (BK * 128), &tma_b, full_bar(s), c.n0 + 64 * j, c.g * p.K + kb * BK);
           } else {
-            while (seg_row >= seg_end) {
+            while (seg_row >= seg_end) {      // next row buffer that has rows of this group
               ++seg;
-              const int* off = p.seg_offsets + (size_t)seg * (p.groups + 1);
-              seg_row = off[c.g];
-              seg_end = off[c.g + 1];
+              seg_row = segs.offsets[seg][c.g];
+              seg_end = segs.offsets[seg][c.g + 1];
             }
-            int row = seg * p.rows_per_segment + seg_row;
+            const CUtensorMap* ma = &segs.a[seg];
+            const CUtensorMap* mb = &segs.b[seg];
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)
-              ptx::tma_load_2d(sa + j * (BK * 128), &tma_a, full_bar(s), c.m0 + 64 * j, row);
+              ptx::tma_load_2d(sa + j * (BK * 128), ma, full_bar(s), c.m0 + 64 * j, seg_row);
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              ptx::tma_load_2d(sb + j * (BK * 128), &tma_b, full_bar(s), c.n0 + 64 * j, row);
+              ptx::tma_load_2d(sb + j * (BK * 128), mb, full_bar(s), c.n0 + 64 * j, seg_row);
             seg_row += BK;
           }
         }
@@ -223,7 +222,7 @@ __global__ void __launch_bounds__((EPI != kEpiNone ? kFusedWarps : 4) * 32 + 64)
       uint32_t it = 0, acc_it = 0;
       bool ok = true;
       for (int id = blockIdx.x; id < total_tiles && ok; id += gridDim.x) {
-        TileCoord c = decode_tile<MODE, TW>(p, id, tiles_n, tiles_m);
+        TileCoord c = decode_tile<MODE, TW>(p, segs, id, tiles_n, tiles_m);
         if (c.unused || c.nkb == 0) continue;
         const int ab = acc_it & 1;
         ok = ptx::mbar_wait(acc_empty(ab), ((acc_it >> 1) & 1) ^ 1, p.status, 22);
@@ -264,7 +263,7 @@ __global__ void __launch_bounds__((EPI != kEpiNone ? kFusedWarps : 4) * 32 + 64)
     const uint32_t slab_base = smem_base + L::kOutOffset + warp * 8192;
     constexpr int SUBW = 128 / (int)sizeof(OutT);      // output columns per 128-byte staging row
     for (int id = blockIdx.x; id < total_tiles && ok; id += gridDim.x) {
-      TileCoord c = decode_tile<MODE, TW>(p, id, tiles_n, tiles_m);
+      TileCoord c = decode_tile<MODE, TW>(p, segs, id, tiles_n, tiles_m);
       if constexpr (EPI != kEpiNone) {
         // ---- fused SwiGLU epilogues: accumulator columns [0, 128) = y0 (gate), [128, 256) = y2 (up) ----
         const int quarter = warp & 3, half = warp >> 2;       // TMEM lane quarter; which 64 hidden columns
@@ -274,7 +273,7 @@ __global__ void __launch_bounds__((EPI != kEpiNone ? kFusedWarps : 4) * 32 + 64)
           continue;
         }
         if (EPI == kEpiWrite && id + (int)gridDim.x < total_tiles) {
-          const TileCoord nx = decode_tile<MODE, TW>(p, id + gridDim.x, tiles_n, tiles_m);
+          const TileCoord nx = decode_tile<MODE, TW>(p, segs, id + gridDim.x, tiles_n, tiles_m);
           if (!nx.unused) prefetch_dh_line(p, nx.out_row0 + quarter * 32 + lane, nx.n0, half);
         }
         const int ab = acc_it & 1;
@@ -449,8 +448,19 @@ at::Tensor& status_word(const at::Device& dev) {
 at::Tensor gemm_status(at::Tensor like) { return status_word(like.device()); }
 
 template <int MODE, int BN, typename OutT, int EPI = kEpiNone>
-static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, dim3 grid) {
+static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, dim3 grid,
+                        const TnSegments* tn_segments = nullptr) {
   auto stream = at::cuda::getCurrentCUDAStream().stream();
+  TnSegments segs;
+  if (tn_segments != nullptr) {
+    segs = *tn_segments;
+  } else {
+    for (int i = 0; i < kMaxTnSegments; ++i) {
+      segs.a[i] = ta;
+      segs.b[i] = tb;
+      segs.offsets[i] = nullptr;
+    }
+  }
   {
     // the write epilogue stages four slabs per warp (64 KB) and is bound by its epilogue: three stages suffice
     constexpr int STAGES = (EPI == kEpiWrite) ? 3 : ((BN >= 192) ? 4 : (BN >= 128 ? 6 : 8));
@@ -485,7 +495,7 @@ static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams
     int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
     int ctas = std::min(total, sms);
     constexpr int kThreads = (EPI != kEpiNone ? kFusedWarps : 4) * 32 + 64;
-    kernel<<<ctas, kThreads, L::kTotal, stream>>>(ta, tb, tout, tout_h, tout_y, p, total, tiles_n, tiles_m);
+    kernel<<<ctas, kThreads, L::kTotal, stream>>>(ta, tb, tout, tout_h, tout_y, segs, p, total, tiles_n, tiles_m);
     C10_CUDA_KERNEL_LAUNCH_CHECK();
     count_launch();
     return;
@@ -596,16 +606,29 @@ at::Tensor gg_nn(at::Tensor x, at::Tensor w, at::Tensor tile_group) {
   return out;
 }
 
-// a: [S*R, M], b: [S*R, N] (S stacked row buffers of R rows each); offsets: [S, G+1] int32 padded group starts.
-at::Tensor gg_tn_segments(at::Tensor a, at::Tensor b, at::Tensor offsets, int64_t num_groups, int64_t segments,
-                          at::ScalarType out_dtype, c10::optional<at::Tensor> accumulate_into) {
-  c10::cuda::CUDAGuard guard(a.device());
-  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && a.is_contiguous() &&
-              b.is_contiguous() && offsets.scalar_type() == at::kInt && offsets.is_contiguous());
-  int64_t rows = a.size(0);
-  int M = a.size(1), N = b.size(1), G = num_groups;
-  TORCH_CHECK(b.size(0) == rows && rows % segments == 0 && M % BM == 0 && N % 64 == 0);
-  TORCH_CHECK(offsets.numel() == segments * (G + 1));
+// out[g] (+)= sum over the buffer pairs s of sum_{r in group g} a_s[r]^T b_s[r].
+// a_s: [R_s, M], b_s: [R_s, N] bf16; offsets_s: [G + 1] int32 padded group starts of pair s; at most kMaxTnSegments
+// pairs per call.
+at::Tensor gg_tn_multi(std::vector<at::Tensor> as, std::vector<at::Tensor> bs, std::vector<at::Tensor> offsets,
+                       int64_t num_groups, at::ScalarType out_dtype, c10::optional<at::Tensor> accumulate_into) {
+  const int S = (int)as.size();
+  TORCH_CHECK(S >= 1 && S <= kMaxTnSegments && (int)bs.size() == S && (int)offsets.size() == S,
+              "gg_tn_multi takes 1 to ", kMaxTnSegments, " (a, b, offsets) triples");
+  c10::cuda::CUDAGuard guard(as[0].device());
+  const int M = as[0].size(1), N = bs[0].size(1), G = (int)num_groups;
+  TORCH_CHECK(M % BM == 0 && N % 64 == 0);
+  TnSegments segs;
+  for (int s = 0; s < kMaxTnSegments; ++s) {
+    const int i = s < S ? s : 0;
+    const at::Tensor &a = as[i], &b = bs[i], &off = offsets[i];
+    TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && a.is_contiguous() &&
+                b.is_contiguous() && a.dim() == 2 && b.dim() == 2 && a.size(1) == M && b.size(1) == N &&
+                a.size(0) == b.size(0) && off.scalar_type() == at::kInt && off.is_contiguous() && off.numel() == G + 1 &&
+                a.device() == as[0].device());
+    segs.a[s] = make_tmap_2d_bf16(a.data_ptr(), a.size(0), M, BK, 64);
+    segs.b[s] = make_tmap_2d_bf16(b.data_ptr(), b.size(0), N, BK, 64);
+    segs.offsets[s] = off.data_ptr<int>();
+  }
   at::Tensor out;
   bool acc = accumulate_into.has_value() && accumulate_into->defined();
   if (acc) {
@@ -613,34 +636,47 @@ at::Tensor gg_tn_segments(at::Tensor a, at::Tensor b, at::Tensor offsets, int64_
     TORCH_CHECK((out.scalar_type() == at::kFloat || out.scalar_type() == at::kBFloat16) && out.is_contiguous() &&
                 out.numel() == (int64_t)G * M * N);
   } else {
-    out = at::empty({G, M, N}, a.options().dtype(out_dtype));
+    out = at::empty({G, M, N}, as[0].options().dtype(out_dtype));
   }
-  auto ta = make_tmap_2d_bf16(a.data_ptr(), rows, M, BK, 64);
-  auto tb = make_tmap_2d_bf16(b.data_ptr(), rows, N, BK, 64);
   GemmParams p{};
-  p.seg_offsets = offsets.data_ptr<int>();
-  p.segments = (int)segments;
-  p.rows_per_segment = (int)(rows / segments);
+  p.segments = S;
   p.groups = G; p.M = M; p.N = N; p.out = out.data_ptr(); p.out_rows = (long long)G * M;
   p.accumulate = acc ? 1 : 0;
-  p.status = status_word(a.device()).data_ptr<int>();
+  p.status = status_word(as[0].device()).data_ptr<int>();
   bool f32 = out.scalar_type() == at::kFloat;
   const int bn = pick_bn(N);
   dim3 grid(M / BM, N / bn, G);
+  const CUtensorMap &ta = segs.a[0], &tb = segs.b[0];
   if (bn == 256) {
-    if (f32) launch_gemm<kTN, 256, float>(ta, tb, p, grid);
-    else launch_gemm<kTN, 256, __nv_bfloat16>(ta, tb, p, grid);
+    if (f32) launch_gemm<kTN, 256, float>(ta, tb, p, grid, &segs);
+    else launch_gemm<kTN, 256, __nv_bfloat16>(ta, tb, p, grid, &segs);
   } else if (bn == 192) {
-    if (f32) launch_gemm<kTN, 192, float>(ta, tb, p, grid);
-    else launch_gemm<kTN, 192, __nv_bfloat16>(ta, tb, p, grid);
+    if (f32) launch_gemm<kTN, 192, float>(ta, tb, p, grid, &segs);
+    else launch_gemm<kTN, 192, __nv_bfloat16>(ta, tb, p, grid, &segs);
   } else if (bn == 128) {
-    if (f32) launch_gemm<kTN, 128, float>(ta, tb, p, grid);
-    else launch_gemm<kTN, 128, __nv_bfloat16>(ta, tb, p, grid);
+    if (f32) launch_gemm<kTN, 128, float>(ta, tb, p, grid, &segs);
+    else launch_gemm<kTN, 128, __nv_bfloat16>(ta, tb, p, grid, &segs);
   } else {
-    if (f32) launch_gemm<kTN, 64, float>(ta, tb, p, grid);
-    else launch_gemm<kTN, 64, __nv_bfloat16>(ta, tb, p, grid);
+    if (f32) launch_gemm<kTN, 64, float>(ta, tb, p, grid, &segs);
+    else launch_gemm<kTN, 64, __nv_bfloat16>(ta, tb, p, grid, &segs);
   }
   return out;
+}
+
+// One buffer pair, or S stacked ones: a: [S*R, M], b: [S*R, N]; offsets: [S, G+1] int32 padded group starts.
+at::Tensor gg_tn_segments(at::Tensor a, at::Tensor b, at::Tensor offsets, int64_t num_groups, int64_t segments,
+                          at::ScalarType out_dtype, c10::optional<at::Tensor> accumulate_into) {
+  TORCH_CHECK(segments >= 1 && a.dim() == 2 && b.dim() == 2 && a.size(0) % segments == 0 && a.size(0) == b.size(0) &&
+              offsets.numel() == segments * (num_groups + 1) && offsets.is_contiguous());
+  const int64_t rows = a.size(0) / segments;
+  std::vector<at::Tensor> as, bs, offs;
+  auto off2 = offsets.view({segments, num_groups + 1});
+  for (int64_t s = 0; s < segments; ++s) {
+    as.push_back(a.narrow(0, s * rows, rows));
+    bs.push_back(b.narrow(0, s * rows, rows));
+    offs.push_back(off2.select(0, s));
+  }
+  return gg_tn_multi(as, bs, offs, num_groups, out_dtype, accumulate_into);
 }
 
 // out[b] = alpha * op(A[b]) . op(B[b])^T-like products without materialised transposes:

@@ -14,9 +14,7 @@ __host__ __device__ constexpr bool is_batched(int m) { return m == kBMM || m == 
 
 struct GemmParams {
   const int* tile_group;    // NT/NN: [tiles]
-  const int* seg_offsets;   // TN: [segments, G + 1] padded row offsets of every group in every segment
-  int segments;             // TN: number of stacked row buffers reduced together
-  int rows_per_segment;     // TN: row stride between stacked buffers
+  int segments;             // TN: number of (a, b) row-buffer pairs reduced together (see TnSegments)
   int groups;
   int M, N, K;              // per-group problem dims (NT/NN: M unused)
   void* out;
@@ -40,6 +38,17 @@ struct GemmParams {
 //                out_h[r, j]   = silu(y0) * y2 * lr1,        out_y = y0 | y2  (each optional output may be absent)
 // where y0 = x W0^T and y2 = x W2^T never leave the tensor memory unless out_y asks for them.
 enum GemmEpilogue { kEpiNone = 0, kEpiSwiGLU = 1, kEpiWrite = 2 };
+
+// Token reduction over several row buffers at once: out[g] (+)= sum_s sum_{r in group g of buffer s} a_s[r]^T b_s[r].
+// Each buffer pair has its own layout (padded group offsets).  Used to add the write gradients of several layers
+// into the fp32 aggregate with ONE read-modify-write of the aggregate instead of one per layer: at the benchmark's
+// shapes that accumulator traffic (1.2 GB per launch) is what bounds the reduction, not the tensor pipe.
+constexpr int kMaxTnSegments = 4;
+struct TnSegments {
+  CUtensorMap a[kMaxTnSegments];
+  CUtensorMap b[kMaxTnSegments];
+  const int* offsets[kMaxTnSegments];    // [G + 1] padded row offsets of buffer s
+};
 
 constexpr int BM = 128;
 constexpr int BK = 64;      // bf16 elements per k block = one 128-byte swizzle row

@@ -1034,18 +1034,60 @@ def _gg_tn_acc_(a, b, plan: GroupPlan, acc: torch.Tensor) -> None:
                                acc.view(plan.num_groups, a.shape[1], b.shape[1]))
 
 
+class WriteStash:
+    """Token reductions of several writer layers, added to the fp32 aggregate in ONE launch per matrix.
+
+    Adding one layer's gradient costs a read-modify-write of the whole aggregate (1.2 GB at the benchmark's shapes,
+    three times the bytes of the operands), so the reduction ran at the speed of that traffic.  The stash keeps the
+    operands of up to ``limit`` layers alive (about 0.9 GB each) and reduces them together: the group's rows of all
+    stashed layers form one long reduction, and the aggregate is read and written once per ``limit`` layers."""
+
+    def __init__(self, limit: int = 4):
+        self.limit = int(limit)
+        self.items = []
+
+    @property
+    def pending(self) -> int:
+        return len(self.items)
+
+    def add(self, dy02_lr, kp, vp, h_lr, plan: GroupPlan, acc02, acc1) -> None:
+        self.items.append((dy02_lr, kp, vp, h_lr, plan.offsets))
+        if len(self.items) >= self.limit:
+            self.flush(plan.num_groups, acc02, acc1)
+
+    def flush(self, num_groups: int, acc02, acc1) -> None:
+        if not self.items:
+            return
+        ext = cuda_ext(acc02)
+        offs = [it[4] for it in self.items]
+        m02, n02 = self.items[0][0].shape[1], self.items[0][1].shape[1]
+        ext.gg_tn_multi([it[0] for it in self.items], [it[1] for it in self.items], offs, num_groups, torch.float32,
+                        acc02.view(num_groups, m02, n02))
+        m1, n1 = self.items[0][2].shape[1], self.items[0][3].shape[1]
+        ext.gg_tn_multi([it[2] for it in self.items], [it[3] for it in self.items], offs, num_groups, torch.float32,
+                        acc1.view(num_groups, m1, n1))
+        _count(0)
+        self.items = []
+
+
 class _FwWriteGradAcc(torch.autograd.Function):
     """:class:`_FwWriteGrad` that adds its result into running fp32 sums (the aggregate over writer layers)
-    inside the token-reduction GEMM's epilogue instead of materialising per-layer gradients."""
+    inside the token-reduction GEMM's epilogue instead of materialising per-layer gradients.  With a
+    :class:`WriteStash` the reduction is deferred until ``flush`` (or until the stash is full)."""
 
     @staticmethod
-    def forward(ctx, kp, vp, lrp, w02, w1, plan, acc02, acc1):
+    def forward(ctx, kp, vp, lrp, w02, w1, plan, acc02, acc1, stash=None, flush=True):
         ctx.save_for_backward(kp, vp, lrp, w02, w1)
         ctx.plan = plan
         with torch.no_grad():
             dy02_lr, h_lr, _ = _write_inner(kp, vp, lrp, w02, w1, plan, False)
-            _gg_tn_acc_(dy02_lr, kp, plan, acc02)
-            _gg_tn_acc_(vp, h_lr, plan, acc1)
+            if stash is None:
+                _gg_tn_acc_(dy02_lr, kp, plan, acc02)
+                _gg_tn_acc_(vp, h_lr, plan, acc1)
+            else:
+                stash.add(dy02_lr, kp.contiguous(), vp.contiguous(), h_lr, plan, acc02, acc1)
+                if flush:
+                    stash.flush(plan.num_groups, acc02, acc1)
         ctx.mark_dirty(acc02, acc1)
         return acc02, acc1
 
@@ -1053,7 +1095,7 @@ class _FwWriteGradAcc(torch.autograd.Function):
     def backward(ctx, c02, c1):
         grads = _FwWriteGrad.backward(ctx, c02.reshape(ctx.plan.num_groups, *c02.shape[-2:]),
                                       c1.reshape(ctx.plan.num_groups, *c1.shape[-2:]))
-        return (*grads, c02, c1)
+        return (*grads, c02, c1, None, None)
 
 
 def fw_write_grad(kp, vp, lrp, w02, w1, plan: GroupPlan):
@@ -1074,14 +1116,27 @@ def _fw_write_kernel_ok(kp, vp, w02, w1) -> bool:
             and kp.shape[1] % 128 == 0)
 
 
-def fw_write_grad_accumulate(kp, vp, lrp, w02, w1, plan: GroupPlan, acc02: torch.Tensor, acc1: torch.Tensor):
+def write_stash_for(acc02: torch.Tensor) -> Optional[WriteStash]:
+    """A stash for the aggregate ``acc02`` when the kernel path will serve it (see :class:`WriteStash`)."""
+    limit = int(os.environ.get("UTTT_B200_WRITE_STASH", "4"))
+    if limit > 1 and acc02.is_cuda and acc02.dtype == torch.float32 and _kernel("gg_tn_multi", acc02) is not None:
+        return WriteStash(min(limit, 4))
+    return None
+
+
+def fw_write_grad_accumulate(kp, vp, lrp, w02, w1, plan: GroupPlan, acc02: torch.Tensor, acc1: torch.Tensor,
+                             stash: Optional[WriteStash] = None, flush: bool = True):
     """acc02 += G02, acc1 += G1 (see :func:`fw_write_grad`); returns the updated sums.
 
-    On the GPU the sums are updated in place by the GEMM epilogue; elsewhere new tensors are returned.
+    On the GPU the sums are updated in place by the GEMM epilogue; elsewhere new tensors are returned.  With a
+    ``stash`` the additions of several calls are fused into one launch: the sums are complete only after a call
+    with ``flush=True`` (the last writer layer).
     """
     if _fw_write_kernel_ok(kp, vp, w02, w1) and acc02.dtype == torch.float32 and acc02.is_contiguous() \
             and acc1.is_contiguous():
-        return _FwWriteGradAcc.apply(kp, vp, lrp.float().contiguous(), w02, w1, plan, acc02, acc1)
+        return _FwWriteGradAcc.apply(kp, vp, lrp.float().contiguous(), w02, w1, plan, acc02, acc1, stash, flush)
+    if stash is not None and stash.pending:
+        stash.flush(plan.num_groups, acc02, acc1)
     g02, g1 = fw_write_grad(kp, vp, lrp, w02, w1, plan)
     return acc02 + g02.view_as(acc02), acc1 + g1.view_as(acc1)
 
