@@ -1182,11 +1182,11 @@ def test_training_step_is_reproducible_run_to_run():
         assert abs(a - b_) <= 2e-4 * abs(a), (runs[0][0], runs[1][0])
     for k, v in runs[0][1].items():
         w = runs[1][1][k]
-        # fp32 masters after two AdamW steps: update size lr = 1e-3; a differing sign of a near-zero gradient moves
-        # an element by at most 2 lr
+        # fp32 masters after two AdamW steps: update size lr = 1e-3 per step; a differing sign of a near-zero
+        # gradient moves an element by at most 2 lr per step
         # Gradients that are sums over all tokens with heavy cancellation (norm weights, biases) move by a few
         # percent from those flips; with lr = 1e-3 that is ~1e-5 on a master, against ~1e-3 if a kernel had read
         # data that was not there yet.
         diff = (v - w).abs()
-        assert float(diff.max()) <= 2.5e-3, (k, float(diff.max()))
+        assert float(diff.max()) <= 4.5e-3, (k, float(diff.max()))
         assert float(diff.mean()) <= 1.5e-4, (k, float(diff.mean()))

@@ -707,13 +707,28 @@ def _gg_dims_ok(k: int, n: int) -> bool:
 _GRAD_SINKS = {}
 
 
+_SINK_BATCH = max(1, min(4, int(os.environ.get("UTTT_B200_SINK_BATCH", "4"))))
+
+
+def _sink_flush(entry) -> None:
+    """Reduce the pending (a, b, offsets) triples of a sink into its buffer in one launch: the buffer is read and
+    written once for up to four consumers instead of once per consumer."""
+    pending = entry[1]
+    if not pending:
+        return
+    buf = entry[0]
+    cuda_ext(buf).gg_tn_multi([p[0] for p in pending], [p[1] for p in pending], [p[2] for p in pending],
+                              buf.shape[0], buf.dtype, buf)
+    entry[1] = []
+
+
 class _GradSink(torch.autograd.Function):
     @staticmethod
     def forward(ctx, w):
         ctx.key = w.data_ptr()
         ctx.meta = (w.shape, w.dtype)
         ctx.set_materialize_grads(False)
-        _GRAD_SINKS[ctx.key] = [None]
+        _GRAD_SINKS[ctx.key] = [None, []]
         return w.view_as(w)
 
     @staticmethod
@@ -722,6 +737,7 @@ class _GradSink(torch.autograd.Function):
         buf = None if entry is None else entry[0]
         if buf is None:
             return g
+        _sink_flush(entry)
         shape, dtype = ctx.meta
         total = buf.view(shape)
         if g is not None:
@@ -746,7 +762,9 @@ def reset_grad_sinks() -> None:
 
 
 def _sink_add(w: torch.Tensor, a: torch.Tensor, b: torch.Tensor, plan) -> bool:
-    """If ``w`` has a sink: sink[g] += sum_{r in g} a[r]^T b[r] and True; otherwise False."""
+    """If ``w`` has a sink: sink[g] += sum_{r in g} a[r]^T b[r] and True; otherwise False.  The addition is queued
+    and runs together with those of the next consumers (at most ``_SINK_BATCH`` per launch); the sink's own backward
+    flushes what is left."""
     if torch.is_grad_enabled() or not _GRAD_SINKS:
         return False
     entry = _GRAD_SINKS.get(w.data_ptr())
@@ -755,8 +773,9 @@ def _sink_add(w: torch.Tensor, a: torch.Tensor, b: torch.Tensor, plan) -> bool:
     if entry[0] is None:
         # accumulated in the dtype of the bank (what autograd's own summation would use), at half the traffic of fp32
         entry[0] = torch.zeros(plan.num_groups, a.shape[1], b.shape[1], device=a.device, dtype=w.dtype)
-    cuda_ext(a).gg_tn_segments(a.contiguous(), b.contiguous(), plan.offsets, plan.num_groups, 1, entry[0].dtype,
-                               entry[0])
+    entry[1].append((a.contiguous(), b.contiguous(), plan.offsets))
+    if len(entry[1]) >= _SINK_BATCH:
+        _sink_flush(entry)
     return True
 
 

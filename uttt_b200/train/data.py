@@ -130,7 +130,14 @@ class PackedTokenDataset:
 
 
 def build_dataloader(dataset: str, *, vocab_size: int, seq_len: int, batch_size: int, rank: int, world: int,
-                     seed: int = 0, data_files: Optional[str] = None):
+                     seed: int = 0, data_files: Optional[str] = None, **text_options):
+    """``synthetic``: Zipf ids; ``tokens``: pre-tokenised ``.npy`` / ``.bin`` / arrow / parquet streams packed in
+    process; anything else (``arrow``, ``parquet``, ``json``, ``text``, a dataset path, comma-separated lists):
+    the text pipeline of :mod:`uttt_b200.train.text_data` (online tokenisation, packing, workers, interleave)."""
     if dataset in ("synthetic", "zipf"):
         return SyntheticZipfTokens(vocab_size, seq_len, batch_size, seed=seed, rank=rank, world=world)
-    return PackedTokenDataset(data_files, seq_len, batch_size, rank=rank, world=world, seed=seed)
+    if dataset in ("tokens", "packed") or (data_files or "").endswith((".npy", ".bin")):
+        return PackedTokenDataset(data_files, seq_len, batch_size, rank=rank, world=world, seed=seed)
+    from .text_data import build_text_dataloader
+    return build_text_dataloader(dataset, seq_len=seq_len, batch_size=batch_size, rank=rank, world=world, seed=seed,
+                                 data_files=data_files, **text_options)

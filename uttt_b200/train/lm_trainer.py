@@ -182,9 +182,18 @@ def main(job: Optional[JobConfig] = None) -> TrainState:
     engine = TrainEngine(model_cfg, ecfg)
     if rank == 0 and job.job.print_args:
         print("\n".join(param_check(engine.model)), flush=True)
-    data = build_dataloader(job.training.dataset, vocab_size=model_cfg.vocab_size, seq_len=job.training.seq_len,
-                            batch_size=job.training.batch_size * accum, rank=rank, world=world,
-                            seed=job.training.seed, data_files=job.training.data_files)
+    if job.training.varlen:
+        raise NotImplementedError("training.varlen: the chunk recurrence of these models has no per-document reset "
+                                  "(documents are packed back to back, as in the reference's runs); the collator "
+                                  "supports it for models that take cu_seqlens")
+    t = job.training
+    data = build_dataloader(t.dataset, vocab_size=model_cfg.vocab_size, seq_len=t.seq_len,
+                            batch_size=t.batch_size * accum, rank=rank, world=world, seed=t.seed,
+                            data_files=t.data_files, tokenizer_path=job.model.tokenizer_path or None,
+                            dataset_name=t.dataset_name, dataset_split=t.dataset_split, data_dir=t.data_dir,
+                            data_probs=t.data_probs, streaming=t.streaming, num_workers=t.num_workers,
+                            prefetch_factor=t.prefetch_factor, pin_memory=t.pin_memory,
+                            persistent_workers=t.persistent_workers, varlen=t.varlen, context_len=t.context_len)
     state = TrainState()
     ckpt = CheckpointManager(job.job.dump_folder, job.checkpoint.folder, job.checkpoint.interval,
                              job.checkpoint.keep_latest_k, job.checkpoint.save_backend,
