@@ -160,3 +160,35 @@ def test_router_types_and_small_ops_on_cpu():
     assert torch.equal(out, emb.weight[ids])
     out.sum().backward()
     assert float(emb.weight.grad[3].abs().sum()) == 0.0 and float(emb.weight.grad[1].sum()) == 4 * 8
+
+
+def test_pool_statistics_are_reported_on_their_interval(monkeypatch):
+    """The `moe/*` statistics of the reference trainer: usage, dead experts, entropy, selected-weight percentiles."""
+    import math
+    import torch
+    from uttt_b200.config import named_config
+    from uttt_b200.models import build_model
+    from uttt_b200.models import moe_stats as ms
+    cfg = named_config("tiny-uttt-moe", memory_num_active_experts=2)
+    model = build_model(cfg).train()
+    ids = torch.randint(0, cfg.vocab_size, (2, 256), generator=torch.Generator().manual_seed(0))
+    monkeypatch.setenv("UTTT_MOE_STATS_INTERVAL", "5")
+    monkeypatch.setenv("FLAME_TRAIN_STEP", "3")
+    assert "moe" not in model(input_ids=ids, labels=ids).moe_stats
+    monkeypatch.setenv("FLAME_TRAIN_STEP", "10")
+    out = model(input_ids=ids, labels=ids)
+    moe = out.moe_stats["moe"]
+    e = cfg.memory_num_experts
+    for prefix in ("apply", "update"):
+        assert 0.0 <= float(moe[f"{prefix}_freq_min"]) <= 1.0 / e <= float(moe[f"{prefix}_freq_max"]) <= 1.0
+        assert 0.0 < float(moe[f"{prefix}_entropy_ratio"]) <= 1.0 + 1e-6
+        assert 0.0 <= float(moe[f"{prefix}_router_entropy"]) <= math.log(e) + 1e-5
+        lo, p50, p95, hi = (float(moe[f"{prefix}_selected_weight_{k}"]) for k in ("min", "p50", "p95", "max"))
+        assert 0.0 <= lo <= p50 <= p95 <= hi <= 1.0
+    out.loss.backward()                                            # the recompute pass must not collect again
+    assert all(layer.route_stats is None for layer in model.model.layers)
+    # usage statistics from known counts: one dead expert out of four
+    counts = torch.tensor([[[10.0, 10.0, 20.0, 0.0]]])
+    u = ms.expert_usage_stats(counts, 4, "x")
+    assert float(u["x_dead_frac_0p25"]) == 0.25 and float(u["x_freq_max_over_uniform"]) == 2.0
+    assert float(ms.expert_usage_stats(torch.zeros(1, 1, 4), 4, "x")["x_freq_max"]) == 0.0

@@ -35,6 +35,8 @@ def _batch(b=2, v=4):
                                                          router_share_mode="per_layer", use_muon=True)),
     ("uttt_nvs.models.uttt_moe_block.MemoryModel", dict(aggregate_write=False)),
     ("uttt_nvs.models.uttt_dense_block.MemoryModel", {}),
+    ("uttt_nvs.models.uttt_dense_partitioned.MemoryModel", dict(num_shared_pools=2, fw_inter_multi=2)),
+    ("uttt_nvs.models.uttt_moe_partitioned.MemoryModel", dict(num_shared_pools=2)),
     ("uttt_nvs.models.transformer_block.TransformerModel", {}),
     ("uttt_nvs.models.deltanet_block.DeltaNetModel", {}),
     ("uttt_nvs.models.gated_deltanet_block.GatedDeltaNetModel", {}),
@@ -256,3 +258,28 @@ def test_debug_helpers_and_trace_ranges():
     finally:
         trace.enable(False)
     assert not trace.enabled()
+
+
+def test_checkpoint_grouping_and_sweep_do_not_change_the_numbers():
+    """`apply_ckpt_group` and `update_ckpt_sweep` only change where activations are recomputed: same loss and the
+    same gradients as the default schedule; invalid group sizes are rejected; master offload is a no-op on CPU."""
+    batch = _batch()
+    results = []
+    for params in (dict(), dict(apply_ckpt_group=2), dict(update_ckpt_sweep=True),
+                   dict(apply_ckpt_group=2, update_ckpt_sweep=True, offload_master_states=True)):
+        torch.manual_seed(0)
+        model = LVSMModel(_cfg(**params))
+        out = model(batch)
+        out["loss_metrics"]["loss"].backward()
+        results.append((float(out["loss_metrics"]["loss"]),
+                        {n: p.grad.clone() for n, p in model.named_parameters() if p.grad is not None}))
+    for loss, grads in results[1:]:
+        assert loss == pytest.approx(results[0][0], rel=1e-6)
+        for n, g in results[0][1].items():
+            torch.testing.assert_close(grads[n], g, rtol=1e-4, atol=1e-6, msg=n)
+    with pytest.raises(ValueError):
+        LVSMModel(_cfg(apply_ckpt_group=3))
+    with pytest.raises(ValueError):
+        LVSMModel(_cfg(aggregate_write=False, offload_master_states=True))
+    with pytest.raises(NotImplementedError):
+        LVSMModel(_cfg(use_shared_expert=True))

@@ -71,6 +71,7 @@ class MoEBlock(nn.Module):
         self.mlp_norm = RMSNorm(d, eps=config.norm_eps)
         self.mlp = GatedMLP(d, config.mlp_intermediate_size)
         self.ep = None            # expert-parallel handle, set by the model
+        self.route_stats = None   # (reads, writes) RouteStats while the model collects pool statistics
 
     # -------------------------------------------------------------------------- read
     def forward(self, h, k_hist, v_hist, w02, w1, router, bias, offset: int):
@@ -89,6 +90,8 @@ class MoEBlock(nn.Module):
             mem = self.memory
             q_rows = mem.head_rows(mem.prep_query(q_flat, offset))
             routing = fw.route_rows(q_rows, router, bias, cfg, getattr(cfg, "memory_bias_in_logits", False), self.ep)
+            if self.route_stats is not None:          # set by the model for the first pass of a statistics step
+                self.route_stats[0].add(q_rows, router, routing.weights)
             y = fw.pool_read(q_rows, w02, w1, routing)
             mem_out = mem.finish_read(y, x_mem_in).to(attn_out.dtype)
             lb_probs, lb_counts = routing.prob_sum, routing.counts
@@ -120,6 +123,8 @@ class MoEBlock(nn.Module):
         v_rows = mem.head_rows(mem.prep_value(v_flat))
         route_in = v_rows if cfg.memory_router_from_v else k_rows
         routing = fw.route_rows(route_in, router, bias, cfg, getattr(cfg, "memory_bias_in_logits", False), self.ep)
+        if self.route_stats is not None:
+            self.route_stats[1].add(route_in, router, routing.weights)
         g02, g1 = fw.pool_raw_grad(k_rows, v_rows, lr_rows, w02, w1, routing, acc=acc)
         m = mem.momentum_coeff(x_in)
         return g02, g1, m, routing.prob_sum, routing.counts
@@ -492,6 +497,13 @@ class UTTTMoEModel(nn.Module):
                 and torch.is_grad_enabled())
         if sink:
             ops.reset_grad_sinks()
+        # pool statistics every N optimizer steps (models/moe_stats.py); collected in this pass only, not when
+        # backward recomputes a region
+        from . import moe_stats as ms
+        collect = cfg.use_memory_block and self.num_experts > 1 and self.training and ms.stats_enabled()
+        routes = (ms.RouteStats(), ms.RouteStats()) if collect else None
+        for layer in self.layers:
+            layer.route_stats = routes
         for start in range(0, seq_len, chunk):
             end = min(start + chunk, seq_len)
             h = inputs_embeds[:, start:end]
@@ -526,6 +538,8 @@ class UTTTMoEModel(nn.Module):
                         states, up, uc = self._chunk_write(states, feats, start)
                     update_probs = update_probs + up
                     update_counts = update_counts + uc
+        for layer in self.layers:
+            layer.route_stats = None
         hidden = self.norm(torch.cat(outputs, dim=1))
         lb_loss = hidden.new_zeros((), dtype=torch.float32)
         stats = None
@@ -538,6 +552,9 @@ class UTTTMoEModel(nn.Module):
             self._store_loss_free_counts(apply_counts, update_counts)
             stats = {"apply_lb": apply_lb.detach(), "update_lb": update_lb.detach(),
                      "apply_counts": apply_counts.detach(), "update_counts": update_counts.detach()}
+            if collect:
+                stats["moe"] = ms.build_moe_stats(self, apply_lb, update_lb, lb_loss, apply_counts, update_counts,
+                                                  routes[0], routes[1])
         return hidden, lb_loss, stats
 
 

@@ -185,12 +185,15 @@ class MemoryModel(nn.Module):
             raise ValueError("aggregate_write=True is only supported with pool_mode='shared'.")
         if offload_master_states and not aggregate_write:
             raise ValueError("offload_master_states=True requires aggregate_write=True")
+        if int(apply_ckpt_group) < 1 or layers % int(apply_ckpt_group) != 0:
+            raise ValueError(f"apply_ckpt_group={apply_ckpt_group} must divide the number of layers ({layers})")
         self.v_gap = v_gap
         self.lb_alpha = load_balancing_loss_alpha
         self.pool_mode, self.router_share_mode, self.aggregate_write = pool_mode, router_share_mode, aggregate_write
         self.num_experts = num_experts
         self.apply_ckpt_group, self.update_ckpt_sweep = int(apply_ckpt_group), bool(update_ckpt_sweep)
         self.offload_master_states = bool(offload_master_states)
+        self.offload_bytes, self.offload_copies = 0, 0          # cumulative, as the reference's counters
         head_dim = fw_head_dim if fw_head_dim is not None else dim
         inter = int(head_dim * fw_inter_multi)
 
@@ -229,6 +232,20 @@ class MemoryModel(nn.Module):
             return checkpoint(fn, *args, use_reentrant=False, preserve_rng_state=False)
         return fn(*args)
 
+    def _master_offload(self):
+        """`offload_master_states`: the fp32 master copies that autograd keeps per view-chunk for the update's backward
+        wait in pinned host memory between forward and backward (uttt_moe_block.py:24-107)."""
+        import contextlib
+        from ..utils.activation_offload import offload_activations
+
+        @contextlib.contextmanager
+        def scope():
+            with offload_activations(min_bytes=4 << 20, enabled=self.offload_master_states, fp32_only=True) as off:
+                yield off
+            self.offload_bytes += off.bytes_offloaded
+            self.offload_copies += off.tensors_offloaded
+        return scope()
+
     def init_states(self, batch: int, dtype) -> List[fw.PoolState]:
         if self.pool_mode == "shared":
             return [_unit_rows_state(self.pool_w0, self.pool_w1, self.pool_w2, batch, dtype)]
@@ -254,13 +271,29 @@ class MemoryModel(nn.Module):
             xi = x[:, start:end]
             mem_ins, outs = [], []
             probs_l, counts_l = [], []
-            for i, block in enumerate(self.blocks):
-                st = states[0] if shared else states[i]
-                xi, mem_in, p, c = self._ckpt(block, xi, st.w02, st.w1, self._router(i))
-                mem_ins.append(mem_in)
-                outs.append(xi)
-                probs_l.append(p)
-                counts_l.append(c)
+            # `apply_ckpt_group` consecutive blocks share one recompute region: fewer, larger regions (the reference
+            # counts 528 -> ceil(24 / K) * 22 regions per step for its large model, uttt_moe_block.py:850-858)
+            k_grp = self.apply_ckpt_group
+            for g0 in range(0, n, k_grp):
+                idx = list(range(g0, g0 + k_grp))
+
+                def _group(x_in, *ws, _idx=idx):
+                    res = []
+                    for j, bi in enumerate(_idx):
+                        x_in, m_in, p_, c_ = self.blocks[bi](x_in, ws[3 * j], ws[3 * j + 1], ws[3 * j + 2])
+                        res += [x_in, m_in, p_, c_]
+                    return tuple(res)
+                ws = []
+                for bi in idx:
+                    st = states[0] if shared else states[bi]
+                    ws += [st.w02, st.w1, self._router(bi)]
+                res = self._ckpt(_group, xi, *ws)
+                for j in range(k_grp):
+                    xi, mem_in, p, c = res[4 * j:4 * j + 4]
+                    mem_ins.append(mem_in)
+                    outs.append(xi)
+                    probs_l.append(p)
+                    counts_l.append(c)
             ap = ap + torch.stack(probs_l)
             ac = ac + torch.stack(counts_l)
             outputs.append(xi)
@@ -293,6 +326,22 @@ class MemoryModel(nn.Module):
 
         if shared and self.aggregate_write:
             st = states[0]
+            if not self.update_ckpt_sweep:
+                # one recompute region per layer's raw gradient; the update itself runs outside them.  The default
+                # of the reference; `update_ckpt_sweep` trades 264 regions for 11 at +743 MiB on its large model
+                # (uttt_moe_block.py:850-861).
+                a02, a1 = torch.zeros_like(st.m02), torch.zeros_like(st.m1)
+                ps, cs = [], []
+                for i, block in enumerate(self.blocks):
+                    def _raw(k_in, v_in, w02, w1, _b=block, _i=i):
+                        return _b.memory.raw_grad(k_in, norm_v(v_in), w02, w1, self._router(_i), keep_mask=keep)
+                    g02, g1, p, c = self._ckpt(_raw, mem_ins[i], pre_vs[i], st.w02, st.w1)
+                    a02, a1 = a02 + g02, a1 + g1
+                    ps.append(p)
+                    cs.append(c)
+                with self._master_offload():
+                    new = apply_unit_update(a02, a1, st, self.blocks[0].memory.use_muon, dt)
+                return [new], torch.stack(ps), torch.stack(cs)
 
             def _agg(w02, w1, m02, m1, *feats):
                 a02, a1 = torch.zeros_like(m02), torch.zeros_like(m1)
@@ -306,7 +355,8 @@ class MemoryModel(nn.Module):
                                         self.blocks[0].memory.use_muon, dt)
                 return new.w02, new.w1, new.m02, new.m1, torch.stack(ps), torch.stack(cs)
 
-            out = self._ckpt(_agg, st.w02, st.w1, st.m02, st.m1, *mem_ins, *pre_vs)
+            with self._master_offload():
+                out = self._ckpt(_agg, st.w02, st.w1, st.m02, st.m1, *mem_ins, *pre_vs)
             return [fw.PoolState(out[0], out[1], out[2], out[3], None, None)], out[4], out[5]
 
         new_states = list(states)
@@ -331,10 +381,13 @@ class PartitionedMemoryModel(nn.Module):
     """Depth-contiguous groups of blocks, each group with its own shared pool; ``num_experts`` is the total
     expert budget split evenly over the groups (uttt_nvs/models/uttt_moe_partitioned.py:10-462)."""
 
-    def __init__(self, layers: int, dim: int, num_partitions: int = 2, num_experts: int = 4, **kwargs):
+    def __init__(self, layers: int, dim: int, num_partitions: Optional[int] = None, num_experts: int = 4,
+                 num_shared_pools: Optional[int] = None, **kwargs):
         super().__init__()
+        # `num_shared_pools` is the reference's name of the option
+        num_partitions = int(num_shared_pools if num_shared_pools is not None else (num_partitions or 2))
         if layers % num_partitions or num_experts % num_partitions:
-            raise ValueError("layers and num_experts must be divisible by num_partitions")
+            raise ValueError("layers and num_experts must be divisible by the number of pools")
         kwargs.setdefault("pool_mode", "shared")
         self.parts = nn.ModuleList([MemoryModel(layers // num_partitions, dim, num_experts=num_experts // num_partitions,
                                                 **kwargs) for _ in range(num_partitions)])
@@ -368,6 +421,28 @@ class DenseMemoryModel(MemoryModel):
 
     def _router(self, i: int) -> torch.Tensor:
         return self._no_router
+
+
+class DensePartitionedMemoryModel(nn.Module):
+    """Depth-contiguous groups of blocks, each group with its own shared dense state of width ``fw_inter_multi``
+    (uttt_nvs/models/uttt_dense_partitioned.py:22-212): between one state for the whole stack (uTTT-Dense) and one
+    per block (TTT-Dense)."""
+
+    def __init__(self, layers: int, dim: int, num_shared_pools: int = 2, **kwargs):
+        super().__init__()
+        pools = int(num_shared_pools)
+        if pools < 1 or layers % pools:
+            raise ValueError("layers must be divisible by num_shared_pools")
+        kwargs.pop("pool_mode", None)
+        self.parts = nn.ModuleList([DenseMemoryModel(layers // pools, dim, shared=True, **kwargs) for _ in range(pools)])
+
+    def forward(self, x, info):
+        lb_total = x.new_zeros((), dtype=torch.float32)
+        infos: List[Any] = []
+        for part in self.parts:              # group g's output sequence feeds group g + 1 over the whole schedule
+            x, lb, infos = part(x, info)
+            lb_total = lb_total + lb
+        return x, lb_total, infos
 
 
 class TransformerBlocks(nn.Module):

@@ -30,7 +30,7 @@ _CLASS_ALIASES = {
     "uttt_nvs.models.uttt_moe_block.MemoryModel": nvs_blocks.MemoryModel,
     "uttt_nvs.models.uttt_moe_partitioned.MemoryModel": nvs_blocks.PartitionedMemoryModel,
     "uttt_nvs.models.uttt_dense_block.MemoryModel": nvs_blocks.DenseMemoryModel,
-    "uttt_nvs.models.uttt_dense_partitioned.MemoryModel": nvs_blocks.DenseMemoryModel,
+    "uttt_nvs.models.uttt_dense_partitioned.MemoryModel": nvs_blocks.DensePartitionedMemoryModel,
     "uttt_nvs.models.ttt_dense_block.MemoryModel": nvs_blocks.DenseMemoryModel,
     "uttt_nvs.models.transformer_block.TransformerModel": nvs_blocks.TransformerBlocks,
     "uttt_nvs.models.deltanet_block.DeltaNetModel": nvs_blocks.DeltaNetBlocks,

@@ -35,12 +35,12 @@ def lm_shapes(scale: str) -> Dict[str, Dict[str, Any]]:
         "ttt_moe_lb": {**base, **MOE, **dict(model_type="ttt_moe_lb", memory_pool_mode="per_layer",
                                              memory_update_aggregate_write=False,
                                              memory_aggregate_momentum_mode="none", memory_num_experts=4,
-                                             memory_lb_scope="layer", memory_loss_free_update_rate=1e-3)},
+                                             memory_lb_scope="layer", memory_loss_free_update_rate=1e-5)},
         "ttt_moe_no_lb": {**base, **MOE, **dict(model_type="ttt_moe_no_lb", memory_pool_mode="per_layer",
                                                 memory_update_aggregate_write=False,
                                                 memory_aggregate_momentum_mode="none", memory_num_experts=4,
                                                 memory_lb_scope="layer", memory_lb_mode="loss",
-                                                memory_lb_loss_alpha=0.01)},
+                                                memory_lb_loss_alpha=0.0)},
         "ttt_dense": dict(base, model_type="ttt_dense", fw_num_heads=4, fw_inter_multi=1, w0_w2_low_rank=0),
         "lact": dict(base, model_type="lact_swiglu", num_lact_heads=4, inter_multi=1, lact_chunk_size=4096),
         "transformer": dict(base, model_type="transformer", use_memory_block=False, window_size=None),
@@ -156,6 +156,25 @@ def nvs_configs() -> Dict[str, Dict[str, Any]]:
         for r in (2, 4, 8):
             out[f"dense/{data}/uttt_dense_r{r}"] = nvs_yaml(f"uttt_dense_r{r}_{data}", dense, dict(
                 attn_head_dim=64, fw_head_dim=64, inter_multi=3, fw_inter_multi=r, use_muon=False, l2_norm=True))
+        # the released studies, under the names of the reference's files
+        dense_base = dict(attn_head_dim=64, fw_head_dim=64, inter_multi=3, fw_inter_multi=1, use_muon=False, l2_norm=True)
+        for e in (32, 64):
+            for k in (1, 2, 4, 8):
+                out[f"width/{data}/uttt_moe_e{e}a{k}"] = nvs_yaml(f"uttt_moe_e{e}a{k}_{data}", moe,
+                                                                 dict(base, num_experts=e, num_active_experts=k))
+            out[f"topology/{data}/uttt_moe_e{e}a1"] = nvs_yaml(f"uttt_moe_e{e}a1_{data}", moe, dict(base, num_experts=e))
+            for pools in (2, 4):
+                out[f"topology/{data}/uttt_moe_p{pools}_e{e}"] = nvs_yaml(
+                    f"uttt_moe_p{pools}_e{e}_{data}", "uttt_nvs.models.uttt_moe_partitioned.MemoryModel",
+                    dict(base, num_experts=e, num_shared_pools=pools))
+        for width, pools in ((1, 2), (1, 4), (2, 4), (4, 2)):
+            out[f"topology/{data}/uttt_dense_w{width}_p{pools}"] = nvs_yaml(
+                f"uttt_dense_w{width}_p{pools}_{data}", "uttt_nvs.models.uttt_dense_partitioned.MemoryModel",
+                dict(dense_base, fw_inter_multi=width, num_shared_pools=pools))
+        out[f"dense/{data}/uttt_dense_r1"] = nvs_yaml(f"uttt_dense_r1_{data}", dense, dict(dense_base))
+        out[f"schedule/{data}/uttt_moe_e64a1"] = nvs_yaml(f"uttt_moe_e64a1_{data}", moe, dict(base))
+        out[f"schedule/{data}/uttt_moe_e64a1_chained"] = nvs_yaml(f"uttt_moe_e64a1_chained_{data}", moe,
+                                                                 dict(base, aggregate_write=False))
         out[f"schedule/{data}/uttt_moe_4in2out"] = nvs_yaml(f"uttt_moe_4in2out_{data}", moe, dict(base), views=6)
         out[f"schedule/{data}/uttt_moe_4in2out"]["model"].update(view_layout="inputs_then_targets", num_input_views=4)
         out[f"transformer/{data}/transformer"] = nvs_yaml(
@@ -165,10 +184,11 @@ def nvs_configs() -> Dict[str, Dict[str, Any]]:
         out[f"reference/{data}/gated_deltanet"] = nvs_yaml(
             f"gated_deltanet_{data}", "uttt_nvs.models.gated_deltanet_block.GatedDeltaNetModel",
             dict(attn_head_dim=64, inter_multi=3))
-    big = dict(base, num_experts=96, fw_head_dim=192, fw_inter_multi=2, attn_head_dim=64)
+    big = dict(base, num_experts=96, fw_head_dim=192, fw_inter_multi=2, attn_head_dim=64, apply_ckpt_group=6)
     for size, batch, total in ((256, 8, 512), (512, 2, 128), (1024, 1, 64)):
-        out[f"scale/obj/uttt_moe_large_{size}"] = nvs_yaml(f"uttt_moe_large_{size}", moe, dict(big), dim=768, layers=24,
-                                                          size=size, batch=batch, total=total)
+        out[f"scale/obj/uttt_moe_large_{size}"] = nvs_yaml(
+            f"uttt_moe_large_{size}", moe, dict(big, offload_master_states=True) if size > 256 else dict(big), dim=768,
+            layers=24, size=size, batch=batch, total=total)
     out["named/uttt_moe_256_4in2out"] = nvs_yaml(
         "uttt_moe_256_4in2out", moe, dict(base, num_experts=16, num_active_experts=2, fw_head_dim=64), dim=768,
         layers=24, size=256, batch=16, total=128, views=6)
@@ -205,6 +225,44 @@ def main() -> None:
             os.makedirs(os.path.dirname(path), exist_ok=True)
             with open(path, "w") as fh:
                 fh.write(config_from_dict(dict(base, **over)).to_json_string())
+    # the released balancing studies, under the names of the reference's files: loss-free update rates for the
+    # layer-local family (expert count / active experts), auxiliary-loss weights for the family without loss-free
+    # balancing, and rate / scope / router-temperature sweeps of the universal pool
+    def rate_tag(r: float) -> str:
+        m, e = f"{r:.0e}".split("e")
+        return f"{m}e{int(e)}"
+    for scale in SCALES:
+        shapes = lm_shapes(scale)
+        small = scale == "124M"
+        named = {}
+        lb_grid = ({(4, 1): (1e-4, 3e-5, 3e-6), (4, 2): (1e-4, 1e-5, 3e-5, 3e-6), (8, 1): (1e-4, 1e-5, 3e-5, 3e-6)}
+                   if small else {(4, 1): (1e-4, 3e-5)})
+        for (e, k), rates in lb_grid.items():
+            for r in rates:
+                named[f"ttt_moe_lb_e{e}a{k}_lossfree_u{rate_tag(r)}"] = dict(
+                    shapes["ttt_moe_lb"], memory_num_experts=e, memory_num_active_experts=k,
+                    memory_loss_free_update_rate=r)
+        for a in ((1e-5, 1e-6) if small else (1e-4, 1e-5, 3e-5)):
+            named[f"ttt_moe_no_lb_e4a1_lb{rate_tag(a)}"] = dict(shapes["ttt_moe_no_lb"], memory_lb_loss_alpha=a)
+        named["ttt_moe_no_lb_e4a2_lb0"] = dict(shapes["ttt_moe_no_lb"], memory_num_active_experts=2)
+        named["ttt_moe_no_lb_e8a1_lb0"] = dict(shapes["ttt_moe_no_lb"], memory_num_experts=8)
+        e = shapes["uttt_moe"]["memory_num_experts"]
+        tail = "agg_poolmean_lr1_full_router_per_layer"
+        if small:
+            grid = [("layer", r, None) for r in (1e-3, 1e-4, 1e-5, 3e-4, 3e-5)] + \
+                   [("pool", r, None) for r in (1e-3, 1e-4, 1e-5, 3e-4)]
+        else:
+            grid = [("pool", r, None) for r in (1e-4, 1e-5, 3e-4, 3e-5)] + \
+                   [("pool", 1e-4, 2), ("pool", 1e-4, 4), ("pool", 3e-4, 2), ("pool", 3e-5, 2)]
+        for scope, r, alpha in grid:
+            name = f"uttt_moe_e{e}a1_lossfree_{scope}_u{rate_tag(r)}" + (f"_alpha{alpha}" if alpha else "") + f"_{tail}"
+            over = dict(memory_lb_scope=scope, memory_loss_free_update_rate=r)
+            if alpha:
+                over["memory_router_alpha"] = float(alpha)
+            named[name] = dict(shapes["uttt_moe"], **over)
+        for name, cfg in named.items():
+            with open(os.path.join(ROOT, "lm", "balancing", scale, f"{name}.json"), "w") as fh:
+                fh.write(config_from_dict(cfg).to_json_string())
     for rel, cfg in nvs_configs().items():
         path = os.path.join(ROOT, "nvs", rel + ".yaml")
         os.makedirs(os.path.dirname(path), exist_ok=True)
@@ -220,11 +278,15 @@ def main() -> None:
                           "view_manifest": "/PATH/TO/MANIFESTS/dl3dv_views_24_seed9595.json", "image_size": 256,
                           "num_scenes": 140}}
     main_entries, tr_entries = [], []
+    seen = set()
     for rel, cfg in sorted(nvs_configs().items()):
         parts = rel.split("/")
         if len(parts) != 3 or parts[1] not in domains or parts[0] in ("scale", "schedule"):
             continue
         ds = domains[parts[1]]
+        if (ds, parts[2]) in seen:           # the same run appears in several studies: one registry entry
+            continue
+        seen.add((ds, parts[2]))
         entry = {"name": f"{ds}/{parts[2]}", "dataset": ds, "config": f"configs/nvs/{rel}.yaml",
                  "checkpoint": f"{ds}/{parts[2]}/ckpt_{steps[ds]:016d}.pt", "paper_model": parts[2],
                  "display_name": parts[2].replace("_", "-"), "checkpoint_impl": parts[2].split("_e")[0], "v_gap": None}

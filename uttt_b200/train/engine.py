@@ -164,6 +164,9 @@ class TrainEngine:
             if n_micro > 1:
                 self.trainer.accumulate_micro_batch()
             self.last_stats = {"ce": out.ce_loss, "lb": out.lb_loss}
+            moe = (getattr(out, "moe_stats", None) or {}).get("moe")
+            if moe:
+                self.last_stats["moe"] = moe
         lr = self.lr_sched.lr()
         stats = self.trainer.step(lr=lr)
         self.lr_sched.step()

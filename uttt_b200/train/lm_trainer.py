@@ -92,6 +92,8 @@ class Metrics:
             for k in ("ce", "lb"):
                 if stats.get(k) is not None:
                     rec[f"loss/{k}"] = float(stats[k])
+            for k, v in (stats.get("moe") or {}).items():          # pool statistics, on their interval
+                rec[f"moe/{k}"] = float(v)
             print(f"step {step:6d}  loss {rec['loss']:.4f}  grad_norm {rec['grad_norm']:.3f}  lr {rec['lr']:.2e}  "
                   f"tps/gpu {tps:,.0f}  mfu {mfu:.1f}%  mem {mem:.1f} GiB", flush=True)
             with open(self.path, "a") as fh:

@@ -16,7 +16,8 @@ import torch
 
 
 class _Offloader:
-    def __init__(self, min_bytes: int, stream: Optional["torch.cuda.Stream"]):
+    def __init__(self, min_bytes: int, stream: Optional["torch.cuda.Stream"], fp32_only: bool = False):
+        self.fp32_only = fp32_only
         self.min_bytes = int(min_bytes)
         self.stream = stream
         self.bytes_offloaded = 0
@@ -25,6 +26,8 @@ class _Offloader:
     def pack(self, t: torch.Tensor):
         if (not t.is_cuda) or isinstance(t, torch.nn.Parameter) or t.numel() * t.element_size() < self.min_bytes:
             return t
+        if self.fp32_only and (t.dtype != torch.float32 or not t.is_contiguous()):
+            return t            # master states only; broadcast views would be materialised at full size
         stream = self.stream or torch.cuda.Stream(t.device)
         self.stream = stream
         host = torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=True)
@@ -52,9 +55,11 @@ class _Offloader:
 
 
 @contextlib.contextmanager
-def offload_activations(min_bytes: int = 1 << 20, stream: Optional["torch.cuda.Stream"] = None, enabled: bool = True):
-    """Context manager; yields the offloader (``bytes_offloaded`` / ``tensors_offloaded`` counters)."""
-    off = _Offloader(min_bytes, stream)
+def offload_activations(min_bytes: int = 1 << 20, stream: Optional["torch.cuda.Stream"] = None, enabled: bool = True,
+                        fp32_only: bool = False):
+    """Context manager; yields the offloader (``bytes_offloaded`` / ``tensors_offloaded`` counters).
+    ``fp32_only`` restricts it to contiguous fp32 tensors (the fast-weight master copies)."""
+    off = _Offloader(min_bytes, stream, fp32_only)
     if not enabled:
         yield off
         return
