@@ -30,8 +30,22 @@ def _unavailable(why: str) -> None:
     print(json.dumps({"impl": "reference", "unavailable": why.replace("\n", " ")[:300]}), flush=True)
 
 
-def _import_reference():
-    if not os.path.isdir(os.path.join(REF_ROOT, "flame", "custom_models", "uttt_moe")):
+# named benchmark shape -> (reference package, its shipped JSON, class prefix, overrides that turn the shipped shape
+# into the named one, metric name)
+MODELS = {
+    "760M-uttt-moe": ("uttt_moe", "760M/uttt_moe.json", "RecurrentLactRefMoeGlobalV45",
+                      dict(num_heads=16, memory_num_experts=32, memory_num_active_experts=2, fw_inter_multi=4,
+                           window_size=2048, chunk_size=2048), "760M uTTT-MoE"),
+    "124M-uttt-moe": ("uttt_moe", "124M/uttt_moe.json", "RecurrentLactRefMoeGlobalV45",
+                      dict(memory_num_experts=16, memory_num_active_experts=2, fw_inter_multi=4, window_size=2048,
+                           chunk_size=2048, memory_lb_mode="loss", memory_lb_loss_alpha=0.01), "124M uTTT-MoE"),
+    "124M-uttt-dense": ("uttt_dense", "124M/uttt_dense_r2.json", "RecurrentLactRefUtttDenseV3",
+                        dict(fw_num_heads=1, window_size=2048, chunk_size=2048), "124M uTTT-Dense"),
+}
+
+
+def _import_reference(package: str = "uttt_moe"):
+    if not os.path.isdir(os.path.join(REF_ROOT, "flame", "custom_models", package)):
         raise FileNotFoundError("baseline/_ref/uttt_llm is missing (copy the reference's uttt_llm tree there)")
     sys.path.insert(0, REF_ROOT)
     for name, path in (("flame", "flame"), ("flame.custom_models", "flame/custom_models")):
@@ -39,11 +53,17 @@ def _import_reference():
             mod = types.ModuleType(name)
             mod.__path__ = [os.path.join(REF_ROOT, path)]
             sys.modules[name] = mod
-    import flame.custom_models.uttt_moe as um
-    return um
+    import importlib
+    return importlib.import_module(f"flame.custom_models.{package}")
 
 
 def run_reference(args) -> None:
+    if args.model == "nvs-uttt-moe":
+        # the view-synthesis half of the reference (uttt_nvs.models.lvsm_moe) imports omegaconf, easydict and lpips
+        # at module level; none of them is installed on this image and nothing can be installed offline
+        _unavailable("the reference's uttt_nvs package needs omegaconf, easydict and lpips, which are not installed "
+                     "on this image (no network to install them)")
+        return
     try:
         _run(args)
     except Exception as exc:  # the contract: say why on one line and exit 0
@@ -73,15 +93,18 @@ def _run(args) -> None:
     dev = torch.device("cuda", local)
     if not dist.is_initialized():
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
-    um = _import_reference()
-    with open(os.path.join(REF_ROOT, "configs", "main", "760M", "uttt_moe.json")) as f:
+    package, shipped, prefix, overrides, metric_name = MODELS[args.model]
+    um = _import_reference(package)
+    with open(os.path.join(REF_ROOT, "configs", "main", shipped)) as f:
         cfgd = json.load(f)
     cfgd.pop("model_type", None)
-    # the named benchmark shape (differs from the shipped JSON): 16 heads, 32 experts of hidden 1536, top-2,
-    # window = chunk = 2048
-    cfgd.update(num_heads=16, memory_num_experts=32, memory_num_active_experts=2, fw_inter_multi=4,
-                window_size=2048, chunk_size=2048, memory_update_backward_mode=args.backward_mode)
-    cfg = um.RecurrentLactRefMoeGlobalV45Config(**cfgd)
+    # the named benchmark shape differs from the shipped JSON (e.g. 760M: 16 heads, 32 experts of hidden 1536, top-2,
+    # window = chunk = 2048)
+    cfgd.update(overrides)
+    if package == "uttt_moe":
+        cfgd.update(memory_update_backward_mode=args.backward_mode)
+    cfg = getattr(um, prefix + "Config")(**cfgd)
+    model_cls = getattr(um, prefix + "ForCausalLM")
     mesh = dist.device_mesh.init_device_mesh("cuda", (world,))
     mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
     seq = args.seq_len
@@ -90,12 +113,12 @@ def _run(args) -> None:
         torch.manual_seed(42)
         try:
             with torch.device(dev):                 # parameters are created on the GPU, not copied from the host
-                model = um.RecurrentLactRefMoeGlobalV45ForCausalLM(cfg)
+                model = model_cls(cfg)
         except torch.OutOfMemoryError:
             raise
         except Exception:                           # a constructor that insists on host tensors: build there, then move
             torch.manual_seed(42)
-            model = um.RecurrentLactRefMoeGlobalV45ForCausalLM(cfg).to(dev)
+            model = model_cls(cfg).to(dev)
         for block in model.model.layers:
             fully_shard(block, mesh=mesh, mp_policy=mp, reshard_after_forward=False)
         fully_shard(model, mesh=mesh, mp_policy=mp, reshard_after_forward=False)
@@ -202,11 +225,11 @@ def _run(args) -> None:
     if rank == 0:
         h2d = host_batches[0]["input_ids"].numel() * host_batches[0]["input_ids"].element_size()
         print(json.dumps({
-            "metric": "train tokens/s, 760M uTTT-MoE 32K ctx", "value": tokens / (ms / 1e3), "unit": "tokens/s",
+            "metric": f"train tokens/s, {metric_name} 32K ctx", "value": tokens / (ms / 1e3), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic Zipf(1.1) token ids, random-init weights", "impl": "reference",
-            "config": {"model": "760M-uttt-moe (reference RecurrentLactRefMoeGlobalV45ForCausalLM)",
+            "config": {"model": f"{args.model} (reference {prefix}ForCausalLM)",
                        "params": n_params, "global_batch": args.per_gpu_batch * world,
                        "per_gpu_batch": args.per_gpu_batch, "micro_batch": micro, "seq_len": seq,
                        "parallelism": f"fsdp{world}", "backward_mode": args.backward_mode,
