@@ -60,7 +60,8 @@ def run_ours(args):
         keep_arg = "0,12" if (args.model == "760M-uttt-moe" and args.micro_batch * args.seq_len <= 4 * 32768) else ""
     keep = tuple(int(i) for i in keep_arg.split(",") if i.strip())
     eng = TrainEngine(cfg, EngineConfig(micro_batch_size=args.micro_batch, lr=1e-3, eps=1e-15, warmup_steps=1024,
-                                        total_steps=40960, seed=42, keep_activation_layers=keep), dev)
+                                        total_steps=40960, seed=42, keep_activation_layers=keep,
+                                        cuda_graph=not args.no_cuda_graph and args.expert_parallel <= 1), dev)
     data = SyntheticZipfTokens(cfg.vocab_size, seq, args.per_gpu_batch, seed=1234, rank=rank, world=world)
     n_params = eng.trainer.num_parameters()
 
@@ -119,7 +120,9 @@ def run_ours(args):
                        "backward_mode": args.backward_mode,
                        "activation_recompute": "per (chunk, layer) and per chunk write" + (
                            f"; layers {list(keep)} keep their activations" if keep else ""),
-                       "cache": "inputs and per-step working set are far larger than L2 (no flush needed)"},
+                       "cache": "inputs and per-step working set are far larger than L2 (no flush needed)",
+                       "cuda_graph": ("forward + backward of a micro-batch replayed as one CUDA graph; optimizer eager"
+                                      if eng._graphs else f"off ({eng.graph_error or 'not requested'})")},
             "clocks": clocks,
             "e2e": {"value": tokens_per_step / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4, "clocks": clocks_e2e,
@@ -225,6 +228,8 @@ def main():
     ap.add_argument("--per-gpu-batch", type=int, default=4)
     ap.add_argument("--micro-batch", type=int, default=int(os.environ.get("UTTT_BENCH_MICRO_BATCH", "4")))
     ap.add_argument("--backward-mode", default="full")
+    ap.add_argument("--no-cuda-graph", action="store_true",
+                    help="launch every kernel of forward + backward from the host instead of replaying a CUDA graph")
     ap.add_argument("--keep-activation-layers", default=os.environ.get("UTTT_BENCH_KEEP_LAYERS", "auto"),
                     help="comma-separated layer indices whose activations are kept instead of recomputed")
     ap.add_argument("--expert-parallel", type=int, default=1,

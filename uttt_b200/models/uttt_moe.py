@@ -344,6 +344,41 @@ class UTTTMoEModel(nn.Module):
         counts.zero_()
         self.memory_loss_free_num_updates.add_(active.long())
 
+    # ------------------------------------------------------------------ host-side decisions (for graph replay)
+    def host_branch_key(self):
+        """The decisions the next training forward takes on the host.  A captured CUDA graph of the step replays
+        the device work of exactly these decisions; ``None`` means the forward must run eagerly (it reads values
+        back for the pool statistics)."""
+        cfg = self.config
+        if not cfg.use_memory_block:
+            return ()
+        from . import moe_stats as ms
+        if self.num_experts > 1 and self.training and ms.stats_enabled():
+            return None
+        branch = 0
+        if self.training and self._loss_free_enabled():
+            steps, warm = self._host_steps, cfg.memory_loss_free_warmup_steps
+            if steps == 0:
+                branch = 1
+            elif steps <= warm:
+                branch = 2
+            elif (steps - warm) % cfg.memory_loss_free_update_interval != 0:
+                branch = 3
+            else:
+                branch = 4
+        return (branch,)
+
+    def host_state(self):
+        return {"host_steps": self._host_steps}
+
+    def load_host_state(self, state) -> None:
+        self._host_steps = int(state["host_steps"])
+
+    def host_step_replayed(self) -> None:
+        """Bookkeeping of one training forward whose device work was replayed from a graph."""
+        if self.training and self.config.use_memory_block and self.num_experts > 1 and self._loss_free_enabled():
+            self._host_steps += 1
+
     @torch.no_grad()
     def _store_loss_free_counts(self, apply_counts: torch.Tensor, update_counts: torch.Tensor) -> None:
         if not self.training or not self._loss_free_enabled():

@@ -10,6 +10,19 @@ namespace uttt {
 extern unsigned long long g_launch_count;
 inline void count_launch(int n = 1) { g_launch_count += (unsigned long long)n; }
 
+// The driver call that encodes a tensor map needs the primary context current on the calling thread, which an
+// autograd worker thread may not have yet.  Done once per thread and device: the call that makes it current is not
+// allowed while a stream is being captured into a graph, and it costs host time on every launch otherwise.
+inline bool ensure_context_current() {
+  thread_local int ready_dev = -1;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  if (ready_dev == dev) return true;
+  if (cudaSetDevice(dev) != cudaSuccess || cudaFree(nullptr) != cudaSuccess) return false;
+  ready_dev = dev;
+  return true;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -332,10 +332,7 @@ static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
 CUtensorMap make_tmap_3d_bf16(const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
                               uint64_t stride2_bytes, uint32_t box0, uint32_t box1) {
   CUtensorMap m;
-  int dev = 0;
-  C10_CUDA_CHECK(cudaGetDevice(&dev));
-  C10_CUDA_CHECK(cudaSetDevice(dev));
-  C10_CUDA_CHECK(cudaFree(nullptr));
+  TORCH_CHECK(ensure_context_current(), "no CUDA context on this thread");
   cuuint64_t dims[3] = {d0, d1, d2};
   cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
   cuuint32_t box[3] = {box0, box1, 1};

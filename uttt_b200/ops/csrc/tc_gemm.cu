@@ -417,13 +417,7 @@ CUtensorMap make_tmap_2d(const void* base, uint64_t rows, uint64_t cols, uint32_
                          bool fp32, bool swizzle64) {
   CUtensorMap m;
   const uint64_t esz = fp32 ? 4 : 2;
-  {
-    // autograd worker threads may not have the primary context current yet; the driver call needs it
-    int dev = 0;
-    C10_CUDA_CHECK(cudaGetDevice(&dev));
-    C10_CUDA_CHECK(cudaSetDevice(dev));
-    C10_CUDA_CHECK(cudaFree(nullptr));
-  }
+  TORCH_CHECK(ensure_context_current(), "no CUDA context on this thread");
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {cols * esz};
   cuuint32_t box[2] = {box_cols, box_rows};

@@ -2,7 +2,7 @@
 
     python -m uttt_b200.ops.microbench [--kernel NAME] [--small] [--iters N]
 
-Kernels: gg_nt, gg_swiglu, gg_write, gg_nn, gg_tn, bmm_nt, swa_fwd, swa_bwd, rms_norm, add_rms_norm, embedding, rope, fw_qk_prep, router, pool_step, plucker,
+Kernels: gg_nt, gg_swiglu, gg_write, gg_nn, gg_tn, bmm_nt, dense, swa_fwd, swa_bwd, rms_norm, add_rms_norm, embedding, rope, fw_qk_prep, router, pool_step, plucker,
 swiglu, permute, patch_decode, frob, fw_write_pw, adamw, ce.  ``--small`` runs one small case
 of the chosen kernel (inputs above L2 size, a few hundred MB on the device) three times, which is what the
 profile summaries under ``profiles/`` were captured from.  Prints one JSON line per case with the achieved
@@ -138,6 +138,16 @@ def run(kernel: str, small: bool, iters: int):
         x = torch.randn(n, d, inter, **bf)
         ms = _time(lambda: F.bmm_nt(x, x), iters, flush)
         rec("bmm_nt[NS X X^T]", ms, flops=2.0 * n * d * d * inter, batch=n)
+    if kernel in ("dense", "all"):
+        # the dense projections of a block (tokens x d -> mlp, mlp -> d, d -> d) on the own batched kernel and on cuBLAS
+        for (m_, k_, n_) in ((8192, 1536, 4096), (8192, 4096, 1536), (8192, 1536, 1536), (8192, 1536, 8192)):
+            x = torch.randn(1, m_, k_, **bf)
+            w = torch.randn(1, n_, k_, **bf) * 0.05
+            ms = _time(lambda: F.bmm_nt(x, w), iters, flush)
+            rec(f"dense NT own [{m_}x{k_} @ {n_}x{k_}^T]", ms, flops=2.0 * m_ * k_ * n_)
+            ms_lib = _time(lambda: torch.mm(x[0], w[0].t()), iters, flush)
+            rec(f"dense NT cuBLAS [{m_}x{k_} @ {n_}x{k_}^T]", ms_lib, flops=2.0 * m_ * k_ * n_,
+                own_over_library=round(ms_lib / ms, 3))
     if kernel in ("swa_fwd", "all"):
         b_, lq, lk, h, hd, win = bsz, 2048, 4096, 16, 96, 2048
         q = torch.randn(b_, lq, h, hd, **bf)

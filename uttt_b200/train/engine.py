@@ -39,6 +39,8 @@ class EngineConfig:
     activation_checkpoint: bool = True
     keep_activation_layers: tuple = ()     # layer indices that skip recomputation (needs spare device memory)
     activation_offload: bool = False       # saved tensors of the forward go to pinned host memory until backward
+    cuda_graph: bool = False               # replay forward + backward of a micro-batch as one CUDA graph
+    cuda_graph_warmup: int = 2             # eager steps before the capture (lazy initialisation happens in them)
 
 
 def init_distributed(backend: Optional[str] = None, timeout_seconds: Optional[float] = None,
@@ -83,6 +85,13 @@ def set_collective_timeout(seconds: float) -> bool:
         return True
     except Exception:
         return False
+
+
+class _StepGraph:
+    """A captured forward + backward: the graph, its static inputs and the output record it refreshes."""
+    graph = None
+    ids = labels = out = None
+    launches = 0
 
 
 class KernelStatusError(RuntimeError):
@@ -133,6 +142,9 @@ class TrainEngine:
         self.step = 0
         self.tokens_seen = 0
         self.last_stats: Dict[str, Any] = {}
+        self._graphs: Dict[Any, "_StepGraph"] = {}
+        self._graph_pool = None
+        self.graph_error: Optional[str] = None     # why graph mode was given up, if it was
 
     # ------------------------------------------------------------------ data movement
     def to_device(self, batch: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
@@ -157,9 +169,12 @@ class TrainEngine:
         n_micro = (bsz + mb - 1) // mb
         total = torch.zeros((), device=self.device, dtype=torch.float32)
         for i in range(n_micro):
-            with self._offload():
-                out = self.model(input_ids=ids_all[i * mb:(i + 1) * mb], labels=labels_all[i * mb:(i + 1) * mb])
-            (out.loss / n_micro).backward()
+            ids, labels = ids_all[i * mb:(i + 1) * mb], labels_all[i * mb:(i + 1) * mb]
+            out = self._replay_forward_backward(ids, labels, n_micro) if self._graph_ready() else None
+            if out is None:
+                with self._offload():
+                    out = self.model(input_ids=ids, labels=labels)
+                (out.loss / n_micro).backward()
             total += out.loss.detach().float() / n_micro
             if n_micro > 1:
                 self.trainer.accumulate_micro_batch()
@@ -175,6 +190,70 @@ class TrainEngine:
         self.last_stats.update(stats)
         self.last_stats["lr"] = lr
         return total
+
+    # ------------------------------------------------------------------ forward + backward as one CUDA graph
+    def _graph_ready(self) -> bool:
+        return (self.cfg.cuda_graph and self.graph_error is None and self.device.type == "cuda"
+                and self.step >= self.cfg.cuda_graph_warmup and self.expert_parallel is None
+                and not self.cfg.activation_offload)
+
+    def _host_branches(self):
+        """What the model's next training forward decides on the host (not on the device): a captured graph is
+        only valid for the decisions it was captured with."""
+        inner = getattr(self.model, "model", self.model)
+        fn = getattr(inner, "host_branch_key", None)
+        return fn() if fn is not None else ()
+
+    def _replay_forward_backward(self, ids: torch.Tensor, labels: torch.Tensor, n_micro: int):
+        """Forward + backward of one micro-batch from a captured graph (captured on first use for this input shape
+        and these host-side decisions).  The step is launch-bound otherwise: tens of thousands of small launches per
+        step keep the host busier than the device.  Returns None when this step has to run eagerly."""
+        branches = self._host_branches()
+        if branches is None:                       # e.g. a statistics step: host-side reads in the forward
+            return None
+        key = (tuple(ids.shape), ids.dtype, n_micro, branches)
+        sg = self._graphs.get(key)
+        if sg is None:
+            try:
+                sg = self._capture(ids, labels, n_micro)
+            except Exception as exc:               # capture refused an operation: stay eager from here on
+                self.graph_error = f"{type(exc).__name__}: {exc}"
+                return None                        # (a failed capture executed nothing: gradients are untouched)
+            self._graphs[key] = sg
+        sg.ids.copy_(ids)
+        sg.labels.copy_(labels)
+        sg.graph.replay()
+        from ..ops import functional as F
+        F._count(sg.launches)
+        inner = getattr(self.model, "model", self.model)
+        done = getattr(inner, "host_step_replayed", None)
+        if done is not None:
+            done()
+        return sg.out
+
+    def _capture(self, ids: torch.Tensor, labels: torch.Tensor, n_micro: int) -> "_StepGraph":
+        from ..ops import functional as F
+        torch.cuda.synchronize(self.device)
+        torch.cuda.empty_cache()                   # the eager steps' cached blocks go back before the graph's pool grows
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        sg = _StepGraph()
+        sg.ids, sg.labels = ids.clone(), labels.clone()
+        sg.graph = torch.cuda.CUDAGraph()
+        inner = getattr(self.model, "model", self.model)
+        host = inner.host_state() if hasattr(inner, "host_state") else None
+        before = F.launch_count()
+        try:
+            with torch.cuda.graph(sg.graph, pool=self._graph_pool):
+                out = self.model(input_ids=sg.ids, labels=sg.labels)
+                (out.loss / n_micro).backward()
+        finally:
+            if host is not None:                   # the capture ran the host side of a step, not the device side
+                inner.load_host_state(host)
+        sg.launches = F.launch_count() - before
+        out.hidden_states = None                   # nothing outside needs the hidden states of a replayed step
+        sg.out = out
+        return sg
 
     def _offload(self):
         from ..utils.activation_offload import offload_activations
