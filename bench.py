@@ -154,7 +154,7 @@ def run_nvs(args):
     cfg = load_config(os.path.join(ROOT, "configs", "nvs", "named", "uttt_moe_256_4in2out.yaml"))
     per_gpu = args.per_gpu_batch if args.per_gpu_batch != 4 else 16
     cfg["training"].update(batch_size_per_gpu=per_gpu, total_batch_size=per_gpu * world, out_dir="/tmp/uttt_nvs_bench",
-                           checkpoint_every=10 ** 9, print_every=10 ** 9, warmup=0)
+                           checkpoint_every=10 ** 9, print_every=10 ** 9, warmup=0, cuda_graph=not args.no_cuda_graph)
     trainer = NVSTrainer(cfg, device=dev)
     views, size = int(cfg["training"]["num_views"]), int(cfg["model"]["image_size"])
     data = SyntheticScenes(per_gpu, views, size, seed=1234, rank=rank)
@@ -204,7 +204,9 @@ def run_nvs(args):
                        "params": trainer.trainer.num_parameters(), "global_batch": scenes, "per_gpu_batch": per_gpu,
                        "views": views, "tokens_per_scene": views * (size // 8) ** 2,
                        "parallelism": f"dp{world}" if world > 1 else "single",
-                       "cache": "inputs and per-step working set are far larger than L2 (no flush needed)"},
+                       "cache": "inputs and per-step working set are far larger than L2 (no flush needed)",
+                       "cuda_graph": ("forward + backward replayed as one CUDA graph; optimizer eager"
+                                      if trainer._graphs else f"off ({trainer.graph_error or 'not requested'})")},
             "clocks": clocks,
             "e2e": {"value": scenes / (ms_e2e / 1e3), "unit": "scenes/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4, "clocks": clocks_e2e,

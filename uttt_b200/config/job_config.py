@@ -37,7 +37,7 @@ _FLAGS: Dict[str, Dict[str, Any]] = {
                      disable_loss_parallel=False, fsdp_reshard_after_forward="default",
                      mixed_precision_param="bfloat16", mixed_precision_reduce="float32", compile=False, gc_freq=50,
                      seed=42, deterministic=False, expected_global_batch_size=None, pin_memory=False,
-                     persistent_workers=False, micro_batch_size=None),
+                     persistent_workers=False, micro_batch_size=None, cuda_graph=False),
     "metrics": dict(log_freq=10, enable_tensorboard=False, disable_color_printing=False, save_tb_folder="tb",
                     save_for_all_ranks=False, enable_wandb=False),
     "experimental": dict(enable_async_tensor_parallel=False, pipeline_parallel_degree=1,
@@ -71,7 +71,8 @@ FLAG_READERS: Dict[str, str] = {
                  "early_step_in_backward: validate",
     "lr_scheduler": "train/lr.py::WarmupDecayLR",
     "training": "lm_trainer.main + train/data.py::build_dataloader; parallel degrees, reshard policy, offload, "
-                "compile, mixed precision: validate; gc_freq, deterministic, seed: lm_trainer.main",
+                "compile, mixed precision: validate; gc_freq, deterministic, seed: lm_trainer.main; cuda_graph: "
+                "train/engine.py (forward + backward replayed as one CUDA graph)",
     "metrics": "lm_trainer.Metrics",
     "experimental": "validate (degrees); expert_parallel_degree: lm_trainer.main -> memory_expert_parallel",
     "checkpoint": "train/checkpoint.py::CheckpointManager (async_mode included)",

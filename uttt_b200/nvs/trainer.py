@@ -155,6 +155,9 @@ class NVSTrainer:
                 self.trainer.load_model_state()
         self.data = self._build_data()
         self.step_times: List[float] = []
+        self._graphs: Dict[Any, Any] = {}
+        self._passes_run = 0                       # of this process (a resumed run also warms up before a capture)
+        self.graph_error: Optional[str] = None
 
     def _build_data(self):
         tr = self.cfg["training"]
@@ -190,14 +193,9 @@ class NVSTrainer:
         t0 = time.time()
         batch = {k: v.to(self.device, non_blocking=True) for k, v in batch.items() if torch.is_tensor(v)}
         self.model.train()
-        result = self.model(batch)
-        loss = result["loss_metrics"]["loss"]
-        vote = torch.isfinite(loss.detach()).float()
-        if self.world > 1:
-            dist.all_reduce(vote, op=dist.ReduceOp.MIN)       # every rank skips together
-        (loss * vote / self.accum).backward()
+        loss, psnr, vote = self._forward_backward(batch)
         self.fwdbwd_step += 1
-        stats: Dict[str, Any] = {"loss": loss.detach(), "psnr": result["loss_metrics"]["psnr"], "finite": vote}
+        stats: Dict[str, Any] = {"loss": loss, "psnr": psnr, "finite": vote}
         if self.accum > 1:
             self.trainer.accumulate_micro_batch()             # every pass, the last one included
         if self.fwdbwd_step % self.accum == 0:
@@ -213,6 +211,49 @@ class NVSTrainer:
             stats.update(grad_norm=out["grad_norm"], skipped=out["skipped"], lr=lr)
         self.step_times.append(time.time() - t0)
         return stats
+
+    def _forward_backward_eager(self, batch):
+        result = self.model(batch)
+        loss = result["loss_metrics"]["loss"]
+        vote = torch.isfinite(loss.detach()).float()
+        if self.world > 1:
+            dist.all_reduce(vote, op=dist.ReduceOp.MIN)       # every rank skips together
+        (loss * vote / self.accum).backward()
+        return loss.detach(), result["loss_metrics"]["psnr"], vote
+
+    def _forward_backward(self, batch):
+        """Eager, or (``training.cuda_graph``) replayed from a graph captured on the third pass with these input
+        shapes: a pass is tens of thousands of small launches, which keep the host busier than the device."""
+        tr = self.cfg["training"]
+        use_graph = (bool(tr.get("cuda_graph", False)) and self.device.type == "cuda" and self.graph_error is None
+                     and self._passes_run >= 2)
+        self._passes_run += 1
+        if not use_graph:
+            return self._forward_backward_eager(batch)
+        key = tuple((k, tuple(v.shape), v.dtype) for k, v in sorted(batch.items()))
+        entry = self._graphs.get(key)
+        if entry is None:
+            try:
+                torch.cuda.synchronize(self.device)
+                torch.cuda.empty_cache()
+                static = {k: v.clone() for k, v in batch.items()}
+                graph = torch.cuda.CUDAGraph()
+                from ..ops import functional as F
+                before = F.launch_count()
+                with torch.cuda.graph(graph):
+                    outs = self._forward_backward_eager(static)
+                entry = (graph, static, outs, F.launch_count() - before)
+            except Exception as exc:                      # capture refused an operation: stay eager from here on
+                self.graph_error = f"{type(exc).__name__}: {exc}"
+                return self._forward_backward_eager(batch)
+            self._graphs[key] = entry
+        graph, static, outs, launches = entry
+        for k, v in batch.items():
+            static[k].copy_(v)
+        graph.replay()
+        from ..ops import functional as F
+        F._count(launches)
+        return outs
 
     def save(self) -> Optional[str]:
         tr = self.cfg["training"]

@@ -180,7 +180,8 @@ def main(job: Optional[JobConfig] = None) -> TrainState:
                         # layers out of it where memory allows.
                         activation_checkpoint=True,
                         keep_activation_layers=tuple(int(i) for i in job.activation_checkpoint.keep_layers),
-                        activation_offload=job.activation_offload.mode == "offload")
+                        activation_offload=job.activation_offload.mode == "offload",
+                        cuda_graph=bool(job.training.cuda_graph))
     engine = TrainEngine(model_cfg, ecfg)
     if rank == 0 and job.job.print_args:
         print("\n".join(param_check(engine.model)), flush=True)
