@@ -130,9 +130,31 @@ def run_ours(args):
             "gpu_launches": launches, "peak_mem_gib": round(peak_gb, 2), "kernel_status": status,
         }
         print(json.dumps(out), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    eng.release_graphs()
+    _leave(world)
+
+
+def _leave(world: int) -> None:
+    """Leave the process group.  The result line is out already; if tearing the communicators down does not return
+    within half a minute the process exits anyway (a wedged teardown must not turn a finished run into a time-out)."""
+    if world <= 1:
+        return
+    import threading
+    import torch.distributed as dist
+    dist.barrier()
+
+    def _teardown():
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+    t = threading.Thread(target=_teardown, daemon=True)
+    t.start()
+    t.join(30.0)
+    if t.is_alive():
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def run_nvs(args):
@@ -213,9 +235,8 @@ def run_nvs(args):
                     "last_loss": losses[-1] if losses else None},
             "gpu_launches": launches, "peak_mem_gib": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 2),
             "kernel_status": status}), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    trainer.release_graphs()
+    _leave(world)
 
 
 def main():

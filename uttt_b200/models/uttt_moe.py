@@ -374,9 +374,21 @@ class UTTTMoEModel(nn.Module):
     def load_host_state(self, state) -> None:
         self._host_steps = int(state["host_steps"])
 
-    def host_step_replayed(self) -> None:
-        """Bookkeeping of one training forward whose device work was replayed from a graph."""
+    def pop_capture_record(self):
+        """What a forward that ran under stream capture left for :meth:`host_step_replayed` (static tensors of the
+        captured graph)."""
+        record, self._capture_record = getattr(self, "_capture_record", None), None
+        return record
+
+    def host_step_replayed(self, record=None) -> None:
+        """Bookkeeping of one training forward whose device work was replayed from a graph.  The cross-rank sum of
+        the expert counts is not part of the graph (a captured graph holds no collective): it runs here."""
         if self.training and self.config.use_memory_block and self.num_experts > 1 and self._loss_free_enabled():
+            if record is not None and record.get("counts") is not None:
+                counts = record["counts"].clone()
+                if torch.distributed.is_available() and torch.distributed.is_initialized():
+                    torch.distributed.all_reduce(counts)
+                self.memory_loss_free_pending_counts.add_(counts)
             self._host_steps += 1
 
     @torch.no_grad()
@@ -387,11 +399,15 @@ class UTTTMoEModel(nn.Module):
         if self.memory_loss_free_pending_counts.dim() == 1:
             counts = counts.sum(dim=0)
         counts = counts.float()
+        self.memory_loss_free_steps.add_(1)
+        self._host_steps += 1
+        if counts.is_cuda and torch.cuda.is_current_stream_capturing():
+            # under graph capture: the sum over ranks and the addition happen after each replay, outside the graph
+            self._capture_record = {"counts": counts}
+            return
         if torch.distributed.is_available() and torch.distributed.is_initialized():
             torch.distributed.all_reduce(counts)
         self.memory_loss_free_pending_counts.add_(counts)
-        self.memory_loss_free_steps.add_(1)
-        self._host_steps += 1
 
     # ------------------------------------------------------------------ write
     def _chunk_write(self, states: List[fw.PoolState], feats: List[Tuple[torch.Tensor, ...]], offset: int):

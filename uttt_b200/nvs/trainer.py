@@ -216,8 +216,10 @@ class NVSTrainer:
         result = self.model(batch)
         loss = result["loss_metrics"]["loss"]
         vote = torch.isfinite(loss.detach()).float()
-        if self.world > 1:
-            dist.all_reduce(vote, op=dist.ReduceOp.MIN)       # every rank skips together
+        if self.world > 1 and not (vote.is_cuda and torch.cuda.is_current_stream_capturing()):
+            # every rank skips together.  A captured graph holds no collective: there a non-finite loss leaves
+            # non-finite gradients, and the optimizer's own all-reduced norm check skips the step on every rank.
+            dist.all_reduce(vote, op=dist.ReduceOp.MIN)
         (loss * vote / self.accum).backward()
         return loss.detach(), result["loss_metrics"]["psnr"], vote
 
@@ -254,6 +256,12 @@ class NVSTrainer:
         from ..ops import functional as F
         F._count(launches)
         return outs
+
+    def release_graphs(self) -> None:
+        self._graphs.clear()
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+            torch.cuda.empty_cache()
 
     def save(self) -> Optional[str]:
         tr = self.cfg["training"]

@@ -90,7 +90,7 @@ def set_collective_timeout(seconds: float) -> bool:
 class _StepGraph:
     """A captured forward + backward: the graph, its static inputs and the output record it refreshes."""
     graph = None
-    ids = labels = out = None
+    ids = labels = out = record = None
     launches = 0
 
 
@@ -228,7 +228,7 @@ class TrainEngine:
         inner = getattr(self.model, "model", self.model)
         done = getattr(inner, "host_step_replayed", None)
         if done is not None:
-            done()
+            done(sg.record)
         return sg.out
 
     def _capture(self, ids: torch.Tensor, labels: torch.Tensor, n_micro: int) -> "_StepGraph":
@@ -251,9 +251,19 @@ class TrainEngine:
             if host is not None:                   # the capture ran the host side of a step, not the device side
                 inner.load_host_state(host)
         sg.launches = F.launch_count() - before
+        sg.record = inner.pop_capture_record() if hasattr(inner, "pop_capture_record") else None
         out.hidden_states = None                   # nothing outside needs the hidden states of a replayed step
         sg.out = out
         return sg
+
+    def release_graphs(self) -> None:
+        """Drop the captured graphs and their memory pool (before the process group goes away, or to return to
+        eager steps with the memory they hold)."""
+        self._graphs.clear()
+        self._graph_pool = None
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+            torch.cuda.empty_cache()
 
     def _offload(self):
         from ..utils.activation_offload import offload_activations
