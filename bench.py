@@ -48,6 +48,7 @@ def run_ours(args):
     rank, world, local = init_distributed()
     assert torch.cuda.is_available(), "bench.py needs a GPU"
     ext = load(required=True)
+    ops.set_dense_gemm(args.dense_gemm == "own")
     dev = torch.device("cuda", local)
     over = dict(memory_update_backward_mode=args.backward_mode) if args.model != "124M-uttt-dense" else {}
     if args.expert_parallel > 1:
@@ -121,6 +122,7 @@ def run_ours(args):
                        "activation_recompute": "per (chunk, layer) and per chunk write" + (
                            f"; layers {list(keep)} keep their activations" if keep else ""),
                        "cache": "inputs and per-step working set are far larger than L2 (no flush needed)",
+                       "dense_gemm": args.dense_gemm,
                        "cuda_graph": ("forward + backward of a micro-batch replayed as one CUDA graph; optimizer eager"
                                       if eng._graphs else f"off ({eng.graph_error or 'not requested'})")},
             "clocks": clocks,
@@ -251,6 +253,8 @@ def main():
     ap.add_argument("--per-gpu-batch", type=int, default=4)
     ap.add_argument("--micro-batch", type=int, default=int(os.environ.get("UTTT_BENCH_MICRO_BATCH", "4")))
     ap.add_argument("--backward-mode", default="full")
+    ap.add_argument("--dense-gemm", default="library", choices=["library", "own"],
+                    help="dense projections on cuBLAS (default) or on the batched tcgen05 kernel of this repository")
     ap.add_argument("--no-cuda-graph", action="store_true",
                     help="launch every kernel of forward + backward from the host instead of replaying a CUDA graph")
     ap.add_argument("--keep-activation-layers", default=os.environ.get("UTTT_BENCH_KEEP_LAYERS", "auto"),

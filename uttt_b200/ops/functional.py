@@ -379,6 +379,55 @@ def _fuse_wgrad(w: torch.Tensor, g2: torch.Tensor) -> bool:
             and not torch.is_grad_enabled())
 
 
+# Dense projections on the batched tcgen05 kernel of this extension instead of the library GEMM.  Measured on a B200
+# at the block's shapes the own kernel runs at 0.90 to 1.03 of the library's speed, so the library stays the default
+# and ``UTTT_B200_DENSE_GEMM=own`` (or :func:`set_dense_gemm`) selects the own kernel.
+_DENSE_OWN = os.environ.get("UTTT_B200_DENSE_GEMM", "library") == "own"
+
+
+def set_dense_gemm(own: bool) -> None:
+    global _DENSE_OWN
+    _DENSE_OWN = bool(own)
+
+
+def _dense_own_ok(m: int, k: int, n: int, *tensors) -> bool:
+    return (_DENSE_OWN and m % 128 == 0 and k % 64 == 0 and n % 64 == 0
+            and all(t.is_cuda and t.dtype == torch.bfloat16 for t in tensors)
+            and _kernel("bmm_general", tensors[0]) is not None)
+
+
+def _mm_nt(x2: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """x2 [M, K] @ w [N, K]^T."""
+    if _dense_own_ok(x2.shape[0], x2.shape[1], w.shape[0], x2, w):
+        return cuda_ext(x2).bmm_general(x2.contiguous()[None], w.contiguous()[None], 0, 1.0, None, 0.0)[0]
+    return torch.mm(x2, w.t())
+
+
+def _mm_nn(g2: torch.Tensor, w: torch.Tensor, addend: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """g2 [M, N] @ w [N, K] (+ addend)."""
+    if _dense_own_ok(g2.shape[0], g2.shape[1], w.shape[1], g2, w) and (addend is None or addend.dtype == g2.dtype):
+        return cuda_ext(g2).bmm_general(g2.contiguous()[None], w.contiguous()[None], 1, 1.0,
+                                        None if addend is None else addend.contiguous()[None],
+                                        0.0 if addend is None else 1.0)[0]
+    if addend is None:
+        return torch.mm(g2, w)
+    return addend.addmm_(g2, w)
+
+
+def _mm_tn(g2: torch.Tensor, x2: torch.Tensor, acc: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """g2 [T, N]^T @ x2 [T, K] -> [N, K]; added into ``acc`` in place when given."""
+    if _dense_own_ok(g2.shape[1], g2.shape[0], x2.shape[1], g2, x2) and (acc is None or acc.dtype == g2.dtype):
+        out = cuda_ext(g2).bmm_general(g2.contiguous()[None], x2.contiguous()[None], 2, 1.0,
+                                       None if acc is None else acc.contiguous()[None], 0.0 if acc is None else 1.0)[0]
+        if acc is None:
+            return out
+        acc.copy_(out)
+        return acc
+    if acc is None:
+        return torch.mm(g2.t(), x2)
+    return acc.addmm_(g2.t(), x2)
+
+
 class _FanoutLinear(torch.autograd.Function):
     """``y_i = x @ W_i^T (+ b_i)`` for several weights reading the same input.
 
@@ -392,6 +441,13 @@ class _FanoutLinear(torch.autograd.Function):
         ctx.save_for_backward(x, *ws)
         ctx.n = n
         ctx.has_bias = [b is not None for b in bs]
+        if _DENSE_OWN:
+            x2 = x.reshape(-1, x.shape[-1])
+            outs = []
+            for w, b in zip(ws, bs):
+                y = _mm_nt(x2, w)
+                outs.append((y if b is None else y + b).view(*x.shape[:-1], w.shape[0]))
+            return tuple(outs)
         outs = tuple(torch.nn.functional.linear(x, w, b) for w, b in zip(ws, bs))
         return outs
 
@@ -409,16 +465,13 @@ class _FanoutLinear(torch.autograd.Function):
                 continue
             g2 = gy.reshape(-1, gy.shape[-1])
             if ctx.needs_input_grad[0]:
-                if dx is None:
-                    dx = torch.mm(g2, w)
-                else:
-                    dx.addmm_(g2, w)
+                dx = _mm_nn(g2, w, dx)
             if ctx.needs_input_grad[2 + i]:
                 if _fuse_wgrad(w, g2):
-                    w.grad.addmm_(g2.t(), x2)
+                    _mm_tn(g2, x2, w.grad)
                     gws.append(None)
                 else:
-                    gws.append(torch.mm(g2.t(), x2))
+                    gws.append(_mm_tn(g2, x2))
             else:
                 gws.append(None)
             gbs.append(g2.sum(0) if (ctx.has_bias[i] and ctx.needs_input_grad[2 + n + i]) else None)
@@ -459,6 +512,8 @@ class _StackedLinear(torch.autograd.Function):
         if wc is None:
             wc = torch.cat([wa.detach(), wb.detach()], dim=0)
         ctx.save_for_backward(x, wa, wb)
+        if _DENSE_OWN:
+            return _mm_nt(x.reshape(-1, x.shape[-1]), wc).view(*x.shape[:-1], wc.shape[0])
         return torch.nn.functional.linear(x, wc)
 
     @staticmethod
@@ -469,16 +524,16 @@ class _StackedLinear(torch.autograd.Function):
             wc = torch.cat([wa.detach(), wb.detach()], dim=0)
         g2 = gy.reshape(-1, gy.shape[-1])
         x2 = x.reshape(-1, x.shape[-1])
-        dx = torch.mm(g2, wc).view_as(x) if ctx.needs_input_grad[0] else None
+        dx = _mm_nn(g2, wc).view_as(x) if ctx.needs_input_grad[0] else None
         ga = gb = None
         if ctx.needs_input_grad[1] or ctx.needs_input_grad[2]:
             gc = None
             if wa.grad is not None and wb.grad is not None and _fuse_wgrad(wa, g2) and _fuse_wgrad(wb, g2):
                 gc = _stacked_view(wa.grad, wb.grad)
             if gc is not None:
-                gc.addmm_(g2.t(), x2)
+                _mm_tn(g2, x2, gc)
             else:
-                full = torch.mm(g2.t(), x2)
+                full = _mm_tn(g2, x2)
                 ga, gb = full[:wa.shape[0]], full[wa.shape[0]:]
         return dx, ga, gb
 
