@@ -1234,3 +1234,96 @@ def test_dense_projections_on_the_own_kernel_match_fp32():
         assert rel(got, want) < 6e-3 and rel(got, lib) < 6e-3
     for got, lib, want in zip(grads, grads_lib, gradsf):
         assert rel(got, want) < 1.2e-2 and rel(got, lib) < 1.2e-2, (rel(got, want), rel(got, lib))
+
+
+def _one_rank_ep_plan(idx, experts):
+    """The expert-parallel layout of a group of one rank (owner = sender), from the same kernels a real group uses."""
+    from uttt_b200 import ops
+    ext = _ext()
+    bsz, n, k = idx.shape
+    local = ops.build_group_plan(idx, experts)
+    sizes32 = local.sizes.to(torch.int32).contiguous()
+    want = 2 * bsz * n * k
+    cap_rows = ((want + 127) // 128 + bsz * experts) * 128
+    remote_start, tile_group, offsets, sizes = ext.ep_plan(sizes32.view(1, -1), 0, bsz, experts, cap_rows // 128)
+    return local, sizes32, remote_start, tile_group, offsets, cap_rows
+
+
+def test_tile_driven_expert_parallel_read_on_one_rank():
+    """push (with per-tile row counters) -> gate|up GEMM that waits for complete tiles -> down GEMM that reports
+    finished tiles -> pull that waits for them: the whole chain on a group of one rank, against the plain kernels
+    and fp32."""
+    from uttt_b200 import ops
+    ext = _ext()
+    torch.manual_seed(0)
+    bsz, n, k, experts, d, inter = 2, 1024, 2, 4, 128, 256
+    idx = torch.randint(0, experts, (bsz, n, k), device=DEV)
+    idx[..., 1] = (idx[..., 0] + 1 + torch.randint(0, experts - 1, (bsz, n), device=DEV)) % experts
+    local, sizes32, remote_start, tile_group, offsets, cap_rows = _one_rank_ep_plan(idx, experts)
+    rows = (torch.randn(bsz * n, d, device=DEV) * 0.5).bfloat16()
+    wts = torch.rand(bsz * n, k, device=DEV)
+    w02 = (torch.randn(bsz * experts, 2 * inter, d, device=DEV) * 0.1).bfloat16()
+    w1 = (torch.randn(bsz * experts, d, inter, device=DEV) * 0.1).bfloat16()
+    tiles = cap_rows // 128
+    recv = torch.full((cap_rows, d), float("nan"), device=DEV, dtype=torch.bfloat16)
+    send = torch.full((cap_rows, d), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ready = torch.zeros(tiles, device=DEV, dtype=torch.int32)
+    done = torch.zeros(tiles, device=DEV, dtype=torch.int32)
+    idx32 = idx.reshape(bsz * n, k).to(torch.int32).contiguous()
+    maps = (idx32, local.dest.contiguous(), local.offsets)
+    per_tile = int(ext.gg_nt_done_per_tile(d))
+    for use in (1, 2):                                     # the send counters only grow: second use, second target
+        ext.ep_push(rows, None, *maps, sizes32, remote_start, [recv.data_ptr()], experts, n, cap_rows,
+                    [ready.data_ptr()])
+        used = tile_group >= 0
+        assert bool((ready[used] == 128).all()) and bool((ready[~used] == 0).all())
+        hid = ext.gg_nt_swiglu(recv, w02, tile_group, ready, 128, 50.0)
+        ready.zero_()
+        ext.gg_nt(hid, w1, tile_group, send, None, 0, done, 50.0)
+        assert bool((done == use * per_tile).all())        # every tile reports, used or not
+        y = ext.ep_pull([send.data_ptr()], wts, *maps, remote_start, experts, n, d, torch.bfloat16, cap_rows,
+                        [done.data_ptr()], use * per_tile, 50.0)
+        _status_ok()
+        # oracle: per routed copy in fp32
+        g = (torch.arange(bsz, device=DEV).repeat_interleave(n)[:, None] * experts + idx.reshape(-1, k))
+        xf = rows.float()
+        want = torch.zeros(bsz * n, d, device=DEV)
+        for j in range(k):
+            w02j, w1j = w02[g[:, j]].float(), w1[g[:, j]].float()
+            y02 = torch.einsum("rnd,rd->rn", w02j, xf)
+            h = (torch.nn.functional.silu(y02[:, :inter]) * y02[:, inter:]).bfloat16().float()
+            want += wts[:, j:j + 1] * torch.einsum("rdi,ri->rd", w1j, h).bfloat16().float()
+        rel = float((y.float() - want).norm() / want.norm())
+        assert rel < 1e-2, rel
+
+
+def test_tile_driven_read_waits_run_out_with_a_status():
+    """Counters that nothing completes: the producer of the gate|up GEMM and the pulling warps give up after a few
+    milliseconds, report 62 / 63 in the status word and return; the kernels work again once the word is cleared."""
+    ext = _ext()
+    torch.manual_seed(0)
+    bsz, n, k, experts, d, inter = 1, 512, 2, 2, 128, 256
+    idx = torch.stack([torch.zeros(bsz, n, dtype=torch.long), torch.ones(bsz, n, dtype=torch.long)], -1).to(DEV)
+    local, sizes32, remote_start, tile_group, offsets, cap_rows = _one_rank_ep_plan(idx, experts)
+    tiles = cap_rows // 128
+    x = torch.randn(cap_rows, d, device=DEV).bfloat16()
+    w02 = (torch.randn(bsz * experts, 2 * inter, d, device=DEV) * 0.1).bfloat16()
+    never = torch.zeros(tiles, device=DEV, dtype=torch.int32)
+    st = ext.gemm_status(torch.zeros(1, device=DEV))
+    st.zero_()
+    ext.gg_nt_swiglu(x, w02, tile_group, never, 128, 5.0)
+    torch.cuda.synchronize()
+    assert int(st[0].item()) == 62
+    st.zero_()
+    idx32 = idx.reshape(bsz * n, k).to(torch.int32).contiguous()
+    ext.ep_pull([x.data_ptr()], None, idx32, local.dest.contiguous(), local.offsets, remote_start, experts, n, d,
+                torch.bfloat16, cap_rows, [never.data_ptr()], 8, 5.0)
+    torch.cuda.synchronize()
+    assert int(st[0].item()) == 63
+    st.zero_()
+    full = torch.full((tiles,), 128, device=DEV, dtype=torch.int32)
+    got = ext.gg_nt_swiglu(x, w02, tile_group, full, 128, 5.0)
+    want = ext.gg_nt_swiglu(x, w02, tile_group)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    _status_ok()

@@ -104,6 +104,10 @@ def pool_read(q_rows: torch.Tensor, state_w02: torch.Tensor, state_w1: torch.Ten
         g = plan.num_groups
         w02 = state_w02.reshape(g, state_w02.shape[2], d)
         w1 = state_w1.reshape(g, d, state_w1.shape[3])
+        if ep.can_fuse_read(q_rows, w02, w1):
+            # rows flow to their owners and back tile by tile (parallel/expert_parallel.py::fused_read)
+            return ep.fused_read(q_rows.reshape(bsz * n, d).to(w02.dtype), routing.weights, w02, w1,
+                                 eplan).view(bsz, n, d)
         xp = ep.dispatch(q_rows.reshape(bsz * n, d).to(w02.dtype), None, eplan)
         hid = ops.gg_swiglu(xp, w02, plan)
         yp = ops.gg_nt(hid, w1, plan)

@@ -36,9 +36,13 @@ int64_t launch_count();
 std::vector<at::Tensor> build_group_plan(at::Tensor expert_idx, int64_t num_experts);
 at::Tensor plucker_embed(at::Tensor image, at::Tensor fxfycxcy, at::Tensor c2w, at::Tensor is_target, int64_t patch);
 
-at::Tensor gg_nt(at::Tensor x, at::Tensor w, at::Tensor tile_group);
+at::Tensor gg_nt(at::Tensor x, at::Tensor w, at::Tensor tile_group, c10::optional<at::Tensor> out_buf,
+                 c10::optional<at::Tensor> ready, int64_t ready_target, c10::optional<at::Tensor> done,
+                 double wait_limit_ms);
+int64_t gg_nt_done_per_tile(int64_t n);
 at::Tensor gg_nn(at::Tensor x, at::Tensor w, at::Tensor tile_group);
-at::Tensor gg_nt_swiglu(at::Tensor x, at::Tensor w02, at::Tensor tile_group);
+at::Tensor gg_nt_swiglu(at::Tensor x, at::Tensor w02, at::Tensor tile_group, c10::optional<at::Tensor> ready,
+                        int64_t ready_target, double wait_limit_ms);
 std::vector<at::Tensor> gg_nt_swiglu_bwd(at::Tensor x, at::Tensor w02, at::Tensor dh, c10::optional<at::Tensor> lr,
                                          at::Tensor tile_group, bool want_h, bool want_y);
 std::vector<at::Tensor> pair_plan(at::Tensor tile_group, at::Tensor offsets, int64_t tiles);
@@ -71,10 +75,11 @@ at::Tensor ag_linear(at::Tensor x, std::vector<int64_t> shard_ptrs, int64_t rank
 std::vector<at::Tensor> ep_plan(at::Tensor sizes_all, int64_t rank, int64_t B, int64_t E, int64_t tiles_cap);
 void ep_push(at::Tensor src, c10::optional<at::Tensor> weights, at::Tensor idx, at::Tensor dest, at::Tensor offsets_local,
              at::Tensor sizes_local, at::Tensor remote_start, std::vector<int64_t> peer_ptrs, int64_t E,
-             int64_t rows_per_batch, int64_t cap_rows);
+             int64_t rows_per_batch, int64_t cap_rows, std::vector<int64_t> ready_ptrs);
 at::Tensor ep_pull(std::vector<int64_t> peer_ptrs, c10::optional<at::Tensor> weights, at::Tensor idx, at::Tensor dest,
                    at::Tensor offsets_local, at::Tensor remote_start, int64_t E, int64_t rows_per_batch, int64_t D,
-                   at::ScalarType dtype, int64_t cap_rows);
+                   at::ScalarType dtype, int64_t cap_rows, std::vector<int64_t> done_ptrs, int64_t done_target,
+                   double wait_limit_ms);
 at::Tensor ep_pull_dot(at::Tensor local, std::vector<int64_t> peer_ptrs, at::Tensor idx, at::Tensor dest,
                        at::Tensor offsets_local, at::Tensor remote_start, int64_t E, int64_t rows_per_batch,
                        int64_t cap_rows);
@@ -123,9 +128,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("launch_count", &launch_count);
   m.def("build_group_plan", &build_group_plan);
   m.def("plucker_embed", &plucker_embed);
-  m.def("gg_nt", &gg_nt);
+  m.def("gg_nt", &gg_nt, py::arg("x"), py::arg("w"), py::arg("tile_group"), py::arg("out") = py::none(),
+        py::arg("ready") = py::none(), py::arg("ready_target") = 0, py::arg("done") = py::none(),
+        py::arg("wait_limit_ms") = 0.0);
+  m.def("gg_nt_done_per_tile", &gg_nt_done_per_tile);
   m.def("gg_nn", &gg_nn);
-  m.def("gg_nt_swiglu", &gg_nt_swiglu);
+  m.def("gg_nt_swiglu", &gg_nt_swiglu, py::arg("x"), py::arg("w02"), py::arg("tile_group"),
+        py::arg("ready") = py::none(), py::arg("ready_target") = 0, py::arg("wait_limit_ms") = 0.0);
   m.def("gg_nt_swiglu_bwd", &gg_nt_swiglu_bwd);
   m.def("pair_plan", &pair_plan);
   m.def("gg_nt_pair", &gg_nt_pair);
@@ -145,8 +154,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("ready"), py::arg("gather_ctas"), py::arg("wait_limit_ms") = 0.0,
         py::arg("withhold_from_block") = -1);
   m.def("ep_plan", &ep_plan);
-  m.def("ep_push", &ep_push);
-  m.def("ep_pull", &ep_pull);
+  m.def("ep_push", &ep_push, py::arg("src"), py::arg("weights"), py::arg("idx"), py::arg("dest"),
+        py::arg("offsets_local"), py::arg("sizes_local"), py::arg("remote_start"), py::arg("peer_ptrs"), py::arg("E"),
+        py::arg("rows_per_batch"), py::arg("cap_rows"), py::arg("ready_ptrs") = std::vector<int64_t>());
+  m.def("ep_pull", &ep_pull, py::arg("peer_ptrs"), py::arg("weights"), py::arg("idx"), py::arg("dest"),
+        py::arg("offsets_local"), py::arg("remote_start"), py::arg("E"), py::arg("rows_per_batch"), py::arg("D"),
+        py::arg("dtype"), py::arg("cap_rows"), py::arg("done_ptrs") = std::vector<int64_t>(),
+        py::arg("done_target") = 0, py::arg("wait_limit_ms") = 0.0);
   m.def("ep_pull_dot", &ep_pull_dot);
   m.def("frob_normalize_fwd", &frob_normalize_fwd);
   m.def("frob_normalize_bwd", &frob_normalize_bwd);

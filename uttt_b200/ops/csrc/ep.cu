@@ -120,10 +120,19 @@ __device__ __forceinline__ void ep_locate(const EpMap& m, long long copy, int& p
 
 // ------------------------------------------------------------------------------------ push
 // VEC = 16-byte pieces per row (row_bytes / 16); rows are moved as raw bytes except when a weight scales them.
+// `ready` (optional): per-owner arrays of row counters, one per 128-row tile of the owner's buffer.  A warp that has
+// stored a row adds one to the counter of the row's tile (after a system-scope fence), the warp that zeroes the
+// padding rows of a group adds their number: a tile whose counter reaches 128 is complete, and the owner's grouped
+// GEMM may start on it while other tiles are still in flight.
+__device__ __forceinline__ void ep_signal_rows(const EpPeers& ready, int peer, long long pos, unsigned int rows) {
+  __threadfence_system();
+  atomicAdd_system(reinterpret_cast<unsigned int*>(ready.p[peer]) + pos / kTile, rows);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) ep_push_kernel(const T* __restrict__ src, const float* __restrict__ weights,
                                                       EpMap m, const int* __restrict__ sizes_local, EpPeers peers,
-                                                      long long copies, int D, int groups) {
+                                                      long long copies, int D, int groups, EpPeers ready) {
   const int lane = threadIdx.x & 31;
   const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
@@ -154,6 +163,10 @@ __global__ void __launch_bounds__(256) ep_push_kernel(const T* __restrict__ src,
         else *reinterpret_cast<float4*>(reinterpret_cast<float*>(d) + v * 4) = make_float4(f[0], f[1], f[2], f[3]);
       }
     }
+    if (ready.p[0] != nullptr) {
+      __syncwarp();
+      if (lane == 0) ep_signal_rows(ready, peer, pos, 1u);
+    }
   }
   // zero the padding rows of this sender's groups in the owners' buffers
   for (long long g = warp; g < groups; g += nwarps) {
@@ -161,21 +174,93 @@ __global__ void __launch_bounds__(256) ep_push_kernel(const T* __restrict__ src,
     const int padded = (sz + kTile - 1) / kTile * kTile;
     const int e = (int)(g % m.E);
     T* base = reinterpret_cast<T*>(peers.p[e / m.El]) + (long long)m.remote_start[g] * D;
+    unsigned int zeroed = 0;
     for (int row = sz; row < padded; ++row)
-      if ((long long)m.remote_start[g] + row < m.cap_rows)
-      for (int v = lane; v < nv; v += 32) reinterpret_cast<uint4*>(base + (long long)row * D)[v] = make_uint4(0, 0, 0, 0);
+      if ((long long)m.remote_start[g] + row < m.cap_rows) {
+        for (int v = lane; v < nv; v += 32) reinterpret_cast<uint4*>(base + (long long)row * D)[v] = make_uint4(0, 0, 0, 0);
+        ++zeroed;
+      }
+    if (ready.p[0] != nullptr && zeroed > 0) {
+      // the padding rows of a group all lie in its last tile
+      __syncwarp();
+      if (lane == 0) ep_signal_rows(ready, e / m.El, (long long)m.remote_start[g] + sz, zeroed);
+    }
   }
 }
 
 // ------------------------------------------------------------------------------------ pull
+// Flags of the tile-driven combine: `done.p[q]` = rank q's array of per-tile completion counters (bumped by the
+// epilogue warps of q's down-projection GEMM); a tile of q's result may be read once its counter has reached
+// `target`.  The waits are bounded: after `limit_ns` a warp writes status 63 and the kernel's remaining rows are
+// skipped (the host reads the status word; the output is then invalid).
+struct EpDone {
+  EpPeers flags;
+  unsigned int target;
+  unsigned long long limit_ns;
+  int* status;
+  int tiles;          // counters per rank
+  int P;
+};
+
+__device__ __forceinline__ bool ep_wait_tile(const EpDone& dn, int peer, int tile, unsigned int* seen, int lane) {
+  const int word = peer * ((dn.tiles + 31) / 32) + (tile >> 5);
+  const unsigned int bit = 1u << (tile & 31);
+  if (seen[word] & bit) return true;             // another warp of this block has already seen it complete
+  int ok = 1;
+  if (lane == 0) {
+    const unsigned int* flag = reinterpret_cast<const unsigned int*>(dn.flags.p[peer]) + tile;
+    uint64_t t0 = 0;
+    ok = 0;
+    for (uint32_t i = 0; i < (1u << 26); ++i) {
+      unsigned int v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+      if (v >= dn.target) { ok = 1; break; }
+      if ((i & 63u) == 63u) {
+        if (dn.status != nullptr && *(volatile int*)dn.status != 0) break;
+        uint64_t now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > dn.limit_ns) break;
+      }
+      __nanosleep(128);
+    }
+    if (ok) atomicOr(&seen[word], bit);
+    else if (dn.status != nullptr) atomicCAS(dn.status, 0, 63);
+  }
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  __syncwarp();
+  return ok != 0;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) ep_pull_kernel(T* __restrict__ out, const float* __restrict__ weights, EpMap m,
-                                                      EpPeers peers, long long rows, int D) {
+                                                      EpPeers peers, long long rows, int D, EpDone dn) {
   const int lane = threadIdx.x & 31;
   const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
   const int nv = D / 8;
+  extern __shared__ unsigned int seen[];         // [P * ceil(tiles / 32)] bits: tile known complete
+  const bool flow = dn.flags.p[0] != nullptr;
+  if (flow) {
+    for (int i = threadIdx.x; i < dn.P * ((dn.tiles + 31) / 32); i += blockDim.x) seen[i] = 0;
+    __syncthreads();
+    // every rank's first counter is waited for whether or not rows of this rank went there, so that no rank runs
+    // ahead of a peer it happens not to read from (buffer reuse is ordered by these waits)
+    if (blockIdx.x == 0 && (threadIdx.x >> 5) < dn.P) {
+      if (!ep_wait_tile(dn, threadIdx.x >> 5, 0, seen, lane)) return;
+    }
+  }
   for (long long r = warp; r < rows; r += nwarps) {
+    if (flow) {
+      bool ok = true;
+      for (int j = 0; j < m.k && ok; ++j) {
+        int peer;
+        long long pos;
+        ep_locate(m, r * m.k + j, peer, pos);
+        if (pos < m.cap_rows) ok = ep_wait_tile(dn, peer, (int)(pos / kTile), seen, lane);
+      }
+      if (!ok) return;
+    }
     for (int v = lane; v < nv; v += 32) {
       float acc[8];
 #pragma unroll
@@ -277,7 +362,7 @@ std::vector<at::Tensor> ep_plan(at::Tensor sizes_all, int64_t rank, int64_t B, i
 
 void ep_push(at::Tensor src, c10::optional<at::Tensor> weights, at::Tensor idx, at::Tensor dest, at::Tensor offsets_local,
              at::Tensor sizes_local, at::Tensor remote_start, std::vector<int64_t> peer_ptrs, int64_t E,
-             int64_t rows_per_batch, int64_t cap_rows) {
+             int64_t rows_per_batch, int64_t cap_rows, std::vector<int64_t> ready_ptrs) {
   c10::cuda::CUDAGuard guard(src.device());
   TORCH_CHECK(src.dim() == 2 && src.is_contiguous() && src.size(0) == idx.size(0));
   const int D = src.size(1);
@@ -285,6 +370,11 @@ void ep_push(at::Tensor src, c10::optional<at::Tensor> weights, at::Tensor idx, 
   const int P = peer_ptrs.size();
   EpMap m = make_map(idx, dest, offsets_local, remote_start, E, P, rows_per_batch, cap_rows);
   EpPeers peers = make_peers(peer_ptrs);
+  EpPeers ready{};
+  if (!ready_ptrs.empty()) {
+    TORCH_CHECK(ready_ptrs.size() == peer_ptrs.size(), "one counter array per rank");
+    ready = make_peers(ready_ptrs);
+  }
   const float* wp = nullptr;
   at::Tensor wc;
   if (weights.has_value() && weights->defined()) {
@@ -298,11 +388,12 @@ void ep_push(at::Tensor src, c10::optional<at::Tensor> weights, at::Tensor idx, 
   const int blocks = ep_blocks(copies);
   if (src.scalar_type() == at::kBFloat16)
     ep_push_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(src.data_ptr()), wp,
-                                                             m, sizes_local.data_ptr<int>(), peers, copies, D, groups);
+                                                             m, sizes_local.data_ptr<int>(), peers, copies, D, groups,
+                                                             ready);
   else {
     TORCH_CHECK(src.scalar_type() == at::kFloat);
     ep_push_kernel<float><<<blocks, 256, 0, stream>>>(src.data_ptr<float>(), wp, m, sizes_local.data_ptr<int>(), peers,
-                                                     copies, D, groups);
+                                                     copies, D, groups, ready);
   }
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   count_launch();
@@ -310,7 +401,8 @@ void ep_push(at::Tensor src, c10::optional<at::Tensor> weights, at::Tensor idx, 
 
 at::Tensor ep_pull(std::vector<int64_t> peer_ptrs, c10::optional<at::Tensor> weights, at::Tensor idx, at::Tensor dest,
                    at::Tensor offsets_local, at::Tensor remote_start, int64_t E, int64_t rows_per_batch, int64_t D,
-                   at::ScalarType dtype, int64_t cap_rows) {
+                   at::ScalarType dtype, int64_t cap_rows, std::vector<int64_t> done_ptrs, int64_t done_target,
+                   double wait_limit_ms) {
   c10::cuda::CUDAGuard guard(idx.device());
   TORCH_CHECK(D % 8 == 0);
   const int P = peer_ptrs.size();
@@ -326,12 +418,25 @@ at::Tensor ep_pull(std::vector<int64_t> peer_ptrs, c10::optional<at::Tensor> wei
   auto out = at::empty({rows, D}, idx.options().dtype(dtype));
   auto stream = at::cuda::getCurrentCUDAStream().stream();
   const int blocks = ep_blocks(rows);
+  EpDone dn{};
+  size_t smem = 0;
+  if (!done_ptrs.empty()) {
+    TORCH_CHECK(done_ptrs.size() == peer_ptrs.size(), "one counter array per rank");
+    dn.flags = make_peers(done_ptrs);
+    dn.target = (unsigned int)done_target;
+    dn.limit_ns = wait_limit_ms > 0 ? (unsigned long long)(wait_limit_ms * 1e6) : 2000000000ull;
+    dn.status = gemm_status(idx).data_ptr<int>();
+    dn.tiles = (int)(cap_rows / kTile);
+    dn.P = P;
+    smem = sizeof(unsigned int) * (size_t)P * ((dn.tiles + 31) / 32);
+    TORCH_CHECK(smem <= 40 * 1024, "expert-parallel combine: too many tiles for the per-block tile bitmap");
+  }
   if (dtype == at::kBFloat16)
-    ep_pull_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(reinterpret_cast<__nv_bfloat16*>(out.data_ptr()), wp, m,
-                                                             peers, rows, (int)D);
+    ep_pull_kernel<__nv_bfloat16><<<blocks, 256, smem, stream>>>(reinterpret_cast<__nv_bfloat16*>(out.data_ptr()), wp,
+                                                                m, peers, rows, (int)D, dn);
   else {
     TORCH_CHECK(dtype == at::kFloat);
-    ep_pull_kernel<float><<<blocks, 256, 0, stream>>>(out.data_ptr<float>(), wp, m, peers, rows, (int)D);
+    ep_pull_kernel<float><<<blocks, 256, smem, stream>>>(out.data_ptr<float>(), wp, m, peers, rows, (int)D, dn);
   }
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   count_launch();

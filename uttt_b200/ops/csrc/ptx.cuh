@@ -115,6 +115,8 @@ __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// all state spaces: orders generic-proxy accesses to global memory with those of the TMA unit
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
 // ---------------------------------------------------------------- TMEM management
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {

@@ -157,6 +157,12 @@ __global__ void __launch_bounds__((EPI != kEpiNone ? kFusedWarps : 4) * 32 + 64)
       for (int id = blockIdx.x; id < total_tiles && ok; id += gridDim.x) {
         TileCoord c = decode_tile<MODE, TW>(p, segs, id, tiles_n, tiles_m);
         if (c.unused || c.nkb == 0) continue;
+        if (MODE == kNT && p.ready != nullptr) {
+          // the rows of this tile come from other ranks: start when all of them have landed
+          ok = wait_tile_rows(p, id / tiles_n);
+          if (!ok) break;
+          ptx::fence_proxy_async_all();    // stored through the generic proxy, read by the TMA unit
+        }
         int seg = 0, seg_row = 0, seg_end = 0;
         if (MODE == kTN) {
           seg_row = segs.offsets[0][c.g];
@@ -301,6 +307,11 @@ __global__ void __launch_bounds__((EPI != kEpiNone ? kFusedWarps : 4) * 32 + 64)
           for (int col = 0; col < BN; col += 16 / (int)sizeof(OutT))
             *reinterpret_cast<uint4*>(orow + col) = make_uint4(0, 0, 0, 0);
         }
+        if (MODE == kNT && p.done != nullptr) {
+          // every tile is signalled on every launch, used or not: the readers wait for launch count x signals
+          __syncwarp();
+          if (lane == 0) signal_tile_done(p, id / tiles_n);
+        }
         continue;
       }
       const int ab = acc_it & 1;
@@ -387,6 +398,11 @@ __global__ void __launch_bounds__((EPI != kEpiNone ? kFusedWarps : 4) * 32 + 64)
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(acc_empty(ab));
       ++acc_it;
+      if (MODE == kNT && p.done != nullptr && lane == 0) {
+        ptx::tma_store_wait_all();         // this warp's rows of the tile are written, not just read from the slabs
+        ptx::fence_proxy_async_all();
+        signal_tile_done(p, id / tiles_n);
+      }
     }
     if (lane == 0) ptx::tma_store_wait_all();
   }
@@ -502,18 +518,48 @@ static int pick_bn(int n) {
   return (n % 128 == 0) ? 128 : 64;
 }
 
-at::Tensor gg_nt(at::Tensor x, at::Tensor w, at::Tensor tile_group) {
+// Tile flow of the expert-parallel read (all optional): `ready` [>= R / 128] uint32 counters of landed rows per row
+// tile of x (a tile is loaded once its counter reaches ready_target), `out` a caller-owned [R, N] result buffer,
+// `done` [>= R / 128] uint32 counters that every epilogue warp bumps once per (row tile, column tile) when its rows
+// are in memory: 4 * (N / tile width) per row tile and launch (gg_nt_done_per_tile).
+static void set_tile_flow(GemmParams& p, const c10::optional<at::Tensor>& ready, int64_t ready_target,
+                          const c10::optional<at::Tensor>& done, double wait_limit_ms, int tiles) {
+  p.wait_limit_ns = wait_limit_ms > 0 ? (unsigned long long)(wait_limit_ms * 1e6) : (unsigned long long)ptx::kWaitLimitNs;
+  if (ready.has_value() && ready->defined()) {
+    TORCH_CHECK(ready->scalar_type() == at::kInt && ready->is_contiguous() && ready->numel() >= tiles);
+    p.ready = reinterpret_cast<const unsigned int*>(ready->data_ptr<int>());
+    p.ready_target = (unsigned int)ready_target;
+  }
+  if (done.has_value() && done->defined()) {
+    TORCH_CHECK(done->scalar_type() == at::kInt && done->is_contiguous() && done->numel() >= tiles);
+    p.done = reinterpret_cast<unsigned int*>(done->data_ptr<int>());
+  }
+}
+
+int64_t gg_nt_done_per_tile(int64_t n) { return 4 * (n / pick_bn((int)n)); }
+
+at::Tensor gg_nt(at::Tensor x, at::Tensor w, at::Tensor tile_group, c10::optional<at::Tensor> out_buf,
+                 c10::optional<at::Tensor> ready, int64_t ready_target, c10::optional<at::Tensor> done,
+                 double wait_limit_ms) {
   c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 && x.is_contiguous() &&
               w.is_contiguous() && tile_group.scalar_type() == at::kInt);
   int R = x.size(0), K = x.size(1), G = w.size(0), N = w.size(1);
   TORCH_CHECK(w.size(2) == K && R % BM == 0 && K % BK == 0 && N % 64 == 0 && tile_group.numel() >= R / BM);
-  auto out = at::empty({R, N}, x.options());
+  at::Tensor out;
+  if (out_buf.has_value() && out_buf->defined()) {
+    out = *out_buf;
+    TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.is_contiguous() && out.dim() == 2 && out.size(0) == R &&
+                out.size(1) == N && out.device() == x.device(), "gg_nt: out must be a contiguous [R, N] bf16 buffer");
+  } else {
+    out = at::empty({R, N}, x.options());
+  }
   auto ta = make_tmap_2d_bf16(x.data_ptr(), R, K, BM, BK);
   GemmParams p{};
   p.tile_group = tile_group.data_ptr<int>();
   p.groups = G; p.N = N; p.K = K; p.out = out.data_ptr(); p.out_rows = R;
   p.status = status_word(x.device()).data_ptr<int>();
+  set_tile_flow(p, ready, ready_target, done, wait_limit_ms, R / BM);
   const int bn = pick_bn(N);
   auto tb = make_tmap_2d_bf16(w.data_ptr(), (uint64_t)G * N, K, bn, BK);
   dim3 grid(N / bn, R / BM);
@@ -526,7 +572,8 @@ at::Tensor gg_nt(at::Tensor x, at::Tensor w, at::Tensor tile_group) {
 
 // hid[r, :] = silu(x[r] . W0[g(r)]^T) * (x[r] . W2[g(r)]^T) with W02 = [W0; W2] stacked on the row axis:
 // x [R, K], w02 [G, 2I, K] -> [R, I].  The pre-activations stay in tensor memory.
-at::Tensor gg_nt_swiglu(at::Tensor x, at::Tensor w02, at::Tensor tile_group) {
+at::Tensor gg_nt_swiglu(at::Tensor x, at::Tensor w02, at::Tensor tile_group, c10::optional<at::Tensor> ready,
+                        int64_t ready_target, double wait_limit_ms) {
   c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w02.scalar_type() == at::kBFloat16 && x.is_contiguous() &&
               w02.is_contiguous() && tile_group.scalar_type() == at::kInt);
@@ -540,6 +587,7 @@ at::Tensor gg_nt_swiglu(at::Tensor x, at::Tensor w02, at::Tensor tile_group) {
   p.tile_group = tile_group.data_ptr<int>();
   p.groups = G; p.N = N; p.K = K; p.out = out.data_ptr(); p.out_rows = R; p.inter = I;
   p.status = status_word(x.device()).data_ptr<int>();
+  set_tile_flow(p, ready, ready_target, c10::nullopt, wait_limit_ms, R / BM);
   launch_gemm<kNT, 256, __nv_bfloat16, kEpiSwiGLU>(ta, tb, p, dim3(I / 128, R / BM));
   return out;
 }

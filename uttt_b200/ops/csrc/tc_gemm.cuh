@@ -29,6 +29,11 @@ struct GemmParams {
   const float* lr;          // kEpiWrite: [R, 3] fp32 per-row learning rates, or nullptr (all ones)
   void* out_h;              // kEpiWrite: [R, I] hidden * lr1, or nullptr
   void* out_y;              // kEpiWrite: [R, 2I] pre-activations, or nullptr
+  // tile flow between ranks (expert parallelism; both optional, NT products only):
+  const unsigned int* ready;       // [tiles] rows that have landed in row tile t of x; the producer loads a tile once
+  unsigned int ready_target;       //   ready[t] >= ready_target (the senders add one per row they stored)
+  unsigned int* done;              // [tiles] += 1 by every epilogue warp once its rows of a tile are in memory
+  unsigned long long wait_limit_ns;  // bound of the wait on `ready` (status 62 when it runs out)
 };
 
 // Epilogue of the NT product against the stacked gate|up weights:
@@ -63,6 +68,35 @@ at::Tensor& status_word(const at::Device& dev);
 
 
 #ifdef __CUDACC__
+// ------------------------------------------------------------------------------------ tile flow between ranks
+// Bounded wait of the TMA producer for the rows of one 128-row tile that other ranks store into x over NVLink.  Gives
+// up after p.wait_limit_ns (or when another CTA has reported a failure): status 62, false; the CTA then winds down
+// like after any failed wait.
+__device__ __forceinline__ bool wait_tile_rows(const GemmParams& p, int tile) {
+  const unsigned int* flag = p.ready + tile;
+  uint64_t t0 = 0;
+  for (uint32_t i = 0; i < ptx::kSpinLimit; ++i) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v >= p.ready_target) return true;
+    if ((i & 63u) == 63u) {
+      if (p.status != nullptr && *(volatile int*)p.status != 0) return false;
+      uint64_t now = ptx::globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > p.wait_limit_ns) break;
+    }
+    __nanosleep(64);
+  }
+  if (p.status != nullptr) atomicCAS(p.status, 0, 62);
+  return false;
+}
+
+// One epilogue warp tells the readers on other ranks that its rows of `tile` are in memory.
+__device__ __forceinline__ void signal_tile_done(const GemmParams& p, int tile) {
+  __threadfence_system();
+  atomicAdd_system(p.done + tile, 1u);
+}
+
 // ------------------------------------------------------------------------------------ fused SwiGLU epilogues
 // Shared by the one-CTA and the two-CTA kernels.  A tile holds 128 hidden columns: accumulator columns [0, 128)
 // are y0 (gate), [128, 256) are y2 (up).  EIGHT epilogue warps work on a tile: warp w owns the 32 rows of lane

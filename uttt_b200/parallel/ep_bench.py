@@ -43,6 +43,16 @@ def _time(fn, iters, flush):
     return float(t)
 
 
+def _measured_tflops() -> float:
+    for cand in ("MEASURED_PEAKS.json", os.path.join(os.path.dirname(__file__), "..", "..", "MEASURED_PEAKS.json")):
+        try:
+            with open(cand) as fh:
+                return float(json.load(fh)["bf16_tflops"])
+        except Exception:
+            continue
+    return 1590.0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--batch", type=int, default=4)
@@ -91,6 +101,41 @@ def main():
                                                ptrs, e, n, cap), args.iters, flush)
             t_pull = _time(lambda: ext.ep_pull(ptrs, w, *_map_args(eplan), e, n, d, rows.dtype, cap), args.iters,
                            flush)
+            # the read of the pool through its owners: dispatch -> gate|up GEMM with SwiGLU -> down GEMM -> combine,
+            # host-ordered (a scalar collective and a staging copy around each transfer) against the tile-driven
+            # chain of four kernels (expert_parallel.py::fused_read)
+            inter = 4 * d
+            g_owner = eplan.owner.num_groups
+            w02 = (torch.randn(g_owner, 2 * inter, d, device=dev) * 0.05).bfloat16()
+            w1 = (torch.randn(g_owner, d, inter, device=dev) * 0.05).bfloat16()
+
+            def read_ordered():
+                xq = ep.dispatch(rows, None, eplan)
+                hid = F_ops.gg_swiglu(xq, w02, eplan.owner)
+                return ep.combine(F_ops.gg_nt(hid, w1, eplan.owner), w, eplan)
+
+            def read_gemms_only():
+                return F_ops.gg_nt(F_ops.gg_swiglu(xp, w02, eplan.owner), w1, eplan.owner)
+
+            y_a = read_ordered()
+            y_b = ep.fused_read(rows, w, w02, w1, eplan)
+            rel = float((y_a.float() - y_b.float()).norm() / y_a.float().norm().clamp_min(1e-12))
+            t_ordered = _time(read_ordered, args.iters, flush)
+            t_fused = _time(lambda: ep.fused_read(rows, w, w02, w1, eplan), args.iters, flush)
+            t_gemms = _time(read_gemms_only, args.iters, flush)
+            flops = 6.0 * b * n * k * d * inter
+            peak = _measured_tflops()
+            t_compute = flops / peak / 1e9
+            t_link = 2.0 * nvlink_bytes / 770.0 / 1e6          # rows out and results back, per direction and rank
+            status = int(ext.gemm_status(torch.zeros(1, device=dev))[0])
+            extra_read = {"host_ordered_ms": round(t_ordered, 4), "tile_driven_ms": round(t_fused, 4),
+                          "gemms_alone_ms": round(t_gemms, 4), "rel_diff_between_the_two": round(rel, 5),
+                          "compute_at_measured_peak_ms": round(t_compute, 4),
+                          "nvlink_at_measured_770GBs_ms": round(t_link, 4),
+                          "tile_driven_roofline_frac": round(max(t_compute, t_link) / t_fused, 3),
+                          "host_ordered_roofline_frac": round(max(t_compute, t_link) / t_ordered, 3),
+                          "kernel_status": status}
+            out["read_through_owners"] = extra_read
             extra = {"push_kernel_ms": round(t_push, 4), "pull_kernel_ms": round(t_pull, 4),
                      "push_kernel_frac_of_measured_peer_copy": round(nvlink_bytes / t_push / 1e6 / 770.0, 3),
                      "pull_kernel_frac_of_measured_peer_copy": round(nvlink_bytes / t_pull / 1e6 / 770.0, 3)}

@@ -21,6 +21,7 @@ Two transports with identical semantics:
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import List, Optional
 
@@ -74,6 +75,14 @@ class ExpertParallel:
         self._recv_i = 0
         self._send_i = 0
         self._cap_rows = 0
+        # tile flow of the fused read (see fused_read): per staging slot, counters of landed rows per tile of the
+        # receive buffer and of finished epilogue warps per tile of the send buffer, and how often each send slot
+        # has been used that way (its counters only grow)
+        self._ready: List[torch.Tensor] = []
+        self._done: List[torch.Tensor] = []
+        self._done_uses = [0, 0]
+        self.wait_limit_ms = 0.0               # 0 = the kernels' own bound (2 s)
+        self.fused = os.environ.get("UTTT_B200_EP_FUSED", "1") != "0"
 
     # ------------------------------------------------------------------ helpers
     def local_experts(self) -> slice:
@@ -93,9 +102,13 @@ class ExpertParallel:
             return
         from .symm import SymmetricHeap
         slot = cap_rows * self.max_row_bytes
-        self.heap = SymmetricHeap(self.device, self.group, capacity_bytes=4 * (slot + 4096) + (1 << 20))
+        self.heap = SymmetricHeap(self.device, self.group,
+                                  capacity_bytes=4 * (slot + 4096) + 16 * (cap_rows // TILE + 1024) + (1 << 20))
         self._recv = [self.heap.alloc(slot, torch.uint8) for _ in range(2)]
         self._send = [self.heap.alloc(slot, torch.uint8) for _ in range(2)]
+        tiles = cap_rows // TILE
+        self._ready = [self.heap.alloc(tiles, torch.int32).zero_() for _ in range(2)]
+        self._done = [self.heap.alloc(tiles, torch.int32).zero_() for _ in range(2)]
         self._cap_rows = cap_rows
         self.heap.barrier()
 
@@ -186,6 +199,51 @@ class ExpertParallel:
 
     def barrier(self) -> None:
         self.heap.barrier()
+
+    # ------------------------------------------------------------------ fused read (forward only)
+    def can_fuse_read(self, rows: torch.Tensor, w02: torch.Tensor, w1: torch.Tensor) -> bool:
+        """The tile-driven read serves bf16 rows on the peer transport when autograd does not record (the first
+        forward of a recomputed region, evaluation, generation); a recorded forward uses dispatch / combine."""
+        return (self.fused and self.transport == "peer" and not torch.is_grad_enabled() and rows.is_cuda
+                and w02.dtype == torch.bfloat16 and w1.dtype == torch.bfloat16 and w02.shape[1] % 256 == 0
+                and rows.shape[-1] % 64 == 0)
+
+    def fused_read(self, rows: torch.Tensor, weights: torch.Tensor, w02: torch.Tensor, w1: torch.Tensor,
+                   plan: EPPlan) -> torch.Tensor:
+        """y[r] = sum_j weights[r, j] * W1_e (silu(W0_e x_r) * W2_e x_r) with the rows travelling tile by tile.
+
+        Four kernels, no host-side ordering between them and no staging copies:
+        1. ``ep_push`` stores every routed copy at its place in its owner's receive buffer over NVLink and counts the
+           rows that have landed per 128-row tile (in the owner's memory);
+        2. the owner's gate|up GEMM (SwiGLU in its epilogue) starts each row tile as soon as its count is complete
+           (bounded wait in the TMA producer), while later tiles are still in flight;
+        3. the owner's down-projection GEMM writes straight into its send buffer and bumps a per-tile counter from
+           every epilogue warp once the warp's rows are in memory;
+        4. ``ep_pull`` on the home rank waits (bounded) for the counters of the tiles it reads, loads the rows over
+           NVLink, un-permutes and forms the gate-weighted sum.
+        A wait that runs out writes the device status word (62 / 63); nothing hangs.
+        """
+        ext = load(required=True)
+        rows = rows.contiguous()
+        d = rows.shape[1]
+        r_owner = plan.owner.rows_padded
+        tiles = r_owner // TILE
+        ri, si = self._recv_i, self._send_i
+        recv = self._slot(self._recv, "recv", r_owner, d, rows.dtype)
+        send = self._slot(self._send, "send", r_owner, d, rows.dtype)
+        ready, done = self._ready[ri], self._done[si]
+        ext.ep_push(rows, None, *_map_args(plan)[:3], plan.sizes32, plan.remote_start, self.heap.peer_ptrs(recv),
+                    self.E, plan.rows_per_batch, r_owner, self.heap.peer_ptrs(ready))
+        g = plan.owner.num_groups
+        hid = ext.gg_nt_swiglu(recv, w02.reshape(g, w02.shape[-2], d), plan.owner.tile_group, ready[:tiles], TILE,
+                               self.wait_limit_ms)
+        ready.zero_()           # after the GEMM in stream order; the peers' next stores into this slot come later
+        ext.gg_nt(hid, w1.reshape(g, d, w1.shape[-1]), plan.owner.tile_group, send, None, 0, done[:tiles],
+                  self.wait_limit_ms)
+        self._done_uses[si] += 1
+        target = self._done_uses[si] * int(ext.gg_nt_done_per_tile(d))
+        return ext.ep_pull(self.heap.peer_ptrs(send), weights, *_map_args(plan), self.E, plan.rows_per_batch, d,
+                           rows.dtype, r_owner, self.heap.peer_ptrs(done), target, self.wait_limit_ms)
 
 
 def _map_args(plan: EPPlan):
