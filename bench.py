@@ -105,6 +105,7 @@ def run_ours(args):
     status = int(ext.gemm_status(torch.zeros(1, device=dev))[0])
     tokens_per_step = args.per_gpu_batch * seq * world
     h2d = host_batches[0]["input_ids"].numel() * host_batches[0]["input_ids"].element_size()
+    out = None
     if rank == 0:
         peak_gb = torch.cuda.max_memory_allocated(dev) / 2 ** 30
         out = {
@@ -131,8 +132,51 @@ def run_ours(args):
                     "last_loss": losses[-1] if losses else None},
             "gpu_launches": launches, "peak_mem_gib": round(peak_gb, 2), "kernel_status": status,
         }
-        print(json.dumps(out), flush=True)
     eng.release_graphs()
+    # extra key: the same step with the pool's experts sharded over all ranks (expert parallelism).  The headline run
+    # above keeps every sequence's pool on its own rank, as the reference does.
+    want_ep = (world > 1 and args.expert_parallel <= 1 and not args.no_ep_extra and args.model != "124M-uttt-dense"
+               and cfg.memory_num_experts % world == 0)
+    if want_ep:
+        import gc
+        import threading
+
+        def give_up():
+            # the extra measurement must never cost the headline line
+            if out is not None:
+                out["ep"] = {"unavailable": "the expert-parallel measurement did not finish within its time limit"}
+                print(json.dumps(out), flush=True)
+            sys.stdout.flush()
+            os._exit(0)
+        guard = threading.Timer(float(args.ep_extra_limit), give_up)
+        guard.daemon = True
+        guard.start()
+        ep_line = None
+        try:
+            del eng
+            gc.collect()
+            torch.cuda.empty_cache()
+            cfg_ep = named_config(args.model, **{**over, "memory_expert_parallel": world})
+            eng = TrainEngine(cfg_ep, EngineConfig(micro_batch_size=args.micro_batch, lr=1e-3, eps=1e-15,
+                                                   warmup_steps=1024, total_steps=40960, seed=42,
+                                                   keep_activation_layers=keep), dev)
+            for _ in range(2):
+                float(eng.train_step(next(data)))
+            ep_batches = [{k: v.to(dev) for k, v in next(data).items()} for _ in range(2)]
+            ms_ep, launches_ep, clocks_ep = timed(lambda b: eng.train_step(b), ep_batches)
+            ep_line = {"value": tokens_per_step / (ms_ep / 1e3), "unit": "tokens/s", "ms_per_step": ms_ep, "steps": 2,
+                       "warmup": 2, "expert_parallel": world, "vs_expert_parallel_off": ms / ms_ep,
+                       "read_path": "tile-driven (row counters per tile, bounded waits)"
+                       if eng.expert_parallel is not None and eng.expert_parallel.fused else "host-ordered",
+                       "kernel_status": int(ext.gemm_status(torch.zeros(1, device=dev))[0]), "clocks": clocks_ep,
+                       "gpu_launches": launches_ep}
+        except Exception as exc:                       # e.g. out of memory: report, keep the headline
+            ep_line = {"unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"}
+        guard.cancel()
+        if out is not None:
+            out["ep"] = ep_line
+    if out is not None:
+        print(json.dumps(out), flush=True)
     _leave(world)
 
 
@@ -253,6 +297,9 @@ def main():
     ap.add_argument("--per-gpu-batch", type=int, default=4)
     ap.add_argument("--micro-batch", type=int, default=int(os.environ.get("UTTT_BENCH_MICRO_BATCH", "4")))
     ap.add_argument("--backward-mode", default="full")
+    ap.add_argument("--no-ep-extra", action="store_true",
+                    help="skip the extra expert-parallel measurement that multi-GPU runs add under the key 'ep'")
+    ap.add_argument("--ep-extra-limit", type=float, default=300.0, help="seconds allowed for that measurement")
     ap.add_argument("--dense-gemm", default="library", choices=["library", "own"],
                     help="dense projections on cuBLAS (default) or on the batched tcgen05 kernel of this repository")
     ap.add_argument("--no-cuda-graph", action="store_true",

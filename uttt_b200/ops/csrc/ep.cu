@@ -121,14 +121,9 @@ __device__ __forceinline__ void ep_locate(const EpMap& m, long long copy, int& p
 // ------------------------------------------------------------------------------------ push
 // VEC = 16-byte pieces per row (row_bytes / 16); rows are moved as raw bytes except when a weight scales them.
 // `ready` (optional): per-owner arrays of row counters, one per 128-row tile of the owner's buffer.  A warp that has
-// stored a row adds one to the counter of the row's tile (after a system-scope fence), the warp that zeroes the
-// padding rows of a group adds their number: a tile whose counter reaches 128 is complete, and the owner's grouped
+// stored its rows adds one per row to the counter of the row's tile (after a system-scope fence) and, for a group
+// whose padding rows it zeroed, their number: a tile whose counter reaches 128 is complete, and the owner's grouped
 // GEMM may start on it while other tiles are still in flight.
-__device__ __forceinline__ void ep_signal_rows(const EpPeers& ready, int peer, long long pos, unsigned int rows) {
-  __threadfence_system();
-  atomicAdd_system(reinterpret_cast<unsigned int*>(ready.p[peer]) + pos / kTile, rows);
-}
-
 template <typename T>
 __global__ void __launch_bounds__(256) ep_push_kernel(const T* __restrict__ src, const float* __restrict__ weights,
                                                       EpMap m, const int* __restrict__ sizes_local, EpPeers peers,
@@ -163,10 +158,6 @@ __global__ void __launch_bounds__(256) ep_push_kernel(const T* __restrict__ src,
         else *reinterpret_cast<float4*>(reinterpret_cast<float*>(d) + v * 4) = make_float4(f[0], f[1], f[2], f[3]);
       }
     }
-    if (ready.p[0] != nullptr) {
-      __syncwarp();
-      if (lane == 0) ep_signal_rows(ready, peer, pos, 1u);
-    }
   }
   // zero the padding rows of this sender's groups in the owners' buffers
   for (long long g = warp; g < groups; g += nwarps) {
@@ -174,17 +165,30 @@ __global__ void __launch_bounds__(256) ep_push_kernel(const T* __restrict__ src,
     const int padded = (sz + kTile - 1) / kTile * kTile;
     const int e = (int)(g % m.E);
     T* base = reinterpret_cast<T*>(peers.p[e / m.El]) + (long long)m.remote_start[g] * D;
-    unsigned int zeroed = 0;
     for (int row = sz; row < padded; ++row)
-      if ((long long)m.remote_start[g] + row < m.cap_rows) {
-        for (int v = lane; v < nv; v += 32) reinterpret_cast<uint4*>(base + (long long)row * D)[v] = make_uint4(0, 0, 0, 0);
-        ++zeroed;
-      }
-    if (ready.p[0] != nullptr && zeroed > 0) {
-      // the padding rows of a group all lie in its last tile
-      __syncwarp();
-      if (lane == 0) ep_signal_rows(ready, e / m.El, (long long)m.remote_start[g] + sz, zeroed);
-    }
+      if ((long long)m.remote_start[g] + row < m.cap_rows)
+      for (int v = lane; v < nv; v += 32) reinterpret_cast<uint4*>(base + (long long)row * D)[v] = make_uint4(0, 0, 0, 0);
+  }
+  if (ready.p[0] == nullptr) return;
+  // Count the rows of this warp as landed: ONE system-scope fence per lane after all of the warp's stores (a fence
+  // per row made every row wait for its own NVLink round trip), then the additions, one lane per row / group.
+  __threadfence_system();
+  __syncwarp();
+  for (long long c = warp + (long long)lane * nwarps; c < copies; c += 32 * nwarps) {
+    int peer;
+    long long pos;
+    ep_locate(m, c, peer, pos);
+    if (pos < m.cap_rows) atomicAdd_system(reinterpret_cast<unsigned int*>(ready.p[peer]) + pos / kTile, 1u);
+  }
+  for (long long g = warp + (long long)lane * nwarps; g < groups; g += 32 * nwarps) {
+    const int sz = sizes_local[g];
+    const int padded = (sz + kTile - 1) / kTile * kTile;
+    const long long first = (long long)m.remote_start[g] + sz;       // the padding rows all lie in the last tile
+    long long zeroed = padded - sz;
+    if (first + zeroed > m.cap_rows) zeroed = m.cap_rows > first ? m.cap_rows - first : 0;
+    if (zeroed > 0)
+      atomicAdd_system(reinterpret_cast<unsigned int*>(ready.p[(int)(g % m.E) / m.El]) + first / kTile,
+                       (unsigned int)zeroed);
   }
 }
 
@@ -202,12 +206,13 @@ struct EpDone {
   int P;
 };
 
-__device__ __forceinline__ bool ep_wait_tile(const EpDone& dn, int peer, int tile, unsigned int* seen, int lane) {
+// Called by the whole warp; lanes with `active` each wait for their own (peer, tile), so the flags of the k copies
+// of a row are polled side by side.
+__device__ __forceinline__ bool ep_wait_tile(const EpDone& dn, bool active, int peer, int tile, unsigned int* seen) {
   const int word = peer * ((dn.tiles + 31) / 32) + (tile >> 5);
   const unsigned int bit = 1u << (tile & 31);
-  if (seen[word] & bit) return true;             // another warp of this block has already seen it complete
   int ok = 1;
-  if (lane == 0) {
+  if (active && !(seen[word] & bit)) {           // else: another warp of this block has already seen it complete
     const unsigned int* flag = reinterpret_cast<const unsigned int*>(dn.flags.p[peer]) + tile;
     uint64_t t0 = 0;
     ok = 0;
@@ -227,7 +232,7 @@ __device__ __forceinline__ bool ep_wait_tile(const EpDone& dn, int peer, int til
     if (ok) atomicOr(&seen[word], bit);
     else if (dn.status != nullptr) atomicCAS(dn.status, 0, 63);
   }
-  ok = __shfl_sync(0xffffffffu, ok, 0);
+  ok = __all_sync(0xffffffffu, ok);
   __syncwarp();
   return ok != 0;
 }
@@ -246,20 +251,17 @@ __global__ void __launch_bounds__(256) ep_pull_kernel(T* __restrict__ out, const
     __syncthreads();
     // every rank's first counter is waited for whether or not rows of this rank went there, so that no rank runs
     // ahead of a peer it happens not to read from (buffer reuse is ordered by these waits)
-    if (blockIdx.x == 0 && (threadIdx.x >> 5) < dn.P) {
-      if (!ep_wait_tile(dn, threadIdx.x >> 5, 0, seen, lane)) return;
+    if (blockIdx.x == 0 && threadIdx.x < 32) {
+      if (!ep_wait_tile(dn, lane < dn.P, lane < dn.P ? lane : 0, 0, seen)) return;
     }
   }
   for (long long r = warp; r < rows; r += nwarps) {
     if (flow) {
-      bool ok = true;
-      for (int j = 0; j < m.k && ok; ++j) {
-        int peer;
-        long long pos;
-        ep_locate(m, r * m.k + j, peer, pos);
-        if (pos < m.cap_rows) ok = ep_wait_tile(dn, peer, (int)(pos / kTile), seen, lane);
-      }
-      if (!ok) return;
+      int peer = 0;
+      long long pos = 0;
+      const bool mine = lane < m.k;              // lane j waits for the tile of copy j
+      if (mine) ep_locate(m, r * m.k + lane, peer, pos);
+      if (!ep_wait_tile(dn, mine && pos < m.cap_rows, peer, (int)(pos / kTile), seen)) return;
     }
     for (int v = lane; v < nv; v += 32) {
       float acc[8];

@@ -265,6 +265,7 @@ __global__ void __launch_bounds__((EPI != kEpiNone ? kFusedWarps : 4) * 32 + 64)
     // 128-byte row segments instead of 16-byte pieces at a row pitch.
     uint32_t acc_it = 0, slab_it = 0;
     bool ok = true;
+    int reported = -1;                     // row tile whose completion this warp still has to report (p.done)
     const int r = warp * 32 + lane;
     const uint32_t slab_base = smem_base + L::kOutOffset + warp * 8192;
     constexpr int SUBW = 128 / (int)sizeof(OutT);      // output columns per 128-byte staging row
@@ -399,12 +400,21 @@ __global__ void __launch_bounds__((EPI != kEpiNone ? kFusedWarps : 4) * 32 + 64)
       ptx::mbar_arrive(acc_empty(ab));
       ++acc_it;
       if (MODE == kNT && p.done != nullptr && lane == 0) {
-        ptx::tma_store_wait_all();         // this warp's rows of the tile are written, not just read from the slabs
-        ptx::fence_proxy_async_all();
-        signal_tile_done(p, id / tiles_n);
+        // Report the PREVIOUS tile of this warp: its stores are written once at most this tile's BN / SUBW store
+        // groups are still in flight, so the report costs no stall (waiting for the tile just issued did).
+        if (reported >= 0) {
+          ptx::tma_store_wait_written<BN / SUBW>();
+          ptx::fence_proxy_async_all();
+          signal_tile_done(p, reported);
+        }
+        reported = id / tiles_n;
       }
     }
     if (lane == 0) ptx::tma_store_wait_all();
+    if (MODE == kNT && p.done != nullptr && lane == 0 && reported >= 0) {
+      ptx::fence_proxy_async_all();
+      signal_tile_done(p, reported);
+    }
   }
   ptx::tc_fence_before_sync();
   __syncthreads();

@@ -123,6 +123,35 @@ def main():
             t_ordered = _time(read_ordered, args.iters, flush)
             t_fused = _time(lambda: ep.fused_read(rows, w, w02, w1, eplan), args.iters, flush)
             t_gemms = _time(read_gemms_only, args.iters, flush)
+            # the four kernels of the tile-driven chain one by one (counters already satisfied, so nothing waits)
+            tiles = cap // 128
+            rdy, dne = ep._ready[0], ep._done[0]
+            snd = ep._slot(ep._send, "send", cap, d, rows.dtype)
+            full = torch.full_like(rdy, 1 << 30)
+            hid0 = F_ops.gg_swiglu(xp, w02, eplan.owner)
+            t_push_sig = _time(lambda: ext.ep_push(rows, None, *_map_args(eplan)[:3], eplan.sizes32,
+                                                   eplan.remote_start, ptrs, e, n, cap, ep.heap.peer_ptrs(rdy)),
+                               args.iters, flush)
+            dist.barrier()
+            rdy.zero_()
+            t_up_flow = _time(lambda: ext.gg_nt_swiglu(slot, w02, eplan.owner.tile_group, full[:tiles], 128, 0.0),
+                              args.iters, flush)
+            t_up = _time(lambda: ext.gg_nt_swiglu(slot, w02, eplan.owner.tile_group), args.iters, flush)
+            t_down_flow = _time(lambda: ext.gg_nt(hid0, w1, eplan.owner.tile_group, snd, None, 0, dne[:tiles], 0.0),
+                                args.iters, flush)
+            t_down = _time(lambda: ext.gg_nt(hid0, w1, eplan.owner.tile_group, snd), args.iters, flush)
+            dist.barrier()
+            t_pull_flow = _time(lambda: ext.ep_pull(ep.heap.peer_ptrs(snd), w, *_map_args(eplan), e, n, d, rows.dtype,
+                                                    cap, ep.heap.peer_ptrs(dne), 1, 0.0), args.iters, flush)
+            dist.barrier()
+            for t in ep._done:
+                t.zero_()
+            ep._done_uses = [0, 0]
+            dist.barrier()
+            pieces = {"push_with_row_counts_ms": round(t_push_sig, 4), "push_plain_ms": round(t_push, 4),
+                      "gate_up_gemm_with_tile_waits_ms": round(t_up_flow, 4), "gate_up_gemm_plain_ms": round(t_up, 4),
+                      "down_gemm_with_tile_reports_ms": round(t_down_flow, 4), "down_gemm_plain_ms": round(t_down, 4),
+                      "pull_with_tile_waits_ms": round(t_pull_flow, 4), "pull_plain_ms": round(t_pull, 4)}
             flops = 6.0 * b * n * k * d * inter
             peak = _measured_tflops()
             t_compute = flops / peak / 1e9
@@ -134,7 +163,7 @@ def main():
                           "nvlink_at_measured_770GBs_ms": round(t_link, 4),
                           "tile_driven_roofline_frac": round(max(t_compute, t_link) / t_fused, 3),
                           "host_ordered_roofline_frac": round(max(t_compute, t_link) / t_ordered, 3),
-                          "kernel_status": status}
+                          "kernel_status": status, "kernels": pieces}
             out["read_through_owners"] = extra_read
             extra = {"push_kernel_ms": round(t_push, 4), "pull_kernel_ms": round(t_pull, 4),
                      "push_kernel_frac_of_measured_peer_copy": round(nvlink_bytes / t_push / 1e6 / 770.0, 3),
