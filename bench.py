@@ -130,7 +130,8 @@ def run_ours(args):
             "e2e": {"value": tokens_per_step / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4, "clocks": clocks_e2e,
                     "last_loss": losses[-1] if losses else None},
-            "gpu_launches": launches, "peak_mem_gib": round(peak_gb, 2), "kernel_status": status,
+            "gpu_launches": launches, "peak_mem_gib": round(peak_gb, 2),
+            "peak_reserved_gib": round(torch.cuda.max_memory_reserved(dev) / 2 ** 30, 2), "kernel_status": status,
         }
     eng.release_graphs()
     # extra key: the same step with the pool's experts sharded over all ranks (expert parallelism).  The headline run

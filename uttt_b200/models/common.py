@@ -101,6 +101,9 @@ class SlidingWindowAttention(nn.Module):
         self.v_proj = nn.Linear(self.hidden_size, self.kv_dim, bias=config.qkv_bias)
         self.o_proj = nn.Linear(self.hidden_size, self.hidden_size, bias=False) \
             if config.enable_attention_output_proj else None
+        # set by the model around a training forward whose regions are recomputed in backward: the attention output
+        # of the first pass (25 MB per chunk at the 760M shape) is kept and handed to the recomputation
+        self.reuse_store: Optional[dict] = None
 
     def history_len(self, chunk: int) -> int:
         """Keys carried between chunks.  A window of W needs W-1 predecessors; W are kept when that makes the
@@ -131,7 +134,8 @@ class SlidingWindowAttention(nn.Module):
             full_v = torch.cat([v_hist, v], dim=1)
         else:
             full_k, full_v = k, v
-        o = ops.swa_attention(q, full_k, full_v, self.window_size, causal=True)
+        reuse = None if self.reuse_store is None else (self.reuse_store, offset)
+        o = ops.swa_attention(q, full_k, full_v, self.window_size, causal=True, reuse=reuse)
         o = o.reshape(b, l, self.hidden_size)
         if self.o_proj is not None:
             o = ops.linear(o, self.o_proj.weight)

@@ -67,10 +67,10 @@ class Routing:
 
 
 def route_rows(rows: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Tensor], cfg,
-               bias_in_logits: bool = False, ep=None) -> Routing:
+               bias_in_logits: bool = False, ep=None, reuse=None) -> Routing:
     """rows: [B, N, D]; router: [E, D] (fp32 logits outside autocast; moe_routing.py:7-75).
     With an expert-parallel handle the routing also carries the cross-rank plan."""
-    routing = _route_rows_local(rows, router, bias, cfg, bias_in_logits)
+    routing = _route_rows_local(rows, router, bias, cfg, bias_in_logits, reuse)
     if ep is not None and ep.P > 1:
         routing.ep = ep
         routing.ep_plan = ep.plan(routing.plan, routing.idx)
@@ -78,7 +78,9 @@ def route_rows(rows: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Te
 
 
 def _route_rows_local(rows: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Tensor], cfg,
-                      bias_in_logits: bool = False) -> Routing:
+                      bias_in_logits: bool = False, reuse=None) -> Routing:
+    """``reuse = (dict, key)``: routing and layout of the first pass over a region are handed to its recomputation
+    (see ops.functional._Router)."""
     bsz, n, _ = rows.shape
     e = router.shape[0]
     k = cfg.memory_num_active_experts
@@ -89,8 +91,9 @@ def _route_rows_local(rows: torch.Tensor, router: torch.Tensor, bias: Optional[t
         return Routing(plan, ones, ones.view(bsz, n).sum(1, keepdim=True), plan.sizes.view(bsz, 1).float(), idx=idx)
     idx, weights, psum = ops.route_topk(rows, router, bias, k, cfg.memory_router_alpha, bias_in_logits,
                                         cfg.memory_router_combine_mode == "topk_renorm", cfg.memory_router_type,
-                                        cfg.memory_router_scale, cfg.memory_router_norm_eps)
-    plan = ops.build_group_plan(idx, e)
+                                        cfg.memory_router_scale, cfg.memory_router_norm_eps,
+                                        reuse=None if reuse is None else (reuse[0], (reuse[1], "route")))
+    plan = ops.build_group_plan(idx, e, None if reuse is None else (reuse[0], (reuse[1], "plan")))
     return Routing(plan, weights, psum, plan.sizes.view(bsz, e).float(), idx=idx)
 
 

@@ -14,6 +14,8 @@ same tile-padded layout, grouped GEMMs and fused write-gradient node serve the d
 """
 from __future__ import annotations
 
+import os
+
 from typing import Any, List, Optional, Tuple
 
 import torch
@@ -289,6 +291,10 @@ class DenseFWModel(nn.Module):
         hist = [(None, None)] * n_layers
         keep = self.layers[0].attn.history_len(chunk) if cfg.window_size is not None else None
         outputs = []
+        reuse = (self.activation_checkpoint and self.training and torch.is_grad_enabled()
+                 and os.environ.get("UTTT_B200_REUSE_ATTENTION", "1") != "0")
+        for layer in self.layers:
+            layer.attn.reuse_store = {} if reuse else None      # attention outputs kept for the recomputation
         for start in range(0, seq_len, chunk):
             end = min(start + chunk, seq_len)
             h = inputs_embeds[:, start:end]

@@ -15,6 +15,8 @@ Design differences (same math):
 """
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass
 from typing import Any, Dict, List, Optional, Tuple
 
@@ -71,7 +73,15 @@ class MoEBlock(nn.Module):
         self.mlp_norm = RMSNorm(d, eps=config.norm_eps)
         self.mlp = GatedMLP(d, config.mlp_intermediate_size)
         self.ep = None            # expert-parallel handle, set by the model
+        self.write_recomputed = False   # set by the model: the chunk write of this layer runs twice (recomputation)
         self.route_stats = None   # (reads, writes) RouteStats while the model collects pool statistics
+
+    def _reuse(self, offset: int, what: str):
+        """(store, key) under which a routed call of this layer keeps its result for the recomputation, or None."""
+        store = self.attn.reuse_store
+        if store is None or self.ep is not None or os.environ.get("UTTT_B200_REUSE_ROUTING", "1") == "0":
+            return None
+        return (store, (offset, what))
 
     # -------------------------------------------------------------------------- read
     def forward(self, h, k_hist, v_hist, w02, w1, router, bias, offset: int):
@@ -89,7 +99,8 @@ class MoEBlock(nn.Module):
                 x_mem_in = x_attn_in
             mem = self.memory
             q_rows = mem.head_rows(mem.prep_query(q_flat, offset))
-            routing = fw.route_rows(q_rows, router, bias, cfg, getattr(cfg, "memory_bias_in_logits", False), self.ep)
+            routing = fw.route_rows(q_rows, router, bias, cfg, getattr(cfg, "memory_bias_in_logits", False), self.ep,
+                                    reuse=self._reuse(offset, "read"))
             if self.route_stats is not None:          # set by the model for the first pass of a statistics step
                 self.route_stats[0].add(q_rows, router, routing.weights)
             y = fw.pool_read(q_rows, w02, w1, routing)
@@ -122,7 +133,8 @@ class MoEBlock(nn.Module):
         k_rows = mem.head_rows(mem.prep_key(k_flat, offset))
         v_rows = mem.head_rows(mem.prep_value(v_flat))
         route_in = v_rows if cfg.memory_router_from_v else k_rows
-        routing = fw.route_rows(route_in, router, bias, cfg, getattr(cfg, "memory_bias_in_logits", False), self.ep)
+        routing = fw.route_rows(route_in, router, bias, cfg, getattr(cfg, "memory_bias_in_logits", False), self.ep,
+                                reuse=self._reuse(offset, "write") if self.write_recomputed else None)
         if self.route_stats is not None:
             self.route_stats[1].add(route_in, router, routing.weights)
         g02, g1 = fw.pool_raw_grad(k_rows, v_rows, lr_rows, w02, w1, routing, acc=acc)
@@ -509,6 +521,12 @@ class UTTTMoEModel(nn.Module):
             self._writer_idx = cached
         return cached
 
+    def _reuse_attention(self, layer_idx: int) -> bool:
+        """Whether layer ``layer_idx`` keeps its attention outputs for the recomputation of its regions."""
+        return (self.activation_checkpoint and self.training and torch.is_grad_enabled()
+                and layer_idx not in self.keep_activation_layers
+                and os.environ.get("UTTT_B200_REUSE_ATTENTION", "1") != "0")
+
     def _ckpt(self, fn, *args):
         if self.activation_checkpoint and torch.is_grad_enabled():
             return checkpoint(fn, *args, use_reentrant=False, preserve_rng_state=False)
@@ -522,6 +540,8 @@ class UTTTMoEModel(nn.Module):
             inputs_embeds = self.embeddings(input_ids)
         if cfg.use_memory_block:
             self._maybe_update_loss_free_bias()
+        for layer in self.layers:
+            layer.attn.reuse_store = None
         if use_cache and not self.training:
             from .generation import forward_with_cache
             return forward_with_cache(self, inputs_embeds, past_key_values)
@@ -553,8 +573,10 @@ class UTTTMoEModel(nn.Module):
         from . import moe_stats as ms
         collect = cfg.use_memory_block and self.num_experts > 1 and self.training and ms.stats_enabled()
         routes = (ms.RouteStats(), ms.RouteStats()) if collect else None
-        for layer in self.layers:
+        for li, layer in enumerate(self.layers):
             layer.route_stats = routes
+            layer.attn.reuse_store = {} if self._reuse_attention(li) else None
+            layer.write_recomputed = cfg.memory_update_backward_mode not in ("stop_state", "cross_layer_cut")
         for start in range(0, seq_len, chunk):
             end = min(start + chunk, seq_len)
             h = inputs_embeds[:, start:end]

@@ -231,10 +231,22 @@ class _SWA(torch.autograd.Function):
     otherwise the flash-attn library backward fed with this forward's output and log-sum-exp."""
 
     @staticmethod
-    def forward(ctx, q, k, v, window, causal, scale):
+    def forward(ctx, q, k, v, window, causal, scale, reuse=None):
         ext = cuda_ext(q)
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-        o, lse = ext.swa_fwd(q, k, v, int(window or 0), bool(causal), float(scale))
+        hit = None
+        if reuse is not None:
+            # (store, key): the first call under this key keeps its output and log-sum-exp in the store, the second
+            # call (the recomputation of a checkpointed region, same inputs) takes them back instead of running the
+            # kernel again.  The output is a fraction of the size of what the region would otherwise have to keep.
+            store, key = reuse
+            hit = store.pop(key, None)
+        if hit is not None:
+            o, lse = hit
+        else:
+            o, lse = ext.swa_fwd(q, k, v, int(window or 0), bool(causal), float(scale))
+            if reuse is not None:
+                store[key] = (o.detach(), lse)        # an alias that never carries autograd history
         ctx.save_for_backward(q, k, v, o, lse)
         ctx.args = (window, causal, scale)
         return o
@@ -246,21 +258,22 @@ class _SWA(torch.autograd.Function):
         ext = cuda_ext(q)
         if hasattr(ext, "swa_bwd"):
             dq, dk, dv = ext.swa_bwd(do.contiguous(), q, k, v, o, lse, int(window or 0), bool(causal), float(scale))
-            return dq, dk, dv, None, None, None
+            return dq, dk, dv, None, None, None, None
         from flash_attn.flash_attn_interface import _flash_attn_backward
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         left = -1 if (window is None or not causal) else window - 1
         _flash_attn_backward(do.contiguous(), q, k, v, o, lse, dq, dk, dv, 0.0, float(scale), bool(causal),
                              left, 0 if causal else -1, 0.0, None, False)
-        return dq, dk, dv, None, None, None
+        return dq, dk, dv, None, None, None, None
 
 
-def swa_attention(q, k, v, window: Optional[int], causal: bool = True, scale: Optional[float] = None):
-    """Sliding-window attention; queries are aligned to the last ``lq`` keys.  [b, l, h, hd] layout."""
+def swa_attention(q, k, v, window: Optional[int], causal: bool = True, scale: Optional[float] = None, reuse=None):
+    """Sliding-window attention; queries are aligned to the last ``lq`` keys.  [b, l, h, hd] layout.
+    ``reuse = (dict, key)``: keep the result of the first call under ``key`` for the second one (see ``_SWA``)."""
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
     if _kernel("swa_fwd", q) is not None and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 96, 128) \
             and q.shape[2] == k.shape[2]:
-        return _SWA.apply(q, k, v, window, causal, scale)
+        return _SWA.apply(q, k, v, window, causal, scale, reuse if torch.is_grad_enabled() else None)
     if q.is_cuda:
         return _sdpa_attention(q, k, v, window, causal, scale)
     return ref.swa_attention(q, k, v, window, causal, scale)
@@ -324,7 +337,17 @@ class GroupPlan:
     pairs: Optional[tuple] = None   # (entries [tiles, 2], count [1]) of the two-CTA GEMMs, built on first use
 
 
-def build_group_plan(expert_idx: torch.Tensor, num_experts: int) -> GroupPlan:
+def build_group_plan(expert_idx: torch.Tensor, num_experts: int, reuse=None) -> GroupPlan:
+    """``reuse = (dict, key)``: the first call under ``key`` keeps its plan, the second one (the recomputation of the
+    same region, same routing) takes it back."""
+    if reuse is not None and torch.is_grad_enabled():
+        store, key = reuse
+        hit = store.pop(key, None)
+        if hit is not None:
+            return hit
+        plan = build_group_plan(expert_idx, num_experts)
+        store[key] = plan
+        return plan
     bsz, n, k = expert_idx.shape
     ext = _kernel("build_group_plan", expert_idx)
     if ext is not None and num_experts <= 256:
@@ -623,11 +646,23 @@ class _Router(torch.autograd.Function):
     """Fused router (logits, softmax or normalised variant, top-k, combine weights, per-sequence probability sums)."""
 
     @staticmethod
-    def forward(ctx, rows, router, bias, topk, rows_per_batch, alpha, bias_in_logits, renorm, mode, rscale, eps):
+    def forward(ctx, rows, router, bias, topk, rows_per_batch, alpha, bias_in_logits, renorm, mode, rscale, eps,
+                reuse=None):
         ext = cuda_ext(rows)
-        idx, w, probs, psum, logits = ext.router_fwd(rows, router, bias, int(topk), int(rows_per_batch), float(alpha),
-                                                     bool(bias_in_logits), bool(renorm), int(mode), float(rscale),
-                                                     float(eps))
+        hit = None
+        if reuse is not None:
+            # (store, key), as in _SWA: the recomputation of a region takes the routing of its first pass back
+            # (a few MB per call) instead of running the router again
+            store, key = reuse
+            hit = store.pop(key, None)
+        if hit is not None:
+            idx, w, probs, psum, logits = hit
+        else:
+            idx, w, probs, psum, logits = ext.router_fwd(rows, router, bias, int(topk), int(rows_per_batch),
+                                                         float(alpha), bool(bias_in_logits), bool(renorm), int(mode),
+                                                         float(rscale), float(eps))
+            if reuse is not None:
+                store[key] = (idx.detach(), w.detach(), probs, psum.detach(), logits)
         ctx.save_for_backward(rows, router, probs, idx, logits)
         ctx.args = (int(rows_per_batch), float(alpha), bool(renorm), int(mode), float(rscale), float(eps))
         ctx.mark_non_differentiable(idx)
@@ -640,12 +675,13 @@ class _Router(torch.autograd.Function):
         ext = cuda_ext(rows)
         drows, drouter = ext.router_bwd(rows, router, probs, idx, gw, gpsum, rpb, alpha, renorm,
                                         bool(ctx.needs_input_grad[0]), mode, rscale, eps, logits if mode else None)
-        return (drows if ctx.needs_input_grad[0] else None), drouter, None, None, None, None, None, None, None, None, None
+        return ((drows if ctx.needs_input_grad[0] else None), drouter, None, None, None, None, None, None, None, None,
+                None, None)
 
 
 def route_topk(rows, router, bias, topk: int, alpha: float = 1.0, bias_in_logits: bool = False,
                renorm: bool = False, router_type: str = "softmax", router_scale: float = 0.0,
-               norm_eps: float = 1e-6):
+               norm_eps: float = 1e-6, reuse=None):
     """rows [B, N, D], router [E, D], bias [E] or None -> (idx [B, N, k] int, weights [B*N, k] fp32,
     probs_sum [B, E] fp32).  ``router_type``: 'softmax', 'norm_softmax' (softmax of the L2-normalised logits times
     ``router_scale``, sqrt(E) when 0) or 'norm_relu' (their rectified values, normalised to sum 1).  The bias shifts
@@ -657,7 +693,8 @@ def route_topk(rows, router, bias, topk: int, alpha: float = 1.0, bias_in_logits
     if ext is not None and ext.router_supported(d, e, topk) and rows.dtype in (torch.bfloat16, torch.float32):
         idx, w, psum = _Router.apply(rows.reshape(bsz * n, d).contiguous(), router.float().contiguous(),
                                      None if bias is None else bias.detach(), topk, n, alpha, bias_in_logits, renorm,
-                                     _ROUTER_MODES[router_type], rscale, norm_eps)
+                                     _ROUTER_MODES[router_type], rscale, norm_eps,
+                                     reuse if torch.is_grad_enabled() else None)
         return idx.view(bsz, n, topk), w, psum
     logits = torch.matmul(rows.float(), router.float().t())
     if bias is not None and bias_in_logits:
