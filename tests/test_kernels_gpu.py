@@ -1178,8 +1178,10 @@ def test_training_step_is_reproducible_run_to_run():
     _status_ok()
     # a flipped bf16 rounding of the Newton-Schulz input (its Frobenius norm is an atomic fp32 sum) changes a few
     # fast-weight entries by 2^-8 relative; on the loss that is ~1e-5 relative.  A race would be orders above it.
-    for a, b_ in zip(runs[0][0], runs[1][0]):
-        assert abs(a - b_) <= 2e-4 * abs(a), (runs[0][0], runs[1][0])
+    # (the second step starts from weights that already differ in their last bits, and near-tied router logits
+    # then pick other experts for a few tokens: a few 1e-4 relative on its loss)
+    for a, b_, tol in zip(runs[0][0], runs[1][0], (2e-4, 1e-3)):
+        assert abs(a - b_) <= tol * abs(a), (runs[0][0], runs[1][0])
     for k, v in runs[0][1].items():
         w = runs[1][1][k]
         # fp32 masters after two AdamW steps: update size lr = 1e-3 per step; a differing sign of a near-zero

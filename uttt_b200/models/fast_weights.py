@@ -132,7 +132,9 @@ def pool_raw_grad(k_rows: torch.Tensor, v_rows: torch.Tensor, lr_rows: torch.Ten
 
     k_rows, v_rows: [B, N, D]; lr_rows: [B, N, 3] -> (G02 [B, E, 2I, D], G1 [B, E, D, I]) in fp32.
     With ``acc = (A02, A1)`` the gradients are added to those running sums and the sums are returned;
-    ``acc = (A02, A1, stash, last)`` defers the additions of several layers into one launch (ops.WriteStash).
+    ``acc = (A02, A1, stash, last)`` defers the additions of several layers into one launch (ops.WriteStash);
+    a fifth element ``True`` says that A02 / A1 already hold the complete sums (kept from the first pass over a
+    recomputed region): the node is recorded, the arithmetic is skipped.
     """
     bsz, n, d = k_rows.shape
     inter2 = state_w02.shape[2]
@@ -155,7 +157,8 @@ def pool_raw_grad(k_rows: torch.Tensor, v_rows: torch.Tensor, lr_rows: torch.Ten
     w1 = state_w1.reshape(g, d, inter2 // 2)
     if acc is not None:
         stash, last = (acc[2], acc[3]) if len(acc) > 2 else (None, True)
-        return ops.fw_write_grad_accumulate(kp, vp, lrp, w02, w1, plan, acc[0], acc[1], stash, last)
+        skip = bool(acc[4]) if len(acc) > 4 else False
+        return ops.fw_write_grad_accumulate(kp, vp, lrp, w02, w1, plan, acc[0], acc[1], stash, last, skip)
     g02, g1 = ops.fw_write_grad(kp, vp, lrp, w02, w1, plan)
     return g02.view(*state_w02.shape[:2], inter2, d), g1.view(*state_w02.shape[:2], d, inter2 // 2)
 

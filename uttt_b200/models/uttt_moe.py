@@ -469,12 +469,24 @@ class UTTTMoEModel(nn.Module):
             f = args[:3 * len(writers)]
             st = list(args[3 * len(writers):]) + [None] * (6 - n_state)
             s = fw.PoolState.from_tensors(st)
-            a02 = torch.zeros_like(s.m02)
-            a1 = torch.zeros_like(s.m1)
-            ms, probs, counts = [], [], []
             detach_g = mode in ("first_order_state", "stop_state")
+            # The aggregate of the first pass over this region (0.9 GB at the 760M shape) is kept for its
+            # recomputation, which then records the writers' nodes without redoing their GEMMs and reductions.
+            store = self._aggregate_store
+            kept = None
+            if (store is not None and not detach_g and self.ep is None and torch.is_grad_enabled()
+                    and ops.fw_write_accumulate_skips(s.m02, s.w02)):
+                kept = store.pop(offset, None)
+            else:
+                store = None
+            if kept is not None:
+                a02, a1 = kept
+            else:
+                a02 = torch.zeros_like(s.m02)
+                a1 = torch.zeros_like(s.m1)
+            ms, probs, counts = [], [], []
             # the writers' token reductions are added to the aggregate several layers per launch
-            stash = None if detach_g else ops.write_stash_for(a02)
+            stash = None if (detach_g or kept is not None) else ops.write_stash_for(a02)
             for wi, li in enumerate(writers):
                 args_l = (f[3 * wi], f[3 * wi + 1], f[3 * wi + 2], s.w02, s.w1, self._router(li),
                           self._router_bias(li), offset)
@@ -483,11 +495,13 @@ class UTTTMoEModel(nn.Module):
                     a02, a1 = a02 + g02.detach(), a1 + g1.detach()
                 else:
                     a02, a1, m, p, c = self.layers[li].raw_grad(
-                        *args_l, acc=(a02, a1, stash, wi == len(writers) - 1))
+                        *args_l, acc=(a02, a1, stash, wi == len(writers) - 1, kept is not None))
                 if m is not None:
                     ms.append(m.detach() if (cfg.memory_detach_m_coeff or mode == "stop_state") else m)
                 probs.append(p)
                 counts.append(c)
+            if store is not None and kept is None:
+                store[offset] = (a02.detach(), a1.detach())
             mc = None
             if cfg.memory_aggregate_momentum_mode == "pool_mean" and ms:
                 mc = torch.stack(ms, dim=0).mean(dim=0)
@@ -542,6 +556,7 @@ class UTTTMoEModel(nn.Module):
             self._maybe_update_loss_free_bias()
         for layer in self.layers:
             layer.attn.reuse_store = None
+        self._aggregate_store = None
         if use_cache and not self.training:
             from .generation import forward_with_cache
             return forward_with_cache(self, inputs_embeds, past_key_values)
@@ -573,6 +588,8 @@ class UTTTMoEModel(nn.Module):
         from . import moe_stats as ms
         collect = cfg.use_memory_block and self.num_experts > 1 and self.training and ms.stats_enabled()
         routes = (ms.RouteStats(), ms.RouteStats()) if collect else None
+        self._aggregate_store = {} if (self._reuse_attention(-1) and cfg.memory_update_backward_mode == "full"
+                                       and os.environ.get("UTTT_B200_REUSE_AGGREGATE", "1") != "0") else None
         for li, layer in enumerate(self.layers):
             layer.route_stats = routes
             layer.attn.reuse_store = {} if self._reuse_attention(li) else None

@@ -1187,9 +1187,14 @@ class _FwWriteGradAcc(torch.autograd.Function):
     :class:`WriteStash` the reduction is deferred until ``flush`` (or until the stash is full)."""
 
     @staticmethod
-    def forward(ctx, kp, vp, lrp, w02, w1, plan, acc02, acc1, stash=None, flush=True):
+    def forward(ctx, kp, vp, lrp, w02, w1, plan, acc02, acc1, stash=None, flush=True, skip=False):
         ctx.save_for_backward(kp, vp, lrp, w02, w1)
         ctx.plan = plan
+        if skip:
+            # the sums already hold the result (kept from the first pass over this region): only the node and its
+            # saved inputs are wanted
+            ctx.mark_dirty(acc02, acc1)
+            return acc02, acc1
         with torch.no_grad():
             dy02_lr, h_lr, _ = _write_inner(kp, vp, lrp, w02, w1, plan, False)
             if stash is None:
@@ -1206,7 +1211,7 @@ class _FwWriteGradAcc(torch.autograd.Function):
     def backward(ctx, c02, c1):
         grads = _FwWriteGrad.backward(ctx, c02.reshape(ctx.plan.num_groups, *c02.shape[-2:]),
                                       c1.reshape(ctx.plan.num_groups, *c1.shape[-2:]))
-        return (*grads, c02, c1, None, None)
+        return (*grads, c02, c1, None, None, None)
 
 
 def fw_write_grad(kp, vp, lrp, w02, w1, plan: GroupPlan):
@@ -1227,6 +1232,14 @@ def _fw_write_kernel_ok(kp, vp, w02, w1) -> bool:
             and kp.shape[1] % 128 == 0)
 
 
+def fw_write_accumulate_skips(acc02: torch.Tensor, w02: torch.Tensor) -> bool:
+    """Whether :func:`fw_write_grad_accumulate` runs as the in-place kernel node for these tensors, which is what a
+    caller needs to know before it hands over already complete sums with ``skip=True``."""
+    return (acc02.is_cuda and acc02.dtype == torch.float32 and w02.dtype == torch.bfloat16
+            and _kernel("gg_tn_segments", acc02) is not None and w02.shape[-1] % 128 == 0
+            and w02.shape[-2] % 256 == 0)
+
+
 def write_stash_for(acc02: torch.Tensor) -> Optional[WriteStash]:
     """A stash for the aggregate ``acc02`` when the kernel path will serve it (see :class:`WriteStash`)."""
     limit = int(os.environ.get("UTTT_B200_WRITE_STASH", "4"))
@@ -1236,16 +1249,19 @@ def write_stash_for(acc02: torch.Tensor) -> Optional[WriteStash]:
 
 
 def fw_write_grad_accumulate(kp, vp, lrp, w02, w1, plan: GroupPlan, acc02: torch.Tensor, acc1: torch.Tensor,
-                             stash: Optional[WriteStash] = None, flush: bool = True):
+                             stash: Optional[WriteStash] = None, flush: bool = True, skip: bool = False):
     """acc02 += G02, acc1 += G1 (see :func:`fw_write_grad`); returns the updated sums.
 
     On the GPU the sums are updated in place by the GEMM epilogue; elsewhere new tensors are returned.  With a
     ``stash`` the additions of several calls are fused into one launch: the sums are complete only after a call
-    with ``flush=True`` (the last writer layer).
+    with ``flush=True`` (the last writer layer).  ``skip``: the sums are already complete (see
+    :func:`fw_write_accumulate_skips`); record the node, do no arithmetic.
     """
     if _fw_write_kernel_ok(kp, vp, w02, w1) and acc02.dtype == torch.float32 and acc02.is_contiguous() \
             and acc1.is_contiguous():
-        return _FwWriteGradAcc.apply(kp, vp, lrp.float().contiguous(), w02, w1, plan, acc02, acc1, stash, flush)
+        return _FwWriteGradAcc.apply(kp, vp, lrp.float().contiguous(), w02, w1, plan, acc02, acc1, stash, flush,
+                                     skip)
+    assert not skip, "skipping is only offered where fw_write_accumulate_skips() says so"
     if stash is not None and stash.pending:
         stash.flush(plan.num_groups, acc02, acc1)
     g02, g1 = fw_write_grad(kp, vp, lrp, w02, w1, plan)
