@@ -167,8 +167,8 @@ def run_ours(args):
             ms_ep, launches_ep, clocks_ep = timed(lambda b: eng.train_step(b), ep_batches)
             ep_line = {"value": tokens_per_step / (ms_ep / 1e3), "unit": "tokens/s", "ms_per_step": ms_ep, "steps": 2,
                        "warmup": 2, "expert_parallel": world, "vs_expert_parallel_off": ms / ms_ep,
-                       "read_path": "tile-driven (row counters per tile, bounded waits)"
-                       if eng.expert_parallel is not None and eng.expert_parallel.fused else "host-ordered",
+                       "read_path": "host-ordered dispatch / combine (autograd records every training forward; "
+                                    "the tile-driven read serves forwards without autograd)",
                        "kernel_status": int(ext.gemm_status(torch.zeros(1, device=dev))[0]), "clocks": clocks_ep,
                        "gpu_launches": launches_ep}
         except Exception as exc:                       # e.g. out of memory: report, keep the headline

@@ -202,8 +202,8 @@ class ExpertParallel:
 
     # ------------------------------------------------------------------ fused read (forward only)
     def can_fuse_read(self, rows: torch.Tensor, w02: torch.Tensor, w1: torch.Tensor) -> bool:
-        """The tile-driven read serves bf16 rows on the peer transport when autograd does not record (the first
-        forward of a recomputed region, evaluation, generation); a recorded forward uses dispatch / combine."""
+        """The tile-driven read serves bf16 rows on the peer transport when autograd does not record (evaluation,
+        validation, generation); a recorded forward uses dispatch / combine."""
         return (self.fused and self.transport == "peer" and not torch.is_grad_enabled() and rows.is_cuda
                 and w02.dtype == torch.bfloat16 and w1.dtype == torch.bfloat16 and w02.shape[1] % 256 == 0
                 and rows.shape[-1] % 64 == 0)
