@@ -221,6 +221,12 @@ def run_nvs(args):
     ext = load(required=True)
     dev = torch.device("cuda", local)
     cfg = load_config(os.path.join(ROOT, "configs", "nvs", "named", "uttt_moe_256_4in2out.yaml"))
+    autoregressive = args.model == "nvs-uttt-moe-ar"
+    if autoregressive:
+        # the reference's stock layout: every view but the last is an input, every view but the first a target
+        # (2 x 5 view slots of 1024 tokens for 6 views); this is the shape its own model can run
+        cfg["model"]["view_layout"] = "autoregressive"
+        cfg["model"].pop("num_input_views", None)
     per_gpu = args.per_gpu_batch if args.per_gpu_batch != 4 else 16
     cfg["training"].update(batch_size_per_gpu=per_gpu, total_batch_size=per_gpu * world, out_dir="/tmp/uttt_nvs_bench",
                            checkpoint_every=10 ** 9, print_every=10 ** 9, warmup=0, cuda_graph=not args.no_cuda_graph)
@@ -264,14 +270,16 @@ def run_nvs(args):
     h2d = sum(v.numel() * v.element_size() for v in host_batches[0].values())
     if rank == 0:
         print(json.dumps({
-            "metric": "train scenes/s, NVS uTTT-MoE 256x256, 4 input + 2 target views", "value": scenes / (ms / 1e3),
+            "metric": ("train scenes/s, NVS uTTT-MoE 256x256, 6 views per scene in the reference's stock layout"
+                       if autoregressive else "train scenes/s, NVS uTTT-MoE 256x256, 4 input + 2 target views"),
+            "value": scenes / (ms / 1e3),
             "unit": "scenes/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic scenes (smoothed Gaussian-noise images, cameras on a radius-2 sphere, FOV 50)",
             "impl": "uttt_b200",
-            "config": {"model": "nvs-uttt-moe (24 layers, d 768, 12 heads, 16 experts, top-2)",
+            "config": {"model": args.model + " (24 layers, d 768, 12 heads, 16 experts, top-2)",
                        "params": trainer.trainer.num_parameters(), "global_batch": scenes, "per_gpu_batch": per_gpu,
-                       "views": views, "tokens_per_scene": views * (size // 8) ** 2,
+                       "views": views, "tokens_per_scene": (2 * (views - 1) if autoregressive else views) * (size // 8) ** 2,
                        "parallelism": f"dp{world}" if world > 1 else "single",
                        "cache": "inputs and per-step working set are far larger than L2 (no flush needed)",
                        "cuda_graph": ("forward + backward replayed as one CUDA graph; optimizer eager"
@@ -293,7 +301,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="760M-uttt-moe",
-                    choices=["760M-uttt-moe", "124M-uttt-moe", "124M-uttt-dense", "nvs-uttt-moe"])
+                    choices=["760M-uttt-moe", "124M-uttt-moe", "124M-uttt-dense", "nvs-uttt-moe", "nvs-uttt-moe-ar"])
     ap.add_argument("--seq-len", type=int, default=32768)
     ap.add_argument("--per-gpu-batch", type=int, default=4)
     ap.add_argument("--micro-batch", type=int, default=int(os.environ.get("UTTT_BENCH_MICRO_BATCH", "4")))
@@ -314,7 +322,7 @@ def main():
     if args.impl == "reference":
         from baseline.run_reference import run_reference
         run_reference(args)
-    elif args.model == "nvs-uttt-moe":
+    elif args.model in ("nvs-uttt-moe", "nvs-uttt-moe-ar"):
         run_nvs(args)
     else:
         run_ours(args)
