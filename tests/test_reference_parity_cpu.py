@@ -245,3 +245,29 @@ def test_loss_free_bias_moves_like_the_reference(reference):
         torch.testing.assert_close(bo.float(), br.float(), rtol=1e-6, atol=1e-7, msg=f"bias after forward {step}")
         moved = max(moved, float(br.abs().max()))
     assert moved > 0.0
+
+
+@pytest.mark.parametrize("over", [
+    # the memory's own q / k / v projections of the memory input
+    dict(memory_kv_mode="to_kv", memory_kv_proj="ttt_kv_proj", memory_kv_feature="x_memory_in"),
+    # the attention's projections applied to the memory input, sequential residual (the memory has its own norm)
+    dict(memory_kv_mode="to_kv", memory_kv_proj="reuse_attn_kv_proj", memory_kv_feature="x_memory_in",
+         residual_style="sequential"),
+    # one model-level pair of projections shared by every layer
+    dict(memory_k_compose_mode="shared", memory_v_compose_mode="shared"),
+    # values taken from the next layer's output (normalised, through the attention's v projection)
+    dict(memory_v_gap=1),
+    # keys from the previous layer, values from the next one, both reused as they are
+    dict(memory_k_gap=-1, memory_v_gap=1, memory_k_compose_mode="reuse", memory_v_compose_mode="reuse"),
+    # default sources, but the learning rates / momentum read the memory's own normalised input
+    dict(residual_style="sequential", memory_kv_feature="x_memory_in"),
+    # legacy switches for the same thing
+    dict(memory_perlayer_k_share_v=True, memory_kv_mode="to_kv", memory_kv_proj="reuse_attn_kv_proj"),
+])
+def test_write_sources_match_reference(reference, over):
+    """Where the write's keys / values come from: gapped layers, projections of a feature (ref_base.py:78-147,
+    1219-1261), and which projection forms the query (ref_base.py:914-919)."""
+    d = _tiny(use_moun=False, num_hidden_layers=3, **over)
+    ref, ours = _build_pair(reference, d)
+    ids = torch.randint(0, d["vocab_size"], (2, 256), generator=torch.Generator().manual_seed(4))
+    _compare_step(ref, ours, ids, 2e-6, 2e-5)

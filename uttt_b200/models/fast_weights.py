@@ -230,6 +230,19 @@ class FastWeightMemory(nn.Module):
             self.ttt_scale_proj = nn.Linear(d, self.fw_heads)
         self.output_proj = nn.Linear(d, d, bias=False) if config.enable_memory_output_proj else None
         self.norm_type = config.memory_qk_norm_type if config.memory_qk_norm else None
+        # dedicated q / k / v projections of the memory, only for the sources that use them (ref_base.py:285-304)
+        kv_mode = getattr(config, "memory_kv_mode", "reuse_kv")
+        own_proj = getattr(config, "memory_kv_proj", "ttt_kv_proj") == "ttt_kv_proj"
+        v_only = (own_proj and kv_mode == "reuse_kv" and getattr(config, "memory_v_compose_mode", None) == "ttt-proj"
+                  and getattr(config, "memory_k_compose_mode", None) in (None, "reuse")
+                  and getattr(config, "memory_k_gap", None) == 0 and getattr(config, "memory_v_gap", None) is not None)
+        self.to_q = self.to_k = self.to_v = None
+        if own_proj and kv_mode != "reuse_kv":
+            self.to_q = nn.Linear(d, d, bias=False)
+            self.to_k = nn.Linear(d, d, bias=False)
+            self.to_v = nn.Linear(d, d, bias=False)
+        elif v_only:
+            self.to_v = nn.Linear(d, d, bias=False)
 
     def reset_parameters(self) -> None:
         if self.qk_rescale:

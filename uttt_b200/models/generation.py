@@ -79,8 +79,12 @@ def forward_with_cache(model, inputs_embeds: torch.Tensor, past: Optional[Genera
             else:
                 out = layer(h, k_ctx, v_ctx, None, None, None, None, offset)
             h, x_in, k_flat, v_flat, k_rot, v_new = out[:6]
+            if cfg.use_memory_block and not model.default_write_source:
+                raise NotImplementedError("cached generation covers the default write source (the attention's own "
+                                          "k / v of the same layer); got other memory compose modes or gaps")
             past.chunk_kv[li] = (_cat(ck, k_rot), _cat(cv, v_new))
-            past.feats[li].append((x_in, k_flat, v_flat))
+            pre = out[8] if (len(out) > 8 and getattr(model, "write_feature", "x_attn_in") == "x_memory_in") else x_in
+            past.feats[li].append((pre, k_flat, v_flat))
         outputs.append(h)
         pos += take
         past.chunk_fill += take

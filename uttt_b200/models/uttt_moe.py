@@ -53,15 +53,6 @@ class MoEBlock(nn.Module):
         self.attn_norm = RMSNorm(d, eps=config.norm_eps)
         self.attn = SlidingWindowAttention(config, layer_idx)
         if config.use_memory_block:
-            # every released configuration feeds the memory from the attention's own q / k / v projections
-            # ("reuse_kv"); the other sources the schema can name (separate projections, gapped layers) are rejected
-            # instead of being silently replaced
-            unsupported = [n for n in ("memory_k_gap", "memory_v_gap", "memory_k_compose_mode", "memory_v_compose_mode")
-                           if getattr(config, n, None) is not None]
-            if getattr(config, "memory_kv_mode", "reuse_kv") != "reuse_kv" or unsupported:
-                raise NotImplementedError(
-                    "the memory branch implements memory_kv_mode='reuse_kv' without k/v gaps or compose modes; got "
-                    f"memory_kv_mode={getattr(config, 'memory_kv_mode', None)!r}, {unsupported}")
             self.memory_norm = RMSNorm(d, eps=config.norm_eps) if config.residual_style == "sequential" else None
             self.memory = fw.FastWeightMemory(config, layer_idx, momentum_out=1)
             self.to_lr = nn.Linear(d, 3 * config.fw_heads if config.per_head_lr else 3)
@@ -72,6 +63,7 @@ class MoEBlock(nn.Module):
         self.memory_output_proj = nn.Linear(d, d, bias=False) if config.enable_attention_memory_output_proj else None
         self.mlp_norm = RMSNorm(d, eps=config.norm_eps)
         self.mlp = GatedMLP(d, config.mlp_intermediate_size)
+        self.return_memory_input = False   # set by the model when a write source other than the default is configured
         self.ep = None            # expert-parallel handle, set by the model
         self.write_recomputed = False   # set by the model: the chunk write of this layer runs twice (recomputation)
         self.route_stats = None   # (reads, writes) RouteStats while the model collects pool statistics
@@ -91,6 +83,7 @@ class MoEBlock(nn.Module):
         x_attn_in = self.attn_norm(h)
         attn_out, q_flat, k_flat, v_flat, k_rot, v_new = self.attn(x_attn_in, k_hist, v_hist, offset)
         lb_probs = lb_counts = None
+        x_mem_in = x_attn_in
         if self.memory is not None:
             if cfg.residual_style == "sequential":
                 h, x_mem_in = self.memory_norm.add_forward(residual, attn_out)
@@ -98,7 +91,15 @@ class MoEBlock(nn.Module):
             else:
                 x_mem_in = x_attn_in
             mem = self.memory
-            q_rows = mem.head_rows(mem.prep_query(q_flat, offset))
+            # query source (ref_base.py:914-919): the attention's own query, the attention's q projection of the
+            # memory input, or the memory's own projection
+            if getattr(cfg, "memory_kv_mode", "reuse_kv") == "reuse_kv":
+                q_src = q_flat
+            elif cfg.memory_kv_proj == "reuse_attn_kv_proj":
+                q_src = ops.linear(x_mem_in, self.attn.q_proj.weight, self.attn.q_proj.bias)
+            else:
+                q_src = ops.linear(x_mem_in, mem.to_q.weight)
+            q_rows = mem.head_rows(mem.prep_query(q_src, offset))
             routing = fw.route_rows(q_rows, router, bias, cfg, getattr(cfg, "memory_bias_in_logits", False), self.ep,
                                     reuse=self._reuse(offset, "read"))
             if self.route_stats is not None:          # set by the model for the first pass of a statistics step
@@ -116,6 +117,9 @@ class MoEBlock(nn.Module):
         if lb_probs is None:
             lb_probs = h.new_zeros((h.shape[0], 1), dtype=torch.float32)
             lb_counts = lb_probs
+        if self.return_memory_input:
+            # only for the write sources that read it (see UTTTMoEModel.compose_write_inputs)
+            return h, x_attn_in, k_flat, v_flat, k_rot, v_new, lb_probs, lb_counts, x_mem_in
         return h, x_attn_in, k_flat, v_flat, k_rot, v_new, lb_probs, lb_counts
 
     # -------------------------------------------------------------------------- write
@@ -140,6 +144,34 @@ class MoEBlock(nn.Module):
         g02, g1 = fw.pool_raw_grad(k_rows, v_rows, lr_rows, w02, w1, routing, acc=acc)
         m = mem.momentum_coeff(x_in)
         return g02, g1, m, routing.prob_sum, routing.counts
+
+
+def memory_compose_modes(cfg) -> Tuple[str, str]:
+    """Where the keys and the values of the write come from (ref_base.py:78-147): ``reuse`` the attention's own
+    pre-rotary k / v, ``attn-proj`` = the attention's k / v projection applied to a feature, ``shared`` = one
+    model-level projection, ``ttt-proj`` = the memory's own projection."""
+    explicit_k = getattr(cfg, "memory_k_compose_mode", None)
+    explicit_v = getattr(cfg, "memory_v_compose_mode", None)
+    if explicit_k is None and explicit_v is None:
+        if getattr(cfg, "memory_perlayer_k_share_v", False):
+            return "attn-proj", "shared"
+        if getattr(cfg, "memory_perlayer_k_reuse_v", False):
+            return "attn-proj", "reuse"
+        if getattr(cfg, "memory_shared_kv_cache", False):
+            return "shared", "shared"
+        if getattr(cfg, "memory_reuse_kv_cache", False):
+            return "reuse", "reuse"
+    if getattr(cfg, "memory_kv_mode", "reuse_kv") == "reuse_kv":
+        base = "reuse"
+    else:
+        table = {"reuse_attn_kv_proj": "attn-proj", "model_kv_proj": "shared", "ttt_kv_proj": "ttt-proj"}
+        if cfg.memory_kv_proj not in table:
+            raise ValueError(f"Invalid memory_kv_proj: {cfg.memory_kv_proj}")
+        base = table[cfg.memory_kv_proj]
+    k_mode = v_mode = base
+    if getattr(cfg, "memory_v_gap", None) is not None and explicit_v is None:
+        v_mode = "attn-proj"          # a gapped value source is normalised and sent through the attention's v projection
+    return explicit_k or k_mode, explicit_v or v_mode
 
 
 class UTTTMoEModel(nn.Module):
@@ -169,6 +201,7 @@ class UTTTMoEModel(nn.Module):
         self.keep_activation_layers = frozenset()
         self.ep = None
         if config.use_memory_block:
+            self._init_write_sources()
             self._init_pool_parameters()
             self._init_loss_free_buffers()
             if self.per_layer_pool:
@@ -213,6 +246,68 @@ class UTTTMoEModel(nn.Module):
             state_dict[prefix + "per_layer_router_proj_weights"] = torch.stack([state_dict.pop(k) for k in keys], dim=0)
 
     # ------------------------------------------------------------------ parameters
+    def _init_write_sources(self) -> None:
+        """Sources of the write's keys / values other than the attention's own k / v of the same layer: gapped
+        layers, projections of a feature (ref_base.py:1090-1141)."""
+        cfg = self.config
+        n = cfg.num_hidden_layers
+        self.k_mode, self.v_mode = memory_compose_modes(cfg)
+        self.k_gap, self.v_gap = getattr(cfg, "memory_k_gap", None), getattr(cfg, "memory_v_gap", None)
+        self.k_source = [max(min(i + (self.k_gap or 0), n - 1), 0) for i in range(n)]
+        self.v_source = [max(min(i + (self.v_gap or 0), n - 1), 0) for i in range(n)]
+        if (getattr(cfg, "memory_kv_mode", "reuse_kv") != "reuse_kv" and cfg.memory_kv_proj == "model_kv_proj"):
+            # the query would need the memory's own projection, which only memory_kv_proj="ttt_kv_proj" creates
+            # (the reference fails on its first forward with this combination)
+            raise ValueError('memory_kv_mode="to_kv" with memory_kv_proj="model_kv_proj" has no query projection; '
+                             'use memory_k_compose_mode / memory_v_compose_mode = "shared" with memory_kv_mode='
+                             '"reuse_kv"')
+        self.write_feature = getattr(cfg, "memory_kv_feature", "x_attn_in")
+        if self.write_feature not in ("x_attn_in", "x_memory_in"):
+            raise ValueError(f"memory_kv_feature must be 'x_attn_in' or 'x_memory_in', got {self.write_feature!r}")
+        self.default_write_source = (self.k_mode == "reuse" and self.v_mode == "reuse" and not self.k_gap
+                                     and not self.v_gap)
+        d = cfg.hidden_size
+        kv_dim = cfg.kv_heads * cfg.head_dim
+        self.pre_memory_v_rms_norm = (RMSNorm(d, eps=cfg.norm_eps)
+                                      if self.v_gap is not None and self.v_mode in ("attn-proj", "shared") else None)
+        self.memory_shared_k_proj = nn.Linear(d, kv_dim, bias=cfg.qkv_bias) if self.k_mode == "shared" else None
+        self.memory_shared_v_proj = nn.Linear(d, kv_dim, bias=cfg.qkv_bias) if self.v_mode == "shared" else None
+        want_memory_input = (not self.default_write_source or cfg.memory_kv_mode != "reuse_kv"
+                             or (self.write_feature == "x_memory_in" and cfg.residual_style == "sequential"))
+        for layer in self.layers:
+            layer.return_memory_input = bool(want_memory_input)
+
+    def compose_write_inputs(self, caches: List[Dict[str, torch.Tensor]]) -> List[Tuple[torch.Tensor, ...]]:
+        """Per layer (feature for learning rates and momentum, keys, values) of this chunk's write, from the layers'
+        caches {x_attn_in, x_memory_in, xi_out, attn_k, attn_v} (ref_base.py:1219-1261)."""
+        out = []
+        for li, layer in enumerate(self.layers):
+            ck, cv = caches[self.k_source[li]], caches[self.v_source[li]]
+            pre = k_feature = ck[self.write_feature]
+            if self.v_gap is not None:
+                v_feature = cv["xi_out"]
+                if self.pre_memory_v_rms_norm is not None:
+                    v_feature = self.pre_memory_v_rms_norm(v_feature)
+            else:
+                v_feature = cv[self.write_feature]
+            ki = self._project_write_source(layer, self.k_mode, "k", k_feature, ck["attn_k"])
+            vi = self._project_write_source(layer, self.v_mode, "v", v_feature, cv["attn_v"])
+            out.append((pre, ki, vi))
+        return out
+
+    def _project_write_source(self, layer, mode: str, which: str, feature, own):
+        if mode == "reuse":
+            return own
+        if mode == "attn-proj":
+            proj = layer.attn.k_proj if which == "k" else layer.attn.v_proj
+        elif mode == "shared":
+            proj = self.memory_shared_k_proj if which == "k" else self.memory_shared_v_proj
+        elif mode == "ttt-proj":
+            proj = layer.memory.to_k if which == "k" else layer.memory.to_v
+        else:
+            raise ValueError(f"Invalid memory compose mode: {mode}")
+        return self._ckpt(lambda f, _p=proj: ops.linear(f, _p.weight, _p.bias), feature)
+
     def _init_pool_parameters(self) -> None:
         cfg = self.config
         e, i_dim, d_dim = cfg.memory_num_experts, cfg.fw_inter_dim, cfg.fw_head_dim
@@ -601,7 +696,7 @@ class UTTTMoEModel(nn.Module):
                 # all readers and writers of this chunk add their bank gradients into one buffer (see ops.grad_sink)
                 s0 = states[0]
                 states = [fw.PoolState(ops.grad_sink(s0.w02), ops.grad_sink(s0.w1), s0.m02, s0.m1, s0.z02, s0.z1)]
-            feats = []
+            caches = []
             layer_probs, layer_counts = [], []
             for li, layer in enumerate(self.layers):
                 if cfg.use_memory_block:
@@ -614,9 +709,11 @@ class UTTTMoEModel(nn.Module):
                 run = layer.__call__ if li in self.keep_activation_layers else (
                     lambda *a, _layer=layer: self._ckpt(_layer, *a))
                 with trace_range(f"chunk{start // chunk}.layer{li}.read"):
-                    h, x_in, k_flat, v_flat, k_rot, v_new, p, c = run(h, k_hist, v_hist, w02, w1, router, bias, start)
+                    res = run(h, k_hist, v_hist, w02, w1, router, bias, start)
+                h, x_in, k_flat, v_flat, k_rot, v_new, p, c = res[:8]
                 hist[li] = trim_history(k_hist, v_hist, k_rot, v_new, keep)
-                feats.append((x_in, k_flat, v_flat))
+                caches.append({"x_attn_in": x_in, "x_memory_in": res[8] if len(res) > 8 else x_in, "xi_out": h,
+                               "attn_k": k_flat, "attn_v": v_flat})
                 layer_probs.append(p)
                 layer_counts.append(c)
             outputs.append(h)
@@ -625,7 +722,7 @@ class UTTTMoEModel(nn.Module):
                 apply_counts = apply_counts + torch.stack(layer_counts)
                 if end < seq_len:   # apply-then-update; the last chunk never writes
                     with trace_range(f"chunk{start // chunk}.write"):
-                        states, up, uc = self._chunk_write(states, feats, start)
+                        states, up, uc = self._chunk_write(states, self.compose_write_inputs(caches), start)
                     update_probs = update_probs + up
                     update_counts = update_counts + uc
         for layer in self.layers:
