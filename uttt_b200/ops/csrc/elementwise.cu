@@ -1155,7 +1155,7 @@ template <typename T>
 __global__ void unpermute_rows_bwd_kernel(const T* __restrict__ dout, const T* __restrict__ y,
                                           const int64_t* __restrict__ dest, const float* __restrict__ w,
                                           T* __restrict__ dy, float* __restrict__ dw, size_t n_copies, int k, int d,
-                                          PadLayout pad) {
+                                          PadLayout pad, long long rows_in, int* __restrict__ status) {
   if (zero_pad_block(dy, d * (int)sizeof(T) / 16, pad)) return;
   size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   int lane = threadIdx.x & 31;
@@ -1163,6 +1163,7 @@ __global__ void unpermute_rows_bwd_kernel(const T* __restrict__ dout, const T* _
   int nv = d >> 3;
   for (size_t c = warp; c < n_copies; c += nwarps) {
     size_t r = c / k;
+    if (!UTTT_INDEX_OK(dest[c], rows_in, status, 72)) continue;
     size_t dr = (size_t)dest[c];
     float wj = w[c];
     float dot = 0.f;
@@ -1252,7 +1253,8 @@ std::vector<at::Tensor> unpermute_rows_bwd(at::Tensor dout, at::Tensor y, at::Te
   auto dw = at::empty({dest.size(0), k}, y.options().dtype(at::kFloat));
   UTTT_DISPATCH_FLOAT(y, {
     unpermute_rows_bwd_kernel<T><<<blocks + 2 * pad.groups, 256, 0, cur_stream()>>>(
-        ptr<T>(dout), ptr<T>(y), ptr<int64_t>(dest), ptr<float>(wf), ptr<T>(dy), ptr<float>(dw), n, k, d, pad);
+        ptr<T>(dout), ptr<T>(y), ptr<int64_t>(dest), ptr<float>(wf), ptr<T>(dy), ptr<float>(dw), n, k, d, pad,
+        (long long)y.size(0), gemm_status(y).data_ptr<int>());
   });
   count_launch();
   return {dy, dw};

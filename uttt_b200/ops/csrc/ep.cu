@@ -112,7 +112,14 @@ struct EpMap {
 
 __device__ __forceinline__ void ep_locate(const EpMap& m, long long copy, int& peer, long long& pos) {
   const long long r = copy / m.k;
-  const int e = m.idx[copy];
+  int e = m.idx[copy];
+#ifdef UTTT_BOUNDS_CHECK
+  if (e < 0 || e >= m.E) {                   // an expert the pool does not have: the copy is dropped
+    peer = 0;
+    pos = m.cap_rows;
+    return;
+  }
+#endif
   const int g = (int)(r / m.rows_per_batch) * m.E + e;
   peer = e / m.El;
   pos = (long long)m.remote_start[g] + (m.dest[copy] - m.offsets_local[g]);

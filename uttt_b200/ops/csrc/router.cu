@@ -274,6 +274,9 @@ __global__ void __launch_bounds__(256) router_bwd_rows_kernel(
         for (int j = 0; j < kMaxTopK; ++j) {
           if (j >= topk) break;
           ej[j] = idx[(size_t)row * topk + j];
+#ifdef UTTT_BOUNDS_CHECK
+          if (ej[j] < 0 || ej[j] >= E) ej[j] = 0;         // reported by the host-side check of the index table
+#endif
           gj[j] = dw[(size_t)row * topk + j];
           float pj = __shfl_sync(0xffffffffu, (ej[j] >> 5) == 0 ? pr[0] : pr[EPL - 1], ej[j] & 31);
           s_sel += pj;

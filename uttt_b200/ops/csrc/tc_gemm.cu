@@ -63,6 +63,12 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, const TnSe
     int t = id / tiles_n;
     c.n0 = (id % tiles_n) * BN;
     c.g = p.tile_group[t];
+#ifdef UTTT_BOUNDS_CHECK
+    if (c.g >= p.groups) {                   // a layout table that names a group the weights do not have
+      if (p.status != nullptr) atomicCAS(p.status, 0, 74);
+      c.g = -1;
+    }
+#endif
     c.a_row0 = t * BM;
     c.out_row0 = (size_t)t * BM;
     c.unused = c.g < 0;

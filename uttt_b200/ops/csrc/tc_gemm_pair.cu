@@ -128,6 +128,12 @@ __device__ __forceinline__ PairWork pair_decode(const GemmParams& p, const int2*
   w.t0 = e.x;
   w.t1 = e.y;
   w.g = e.x >= 0 ? p.tile_group[e.x] : -1;
+#ifdef UTTT_BOUNDS_CHECK
+  if (w.g >= p.groups) {
+    if (p.status != nullptr) atomicCAS(p.status, 0, 74);
+    w.g = -1;
+  }
+#endif
   if (EPI != kEpiNone) {
     w.n0 = j * 128;
     w.bn = 256;
