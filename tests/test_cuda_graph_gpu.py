@@ -137,3 +137,29 @@ def test_recomputation_takes_the_write_aggregate_back(monkeypatch):
             continue
         noise = _rel(grads["full_b"][1][k], g)
         assert _rel(grads["kept"][1][k], g) <= 3.0 * noise + 5e-2, (k, _rel(grads["kept"][1][k], g), noise)
+
+
+def test_dense_family_keeps_its_write_aggregate_too(monkeypatch):
+    """uTTT-Dense: stashed token reductions and the kept aggregate give the gradients of the plain recomputation
+    (the dense family has no router, so two runs agree to rounding)."""
+    from uttt_b200.config import named_config
+    from uttt_b200.train.engine import EngineConfig, TrainEngine
+    out = {}
+    for flag in ("0", "1"):
+        monkeypatch.setenv("UTTT_B200_REUSE_AGGREGATE", flag)
+        monkeypatch.setenv("UTTT_B200_WRITE_STASH", "1" if flag == "0" else "4")
+        cfg = named_config("124M-uttt-dense", num_hidden_layers=3, vocab_size=2048, chunk_size=256, window_size=256)
+        eng = TrainEngine(cfg, EngineConfig(micro_batch_size=2, warmup_steps=0, total_steps=10, seed=0),
+                          torch.device("cuda", 0))
+        ids = torch.randint(0, cfg.vocab_size, (2, 4 * cfg.chunk_size),
+                            generator=torch.Generator().manual_seed(2)).to(eng.device)
+        eng.model.train()
+        res = eng.model(input_ids=ids, labels=ids)
+        res.loss.backward()
+        assert not eng.model.model._aggregate_store
+        out[flag] = (float(res.loss.detach()), _take_grads(eng))
+    assert abs(out["0"][0] - out["1"][0]) <= 1e-4 * abs(out["0"][0]), (out["0"][0], out["1"][0])
+    for k, g in out["0"][1].items():
+        if g.numel() < 64 or float(g.norm()) == 0.0:
+            continue
+        assert _rel(out["1"][1][k], g) <= 6e-2, (k, _rel(out["1"][1][k], g))    # bf16 gradients, other summation order

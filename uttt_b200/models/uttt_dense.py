@@ -241,7 +241,20 @@ class DenseFWModel(nn.Module):
             def _agg(*args):
                 f = args[:3 * n_layers]
                 s = unpack(args[3 * n_layers:])
-                a02, a1 = torch.zeros_like(s.m02), torch.zeros_like(s.m1)
+                # the sums of the first pass over this region are kept for its recomputation, which then records
+                # the writers' nodes without redoing their GEMMs and reductions (as in models/uttt_moe.py)
+                store = getattr(self, "_aggregate_store", None)
+                kept = None
+                if (store is not None and not detach_g and torch.is_grad_enabled()
+                        and ops.fw_write_accumulate_skips(s.m02, s.w02)):
+                    kept = store.pop(offset, None)
+                else:
+                    store = None
+                if kept is not None:
+                    a02, a1 = kept
+                else:
+                    a02, a1 = torch.zeros_like(s.m02), torch.zeros_like(s.m1)
+                stash = None if (detach_g or kept is not None) else ops.write_stash_for(a02)
                 ms = []
                 for li, layer in enumerate(self.layers):
                     if detach_g:
@@ -249,9 +262,11 @@ class DenseFWModel(nn.Module):
                         a02, a1 = a02 + g02.detach(), a1 + g1.detach()
                     else:
                         a02, a1, m = layer.raw_grad(f[3 * li], f[3 * li + 1], f[3 * li + 2], s.w02, s.w1, offset,
-                                                    acc=(a02, a1))
+                                                    acc=(a02, a1, stash, li == n_layers - 1, kept is not None))
                     if m is not None:
                         ms.append(m)
+                if store is not None and kept is None:
+                    store[offset] = (a02.detach(), a1.detach())
                 if getattr(cfg, "uttt_agg_reduce", "mean") == "mean":
                     a02, a1 = a02 / n_layers, a1 / n_layers
                 mc = torch.stack(ms).mean(0).view(a02.shape[0], -1, 1, 1) if ms else None
@@ -295,6 +310,8 @@ class DenseFWModel(nn.Module):
                  and os.environ.get("UTTT_B200_REUSE_ATTENTION", "1") != "0")
         for layer in self.layers:
             layer.attn.reuse_store = {} if reuse else None      # attention outputs kept for the recomputation
+        self._aggregate_store = {} if (reuse and getattr(cfg, "memory_update_backward_mode", "full") == "full"
+                                       and os.environ.get("UTTT_B200_REUSE_AGGREGATE", "1") != "0") else None
         for start in range(0, seq_len, chunk):
             end = min(start + chunk, seq_len)
             h = inputs_embeds[:, start:end]
