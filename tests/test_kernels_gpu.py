@@ -1381,3 +1381,29 @@ def test_checked_build_reports_bad_indices_instead_of_following_them():
     torch.cuda.synchronize()
     assert torch.equal(out[128:], want[128:])
     _status_ok()
+
+
+def test_split_linear_matches_fp32():
+    """One q|k|v weight, three contiguous outputs; input gradient accumulated in the GEMMs, weight gradient written
+    block by block."""
+    from uttt_b200 import ops
+    torch.manual_seed(0)
+    x = (torch.randn(2, 256, 192, device=DEV) * 0.5).bfloat16().requires_grad_(True)
+    w = (torch.randn(3 * 192, 192, device=DEV) * 0.05).bfloat16().requires_grad_(True)
+    q, k, v = ops.split_linear(x, w, 3)
+    assert q.is_contiguous() and k.is_contiguous() and v.is_contiguous() and q.shape == (2, 256, 192)
+    loss = (q.float() * 1.0).pow(2).sum() + (k.float() * 2.0).sum() + (v.float().pow(3)).sum()
+    dx, dw = torch.autograd.grad(loss, [x, w])
+    xf, wf = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    qf, kf, vf = torch.nn.functional.linear(xf, wf).chunk(3, dim=-1)
+    lossf = qf.pow(2).sum() + (kf * 2.0).sum() + vf.pow(3).sum()
+    dxf, dwf = torch.autograd.grad(lossf, [xf, wf])
+
+    def rel(a, b):
+        return float((a.float() - b).norm() / b.norm())
+    assert rel(q, qf) < 6e-3 and rel(k, kf) < 6e-3 and rel(v, vf) < 6e-3
+    assert rel(dx, dxf) < 1.2e-2 and rel(dw, dwf) < 1.2e-2, (rel(dx, dxf), rel(dw, dwf))
+    # only one of the three outputs used: the other blocks of the weight gradient are zero
+    q2, _, _ = ops.split_linear(x, w, 3)
+    (dw2,) = torch.autograd.grad(q2.float().sum(), [w])
+    assert float(dw2[192:].abs().max()) == 0.0 and float(dw2[:192].abs().max()) > 0.0

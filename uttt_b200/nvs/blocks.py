@@ -58,8 +58,8 @@ class SelfAttention(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         b, l, _ = x.shape
         h = self.dim // self.head_dim
-        qkv = self.to_qkv(x).view(b, l, 3, h, self.head_dim)
-        q, k, v = qkv[:, :, 0].contiguous(), qkv[:, :, 1].contiguous(), qkv[:, :, 2].contiguous()
+        # three contiguous outputs of the one q|k|v weight (no strided copies, no zero-filled wide gradient)
+        q, k, v = (t.view(b, l, h, self.head_dim) for t in ops.split_linear(x, self.to_qkv.weight, 3))
         o = ops.swa_attention(q, k, v, None, causal=False)
         return self.to_out(o.reshape(b, l, self.dim))
 
@@ -110,9 +110,21 @@ class FastWeightMemory(nn.Module):
             return F.normalize(rows.float(), dim=-1, eps=1e-5).to(x.dtype)
         return ops.rms_norm(rows, None, 1e-5)
 
+    def _proj_rows(self, proj: nn.Sequential, x: torch.Tensor) -> torch.Tensor:
+        """Per-head normalised rows of a (Linear, SiLU) projection.  On the GPU in bf16 the SiLU and the per-head norm
+        run in the fused preprocessing kernel of the memory branch (its L2 form divides by |y| + 1e-5 where
+        ``F.normalize`` divides by max(|y|, 1e-5): 1e-5 relative at most for rows of ordinary size, far inside
+        bf16 rounding)."""
+        b, l, _ = x.shape
+        if x.is_cuda and x.dtype == torch.bfloat16 and self.head_dim % 8 == 0:
+            y = ops.fw_qk_prep(ops.linear(x, proj[0].weight), None, None, self.num_heads, 0, 0.0, 0, True,
+                               "l2" if self.l2_norm else "rms")
+            return y.reshape(b, l * self.num_heads, self.head_dim)
+        return self._rows(proj(x))
+
     def read(self, x: torch.Tensor, w02: torch.Tensor, w1: torch.Tensor, router: torch.Tensor):
         b, l, _ = x.shape
-        rows = self._rows(self.input_proj(x))
+        rows = self._proj_rows(self.input_proj, x)
         routing = fw.route_rows(rows, router, None, self.route_cfg)
         y = fw.pool_read(rows, w02, w1, routing)
         y = ops.rms_norm(y, None, 1e-5).reshape(b, l, self.dim)
@@ -120,7 +132,7 @@ class FastWeightMemory(nn.Module):
 
     def raw_grad(self, pre_k, pre_v, w02, w1, router, acc=None, keep_mask: Optional[torch.Tensor] = None):
         b, l, _ = pre_k.shape
-        k_rows = self._rows(self.k_input_proj(pre_k))
+        k_rows = self._proj_rows(self.k_input_proj, pre_k)
         v_rows = self.to_v(pre_v).reshape(b, l * self.num_heads, self.head_dim)
         lr = F.softplus(F.linear(pre_v.float(), self.to_lr.weight.float()) + self.base_lr_inv)
         if keep_mask is not None:

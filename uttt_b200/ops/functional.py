@@ -501,6 +501,53 @@ class _FanoutLinear(torch.autograd.Function):
         return (None if dx is None else dx.view_as(x), None, *gws, *gbs)
 
 
+class _SplitLinear(torch.autograd.Function):
+    """``x @ W^T`` with the rows of ``W`` in ``n`` equal blocks, returned as ``n`` contiguous outputs (a fused q|k|v
+    projection whose consumers want contiguous q, k and v: slicing one wide output would cost a strided copy per
+    slice, and autograd would rebuild the wide gradient by zero-fill and adds).  Backward accumulates the input
+    gradient inside the GEMMs and writes each block of the weight gradient in place."""
+
+    @staticmethod
+    def forward(ctx, x, w, n):
+        ctx.save_for_backward(x, w)
+        ctx.n = n
+        x2 = x.reshape(-1, x.shape[-1])
+        rows = w.shape[0] // n
+        return tuple(_mm_nt(x2, w[i * rows:(i + 1) * rows]).view(*x.shape[:-1], rows) for i in range(n))
+
+    @staticmethod
+    def backward(ctx, *gys):
+        x, w = ctx.saved_tensors
+        n = ctx.n
+        rows = w.shape[0] // n
+        x2 = x.reshape(-1, x.shape[-1])
+        fuse = ctx.needs_input_grad[1] and _fuse_wgrad(w, x2)
+        dw = None
+        if ctx.needs_input_grad[1] and not fuse:
+            dw = torch.zeros_like(w) if any(g is None for g in gys) else torch.empty_like(w)
+        dx = None
+        for i, gy in enumerate(gys):
+            if gy is None:
+                continue
+            g2 = gy.reshape(-1, rows)
+            wi = w[i * rows:(i + 1) * rows]
+            if ctx.needs_input_grad[0]:
+                dx = _mm_nn(g2, wi, dx)
+            if fuse:
+                w.grad[i * rows:(i + 1) * rows].addmm_(g2.t(), x2)
+            elif dw is not None:
+                torch.mm(g2.t(), x2, out=dw[i * rows:(i + 1) * rows])
+        return (None if dx is None else dx.view_as(x)), dw, None
+
+
+def split_linear(x: torch.Tensor, weight: torch.Tensor, n: int):
+    """``n`` contiguous outputs of ``x @ W^T`` for ``W`` = ``n`` equal row blocks; see ``_SplitLinear``."""
+    if not x.is_cuda or weight.shape[0] % n != 0:
+        y = torch.nn.functional.linear(x, weight)
+        return tuple(t.contiguous() for t in y.chunk(n, dim=-1))
+    return _SplitLinear.apply(x, weight, n)
+
+
 def fanout_linear(x: torch.Tensor, weights, biases=None):
     """Several linear maps of one input; see ``_FanoutLinear``.  Returns a tuple of outputs."""
     weights = list(weights)
