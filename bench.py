@@ -62,7 +62,8 @@ def run_ours(args):
     keep = tuple(int(i) for i in keep_arg.split(",") if i.strip())
     eng = TrainEngine(cfg, EngineConfig(micro_batch_size=args.micro_batch, lr=1e-3, eps=1e-15, warmup_steps=1024,
                                         total_steps=40960, seed=42, keep_activation_layers=keep,
-                                        cuda_graph=not args.no_cuda_graph and args.expert_parallel <= 1), dev)
+                                        cuda_graph=not args.no_cuda_graph and args.expert_parallel <= 1,
+                                        expert_capacity_factor=float(min(max(args.expert_parallel, 2), 4))), dev)
     data = SyntheticZipfTokens(cfg.vocab_size, seq, args.per_gpu_batch, seed=1234, rank=rank, world=world)
     n_params = eng.trainer.num_parameters()
 
@@ -160,7 +161,11 @@ def run_ours(args):
             cfg_ep = named_config(args.model, **{**over, "memory_expert_parallel": world})
             eng = TrainEngine(cfg_ep, EngineConfig(micro_batch_size=args.micro_batch, lr=1e-3, eps=1e-15,
                                                    warmup_steps=1024, total_steps=40960, seed=42,
-                                                   keep_activation_layers=keep), dev)
+                                                   keep_activation_layers=keep,
+                                                   # staging for up to four times the balanced share per owner
+                                                   # (the worst case up to 4 ranks): a random-init router sends a
+                                                   # quarter of the experts more than twice their share
+                                                   expert_capacity_factor=float(min(world, 4))), dev)
             for _ in range(2):
                 float(eng.train_step(next(data)))
             ep_batches = [{k: v.to(dev) for k, v in next(data).items()} for _ in range(2)]
@@ -171,6 +176,10 @@ def run_ours(args):
                                     "the tile-driven read serves forwards without autograd)",
                        "kernel_status": int(ext.gemm_status(torch.zeros(1, device=dev))[0]), "clocks": clocks_ep,
                        "gpu_launches": launches_ep}
+            if ep_line["kernel_status"] != 0:
+                # after a reported overflow or a failed wait the tensor-core kernels return at once: no valid timing
+                ep_line = {"unavailable": f"device status word {ep_line['kernel_status']} during the "
+                                          f"expert-parallel steps (61 = staging overflow, 6x = a bounded wait ran out)"}
         except Exception as exc:                       # e.g. out of memory: report, keep the headline
             ep_line = {"unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"}
         guard.cancel()

@@ -39,6 +39,7 @@ class EngineConfig:
     activation_checkpoint: bool = True
     keep_activation_layers: tuple = ()     # layer indices that skip recomputation (needs spare device memory)
     activation_offload: bool = False       # saved tensors of the forward go to pinned host memory until backward
+    expert_capacity_factor: float = 2.0    # expert-parallel staging rows / balanced load (0 = size for the worst case)
     cuda_graph: bool = False               # replay forward + backward of a micro-batch as one CUDA graph
     cuda_graph_warmup: int = 2             # eager steps before the capture (lazy initialisation happens in them)
 
@@ -130,7 +131,8 @@ class TrainEngine:
                 if start <= rank < start + ep_size:
                     mine = grp
             self.expert_parallel = ExpertParallel(mine, device, model_config.memory_num_experts,
-                                                  max_row_bytes=4 * model_config.fw_head_dim)
+                                                  max_row_bytes=4 * model_config.fw_head_dim,
+                                                  capacity_factor=float(self.cfg.expert_capacity_factor))
             inner.set_expert_parallel(self.expert_parallel)
         opt = AdamWConfig(lr=self.cfg.lr, beta1=self.cfg.beta1, beta2=self.cfg.beta2, eps=self.cfg.eps,
                           weight_decay=self.cfg.weight_decay, max_norm=self.cfg.max_norm,
