@@ -49,6 +49,7 @@ def run_ours(args):
     assert torch.cuda.is_available(), "bench.py needs a GPU"
     ext = load(required=True)
     ops.set_dense_gemm(args.dense_gemm == "own")
+    ops.set_strict(True)          # a bf16 GPU tensor that leaves the extension's kernels raises instead of falling back
     dev = torch.device("cuda", local)
     over = dict(memory_update_backward_mode=args.backward_mode) if args.model != "124M-uttt-dense" else {}
     if args.expert_parallel > 1:

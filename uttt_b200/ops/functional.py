@@ -50,6 +50,37 @@ def _kernel(name: str, *tensors):
     return ext
 
 
+# Library / plain-PyTorch stand-ins on the GPU.  Every op falls back to a plain PyTorch (or library) statement when its
+# kernel does not cover a shape or dtype; on CPU that is the intended path.  For bf16 tensors on a GPU it means the
+# hot path left the kernels of this extension: the fallbacks are counted per op (``library_fallbacks()``), and in
+# strict mode (``set_strict(True)`` or ``UTTT_B200_STRICT=1``; ``bench.py`` and the smoke run turn it on) they raise.
+class KernelCoverageError(RuntimeError):
+    """A bf16 tensor on the GPU reached an op whose kernel does not cover its shape (strict mode)."""
+
+
+_STRICT = os.environ.get("UTTT_B200_STRICT", "0") == "1"
+_FALLBACK_COUNTS = {}
+
+
+def set_strict(flag: bool) -> None:
+    global _STRICT
+    _STRICT = bool(flag)
+
+
+def library_fallbacks() -> dict:
+    """How often each op ran as plain PyTorch / a library call on bf16 GPU tensors in this process."""
+    return dict(_FALLBACK_COUNTS)
+
+
+def _note_fallback(op: str, t, why: str = "") -> None:
+    if not (torch.is_tensor(t) and t.is_cuda and t.dtype == torch.bfloat16):
+        return
+    _FALLBACK_COUNTS[op] = _FALLBACK_COUNTS.get(op, 0) + 1
+    if _STRICT:
+        raise KernelCoverageError(f"{op}: no kernel of this extension covers {tuple(t.shape)} {t.dtype}"
+                                  f"{' (' + why + ')' if why else ''}; set UTTT_B200_STRICT=0 to run it as plain PyTorch")
+
+
 # =========================================================================== norms
 class _RMSNorm(torch.autograd.Function):
     @staticmethod
@@ -73,6 +104,7 @@ class _RMSNorm(torch.autograd.Function):
 def rms_norm(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float = 1e-6) -> torch.Tensor:
     if _kernel("rms_norm_fwd", x) is not None and x.shape[-1] % 8 == 0:
         return _RMSNorm.apply(x, weight, eps)
+    _note_fallback("rms_norm", x)
     return ref.rms_norm(x, weight, eps)
 
 
@@ -184,6 +216,7 @@ def rope(x: torch.Tensor, offset: int, theta: float, inverse: bool = False) -> t
     """Rotary embedding (first-half/second-half pairing) on x: [b, l, nh, hd]."""
     if _kernel("rope_fwd", x) is not None and x.shape[-1] % 2 == 0:
         return _Rope.apply(x, offset, theta, inverse)
+    _note_fallback("rope", x)
     return ref.rope(x, offset, theta, inverse)
 
 
@@ -222,13 +255,13 @@ def fw_qk_prep(x, scale, shift, fw_heads: int, rope_dim: int, theta: float, offs
     ok = (d // fw_heads) % 8 == 0 and (rope_dim == 0 or (rope_dim % 2 == 0 and (d // fw_heads) % rope_dim == 0))
     if _kernel("fw_qk_prep_fwd", x) is not None and ok:
         return _FwQkPrep.apply(x, scale, shift, fw_heads, rope_dim, theta, offset, silu, norm)
+    _note_fallback("fw_qk_prep", x)
     return ref.fw_qk_prep(x, scale, shift, fw_heads, rope_dim, theta, offset, silu, norm)
 
 
 # =========================================================================== attention
 class _SWA(torch.autograd.Function):
-    """Forward: the tcgen05 sliding-window kernel.  Backward: hand-written kernel when the extension has one,
-    otherwise the flash-attn library backward fed with this forward's output and log-sum-exp."""
+    """Forward and backward: the tcgen05 sliding-window kernels of this extension."""
 
     @staticmethod
     def forward(ctx, q, k, v, window, causal, scale, reuse=None):
@@ -256,14 +289,9 @@ class _SWA(torch.autograd.Function):
         q, k, v, o, lse = ctx.saved_tensors
         window, causal, scale = ctx.args
         ext = cuda_ext(q)
-        if hasattr(ext, "swa_bwd"):
-            dq, dk, dv = ext.swa_bwd(do.contiguous(), q, k, v, o, lse, int(window or 0), bool(causal), float(scale))
-            return dq, dk, dv, None, None, None, None
-        from flash_attn.flash_attn_interface import _flash_attn_backward
-        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-        left = -1 if (window is None or not causal) else window - 1
-        _flash_attn_backward(do.contiguous(), q, k, v, o, lse, dq, dk, dv, 0.0, float(scale), bool(causal),
-                             left, 0 if causal else -1, 0.0, None, False)
+        if not hasattr(ext, "swa_bwd"):
+            raise RuntimeError("the loaded extension has no swa_bwd: rebuild it (python -m uttt_b200.ops.build)")
+        dq, dk, dv = ext.swa_bwd(do.contiguous(), q, k, v, o, lse, int(window or 0), bool(causal), float(scale))
         return dq, dk, dv, None, None, None, None
 
 
@@ -275,6 +303,7 @@ def swa_attention(q, k, v, window: Optional[int], causal: bool = True, scale: Op
             and q.shape[2] == k.shape[2]:
         return _SWA.apply(q, k, v, window, causal, scale, reuse if torch.is_grad_enabled() else None)
     if q.is_cuda:
+        _note_fallback("swa_attention", q, "head dim or head grouping outside the kernel")
         return _sdpa_attention(q, k, v, window, causal, scale)
     return ref.swa_attention(q, k, v, window, causal, scale)
 
@@ -355,6 +384,7 @@ def build_group_plan(expert_idx: torch.Tensor, num_experts: int, reuse=None) -> 
                                                                    int(num_experts))
         rows_padded = ((bsz * n * k + TILE_ROWS - 1) // TILE_ROWS + bsz * num_experts) * TILE_ROWS
     else:
+        _note_fallback("build_group_plan", None)
         dest, offsets, sizes, tile_group, rows_padded = ref.build_group_plan(expert_idx, num_experts)
     return GroupPlan(dest, offsets, sizes, tile_group, int(rows_padded), bsz * num_experts, k)
 
@@ -743,6 +773,7 @@ def route_topk(rows, router, bias, topk: int, alpha: float = 1.0, bias_in_logits
                                      _ROUTER_MODES[router_type], rscale, norm_eps,
                                      reuse if torch.is_grad_enabled() else None)
         return idx.view(bsz, n, topk), w, psum
+    _note_fallback("route_topk", rows, "the router kernel wants D % 8 == 0, D <= 512, E % 8 == 0, E <= 64")
     logits = torch.matmul(rows.float(), router.float().t())
     if bias is not None and bias_in_logits:
         logits = logits + bias.view(1, 1, e)
@@ -815,6 +846,7 @@ def permute_rows(x: torch.Tensor, plan: GroupPlan, weights: Optional[torch.Tenso
     if _kernel("permute_rows", x) is not None and x.shape[-1] % 8 == 0:
         return _Permute.apply(x, plan.dest, plan.rows_padded, weights, plan.offsets, plan.sizes)
     if weights is None:
+        _note_fallback("permute_rows", x)
         return ref.permute_rows(x, plan.dest, plan.rows_padded)
     k = plan.dest.shape[1]
     scaled = (x.unsqueeze(1).float() * weights.unsqueeze(-1).float()).to(x.dtype).reshape(-1, x.shape[-1])
@@ -826,6 +858,7 @@ def unpermute_rows(y: torch.Tensor, plan: GroupPlan, weights: Optional[torch.Ten
     """Expert-major rows back to token-major, summing the top-k copies with ``weights`` [R, k]."""
     if _kernel("unpermute_rows", y) is not None and y.shape[-1] % 8 == 0:
         return _Unpermute.apply(y, plan.dest, weights, plan.offsets, plan.sizes)
+    _note_fallback("unpermute_rows", y)
     return ref.unpermute_rows(y, plan.dest, weights)
 
 
@@ -988,6 +1021,7 @@ def gg_nt(x, w, plan: GroupPlan):
     """out[r] = x[r] @ w[group(r)]^T;  x [R, K], w [G, N, K] -> [R, N]."""
     if _gg_kernel_ok(x, w) and _gg_dims_ok(x.shape[1], w.shape[1]):
         return _GGNT.apply(x, w, plan)
+    _note_fallback("gg_nt", x)
     return ref.gg_nt(x, w, plan.tile_group)
 
 
@@ -995,6 +1029,7 @@ def gg_nn(x, w, plan: GroupPlan):
     """out[r] = x[r] @ w[group(r)];  x [R, K], w [G, K, N] -> [R, N]."""
     if _gg_kernel_ok(x, w) and _gg_dims_ok(x.shape[1], w.shape[2]):
         return _GGNN.apply(x, w, plan)
+    _note_fallback("gg_nn", x)
     return ref.gg_nn(x, w, plan.tile_group)
 
 
@@ -1005,6 +1040,7 @@ def gg_tn(a, b, plan: GroupPlan, out_dtype: torch.dtype = torch.float32):
     if _gg_kernel_ok(a, b) and b.shape[1] % 128 == 0 and a.shape[1] % 64 == 0:
         # the kernel wants 128 rows of output per tile: compute the transposed product and view it back
         return _GGTN.apply(b, a, plan, out_dtype).transpose(1, 2)
+    _note_fallback("gg_tn", a)
     return ref.gg_tn(a, b, plan.tile_group, plan.num_groups, out_dtype)
 
 
@@ -1039,6 +1075,7 @@ class _SwiGLUBwd(torch.autograd.Function):
 def swiglu(y02: torch.Tensor) -> torch.Tensor:
     if _kernel("swiglu_fwd", y02) is not None and y02.shape[-1] % 16 == 0:
         return _SwiGLU.apply(y02)
+    _note_fallback("swiglu", y02)
     return ref.swiglu(y02)
 
 
@@ -1107,6 +1144,7 @@ def fw_write_pointwise(y02, dh, lr):
     """Inner-gradient pointwise block of the write: returns (dy02*lr, hidden*lr1)."""
     if _kernel("fw_write_pw_fwd", y02) is not None and y02.shape[-1] % 16 == 0:
         return _FwWritePW.apply(y02, dh, lr.float())
+    _note_fallback("fw_write_pointwise", y02)
     return ref.fw_write_pointwise(y02, dh, lr)
 
 
@@ -1320,6 +1358,7 @@ def newton_schulz(g: torch.Tensor, coeffs=ref.NS5_COEFFS) -> torch.Tensor:
     """Batched Newton-Schulz orthogonalisation (Muon).  g: [b, m, n] -> same shape, bf16 on GPU."""
     ext = _kernel("bmm_general", g)
     if ext is None or g.shape[1] % 128 != 0 or g.shape[2] % 128 != 0:
+        _note_fallback("newton_schulz", g)
         return ref.newton_schulz(g, coeffs)
     return _newton_schulz_kernels(g, coeffs)
 
@@ -1372,6 +1411,7 @@ def bmm(a, b, mode: int = 0, alpha: float = 1.0, d=None, beta: float = 0.0):
     if _kernel("bmm_general", a) is not None and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 \
             and _bmm_shapes_ok(a, b, mode):
         return _Bmm.apply(a, b, mode, alpha, d, beta)
+    _note_fallback("bmm", a, "M % 128, N % 64, K % 64")
     if mode == 0:
         out = torch.bmm(a, b.transpose(1, 2))
     elif mode == 1:
@@ -1471,4 +1511,5 @@ def plucker_embed(image, fxfycxcy, c2w, is_target, patch: int) -> torch.Tensor:
     if ext is not None and image.shape[-1] % patch == 0 and image.shape[-2] % patch == 0:
         return ext.plucker_embed(image.float().contiguous(), fxfycxcy.float().contiguous(), c2w.float().contiguous(),
                                  is_target.to(torch.uint8).contiguous(), int(patch))
+    _note_fallback("plucker_embed", image)
     return ref.plucker_embed(image, fxfycxcy, c2w, is_target, patch)
