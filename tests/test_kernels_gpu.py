@@ -1407,3 +1407,25 @@ def test_split_linear_matches_fp32():
     q2, _, _ = ops.split_linear(x, w, 3)
     (dw2,) = torch.autograd.grad(q2.float().sum(), [w])
     assert float(dw2[192:].abs().max()) == 0.0 and float(dw2[:192].abs().max()) > 0.0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_rms_norm_gated_matches_fp32(dtype):
+    """Per-head norm of the memory read with its gate in the same kernel; gate gradient from the norm's backward."""
+    from uttt_b200 import ops
+    torch.manual_seed(0)
+    x = torch.randn(3, 70, 4, 384, device=DEV, dtype=dtype, requires_grad=True)
+    w = (torch.randn(384, device=DEV) * 0.1 + 1).to(dtype).requires_grad_(True)
+    gate = torch.randn(3, 70, 4, device=DEV, dtype=dtype, requires_grad=True)
+    y = ops.rms_norm_gated(x, w, gate, 1e-5)
+    dy = torch.randn_like(y)
+    gx, gw, gg = torch.autograd.grad(y, [x, w, gate], dy)
+    xf, wf, gf = (t.detach().float().requires_grad_(True) for t in (x, w, gate))
+    yf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * wf * gf.unsqueeze(-1)
+    fx, fw_, fg = torch.autograd.grad(yf, [xf, wf, gf], dy.float())
+
+    def rel(a, b):
+        return float((a.float() - b).norm() / b.norm())
+    tol = 6e-3 if dtype == torch.bfloat16 else 1e-5
+    assert rel(y, yf) < tol and rel(gx, fx) < 2 * tol and rel(gw, fw_) < 2 * tol and rel(gg, fg) < 2 * tol, (
+        rel(y, yf), rel(gx, fx), rel(gw, fw_), rel(gg, fg))

@@ -13,6 +13,8 @@ read ``:296-349`` / ``:572-628``, inner gradient ``:389-451`` (loop oracle) and
 """
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass
 from typing import Optional, Tuple
 
@@ -23,6 +25,10 @@ import torch.nn.functional as F
 from .. import ops
 from ..ops import reference as ref
 from .common import RMSNorm
+
+
+# the gate of the memory read is applied inside the per-head norm kernel (UTTT_B200_GATED_NORM=0: separate multiply)
+_GATED_NORM = os.environ.get("UTTT_B200_GATED_NORM", "1") != "0"
 
 
 @dataclass
@@ -280,10 +286,15 @@ class FastWeightMemory(nn.Module):
     def finish_read(self, y_rows: torch.Tensor, x_in: torch.Tensor) -> torch.Tensor:
         """Per-head RMSNorm of the memory output, times the learned per-head SiLU gate."""
         b, l, _ = x_in.shape
-        y = self.ttt_norm(y_rows.reshape(b, l, self.fw_heads, self.head_dim))
+        y = y_rows.reshape(b, l, self.fw_heads, self.head_dim)
         if self.learnable_ttt_scale:
-            gate = F.silu(self.ttt_scale_proj(x_in))
-            y = y * gate.unsqueeze(-1).to(y.dtype)
+            gate = F.silu(self.ttt_scale_proj(x_in))                  # [b, l, heads]
+            if _GATED_NORM:
+                y = ops.rms_norm_gated(y, self.ttt_norm.weight, gate.to(y.dtype), self.ttt_norm.eps)
+            else:
+                y = self.ttt_norm(y) * gate.unsqueeze(-1).to(y.dtype)
+        else:
+            y = self.ttt_norm(y)
         y = y.reshape(b, l, -1)
         if self.output_proj is not None:
             y = self.output_proj(y)

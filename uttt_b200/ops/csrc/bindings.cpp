@@ -4,6 +4,9 @@
 namespace uttt {
 std::vector<at::Tensor> rms_norm_fwd(at::Tensor x, c10::optional<at::Tensor> w, double eps);
 std::vector<at::Tensor> rms_norm_bwd(at::Tensor dy, at::Tensor x, c10::optional<at::Tensor> w, at::Tensor rstd);
+std::vector<at::Tensor> rms_norm_gated_fwd(at::Tensor x, c10::optional<at::Tensor> w, at::Tensor gate, double eps);
+std::vector<at::Tensor> rms_norm_gated_bwd(at::Tensor dy, at::Tensor x, c10::optional<at::Tensor> w, at::Tensor rstd,
+                                           at::Tensor gate);
 at::Tensor embedding_fwd(at::Tensor table, at::Tensor ids);
 at::Tensor embedding_bwd(at::Tensor dy, at::Tensor ids, int64_t vocab);
 std::vector<at::Tensor> add_rms_norm_fwd(at::Tensor x, at::Tensor delta, c10::optional<at::Tensor> w, double eps);
@@ -105,6 +108,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   using namespace uttt;
   m.def("rms_norm_fwd", &rms_norm_fwd);
   m.def("rms_norm_bwd", &rms_norm_bwd);
+  m.def("rms_norm_gated_fwd", &rms_norm_gated_fwd);
+  m.def("rms_norm_gated_bwd", &rms_norm_gated_bwd);
   m.def("embedding_fwd", &embedding_fwd);
   m.def("embedding_bwd", &embedding_bwd);
   m.def("add_rms_norm_fwd", &add_rms_norm_fwd);

@@ -40,7 +40,8 @@ static inline int sm_count() { return at::cuda::getCurrentDeviceProperties()->mu
 template <typename T>
 __global__ void rms_norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
                                     float* __restrict__ rstd, int rows, int d, float eps,
-                                    const T* __restrict__ add = nullptr, T* __restrict__ sum_out = nullptr) {
+                                    const T* __restrict__ add = nullptr, T* __restrict__ sum_out = nullptr,
+                                    const T* __restrict__ row_scale = nullptr) {
   int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   int nwarps = (gridDim.x * blockDim.x) >> 5;
   int nv = d >> 3;
@@ -73,6 +74,8 @@ __global__ void rms_norm_fwd_kernel(const T* __restrict__ x, const T* __restrict
     ss = warp_sum(ss);
     float rs = rsqrtf(ss / d + eps);
     if (lane == 0) rstd[r] = rs;
+    // an optional per-row factor (the gate of the memory read) is applied to the normalised row in the same pass
+    const float rscale = row_scale != nullptr ? rs * to_f<T>(row_scale[r]) : rs;
     T* yr = y + (size_t)r * d;
     for (int v = lane; v < nv; v += 32) {
       float f[8], g[8];
@@ -80,10 +83,10 @@ __global__ void rms_norm_fwd_kernel(const T* __restrict__ x, const T* __restrict
       if (w) {
         Vec8<T>::load(w + v * 8, g);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] = f[i] * rs * g[i];
+        for (int i = 0; i < 8; ++i) f[i] = f[i] * rscale * g[i];
       } else {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] *= rs;
+        for (int i = 0; i < 8; ++i) f[i] *= rscale;
       }
       Vec8<T>::store(yr + v * 8, f);
     }
@@ -95,7 +98,8 @@ __global__ void rms_norm_fwd_kernel(const T* __restrict__ x, const T* __restrict
 template <typename T, int MAXV>
 __global__ void rms_norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
                                     const float* __restrict__ rstd, T* __restrict__ dx, float* __restrict__ dw,
-                                    int rows, int d, const T* __restrict__ dres = nullptr) {
+                                    int rows, int d, const T* __restrict__ dres = nullptr,
+                                    const T* __restrict__ row_scale = nullptr, float* __restrict__ dscale = nullptr) {
   int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   int nwarps = (gridDim.x * blockDim.x) >> 5;
   int nv = d >> 3;
@@ -108,6 +112,8 @@ __global__ void rms_norm_bwd_kernel(const T* __restrict__ dy, const T* __restric
     const T* xr = x + (size_t)r * d;
     const T* gr = dy + (size_t)r * d;
     float rs = rstd[r];
+    // y = xhat * w * s with a per-row factor s: the cotangent of xhat * w is s * dy, and ds = <dy, xhat * w>
+    const float sc = row_scale != nullptr ? to_f<T>(row_scale[r]) : 1.f;
     float dot = 0.f;
 #pragma unroll
     for (int j = 0; j < MAXV; ++j) {
@@ -122,11 +128,13 @@ __global__ void rms_norm_bwd_kernel(const T* __restrict__ dy, const T* __restric
           float xh = fx[i] * rs;
           float gw = w ? fg[i] * fw[i] : fg[i];
           dot += gw * xh;
-          acc[j][i] += fg[i] * xh;
+          acc[j][i] += fg[i] * sc * xh;
         }
       }
     }
-    dot = warp_sum(dot) / d;
+    dot = warp_sum(dot);
+    if (dscale != nullptr && lane == 0) dscale[r] = dot;
+    dot = dot * sc / d;
     T* dxr = dx + (size_t)r * d;
 #pragma unroll
     for (int j = 0; j < MAXV; ++j) {
@@ -138,7 +146,7 @@ __global__ void rms_norm_bwd_kernel(const T* __restrict__ dy, const T* __restric
         if (w) Vec8<T>::load(w + v * 8, fw);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          float gw = w ? fg[i] * fw[i] : fg[i];
+          float gw = (w ? fg[i] * fw[i] : fg[i]) * sc;
           o[i] = rs * (gw - fx[i] * rs * dot);
         }
         if (dres != nullptr) {                   // gradient that reached the residual sum directly
@@ -175,7 +183,8 @@ __global__ void rms_norm_bwd_kernel(const T* __restrict__ dy, const T* __restric
 }
 
 static std::vector<at::Tensor> rms_norm_fwd_impl(at::Tensor x, c10::optional<at::Tensor> w, double eps,
-                                                 c10::optional<at::Tensor> add) {
+                                                 c10::optional<at::Tensor> add,
+                                                 c10::optional<at::Tensor> row_scale = c10::nullopt) {
   c10::cuda::CUDAGuard guard(x.device());
   int rows = x.size(0), d = x.size(1);
   TORCH_CHECK(x.is_contiguous() && d % 8 == 0);
@@ -190,10 +199,16 @@ static std::vector<at::Tensor> rms_norm_fwd_impl(at::Tensor x, c10::optional<at:
   at::Tensor wc;
   if (w.has_value() && w->defined()) wc = w->to(x.scalar_type()).contiguous();
   int blocks = std::min((rows + 7) / 8, sm_count() * 8);
+  at::Tensor sc;
+  if (row_scale.has_value() && row_scale->defined()) {
+    sc = row_scale->to(x.scalar_type()).contiguous();
+    TORCH_CHECK(sc.numel() == rows, "one factor per row");
+  }
   UTTT_DISPATCH_FLOAT(x, {
     rms_norm_fwd_kernel<T><<<std::max(blocks, 1), 256, 0, cur_stream()>>>(
         ptr<T>(x), wc.defined() ? ptr<T>(wc) : nullptr, ptr<T>(y), ptr<float>(rstd), rows, d, (float)eps,
-        addc.defined() ? ptr<T>(addc) : nullptr, addc.defined() ? ptr<T>(sum) : nullptr);
+        addc.defined() ? ptr<T>(addc) : nullptr, addc.defined() ? ptr<T>(sum) : nullptr,
+        sc.defined() ? ptr<T>(sc) : nullptr);
   });
   count_launch();
   if (addc.defined()) return {sum, y, rstd};
@@ -202,13 +217,18 @@ static std::vector<at::Tensor> rms_norm_fwd_impl(at::Tensor x, c10::optional<at:
 std::vector<at::Tensor> rms_norm_fwd(at::Tensor x, c10::optional<at::Tensor> w, double eps) {
   return rms_norm_fwd_impl(x, w, eps, c10::nullopt);
 }
+// y[r] = rms_norm(x[r]) * w * gate[r]  ->  {y, rstd}
+std::vector<at::Tensor> rms_norm_gated_fwd(at::Tensor x, c10::optional<at::Tensor> w, at::Tensor gate, double eps) {
+  return rms_norm_fwd_impl(x, w, eps, c10::nullopt, gate);
+}
 // s = x + delta, y = rms_norm(s) * w  ->  {s, y, rstd}
 std::vector<at::Tensor> add_rms_norm_fwd(at::Tensor x, at::Tensor delta, c10::optional<at::Tensor> w, double eps) {
   return rms_norm_fwd_impl(x, w, eps, delta);
 }
 
 static std::vector<at::Tensor> rms_norm_bwd_impl(at::Tensor dy, at::Tensor x, c10::optional<at::Tensor> w,
-                                                 at::Tensor rstd, c10::optional<at::Tensor> dres) {
+                                                 at::Tensor rstd, c10::optional<at::Tensor> dres,
+                                                 c10::optional<at::Tensor> row_scale = c10::nullopt) {
   c10::cuda::CUDAGuard guard(x.device());
   at::Tensor dresc;
   if (dres.has_value() && dres->defined()) {
@@ -227,26 +247,40 @@ static std::vector<at::Tensor> rms_norm_bwd_impl(at::Tensor dy, at::Tensor x, c1
     dw = at::zeros({1}, x.options().dtype(at::kFloat));
   }
   int nv = d / 8;
+  at::Tensor sc, dsc;
+  if (row_scale.has_value() && row_scale->defined()) {
+    sc = row_scale->to(x.scalar_type()).contiguous();
+    TORCH_CHECK(sc.numel() == rows, "one factor per row");
+    dsc = at::empty({rows}, x.options().dtype(at::kFloat));
+  }
   UTTT_DISPATCH_FLOAT(x, {
     const T* wp = wc.defined() ? ptr<T>(wc) : nullptr;
     float* dwp = wc.defined() ? ptr<float>(dw) : nullptr;
     const T* rp = dresc.defined() ? ptr<T>(dresc) : nullptr;
+    const T* sp = sc.defined() ? ptr<T>(sc) : nullptr;
+    float* dsp = sc.defined() ? ptr<float>(dsc) : nullptr;
     if (nv <= 32 * 2)
       rms_norm_bwd_kernel<T, 2><<<blocks, 128, 0, cur_stream()>>>(ptr<T>(dy), ptr<T>(x), wp, ptr<float>(rstd),
-                                                                   ptr<T>(dx), dwp, rows, d, rp);
+                                                                   ptr<T>(dx), dwp, rows, d, rp, sp, dsp);
     else if (nv <= 32 * 8)
       rms_norm_bwd_kernel<T, 8><<<blocks, 128, 0, cur_stream()>>>(ptr<T>(dy), ptr<T>(x), wp, ptr<float>(rstd),
-                                                                   ptr<T>(dx), dwp, rows, d, rp);
+                                                                   ptr<T>(dx), dwp, rows, d, rp, sp, dsp);
     else
       rms_norm_bwd_kernel<T, 16><<<blocks, 128, 0, cur_stream()>>>(ptr<T>(dy), ptr<T>(x), wp, ptr<float>(rstd),
-                                                                    ptr<T>(dx), dwp, rows, d, rp);
+                                                                    ptr<T>(dx), dwp, rows, d, rp, sp, dsp);
   });
   count_launch();
   if (wc.defined()) dw = dw.sum(0);
+  if (sc.defined()) return {dx, dw, dsc};
   return {dx, dw};
 }
 std::vector<at::Tensor> rms_norm_bwd(at::Tensor dy, at::Tensor x, c10::optional<at::Tensor> w, at::Tensor rstd) {
   return rms_norm_bwd_impl(dy, x, w, rstd, c10::nullopt);
+}
+// -> {dx, dw, dgate [rows] fp32}
+std::vector<at::Tensor> rms_norm_gated_bwd(at::Tensor dy, at::Tensor x, c10::optional<at::Tensor> w, at::Tensor rstd,
+                                           at::Tensor gate) {
+  return rms_norm_bwd_impl(dy, x, w, rstd, c10::nullopt, gate);
 }
 // backward of add_rms_norm_fwd: d(x) = d(delta) = ds + rms_norm_bwd(dy, s)  ->  {dsum, dw}
 std::vector<at::Tensor> add_rms_norm_bwd(at::Tensor dy, c10::optional<at::Tensor> ds, at::Tensor s,

@@ -108,6 +108,36 @@ def rms_norm(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float = 1e-6)
     return ref.rms_norm(x, weight, eps)
 
 
+class _RMSNormGated(torch.autograd.Function):
+    """``rms_norm(x) * weight * gate[row]`` in one pass; the backward gives the gate's gradient from the same kernel
+    that produces the input and weight gradients (no separate multiply, product or row-sum launches)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, gate, eps):
+        ext = cuda_ext(x)
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        g1 = gate.reshape(-1).to(x2.dtype).contiguous()
+        y, rstd = ext.rms_norm_gated_fwd(x2, weight, g1, float(eps))
+        ctx.save_for_backward(x2, weight, rstd, g1)
+        ctx.shape, ctx.gate_shape, ctx.gate_dtype = x.shape, gate.shape, gate.dtype
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight, rstd, g1 = ctx.saved_tensors
+        ext = cuda_ext(x2)
+        dx, dw, dg = ext.rms_norm_gated_bwd(dy.reshape(x2.shape).contiguous(), x2, weight, rstd, g1)
+        dwo = None if weight is None else dw.to(weight.dtype)
+        return dx.view(ctx.shape), dwo, dg.view(ctx.gate_shape).to(ctx.gate_dtype), None
+
+
+def rms_norm_gated(x: torch.Tensor, weight: Optional[torch.Tensor], gate: torch.Tensor, eps: float = 1e-6):
+    """``rms_norm(x, weight) * gate[..., None]`` with one factor per row (``gate.shape == x.shape[:-1]``)."""
+    if _kernel("rms_norm_gated_fwd", x) is not None and x.shape[-1] % 8 == 0 and x.shape[-1] <= 4096:
+        return _RMSNormGated.apply(x, weight, gate, eps)
+    return rms_norm(x, weight, eps) * gate.unsqueeze(-1).to(x.dtype)
+
+
 class _AddRMSNorm(torch.autograd.Function):
     """s = x + delta; y = rms_norm(s) * weight in one kernel; the backward adds the gradient that reached s
     directly inside the norm's backward kernel."""
