@@ -1473,6 +1473,63 @@ class _FrobNormalize(torch.autograd.Function):
         return cuda_ext(g).frob_normalize_bwd(g, sumsq, dx, ctx.eps), None
 
 
+class _NSIteration(torch.autograd.Function):
+    """One Newton-Schulz iteration ``X' = a X + B X`` (wide; ``A = X X^T``) or ``X' = a X + X B`` (tall;
+    ``A = X^T X``) with ``B = b A + c A A``, and its hand-written backward: six batched GEMMs whose epilogues add the
+    partial gradients as they are formed (``alpha * product + beta * addend``).  Left to autograd the same six products
+    are followed by four bank-sized additions and a scaling per iteration."""
+
+    @staticmethod
+    def forward(ctx, x, a, b, c, tall):
+        ext = cuda_ext(x)
+        x = x.contiguous()
+        if tall:
+            aa = ext.bmm_general(x, x, 2, 1.0, None, 0.0)            # X^T X   [n, n]
+            bb = ext.bmm_general(aa, aa, 0, float(c), aa, float(b))  # c A A^T + b A (A symmetric)
+            out = ext.bmm_general(x, bb, 1, 1.0, x, float(a))        # X B + a X
+        else:
+            aa = ext.bmm_general(x, x, 0, 1.0, None, 0.0)            # X X^T   [m, m]
+            bb = ext.bmm_general(aa, aa, 0, float(c), aa, float(b))
+            out = ext.bmm_general(bb, x, 1, 1.0, x, float(a))        # B X + a X
+        _count(0)
+        ctx.save_for_backward(x, aa, bb)
+        ctx.coef, ctx.tall = (float(a), float(b), float(c)), bool(tall)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        x, aa, bb = ctx.saved_tensors
+        a, b, c = ctx.coef
+        ext = cuda_ext(x)
+        g = g.to(x.dtype).contiguous()
+        mm = ext.bmm_general
+        if ctx.tall:
+            t1 = mm(g, bb, 1, 1.0, g, a)                  # G B + a G            (B symmetric)
+            db = mm(x, g, 2, 1.0, None, 0.0)              # X^T G
+            u = mm(db, aa, 1, c, db, b)                   # c dB A + b dB
+            da = mm(aa, db, 1, c, u, 1.0)                 # c A dB + u
+            t2 = mm(x, da, 1, 1.0, t1, 1.0)               # X dA + t1
+            dx = mm(x, da, 0, 1.0, t2, 1.0)               # X dA^T + t2
+        else:
+            t1 = mm(bb, g, 1, 1.0, g, a)                  # B G + a G
+            db = mm(g, x, 0, 1.0, None, 0.0)              # G X^T
+            u = mm(db, aa, 1, c, db, b)
+            da = mm(aa, db, 1, c, u, 1.0)
+            t2 = mm(da, x, 1, 1.0, t1, 1.0)               # dA X + t1
+            dx = mm(da, x, 2, 1.0, t2, 1.0)               # dA^T X + t2
+        return dx, None, None, None, None
+
+
+_NS_FUSED_BACKWARD = os.environ.get("UTTT_B200_NS_FUSED_BACKWARD", "1") != "0"
+
+
+def _ns_iteration_ok(x: torch.Tensor, tall: bool) -> bool:
+    m, n = x.shape[1], x.shape[2]
+    inner = n if tall else m                      # side of the square Gram matrix
+    return (_NS_FUSED_BACKWARD and x.dtype == torch.bfloat16 and m % 128 == 0 and n % 128 == 0 and inner % 128 == 0
+            and _kernel("bmm_general", x) is not None)
+
+
 def _newton_schulz_kernels(g, coeffs):
     """Newton-Schulz in the given orientation: wide X iterates with X X^T on the left, tall X with X^T X on the
     right (X p(X^T X) = p(X X^T) X), so no transpose is ever materialised."""
@@ -1484,6 +1541,9 @@ def _newton_schulz_kernels(g, coeffs):
         x = (x / (x.float().norm(dim=(1, 2), keepdim=True) + 1e-7).to(torch.bfloat16)).contiguous()
     tall = g.size(1) > g.size(2)
     for a, b, c in coeffs:
+        if _ns_iteration_ok(x, tall):
+            x = _NSIteration.apply(x, a, b, c, tall)
+            continue
         if tall:
             aa = bmm(x, x, 2)                       # X^T X   [n, n]
             bb = bmm(aa, aa, 0, c, aa, b)           # c A A^T + b A (A symmetric)
