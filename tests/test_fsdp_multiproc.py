@@ -56,6 +56,47 @@ def _worker(rank: int, world: int, port: int, backend: str, out_path: str):
     dist.destroy_process_group()
 
 
+def _hybrid_worker(rank: int, world: int, port: int, replicas: int, out_path: str):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from uttt_b200.train.engine import EngineConfig, TrainEngine
+    eng = TrainEngine(_cfg(), EngineConfig(micro_batch_size=2, lr=1e-2, warmup_steps=0, total_steps=10, seed=0,
+                                           weight_decay=0.1, eps=1e-3, data_parallel_replicate_degree=replicas),
+                      torch.device("cpu"))
+    assert eng.trainer.world == world // replicas and eng.trainer.replicas == replicas
+    stats = None
+    for _ in range(2):
+        eng.train_step(_batch(rank))
+        stats = eng.last_stats
+    sd = {k: v.detach().float().cpu() for k, v in eng.model.state_dict().items()}
+    torch.save({"model": sd, "grad_norm": float(stats["grad_norm"]),
+                "master_numel": sum(u.master.numel() for u in eng.trainer.units)}, out_path + f".{rank}")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_hybrid_sharding_matches_full_sharding(tmp_path):
+    """Four gloo ranks as 2 shard groups x 2 replicas (optimizer state sharded over two ranks, gradients all-reduced
+    across the two replicas of each shard) train exactly like four ranks that shard over all of them."""
+    runs = {}
+    for replicas in (1, 2):
+        out = str(tmp_path / f"h{replicas}.pt")
+        mp.spawn(_hybrid_worker, args=(4, _free_port(), replicas, out), nprocs=4, join=True)
+        runs[replicas] = [torch.load(out + f".{r}", weights_only=False) for r in range(4)]
+    for r in range(4):                                   # every rank ends with the same parameters
+        for k, v in runs[2][0]["model"].items():
+            if v.is_floating_point():
+                torch.testing.assert_close(runs[2][r]["model"][k], v, atol=0, rtol=0, msg=f"rank {r}: {k}")
+    ratio = runs[2][0]["master_numel"] / runs[1][0]["master_numel"]          # shards are twice as large (up to padding)
+    assert 1.95 < ratio < 2.05, ratio
+    assert abs(runs[2][0]["grad_norm"] - runs[1][0]["grad_norm"]) <= 1e-5 * runs[1][0]["grad_norm"]
+    for k, v in runs[1][0]["model"].items():
+        if v.is_floating_point() and "loss_free" not in k:
+            torch.testing.assert_close(runs[2][0]["model"][k], v, atol=2e-5, rtol=2e-4, msg=k)
+
+
 def _single_process_reference(device: str, dtype_note: str):
     sys.path.insert(0, ROOT)
     from uttt_b200.train.engine import EngineConfig, TrainEngine

@@ -97,16 +97,19 @@ def test_every_flag_has_a_reader_or_is_rejected(tmp_path):
     job, model = _write(tmp_path)
     base = ["--job.config_file", job, "--model.config", model]
     for bad in (["--training.compile"], ["--optimizer.name", "Lion"], ["--optimizer.early_step_in_backward"],
-                ["--training.data_parallel_replicate_degree", "2"], ["--training.enable_cpu_offload"],
+                ["--training.enable_cpu_offload"],
                 ["--training.fsdp_reshard_after_forward", "always"], ["--fault_tolerance.enable"],
                 ["--training.mixed_precision_param", "float16"], ["--model.converters", "float8"],
                 ["--experimental.enable_compiled_autograd"]):
         with pytest.raises(NotImplementedError):
             JobConfig().parse_args(base + bad)
     for bad in (["--checkpoint.async_mode", "sometimes"], ["--activation_checkpoint.mode", "maybe"],
-                ["--activation_offload.mode", "disk"]):
+                ["--activation_offload.mode", "disk"], ["--training.data_parallel_replicate_degree", "0"]):
         with pytest.raises(ValueError):
             JobConfig().parse_args(base + bad)
+    # hybrid sharding is accepted when it divides the job size (a single process accepts any positive degree here;
+    # the engine checks it against the real job)
+    JobConfig().parse_args(base + ["--training.data_parallel_replicate_degree", "2"])
     # the reference's own job file values are all accepted
     JobConfig().parse_args(base + ["--training.fsdp_reshard_after_forward", "never", "--activation_checkpoint.mode",
                                    "none", "--activation_checkpoint.selective_ac_option", "1"])

@@ -70,7 +70,8 @@ FLAG_READERS: Dict[str, str] = {
     "optimizer": "train/engine.py::EngineConfig (lr, betas, eps, decay); name / implementation / "
                  "early_step_in_backward: validate",
     "lr_scheduler": "train/lr.py::WarmupDecayLR",
-    "training": "lm_trainer.main + train/data.py::build_dataloader; parallel degrees, reshard policy, offload, "
+    "training": "lm_trainer.main + train/data.py::build_dataloader; data_parallel_replicate_degree: train/engine.py "
+                "(hybrid sharding); other parallel degrees, reshard policy, offload, "
                 "compile, mixed precision: validate; gc_freq, deterministic, seed: lm_trainer.main; cuda_graph: "
                 "train/engine.py (forward + backward replayed as one CUDA graph)",
     "metrics": "lm_trainer.Metrics",
@@ -154,12 +155,15 @@ class JobConfig:
         if o.early_step_in_backward:
             raise NotImplementedError("optimizer.early_step_in_backward: the step needs the global gradient norm "
                                       "for clipping, so it runs after backward")
-        if t.data_parallel_replicate_degree != 1:
-            raise NotImplementedError("training.data_parallel_replicate_degree != 1 (HSDP): optimizer state is sharded "
-                                      "over all data-parallel ranks of the job")
-        if t.data_parallel_shard_degree not in (-1, 0) and t.data_parallel_shard_degree != int(
-                __import__("os").environ.get("WORLD_SIZE", t.data_parallel_shard_degree)):
-            raise NotImplementedError("training.data_parallel_shard_degree must be -1 or the job size")
+        world = int(__import__("os").environ.get("WORLD_SIZE", "1"))
+        rep = int(t.data_parallel_replicate_degree)
+        if rep < 1 or (world > 1 and world % rep != 0):
+            raise ValueError(f"training.data_parallel_replicate_degree={rep} does not divide the job size {world}")
+        # hybrid sharding: the optimizer state is sharded over world / replicate ranks, replicated `replicate` times
+        if t.data_parallel_shard_degree not in (-1, 0) and world > 1 and \
+                t.data_parallel_shard_degree * rep != world:
+            raise ValueError("training.data_parallel_shard_degree x training.data_parallel_replicate_degree must equal "
+                             "the job size (or leave the shard degree at -1)")
         if str(t.fsdp_reshard_after_forward) not in ("default", "never"):
             raise NotImplementedError("training.fsdp_reshard_after_forward='always': parameters stay gathered between "
                                       "steps (the reference's setting for these models is 'never')")

@@ -120,12 +120,17 @@ class ShardedTrainer:
     def __init__(self, model: nn.Module, unit_modules: Optional[Sequence[Tuple[str, nn.Module]]] = None,
                  opt: Optional[AdamWConfig] = None, compute_dtype: Optional[torch.dtype] = None,
                  no_decay: Callable[[str, nn.Parameter], bool] = default_no_decay, process_group=None,
-                 use_symmetric_memory: Optional[bool] = None):
+                 use_symmetric_memory: Optional[bool] = None, replicate_group=None):
+        """``process_group``: the ranks that shard the optimizer state (default: all).  ``replicate_group``: the ranks
+        that hold the same shard in other shard groups (hybrid sharding: gradients are reduce-scattered inside a shard
+        group and all-reduced across the replicas of each shard; ``training.data_parallel_replicate_degree``)."""
         self.model = model
         self.opt = opt or AdamWConfig()
         self.group = process_group
         self.world = dist.get_world_size(process_group) if _dist_ready() else 1
         self.rank = dist.get_rank(process_group) if _dist_ready() else 0
+        self.replicate_group = replicate_group
+        self.replicas = dist.get_world_size(replicate_group) if (_dist_ready() and replicate_group is not None) else 1
         first = next(model.parameters())
         self.device = first.device
         if compute_dtype is None:
@@ -222,7 +227,8 @@ class ShardedTrainer:
         opt = self.opt
         lr = opt.lr if lr is None else lr
         self.step_count += 1
-        scale = 1.0 / (self.world * grad_divisor)
+        scale = 1.0 / (self.world * self.replicas * grad_divisor)
+        hybrid = self.replicas > 1
         shards: List[torch.Tensor] = []
         sq = torch.zeros((), dtype=torch.float32, device=self.device)
         fused = self.symm is not None
@@ -237,12 +243,15 @@ class ShardedTrainer:
             src = u.grad_accum if u.grad_accum is not None else u.grad
             gmul = 1.0
             if fused:
-                g = self.symm.reduce_scatter_sumsq(u, src, scale, sq1)
+                g = self.symm.reduce_scatter_sumsq(u, src, scale, torch.zeros_like(sq1) if hybrid else sq1)
             elif self.world > 1:
                 g = torch.empty(u.shard_numel, dtype=torch.float32, device=self.device)
                 dist.reduce_scatter_tensor(g, src.float(), group=self.group)
                 g.mul_(scale)
-                sq += g.pow(2).sum()
+                if not hybrid:
+                    sq += g.pow(2).sum()
+            elif hybrid:
+                g = src.float() * scale
             elif native:
                 # single rank: the optimizer kernel reads the gradient buffer in place
                 g, gmul = src, scale
@@ -250,6 +259,10 @@ class ShardedTrainer:
             else:
                 g = src.float() * scale if scale != 1.0 or src.dtype != torch.float32 else src
                 sq += g.pow(2).sum()
+            if hybrid:
+                # the same shard of the other shard groups: sum across the replicas, then its share of the norm
+                dist.all_reduce(g, group=self.replicate_group)
+                sq += g.float().pow(2).sum()
             shards.append(g)
             gmuls.append(gmul)
         if self.world > 1:

@@ -39,6 +39,7 @@ class EngineConfig:
     activation_checkpoint: bool = True
     keep_activation_layers: tuple = ()     # layer indices that skip recomputation (needs spare device memory)
     activation_offload: bool = False       # saved tensors of the forward go to pinned host memory until backward
+    data_parallel_replicate_degree: int = 1   # hybrid sharding: optimizer state sharded over world / R ranks, R replicas
     expert_capacity_factor: float = 2.0    # expert-parallel staging rows / balanced load (0 = size for the worst case)
     cuda_graph: bool = False               # replay forward + backward of a micro-batch as one CUDA graph
     cuda_graph_warmup: int = 2             # eager steps before the capture (lazy initialisation happens in them)
@@ -137,7 +138,9 @@ class TrainEngine:
         opt = AdamWConfig(lr=self.cfg.lr, beta1=self.cfg.beta1, beta2=self.cfg.beta2, eps=self.cfg.eps,
                           weight_decay=self.cfg.weight_decay, max_norm=self.cfg.max_norm,
                           skip_nan_inf=self.cfg.skip_nan_inf)
-        self.trainer = ShardedTrainer(self.model, lm_fsdp_units(self.model), opt)
+        shard_group, replicate_group = self._hybrid_groups(int(self.cfg.data_parallel_replicate_degree or 1))
+        self.trainer = ShardedTrainer(self.model, lm_fsdp_units(self.model), opt, process_group=shard_group,
+                                      replicate_group=replicate_group)
         self.lr_sched = WarmupDecayLR(self.cfg.lr, self.cfg.total_steps, self.cfg.warmup_steps,
                                       self.cfg.decay_type, self.cfg.lr_min)
         self.copy_stream = torch.cuda.Stream(device) if device.type == "cuda" else None
@@ -147,6 +150,28 @@ class TrainEngine:
         self._graphs: Dict[Any, "_StepGraph"] = {}
         self._graph_pool = None
         self.graph_error: Optional[str] = None     # why graph mode was given up, if it was
+
+    @staticmethod
+    def _hybrid_groups(replicas: int):
+        """(shard group, replicate group) of this rank for hybrid sharding, or (None, None): consecutive ranks shard
+        (they share an NVLink domain), ranks at the same position of every shard group replicate
+        (uttt_llm/flame/models/parallelize_fla.py:632-648 builds the same two mesh dimensions)."""
+        if replicas <= 1 or not (dist.is_available() and dist.is_initialized()):
+            return None, None
+        world, rank = dist.get_world_size(), dist.get_rank()
+        if world % replicas != 0:
+            raise ValueError(f"data_parallel_replicate_degree={replicas} does not divide the job size {world}")
+        shard = world // replicas
+        mine_s = mine_r = None
+        for r in range(replicas):                       # every rank creates every group, in the same order
+            g = dist.new_group(list(range(r * shard, (r + 1) * shard)))
+            if r * shard <= rank < (r + 1) * shard:
+                mine_s = g
+        for j in range(shard):
+            g = dist.new_group([r * shard + j for r in range(replicas)])
+            if rank % shard == j:
+                mine_r = g
+        return mine_s, mine_r
 
     # ------------------------------------------------------------------ data movement
     def to_device(self, batch: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:

@@ -181,7 +181,8 @@ def main(job: Optional[JobConfig] = None) -> TrainState:
                         activation_checkpoint=True,
                         keep_activation_layers=tuple(int(i) for i in job.activation_checkpoint.keep_layers),
                         activation_offload=job.activation_offload.mode == "offload",
-                        cuda_graph=bool(job.training.cuda_graph))
+                        cuda_graph=bool(job.training.cuda_graph),
+                        data_parallel_replicate_degree=int(job.training.data_parallel_replicate_degree))
     engine = TrainEngine(model_cfg, ecfg)
     if rank == 0 and job.job.print_args:
         print("\n".join(param_check(engine.model)), flush=True)
