@@ -283,3 +283,51 @@ def test_checkpoint_grouping_and_sweep_do_not_change_the_numbers():
         LVSMModel(_cfg(aggregate_write=False, offload_master_states=True))
     with pytest.raises(NotImplementedError):
         LVSMModel(_cfg(use_shared_expert=True))
+
+
+def test_shared_expert_raw_gradient_is_the_squared_error_gradient():
+    """The always-on expert's raw update equals autograd's gradient of 1/2 |f(k) - v|^2, each matrix scaled by its
+    learning rate averaged over the sequence (uttt_nvs/models/uttt_moe_block.py:425-462)."""
+    from uttt_b200.nvs.blocks import FastWeightMemory
+    torch.manual_seed(0)
+    b, t, d, inter = 2, 24, 16, 32
+    k, v = torch.randn(b, t, d), torch.randn(b, t, d)
+    lr = torch.rand(b, t, 3)
+    se = tuple(torch.randn(b, 1, *shape, requires_grad=True) for shape in ((inter, d), (d, inter), (inter, d)))
+    d0, d1, d2 = FastWeightMemory.shared_expert_grad(k, v, lr, tuple(w.detach() for w in se))
+    out = FastWeightMemory.shared_expert_ffn(k, se)
+    g0, g1, g2 = torch.autograd.grad(0.5 * (out - v).pow(2).sum(), se)
+    mean = lr.mean(dim=1)
+    for got, want, i in ((d0, g0, 0), (d1, g1, 1), (d2, g2, 2)):
+        torch.testing.assert_close(got, want * mean[:, i].view(b, 1, 1, 1), atol=1e-4, rtol=1e-4)
+
+
+@pytest.mark.parametrize("aggregate", [True, False])
+def test_view_synthesis_with_per_layer_shared_expert(aggregate):
+    """``use_shared_expert`` with one always-on expert per layer: the parameters carry the reference's names, take
+    gradients, and the model differs from the one without it."""
+    from uttt_b200.nvs.data import SyntheticScenes
+    from uttt_b200.nvs.model import LVSMModel
+    params = {"attn_head_dim": 16, "fw_head_dim": 16, "inter_multi": 2, "fw_inter_multi": 1, "use_muon": False,
+              "num_experts": 4, "num_active_experts": 2, "l2_norm": True, "pool_mode": "shared",
+              "router_share_mode": "share_all", "aggregate_write": aggregate, "use_shared_expert": True,
+              "shared_expert_per_layer": True}
+    cfg = {"model": {"image_size": 16, "patch_size": 8, "dim": 32, "layers": 2,
+                     "block_config": {"type": "uttt_nvs.models.uttt_moe_block.MemoryModel", "params": params}},
+           "training": {"num_views": 3, "lpips_loss_weight": 0.0}}
+    torch.manual_seed(0)
+    model = LVSMModel(cfg)
+    keys = set(model.state_dict())
+    for name in ("w0", "w1", "w2"):
+        for layer in range(2):
+            assert f"transformer_blocks.shared_expert_{name}_list.{layer}" in keys
+    batch = next(SyntheticScenes(2, 3, 16, seed=1, rank=0, pin=False))
+    out = model(batch)
+    out["loss_metrics"]["loss"].backward()
+    for name in ("w0", "w1", "w2"):
+        for p in getattr(model.transformer_blocks, f"shared_expert_{name}_list"):
+            assert p.grad is not None and float(p.grad.abs().max()) > 0
+    with pytest.raises(NotImplementedError):
+        params2 = dict(params, shared_expert_per_layer=False)
+        LVSMModel({"model": {**cfg["model"], "block_config": {"type": cfg["model"]["block_config"]["type"],
+                                                              "params": params2}}, "training": cfg["training"]})

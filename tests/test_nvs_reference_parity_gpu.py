@@ -20,7 +20,9 @@ REF = os.path.join(ROOT, "baseline", "_ref")
 
 @pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "uttt_nvs", "models")),
                     reason="reference tree (baseline/_ref/uttt_nvs) not present")
-def test_view_synthesis_model_matches_the_reference_on_gpu():
+@pytest.mark.parametrize("extra", [dict(), dict(use_shared_expert=True, shared_expert_per_layer=True)],
+                         ids=["routed pool", "with a per-layer always-on expert"])
+def test_view_synthesis_model_matches_the_reference_on_gpu(extra):
     import yaml
     sys.path.insert(0, os.path.join(ROOT, "baseline"))
     import run_reference as rr
@@ -35,7 +37,7 @@ def test_view_synthesis_model_matches_the_reference_on_gpu():
     with open(os.path.join(REF, "uttt_nvs", "configs", "width", "obj", "uttt_moe_e32a2.yaml")) as fh:
         cfg = yaml.safe_load(fh)
     cfg["model"].update(dim=256, layers=2, image_size=128)
-    cfg["model"]["block_config"]["params"].update(num_experts=8, num_active_experts=2)
+    cfg["model"]["block_config"]["params"].update(num_experts=8, num_active_experts=2, **extra)
     cfg["training"].update(num_views=4, lpips_loss_weight=0.0)
     dev = torch.device("cuda", 0)
     torch.manual_seed(0)
@@ -72,3 +74,8 @@ def test_view_synthesis_model_matches_the_reference_on_gpu():
     cos = float(torch.nn.functional.cosine_similarity(g_r, g_o, dim=0))
     assert cos > 0.9, cos
     assert 0.5 < float(g_o.norm() / g_r.norm()) < 2.0
+    if extra.get("use_shared_expert"):
+        # the always-on experts' initial weights take the same gradient in both implementations
+        g_r = ref.transformer_blocks.shared_expert_w1_list[0].grad.float().flatten()
+        g_o = ours.transformer_blocks.shared_expert_w1_list[0].grad.float().flatten()
+        assert float(torch.nn.functional.cosine_similarity(g_r, g_o, dim=0)) > 0.9

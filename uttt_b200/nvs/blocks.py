@@ -87,8 +87,7 @@ class FastWeightMemory(nn.Module):
         super().__init__()
         if sigmoid_router:
             raise NotImplementedError("sigmoid routing is not supported")
-        if use_shared_expert:
-            raise NotImplementedError("the always-on shared expert is not implemented")
+        self.use_shared_expert = bool(use_shared_expert)
         self.dim = dim
         self.head_dim = fw_head_dim or dim
         self.num_heads = dim // self.head_dim
@@ -122,15 +121,50 @@ class FastWeightMemory(nn.Module):
             return y.reshape(b, l * self.num_heads, self.head_dim)
         return self._rows(proj(x))
 
-    def read(self, x: torch.Tensor, w02: torch.Tensor, w1: torch.Tensor, router: torch.Tensor):
+    @staticmethod
+    def shared_expert_ffn(rows: torch.Tensor, se) -> torch.Tensor:
+        """The always-on expert of a layer: an un-routed SwiGLU on every row (uttt_moe_block.py:350-360).
+        rows [B, T, D]; se = (sw0 [B, 1, I, D], sw1 [B, 1, D, I], sw2 [B, 1, I, D])."""
+        sw0, sw1, sw2 = (t.squeeze(1) for t in se)
+        hidden = F.silu(torch.bmm(rows, sw0.transpose(1, 2))) * torch.bmm(rows, sw2.transpose(1, 2))
+        return torch.bmm(hidden, sw1.transpose(1, 2))
+
+    @staticmethod
+    def shared_expert_grad(k: torch.Tensor, v: torch.Tensor, lr: torch.Tensor, se):
+        """Raw update of the always-on expert: the gradient of 1/2 |f(k) - v|^2 per matrix, each scaled by its
+        learning rate averaged over the rows of a sequence (uttt_moe_block.py:425-462).  k, v [B, T, D]; lr [B, T, 3]
+        (lr0, lr1, lr2) -> (dsw0, dsw1, dsw2) shaped like the weights."""
+        sw0, sw1, sw2 = (t.squeeze(1) for t in se)
+        gate = torch.bmm(k, sw0.transpose(1, 2))
+        up = torch.bmm(k, sw2.transpose(1, 2))
+        act = F.silu(gate)
+        hidden = act * up
+        err = torch.bmm(hidden, sw1.transpose(1, 2)) - v
+        d1 = torch.bmm(err.transpose(1, 2), hidden)
+        dh = torch.bmm(err, sw1)
+        sig = torch.sigmoid(gate)
+        dgate = dh * up * (sig * (1.0 + gate * (1.0 - sig)))
+        d0 = torch.bmm(dgate.transpose(1, 2), k)
+        d2 = torch.bmm((dh * act).transpose(1, 2), k)
+        mean = lr.mean(dim=1)                                           # [B, 3]
+        scale = [mean[:, i].view(-1, 1, 1).to(d0.dtype) for i in range(3)]
+        return (d0 * scale[0]).unsqueeze(1), (d1 * scale[1]).unsqueeze(1), (d2 * scale[2]).unsqueeze(1)
+
+    def read(self, x: torch.Tensor, w02: torch.Tensor, w1: torch.Tensor, router: torch.Tensor, se=None):
         b, l, _ = x.shape
         rows = self._proj_rows(self.input_proj, x)
         routing = fw.route_rows(rows, router, None, self.route_cfg)
         y = fw.pool_read(rows, w02, w1, routing)
+        if se is not None:
+            y = y + self.shared_expert_ffn(rows, se).to(y.dtype)
         y = ops.rms_norm(y, None, 1e-5).reshape(b, l, self.dim)
         return self.output_proj(y.to(x.dtype)), routing.prob_sum, routing.counts
 
-    def raw_grad(self, pre_k, pre_v, w02, w1, router, acc=None, keep_mask: Optional[torch.Tensor] = None):
+    def raw_grad(self, pre_k, pre_v, w02, w1, router, acc=None, keep_mask: Optional[torch.Tensor] = None, se=None):
+        """Routed raw gradient (added to ``acc`` when given) with its balance sums; with ``se`` (the layer's always-on
+        expert) the tuple ends with that expert's three raw gradients in fp32."""
+        if se is not None and keep_mask is not None:
+            raise ValueError("per-token update masking is unsupported when use_shared_expert=True")
         b, l, _ = pre_k.shape
         k_rows = self._proj_rows(self.k_input_proj, pre_k)
         v_rows = self.to_v(pre_v).reshape(b, l * self.num_heads, self.head_dim)
@@ -140,6 +174,9 @@ class FastWeightMemory(nn.Module):
         lr_rows = lr.reshape(b, l * self.num_heads, 3)
         routing = fw.route_rows(v_rows if self.router_from_v else k_rows, router, None, self.route_cfg)
         g02, g1 = fw.pool_raw_grad(k_rows, v_rows, lr_rows, w02, w1, routing, acc=acc)
+        if se is not None:
+            d0, d1, d2 = self.shared_expert_grad(k_rows, v_rows.to(k_rows.dtype), lr_rows, se)
+            return g02, g1, routing.prob_sum, routing.counts, d0.float(), d1.float(), d2.float()
         return g02, g1, routing.prob_sum, routing.counts
 
 
@@ -154,10 +191,10 @@ class MemoryBlock(nn.Module):
         self.ln_mlp = nn.RMSNorm(dim, eps=1e-5)
         self.mlp = MLP(dim, inter_multi)
 
-    def forward(self, x, w02, w1, router):
+    def forward(self, x, w02, w1, router, *se):
         x = x + self.self_attention(ops.rms_norm(x, self.ln_attn.weight, 1e-5))
         mem_in = ops.rms_norm(x, self.ln_memory.weight, 1e-5)
-        y, probs, counts = self.memory.read(mem_in, w02, w1, router)
+        y, probs, counts = self.memory.read(mem_in, w02, w1, router, se if se else None)
         x = x + y
         x = x + self.mlp(ops.rms_norm(x, self.ln_mlp.weight, 1e-5))
         return x, mem_in, probs, counts
@@ -224,6 +261,22 @@ class MemoryModel(nn.Module):
                 [nn.Parameter(torch.randn(1, num_experts, head_dim) / math.sqrt(head_dim)) for _ in range(layers)])
         else:
             self.shared_router_proj_weights = nn.Parameter(torch.randn(1, num_experts, head_dim) / math.sqrt(head_dim))
+        self.use_shared_expert = bool(use_shared_expert)
+        if self.use_shared_expert:
+            # one always-on expert per layer beside the routed pool (uttt_moe_block.py:922-960)
+            if not (shared_expert_per_layer or pool_mode == "per_block"):
+                raise NotImplementedError("use_shared_expert needs shared_expert_per_layer=True (or pool_mode="
+                                          "'per_block'): one always-on expert shared by all layers is not built")
+            if int(apply_ckpt_group) > 1:
+                raise NotImplementedError("apply_ckpt_group > 1 with use_shared_expert is not implemented "
+                                          "(the reference rejects it too)")
+
+            def se(n_out, n_in, fan):
+                return nn.ParameterList([nn.Parameter(torch.randn(1, 1, n_out, n_in) / math.sqrt(fan))
+                                         for _ in range(layers)])
+            self.shared_expert_w0_list = se(inter, head_dim, head_dim)
+            self.shared_expert_w1_list = se(head_dim, inter, inter)
+            self.shared_expert_w2_list = se(inter, head_dim, head_dim)
         self.blocks = nn.ModuleList([
             MemoryBlock(dim=dim, num_experts=num_experts, fw_head_dim=fw_head_dim, fw_inter_multi=fw_inter_multi,
                         use_shared_expert=use_shared_expert, **kwargs) for _ in range(layers)])
@@ -264,6 +317,17 @@ class MemoryModel(nn.Module):
         return [_unit_rows_state(self.block_w0_list[i], self.block_w1_list[i], self.block_w2_list[i], batch, dtype)
                 for i in range(len(self.blocks))]
 
+    def init_shared_experts(self, batch: int, dtype):
+        """Per layer (fast, masters) of the always-on expert, or None."""
+        if not self.use_shared_expert:
+            return None
+        out = []
+        for i in range(len(self.blocks)):
+            masters = tuple(p[i].float().repeat(batch, 1, 1, 1) for p in
+                            (self.shared_expert_w0_list, self.shared_expert_w1_list, self.shared_expert_w2_list))
+            out.append((_unit_rows(masters, dtype), masters))
+        return out
+
     def forward(self, x: torch.Tensor, info: Dict[str, Any]):
         """x: [b, tokens, dim]; info['ttt_config']: list of TTTConfig(start, end, fast_weight, update, apply)."""
         bsz = x.shape[0]
@@ -271,6 +335,7 @@ class MemoryModel(nn.Module):
         dt = x.dtype
         shared = self.pool_mode == "shared"
         states = self.init_states(bsz, dt)
+        se_states = self.init_shared_experts(bsz, dt)
         e = self.num_experts
         ap = torch.zeros(n, bsz, e, device=x.device)
         ac = torch.zeros_like(ap)
@@ -289,16 +354,20 @@ class MemoryModel(nn.Module):
             for g0 in range(0, n, k_grp):
                 idx = list(range(g0, g0 + k_grp))
 
-                def _group(x_in, *ws, _idx=idx):
+                per = 6 if se_states is not None else 3          # tensors per block: pool, router (+ always-on expert)
+
+                def _group(x_in, *ws, _idx=idx, _per=per):
                     res = []
                     for j, bi in enumerate(_idx):
-                        x_in, m_in, p_, c_ = self.blocks[bi](x_in, ws[3 * j], ws[3 * j + 1], ws[3 * j + 2])
+                        x_in, m_in, p_, c_ = self.blocks[bi](x_in, *ws[_per * j:_per * (j + 1)])
                         res += [x_in, m_in, p_, c_]
                     return tuple(res)
                 ws = []
                 for bi in idx:
                     st = states[0] if shared else states[bi]
                     ws += [st.w02, st.w1, self._router(bi)]
+                    if se_states is not None:
+                        ws += list(se_states[bi][0])
                 res = self._ckpt(_group, xi, *ws)
                 for j in range(k_grp):
                     xi, mem_in, p, c = res[4 * j:4 * j + 4]
@@ -315,7 +384,7 @@ class MemoryModel(nn.Module):
                     keep = self._update_mask_callback(source_view, start, end, x)
                 pre_vs = [outs[self.v_layer_idxs[i]] if self.v_layer_idxs is not None else mem_ins[i]
                           for i in range(n)]
-                states, p_u, c_u = self._write(states, mem_ins, pre_vs, keep, dt)
+                states, p_u, c_u = self._write(states, mem_ins, pre_vs, keep, dt, se_states)
                 up = up + p_u
                 uc = uc + c_u
                 source_view += 1
@@ -329,12 +398,17 @@ class MemoryModel(nn.Module):
                      "apply_max_violation_rate": (freq.max(1).values * e - 1).mean().detach()}
         return out, lb, [stats]
 
-    def _write(self, states, mem_ins, pre_vs, keep, dt):
+    def _write(self, states, mem_ins, pre_vs, keep, dt, se_states=None):
+        """Updates the pool state(s); with always-on experts, ``se_states`` is updated in place (one entry per
+        layer: each layer's expert takes its own raw gradient, whatever the write mode of the pool)."""
         n = len(self.blocks)
         shared = self.pool_mode == "shared"
 
         def norm_v(t):
             return ops.rms_norm(t, None, 1e-5)
+
+        if se_states is not None:
+            return self._write_with_shared_experts(states, mem_ins, pre_vs, keep, dt, se_states, norm_v)
 
         if shared and self.aggregate_write:
             st = states[0]
@@ -387,6 +461,50 @@ class MemoryModel(nn.Module):
             ps.append(out[4])
             cs.append(out[5])
         return new_states, torch.stack(ps), torch.stack(cs)
+
+
+def _unit_rows(masters, dtype):
+    return tuple(F.normalize(m, dim=3, eps=1e-5).to(dtype) for m in masters)
+
+
+def apply_shared_expert_update(raw, masters, use_muon: bool, dtype):
+    """masters += (Newton-Schulz of) raw, then unit rows (uttt_moe_block.py:690-714).  -> (fast, masters)"""
+    if use_muon:
+        raw = tuple(ops.newton_schulz(g.flatten(0, 1), ref.NS_FIXED_COEFFS).reshape(g.shape) for g in raw)
+    new = tuple(m + g.float() for m, g in zip(masters, raw))
+    return _unit_rows(new, dtype), new
+
+
+def _write_with_shared_experts(self, states, mem_ins, pre_vs, keep, dt, se_states, norm_v):
+    """The write of :class:`MemoryModel` when every layer has an always-on expert: one recompute region per layer
+    returns the routed raw gradient and the expert's; the pool is updated once from the aggregate
+    (``aggregate_write``) or layer by layer, every expert from its own gradient (uttt_moe_block.py:1128-1183, 1340-1420)."""
+    n = len(self.blocks)
+    shared = self.pool_mode == "shared"
+    use_muon = self.blocks[0].memory.use_muon
+    ps, cs = [], []
+    new_states = list(states)
+    a02 = a1 = None
+    for i, block in enumerate(self.blocks):
+        st = new_states[0 if shared else i]
+
+        def _raw(k_in, v_in, w02, w1, s0, s1, s2, _b=block, _i=i):
+            return _b.memory.raw_grad(k_in, norm_v(v_in), w02, w1, self._router(_i), keep_mask=keep, se=(s0, s1, s2))
+        g02, g1, p, c, d0, d1, d2 = self._ckpt(_raw, mem_ins[i], pre_vs[i], st.w02, st.w1, *se_states[i][0])
+        ps.append(p)
+        cs.append(c)
+        se_states[i] = apply_shared_expert_update((d0, d1, d2), se_states[i][1], use_muon, dt)
+        if shared and self.aggregate_write:
+            a02, a1 = (g02, g1) if a02 is None else (a02 + g02, a1 + g1)
+        else:
+            new_states[0 if shared else i] = apply_unit_update(g02, g1, st, block.memory.use_muon, dt)
+    if shared and self.aggregate_write:
+        with self._master_offload():
+            new_states = [apply_unit_update(a02, a1, states[0], use_muon, dt)]
+    return new_states, torch.stack(ps), torch.stack(cs)
+
+
+MemoryModel._write_with_shared_experts = _write_with_shared_experts
 
 
 class PartitionedMemoryModel(nn.Module):
