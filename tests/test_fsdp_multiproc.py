@@ -97,6 +97,41 @@ def test_hybrid_sharding_matches_full_sharding(tmp_path):
             torch.testing.assert_close(runs[2][0]["model"][k], v, atol=2e-5, rtol=2e-4, msg=k)
 
 
+def _sharded_param_worker(rank: int, world: int, port: int, shard: bool, out_path: str):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from uttt_b200.train.engine import EngineConfig, TrainEngine
+    eng = TrainEngine(_cfg(), EngineConfig(micro_batch_size=2, lr=1e-2, warmup_steps=0, total_steps=10, seed=0,
+                                           weight_decay=0.1, eps=1e-3, shard_parameters=shard), torch.device("cpu"))
+    released = []
+    for _ in range(2):
+        eng.train_step(_batch(rank))
+        released.append(all(u.compute.untyped_storage().size() == 0 for u in eng.trainer.units))
+    eval_loss = float(eng.eval_loss(_batch(0)))                 # gathers through the forward pre-hook
+    sd = {k: v.detach().float().cpu() for k, v in eng.model.state_dict().items()}
+    torch.save({"model": sd, "released": released, "eval": eval_loss}, out_path + f".{rank}")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_parameter_shards_between_steps_train_like_full_buffers(tmp_path):
+    """``shard_parameters`` (``training.fsdp_reshard_after_forward = "always"``): after a step each rank holds only its
+    shard of the parameters (the full buffers have no storage), the next forward / state_dict gathers them, and
+    training is bit-identical to keeping the full buffers."""
+    runs = {}
+    for shard in (False, True):
+        out = str(tmp_path / f"s{int(shard)}.pt")
+        mp.spawn(_sharded_param_worker, args=(2, _free_port(), shard, out), nprocs=2, join=True)
+        runs[shard] = [torch.load(out + f".{r}", weights_only=False) for r in range(2)]
+    assert runs[True][0]["released"] == [True, True] and runs[False][0]["released"] == [False, False]
+    for r in range(2):
+        assert runs[True][r]["eval"] == runs[False][r]["eval"]
+        for k, v in runs[False][r]["model"].items():
+            torch.testing.assert_close(runs[True][r]["model"][k], v, atol=0, rtol=0, msg=k)
+
+
 def _single_process_reference(device: str, dtype_note: str):
     sys.path.insert(0, ROOT)
     from uttt_b200.train.engine import EngineConfig, TrainEngine

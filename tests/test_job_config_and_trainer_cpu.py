@@ -98,13 +98,14 @@ def test_every_flag_has_a_reader_or_is_rejected(tmp_path):
     base = ["--job.config_file", job, "--model.config", model]
     for bad in (["--training.compile"], ["--optimizer.name", "Lion"], ["--optimizer.early_step_in_backward"],
                 ["--training.enable_cpu_offload"],
-                ["--training.fsdp_reshard_after_forward", "always"], ["--fault_tolerance.enable"],
+                ["--fault_tolerance.enable"],
                 ["--training.mixed_precision_param", "float16"], ["--model.converters", "float8"],
                 ["--experimental.enable_compiled_autograd"]):
         with pytest.raises(NotImplementedError):
             JobConfig().parse_args(base + bad)
     for bad in (["--checkpoint.async_mode", "sometimes"], ["--activation_checkpoint.mode", "maybe"],
-                ["--activation_offload.mode", "disk"], ["--training.data_parallel_replicate_degree", "0"]):
+                ["--activation_offload.mode", "disk"], ["--training.data_parallel_replicate_degree", "0"],
+                ["--training.fsdp_reshard_after_forward", "sometimes"]):
         with pytest.raises(ValueError):
             JobConfig().parse_args(base + bad)
     # hybrid sharding is accepted when it divides the job size (a single process accepts any positive degree here;

@@ -71,7 +71,8 @@ FLAG_READERS: Dict[str, str] = {
                  "early_step_in_backward: validate",
     "lr_scheduler": "train/lr.py::WarmupDecayLR",
     "training": "lm_trainer.main + train/data.py::build_dataloader; data_parallel_replicate_degree: train/engine.py "
-                "(hybrid sharding); other parallel degrees, reshard policy, offload, "
+                "(hybrid sharding), fsdp_reshard_after_forward: train/engine.py (parameter shards between steps); "
+                "other parallel degrees, offload, "
                 "compile, mixed precision: validate; gc_freq, deterministic, seed: lm_trainer.main; cuda_graph: "
                 "train/engine.py (forward + backward replayed as one CUDA graph)",
     "metrics": "lm_trainer.Metrics",
@@ -164,9 +165,10 @@ class JobConfig:
                 t.data_parallel_shard_degree * rep != world:
             raise ValueError("training.data_parallel_shard_degree x training.data_parallel_replicate_degree must equal "
                              "the job size (or leave the shard degree at -1)")
-        if str(t.fsdp_reshard_after_forward) not in ("default", "never"):
-            raise NotImplementedError("training.fsdp_reshard_after_forward='always': parameters stay gathered between "
-                                      "steps (the reference's setting for these models is 'never')")
+        # "always": ranks keep only their parameter shards between steps (gathered once per step: every layer is used
+        # by every chunk of the sequence, so re-sharding inside the forward would gather each layer once per chunk)
+        if str(t.fsdp_reshard_after_forward) not in ("default", "never", "always"):
+            raise ValueError("training.fsdp_reshard_after_forward must be 'default', 'never' or 'always'")
         if t.enable_cpu_offload:
             raise NotImplementedError("training.enable_cpu_offload: parameters and optimizer state live in HBM")
         if t.compile or e.enable_compiled_autograd:

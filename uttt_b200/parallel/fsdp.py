@@ -120,10 +120,13 @@ class ShardedTrainer:
     def __init__(self, model: nn.Module, unit_modules: Optional[Sequence[Tuple[str, nn.Module]]] = None,
                  opt: Optional[AdamWConfig] = None, compute_dtype: Optional[torch.dtype] = None,
                  no_decay: Callable[[str, nn.Parameter], bool] = default_no_decay, process_group=None,
-                 use_symmetric_memory: Optional[bool] = None, replicate_group=None):
+                 use_symmetric_memory: Optional[bool] = None, replicate_group=None, shard_parameters: bool = False):
         """``process_group``: the ranks that shard the optimizer state (default: all).  ``replicate_group``: the ranks
         that hold the same shard in other shard groups (hybrid sharding: gradients are reduce-scattered inside a shard
-        group and all-reduced across the replicas of each shard; ``training.data_parallel_replicate_degree``)."""
+        group and all-reduced across the replicas of each shard; ``training.data_parallel_replicate_degree``).
+        ``shard_parameters``: between steps a rank keeps only its shard of the low-precision parameters; the full
+        buffers are gathered before the model runs and dropped after backward (``release_params``).  This mode uses
+        library collectives (the peer-memory optimizer kernels write every rank's full buffer, which it does not have)."""
         self.model = model
         self.opt = opt or AdamWConfig()
         self.group = process_group
@@ -140,6 +143,10 @@ class ShardedTrainer:
         self.skipped_steps = 0
         self.micro_batches = 0
         self.symm = None
+        self.shard_parameters = bool(shard_parameters) and self.world > 1
+        self.params_released = False
+        if self.shard_parameters:
+            use_symmetric_memory = False
         if use_symmetric_memory is None:
             use_symmetric_memory = first.is_cuda and self.world > 1
         # --- partition parameters into units: one per listed module, the remainder is the root unit
@@ -181,6 +188,13 @@ class ShardedTrainer:
             if buf.is_floating_point() and buf.dtype != torch.float32 and "loss_free" in buf_name:
                 buf.data = buf.data.float()
         self._norm_buf = torch.zeros(2, dtype=torch.float32, device=self.device)
+        if self.shard_parameters:
+            for u in self.units:
+                lo, hi = u.shard_range
+                u.compute_shard = u.compute[lo:hi].clone()
+            # whoever runs the model or asks for its state finds the parameters gathered
+            model.register_forward_pre_hook(lambda *_: self.gather_params())
+            model.register_state_dict_pre_hook(lambda *_: self.gather_params())
         if self.symm is not None:
             self.symm.finalize()
         if self.device.type == "cuda":
@@ -188,6 +202,33 @@ class ShardedTrainer:
             # gradients into them inside the GEMM
             from ..ops import set_fused_weight_grad
             set_fused_weight_grad(True)
+
+    # ------------------------------------------------------------------ parameter sharding
+    def release_params(self) -> None:
+        """Drop the full low-precision parameter buffers (each rank keeps its shard).  Call after backward."""
+        if not self.shard_parameters or self.params_released:
+            return
+        for u in self.units:
+            lo, hi = u.shard_range
+            u.compute_shard.copy_(u.compute[lo:hi])
+            u.compute.untyped_storage().resize_(0)
+        self.params_released = True
+
+    def gather_params(self) -> None:
+        """Bring the full parameter buffers back from the ranks' shards (no-op while they are present)."""
+        if not self.shard_parameters or not self.params_released:
+            return
+        for u in self.units:
+            u.compute.untyped_storage().resize_(u.numel * u.compute.element_size())
+            dist.all_gather_into_tensor(u.compute, u.compute_shard, group=self.group)
+        self.params_released = False
+
+    def _param_shard(self, u: "FlatUnit") -> torch.Tensor:
+        """Where the optimizer writes this rank's new low-precision parameters."""
+        if self.shard_parameters and self.params_released:
+            return u.compute_shard
+        lo, hi = u.shard_range
+        return u.compute[lo:hi]
 
     # ------------------------------------------------------------------ bookkeeping
     def num_parameters(self) -> int:
@@ -300,13 +341,15 @@ class ShardedTrainer:
             if self.symm is not None:
                 self.symm.adamw_scatter(u, g, lr, opt, self.step_count, gscale, apply, decay_hi)
                 return
-            ext.adamw_flat(u.master, g, u.exp_avg, u.exp_avg_sq, u.compute[lo:hi], float(lr), opt.beta1, opt.beta2,
+            ext.adamw_flat(u.master, g, u.exp_avg, u.exp_avg_sq, self._param_shard(u), float(lr), opt.beta1, opt.beta2,
                            opt.eps, opt.weight_decay, int(self.step_count), gscale, apply, float(gmul),
                            int(decay_hi))
         else:
             self._adamw_torch(u, g, lr, gscale, apply, decay_hi)
-            if self.world > 1:
-                dist.all_gather_into_tensor(u.compute, u.compute[lo:hi].clone(), group=self.group)
+        # without the peer-memory kernels the other ranks' shards arrive through a library all-gather (unless the
+        # full buffers are released: then they are gathered before the next forward)
+        if self.world > 1 and not (self.shard_parameters and self.params_released):
+            dist.all_gather_into_tensor(u.compute, u.compute[lo:hi].clone(), group=self.group)
 
     def _adamw_torch(self, u, g, lr, gscale, apply, decay_hi):
         opt = self.opt
@@ -324,7 +367,7 @@ class ShardedTrainer:
         u.exp_avg.copy_(torch.where(keep, m_new, u.exp_avg))
         u.exp_avg_sq.copy_(torch.where(keep, v_new, u.exp_avg_sq))
         u.master.copy_(torch.where(keep, p_new, u.master))
-        u.compute[lo:hi].copy_(u.master)
+        self._param_shard(u).copy_(u.master)
 
     # ------------------------------------------------------------------ state dict (full, rank-agnostic)
     def _gather_shards(self, shard: torch.Tensor, u: FlatUnit) -> torch.Tensor:

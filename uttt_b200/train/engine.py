@@ -40,6 +40,7 @@ class EngineConfig:
     keep_activation_layers: tuple = ()     # layer indices that skip recomputation (needs spare device memory)
     activation_offload: bool = False       # saved tensors of the forward go to pinned host memory until backward
     data_parallel_replicate_degree: int = 1   # hybrid sharding: optimizer state sharded over world / R ranks, R replicas
+    shard_parameters: bool = False         # ranks keep only their parameter shards between steps (library collectives)
     expert_capacity_factor: float = 2.0    # expert-parallel staging rows / balanced load (0 = size for the worst case)
     cuda_graph: bool = False               # replay forward + backward of a micro-batch as one CUDA graph
     cuda_graph_warmup: int = 2             # eager steps before the capture (lazy initialisation happens in them)
@@ -140,7 +141,8 @@ class TrainEngine:
                           skip_nan_inf=self.cfg.skip_nan_inf)
         shard_group, replicate_group = self._hybrid_groups(int(self.cfg.data_parallel_replicate_degree or 1))
         self.trainer = ShardedTrainer(self.model, lm_fsdp_units(self.model), opt, process_group=shard_group,
-                                      replicate_group=replicate_group)
+                                      replicate_group=replicate_group,
+                                      shard_parameters=bool(self.cfg.shard_parameters))
         self.lr_sched = WarmupDecayLR(self.cfg.lr, self.cfg.total_steps, self.cfg.warmup_steps,
                                       self.cfg.decay_type, self.cfg.lr_min)
         self.copy_stream = torch.cuda.Stream(device) if device.type == "cuda" else None
@@ -195,6 +197,7 @@ class TrainEngine:
         mb = min(self.cfg.micro_batch_size, bsz)
         n_micro = (bsz + mb - 1) // mb
         total = torch.zeros((), device=self.device, dtype=torch.float32)
+        self.trainer.gather_params()                   # no-op unless the parameters are sharded between steps
         for i in range(n_micro):
             ids, labels = ids_all[i * mb:(i + 1) * mb], labels_all[i * mb:(i + 1) * mb]
             out = self._replay_forward_backward(ids, labels, n_micro) if self._graph_ready() else None
@@ -205,6 +208,8 @@ class TrainEngine:
             total += out.loss.detach().float() / n_micro
             if n_micro > 1:
                 self.trainer.accumulate_micro_batch()
+            if i == n_micro - 1:
+                self.trainer.release_params()          # parameter-sharded mode: the full buffers go before the optimizer runs
             self.last_stats = {"ce": out.ce_loss, "lb": out.lb_loss}
             moe = (getattr(out, "moe_stats", None) or {}).get("moe")
             if moe:
@@ -222,7 +227,9 @@ class TrainEngine:
     def _graph_ready(self) -> bool:
         return (self.cfg.cuda_graph and self.graph_error is None and self.device.type == "cuda"
                 and self.step >= self.cfg.cuda_graph_warmup and self.expert_parallel is None
-                and not self.cfg.activation_offload)
+                and not self.cfg.activation_offload
+                # a graph replays fixed addresses: not with parameter buffers that are dropped and brought back
+                and not self.trainer.shard_parameters)
 
     def _host_branches(self):
         """What the model's next training forward decides on the host (not on the device): a captured graph is

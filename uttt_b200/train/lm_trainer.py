@@ -182,7 +182,8 @@ def main(job: Optional[JobConfig] = None) -> TrainState:
                         keep_activation_layers=tuple(int(i) for i in job.activation_checkpoint.keep_layers),
                         activation_offload=job.activation_offload.mode == "offload",
                         cuda_graph=bool(job.training.cuda_graph),
-                        data_parallel_replicate_degree=int(job.training.data_parallel_replicate_degree))
+                        data_parallel_replicate_degree=int(job.training.data_parallel_replicate_degree),
+                        shard_parameters=str(job.training.fsdp_reshard_after_forward) == "always")
     engine = TrainEngine(model_cfg, ecfg)
     if rank == 0 and job.job.print_args:
         print("\n".join(param_check(engine.model)), flush=True)
