@@ -20,14 +20,14 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _cfg(ep: int):
+def _cfg(ep: int, **over):
     from uttt_b200.config import named_config
     return named_config("tiny-uttt-moe", hidden_size=256, num_heads=4, fw_num_heads=2, memory_num_experts=4,
                         memory_num_active_experts=2, chunk_size=64, window_size=64, memory_lb_loss_alpha=0.01,
-                        memory_expert_parallel=ep)
+                        memory_expert_parallel=ep, **over)
 
 
-def _worker(rank: int, world: int, port: int, backend: str, out_dir: str):
+def _worker(rank: int, world: int, port: int, backend: str, out_dir: str, over=None):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       LOCAL_RANK=str(rank))
@@ -45,7 +45,7 @@ def _worker(rank: int, world: int, port: int, backend: str, out_dir: str):
     batch = {"input_ids": ids, "labels": ids}
     result = {}
     for ep in (1, 2):
-        eng = TrainEngine(_cfg(ep), EngineConfig(micro_batch_size=2, lr=1e-2, warmup_steps=0, total_steps=10, seed=0,
+        eng = TrainEngine(_cfg(ep, **(over or {})), EngineConfig(micro_batch_size=2, lr=1e-2, warmup_steps=0, total_steps=10, seed=0,
                                                  weight_decay=0.0, eps=1e-3), device)
         # evaluation first, on the initial weights and without autograd: the write path then issues its three
         # dispatches (keys, values, learning rates) back to back before any of them is consumed
@@ -77,9 +77,27 @@ def test_two_gloo_ranks_expert_parallel_matches_data_parallel(tmp_path):
     _check(str(tmp_path), 3e-5, 3e-4, "a2a")
 
 
+def test_two_gloo_ranks_expert_parallel_with_chained_writes(tmp_path):
+    """Every writer layer applies its own update to the sharded bank in turn (no aggregate): the owners gather the
+    momentum gates of all sequences of the group, as for the aggregated write."""
+    mp.spawn(_worker, args=(2, _free_port(), "gloo", str(tmp_path), dict(memory_update_aggregate_write=False, memory_aggregate_momentum_mode="none")),
+             nprocs=2, join=True)
+    _check(str(tmp_path), 3e-5, 3e-4, "a2a")
+
+
+def test_two_gloo_ranks_expert_parallel_with_cross_layer_cut(tmp_path):
+    """Per-reader streams of the bank (each reader's gradient reaches only its own writer) over sharded experts."""
+    mp.spawn(_worker, args=(2, _free_port(), "gloo", str(tmp_path), dict(memory_update_backward_mode="cross_layer_cut")),
+             nprocs=2, join=True)
+    _check(str(tmp_path), 3e-5, 3e-4, "a2a")
+
+
 @pytest.mark.gpu
-def test_two_gpu_ranks_peer_dispatch_combine_matches_data_parallel(tmp_path):
+@pytest.mark.parametrize("over", [None, dict(memory_update_aggregate_write=False, memory_aggregate_momentum_mode="none"),
+                                  dict(memory_update_backward_mode="cross_layer_cut")],
+                         ids=["aggregated write", "chained writes", "cross_layer_cut"])
+def test_two_gpu_ranks_peer_dispatch_combine_matches_data_parallel(tmp_path, over):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    mp.spawn(_worker, args=(2, _free_port(), "nccl", str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, _free_port(), "nccl", str(tmp_path), over), nprocs=2, join=True)
     _check(str(tmp_path), 4e-2, 4e-2, "peer")

@@ -131,6 +131,9 @@ def cross_layer_cut_write(model, states: Sequence[fw.PoolState], feats, offset: 
     wout = model._ckpt(_writers, *wargs)
     raw = [(wout[5 * i], wout[5 * i + 1]) for i in range(n)]
     gates = [wout[5 * i + 2] for i in range(n)]
+    if getattr(model, "ep", None) is not None:
+        # expert parallelism: the owner of an expert updates every sequence of the group, so it needs their gates
+        gates = [model.ep.gather_sequences(g.reshape(-1)) for g in gates]
     probs = torch.stack([wout[5 * i + 3] for i in range(n)]).float()
     counts = torch.stack([wout[5 * i + 4] for i in range(n)]).float()
 

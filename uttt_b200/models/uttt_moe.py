@@ -400,10 +400,9 @@ class UTTTMoEModel(nn.Module):
         """Shard the experts of the pool over the ranks of ``ep`` (parallel/expert_parallel.py): this rank then
         keeps the state of every sequence of the group for its own experts only."""
         if ep is not None and ep.P > 1:
-            if self.per_layer_pool or not self.config.memory_update_aggregate_write:
-                raise NotImplementedError("expert parallelism covers the shared pool with aggregated writes")
-            if self.config.memory_update_backward_mode == "cross_layer_cut":
-                raise NotImplementedError("expert parallelism with cross_layer_cut is not implemented")
+            if self.per_layer_pool:
+                raise NotImplementedError("expert parallelism covers the shared pool (aggregated or chained writes)")
+
         else:
             ep = None
         self.ep = ep
@@ -539,7 +538,11 @@ class UTTTMoEModel(nn.Module):
                         g02, g1 = g02.detach(), g1.detach()
                     if m is not None and (cfg.memory_detach_m_coeff or mode == "stop_state"):
                         m = m.detach()
-                    mc = None if m is None else m.view(-1, 1, 1, 1)
+                    mc = None
+                    if m is not None:
+                        if self.ep is not None:                  # the owner updates every sequence of the group
+                            m = self.ep.gather_sequences(m.reshape(-1))
+                        mc = m.view(-1, 1, 1, 1)
                     new = fw.apply_pool_update(g02, g1, state, mc, 1.0, cfg.use_moun, compute_dtype=dt)
                     return (*[t for t in new.tensors() if t is not None], p, c)
 
