@@ -100,11 +100,18 @@ def test_cross_layer_cut_forward_equals_full_and_cuts_routes():
         torch.testing.assert_close(cut(input_ids=ids, labels=ids).loss, lf.detach(), atol=1e-5, rtol=1e-5)
 
 
-def test_cached_generation_matches_one_shot_forward():
+@pytest.mark.parametrize("over", [
+    dict(),
+    # write sources other than the attention's own k / v of the same layer: the cache keeps what they read
+    dict(memory_v_gap=1),
+    dict(memory_kv_mode="to_kv", memory_kv_proj="ttt_kv_proj", memory_kv_feature="x_memory_in",
+         residual_style="sequential"),
+], ids=["default sources", "values from the next layer", "own projections of the memory input"])
+def test_cached_generation_matches_one_shot_forward(over):
     torch.manual_seed(0)
     cfg = config_from_dict(dict(BASE, model_type="uttt_moe", fw_inter_multi=2, memory_num_experts=4,
                                 memory_update_aggregate_write=True, memory_aggregate_momentum_mode="pool_mean",
-                                memory_update_backward_mode="full"))
+                                memory_update_backward_mode="full", **over))
     model = build_model(cfg).eval()
     ids = _ids(2, b=1, s=80)
     with torch.no_grad():

@@ -23,7 +23,7 @@ class GenerationCache:
     states: List[Any]
     hist: List[Any]                       # per layer (k, v) of the previous chunks (window history)
     chunk_kv: List[Any]                   # per layer (k, v) of the current chunk so far
-    feats: List[List[Any]]                # per layer list of (x_in, k_flat, v_flat) fragments
+    feats: List[List[Any]]                # per layer list of (x_attn_in, x_memory_in, xi_out, k_flat, v_flat) fragments
     chunk_start: int = 0
     chunk_fill: int = 0
     seen_tokens: int = 0
@@ -57,8 +57,15 @@ def forward_with_cache(model, inputs_embeds: torch.Tensor, past: Optional[Genera
     shared = not getattr(model, "per_layer_pool", False)
     while pos < total:
         if past.chunk_fill == chunk:
-            feats = [tuple(torch.cat([f[i] for f in frags], dim=1) for i in range(3)) for frags in past.feats]
             if cfg.use_memory_block:
+                keys = ("x_attn_in", "x_memory_in", "xi_out", "attn_k", "attn_v")
+                caches = [{k: torch.cat([f[i] for f in frags], dim=1) for i, k in enumerate(keys)}
+                          for frags in past.feats]
+                # the same composition of the write's inputs as in training (gapped layers, projections of a feature)
+                if hasattr(model, "compose_write_inputs"):
+                    feats = model.compose_write_inputs(caches)
+                else:
+                    feats = [(c["x_attn_in"], c["attn_k"], c["attn_v"]) for c in caches]
                 past.states, _, _ = model._chunk_write(past.states, feats, past.chunk_start)
             past.hist = [trim_history(hk, hv, ck, cv, keep) for (hk, hv), (ck, cv) in zip(past.hist, past.chunk_kv)]
             past.chunk_kv = [(None, None)] * n_layers
@@ -79,12 +86,8 @@ def forward_with_cache(model, inputs_embeds: torch.Tensor, past: Optional[Genera
             else:
                 out = layer(h, k_ctx, v_ctx, None, None, None, None, offset)
             h, x_in, k_flat, v_flat, k_rot, v_new = out[:6]
-            if cfg.use_memory_block and not model.default_write_source:
-                raise NotImplementedError("cached generation covers the default write source (the attention's own "
-                                          "k / v of the same layer); got other memory compose modes or gaps")
             past.chunk_kv[li] = (_cat(ck, k_rot), _cat(cv, v_new))
-            pre = out[8] if (len(out) > 8 and getattr(model, "write_feature", "x_attn_in") == "x_memory_in") else x_in
-            past.feats[li].append((pre, k_flat, v_flat))
+            past.feats[li].append((x_in, out[8] if len(out) > 8 else x_in, h, k_flat, v_flat))
         outputs.append(h)
         pos += take
         past.chunk_fill += take
