@@ -31,7 +31,8 @@ def _model_cfg():
 def toy(tmp_path):
     manifest = make_toy_dataset(str(tmp_path / "data"), num_scenes=4, num_frames=10, image_size=32, seed=3)
     views = str(tmp_path / "views.json")
-    views_main(["--manifest", manifest, "--output", views, "--num-views", "6", "--seed", "9595"])
+    views_main(["--dataset-manifest", manifest, "--dataset", "toy", "--output", views, "--num-views", "6",
+                "--seed", "9595"])
     cfg = tmp_path / "model.yaml"
     cfg.write_text(yaml.safe_dump(_model_cfg()))
     reg = tmp_path / "experiments.yaml"
@@ -49,9 +50,9 @@ def test_view_manifest_is_frozen_and_deterministic(toy):
     b = build_view_manifest(toy["manifest"], 6, 9595)
     c = build_view_manifest(toy["manifest"], 6, 1)
     assert a["scenes"] == b["scenes"] and a["scenes"] != c["scenes"]
-    assert all(len(set(s["frames"])) == 6 for s in a["scenes"])
+    assert all(len(set(s["frame_indices"])) == 6 for s in a["scenes"])
     doc = load_view_manifest(toy["views"])
-    doc["scenes"][0]["frames"][0] = (doc["scenes"][0]["frames"][0] + 1) % 10
+    doc["scenes"][0]["frame_indices"] = doc["scenes"][0]["frame_indices"][::-1]
     edited = toy["root"] / "edited.json"
     edited.write_text(json.dumps(doc))
     with pytest.raises(ValueError):

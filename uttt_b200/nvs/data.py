@@ -16,12 +16,15 @@ import json
 import math
 import os
 import random
+from concurrent.futures import ThreadPoolExecutor
 from typing import Dict, Iterator, List, Optional
 
 import numpy as np
 import torch
 import torch.nn.functional as F
 from torch.utils.data import Dataset, DistributedSampler
+
+from . import manifests
 
 
 def look_at_c2w(eye: torch.Tensor, target: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -89,17 +92,24 @@ class SyntheticScenes:
 
 
 def make_toy_dataset(out_dir: str, num_scenes: int = 4, num_frames: int = 16, image_size: int = 64,
-                     seed: int = 0) -> str:
-    """Procedural scenes (coloured discs on a gradient) seen from a circular orbit; writes PNG frames, one camera
-    JSON per scene and a manifest listing the JSON paths.  Returns the manifest path."""
+                     seed: int = 0, repeat: int = 1) -> str:
+    """Procedural scenes (coloured discs on a gradient) seen from a circular orbit, in the loader's on-disk layout:
+    ``scene_NNN/images/NNN.png``, one ``scene_NNN/opencv_cameras.json`` with per-frame ``fx fy cx cy w2c
+    file_path`` (image paths relative to the camera file), and ``manifest.txt`` listing the absolute camera paths
+    ``repeat`` times each (a manifest line is a sample, so a few scenes can fill a large global batch).
+    Returns the manifest path."""
     from PIL import Image
+    for name, value in (("num_scenes", num_scenes), ("num_frames", num_frames), ("image_size", image_size),
+                        ("repeat", repeat)):
+        if type(value) is not int or value < 1:
+            raise ValueError(f"{name} must be a positive integer")
+    out_dir = os.path.abspath(os.path.expanduser(out_dir))
     rng = np.random.default_rng(seed)
-    os.makedirs(out_dir, exist_ok=True)
     manifest = []
     f = 0.5 * image_size / math.tan(math.radians(50) / 2)
     for s in range(num_scenes):
-        scene_dir = os.path.join(out_dir, f"scene_{s:04d}")
-        os.makedirs(scene_dir, exist_ok=True)
+        scene_dir = os.path.join(out_dir, f"scene_{s:03d}")
+        os.makedirs(os.path.join(scene_dir, "images"), exist_ok=True)
         centres = rng.uniform(-0.5, 0.5, size=(5, 3))
         colours = rng.uniform(0.2, 1.0, size=(5, 3))
         frames = []
@@ -117,29 +127,37 @@ def make_toy_dataset(out_dir: str, num_scenes: int = 4, num_frames: int = 16, im
                 r = 0.18 * f / p[2]
                 yy, xx = np.mgrid[0:image_size, 0:image_size]
                 img[(xx - u) ** 2 + (yy - v) ** 2 < r * r] = col
-            path = os.path.join(scene_dir, f"{i:03d}.png")
-            Image.fromarray((img * 255).astype(np.uint8)).save(path)
-            frames.append({"image_path": path, "fxfycxcy": [f, f, image_size / 2, image_size / 2],
-                           "w2c": w2c.tolist()})
-        jpath = os.path.join(scene_dir, "cameras.json")
-        with open(jpath, "w") as fh:
-            json.dump({"scene_name": f"scene_{s:04d}", "frames": frames}, fh)
+            rel = f"images/{i:03d}.png"
+            Image.fromarray((img * 255).astype(np.uint8)).save(os.path.join(scene_dir, rel))
+            frames.append({"fx": f, "fy": f, "cx": image_size / 2, "cy": image_size / 2, "w2c": w2c.tolist(),
+                           "file_path": rel})
+        jpath = os.path.join(scene_dir, "opencv_cameras.json")
+        with open(jpath, "w", encoding="utf-8") as fh:
+            json.dump({"scene_name": f"scene_{s:03d}", "frames": frames}, fh)
         manifest.append(jpath)
     mpath = os.path.join(out_dir, "manifest.txt")
-    with open(mpath, "w") as fh:
-        fh.write("\n".join(manifest) + "\n")
+    with open(mpath, "w", encoding="utf-8") as fh:
+        fh.write("\n".join(manifest * repeat) + "\n")
     return mpath
 
 
 class NVSDataset(Dataset):
+    """One sample per manifest line: ``num_views`` frames of that scene drawn without replacement.
+
+    ``max_num_objects`` keeps the first n scenes and repeats them so that the epoch length stays (about) what it
+    was (uttt_nvs/data/loader.py:150-154).  A sample that cannot be read is replaced by another one; after
+    ``MAX_CONSECUTIVE_FAILURES`` failures in a row the error is raised with the last failing path."""
     MAX_CONSECUTIVE_FAILURES = 100
+    LOAD_THREADS = 8
 
     def __init__(self, manifest: str, num_views: int, image_size: int, max_num_objects: Optional[int] = None,
                  seed: int = 0):
-        with open(manifest) as fh:
-            self.scenes = [ln.strip() for ln in fh if ln.strip()]
-        if max_num_objects:
-            self.scenes = self.scenes[:max_num_objects]
+        self.scenes = manifests.read_manifest(manifest)
+        manifests.drop_clients()            # a client made here must not travel to worker processes
+        if max_num_objects and int(max_num_objects) > 0 and self.scenes:
+            total = len(self.scenes)
+            kept = self.scenes[:int(max_num_objects)]
+            self.scenes = kept * max(total // len(kept), 1)
         if not self.scenes:
             raise ValueError(f"empty manifest {manifest}")
         self.num_views, self.image_size, self.seed = num_views, image_size, seed
@@ -147,14 +165,16 @@ class NVSDataset(Dataset):
     def __len__(self):
         return len(self.scenes)
 
-    def _load_frame(self, frame):
+    def _load_frame(self, frame, base_dir: str = ""):
         from PIL import Image
-        img = Image.open(frame["image_path"])
+        with manifests.open_file(manifests.frame_image(frame, base_dir)) as fh:
+            img = Image.open(fh)
+            img.load()
         if img.mode == "RGBA":
             bg = Image.new("RGBA", img.size, (255, 255, 255, 255))
             img = Image.alpha_composite(bg, img)
         img = img.convert("RGB")
-        fx, fy, cx, cy = frame["fxfycxcy"]
+        fx, fy, cx, cy = manifests.frame_intrinsics(frame)
         w, h = img.size
         s = self.image_size
         scale = max(s / w, s / h)                       # resize so the image covers the square, then centre-crop
@@ -167,45 +187,43 @@ class NVSDataset(Dataset):
         c2w = torch.linalg.inv(torch.tensor(frame["w2c"], dtype=torch.float32))
         return arr, torch.tensor([fx, fy, cx, cy], dtype=torch.float32), c2w
 
+    def load_views(self, camera_path: str, picks):
+        """The given frames of one scene, read by a small thread pool: (images, intrinsics, poses)."""
+        frames = manifests.read_frames(camera_path)
+        base = manifests.parent_of(camera_path)
+        if len(picks) > 1 and self.LOAD_THREADS > 1:
+            with ThreadPoolExecutor(max_workers=min(self.LOAD_THREADS, len(picks))) as pool:
+                out = list(pool.map(lambda i: self._load_frame(frames[i], base), picks))
+        else:
+            out = [self._load_frame(frames[i], base) for i in picks]
+        imgs, intr, poses = zip(*out)
+        return torch.stack(imgs), torch.stack(intr), torch.stack(poses)
+
     def __getitem__(self, idx: int):
         failures = 0
         rng = random.Random((self.seed, idx).__hash__())
         while True:
             try:
-                with open(self.scenes[idx]) as fh:
-                    scene = json.load(fh)
-                frames = scene["frames"]
-                if len(frames) < self.num_views:
+                n_frames = len(manifests.read_frames(self.scenes[idx]))
+                if n_frames < self.num_views:
                     raise ValueError("scene has too few frames")
-                picks = rng.sample(range(len(frames)), self.num_views)
-                imgs, intr, poses = zip(*[self._load_frame(frames[i]) for i in picks])
-                index = torch.tensor([[idx, i] for i in picks])
-                return {"image": torch.stack(imgs), "fxfycxcy": torch.stack(intr), "c2w": torch.stack(poses),
-                        "index": index}
-            except Exception:
+                picks = rng.sample(range(n_frames), self.num_views)
+                imgs, intr, poses = self.load_views(self.scenes[idx], picks)
+                index = torch.tensor([[i, idx] for i in picks])           # (frame, scene): the scene id is last
+                return {"image": imgs, "fxfycxcy": intr, "c2w": poses, "index": index}
+            except Exception as exc:
                 failures += 1
                 if failures >= self.MAX_CONSECUTIVE_FAILURES:
-                    raise
+                    raise RuntimeError(
+                        f"Failed to load {failures} samples in a row; the last failing path was "
+                        f"'{self.scenes[idx]}'. Check that the manifest is readable and that every path in it "
+                        f"is reachable.") from exc
                 idx = rng.randrange(len(self.scenes))
 
 
-def check_manifest(manifest: str) -> List[str]:
-    """Static validation of a manifest: every JSON parses, has frames with intrinsics, 4x4 poses and images."""
-    problems = []
-    with open(manifest) as fh:
-        scenes = [ln.strip() for ln in fh if ln.strip()]
-    for path in scenes:
-        try:
-            with open(path) as fh:
-                scene = json.load(fh)
-            for fr in scene["frames"]:
-                if len(fr["fxfycxcy"]) != 4 or np.asarray(fr["w2c"]).shape != (4, 4):
-                    problems.append(f"{path}: malformed camera")
-                if not os.path.exists(fr["image_path"]):
-                    problems.append(f"{path}: missing {fr['image_path']}")
-        except Exception as exc:
-            problems.append(f"{path}: {exc}")
-    return problems
+def check_manifest(manifest: str, min_views: int = 1, check_images: bool = False) -> List[str]:
+    """Error lines of :func:`uttt_b200.nvs.manifests.validate_manifest` (empty when the manifest is sound)."""
+    return manifests.validate_manifest(manifest, min_views, check_images)["errors"]
 
 
 class ResumableDistributedSampler(DistributedSampler):
@@ -232,48 +250,40 @@ class ResumableDistributedSampler(DistributedSampler):
 
 
 def main(argv=None):
-    """``python -m uttt_b200.nvs.data make-toy --output DIR [--num-scenes 4] [--num-frames 16] [--image-size 64]``
-    ``python -m uttt_b200.nvs.data check-manifest MANIFEST``
-    ``python -m uttt_b200.nvs.data build-manifest --root DIR --output manifest.txt [--pattern "**/cameras.json"]``"""
+    """``python -m uttt_b200.nvs.data make-toy --output DIR [--num-scenes 4] [--num-frames 16] [--image-size 64]
+    [--repeat 1]``; ``check-manifest MANIFEST [--min-views N] [--check-images]``; ``build-manifest --root DIR
+    --output manifest.txt [--pattern "opencv_cameras*.json"] [--limit N]`` (the last two are also
+    ``python -m uttt_b200.nvs.manifests check | build``)."""
     import argparse
-    import glob
     import sys
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
     a = sub.add_parser("make-toy")
-    a.add_argument("--output", required=True)
-    a.add_argument("--num-scenes", type=int, default=4)
-    a.add_argument("--num-frames", type=int, default=16)
-    a.add_argument("--image-size", type=int, default=64)
+    a.add_argument("--output", "--out", dest="output", required=True)
+    a.add_argument("--num-scenes", "--scenes", dest="num_scenes", type=int, default=4)
+    a.add_argument("--num-frames", "--views", dest="num_frames", type=int, default=16)
+    a.add_argument("--image-size", "--size", dest="image_size", type=int, default=64)
+    a.add_argument("--repeat", type=int, default=1)
     a.add_argument("--seed", type=int, default=0)
     b = sub.add_parser("check-manifest")
     b.add_argument("manifest")
+    b.add_argument("--min-views", type=int, default=1)
+    b.add_argument("--check-images", action="store_true")
     c = sub.add_parser("build-manifest")
     c.add_argument("--root", required=True)
-    c.add_argument("--output", required=True)
-    c.add_argument("--pattern", default="**/*.json")
+    c.add_argument("--output", "--out", dest="output", required=True)
+    c.add_argument("--pattern", default=manifests.CAMERA_PATTERN)
+    c.add_argument("--limit", type=int, default=0)
     args = ap.parse_args(argv)
     if args.cmd == "make-toy":
-        print(make_toy_dataset(args.output, args.num_scenes, args.num_frames, args.image_size, args.seed))
+        print(make_toy_dataset(args.output, args.num_scenes, args.num_frames, args.image_size, args.seed,
+                               args.repeat))
     elif args.cmd == "check-manifest":
-        problems = check_manifest(args.manifest)
-        for p in problems:
-            print("ERROR", p)
-        print(f"{len(problems)} problem(s)")
-        sys.exit(1 if problems else 0)
+        sys.exit(manifests.main(["check", args.manifest, "--min-views", str(args.min_views)]
+                                + (["--check-images"] if args.check_images else [])))
     else:
-        paths = sorted(os.path.abspath(p) for p in glob.glob(os.path.join(args.root, args.pattern), recursive=True))
-        keep = []
-        for p in paths:
-            try:
-                with open(p) as fh:
-                    if "frames" in json.load(fh):
-                        keep.append(p)
-            except Exception:
-                continue
-        with open(args.output, "w") as fh:
-            fh.write("\n".join(keep) + "\n")
-        print(f"{len(keep)} scenes -> {args.output}")
+        sys.exit(manifests.main(["build", "--root", args.root, "--out", args.output, "--pattern", args.pattern,
+                                 "--limit", str(args.limit)]))
 
 
 if __name__ == "__main__":

@@ -81,7 +81,8 @@ def evaluate_experiment(exp, out_dir: Path, device: str = "cpu", amp_dtype: str 
                         progress_every: int = 10, lpips=None):
     out_dir.mkdir(parents=True, exist_ok=True)
     model, ckpt_info = load_model(exp, device, allow_missing_checkpoint)
-    ds = FixedViewDataset(str(exp.view_manifest), exp.image_size, shard_index, num_shards, max_scenes)
+    ds = FixedViewDataset(str(exp.view_manifest), exp.image_size, shard_index, num_shards, max_scenes,
+                          dataset_manifest=str(exp.manifest), expected_num_views=exp.num_views)
     loader = torch.utils.data.DataLoader(ds, batch_size=batch_size, num_workers=num_workers, shuffle=False)
     rows = []
     t0 = time.time()

@@ -48,7 +48,7 @@ def render(registry, dataset: str, experiments, out_dir: Path, scene_ids=None, s
         problems = preflight(e, require_checkpoint=not allow_missing_checkpoint)
         if problems:
             raise SystemExit("preflight failed:\n  " + "\n  ".join(problems))
-    ds = FixedViewDataset(str(exps[0].view_manifest), exps[0].image_size)
+    ds = FixedViewDataset(str(exps[0].view_manifest), exps[0].image_size, dataset_manifest=str(exps[0].manifest))
     order = list(range(len(ds)))
     if scene_ids:
         wanted = set(scene_ids)
