@@ -15,4 +15,4 @@ set -euo pipefail
 cd "${SLURM_SUBMIT_DIR:-$(pwd)}"
 export NPROC_PER_NODE=8
 export JOB_UUID="uttt-lm-${SLURM_JOB_ID:-$$}"
-bash launch/train_lm.sh configs/lm/exp/train_760M_32k.toml configs/lm/760M/uttt_moe.json "run-${SLURM_JOB_ID:-local}" "$@"
+bash launch/train_lm.sh configs/lm/exp/train_760M_32k.toml configs/lm/main/760M/uttt_moe.json "run-${SLURM_JOB_ID:-local}" "$@"

@@ -16,6 +16,6 @@ def test_catalog_is_fresh():
 
 def test_architecture_json_schema_accepts_upstream_style_keys():
     """Unknown keys are preserved and model_type aliases resolve (schema compatibility)."""
-    path = glob.glob(os.path.join(ROOT, "lm", "760M", "uttt_moe.json"))[0]
+    path = glob.glob(os.path.join(ROOT, "lm", "main", "760M", "uttt_moe.json"))[0]
     cfg = load_config(path, attention_bias=False, transformers_version="5.5.0")
     assert cfg.extra["transformers_version"] == "5.5.0" and cfg.memory_num_experts == 96

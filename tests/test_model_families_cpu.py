@@ -145,3 +145,31 @@ def test_loss_free_bias_moves_against_overloaded_experts():
     assert abs(float(bias.mean())) < 1e-6
     over = counts > counts.mean()
     assert bool((bias[over] < 0).all()) and bool((bias[counts < counts.mean()] > 0).all())
+
+
+def test_lact_accepts_and_writes_the_reference_key_layout():
+    """The LaCT baseline's parameters under the reference's names: everything of a layer below ``attn`` with a fused
+    ``qkv`` projection (lact/lact_model/layer_lact_swiglu.py).  Loading that layout and writing it back is lossless."""
+    cfg = load_config("configs/lm/main/124M/lact.json")
+    d = cfg.to_dict()
+    d.update(hidden_size=64, num_hidden_layers=2, num_heads=4, num_attn_heads=4, vocab_size=256, num_lact_heads=2,
+             w0_w2_low_rank=4, window_size=32, lact_chunk_size=32, chunk_size=32, max_position_embeddings=128)
+    torch.manual_seed(0)
+    a, b = build_model(config_from_dict(d)), build_model(config_from_dict(d))
+    theirs = a.reference_state_dict()
+    for key, shape in (("model.layers.0.attn.qkv.weight", (192, 64)), ("model.layers.1.attn.o_proj.weight", (64, 64)),
+                       ("model.layers.0.attn.lr_proj.weight", None), ("model.layers.0.attn.w0.w_left", (2, 32, 4)),
+                       ("model.layers.0.attn.w1", (2, 32, 32)), ("model.layers.0.attn.ttt_norm.weight", None),
+                       ("model.layers.0.attn.momentum_proj.0.bias", None), ("model.layers.0.attn.qk_scale", None),
+                       ("model.layers.0.mlp.gate_proj.weight", None), ("lm_head.weight", (256, 64))):
+        assert key in theirs, key
+        assert shape is None or tuple(theirs[key].shape) == shape, key
+    assert not any(".memory." in k or ".to_lr." in k or "q_proj" in k for k in theirs)
+    assert len(theirs) == len(a.state_dict()) - 4                      # q, k, v fused per layer
+    res = b.load_state_dict(theirs, strict=True)
+    assert not res.missing_keys and not res.unexpected_keys
+    for (k, va), vb in zip(a.state_dict().items(), b.state_dict().values()):
+        assert torch.equal(va, vb), k
+    ids = torch.randint(0, 256, (1, 64))
+    with torch.no_grad():
+        torch.testing.assert_close(a(input_ids=ids, labels=ids).loss, b(input_ids=ids, labels=ids).loss)

@@ -19,6 +19,8 @@ def _cfg(block="uttt_nvs.models.uttt_moe_block.MemoryModel", **params):
              num_active_experts=2, l2_norm=True, pool_mode="shared", router_share_mode="share_all",
              aggregate_write=True, load_balancing_loss_alpha=1e-5)
     p.update(params)
+    if "only" in params:                     # a family with its own parameter set (strict signatures)
+        p = dict(params["only"])
     return {"exp_name": "t", "model": {"image_size": 32, "patch_size": 8, "dim": 64, "layers": 2,
                                        "block_config": {"type": block, "params": p}},
             "training": {"batch_size_per_gpu": 2, "total_batch_size": 2, "num_views": 4, "lr": 1e-3, "warmup": 0,
@@ -37,9 +39,23 @@ def _batch(b=2, v=4):
     ("uttt_nvs.models.uttt_dense_block.MemoryModel", {}),
     ("uttt_nvs.models.uttt_dense_partitioned.MemoryModel", dict(num_shared_pools=2, fw_inter_multi=2)),
     ("uttt_nvs.models.uttt_moe_partitioned.MemoryModel", dict(num_shared_pools=2)),
-    ("uttt_nvs.models.transformer_block.TransformerModel", {}),
-    ("uttt_nvs.models.deltanet_block.DeltaNetModel", {}),
-    ("uttt_nvs.models.gated_deltanet_block.GatedDeltaNetModel", {}),
+    ("uttt_nvs.models.ttt_dense_block.MemoryModel", dict(only=dict(attn_head_dim=32, fw_head_dim=16, inter_multi=2,
+                                                                 fw_inter_multi=2, l2_norm=False, use_muon=True))),
+    ("uttt_nvs.models.uttt_dense_block.MemoryModel", dict(aggregate_write=False, v_gap=1)),
+    ("uttt_nvs.models.transformer_block.MemoryModel", dict(only=dict(attn_head_dim=32, inter_multi=2,
+                                                                   transformer_version="v0", vi_rms_norm=True))),
+    ("uttt_nvs.models.transformer_block.MemoryModel", dict(only=dict(attn_head_dim=32, transformer_version="v3", v_gap=1,
+                                                                   to_kv_mode="per_layer", pre_vi_source="xi_out"))),
+    ("uttt_nvs.models.transformer_block.MemoryModel", dict(only=dict(attn_head_dim=32, transformer_version="v1", bias=True,
+                                                                   use_separate_last_to_kv=True))),
+    ("uttt_nvs.models.deltanet_block.MemoryModel", dict(only=dict(attn_head_dim=32, fw_num_heads=2, inter_multi=2,
+                                                                repeat_function="repeat", use_short_conv=False,
+                                                                use_output_gate=False))),
+    ("uttt_nvs.models.deltanet_block.MemoryModel", dict(only=dict(attn_head_dim=32, fw_num_heads=2, expand_v=2.0,
+                                                                qk_activation="elu", qk_norm="sum", use_muon=True,
+                                                                allow_neg_eigval=True, repeat_function="linear"))),
+    ("uttt_nvs.models.gated_deltanet_block.MemoryModel", dict(only=dict(attn_head_dim=32, fw_num_heads=2, expand_v=2.0,
+                                                                      repeat_function="repeat", noise_repeat=2))),
 ])
 def test_block_families_train(block, params):
     torch.manual_seed(0)
@@ -48,7 +64,8 @@ def test_block_families_train(block, params):
     loss = out["loss_metrics"]["loss"]
     assert torch.isfinite(loss) and out["rendering"].shape == (2, 3, 3, 32, 32)
     loss.backward()
-    assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in model.parameters())
+    for name, p in model.named_parameters():
+        assert p.grad is not None and torch.isfinite(p.grad).all(), name
 
 
 def test_state_dict_layout_and_aggregate_differs_from_chained():
@@ -206,7 +223,7 @@ def test_grad_accumulation_keeps_every_micro_batch(tmp_path):
     big = _batch(b=4)
 
     def run(accum):
-        cfg = _cfg(block="uttt_nvs.models.transformer_block.TransformerModel")
+        cfg = _cfg(block="uttt_nvs.models.transformer_block.MemoryModel", only=dict(attn_head_dim=32, inter_multi=2, transformer_version="v0"))
         tr = cfg["training"]
         tr.update(out_dir=str(tmp_path / f"a{accum}"), grad_accum_steps=accum, batch_size_per_gpu=4 // accum,
                   total_batch_size=4, grad_clip_norm=0.0, weight_decay=0.0)
@@ -223,7 +240,7 @@ def test_grad_accumulation_keeps_every_micro_batch(tmp_path):
         torch.testing.assert_close(two[n], one[n], rtol=1e-4, atol=2e-5, msg=n)
     # dropping the last micro-batch changes the update by far more than the tolerance above
     ref0 = {n: p.detach().clone() for n, p in NVSTrainer(
-        {**_cfg(block="uttt_nvs.models.transformer_block.TransformerModel"),
+        {**_cfg(block="uttt_nvs.models.transformer_block.MemoryModel", only=dict(attn_head_dim=32, inter_multi=2, transformer_version="v0")),
          "training": {**_cfg()["training"], "out_dir": str(tmp_path / "z")}},
         device=torch.device("cpu")).model.named_parameters()}
     assert any((one[n] - ref0[n]).abs().max() > 1e-4 for n in one)
@@ -331,3 +348,37 @@ def test_view_synthesis_with_per_layer_shared_expert(aggregate):
         params2 = dict(params, shared_expert_per_layer=False)
         LVSMModel({"model": {**cfg["model"], "block_config": {"type": cfg["model"]["block_config"]["type"],
                                                               "params": params2}}, "training": cfg["training"]})
+
+
+def test_partitioned_pool_layout_and_rebinding():
+    """Flat parameter layout of the depth-partitioned routed stack, both router modes, and the group runners following
+    the registered parameters through a conversion that replaces them."""
+    base = dict(num_shared_pools=2, num_experts=4, aggregate_write=True)
+    per_pool = LVSMModel(_cfg("uttt_nvs.models.uttt_moe_partitioned.MemoryModel", router_share_mode="share_pool", **base))
+    keys = set(per_pool.state_dict())
+    for k in ("transformer_blocks.pool_w0_list.0", "transformer_blocks.pool_w2_list.1",
+              "transformer_blocks.pool_router_proj_weights_list.1", "transformer_blocks.blocks.1.memory.to_lr.weight"):
+        assert k in keys, k
+    assert not any(".parts." in k for k in keys) and "transformer_blocks.shared_router_proj_weights" not in keys
+    assert per_pool.state_dict()["transformer_blocks.pool_w0_list.0"].shape[1] == 2          # experts per pool
+    one_router = LVSMModel(_cfg("uttt_nvs.models.uttt_moe_partitioned.MemoryModel", **base))    # share_all
+    stack = one_router.transformer_blocks
+    assert "transformer_blocks.shared_router_proj_weights" in one_router.state_dict()
+    assert all(p.shared_router_proj_weights is stack.shared_router_proj_weights for p in stack.parts)
+    assert len(list(one_router.parameters())) == len(one_router.state_dict())                  # nothing counted twice
+    b = _batch()
+    with torch.no_grad():
+        before = one_router(b)["rendering"]
+    copy_ = LVSMModel(_cfg("uttt_nvs.models.uttt_moe_partitioned.MemoryModel", **base))
+    with torch.device("meta"):
+        hollow = LVSMModel(_cfg("uttt_nvs.models.uttt_moe_partitioned.MemoryModel", **base))
+    hollow = hollow.to_empty(device="cpu")                     # new parameter objects everywhere
+    hollow.load_state_dict(one_router.state_dict())
+    copy_.load_state_dict(one_router.state_dict())
+    with torch.no_grad():
+        torch.testing.assert_close(copy_(b)["rendering"], before)
+        torch.testing.assert_close(hollow(b)["rendering"], before)
+    with pytest.raises(NotImplementedError):
+        LVSMModel(_cfg("uttt_nvs.models.uttt_moe_partitioned.MemoryModel", v_gap=1, **base))
+    with pytest.raises(ValueError):
+        LVSMModel(_cfg("uttt_nvs.models.uttt_moe_partitioned.MemoryModel", num_shared_pools=2, num_experts=3))

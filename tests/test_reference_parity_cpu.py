@@ -177,7 +177,7 @@ def test_layer_local_pools_match_reference(reference, package, config, ver, over
     if not os.path.isdir(os.path.join(rs.REF_ROOT, "flame", "custom_models", package)):
         pytest.skip("reference package not present")
     um = _reference_package(package)
-    with open(os.path.join(HERE, "..", "configs", "lm", "124M", config)) as fh:
+    with open(os.path.join(HERE, "..", "configs", "lm", "main", "124M", config)) as fh:
         d = json.load(fh)
     d.update(hidden_size=64, num_hidden_layers=2, num_heads=4, vocab_size=1024, chunk_size=64, window_size=128,
              fw_num_heads=1, memory_num_experts=4, max_position_embeddings=256, fuse_norm=False,
@@ -208,6 +208,8 @@ def test_layer_local_pools_match_reference(reference, package, config, ver, over
     ("uttt_dense", "uttt_dense_r4.json", "RecurrentLactRefUtttDenseV3", dict(use_moun=False, fw_num_heads=2)),
     ("ttt_dense", "ttt_dense.json", "RecurrentLactRef", dict(use_moun=False)),
     ("ttt_dense", "ttt_dense.json", "RecurrentLactRef", dict()),
+    # layer-private w0 / w2 as identity / 2 + a rank-4 product (the shipped TTT-Dense files use rank 32)
+    ("ttt_dense", "ttt_dense.json", "RecurrentLactRef", dict(use_moun=False, w0_w2_low_rank=4)),
 ])
 def test_dense_families_match_reference(reference, package, config, classes, over):
     """uTTT-Dense (one shared dense state, aggregate write, Newton-Schulz and renormalisation per D x D slice) and
@@ -215,7 +217,7 @@ def test_dense_families_match_reference(reference, package, config, classes, ove
     if not os.path.isdir(os.path.join(rs.REF_ROOT, "flame", "custom_models", package)):
         pytest.skip("reference package not present")
     um = _reference_package(package)
-    with open(os.path.join(HERE, "..", "configs", "lm", "124M", config)) as fh:
+    with open(os.path.join(HERE, "..", "configs", "lm", "main", "124M", config)) as fh:
         d = json.load(fh)
     d.update(hidden_size=64, num_hidden_layers=2, num_heads=4, vocab_size=1024, chunk_size=64, window_size=128,
              fw_num_heads=1, max_position_embeddings=256, fuse_norm=False, fuse_cross_entropy=False, w0_w2_low_rank=0)

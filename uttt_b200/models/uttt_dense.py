@@ -25,7 +25,7 @@ import torch.nn.functional as F
 from .. import ops
 from ..ops import reference as ref
 from . import fast_weights as fw
-from .common import (GatedMLP, RMSNorm, SlidingWindowAttention, TokenEmbedding, init_linear_weights, inv_softplus,
+from .common import (GatedMLP, LowRankFastWeight, RMSNorm, SlidingWindowAttention, TokenEmbedding, init_linear_weights, inv_softplus,
                      trim_history)
 from .uttt_moe import UTTTMoEForCausalLM
 
@@ -100,9 +100,21 @@ class DenseBlock(nn.Module):
         self.mlp = GatedMLP(d, config.mlp_intermediate_size)
         if private_weights:
             h, dd, ii = config.fw_heads, config.fw_head_dim, config.fw_inter_dim
-            self.memory.w0 = nn.Parameter(torch.randn(h, ii, dd) / dd ** 0.5)
-            self.memory.w2 = nn.Parameter(torch.randn(h, ii, dd) / dd ** 0.5)
+            if config.w0_w2_low_rank > 0:
+                # identity / 2 plus a low-rank product (ttt_dense/modeling_recurrent_lact.py:138-186, 227-244)
+                self.memory.w0 = LowRankFastWeight(h, ii, dd, config.w0_w2_low_rank, config.fw_init_gain, True)
+                self.memory.w2 = LowRankFastWeight(h, ii, dd, config.w0_w2_low_rank, config.fw_init_gain, True)
+            else:
+                self.memory.w0 = nn.Parameter(torch.randn(h, ii, dd) / dd ** 0.5)
+                self.memory.w2 = nn.Parameter(torch.randn(h, ii, dd) / dd ** 0.5)
             self.memory.w1 = nn.Parameter(torch.randn(h, dd, ii) / ii ** 0.5)
+
+    def private_weights(self):
+        """(w0, w1, w2) of a block that owns its fast weights."""
+        m = self.memory
+        if isinstance(m.w0, LowRankFastWeight):
+            return m.w0(), m.w1, m.w2()
+        return m.w0, m.w1, m.w2
 
     def forward(self, h, k_hist, v_hist, w02, w1, offset: int):
         cfg = self.config
@@ -178,8 +190,12 @@ class DenseFWModel(nn.Module):
         for layer in self.layers:
             layer.memory.reset_parameters()
             if not self.shared:
-                nn.init.normal_(layer.memory.w0, std=dd ** -0.5)
-                nn.init.normal_(layer.memory.w2, std=dd ** -0.5)
+                if isinstance(layer.memory.w0, LowRankFastWeight):
+                    layer.memory.w0.reset_parameters()
+                    layer.memory.w2.reset_parameters()
+                else:
+                    nn.init.normal_(layer.memory.w0, std=dd ** -0.5)
+                    nn.init.normal_(layer.memory.w2, std=dd ** -0.5)
                 nn.init.normal_(layer.memory.w1, std=ii ** -0.5)
         if self.shared:
             if cfg.w0_w2_low_rank > 0:
@@ -212,7 +228,7 @@ class DenseFWModel(nn.Module):
         if self.shared:
             w0, w1, w2 = self._shared_weights()
             return [fw.init_pool_state(w0, w1, w2, bsz, cfg.use_momentum, dt)]
-        return [fw.init_pool_state(l.memory.w0, l.memory.w1, l.memory.w2, bsz, cfg.use_momentum, dt)
+        return [fw.init_pool_state(*l.private_weights(), bsz, cfg.use_momentum, dt)
                 for l in self.layers]
 
     def _ckpt(self, fn, *args):
@@ -346,4 +362,56 @@ class TTTDenseForCausalLM(UTTTMoEForCausalLM):
 
 
 class LaCTForCausalLM(TTTDenseForCausalLM):
-    """Published LaCT baseline: layer-private large-chunk TTT with SwiGLU fast weights."""
+    """Published LaCT baseline: layer-private large-chunk TTT with SwiGLU fast weights.
+
+    The parameters map one to one onto the reference's ``LaCTForCausalLM`` (lact/lact_model/layer_lact_swiglu.py), which
+    keeps them all under ``layers.N.attn`` with a fused ``qkv`` projection.  :meth:`load_state_dict` accepts that
+    layout (detected by its ``attn.qkv.weight`` keys) and :meth:`reference_state_dict` writes it."""
+
+    _TO_MEMORY = ("momentum_proj.", "qk_scale", "qk_offset", "ttt_norm.", "ttt_scale_proj.", "w0", "w1", "w2")
+
+    @classmethod
+    def from_reference_keys(cls, sd):
+        out = {}
+        for k, v in sd.items():
+            if ".attn." not in k:
+                out[k] = v
+                continue
+            head, tail = k.split(".attn.", 1)
+            if tail == "qkv.weight":
+                q, kk, vv = v.chunk(3, dim=0)
+                out[f"{head}.attn.q_proj.weight"], out[f"{head}.attn.k_proj.weight"] = q, kk
+                out[f"{head}.attn.v_proj.weight"] = vv
+            elif tail.startswith("o_proj."):
+                out[f"{head}.memory_output_proj.{tail[7:]}"] = v
+            elif tail.startswith("lr_proj."):
+                out[f"{head}.to_lr.{tail[8:]}"] = v
+            elif tail.startswith(cls._TO_MEMORY):
+                out[f"{head}.memory.{tail}"] = v
+            else:
+                out[k] = v
+        return out
+
+    def load_state_dict(self, state_dict, strict: bool = True, assign: bool = False):
+        if any(k.endswith(".attn.qkv.weight") for k in state_dict):
+            state_dict = self.from_reference_keys(state_dict)
+        return super().load_state_dict(state_dict, strict=strict, assign=assign)
+
+    def reference_state_dict(self):
+        sd, out = self.state_dict(), {}
+        for k, v in sd.items():
+            if k.endswith(".attn.q_proj.weight"):
+                head = k[:-len(".attn.q_proj.weight")]
+                out[f"{head}.attn.qkv.weight"] = torch.cat([v, sd[f"{head}.attn.k_proj.weight"],
+                                                            sd[f"{head}.attn.v_proj.weight"]], dim=0)
+            elif k.endswith((".attn.k_proj.weight", ".attn.v_proj.weight")):
+                continue
+            elif ".memory_output_proj." in k:
+                out[k.replace(".memory_output_proj.", ".attn.o_proj.")] = v
+            elif ".to_lr." in k:
+                out[k.replace(".to_lr.", ".attn.lr_proj.")] = v
+            elif ".memory." in k:
+                out[k.replace(".memory.", ".attn.")] = v
+            else:
+                out[k] = v
+        return out

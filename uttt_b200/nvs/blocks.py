@@ -508,168 +508,79 @@ MemoryModel._write_with_shared_experts = _write_with_shared_experts
 
 
 class PartitionedMemoryModel(nn.Module):
-    """Depth-contiguous groups of blocks, each group with its own shared pool; ``num_experts`` is the total
-    expert budget split evenly over the groups (uttt_nvs/models/uttt_moe_partitioned.py:10-462)."""
+    """Depth-contiguous groups of blocks, each group with its own shared pool; ``num_experts`` is the total expert
+    budget, split evenly over the groups (uttt_nvs/models/uttt_moe_partitioned.py:10-462).
+
+    Parameters and blocks are registered in the reference's flat layout: ``pool_w{0,1,2}_list[p]``, ``blocks[i]``,
+    ``pool_router_proj_weights_list[p]`` (``router_share_mode="share_pool"``, one router per group) or
+    ``shared_router_proj_weights`` (``"share_all"``, one router for every group), ``shared_expert_w{0,1,2}_list[i]``.
+    Each group is run by a :class:`MemoryModel` over its slice of the blocks and its pool; these runners hold the same
+    parameter and module objects and are not registered as children.  A group's writes depend on its own blocks only,
+    so running group after group over the whole schedule gives what the layer-interleaved walk gives; this needs
+    ``v_gap`` to stay inside a group, so ``v_gap`` with more than one group is refused."""
 
     def __init__(self, layers: int, dim: int, num_partitions: Optional[int] = None, num_experts: int = 4,
-                 num_shared_pools: Optional[int] = None, **kwargs):
+                 num_shared_pools: Optional[int] = None, pool_mode: str = "shared",
+                 router_share_mode: str = "share_pool", v_gap: Optional[int] = None, **kwargs):
         super().__init__()
         # `num_shared_pools` is the reference's name of the option
-        num_partitions = int(num_shared_pools if num_shared_pools is not None else (num_partitions or 2))
-        if layers % num_partitions or num_experts % num_partitions:
+        pools = int(num_shared_pools if num_shared_pools is not None else (num_partitions or 1))
+        if pools <= 0:
+            raise ValueError("num_shared_pools must be positive.")
+        if pool_mode != "shared":
+            raise ValueError("the partitioned stack only supports pool_mode='shared'.")
+        if layers % pools or num_experts % pools:
             raise ValueError("layers and num_experts must be divisible by the number of pools")
-        kwargs.setdefault("pool_mode", "shared")
-        self.parts = nn.ModuleList([MemoryModel(layers // num_partitions, dim, num_experts=num_experts // num_partitions,
-                                                **kwargs) for _ in range(num_partitions)])
+        if router_share_mode not in ("share_pool", "share_all"):
+            raise ValueError("router_share_mode must be either 'share_pool' or 'share_all'.")
+        if v_gap is not None and pools > 1:
+            raise NotImplementedError("v_gap across partitions is not built: the groups run one after the other")
+        self.num_shared_pools, self.router_share_mode = pools, router_share_mode
+        self.pool_size, self.experts_per_pool = layers // pools, num_experts // pools
+        runners = [MemoryModel(self.pool_size, dim, num_experts=self.experts_per_pool, pool_mode="shared",
+                               router_share_mode="share_all", v_gap=v_gap, **kwargs) for _ in range(pools)]
+        self.pool_w0_list = nn.ParameterList([r.pool_w0 for r in runners])
+        self.pool_w1_list = nn.ParameterList([r.pool_w1 for r in runners])
+        self.pool_w2_list = nn.ParameterList([r.pool_w2 for r in runners])
+        if router_share_mode == "share_pool":
+            self.pool_router_proj_weights_list = nn.ParameterList([r.shared_router_proj_weights for r in runners])
+        else:
+            self.shared_router_proj_weights = runners[0].shared_router_proj_weights
+            for r in runners[1:]:
+                r.shared_router_proj_weights = self.shared_router_proj_weights
+        if runners[0].use_shared_expert:
+            for name in ("shared_expert_w0_list", "shared_expert_w1_list", "shared_expert_w2_list"):
+                setattr(self, name, nn.ParameterList([p for r in runners for p in getattr(r, name)]))
+        self.blocks = nn.ModuleList([b for r in runners for b in r.blocks])
+        object.__setattr__(self, "parts", runners)                   # same objects as above; not registered twice
+        self.activation_checkpoint = True
+
+    def set_update_mask_callback(self, fn) -> None:
+        for part in self.parts:
+            part.set_update_mask_callback(fn)
+
+    def _bind(self) -> None:
+        """Points the runners at the registered parameters again (a conversion such as ``to_empty`` replaces the
+        parameter objects of this module, which the unregistered runners would not see)."""
+        n = self.pool_size
+        for p, r in enumerate(self.parts):
+            if r.pool_w0 is self.pool_w0_list[p]:
+                continue
+            r.pool_w0, r.pool_w1, r.pool_w2 = self.pool_w0_list[p], self.pool_w1_list[p], self.pool_w2_list[p]
+            r.shared_router_proj_weights = self.pool_router_proj_weights_list[p] \
+                if self.router_share_mode == "share_pool" else self.shared_router_proj_weights
+            if r.use_shared_expert:
+                for name in ("shared_expert_w0_list", "shared_expert_w1_list", "shared_expert_w2_list"):
+                    setattr(r, name, nn.ParameterList(list(getattr(self, name))[p * n:(p + 1) * n]))
 
     def forward(self, x, info):
+        self._bind()
         lb_total = x.new_zeros((), dtype=torch.float32)
         infos: List[Any] = []
         # every group sees the whole schedule: group g's output sequence feeds group g+1
         for part in self.parts:
+            part.activation_checkpoint = self.activation_checkpoint
             x, lb, inf = part(x, info)
             lb_total = lb_total + lb
             infos = inf
         return x, lb_total, infos
-
-
-class DenseMemoryModel(MemoryModel):
-    """uTTT-Dense / TTT-Dense for view synthesis: a pool with a single expert (no routing)
-    (uttt_nvs/models/uttt_dense_block.py:39-521, ttt_dense_block.py:96-473)."""
-
-    def __init__(self, layers: int, dim: int, shared: bool = True, **kwargs):
-        for key in ("num_experts", "num_active_experts", "router_share_mode", "load_balancing_loss_alpha"):
-            kwargs.pop(key, None)
-        mode = kwargs.pop("pool_mode", "shared" if shared else "per_block")
-        kwargs["aggregate_write"] = bool(kwargs.get("aggregate_write", True)) and mode == "shared"
-        super().__init__(layers, dim, num_experts=1, num_active_experts=1, pool_mode=mode,
-                         router_share_mode="share_all", **kwargs)
-        # a single expert needs no router: drop the parameter, keep a constant stand-in for the call signature
-        head_dim = self.shared_router_proj_weights.shape[-1]
-        del self.shared_router_proj_weights
-        self.register_buffer("_no_router", torch.zeros(1, head_dim), persistent=False)
-
-    def _router(self, i: int) -> torch.Tensor:
-        return self._no_router
-
-
-class DensePartitionedMemoryModel(nn.Module):
-    """Depth-contiguous groups of blocks, each group with its own shared dense state of width ``fw_inter_multi``
-    (uttt_nvs/models/uttt_dense_partitioned.py:22-212): between one state for the whole stack (uTTT-Dense) and one
-    per block (TTT-Dense)."""
-
-    def __init__(self, layers: int, dim: int, num_shared_pools: int = 2, **kwargs):
-        super().__init__()
-        pools = int(num_shared_pools)
-        if pools < 1 or layers % pools:
-            raise ValueError("layers must be divisible by num_shared_pools")
-        kwargs.pop("pool_mode", None)
-        self.parts = nn.ModuleList([DenseMemoryModel(layers // pools, dim, shared=True, **kwargs) for _ in range(pools)])
-
-    def forward(self, x, info):
-        lb_total = x.new_zeros((), dtype=torch.float32)
-        infos: List[Any] = []
-        for part in self.parts:              # group g's output sequence feeds group g + 1 over the whole schedule
-            x, lb, infos = part(x, info)
-            lb_total = lb_total + lb
-        return x, lb_total, infos
-
-
-class TransformerBlocks(nn.Module):
-    """Reference transformer decoder: causal over view-chunks with a growing key/value cache
-    (uttt_nvs/models/transformer_block.py)."""
-
-    def __init__(self, layers: int, dim: int, attn_head_dim: int = 64, inter_multi: float = 4, **_unused):
-        super().__init__()
-        self.head_dim = attn_head_dim
-        self.blocks = nn.ModuleList()
-        for _ in range(layers):
-            blk = nn.Module()
-            blk.ln_attn = nn.RMSNorm(dim, eps=1e-5)
-            blk.to_qkv = nn.Linear(dim, 3 * dim, bias=False)
-            blk.to_out = nn.Linear(dim, dim, bias=False)
-            blk.ln_mlp = nn.RMSNorm(dim, eps=1e-5)
-            blk.mlp = MLP(dim, inter_multi)
-            self.blocks.append(blk)
-
-    def forward(self, x, info):
-        b, _, dim = x.shape
-        h = dim // self.head_dim
-        caches = [[None, None] for _ in self.blocks]
-        outputs = []
-        for cfg in info["ttt_config"]:
-            xi = x[:, cfg.start:cfg.end]
-            l = xi.shape[1]
-            for blk, cache in zip(self.blocks, caches):
-                qkv = blk.to_qkv(ops.rms_norm(xi, blk.ln_attn.weight, 1e-5)).view(b, l, 3, h, self.head_dim)
-                q, k, v = qkv[:, :, 0].contiguous(), qkv[:, :, 1].contiguous(), qkv[:, :, 2].contiguous()
-                kk = k if cache[0] is None else torch.cat([cache[0], k], dim=1)
-                vv = v if cache[1] is None else torch.cat([cache[1], v], dim=1)
-                # a view attends to every posed (update) view before it and to itself, without a causal mask
-                o = ops.swa_attention(q, kk, vv, None, causal=False)
-                xi = xi + blk.to_out(o.reshape(b, l, dim))
-                xi = xi + blk.mlp(ops.rms_norm(xi, blk.ln_mlp.weight, 1e-5))
-                if cfg.update:
-                    cache[0], cache[1] = kk, vv
-            outputs.append(xi)
-        return torch.cat(outputs, dim=1), x.new_zeros((), dtype=torch.float32), [{}]
-
-
-class DeltaNetBlocks(nn.Module):
-    """Delta-rule (optionally gated) linear-state reference: the state ``S [h, dk, dv]`` is written by the posed
-    views and read by every view (uttt_nvs/models/deltanet_block.py, gated_deltanet_block.py)."""
-
-    def __init__(self, layers: int, dim: int, attn_head_dim: int = 64, inter_multi: float = 4, gated: bool = False,
-                 **_unused):
-        super().__init__()
-        self.head_dim, self.gated = attn_head_dim, gated
-        self.blocks = nn.ModuleList()
-        for _ in range(layers):
-            blk = nn.Module()
-            blk.ln_attn = nn.RMSNorm(dim, eps=1e-5)
-            blk.self_attention = SelfAttention(dim, attn_head_dim)
-            blk.ln_mem = nn.RMSNorm(dim, eps=1e-5)
-            blk.to_qkv = nn.Linear(dim, 3 * dim, bias=False)
-            blk.to_beta = nn.Linear(dim, dim // attn_head_dim, bias=False)
-            blk.to_gate = nn.Linear(dim, dim // attn_head_dim, bias=False) if gated else None
-            blk.to_out = nn.Linear(dim, dim, bias=False)
-            blk.ln_mlp = nn.RMSNorm(dim, eps=1e-5)
-            blk.mlp = MLP(dim, inter_multi)
-            self.blocks.append(blk)
-
-    def forward(self, x, info):
-        b, _, dim = x.shape
-        h = dim // self.head_dim
-        states = [x.new_zeros(b, h, self.head_dim, self.head_dim, dtype=torch.float32) for _ in self.blocks]
-        outputs = []
-        for cfg in info["ttt_config"]:
-            xi = x[:, cfg.start:cfg.end]
-            l = xi.shape[1]
-            for bi, blk in enumerate(self.blocks):
-                xi = xi + blk.self_attention(ops.rms_norm(xi, blk.ln_attn.weight, 1e-5))
-                m = ops.rms_norm(xi, blk.ln_mem.weight, 1e-5)
-                qkv = blk.to_qkv(m).view(b, l, 3, h, self.head_dim).float()
-                q = F.normalize(F.silu(qkv[:, :, 0]), dim=-1).transpose(1, 2)      # [b,h,l,d]
-                k = F.normalize(F.silu(qkv[:, :, 1]), dim=-1).transpose(1, 2)
-                v = qkv[:, :, 2].transpose(1, 2)
-                s = states[bi]
-                y = torch.einsum("bhld,bhde->bhle", q, s)
-                xi = xi + blk.to_out(y.transpose(1, 2).reshape(b, l, dim).to(xi.dtype))
-                if cfg.update:
-                    beta = torch.sigmoid(blk.to_beta(m)).float().transpose(1, 2).unsqueeze(-1)   # [b,h,l,1]
-                    if self.gated:
-                        decay = torch.sigmoid(blk.to_gate(m)).float().mean(dim=1).view(b, h, 1, 1)
-                        s = s * decay
-                    # chunk-level delta rule: S += K^T (beta * (V - K S)) / l
-                    err = v - torch.einsum("bhld,bhde->bhle", k, s)
-                    s = s + torch.einsum("bhld,bhle->bhde", k, beta * err) / l
-                    states[bi] = s
-                xi = xi + blk.mlp(ops.rms_norm(xi, blk.ln_mlp.weight, 1e-5))
-            outputs.append(xi)
-        return torch.cat(outputs, dim=1), x.new_zeros((), dtype=torch.float32), [{}]
-
-
-class GatedDeltaNetBlocks(DeltaNetBlocks):
-    def __init__(self, layers: int, dim: int, **kwargs):
-        kwargs["gated"] = True
-        super().__init__(layers, dim, **kwargs)

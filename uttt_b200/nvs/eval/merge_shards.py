@@ -1,70 +1,106 @@
-"""Merge the shards of one experiment into a single evaluation (uttt_nvs/eval/merge_sharded_evaluations.py).
+"""Merge the scene shards of one experiment into a single evaluation (uttt_nvs/eval/merge_sharded_evaluations.py).
 
     python -m uttt_b200.nvs.eval.merge_shards --registry R --experiment E --shards-root DIR --num-shards S \
         --output-root OUT [--overwrite]
 
-Every shard must be complete; scenes must not repeat across shards; the merged row count is checked against the
-registry's expected scene count when it is given.
+Shard ``i`` is expected in ``<shards-root>/shard_<i>/<dataset>/<id>/`` (what ``evaluate --shard-index i --num-shards S
+--output-root <shards-root>/shard_<i>`` writes).  A shard counts only with its ``completion.json``; its metadata must
+name the right shard index and count; all shards must agree on experiment, dataset, checkpoint / config / view
+manifest / evaluator digests and attention gap; no (scene, view) pair may repeat; the merged table must cover the
+registry's expected scenes and rows.  The summaries are recomputed from the merged rows (10 000 resamples) and a new
+``completion.json`` closes the merged folder.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import shutil
+import time
 from pathlib import Path
 
-from .evaluate import shard_dir, summarize
-from .registry import load_registry
+from . import stats
+from .registry import experiment_dir, resolve_experiment
+
+INVARIANT_KEYS = ("experiment_id", "dataset", "checkpoint_sha256", "config_sha256", "view_manifest_sha256",
+                  "evaluation_code_sha256", "v_gap")
 
 
-def merge(exp, shards_root: Path, num_shards: int, out_root: Path, bootstrap_samples: int = 10000,
-          overwrite: bool = False, allow_incomplete: bool = False):
-    rows, seen = [], set()
+def merge(exp, shards_root: Path, num_shards: int, out_root: Path, bootstrap_samples: int = 10_000,
+          overwrite: bool = False, wandb_mode: str = "disabled"):
+    if num_shards <= 0:
+        raise ValueError("--num-shards must be positive")
+    out_dir = experiment_dir(out_root, exp)
+    completion = out_dir / "completion.json"
+    if completion.exists() and not overwrite:
+        raise FileExistsError(f"{completion} already marks a complete merge")
+    records, metas = [], []
     for i in range(num_shards):
-        d = shard_dir(shards_root, exp.name, i, num_shards)
-        if not (d / "summary.json").exists():
-            raise FileNotFoundError(f"shard {i} of {num_shards} is not finished: {d}")
-        with open(d / "raw_metrics.jsonl") as fh:
-            shard_rows = [json.loads(ln) for ln in fh if ln.strip()]
-        shard_scenes = {r["scene_id"] for r in shard_rows}
-        if seen & shard_scenes:
-            raise ValueError(f"shard {i} repeats scenes of an earlier shard: {sorted(seen & shard_scenes)[:3]}")
-        seen |= shard_scenes
-        rows.extend(shard_rows)
-    if exp.expected_scenes and len(seen) != int(exp.expected_scenes) and not allow_incomplete:
-        raise ValueError(f"merged {len(seen)} scenes, the registry expects {exp.expected_scenes}")
-    out_dir = shard_dir(out_root, exp.name, 0, 1)
-    if (out_dir / "summary.json").exists() and not overwrite:
-        raise FileExistsError(f"{out_dir} already holds a merged evaluation")
+        d = experiment_dir(Path(shards_root) / f"shard_{i}", exp)
+        need = [d / "completion.json", d / "raw_metrics.csv", d / "run_metadata.json"]
+        if not all(p.is_file() for p in need):
+            raise FileNotFoundError(f"incomplete shard {i}: {d}")
+        meta = json.loads(need[2].read_text(encoding="utf-8"))
+        if meta.get("shard_index") != i:
+            raise ValueError(f"{d}: wrong shard_index metadata")
+        if meta.get("num_shards") != num_shards:
+            raise ValueError(f"{d}: wrong num_shards metadata")
+        metas.append(meta)
+        records.extend(stats.read_raw_csv(need[1]))
+    for meta in metas[1:]:
+        differ = [k for k in INVARIANT_KEYS if meta.get(k) != metas[0].get(k)]
+        if differ:
+            raise ValueError(f"shards disagree on metadata: {differ}")
+    keys = [(r["scene_id"], r["view_index"]) for r in records]
+    if len(keys) != len(set(keys)):
+        raise ValueError("duplicate scene/view records across shards")
+    scored = exp.scored_views
+    scenes = exp.expected_scenes if exp.expected_scenes is not None else len({k[0] for k in keys})
+    rows = exp.expected_rows if exp.expected_rows is not None else scenes * scored
+    stats.validate_complete(records, scenes, rows, scored)
+    if overwrite:
+        shutil.rmtree(out_dir, ignore_errors=True)
     out_dir.mkdir(parents=True, exist_ok=True)
-    rows.sort(key=lambda r: (r["scene_id"], r["view"]))
-    with open(out_dir / "raw_metrics.jsonl", "w") as fh:
-        for r in rows:
-            fh.write(json.dumps(r) + "\n")
-    per_scene, summary = summarize(rows, bootstrap_samples)
-    summary.update({"experiment": exp.name, "dataset": exp.dataset, "paper_model": exp.paper_model,
-                    "display_name": exp.display_name, "merged_from_shards": num_shards})
-    with open(out_dir / "scene_metrics.json", "w") as fh:
-        json.dump(per_scene, fh, indent=1, sort_keys=True)
-    with open(out_dir / "summary.json", "w") as fh:
-        json.dump(summary, fh, indent=1, sort_keys=True)
-    return summary
+    records.sort(key=lambda r: (r["scene_id"], r["view_index"]))
+    t0 = time.time()
+    overall, _ = stats.write_evaluation_outputs(records, out_dir, bootstrap_samples, exp.bootstrap_seed, scored)
+    meta = dict(metas[0])
+    meta.update(max_scenes=None, shard_index=None, num_shards=num_shards,
+                merge_protocol="deterministic strided scene shards", merged_at_unix=time.time())
+    (out_dir / "run_metadata.json").write_text(json.dumps(meta, indent=2, sort_keys=True) + "\n", encoding="utf-8")
+    overall.update(runtime_seconds=time.time() - t0, expected_scenes=scenes, expected_rows=rows)
+    (out_dir / "overall_summary.json").write_text(json.dumps(overall, indent=2, sort_keys=True) + "\n",
+                                                  encoding="utf-8")
+    from .evaluate import Tracker
+    tracker = Tracker(wandb_mode, exp, meta, None, out_dir)
+    try:
+        tracker.summary(**overall, state="complete")
+    finally:
+        tracker.finish()
+    completion.write_text(json.dumps({
+        "state": "complete", "experiment_id": exp.name, "dataset": exp.dataset, "expected_scenes": scenes,
+        "expected_rows": rows, **{k: meta.get(k) for k in ("checkpoint_sha256", "config_sha256",
+                                                          "view_manifest_sha256", "evaluation_code_sha256")},
+        "wandb_run_id": tracker.id, "wandb_mode": wandb_mode}, indent=2, sort_keys=True) + "\n", encoding="utf-8")
+    return overall
 
 
-def main(argv=None):
-    ap = argparse.ArgumentParser()
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description="Validate and merge the scene shards of one evaluation.")
     ap.add_argument("--registry", type=Path, required=True)
     ap.add_argument("--experiment", required=True)
     ap.add_argument("--shards-root", type=Path, required=True)
     ap.add_argument("--num-shards", type=int, required=True)
     ap.add_argument("--output-root", type=Path, required=True)
     ap.add_argument("--bootstrap-samples", type=int, default=10_000)
-    ap.add_argument("--allow-incomplete", action="store_true")
+    ap.add_argument("--wandb-mode", choices=("online", "offline", "disabled"), default="disabled")
     ap.add_argument("--overwrite", action="store_true")
     args = ap.parse_args(argv)
-    exp = load_registry(args.registry)[args.experiment]
-    print(json.dumps(merge(exp, args.shards_root, args.num_shards, args.output_root, args.bootstrap_samples,
-                           args.overwrite, args.allow_incomplete), sort_keys=True))
+    exp = resolve_experiment(args.registry, args.experiment)
+    overall = merge(exp, args.shards_root, args.num_shards, args.output_root, args.bootstrap_samples, args.overwrite,
+                    args.wandb_mode)
+    print(json.dumps({"experiment": exp.name, "overall": overall}, indent=2))
+    return 0
 
 
 if __name__ == "__main__":
-    main()
+    raise SystemExit(main())

@@ -18,7 +18,7 @@ from pathlib import Path
 import numpy as np
 import torch
 
-from .evaluate import AMP, load_model
+from .evaluate import AMP, load_config, load_model
 from .registry import load_registry, preflight
 from .views import FixedViewDataset
 
@@ -48,7 +48,8 @@ def render(registry, dataset: str, experiments, out_dir: Path, scene_ids=None, s
         problems = preflight(e, require_checkpoint=not allow_missing_checkpoint)
         if problems:
             raise SystemExit("preflight failed:\n  " + "\n  ".join(problems))
-    ds = FixedViewDataset(str(exps[0].view_manifest), exps[0].image_size, dataset_manifest=str(exps[0].manifest))
+    size = exps[0].image_size or int(load_config(exps[0])["model"]["image_size"])
+    ds = FixedViewDataset(str(exps[0].view_manifest), size, dataset_manifest=str(exps[0].manifest))
     order = list(range(len(ds)))
     if scene_ids:
         wanted = set(scene_ids)

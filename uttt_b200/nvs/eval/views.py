@@ -238,7 +238,9 @@ class FixedViewDataset(Dataset):
 
     def __init__(self, view_manifest: str, image_size: int, shard_index: int = 0, num_shards: int = 1,
                  max_scenes: int = 0, dataset_manifest: Optional[str] = None, verify_camera_sha256: bool = True,
-                 expected_num_views: Optional[int] = None):
+                 expected_num_views: Optional[int] = None, load_threads: int = 8):
+        if load_threads <= 0:
+            raise ValueError(f"load_threads must be positive, got {load_threads}")
         doc = load_view_manifest(view_manifest, expected_num_views)
         scenes: List[Dict] = [dict(s) for s in doc["scenes"]]
         if dataset_manifest is not None:
@@ -248,14 +250,15 @@ class FixedViewDataset(Dataset):
                                         f"{len(scenes)} scenes")
             for s, cam in zip(scenes, cameras):
                 s["camera_path"] = cam
+        self.scenes = scenes[shard_index::num_shards]           # strided shard first, then the smoke-run cut
         if max_scenes:
-            scenes = scenes[:max_scenes]
-        self.scenes = scenes[shard_index::num_shards]
+            self.scenes = self.scenes[:max_scenes]
         self.num_views = doc["num_views"]
         self.dataset = str(doc.get("dataset", ""))
         self.verify_camera_sha256 = verify_camera_sha256
         self._loader = NVSDataset.__new__(NVSDataset)
         self._loader.image_size = image_size
+        self._loader.LOAD_THREADS = load_threads
 
     def __len__(self):
         return len(self.scenes)

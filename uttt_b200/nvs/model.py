@@ -23,18 +23,23 @@ import torch.nn.functional as F
 from .. import ops
 from ..ops import reference as ref
 from . import blocks as nvs_blocks
+from . import stacks as nvs_stacks
 from .schedule import inputs_then_targets_config, parallel_ttt_config
 
 # class paths used by the reference YAML files -> classes of this package
 _CLASS_ALIASES = {
     "uttt_nvs.models.uttt_moe_block.MemoryModel": nvs_blocks.MemoryModel,
     "uttt_nvs.models.uttt_moe_partitioned.MemoryModel": nvs_blocks.PartitionedMemoryModel,
-    "uttt_nvs.models.uttt_dense_block.MemoryModel": nvs_blocks.DenseMemoryModel,
-    "uttt_nvs.models.uttt_dense_partitioned.MemoryModel": nvs_blocks.DensePartitionedMemoryModel,
-    "uttt_nvs.models.ttt_dense_block.MemoryModel": nvs_blocks.DenseMemoryModel,
-    "uttt_nvs.models.transformer_block.TransformerModel": nvs_blocks.TransformerBlocks,
-    "uttt_nvs.models.deltanet_block.DeltaNetModel": nvs_blocks.DeltaNetBlocks,
-    "uttt_nvs.models.gated_deltanet_block.GatedDeltaNetModel": nvs_blocks.GatedDeltaNetBlocks,
+    "uttt_nvs.models.uttt_dense_block.MemoryModel": nvs_stacks.UTTTDenseModel,
+    "uttt_nvs.models.uttt_dense_partitioned.MemoryModel": nvs_stacks.UTTTDensePartitionedModel,
+    "uttt_nvs.models.ttt_dense_block.MemoryModel": nvs_stacks.TTTDenseModel,
+    "uttt_nvs.models.transformer_block.MemoryModel": nvs_stacks.TransformerModel,
+    "uttt_nvs.models.deltanet_block.MemoryModel": nvs_stacks.DeltaNetModel,
+    "uttt_nvs.models.gated_deltanet_block.MemoryModel": nvs_stacks.GatedDeltaNetModel,
+    # spellings used by earlier configuration files of this package
+    "uttt_nvs.models.transformer_block.TransformerModel": nvs_stacks.TransformerModel,
+    "uttt_nvs.models.deltanet_block.DeltaNetModel": nvs_stacks.DeltaNetModel,
+    "uttt_nvs.models.gated_deltanet_block.GatedDeltaNetModel": nvs_stacks.GatedDeltaNetModel,
 }
 
 

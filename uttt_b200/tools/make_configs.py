@@ -1,6 +1,6 @@
 """Writes the configuration tree under ``configs/``:  ``python -m uttt_b200.tools.make_configs``.
 
-* ``configs/lm/{124M,760M}/<model>.json`` - architecture files of every language-model family at the two paper
+* ``configs/lm/main/{124M,760M}/<model>.json`` - architecture files of every language-model family at the two paper
   scales (the shapes shipped with the reference, uttt_llm/configs/main), plus ``configs/lm/named/*.json`` for the
   benchmark-named shapes and ``configs/lm/balancing/*`` for the loss-free-rate / scope / router-alpha sweeps;
 * ``configs/lm/exp/train_{124M,760M}_32k.toml`` and ``eval_ptl.toml`` - job files (global batch 32 at 32K);
@@ -41,13 +41,25 @@ def lm_shapes(scale: str) -> Dict[str, Dict[str, Any]]:
                                                 memory_aggregate_momentum_mode="none", memory_num_experts=4,
                                                 memory_lb_scope="layer", memory_lb_mode="loss",
                                                 memory_lb_loss_alpha=0.0)},
-        "ttt_dense": dict(base, model_type="ttt_dense", fw_num_heads=4, fw_inter_multi=1, w0_w2_low_rank=0),
-        "lact": dict(base, model_type="lact_swiglu", num_lact_heads=4, inter_multi=1, lact_chunk_size=4096),
+        # w0 / w2 of the per-layer dense families start as identity + a rank-32 product
+        "ttt_dense": dict(base, model_type="ttt_dense", fw_num_heads=4, fw_inter_multi=1, w0_w2_low_rank=32),
+        "lact": dict(base, model_type="lact_swiglu", num_lact_heads=4, inter_multi=1, lact_chunk_size=4096,
+                     w0_w2_low_rank=32, num_attn_heads=SCALES[scale]["num_heads"]),
         "transformer": dict(base, model_type="transformer", use_memory_block=False, window_size=None),
         "transformer_swa": dict(base, model_type="transformer", use_memory_block=False),
     }
-    for mixer in ("deltanet", "gated_deltanet", "kda", "mamba2", "mom"):
-        out[f"{mixer}_swa"] = dict(base, model_type=f"{mixer}_swa", use_memory_block=False, mixer_head_dim=64)
+    # the bounded-state baselines, sized to the parameter budget of the fast-weight models: no short convolutions,
+    # the MLP narrowed where the mixer itself carries more parameters (gate, decay, state projections)
+    h = SCALES[scale]["hidden_size"]
+    mixers = {
+        "deltanet": dict(use_short_conv=False),
+        "gated_deltanet": dict(use_short_conv=False, use_gate=True, hidden_ratio=3.5),
+        "kda": dict(use_short_conv=False, hidden_ratio=None, intermediate_size={768: 1984, 1536: 4032}[h]),
+        "mamba2": dict(hidden_ratio=3.5, intermediate_size=h * 3 // 2, state_size=h * 3 // 4, chunk_size=256),
+        "mom": dict(use_short_conv=False, use_gate=True, hidden_ratio=3.5, num_memories=4, topk_memories=1),
+    }
+    for mixer, extra in mixers.items():
+        out[f"{mixer}_swa"] = dict(base, model_type=f"{mixer}_swa", use_memory_block=False, mixer_head_dim=64, **extra)
     if small:
         for r in (1, 2, 4, 6):
             out[f"uttt_dense_r{r}"] = dict(base, model_type="uttt_dense", fw_num_heads=4, uttt_dense_r=r,
@@ -134,12 +146,16 @@ def nvs_configs() -> Dict[str, Dict[str, Any]]:
         out[f"ownership/{data}/ttt_moe_e8a1"] = nvs_yaml(
             f"ttt_moe_e8a1_{data}", moe, dict(base, num_experts=8, pool_mode="per_block", aggregate_write=False,
                                               router_share_mode="per_layer"))
+        out[f"ownership/{data}/ttt_moe_e4a1"] = nvs_yaml(
+            f"ttt_moe_e4a1_{data}", moe, dict(base, num_experts=4, pool_mode="per_block", aggregate_write=False,
+                                              router_share_mode="per_layer"))
         out[f"ownership/{data}/uttt_dense_r1"] = nvs_yaml(f"uttt_dense_r1_{data}", dense, dict(
-            attn_head_dim=64, fw_head_dim=64, inter_multi=3, fw_inter_multi=1, use_muon=False, l2_norm=True))
-        out[f"ownership/{data}/ttt_dense"] = nvs_yaml(f"ttt_dense_{data}", dense, dict(
             attn_head_dim=64, fw_head_dim=64, inter_multi=3, fw_inter_multi=1, use_muon=False, l2_norm=True,
-            pool_mode="per_block"))
-        for e in (16, 32, 128, 256):
+            aggregate_write=True))
+        # TTT-Dense: every block owns its head-wise fast weights (no sharing, no aggregate)
+        out[f"ownership/{data}/ttt_dense"] = nvs_yaml(f"ttt_dense_{data}", "uttt_nvs.models.ttt_dense_block.MemoryModel", dict(
+            attn_head_dim=64, fw_head_dim=64, inter_multi=3, fw_inter_multi=1, l2_norm=True, use_muon=False))
+        for e in (8, 16, 32, 64, 128, 256):
             out[f"capacity/{data}/uttt_moe_e{e}a1"] = nvs_yaml(f"uttt_moe_e{e}a1_{data}", moe, dict(base, num_experts=e))
         for k in (2, 4):
             out[f"topology/{data}/uttt_moe_e64a{k}"] = nvs_yaml(f"uttt_moe_e64a{k}_{data}", moe,
@@ -155,9 +171,11 @@ def nvs_configs() -> Dict[str, Dict[str, Any]]:
                                                                dict(base, fw_inter_multi=m))
         for r in (2, 4, 8):
             out[f"dense/{data}/uttt_dense_r{r}"] = nvs_yaml(f"uttt_dense_r{r}_{data}", dense, dict(
-                attn_head_dim=64, fw_head_dim=64, inter_multi=3, fw_inter_multi=r, use_muon=False, l2_norm=True))
+                attn_head_dim=64, fw_head_dim=64, inter_multi=3, fw_inter_multi=r, use_muon=False, l2_norm=True,
+                aggregate_write=True))
         # the released studies, under the names of the reference's files
-        dense_base = dict(attn_head_dim=64, fw_head_dim=64, inter_multi=3, fw_inter_multi=1, use_muon=False, l2_norm=True)
+        dense_base = dict(attn_head_dim=64, fw_head_dim=64, inter_multi=3, fw_inter_multi=1, use_muon=False, l2_norm=True,
+                          aggregate_write=True)
         for e in (32, 64):
             for k in (1, 2, 4, 8):
                 out[f"width/{data}/uttt_moe_e{e}a{k}"] = nvs_yaml(f"uttt_moe_e{e}a{k}_{data}", moe,
@@ -170,7 +188,7 @@ def nvs_configs() -> Dict[str, Dict[str, Any]]:
         for width, pools in ((1, 2), (1, 4), (2, 4), (4, 2)):
             out[f"topology/{data}/uttt_dense_w{width}_p{pools}"] = nvs_yaml(
                 f"uttt_dense_w{width}_p{pools}_{data}", "uttt_nvs.models.uttt_dense_partitioned.MemoryModel",
-                dict(dense_base, fw_inter_multi=width, num_shared_pools=pools))
+                dict(dense_base, fw_inter_multi=width, num_shared_pools=pools, pool_mode="shared"))
         out[f"dense/{data}/uttt_dense_r1"] = nvs_yaml(f"uttt_dense_r1_{data}", dense, dict(dense_base))
         out[f"schedule/{data}/uttt_moe_e64a1"] = nvs_yaml(f"uttt_moe_e64a1_{data}", moe, dict(base))
         out[f"schedule/{data}/uttt_moe_e64a1_chained"] = nvs_yaml(f"uttt_moe_e64a1_chained_{data}", moe,
@@ -178,17 +196,34 @@ def nvs_configs() -> Dict[str, Dict[str, Any]]:
         out[f"schedule/{data}/uttt_moe_4in2out"] = nvs_yaml(f"uttt_moe_4in2out_{data}", moe, dict(base), views=6)
         out[f"schedule/{data}/uttt_moe_4in2out"]["model"].update(view_layout="inputs_then_targets", num_input_views=4)
         out[f"transformer/{data}/transformer"] = nvs_yaml(
-            f"transformer_{data}", "uttt_nvs.models.transformer_block.TransformerModel", dict(attn_head_dim=64, inter_multi=4))
+            f"transformer_{data}", "uttt_nvs.models.transformer_block.MemoryModel",
+            dict(attn_head_dim=64, inter_multi=3, transformer_version="v0", vi_rms_norm=True,
+                 pre_vi_source="xi_memory_in", use_separate_last_to_kv=False), num_workers=8)
+        # widths of the slow MLP chosen so that the baselines match the parameter count of the fast-weight models
         out[f"reference/{data}/deltanet"] = nvs_yaml(
-            f"deltanet_{data}", "uttt_nvs.models.deltanet_block.DeltaNetModel", dict(attn_head_dim=64, inter_multi=3))
+            f"deltanet_{data}", "uttt_nvs.models.deltanet_block.MemoryModel",
+            dict(attn_head_dim=64, inter_multi=3.09375, fw_num_heads=8, expand_k=1.0, expand_v=1.0, use_beta=True,
+                 use_short_conv=False, conv_size=4, conv_bias=False, qk_activation="silu", qk_norm="l2",
+                 use_output_gate=False, allow_neg_eigval=False, noise_repeat=1, repeat_function="repeat",
+                 use_muon=False), batch=16, num_workers=8)
         out[f"reference/{data}/gated_deltanet"] = nvs_yaml(
-            f"gated_deltanet_{data}", "uttt_nvs.models.gated_deltanet_block.GatedDeltaNetModel",
-            dict(attn_head_dim=64, inter_multi=3))
-    big = dict(base, num_experts=96, fw_head_dim=192, fw_inter_multi=2, attn_head_dim=64, apply_ckpt_group=6)
-    for size, batch, total in ((256, 8, 512), (512, 2, 128), (1024, 1, 64)):
+            f"gated_deltanet_{data}", "uttt_nvs.models.gated_deltanet_block.MemoryModel",
+            dict(attn_head_dim=64, inter_multi=2.75, fw_num_heads=8, expand_v=1.0, use_short_conv=False, conv_size=4,
+                 conv_bias=False, use_output_gate=True, noise_repeat=1, repeat_function="repeat", use_muon=False),
+            batch=16, num_workers=8)
+    big = dict(base, num_experts=96, fw_head_dim=192, fw_inter_multi=2, attn_head_dim=64, apply_ckpt_group=6,
+               offload_master_states=True)
+    # resolution curriculum of the large model: 256 from scratch, then 512 and 1024 from the previous stage's weights
+    # with a fresh optimizer at a small constant-peak rate; perceptual loss after an l2-only warm-up
+    stages = {256: dict(batch=8, total=512, max_fwdbwd_passes=81038),
+              512: dict(batch=2, total=128, max_fwdbwd_passes=70000, lr=1e-5, reset_training_state=True,
+                        load_optimizer_state_when_reset_training_state=False),
+              1024: dict(batch=1, total=64, max_fwdbwd_passes=4500, lr=1e-5, reset_training_state=True,
+                         load_optimizer_state_when_reset_training_state=False)}
+    for size, stage in stages.items():
         out[f"scale/obj/uttt_moe_large_{size}"] = nvs_yaml(
-            f"uttt_moe_large_{size}", moe, dict(big, offload_master_states=True) if size > 256 else dict(big), dim=768,
-            layers=24, size=size, batch=batch, total=total)
+            f"uttt_moe_large_{size}_obj", moe, dict(big), dim=768, layers=24, size=size, num_workers=4,
+            perceptual_loss_weight=0.5, l2_warmup_steps=4000, round_max_fwdbwd_passes_to_epoch=False, **stage)
     out["named/uttt_moe_256_4in2out"] = nvs_yaml(
         "uttt_moe_256_4in2out", moe, dict(base, num_experts=16, num_active_experts=2, fw_head_dim=64), dim=768,
         layers=24, size=256, batch=16, total=128, views=6)
@@ -196,10 +231,68 @@ def nvs_configs() -> Dict[str, Dict[str, Any]]:
     return out
 
 
+def eval_registries() -> Dict[str, Dict[str, Any]]:
+    """``experiments.yaml`` (the evaluated fast-weight models and linear baselines on both test sets) and
+    ``experiments_transformer.yaml`` (the transformer, whose attention gap must be declared null)."""
+    defaults = {"checkpoint_root": "/PATH/TO/CHECKPOINTS", "output_root": "/PATH/TO/EVAL_OUTPUTS",
+                "wandb": {"entity": "YOUR_WANDB_ENTITY", "project": "YOUR_WANDB_PROJECT"}, "seed": 9595, "num_views": 24}
+    datasets = [
+        {"id": "gso", "display_name": "Objaverse/GSO",
+         "local_manifest": "/PATH/TO/MANIFESTS/gso_v0.1_instant3d_test_localssd.txt",
+         "view_manifest": "/PATH/TO/MANIFESTS/gso_views_seed9595_v24.json", "expected_scenes": 1019,
+         "expected_rows": 1019 * 23},
+        {"id": "dl3dv", "display_name": "DL3DV", "local_manifest": "/PATH/TO/MANIFESTS/dl3dv10k_benchmark_local.txt",
+         "view_manifest": "/PATH/TO/MANIFESTS/dl3dv_views_seed9595_v24.json", "expected_scenes": 140,
+         "expected_rows": 140 * 23}]
+    domain = {"gso": ("obj", "object", 24476), "dl3dv": ("dl3dv", "dl3dv", 20046)}
+
+    def entry(ds, study, model, paper, impl, group, label, **extra):
+        folder, ckpt_folder, step = domain[ds]
+        return {"id": f"{ds}_{model}", "dataset": ds, "model": model, "paper_model": paper,
+                "config": f"configs/nvs/{study}/{folder}/{model}.yaml", "checkpoint": f"{ckpt_folder}/{model}/checkpoint.pt",
+                "checkpoint_step": step, "checkpoint_impl": impl, "group": group, "display_name": label, **extra}
+
+    def core(ds):
+        # the per-block routed model was trained with another implementation on DL3DV: the label tells them apart
+        rows = [entry(ds, "ownership", "ttt_dense", "TTT-Dense", "ttt_dense", "ttt_dense", "TTT-Dense")]
+        rows += [entry(ds, "ownership", f"ttt_moe_e{e}a1", "TTT-MoE", "ttt_moe" if ds == "gso" else "ttt_moe_alt",
+                       "ttt_moe", f"TTT-MoE-e{e}a1") for e in (4, 8)]
+        rows += [entry(ds, "dense", f"uttt_dense_r{r}", "uTTT-Dense", "uttt_dense", "uttt_dense", f"uTTT-Dense-r{r}")
+                 for r in (1, 2, 4, 8)]
+        rows += [entry(ds, "capacity", f"uttt_moe_e{e}a1", "uTTT-MoE", "uttt_moe", "uttt_moe", f"uTTT-MoE-e{e}a1")
+                 for e in (8, 16, 32, 64)]
+        rows += [entry(ds, "width", f"uttt_moe_e{e}a{k}", "uTTT-MoE", "uttt_moe", "uttt_moe", f"uTTT-MoE-e{e}a{k}")
+                 for e in (32, 64) for k in (2, 4, 8)]
+        return rows
+
+    def studies(ds):
+        rows = [entry(ds, "topology", f"uttt_moe_p{p}_e{e}", "uTTT-MoE", "uttt_moe_partitioned", "uttt_moe",
+                      f"uTTT-MoE-e{e // p}-p{p}") for e in (32, 64) for p in (2, 4)]
+        rows += [entry(ds, "topology", f"uttt_dense_w{w}_p{p}", "uTTT-Dense", "uttt_dense_partitioned", "uttt_dense",
+                       f"uTTT-Dense-w{w}-p{p}") for w, p in ((4, 2), (2, 4), (1, 2), (1, 4))]
+        rows.append(entry(ds, "schedule", "uttt_moe_e64a1_chained", "uTTT-MoE", "uttt_moe", "uttt_moe",
+                          "uTTT-MoE-e64a1 (chained write)"))
+        rows.append(entry(ds, "reference", "deltanet", "DeltaNet", "deltanet", "reference", "DeltaNet"))
+        rows.append(entry(ds, "reference", "gated_deltanet", "Gated DeltaNet", "gated_deltanet", "reference",
+                          "Gated DeltaNet"))
+        return rows
+
+    main = core("gso") + core("dl3dv") + studies("gso") + studies("dl3dv")
+    transformer = []
+    for ds, ckpt, step in (("dl3dv", "dl3dv_vgapnull", 20000), ("gso", "objaverse_vgapnull", 24000)):
+        row = entry(ds, "transformer", "transformer", "Transformer", "transformer", "transformer", "Transformer",
+                    expected_v_gap=None, evaluation_class="formal_vgap_null")
+        row.update(id=f"{ds}_transformer_vgapnull", checkpoint=f"{ckpt}/checkpoint.pt", checkpoint_step=step)
+        transformer.append(row)
+    return {"experiments.yaml": {"version": 1, "defaults": defaults, "datasets": datasets, "experiments": main},
+            "experiments_transformer.yaml": {"version": 1, "defaults": defaults, "datasets": datasets,
+                                             "experiments": transformer}}
+
+
 def main() -> None:
     for scale in SCALES:
         for name, cfg in lm_shapes(scale).items():
-            path = os.path.join(ROOT, "lm", scale, f"{name}.json")
+            path = os.path.join(ROOT, "lm", "main", scale, f"{name}.json")
             os.makedirs(os.path.dirname(path), exist_ok=True)
             with open(path, "w") as fh:
                 fh.write(config_from_dict(cfg).to_json_string())
@@ -268,35 +361,11 @@ def main() -> None:
         os.makedirs(os.path.dirname(path), exist_ok=True)
         with open(path, "w") as fh:
             yaml.safe_dump(cfg, fh, sort_keys=False)
-    # evaluation registries: one entry per released view-synthesis configuration and test domain
-    domains = {"obj": "gso", "dl3dv": "dl3dv"}
-    steps = {"gso": 24476, "dl3dv": 20046}
-    datasets = {"gso": {"manifest": "/PATH/TO/MANIFESTS/gso_v0.1_instant3d_test_localssd.txt",
-                        "view_manifest": "/PATH/TO/MANIFESTS/gso_views_24_seed9595.json", "image_size": 256,
-                        "num_scenes": 1019},
-                "dl3dv": {"manifest": "/PATH/TO/MANIFESTS/dl3dv10k_benchmark_local.txt",
-                          "view_manifest": "/PATH/TO/MANIFESTS/dl3dv_views_24_seed9595.json", "image_size": 256,
-                          "num_scenes": 140}}
-    main_entries, tr_entries = [], []
-    seen = set()
-    for rel, cfg in sorted(nvs_configs().items()):
-        parts = rel.split("/")
-        if len(parts) != 3 or parts[1] not in domains or parts[0] in ("scale", "schedule"):
-            continue
-        ds = domains[parts[1]]
-        if (ds, parts[2]) in seen:           # the same run appears in several studies: one registry entry
-            continue
-        seen.add((ds, parts[2]))
-        entry = {"name": f"{ds}/{parts[2]}", "dataset": ds, "config": f"configs/nvs/{rel}.yaml",
-                 "checkpoint": f"{ds}/{parts[2]}/ckpt_{steps[ds]:016d}.pt", "paper_model": parts[2],
-                 "display_name": parts[2].replace("_", "-"), "checkpoint_impl": parts[2].split("_e")[0], "v_gap": None}
-        (tr_entries if parts[0] == "transformer" else main_entries).append(entry)
-    defaults = {"checkpoint_root": "/PATH/TO/CHECKPOINTS", "output_root": "eval_outputs", "num_views": 24,
-                "view_seed": 9595}
-    os.makedirs(os.path.join(ROOT, "nvs", "eval"), exist_ok=True)
-    for fname, entries in (("experiments.yaml", main_entries), ("experiments_transformer.yaml", tr_entries)):
+    # evaluation registries, in the reference's layout and with its experiment ids, checkpoint paths and labels
+    for fname, doc in eval_registries().items():
+        os.makedirs(os.path.join(ROOT, "nvs", "eval"), exist_ok=True)
         with open(os.path.join(ROOT, "nvs", "eval", fname), "w") as fh:
-            yaml.safe_dump({"defaults": defaults, "datasets": datasets, "experiments": entries}, fh, sort_keys=False)
+            yaml.safe_dump(doc, fh, sort_keys=False)
     print(f"wrote configs under {ROOT}")
 
 
