@@ -211,7 +211,7 @@ def test_trainer_runs_saves_and_resumes(tmp_path):
     t = NVSTrainer(cfg, device=torch.device("cpu"))
     summary = t.fit()
     assert t.fwdbwd_step == 4 and summary["avg_step_time_s"] > 0
-    assert len(ck.find_checkpoints(t.out_dir)) == 1
+    assert len(ck.find_checkpoints(t.out_dir)) == 2           # passes 2 and 4; the last three are kept by default
     t2 = NVSTrainer(cfg, device=torch.device("cpu"))
     assert t2.fwdbwd_step == 4 and t2.update_step == 4
     for (n1, p1), (n2, p2) in zip(t.model.named_parameters(), t2.model.named_parameters()):
@@ -382,3 +382,67 @@ def test_partitioned_pool_layout_and_rebinding():
         LVSMModel(_cfg("uttt_nvs.models.uttt_moe_partitioned.MemoryModel", v_gap=1, **base))
     with pytest.raises(ValueError):
         LVSMModel(_cfg("uttt_nvs.models.uttt_moe_partitioned.MemoryModel", num_shared_pools=2, num_experts=3))
+
+
+def test_job_overview_rounds_the_pass_budget_to_epochs():
+    from uttt_b200.nvs.trainer import job_overview
+    o = job_overview(num_gpus=4, num_train_samples=1000, batch_size_per_gpu=8, grad_accum_steps=2,
+                     max_fwdbwd_passes=100)
+    assert o["num_fwdbwd_passes_per_epoch"] == 31 and o["num_epochs"] == 4 and o["num_fwdbwd_passes"] == 124
+    assert o["num_param_updates"] == 62 and o["batch_size_per_param_update"] == 64
+    exact = job_overview(4, 1000, 8, 2, 100, round_max_fwdbwd_passes_to_epoch=False)
+    assert exact["num_fwdbwd_passes"] == 100 and exact["num_epochs"] == 4 and exact["num_param_updates"] == 50
+    assert job_overview(8, 10, 4, 1, 5)["num_fwdbwd_passes_per_epoch"] == 1          # fewer samples than one pass
+
+
+def test_in_training_evaluation_visuals_metrics_and_warmup(tmp_path):
+    """Evaluation after the first pass and every ``eval_every`` passes (24-view synthetic scenes here), visuals every
+    ``vis_every`` passes, a metrics line per logged pass, and the squared-error-only warm-up."""
+    import json
+    cfg = _cfg()
+    cfg["training"].update(out_dir=str(tmp_path), max_fwdbwd_passes=4, eval_every=3, vis_every=2, eval_num_views=5,
+                           checkpoint_every=100, l2_warmup_steps=2, print_every=1)
+    t = NVSTrainer(cfg, device=torch.device("cpu"))
+    warm = []
+    real_pass = t._forward_backward
+    t._forward_backward = lambda b: (warm.append(t.model._l2_only), real_pass(b))[1]
+    t.fit()
+    assert warm == [True, True, False, False]
+    made = sorted(os.listdir(t.out_dir))
+    assert {"eval_00000001", "eval_00000003", "iter_00000002", "iter_00000004", "metrics.jsonl"} <= set(made)
+    files = sorted(os.listdir(os.path.join(t.out_dir, "eval_00000003")))
+    assert files[0].startswith("input_") and files[1].startswith("supervision_") and files[2] == "uids.txt"
+    from PIL import Image
+    w, h = Image.open(os.path.join(t.out_dir, "eval_00000003", files[1])).size
+    assert (w, h) == (4 * 2 * 32, 2 * 32)                     # 4 scored views x (target | rendering), 2 scenes
+    lines = [json.loads(ln) for ln in open(os.path.join(t.out_dir, "metrics.jsonl"))]
+    train = [ln for ln in lines if "train/loss" in ln]
+    evals = [ln for ln in lines if "eval/loss" in ln]
+    assert [ln["step"] for ln in train] == [1, 2, 3, 4] and [ln["step"] for ln in evals] == [1, 3]
+    assert {"eval/psnr", "eval/moe_freq_max", "eval_loc/psnr_loc_000", "eval_loc/psnr_loc_003"} <= set(evals[0])
+    assert t.model.training and not t.model._l2_only
+    out = t.model(_batch())
+    assert set(out) == {"input", "target", "loss_metrics", "rendering", "op2block2info"}
+    assert out["target"].image.shape == (2, 3, 3, 32, 32) and out["input"]["c2w"].shape == (2, 3, 4, 4)
+
+
+def test_trainer_refuses_what_the_reference_refuses(tmp_path):
+    cfg = _cfg()
+    cfg["training"]["out_dir"] = str(tmp_path)
+    cfg["model"]["act_ckpt"] = True
+    with pytest.raises(NotImplementedError, match="act_ckpt"):
+        NVSTrainer(cfg, device=torch.device("cpu"))
+    cfg["model"]["act_ckpt"] = False
+    manifest = make_toy_dataset(str(tmp_path / "toy"), num_scenes=2, num_frames=6, image_size=32, repeat=2)
+    cfg["training"].update(dataset="toy", dataset_path=manifest, max_fwdbwd_passes=1, eval_every=1)
+    cfg["eval_dataset_path"] = "PATH/TO/eval_manifest.txt"
+    t = NVSTrainer(cfg, device=torch.device("cpu"))
+    assert t.num_train_samples == 4 and t.overview["num_fwdbwd_passes_per_epoch"] == 2
+    assert t.total == 2                                        # one pass asked for, rounded up to the epoch
+    with pytest.raises(ValueError, match="eval_dataset_path"):
+        t.fit()
+    cfg["eval_dataset_path"] = manifest
+    cfg["training"].update(eval_num_views=6, out_dir=str(tmp_path / "second"))
+    t = NVSTrainer(cfg, device=torch.device("cpu"))
+    t.fit()
+    assert os.path.isdir(os.path.join(t.out_dir, "eval_00000002")) and t.fwdbwd_step == 2

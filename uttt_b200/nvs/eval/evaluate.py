@@ -213,7 +213,7 @@ def evaluate_experiment(exp: Experiment, out_dir: Path, registry_path: Optional[
                     batch = {k: v.to(device, non_blocking=True) for k, v in batch.items()}
                     with torch.autocast("cuda", dtype=AMP[amp_dtype], enabled=use_amp):
                         out = model(batch)
-                    pred, tgt = out["rendering"].float(), out["target"].float()       # [b, V-1, 3, H, W]
+                    pred, tgt = out["rendering"].float(), out["target"]["image"].float()       # [b, V-1, 3, H, W]
                     if pred.shape[1] != scored or tgt.shape[1] != scored:
                         raise RuntimeError(f"model must produce exactly View 1..{scored}; got target "
                                            f"{tuple(tgt.shape)} and prediction {tuple(pred.shape)}")

@@ -14,6 +14,7 @@ Two view layouts are supported:
 from __future__ import annotations
 
 import importlib
+import os
 from typing import Any, Dict, List, Optional
 
 import torch
@@ -74,6 +75,16 @@ def _cfg_get(cfg, key, default=None):
     return getattr(cfg, key, default)
 
 
+class Views(dict):
+    """The per-view fields of one side (inputs or targets) of a batch; entries are also attributes."""
+
+    def __getattr__(self, key):
+        try:
+            return self[key]
+        except KeyError as exc:
+            raise AttributeError(key) from exc
+
+
 class LVSMModel(nn.Module):
     """``forward(batch)`` with ``batch = {image [b,v,3,H,W], fxfycxcy [b,v,4], c2w [b,v,4,4]}``."""
 
@@ -98,13 +109,35 @@ class LVSMModel(nn.Module):
         tr = config.get("training", {})
         self.lpips_weight = float(tr.get("lpips_loss_weight", 0.0) or 0.0)
         self.perceptual_weight = float(tr.get("perceptual_loss_weight", 0.0) or 0.0)
-        self.perceptual = None
+        # the loss networks are plain attributes, not submodules: they never enter the state dict
+        # (uttt_nvs/models/lvsm_moe.py:30-58)
+        object.__setattr__(self, "perceptual", None)
+        object.__setattr__(self, "lpips", None)
         if self.perceptual_weight > 0:
             from .perceptual import PerceptualLoss
-            self.perceptual = PerceptualLoss()
+            with torch.random.fork_rng(devices=[]):             # its throw-away initialisation must not move the RNG
+                object.__setattr__(self, "perceptual", PerceptualLoss())
+        if self.lpips_weight > 0:
+            from .perceptual import build_lpips
+            with torch.random.fork_rng(devices=[]):
+                object.__setattr__(self, "lpips", build_lpips())
+        self._l2_only = False
         for mod in self.modules():
             if isinstance(mod, nn.Linear):
                 nn.init.normal_(mod.weight, std=0.02)
+
+    def l2_warmup(self, set: bool = True) -> None:
+        """While set, the loss is the squared error (+ load-balancing term) alone; the trainer sets it from the global
+        pass counter (``training.l2_warmup_steps``), so a resumed run does not warm up again
+        (uttt_nvs/models/lvsm_moe.py:60-76)."""
+        self._l2_only = bool(set)
+
+    def _apply(self, fn, recurse=True):
+        out = super()._apply(fn, recurse)
+        for net in (self.perceptual, self.lpips):                   # follow the model across devices / dtypes
+            if net is not None:
+                net._apply(fn)
+        return out
 
     # ------------------------------------------------------------------ tokens
     def build_tokens(self, batch):
@@ -158,8 +191,11 @@ class LVSMModel(nn.Module):
         pixels = 3 * self.image_size[0] * self.image_size[1]
         mse = sse.sum() / (sse.numel() * pixels)
         loss = mse + lb_loss
-        perceptual = rendering.new_zeros(())
-        if self.perceptual is not None:
+        perceptual, lpips_loss = rendering.new_zeros(()), rendering.new_zeros(())
+        if self.lpips is not None and not self._l2_only:
+            lpips_loss = self.lpips(rendering.flatten(0, 1).float(), tgt.flatten(0, 1).clamp(0, 1)).mean()
+            loss = loss + self.lpips_weight * lpips_loss
+        if self.perceptual is not None and not self._l2_only:
             perceptual = self.perceptual(rendering.flatten(0, 1), tgt.flatten(0, 1))
             loss = loss + self.perceptual_weight * perceptual
         with torch.no_grad():
@@ -168,10 +204,64 @@ class LVSMModel(nn.Module):
             psnr = psnr_loc.mean()
         metrics = {"loss": loss, "l2_loss": mse.detach(), "lb_loss": lb_loss.detach(), "psnr": psnr,
                    "psnr_loc": psnr_loc, "perceptual_loss": perceptual.detach(),
-                   "lpips_loss": rendering.new_zeros(())}
+                   "lpips_loss": lpips_loss.detach()}
         if infos and isinstance(infos[-1], dict):
             metrics.update({k: v for k, v in infos[-1].items()})
-        return {"loss_metrics": metrics, "rendering": rendering, "target": targets}
+        v = batch["image"].shape[1]
+        if self.view_layout == "inputs_then_targets":
+            n_in = self.num_input_views or (v - 1)
+            cut_in, cut_tg = slice(0, n_in), slice(n_in, v)
+        else:
+            cut_in, cut_tg = slice(0, v - 1), slice(1, v)
+        fields = {k: t for k, t in batch.items() if torch.is_tensor(t) and t.dim() >= 2 and t.shape[1] == v}
+        return {"input": Views({k: t[:, cut_in] for k, t in fields.items()}),
+                "target": Views({k: t[:, cut_tg] for k, t in fields.items()}),
+                "loss_metrics": metrics, "rendering": rendering, "op2block2info": infos}
+
+    @torch.no_grad()
+    def save_visuals(self, out_dir: str, result: Dict[str, Any], batch: Optional[Dict[str, torch.Tensor]] = None):
+        """Writes ``supervision_<first>_<last>.jpg`` (target | rendering per view, scenes stacked), ``input_...jpg``,
+        ``uids.txt`` (scene numbers: last column of ``index``) and returns the images plus a per-view PSNR chart
+        (uttt_nvs/models/lvsm.py:242-300).  No plotting library is needed: the chart is drawn with Pillow."""
+        from PIL import Image, ImageDraw
+        os.makedirs(out_dir, exist_ok=True)
+        inp, tgt, ren = result["input"], result["target"], result["rendering"]
+
+        def sheet(t):                                     # [b, v, 3, h, w] -> uint8 [(b h), (v w), 3]
+            b, v, c, h, w = t.shape
+            arr = t.detach().float().cpu().permute(0, 3, 1, 4, 2).reshape(b * h, v * w, c).numpy()
+            return (arr * 255.0).clip(0.0, 255.0).astype("uint8")[..., :3]
+
+        pair = torch.cat((tgt["image"].to(ren.dtype), ren), dim=4)              # target beside rendering
+        if "index" in tgt:
+            uids = [int(tgt["index"][b, 0, -1]) for b in range(tgt["index"].shape[0])]
+        else:
+            uids = list(range(ren.shape[0]))
+        tag = f"{uids[0]:08}_{uids[-1]:08}"
+        supervision = Image.fromarray(sheet(pair))
+        supervision.save(os.path.join(out_dir, f"supervision_{tag}.jpg"))
+        with open(os.path.join(out_dir, "uids.txt"), "w") as fh:
+            fh.write("_".join(f"{u:08}" for u in uids))
+        inputs = Image.fromarray(sheet(inp["image"]))
+        inputs.save(os.path.join(out_dir, f"input_{tag}.jpg"))
+        vals = [float(x) for x in result["loss_metrics"]["psnr_loc"].detach().float().cpu().flatten()]
+        w, h, pad = 640, 480, 50
+        chart = Image.new("RGB", (w, h), "white")
+        draw = ImageDraw.Draw(chart)
+        lo, hi = min(vals), max(vals)
+        span = (hi - lo) or 1.0
+        draw.rectangle((pad, pad, w - pad, h - pad), outline="black")
+        pts = [(pad + (w - 2 * pad) * (i / max(len(vals) - 1, 1)), h - pad - (h - 2 * pad) * ((v_ - lo) / span))
+               for i, v_ in enumerate(vals)]
+        if len(pts) > 1:
+            draw.line(pts, fill=(31, 119, 180), width=2)
+        for x, y in pts:
+            draw.ellipse((x - 3, y - 3, x + 3, y + 3), fill=(31, 119, 180))
+        draw.text((w // 2 - 40, 15), "Per-view PSNR", fill="black")
+        draw.text((5, pad - 5), f"{hi:.2f}", fill="black")
+        draw.text((5, h - pad - 5), f"{lo:.2f}", fill="black")
+        draw.text((w // 2 - 40, h - 30), f"View (1->{len(vals)})", fill="black")
+        return {"supervision": supervision, "input": inputs, "psnr_loc": chart}
 
     def get_overview(self) -> Dict[str, int]:
         count = lambda mod: sum(p.numel() for p in mod.parameters() if p.requires_grad)

@@ -8,7 +8,12 @@ a ``datasets.yaml`` registry keyed by ``training.dataset``, a global-batch guard
 (``batch_size_per_gpu * world * grad_accum_steps == total_batch_size``), bf16 compute, AdamW with decay on
 tensors of rank >= 2, warmup + cosine schedule, a collective finite-loss vote before every backward,
 gradient clipping with outlier-step skipping, atomic ``ckpt_<step>.pt`` checkpoints with retention and
-resume, and a ``[TRAIN_SUMMARY]`` line with the average step time and peak memory.
+resume, and a ``[TRAIN_SUMMARY]`` line with the average step time and peak memory.  Also as there: the pass budget
+``max_fwdbwd_passes x grad_accum_steps`` rounded up to whole epochs unless ``round_max_fwdbwd_passes_to_epoch`` is off
+(:func:`job_overview`), squared-error-only warm-up for ``l2_warmup_steps`` passes, in-training evaluation every
+``eval_every`` passes (and after the first pass unless ``eval_first_step`` is off) on ``eval_dataset_path`` with
+``eval_num_views`` views, visuals every ``vis_every`` passes, metrics every ``wandb_log_every`` passes
+(``metrics.jsonl`` in the run folder; Weights & Biases too when the package and a key are present).
 
 Data parallelism runs through :class:`uttt_b200.parallel.fsdp.ShardedTrainer`: gradients are reduced and
 AdamW is applied on per-rank shards by the fused peer-memory kernels (the role DDP's bucketed all-reduce
@@ -82,6 +87,72 @@ def check_batch_arithmetic(cfg: Dict[str, Any], world: int) -> int:
     return accum
 
 
+def job_overview(num_gpus: int, num_train_samples: int, batch_size_per_gpu: int, grad_accum_steps: int,
+                 max_fwdbwd_passes: int = int(1e10), round_max_fwdbwd_passes_to_epoch: bool = True) -> Dict[str, int]:
+    """Sizes of a run (uttt_nvs/train/checkpoint.py:213-255).  ``max_fwdbwd_passes`` is the budget in passes; with
+    rounding the run ends on an epoch boundary after it (always at least one more partial epoch's worth)."""
+    per_pass = batch_size_per_gpu * num_gpus
+    per_epoch = max(1, int(num_train_samples / per_pass))
+    if round_max_fwdbwd_passes_to_epoch:
+        epochs = int(max_fwdbwd_passes / per_epoch) + 1
+        passes = per_epoch * epochs
+    else:
+        passes = max_fwdbwd_passes
+        epochs = (passes + per_epoch - 1) // per_epoch
+    return {"batch_size_per_fwdbwd_pass": per_pass, "batch_size_per_param_update": per_pass * grad_accum_steps,
+            "num_fwdbwd_passes_per_epoch": per_epoch, "num_param_updates_per_epoch": int(per_epoch / grad_accum_steps),
+            "num_fwdbwd_passes": passes, "num_param_updates": (passes + grad_accum_steps - 1) // grad_accum_steps,
+            "num_epochs": epochs}
+
+
+class MetricsLog:
+    """Rank 0's metric sink: one JSON object per line in ``<run>/metrics.jsonl``; mirrored to Weights & Biases when the
+    package is importable and a key is available (``WANDB_API_KEY`` or ``wandb:`` in ``training.api_key_path``).
+    The run id is kept in ``wandb_id.txt`` so that a resumed job continues the same run."""
+
+    def __init__(self, out_dir: str, cfg: Dict[str, Any], enabled: bool):
+        self.path, self.run = None, None
+        if not enabled:
+            return
+        os.makedirs(out_dir, exist_ok=True)
+        self.path = os.path.join(out_dir, "metrics.jsonl")
+        tr = cfg.get("training", {})
+        key = os.environ.get("WANDB_API_KEY", "")
+        key_file = tr.get("api_key_path")
+        if not key and key_file and os.path.exists(str(key_file)):
+            with open(key_file) as fh:
+                key = str((yaml.safe_load(fh) or {}).get("wandb", "") or "")
+        if not key or key.startswith("YOUR_"):
+            return
+        try:
+            import wandb
+        except ImportError:
+            print("wandb is not installed: metrics go to metrics.jsonl only", flush=True)
+            return
+        os.environ.setdefault("WANDB_API_KEY", key)
+        if tr.get("wandb_offline", False):
+            os.environ["WANDB_MODE"] = "offline"
+        id_file = os.path.join(out_dir, "wandb_id.txt")
+        run_id = open(id_file).read().strip() if os.path.exists(id_file) else None
+        self.run = wandb.init(project=os.environ.get("WANDB_PROJECT", "uttt-nvs"), name=cfg.get("exp_name", "run"),
+                              dir=os.path.join(out_dir, "wandb"), id=run_id, resume=tr.get("wandb_resume", "allow"),
+                              config=cfg)
+        if run_id is None:
+            with open(id_file, "w") as fh:
+                fh.write(self.run.id)
+
+    def log(self, payload: Dict[str, Any], step: int, images: Optional[Dict[str, Any]] = None) -> None:
+        if self.path is None:
+            return
+        import json
+        with open(self.path, "a") as fh:
+            fh.write(json.dumps({"step": step, **payload}) + "\n")
+        if self.run is not None:
+            import wandb
+            extra = {k: wandb.Image(v) for k, v in (images or {}).items()}
+            self.run.log({**payload, **extra}, step=step)
+
+
 def lr_at(step: int, base: float, warmup: int, total: int, kind: str = "cosine", init_ratio: float = 0.0) -> float:
     if step < warmup:
         return base * (init_ratio + (1 - init_ratio) * (step + 1) / max(warmup, 1))
@@ -126,6 +197,9 @@ class NVSTrainer:
         self.device = device or (torch.device("cuda", local) if torch.cuda.is_available() else torch.device("cpu"))
         tr = cfg["training"]
         self.accum = check_batch_arithmetic(cfg, self.world)
+        if cfg["model"].get("act_ckpt"):
+            raise NotImplementedError("model.act_ckpt is not supported: gradient checkpointing is already applied "
+                                      "inside the blocks. Remove `act_ckpt: true` from the config.")
         torch.manual_seed(int(tr.get("seed", 0)))
         model_cls = LVSMModel if "class_name" not in cfg["model"] else LVSMModel
         self.model = model_cls(cfg).to(self.device)
@@ -138,22 +212,37 @@ class NVSTrainer:
         self.optimizer, self.schedule = _OptimizerView(self.trainer), _Schedule()
         self.out_dir = os.path.join(tr.get("out_dir", os.environ.get("UTTT_NVS_OUT_DIR", "experiments")),
                                     cfg.get("exp_name", "run"))
-        self.total = int(tr.get("max_fwdbwd_passes", 20000))
         self.fwdbwd_step = 0
         self.update_step = 0
         resume = select_resume_path(self.out_dir, load, tr.get("load", "") or "")
         if resume:
+            # a run continued from its own folder keeps its counters whatever the file says; weights brought in from
+            # elsewhere may start the counters (and, unless asked otherwise, the optimizer) afresh
+            reset = (bool(tr.get("reset_training_state", False)) and resume != self.out_dir) \
+                or bool(tr.get("force_reset_training_state", False))
             _, _, self.fwdbwd_step, self.update_step = resume_job(
-                resume, self.model, self.optimizer, self.schedule,
-                reset_training_state=bool(tr.get("reset_training_state", False)),
+                resume, self.model, self.optimizer, self.schedule, reset_training_state=reset,
                 load_optimizer_state_when_reset_training_state=bool(
-                    tr.get("load_optimizer_state_when_reset_training_state", False)))
+                    tr.get("load_optimizer_state_when_reset_training_state", False)) and reset)
             if not self.optimizer.loaded:
                 # only the model came back (a reset of the training state): rebuild the fp32 masters from it.
                 # With optimizer state loaded the masters are already exact; re-reading the bf16 compute copy
                 # would round them.
                 self.trainer.load_model_state()
+        self.num_train_samples: Optional[int] = None               # None: the synthetic stream has no epochs
         self.data = self._build_data()
+        budget = int(tr.get("max_fwdbwd_passes", int(1e10))) * self.accum
+        if self.num_train_samples is None:
+            self.overview = {"num_fwdbwd_passes": int(tr.get("max_fwdbwd_passes", 20000)),
+                             "num_fwdbwd_passes_per_epoch": int(tr.get("max_fwdbwd_passes", 20000)),
+                             "num_param_updates": max(int(tr.get("max_fwdbwd_passes", 20000)) // self.accum, 1)}
+        else:
+            self.overview = job_overview(self.world, self.num_train_samples, int(tr["batch_size_per_gpu"]), self.accum,
+                                         budget, bool(tr.get("round_max_fwdbwd_passes_to_epoch", True)))
+        self.total = self.overview["num_fwdbwd_passes"]
+        self.start_step = self.fwdbwd_step
+        self.metrics = MetricsLog(self.out_dir, cfg, enabled=self.rank == 0 and bool(tr.get("log_metrics", True)))
+        self._eval_data = None
         self.step_times: List[float] = []
         self._graphs: Dict[Any, Any] = {}
         self._passes_run = 0                       # of this process (a resumed run also warms up before a capture)
@@ -169,6 +258,7 @@ class NVSTrainer:
             src.step = self.fwdbwd_step
             return iter(src)
         ds = NVSDataset(tr["dataset_path"], int(tr.get("num_views", 12)), size, tr.get("max_num_objects"))
+        self.num_train_samples = len(ds)
         sampler = ResumableDistributedSampler(ds, num_replicas=self.world, rank=self.rank, shuffle=True, seed=0,
                                               drop_last=True)
         per_epoch = max(len(sampler) // int(tr["batch_size_per_gpu"]), 1)
@@ -176,7 +266,8 @@ class NVSTrainer:
         sampler.set_resume_offset((self.fwdbwd_step % per_epoch) * int(tr["batch_size_per_gpu"]))
         loader = torch.utils.data.DataLoader(ds, batch_size=int(tr["batch_size_per_gpu"]), sampler=sampler,
                                              num_workers=int(tr.get("num_workers", 0)), drop_last=True,
-                                             pin_memory=torch.cuda.is_available())
+                                             pin_memory=torch.cuda.is_available(),
+                                             **self._worker_options(int(tr.get("num_workers", 0))))
 
         def forever():
             epoch = self.fwdbwd_step // per_epoch
@@ -187,24 +278,33 @@ class NVSTrainer:
                 sampler.set_epoch(epoch)
         return forever()
 
+    def _worker_options(self, workers: int) -> Dict[str, Any]:
+        pf = self.cfg["training"].get("prefetch_factor")
+        return {"prefetch_factor": int(pf), "persistent_workers": True} if workers > 0 and pf else {}
+
     def train_pass(self, batch: Dict[str, torch.Tensor]) -> Dict[str, float]:
         """One forward/backward pass; an optimizer step every ``grad_accum_steps`` passes."""
         tr = self.cfg["training"]
         t0 = time.time()
         batch = {k: v.to(self.device, non_blocking=True) for k, v in batch.items() if torch.is_tensor(v)}
         self.model.train()
+        warm = self.fwdbwd_step < int(tr.get("l2_warmup_steps", 0))
+        if warm != self.model._l2_only:
+            self.model.l2_warmup(warm)
+            self.release_graphs()                             # a captured pass has the loss terms baked in
         loss, psnr, vote = self._forward_backward(batch)
         self.fwdbwd_step += 1
         stats: Dict[str, Any] = {"loss": loss, "psnr": psnr, "finite": vote}
         if self.accum > 1:
             self.trainer.accumulate_micro_batch()             # every pass, the last one included
-        if self.fwdbwd_step % self.accum == 0:
+        if self.fwdbwd_step % self.accum == 0 or self.fwdbwd_step == self.total:
             lr = lr_at(self.update_step, float(tr.get("lr", 4e-4)), int(tr.get("warmup", 0)),
-                       max(self.total // self.accum, 1), tr.get("scheduler_type", "cosine"),
+                       self.overview["num_param_updates"], tr.get("scheduler_type", "cosine"),
                        float(tr.get("warmup_init_ratio", 0.0)))
             skip_above = None
-            if self.update_step > int(tr.get("may_skip_gradnorm_after", 1 << 60)):
-                skip_above = float(tr.get("allowed_gradnorm_factor", 5)) * float(tr.get("grad_clip_norm", 1.0))
+            clip = float(tr.get("grad_clip_norm", 1.0))
+            if clip > 0 and self.fwdbwd_step > int(tr.get("may_skip_gradnorm_after", 0)):
+                skip_above = float(tr.get("allowed_gradnorm_factor", 5)) * clip
             out = self.trainer.step(lr=lr, skip_above=skip_above)
             self.update_step += 1
             self.schedule.step_count = self.update_step
@@ -273,26 +373,148 @@ class NVSTrainer:
                     return opt_sd
             path = checkpoint_job(self.out_dir, self.model, _Frozen(), self.schedule, self.fwdbwd_step,
                                   self.update_step)
-            delete_previous_job(self.out_dir, self.fwdbwd_step, int(tr.get("save_last_n_ckpts", 1)))
+            delete_previous_job(self.out_dir, self.fwdbwd_step, int(tr.get("save_last_n_ckpts", 3)))
         if self.world > 1:
             dist.barrier()
         return path
 
+    # ------------------------------------------------------------------ in-training evaluation and visuals
+    def _build_eval(self):
+        """(iterator factory, number of batches per evaluation).  Real data: ``eval_dataset_path`` with
+        ``eval_num_views`` views, epoch 0 of a sharded sampler every time; synthetic data: a fixed-seed stream."""
+        tr = self.cfg["training"]
+        bs = int(tr["batch_size_per_gpu"])
+        views = int(tr.get("eval_num_views", tr.get("num_views", 12)))
+        size = self.cfg["model"]["image_size"]
+        size = size if isinstance(size, int) else size[0]
+        steps = min(511 // bs // self.world + 1, 8)
+        if self.num_train_samples is None:
+            return (lambda: iter(SyntheticScenes(bs, views, size, seed=9595, rank=self.rank))), steps
+        path = self.cfg.get("eval_dataset_path")
+        if not path or str(path).startswith("PATH/TO/"):
+            raise ValueError("`eval_dataset_path` still holds its placeholder value. Point it at an evaluation "
+                             "manifest (python -m uttt_b200.nvs.manifests build ...), or switch the in-training "
+                             "evaluation off with `-s training.eval_every 0`.")
+        ds = NVSDataset(path, views, size)
+        available = len(ds) // self.world // bs
+        if available < 1:
+            raise ValueError(
+                f"In-training evaluation cannot run: {len(ds)} evaluation scenes split over {self.world} ranks at "
+                f"{bs} per rank leaves some ranks with no batch at all.\nDisable it with `-s training.eval_every 0` and "
+                f"evaluate separately with `python -m uttt_b200.nvs.eval.evaluate`, or run on at most "
+                f"{max(len(ds) // bs, 1)} ranks.")
+        sampler = ResumableDistributedSampler(ds, num_replicas=self.world, rank=self.rank, shuffle=True, seed=0,
+                                              drop_last=True)
+        loader = torch.utils.data.DataLoader(ds, batch_size=bs, sampler=sampler, drop_last=True,
+                                             num_workers=int(tr.get("num_workers", 0)),
+                                             pin_memory=torch.cuda.is_available())
+
+        def fresh():
+            sampler.set_epoch(0)
+            return iter(loader)
+        return fresh, max(min(steps, available), 1)
+
+    def _avg(self, t: torch.Tensor) -> torch.Tensor:
+        t = t.detach().float().clone()
+        if self.world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.SUM)
+            t /= self.world
+        return t
+
+    @torch.no_grad()
+    def evaluate(self) -> Dict[str, float]:
+        """Mean loss / PSNR / per-view PSNR / expert-frequency extrema over the evaluation batches and ranks; visuals
+        of the last batch in ``eval_<pass>/``."""
+        if self._eval_data is None:
+            self._eval_data = self._build_eval()
+        fresh, steps = self._eval_data
+        if self.rank == 0:
+            print(f"Evaluating at iter {self.fwdbwd_step} eval_steps {steps}", flush=True)
+        was_warm = self.model._l2_only
+        self.model.eval()
+        if self.device.type == "cuda":
+            torch.cuda.empty_cache()
+        it = fresh()
+        sums: Dict[str, torch.Tensor] = {}
+        result = batch = None
+        for _ in range(steps):
+            batch = {k: v.to(self.device, non_blocking=True) for k, v in next(it).items() if torch.is_tensor(v)}
+            result = self.model(batch)
+            for key in ("loss", "psnr", "psnr_loc", "moe_freq_max", "moe_freq_min"):
+                if key in result["loss_metrics"]:
+                    v = result["loss_metrics"][key].detach().float() / steps
+                    sums[key] = v if key not in sums else sums[key] + v
+        result["loss_metrics"]["psnr_loc"] = self._avg(result["loss_metrics"]["psnr_loc"])
+        images = None
+        if self.rank == 0:
+            images = self.model.save_visuals(os.path.join(self.out_dir, f"eval_{self.fwdbwd_step:08d}"), result, batch)
+        out: Dict[str, float] = {}
+        for key, v in sums.items():
+            v = self._avg(v)
+            if key.endswith("_loc"):
+                out.update({f"{key}_{i:03}": float(x) for i, x in enumerate(v)})
+            else:
+                out[key] = float(v)
+        payload = {**{f"eval/{k}": v for k, v in out.items() if "_loc_" not in k},
+                   **{f"eval_loc/{k}": v for k, v in out.items() if "_loc_" in k}}
+        self.metrics.log(payload, self.fwdbwd_step, {f"eval_{k}": v for k, v in (images or {}).items()})
+        if self.rank == 0:
+            print(f"eval/loss: {out['loss']}, eval/psnr: {out['psnr']} at iter {self.fwdbwd_step}", flush=True)
+        if self.world > 1:
+            dist.barrier()
+        self.model.train()
+        self.model.l2_warmup(was_warm)
+        return out
+
+    @torch.no_grad()
+    def _visuals(self, batch) -> None:
+        if self.rank == 0:
+            batch = {k: v.to(self.device, non_blocking=True) for k, v in batch.items() if torch.is_tensor(v)}
+            images = self.model.save_visuals(os.path.join(self.out_dir, f"iter_{self.fwdbwd_step:08d}"),
+                                             self.model(batch), batch)
+            self.metrics.log({}, self.fwdbwd_step, {f"train_{k}": v for k, v in images.items()})
+        if self.world > 1:
+            dist.barrier()
+
     def fit(self, max_passes: Optional[int] = None) -> Dict[str, float]:
         tr = self.cfg["training"]
         total = self.total if max_passes is None else min(self.total, self.fwdbwd_step + max_passes)
+        eval_every = int(tr.get("eval_every", 2000))
+        vis_every = int(tr.get("vis_every", 0) or 0)
+        log_every = int(tr.get("wandb_log_every", 50) or 50)
+        per_epoch = self.overview["num_fwdbwd_passes_per_epoch"]
+        t_start = time.time()
         while self.fwdbwd_step < total:
-            stats = self.train_pass(next(self.data))
-            if self.rank == 0 and self.fwdbwd_step % int(tr.get("print_every", 20)) == 0:
-                print(f"[pass {self.fwdbwd_step}] loss {float(stats['loss']):.5f} psnr {float(stats['psnr']):.2f} "
-                      f"lr {stats.get('lr', 0):.2e} time {self.step_times[-1]:.3f}s", flush=True)
-            if self.fwdbwd_step % int(tr.get("checkpoint_every", 500)) == 0 or self.fwdbwd_step == total:
+            batch = next(self.data)
+            stats = self.train_pass(batch)
+            step = self.fwdbwd_step
+            if self.rank == 0 and step % int(tr.get("print_every", 20)) == 0:
+                print(f"epoch: {(step - 1) // per_epoch}, fwdbwd_pass_step: {step}/{per_epoch}, "
+                      f"time: {self.step_times[-1]:06f}, param_update_step: {self.update_step}, "
+                      f"lr: {stats.get('lr', 0):06f}\n\tloss: {float(stats['loss']):06f}, "
+                      f"psnr: {float(stats['psnr']):06f}", flush=True)
+            if step % log_every == 0 or step < 100 + self.start_step:
+                payload = {"iter": step, "fwdbwd_pass_step": step, "param_update_step": self.update_step,
+                           "lr": float(stats.get("lr", 0.0)), "iter_time": self.step_times[-1],
+                           "epoch": (step - 1) // per_epoch, "train/loss": float(self._avg(stats["loss"])),
+                           "train/psnr": float(self._avg(stats["psnr"]))}
+                if "grad_norm" in stats:
+                    payload["grad_norm"] = float(stats["grad_norm"])
+                self.metrics.log(payload, step)
+            if step % int(tr.get("checkpoint_every", 500)) == 0 or step == total:
                 self.save()
-        summary = {"avg_step_time_s": sum(self.step_times) / max(len(self.step_times), 1),
+            if vis_every > 0 and step % vis_every == 0:
+                self._visuals(batch)
+            if eval_every > 0 and (step % eval_every == 0 or (bool(tr.get("eval_first_step", True))
+                                                              and step == self.start_step + 1)):
+                self.evaluate()
+        passes = max(len(self.step_times), 1)
+        summary = {"avg_step_time_s": sum(self.step_times) / passes,
                    "peak_allocated_gib": torch.cuda.max_memory_allocated() / 2 ** 30 if torch.cuda.is_available() else 0.0,
                    "peak_reserved_gib": torch.cuda.max_memory_reserved() / 2 ** 30 if torch.cuda.is_available() else 0.0}
         if self.rank == 0:
-            print("[TRAIN_SUMMARY] " + " ".join(f"{k}={v:.4f}" for k, v in summary.items()), flush=True)
+            print(f"[TRAIN_SUMMARY] steps={len(self.step_times)} total_time={time.time() - t_start:.1f}s "
+                  + " ".join(f"{k}={v:.4f}" for k, v in summary.items()), flush=True)
         return summary
 
 

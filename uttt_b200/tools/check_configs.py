@@ -79,6 +79,26 @@ def check_nvs_yaml(path: str) -> List[str]:
         errs.append(f"{path}: more active experts than experts")
     if tr["total_batch_size"] % (tr["batch_size_per_gpu"] * tr.get("grad_accum_steps", 1)):
         errs.append(f"{path}: total_batch_size is not reachable with batch_size_per_gpu x grad_accum_steps")
+    if not isinstance(cfg.get("exp_name"), str) or not cfg["exp_name"]:
+        errs.append(f"{path}: exp_name must be a non-empty string")
+    for key in ("total_batch_size", "batch_size_per_gpu", "num_views", "eval_num_views", "max_fwdbwd_passes",
+                "checkpoint_every"):
+        if key in tr and (type(tr[key]) is not int or tr[key] < 1):
+            errs.append(f"{path}: training.{key} must be a positive integer, got {tr[key]!r}")
+    if p.get("aggregate_write") and p.get("pool_mode", "shared") != "shared":
+        errs.append(f"{path}: aggregate_write requires a shared pool")
+    if not errs:
+        # the stack's constructor is the authority on its parameters: build it without allocating anything
+        import copy
+        import torch
+        from ..nvs.model import LVSMModel
+        probe = copy.deepcopy(cfg)
+        probe["training"].update(perceptual_loss_weight=0.0, lpips_loss_weight=0.0)   # their networks need weight files
+        try:
+            with torch.device("meta"):
+                LVSMModel(probe)
+        except Exception as exc:
+            errs.append(f"{path}: the model cannot be built: {type(exc).__name__}: {exc}")
     return errs
 
 

@@ -126,8 +126,8 @@ def nvs_yaml(name: str, block_type: str, params: Dict[str, Any], dim=512, layers
     tr = dict(total_batch_size=total, grad_accum_steps=1, grad_clip_norm=1.0, may_skip_gradnorm_after=1000,
               allowed_gradnorm_factor=5, dataset="synthetic", num_views=views, eval_num_views=24,
               batch_size_per_gpu=batch, num_workers=16, lpips_loss_weight=0.0, max_fwdbwd_passes=20000, lr=4e-4,
-              beta1=0.9, beta2=0.95, weight_decay=0.05, warmup=2500, print_every=20, checkpoint_every=500,
-              save_last_n_ckpts=1)
+              beta1=0.9, beta2=0.95, weight_decay=0.05, warmup=2500, vis_every=1000, print_every=20,
+              checkpoint_every=500, wandb_log_every=50, wandb_offline=False, prefetch_factor=4)
     tr.update(training)
     return {"exp_name": name, "model": {"class_name": "uttt_b200.nvs.model.LVSMModel", "image_size": size,
                                         "patch_size": 8, "dim": dim, "layers": layers,
