@@ -446,3 +446,81 @@ def test_trainer_refuses_what_the_reference_refuses(tmp_path):
     t = NVSTrainer(cfg, device=torch.device("cpu"))
     t.fit()
     assert os.path.isdir(os.path.join(t.out_dir, "eval_00000002")) and t.fwdbwd_step == 2
+
+
+def test_learning_rate_schedule_values():
+    """Against torch's LambdaLR with the multiplier written out: step k of the optimizer runs at lambda(k)."""
+    import math
+    from uttt_b200.nvs.trainer import lr_at
+
+    def expected(k, warmup, total, kind, init):
+        if warmup > 0 and k < warmup:
+            return init + (1 - init) * k / warmup
+        if kind == "constant" or total <= warmup:
+            return 1.0
+        if kind == "linear":
+            return max(0.0, (total - k) / max(1, total - warmup))
+        return 0.5 * (1 + math.cos(math.pi * min(max((k - warmup) / max(1, total - warmup), 0), 1)))
+
+    for kind in ("cosine", "linear", "constant"):
+        for init in (0.0, 0.25):
+            p = torch.nn.Parameter(torch.zeros(1))
+            opt = torch.optim.SGD([p], lr=2.0)
+            sched = torch.optim.lr_scheduler.LambdaLR(opt, lambda k, kind=kind, init=init: expected(k, 5, 20, kind, init))
+            for k in range(24):
+                assert lr_at(k, 2.0, 5, 20, kind, init) == pytest.approx(opt.param_groups[0]["lr"]), (kind, init, k)
+                opt.step()
+                sched.step()
+    assert lr_at(0, 1.0, 10, 100) == 0.0 and lr_at(10, 1.0, 10, 100) == 1.0 and lr_at(100, 1.0, 10, 100) == pytest.approx(0.0)
+    assert lr_at(3, 1.0, 0, 100, "constant") == 1.0
+    with pytest.raises(ValueError):
+        lr_at(0, 1.0, 1, 10, "step")
+
+
+def test_resume_from_a_checkpoint_in_the_reference_format(tmp_path):
+    """A checkpoint as the reference's trainer writes it: fp32 weights under DDP / compile prefixes, the state of a
+    ``torch.optim.AdamW`` with (rank >= 2 | rest) parameter groups, a ``LambdaLR`` state, the two counters."""
+    torch.manual_seed(0)
+    cfg = _cfg()
+    cfg["training"].update(out_dir=str(tmp_path / "run"), max_fwdbwd_passes=8)
+    src = LVSMModel(cfg)
+    named = list(src.named_parameters())
+    opt = torch.optim.AdamW([{"params": [p for _, p in named if p.dim() >= 2], "weight_decay": 0.05},
+                             {"params": [p for _, p in named if p.dim() < 2], "weight_decay": 0.0}], lr=1e-3)
+    sched = torch.optim.lr_scheduler.LambdaLR(opt, lambda k: 1.0)
+    for _ in range(3):
+        src(_batch())["loss_metrics"]["loss"].backward()
+        opt.step()
+        sched.step()
+        opt.zero_grad()
+    os.makedirs(tmp_path / "theirs")
+    path = str(tmp_path / "theirs" / "ckpt_0000000000000003.pt")
+    torch.save({"model": {"module._orig_mod." + k: v for k, v in src.state_dict().items()}, "optimizer": opt.state_dict(),
+                "lr_scheduler": sched.state_dict(), "fwdbwd_pass_step": 3, "param_update_step": 3}, path)
+    t = NVSTrainer(cfg, device=torch.device("cpu"), load=path)
+    assert (t.fwdbwd_step, t.update_step, t.schedule.step_count, t.trainer.step_count) == (3, 3, 3, 3)
+    ours = t.optimizer.state_dict()["state"]
+    theirs = opt.state_dict()["state"]
+    order = [n for n, p in named if p.dim() >= 2] + [n for n, p in named if p.dim() < 2]
+    assert set(ours) == set(order)
+    for idx, name in enumerate(order):
+        torch.testing.assert_close(ours[name]["exp_avg"], theirs[idx]["exp_avg"], msg=name)
+        torch.testing.assert_close(ours[name]["exp_avg_sq"], theirs[idx]["exp_avg_sq"], msg=name)
+        torch.testing.assert_close(ours[name]["master"], dict(named)[name].detach(), msg=name)     # fp32, not re-rounded
+    t.fit(max_passes=1)
+    assert t.fwdbwd_step == 4
+    # a state that does not fit this model is skipped with a warning; weights and counters still load
+    other = _cfg(num_experts=8)
+    other["training"].update(out_dir=str(tmp_path / "other"), max_fwdbwd_passes=8)
+    bad = torch.load(path, weights_only=False)
+    bad["optimizer"]["param_groups"][0]["params"] = bad["optimizer"]["param_groups"][0]["params"][:-1]
+    torch.save(bad, str(tmp_path / "theirs" / "ckpt_0000000000000004.pt"))
+    t2 = NVSTrainer(cfg | {"training": {**cfg["training"], "out_dir": str(tmp_path / "run2")}}, device=torch.device("cpu"),
+                    load=str(tmp_path / "theirs" / "ckpt_0000000000000004.pt"))
+    assert t2.fwdbwd_step == 3 and not t2.optimizer.loaded
+    # weights from elsewhere with a reset: counters start at zero; the run's own folder later wins over `load`
+    cfg3 = cfg | {"training": {**cfg["training"], "out_dir": str(tmp_path / "run3"), "reset_training_state": True}}
+    t3 = NVSTrainer(cfg3, device=torch.device("cpu"), load=path)
+    assert (t3.fwdbwd_step, t3.update_step) == (0, 0)
+    t3.fit(max_passes=2)
+    assert NVSTrainer(cfg3, device=torch.device("cpu"), load=path).fwdbwd_step == 2

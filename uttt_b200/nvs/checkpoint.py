@@ -90,20 +90,39 @@ def resume_job(load_path, model, optimizer, lr_scheduler, reset_training_state: 
         if not os.path.isfile(load_path):
             raise FileNotFoundError(f"Checkpoint does not exist: {load_path}")
         paths = [load_path]
-    last = None
+    blob, last = None, None
     for path in reversed(paths):
         try:
             blob = torch.load(path, map_location="cpu", weights_only=False)
-            target = getattr(model, "module", model)
-            state = {clean_key(k): v for k, v in blob["model"].items()}
-            target.load_state_dict(state, strict=False)
-            if reset_training_state:
-                if load_optimizer_state_when_reset_training_state:
-                    optimizer.load_state_dict(blob["optimizer"])
-                return optimizer, lr_scheduler, 0, 0
-            optimizer.load_state_dict(blob["optimizer"])
-            lr_scheduler.load_state_dict(blob["lr_scheduler"])
-            return optimizer, lr_scheduler, int(blob["fwdbwd_pass_step"]), int(blob["param_update_step"])
-        except Exception as exc:
+            break
+        except Exception as exc:                      # a truncated newest file: fall back to the one before it
             last = exc
-    raise RuntimeError(f"no readable checkpoint in {load_path}") from last
+            print(f"Failed to load {path} ({type(exc).__name__}); trying the next checkpoint in reverse order",
+                  flush=True)
+    if blob is None:
+        raise RuntimeError(f"Failed to load any checkpoint in {load_path}; all ckpt paths: {paths}") from last
+    target = getattr(model, "module", model)
+    state = {clean_key(k): v for k, v in blob["model"].items()}
+    target.load_state_dict(state, strict=False)
+
+    def load_optimizer() -> bool:
+        """A state that does not fit (another architecture, another layout) is skipped with a warning, as in
+        the reference: training continues with fresh moments."""
+        try:
+            try:
+                optimizer.load_state_dict(blob["optimizer"], model_state=state)
+            except TypeError:
+                optimizer.load_state_dict(blob["optimizer"])
+            return True
+        except (ValueError, KeyError) as exc:
+            print(f"[WARNING] Failed to load optimizer state dict (likely a parameter mismatch): {exc}\n"
+                  f"Skipping optimizer state restore.", flush=True)
+            return False
+
+    if reset_training_state:
+        if load_optimizer_state_when_reset_training_state:
+            load_optimizer()
+        return optimizer, lr_scheduler, 0, 0
+    load_optimizer()
+    lr_scheduler.load_state_dict(blob["lr_scheduler"])
+    return optimizer, lr_scheduler, int(blob["fwdbwd_pass_step"]), int(blob["param_update_step"])

@@ -154,27 +154,62 @@ class MetricsLog:
 
 
 def lr_at(step: int, base: float, warmup: int, total: int, kind: str = "cosine", init_ratio: float = 0.0) -> float:
-    if step < warmup:
-        return base * (init_ratio + (1 - init_ratio) * (step + 1) / max(warmup, 1))
-    if kind == "constant":
+    """Learning rate of optimizer step number ``step`` (0-based): linear warm-up from ``init_ratio x base`` over
+    ``warmup`` steps (so the very first step runs at ``init_ratio x base``, zero by default), then cosine / linear
+    decay to zero at ``total`` or constant (uttt_nvs/train/optimizer.py:53-112)."""
+    if kind not in ("cosine", "linear", "constant"):
+        raise ValueError(f"Not support LR scheduler type {kind}.")
+    if not 0.0 <= init_ratio <= 1.0:
+        raise ValueError("warmup_init_ratio must be in [0, 1].")
+    if warmup > 0 and step < warmup:
+        return base * (init_ratio + (1.0 - init_ratio) * step / max(warmup, 1))
+    if kind == "constant" or total <= warmup:
         return base
-    prog = min(max((step - warmup) / max(total - warmup, 1), 0.0), 1.0)
     if kind == "linear":
-        return base * (1 - prog)
-    return base * 0.5 * (1 + math.cos(math.pi * prog))
+        return base * max(0.0, (total - step) / max(total - warmup, 1))
+    prog = min(max((step - warmup) / max(total - warmup, 1), 0.0), 1.0)
+    return base * 0.5 * (1.0 + math.cos(math.pi * prog))
 
 
 class _OptimizerView:
-    """state_dict()/load_state_dict() adapters so the checkpoint file keeps the reference's top-level keys."""
+    """state_dict()/load_state_dict() adapters so the checkpoint file keeps the reference's top-level keys.
 
-    def __init__(self, trainer: ShardedTrainer):
-        self.trainer = trainer
+    Two layouts are read: this package's (fp32 master and moments by parameter name) and ``torch.optim.AdamW``'s as
+    the reference writes it (``state`` by index over two groups: parameters of rank >= 2 in ``named_parameters``
+    order, then the rest; uttt_nvs/train/optimizer.py:15-50).  From the latter the moments and the step count are
+    taken and the fp32 masters come from the checkpoint's own fp32 weights (``model_state``)."""
+
+    def __init__(self, trainer: ShardedTrainer, model: Optional[torch.nn.Module] = None):
+        self.trainer, self.model = trainer, model
         self.loaded = False          # True once fp32 masters and moments came from a checkpoint
 
     def state_dict(self):
         return self.trainer.optimizer_state_dict()
 
-    def load_state_dict(self, sd):
+    def _from_torch_adamw(self, sd, model_state):
+        named = [(n, p) for n, p in self.model.named_parameters() if p.requires_grad]
+        groups = [[n for n, p in named if p.dim() >= 2], [n for n, p in named if p.dim() < 2]]
+        if len(sd["param_groups"]) != 2 or [len(g["params"]) for g in sd["param_groups"]] != [len(g) for g in groups]:
+            raise ValueError("optimizer param groups do not match this model (decay: rank >= 2, no decay: the rest)")
+        shapes = dict((n, tuple(p.shape)) for n, p in named)
+        state, step = {}, 0
+        for group, names in zip(sd["param_groups"], groups):
+            for idx, name in zip(group["params"], names):
+                entry = sd["state"].get(idx)
+                if entry is None:
+                    continue
+                if tuple(entry["exp_avg"].shape) != shapes[name]:
+                    raise ValueError(f"optimizer state of {name} has shape {tuple(entry['exp_avg'].shape)}, "
+                                     f"expected {shapes[name]}")
+                state[name] = {"exp_avg": entry["exp_avg"].float(), "exp_avg_sq": entry["exp_avg_sq"].float()}
+                if model_state is not None and name in model_state:
+                    state[name]["master"] = model_state[name].float()
+                step = max(step, int(entry["step"]))
+        return {"step": step, "skipped_steps": 0, "state": state}
+
+    def load_state_dict(self, sd, model_state=None):
+        if "param_groups" in sd:
+            sd = self._from_torch_adamw(sd, model_state)
         self.trainer.load_optimizer_state_dict(sd)
         self.loaded = True
 
@@ -209,7 +244,7 @@ class NVSTrainer:
         units = [(f"transformer_blocks.blocks.{i}", b) for i, b in
                  enumerate(getattr(self.model.transformer_blocks, "blocks", []))]
         self.trainer = ShardedTrainer(self.model, units, opt, no_decay=lambda n, p: p.dim() < 2)
-        self.optimizer, self.schedule = _OptimizerView(self.trainer), _Schedule()
+        self.optimizer, self.schedule = _OptimizerView(self.trainer, self.model), _Schedule()
         self.out_dir = os.path.join(tr.get("out_dir", os.environ.get("UTTT_NVS_OUT_DIR", "experiments")),
                                     cfg.get("exp_name", "run"))
         self.fwdbwd_step = 0
