@@ -73,3 +73,48 @@ def test_fake_torchrun_receives_argv_and_exit_code_propagates(tmp_path):
     rc = subprocess.call(["bash", os.path.join(ROOT, "launch", "train_lm.sh"), job, model],
                          env=dict(env, NODE_SYNC="exit 3"), stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
     assert rc == 3 and not (tmp_path / "argv.txt").exists()
+
+
+def test_dataset_registry_is_forwarded_before_the_user_flags(tmp_path):
+    job, model, _ = _files(tmp_path)
+    reg = tmp_path / "datasets.yaml"
+    reg.write_text("train:\n  files: /data/shards/data-*.arrow\nptl:\n  files: /data/books/*.arrow\n")
+    env = {"NPROC_PER_NODE": "1", "UTTT_LM_DATASETS": str(reg)}
+    cmd, _ = build_command(["lm", job, model, "--training.data_files", "/mine/*.arrow"], env)
+    first = cmd.index("--training.data_files")
+    assert cmd[first + 1] == "/data/shards/data-*.arrow" and cmd[-2:] == ["--training.data_files", "/mine/*.arrow"]
+    reg.write_text("train:\n  files: PATH/TO/long-data-collections-arrow/data-*.arrow\n")
+    with pytest.raises(LaunchError, match="placeholder"):
+        build_command(["lm", job, model], env)
+    reg.write_text("train: {}\n")
+    with pytest.raises(LaunchError, match="train.files"):
+        build_command(["lm", job, model], env)
+    cmd, _ = build_command(["lm", job, model], {"NPROC_PER_NODE": "1", "UTTT_LM_DATASETS": str(tmp_path / "absent.yaml")})
+    assert "--training.data_files" not in cmd
+
+
+def test_view_synthesis_dataset_registry(tmp_path):
+    import yaml
+    from uttt_b200.nvs.trainer import resolve_datasets
+    reg = tmp_path / "datasets.yaml"
+    reg.write_text(yaml.safe_dump({"obj": {"train": "/m/train.txt", "eval": "/m/eval.txt"},
+                                   "dl3dv": {"train": "PATH/TO/dl3dv_train_manifest.txt", "eval": "/m/e.txt"}}))
+
+    def cfg(**tr):
+        return {"training": dict(tr)}
+
+    out = resolve_datasets(cfg(dataset="obj"), str(reg))
+    assert out["training"]["dataset_path"] == "/m/train.txt" and out["eval_dataset_path"] == "/m/eval.txt"
+    out = resolve_datasets(cfg(dataset="obj", dataset_path="/mine.txt"), str(reg))            # the configuration wins
+    assert out["training"]["dataset_path"] == "/mine.txt" and out["eval_dataset_path"] == "/m/eval.txt"
+    out = resolve_datasets(cfg(dataset="obj", dataset_path="PATH/TO/x.txt", dataset_registry=str(reg)))
+    assert out["training"]["dataset_path"] == "/m/train.txt"                                   # a placeholder does not
+    with pytest.raises(ValueError, match="placeholder"):
+        resolve_datasets(cfg(dataset="dl3dv"), str(reg))
+    with pytest.raises(KeyError, match="Available"):
+        resolve_datasets(cfg(dataset="re10k"), str(reg))
+    with pytest.raises(FileNotFoundError, match="datasets.example.yaml"):
+        resolve_datasets(cfg(dataset="obj"), str(tmp_path / "none.yaml"))
+    assert "dataset_path" not in resolve_datasets(cfg(dataset="synthetic"), str(tmp_path / "none.yaml"))["training"]
+    example = yaml.safe_load(open(os.path.join(ROOT, "configs", "nvs", "datasets.example.yaml")))
+    assert set(example) == {"obj", "dl3dv"} and all(set(v) == {"train", "eval"} for v in example.values())

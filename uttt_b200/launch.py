@@ -87,7 +87,21 @@ def build_command(argv: List[str], env: Dict[str, str]) -> Tuple[List[str], bool
             name, rest = rest[0], rest[1:]
         rdzv, _ = rendezvous_args(env, "uttt-llm")
         cmd = ["torchrun", *rdzv, "-m", "uttt_b200.train.lm_trainer", "--job.config_file", job, "--job.dump_folder",
-               f"runs/{name}", "--model.config", model, *rest]
+               f"runs/{name}", "--model.config", model]
+        registry = env.get("UTTT_LM_DATASETS", os.path.join(root, "configs", "lm", "datasets.yaml"))
+        if os.path.isfile(registry):
+            # a filled-in dataset registry names the training shards once for every job file; flags given on the
+            # command line come later and still win
+            import yaml
+            with open(registry, encoding="utf-8") as fh:
+                doc = yaml.safe_load(fh)
+            files = (doc.get("train") or {}).get("files") if isinstance(doc, dict) else None
+            if not isinstance(files, str) or not files.strip():
+                raise LaunchError(f"{registry} must contain a non-empty train.files string")
+            if files.startswith("PATH/TO/"):
+                raise LaunchError(f"train.files in {registry} still holds its placeholder value")
+            cmd += ["--training.data_files", files]
+        cmd += rest
     elif kind == "nvs":
         if len(rest) < 1:
             raise LaunchError("Expected <config.yaml>; use --help for usage.")

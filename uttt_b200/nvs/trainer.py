@@ -59,21 +59,51 @@ def apply_overrides(cfg: Dict[str, Any], pairs: List[List[str]]) -> Dict[str, An
     return cfg
 
 
+DATASET_REGISTRY = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "configs",
+                                "nvs", "datasets.yaml")
+
+
+def resolve_datasets(cfg: Dict[str, Any], registry_path: Optional[str] = None) -> Dict[str, Any]:
+    """``training.dataset: obj | dl3dv | ...`` selects a block ``{train: manifest, eval: manifest}`` of the dataset
+    registry (``training.dataset_registry``, default ``configs/nvs/datasets.yaml``, a filled-in copy of
+    ``datasets.example.yaml``).  A path written in the configuration wins over the registry; a registry that is
+    missing, lacks the block or still holds ``PATH/TO/`` placeholders is an error
+    (uttt_nvs/train/trainer.py:153-196).  ``dataset: synthetic`` (or none) needs no registry."""
+    tr = cfg.setdefault("training", {})
+    name = tr.get("dataset")
+    if not name or name == "synthetic":
+        return cfg
+    reg_path = registry_path or tr.get("dataset_registry") or DATASET_REGISTRY
+
+    def unset(v) -> bool:
+        return not v or str(v).startswith("PATH/TO/")
+
+    if not os.path.exists(reg_path):
+        if not unset(tr.get("dataset_path")):
+            return cfg                                # the configuration names its manifests itself
+        raise FileNotFoundError(f"Dataset registry '{reg_path}' not found. Copy configs/nvs/datasets.example.yaml to "
+                                f"configs/nvs/datasets.yaml and fill in your manifest paths, or set "
+                                f"training.dataset_path explicitly.")
+    with open(reg_path) as fh:
+        reg = yaml.safe_load(fh) or {}
+    if name not in reg:
+        raise KeyError(f"Dataset '{name}' is not defined in {reg_path}. Available: {sorted(reg)}")
+    for field, holder, key in (("train", tr, "dataset_path"), ("eval", cfg, "eval_dataset_path")):
+        value = (reg[name] or {}).get(field)
+        if not unset(holder.get(key)):
+            continue
+        if unset(value):
+            raise ValueError(f"`{name}.{field}` in {reg_path} still holds its placeholder value. Point it at a "
+                             f"manifest (python -m uttt_b200.nvs.manifests build ...).")
+        holder[key] = value
+    return cfg
+
+
 def load_config(path: str, overrides: Optional[List[List[str]]] = None, datasets_yaml: Optional[str] = None):
     with open(path) as fh:
         cfg = yaml.safe_load(fh)
     cfg = apply_overrides(cfg, overrides or [])
-    tr = cfg.setdefault("training", {})
-    name = tr.get("dataset")
-    if name and name != "synthetic" and "dataset_path" not in tr:
-        reg_path = datasets_yaml or os.path.join(os.path.dirname(os.path.dirname(path)), "datasets.yaml")
-        if os.path.exists(reg_path):
-            with open(reg_path) as fh:
-                reg = yaml.safe_load(fh) or {}
-            entry = reg.get(name, {})
-            tr.setdefault("dataset_path", entry.get("train"))
-            cfg.setdefault("eval_dataset_path", entry.get("eval"))
-    return cfg
+    return resolve_datasets(cfg, datasets_yaml)
 
 
 def check_batch_arithmetic(cfg: Dict[str, Any], world: int) -> int:

@@ -112,6 +112,8 @@ def check_all(root: str = ROOT) -> Tuple[int, List[str]]:
         errs += check_job_toml(path)
         n += 1
     for path in sorted(glob.glob(os.path.join(root, "nvs", "**", "*.yaml"), recursive=True)):
+        if os.path.basename(path).startswith("datasets."):          # dataset registries, not run configurations
+            continue
         if os.sep + "eval" + os.sep in path:
             errs += check_eval_registry(path)
         else:
@@ -138,6 +140,8 @@ def catalog(root: str = ROOT) -> str:
             c = load_config(path)
             extra = f", E={c.memory_num_experts} top-{c.memory_num_active_experts}" if hasattr(c, "memory_num_experts") else ""
             lines.append(f"| {rel} | lm:{c.model_type} | d={c.hidden_size} L={c.num_hidden_layers} chunk={c.chunk_size}{extra} |")
+        elif os.path.basename(path).startswith("datasets."):
+            lines.append(f"| {rel} | registry | dataset paths, to be copied to datasets.yaml and filled in |")
         elif path.endswith(".yaml") and os.sep + "eval" + os.sep in path:
             with open(path) as fh:
                 c = yaml.safe_load(fh)
