@@ -112,7 +112,7 @@ def check_all(root: str = ROOT) -> Tuple[int, List[str]]:
         errs += check_job_toml(path)
         n += 1
     for path in sorted(glob.glob(os.path.join(root, "nvs", "**", "*.yaml"), recursive=True)):
-        if os.path.basename(path).startswith("datasets."):          # dataset registries, not run configurations
+        if os.path.basename(path).startswith(("datasets.", "api_keys.")):   # registries / keys, not run configurations
             continue
         if os.sep + "eval" + os.sep in path:
             errs += check_eval_registry(path)
@@ -142,6 +142,8 @@ def catalog(root: str = ROOT) -> str:
             lines.append(f"| {rel} | lm:{c.model_type} | d={c.hidden_size} L={c.num_hidden_layers} chunk={c.chunk_size}{extra} |")
         elif os.path.basename(path).startswith("datasets."):
             lines.append(f"| {rel} | registry | dataset paths, to be copied to datasets.yaml and filled in |")
+        elif os.path.basename(path).startswith("api_keys."):
+            lines.append(f"| {rel} | keys | logging key, to be copied to api_keys.yaml and filled in |")
         elif path.endswith(".yaml") and os.sep + "eval" + os.sep in path:
             with open(path) as fh:
                 c = yaml.safe_load(fh)
