@@ -1,6 +1,7 @@
 import math
 import os
 
+import pytest
 import torch
 
 from uttt_b200.config import named_config
@@ -102,3 +103,46 @@ def test_validation_loss_and_offload_context_cpu():
         y = lin(x).relu().sum()
     y.backward()
     assert off.tensors_offloaded == 0 and x.grad is not None
+
+
+def test_ptl_job_file_interface_and_summary_tool(tmp_path, capsys):
+    """The job-file interface writes the flat per-position list under the reference's file name; the summary tool
+    reduces it with the published rule (NaN-aware mean from a 0-based first position) and the reference's keys."""
+    import json
+    import math
+    from uttt_b200.config import named_config
+    from uttt_b200.eval import ptl
+    from uttt_b200.models import build_model
+    from uttt_b200.train.checkpoint import export_hf
+    cfg = named_config("tiny-uttt-moe")
+    torch.manual_seed(0)
+    model = build_model(cfg)
+    export_hf(model, cfg, str(tmp_path / "hf"))
+    job = tmp_path / "eval.toml"
+    job.write_text('[job]\ndump_folder = "%s"\n[training]\nbatch_size = 1\nseq_len = 256\nsteps = 2\n'
+                   'dataset = "synthetic"\n[eval]\nper_token_loss_from_hidden = true\nlm_head_chunk_size = 64\n'
+                   % (tmp_path / "out"))
+    assert ptl.main(["--job.config_file", str(job), "--checkpoint.load_path", str(tmp_path / "hf"),
+                     "--training.save_prefix", "tiny"]) == 0
+    path = tmp_path / "out" / "tiny_loss_per_token_position.json"
+    data = json.loads(path.read_text())
+    assert isinstance(data, list) and len(data) == 256 and data[-1] is None and all(v > 0 for v in data[:-1])
+    capsys.readouterr()
+    assert ptl.main(["summarize", str(path), "--min-position", "200", "--expect-positions", "256", "--chunks", "4",
+                     "--output", str(tmp_path / "s.json")]) == 0
+    out = capsys.readouterr().out
+    assert "PTL(>= 200)" in out and "1 NaN position(s) skipped" in out and "blocks:" in out
+    s = json.loads((tmp_path / "s.json").read_text())[str(path)]
+    assert set(s) == {"positions", "min_position", "tail_positions", "tail_nan", "ptl", "mean_all", "chunk_means"}
+    assert s["positions"] == 256 and s["tail_positions"] == 56 and s["tail_nan"] == 1 and len(s["chunk_means"]) == 4
+    assert s["ptl"] == pytest.approx(sum(data[200:-1]) / 55)
+    assert s["chunk_means"][3] == pytest.approx(sum(data[192:-1]) / 63)
+    both = ptl.summarize_positions([1.0, math.nan, 3.0, 5.0], 1)
+    assert both["ptl"] == 4.0 and both["mean_all"] == 3.0 and both["tail_nan"] == 1
+    with pytest.raises(ValueError):
+        ptl.summarize_positions([1.0], 1)
+    (tmp_path / "bad.json").write_text('["a"]')
+    with pytest.raises(ValueError):
+        ptl.load_positions(tmp_path / "bad.json")
+    (tmp_path / "obj.json").write_text(json.dumps({"per_position_loss": [1.0, None], "count": [2, 0]}))
+    assert ptl.load_positions(tmp_path / "obj.json")[0] == 1.0
