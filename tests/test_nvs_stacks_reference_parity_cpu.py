@@ -217,3 +217,55 @@ def test_every_reference_configuration_builds_with_the_reference_state_dict_layo
         rel = os.path.relpath(path, REF)
         assert sorted(set(a) - set(b)) == [] and sorted(set(b) - set(a)) == [], rel
         assert a == b, rel
+
+
+@pytest.mark.parametrize("rel,shrink", [
+    ("dense/obj/uttt_dense_r2.yaml", dict(attn_head_dim=16, fw_head_dim=16)),
+    ("ownership/obj/ttt_dense.yaml", dict(attn_head_dim=16, fw_head_dim=16)),
+    ("reference/obj/gated_deltanet.yaml", dict(attn_head_dim=16, fw_num_heads=4)),
+    ("transformer/obj/transformer.yaml", dict(attn_head_dim=16)),
+], ids=["uttt-dense", "ttt-dense", "gated-deltanet", "transformer"])
+def test_whole_model_matches_the_reference(rel, shrink, monkeypatch):
+    """The reference's ``uttt_nvs.models.lvsm.Images2latent3D`` (rays, Plucker embedding, patch tokens, block stack,
+    decoder, loss) against this package's model from the same YAML file, shrunk to 2 layers of width 64 on 32 x 32
+    images: same state dict, same scenes, bf16 autocast.  ``torch.cross`` of a bf16 and an fp32 operand is promoted by
+    the CUDA autocast rules but not by the CPU ones, so the test promotes it."""
+    import copy
+    import yaml
+    _reference("transformer_block")
+    from easydict import EasyDict
+    from uttt_nvs.models.lvsm import Images2latent3D
+    from uttt_b200.nvs.data import SyntheticScenes
+    from uttt_b200.nvs.model import LVSMModel
+    cross = torch.cross
+    monkeypatch.setattr(torch, "cross", lambda a, b, dim=-1: cross(a.float(), b.float(), dim=dim))
+    with open(os.path.join(REF, "uttt_nvs", "configs", rel)) as fh:
+        cfg = yaml.safe_load(fh)
+    cfg["model"].update(dim=64, layers=2, image_size=32)
+    cfg["model"]["block_config"]["params"].update(shrink)
+    cfg["training"].update(num_views=4, lpips_loss_weight=0.0, perceptual_loss_weight=0.0)
+    torch.manual_seed(0)
+    ref = Images2latent3D(EasyDict(copy.deepcopy(cfg)))
+    ours = LVSMModel(copy.deepcopy(cfg))
+    res = ours.load_state_dict(ref.state_dict(), strict=True)
+    assert not res.missing_keys and not res.unexpected_keys
+    batch = next(SyntheticScenes(2, 4, 32, seed=3, rank=0, pin=False))
+    with torch.autocast("cpu", dtype=torch.bfloat16):
+        out_r = ref({k: v.clone() for k, v in batch.items()})
+        out_o = ours({k: v.clone() for k, v in batch.items()})
+    loss_r, loss_o = out_r["loss_metrics"]["loss"], out_o["loss_metrics"]["loss"]
+    assert abs(float(loss_o) - float(loss_r)) < 2e-3 * abs(float(loss_r))
+    assert out_o["rendering"].shape == out_r["rendering"].shape == (2, 3, 3, 32, 32)
+    assert (out_o["rendering"].float() - out_r["rendering"].float()).abs().mean() < 3e-3
+    torch.testing.assert_close(out_o["loss_metrics"]["psnr_loc"].float(), out_r["loss_metrics"]["psnr_loc"].float(),
+                               atol=2e-2, rtol=0)
+    torch.testing.assert_close(out_o["target"]["image"], out_r["target"]["image"])
+    torch.testing.assert_close(out_o["input"]["c2w"], out_r["input"]["c2w"])
+    loss_r.backward()
+    loss_o.backward()
+    g_r = ref.image_tokenizer[1].weight.grad.flatten().float()
+    g_o = ours.image_tokenizer[1].weight.grad.flatten().float()
+    assert torch.nn.functional.cosine_similarity(g_o, g_r, dim=0) > 0.99
+    g_r = ref.image_token_decoder[1].weight.grad.flatten().float()
+    g_o = ours.image_token_decoder[1].weight.grad.flatten().float()
+    assert torch.nn.functional.cosine_similarity(g_o, g_r, dim=0) > 0.999
