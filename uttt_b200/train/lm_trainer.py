@@ -164,9 +164,11 @@ def main(job: Optional[JobConfig] = None) -> TrainState:
         return TrainState()
     accum = job.training.gradient_accumulation_steps
     if getattr(model_cfg, "memory_lb_mode", None) == "loss_free" and accum > 1:
-        # one bias update per optimizer step: the interval counts forwards
+        # one bias update per optimizer step: interval and warm-up are given in optimizer steps and count forwards
+        # (uttt_llm/flame/train.py:282-292)
         model_cfg = model_cfg.replace(
-            memory_loss_free_update_interval=model_cfg.memory_loss_free_update_interval * accum)
+            memory_loss_free_update_interval=model_cfg.memory_loss_free_update_interval * accum,
+            memory_loss_free_warmup_steps=int(getattr(model_cfg, "memory_loss_free_warmup_steps", 0)) * accum)
     ecfg = EngineConfig(micro_batch_size=job.training.micro_batch_size or job.training.batch_size,
                         lr=job.optimizer.lr, eps=job.optimizer.eps, beta1=job.optimizer.beta1, beta2=job.optimizer.beta2,
                         weight_decay=job.optimizer.weight_decay, max_norm=job.training.max_norm,
