@@ -365,7 +365,16 @@ def main() -> None:
     for fname, doc in eval_registries().items():
         os.makedirs(os.path.join(ROOT, "nvs", "eval"), exist_ok=True)
         with open(os.path.join(ROOT, "nvs", "eval", fname), "w") as fh:
-            yaml.safe_dump(doc, fh, sort_keys=False)
+            # one table row per dataset / experiment: easier to scan and to diff than a block per entry
+            fh.write("# Evaluation registry (layout: uttt_b200/nvs/eval/registry.py).  Generated by "
+                     "uttt_b200/tools/make_configs.py.\n")
+            head = {k: v for k, v in doc.items() if k not in ("datasets", "experiments")}
+            fh.write(yaml.safe_dump(head, sort_keys=False))
+            for key in ("datasets", "experiments"):
+                fh.write(f"{key}:\n")
+                for row in doc[key]:
+                    line = yaml.safe_dump(row, default_flow_style=True, sort_keys=False, width=10 ** 6).strip()
+                    fh.write(f"  - {line}\n")
     print(f"wrote configs under {ROOT}")
 
 
