@@ -524,3 +524,32 @@ def test_resume_from_a_checkpoint_in_the_reference_format(tmp_path):
     assert (t3.fwdbwd_step, t3.update_step) == (0, 0)
     t3.fit(max_passes=2)
     assert NVSTrainer(cfg3, device=torch.device("cpu"), load=path).fwdbwd_step == 2
+
+
+@pytest.mark.parametrize("block,params", [
+    ("uttt_nvs.models.uttt_dense_block.MemoryModel",
+     dict(only=dict(attn_head_dim=32, fw_head_dim=16, inter_multi=2, fw_inter_multi=2, l2_norm=True, use_muon=False,
+                    aggregate_write=True))),
+    ("uttt_nvs.models.ttt_dense_block.MemoryModel",
+     dict(only=dict(attn_head_dim=32, fw_head_dim=16, inter_multi=2, fw_inter_multi=1, l2_norm=True, use_muon=True))),
+    ("uttt_nvs.models.uttt_moe_partitioned.MemoryModel", dict(num_shared_pools=2, router_share_mode="share_pool")),
+    ("uttt_nvs.models.uttt_moe_partitioned.MemoryModel", dict(num_shared_pools=2)),
+    ("uttt_nvs.models.transformer_block.MemoryModel", dict(only=dict(attn_head_dim=32, transformer_version="v1"))),
+    ("uttt_nvs.models.gated_deltanet_block.MemoryModel",
+     dict(only=dict(attn_head_dim=32, fw_num_heads=2, repeat_function="repeat"))),
+])
+def test_every_stack_trains_through_the_sharded_optimizer_and_resumes(tmp_path, block, params):
+    """Flat-buffer optimizer units per block (also where blocks are shared with unregistered runners or a projection
+    is registered under two names), every parameter moves, and a resumed trainer holds the same weights."""
+    cfg = _cfg(block, **params)
+    cfg["training"].update(out_dir=str(tmp_path), max_fwdbwd_passes=3, eval_every=0, checkpoint_every=100)
+    t = NVSTrainer(cfg, device=torch.device("cpu"))
+    before = {n: p.detach().clone() for n, p in t.model.named_parameters()}
+    for _ in range(3):
+        assert torch.isfinite(t.train_pass(next(t.data))["loss"])
+    assert all((p.detach() - before[n]).abs().max() > 0 for n, p in t.model.named_parameters())
+    t.save()
+    t2 = NVSTrainer(cfg, device=torch.device("cpu"))
+    assert t2.fwdbwd_step == 3
+    for (k, a), b in zip(t.model.state_dict().items(), t2.model.state_dict().values()):
+        assert torch.equal(a, b), k
