@@ -291,3 +291,13 @@ def test_frozen_views_round_trip_and_guard_against_drift(tmp_path):
     assert len(views.build_view_manifest(str(dup), num_views=4, unique=True)["scenes"]) == 1
     with pytest.raises(views.ViewManifestError, match="local"):
         views.build_view_manifest("s3://bucket/manifest.txt")
+
+
+def test_views_are_redrawn_every_time_a_scene_comes_up(tmp_path):
+    cam = _write_scene(tmp_path, "s", n_frames=12, size=(8, 8))
+    ds = NVSDataset(str(_manifest(tmp_path, [cam])), num_views=4, image_size=8)
+    draws = {tuple(ds[0]["index"][:, 0].tolist()) for _ in range(6)}
+    assert len(draws) > 1
+    loader = torch.utils.data.DataLoader(ds, batch_size=1, num_workers=2)
+    epochs = [tuple(next(iter(loader))["index"][0, :, 0].tolist()) for _ in range(4)]
+    assert len(set(epochs)) > 1                               # worker copies start afresh each epoch, their seeds do not

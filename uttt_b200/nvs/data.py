@@ -201,7 +201,10 @@ class NVSDataset(Dataset):
 
     def __getitem__(self, idx: int):
         failures = 0
-        rng = random.Random((self.seed, idx).__hash__())
+        # a fresh draw of views every time a scene comes up: the stream depends on the dataset seed, the loader's
+        # per-epoch worker seed and the number of samples this copy of the dataset has served
+        self._served = getattr(self, "_served", 0) + 1
+        rng = random.Random(hash((self.seed, torch.initial_seed(), idx, self._served)))
         while True:
             try:
                 n_frames = len(manifests.read_frames(self.scenes[idx]))
