@@ -298,8 +298,8 @@ def test_checkpoint_grouping_and_sweep_do_not_change_the_numbers():
         LVSMModel(_cfg(apply_ckpt_group=3))
     with pytest.raises(ValueError):
         LVSMModel(_cfg(aggregate_write=False, offload_master_states=True))
-    with pytest.raises(NotImplementedError):
-        LVSMModel(_cfg(use_shared_expert=True))
+    with pytest.raises(ValueError, match="shared_expert_per_layer"):
+        LVSMModel(_cfg(use_shared_expert=True))               # aggregated write + one expert for the whole stack
 
 
 def test_shared_expert_raw_gradient_is_the_squared_error_gradient():
@@ -344,10 +344,15 @@ def test_view_synthesis_with_per_layer_shared_expert(aggregate):
     for name in ("w0", "w1", "w2"):
         for p in getattr(model.transformer_blocks, f"shared_expert_{name}_list"):
             assert p.grad is not None and float(p.grad.abs().max()) > 0
-    with pytest.raises(NotImplementedError):
-        params2 = dict(params, shared_expert_per_layer=False)
-        LVSMModel({"model": {**cfg["model"], "block_config": {"type": cfg["model"]["block_config"]["type"],
-                                                              "params": params2}}, "training": cfg["training"]})
+    # one expert for the whole stack works with chained writes only (an aggregated write has no order of layers)
+    params2 = dict(params, shared_expert_per_layer=False)
+    cfg2 = {"model": {**cfg["model"], "block_config": {"type": cfg["model"]["block_config"]["type"], "params": params2}},
+            "training": cfg["training"]}
+    if aggregate:
+        with pytest.raises(ValueError, match="shared_expert_per_layer"):
+            LVSMModel(cfg2)
+    else:
+        assert "transformer_blocks.shared_expert_w0" in LVSMModel(cfg2).state_dict()
 
 
 def test_partitioned_pool_layout_and_rebinding():
@@ -553,3 +558,46 @@ def test_every_stack_trains_through_the_sharded_optimizer_and_resumes(tmp_path, 
     assert t2.fwdbwd_step == 3
     for (k, a), b in zip(t.model.state_dict().items(), t2.model.state_dict().values()):
         assert torch.equal(a, b), k
+
+
+def test_one_always_on_expert_for_the_whole_stack():
+    """``use_shared_expert`` without ``shared_expert_per_layer`` on a shared pool: a single expert (``shared_expert_w0/1/2``)
+    that every layer reads and, with chained writes, updates in turn."""
+    base = dict(use_shared_expert=True, aggregate_write=False)
+    one = LVSMModel(_cfg(**base))
+    keys = set(one.state_dict())
+    assert {"transformer_blocks.shared_expert_w0", "transformer_blocks.shared_expert_w1",
+            "transformer_blocks.shared_expert_w2"} <= keys and not any("shared_expert_w0_list" in k for k in keys)
+    out = one(_batch())
+    out["loss_metrics"]["loss"].backward()
+    for name in ("shared_expert_w0", "shared_expert_w1", "shared_expert_w2"):
+        g = getattr(one.transformer_blocks, name).grad
+        assert g is not None and torch.isfinite(g).all() and g.abs().sum() > 0
+    # with a single layer it is the per-layer expert
+    cfg1 = _cfg(**base)
+    cfg1["model"]["layers"] = 1
+    cfg2 = _cfg(shared_expert_per_layer=True, **base)
+    cfg2["model"]["layers"] = 1
+    a, b = LVSMModel(cfg1), LVSMModel(cfg2)
+    sd = {k.replace("shared_expert_w0", "shared_expert_w0_list.0").replace("shared_expert_w1", "shared_expert_w1_list.0")
+          .replace("shared_expert_w2", "shared_expert_w2_list.0"): v for k, v in a.state_dict().items()}
+    b.load_state_dict(sd)
+    batch = _batch()
+    with torch.no_grad():
+        torch.testing.assert_close(a(batch)["rendering"], b(batch)["rendering"])
+    # with two layers the second layer reads what the first one wrote: not the per-layer result
+    c, d = LVSMModel(_cfg(**base)), LVSMModel(_cfg(shared_expert_per_layer=True, **base))
+    sd = {}
+    for k, v in c.state_dict().items():
+        if "shared_expert_w" in k:
+            for layer in range(2):
+                sd[f"{k}_list.{layer}"] = v
+        else:
+            sd[k] = v
+    d.load_state_dict(sd)
+    with torch.no_grad():
+        assert (c(batch)["rendering"] - d(batch)["rendering"]).abs().max() > 1e-7
+    with pytest.raises(ValueError, match="shared_expert_per_layer"):
+        LVSMModel(_cfg(use_shared_expert=True, aggregate_write=True))
+    with pytest.raises(NotImplementedError):
+        LVSMModel(_cfg("uttt_nvs.models.uttt_moe_partitioned.MemoryModel", num_shared_pools=2, **base))

@@ -262,21 +262,29 @@ class MemoryModel(nn.Module):
         else:
             self.shared_router_proj_weights = nn.Parameter(torch.randn(1, num_experts, head_dim) / math.sqrt(head_dim))
         self.use_shared_expert = bool(use_shared_expert)
+        # the always-on expert beside the routed pool (uttt_moe_block.py:922-960): one per layer with
+        # ``shared_expert_per_layer`` or with per-block pools, otherwise a single one that every layer reads and
+        # writes in turn (``shared_expert_w0/1/2``)
+        self.shared_expert_is_per_layer = self.use_shared_expert and (bool(shared_expert_per_layer)
+                                                                      or pool_mode == "per_block")
         if self.use_shared_expert:
-            # one always-on expert per layer beside the routed pool (uttt_moe_block.py:922-960)
-            if not (shared_expert_per_layer or pool_mode == "per_block"):
-                raise NotImplementedError("use_shared_expert needs shared_expert_per_layer=True (or pool_mode="
-                                          "'per_block'): one always-on expert shared by all layers is not built")
             if int(apply_ckpt_group) > 1:
                 raise NotImplementedError("apply_ckpt_group > 1 with use_shared_expert is not implemented "
                                           "(the reference rejects it too)")
+            if aggregate_write and not self.shared_expert_is_per_layer:
+                raise ValueError("aggregate_write=True requires shared_expert_per_layer=True when "
+                                 "use_shared_expert=True.")
 
-            def se(n_out, n_in, fan):
-                return nn.ParameterList([nn.Parameter(torch.randn(1, 1, n_out, n_in) / math.sqrt(fan))
-                                         for _ in range(layers)])
-            self.shared_expert_w0_list = se(inter, head_dim, head_dim)
-            self.shared_expert_w1_list = se(head_dim, inter, inter)
-            self.shared_expert_w2_list = se(inter, head_dim, head_dim)
+            def se_param(n_out, n_in, fan):
+                return nn.Parameter(torch.randn(1, 1, n_out, n_in) / math.sqrt(fan))
+            if self.shared_expert_is_per_layer:
+                self.shared_expert_w0_list = nn.ParameterList([se_param(inter, head_dim, head_dim) for _ in range(layers)])
+                self.shared_expert_w1_list = nn.ParameterList([se_param(head_dim, inter, inter) for _ in range(layers)])
+                self.shared_expert_w2_list = nn.ParameterList([se_param(inter, head_dim, head_dim) for _ in range(layers)])
+            else:
+                self.shared_expert_w0 = se_param(inter, head_dim, head_dim)
+                self.shared_expert_w1 = se_param(head_dim, inter, inter)
+                self.shared_expert_w2 = se_param(inter, head_dim, head_dim)
         self.blocks = nn.ModuleList([
             MemoryBlock(dim=dim, num_experts=num_experts, fw_head_dim=fw_head_dim, fw_inter_multi=fw_inter_multi,
                         use_shared_expert=use_shared_expert, **kwargs) for _ in range(layers)])
@@ -318,9 +326,14 @@ class MemoryModel(nn.Module):
                 for i in range(len(self.blocks))]
 
     def init_shared_experts(self, batch: int, dtype):
-        """Per layer (fast, masters) of the always-on expert, or None."""
+        """Per layer (fast, masters) of the always-on expert, or None.  With a single expert for the whole stack every
+        entry is the same pair."""
         if not self.use_shared_expert:
             return None
+        if not self.shared_expert_is_per_layer:
+            masters = tuple(p.float().repeat(batch, 1, 1, 1) for p in
+                            (self.shared_expert_w0, self.shared_expert_w1, self.shared_expert_w2))
+            return [(_unit_rows(masters, dtype), masters)] * len(self.blocks)
         out = []
         for i in range(len(self.blocks)):
             masters = tuple(p[i].float().repeat(batch, 1, 1, 1) for p in
@@ -494,6 +507,8 @@ def _write_with_shared_experts(self, states, mem_ins, pre_vs, keep, dt, se_state
         ps.append(p)
         cs.append(c)
         se_states[i] = apply_shared_expert_update((d0, d1, d2), se_states[i][1], use_muon, dt)
+        if not self.shared_expert_is_per_layer:
+            se_states[:] = [se_states[i]] * n                    # one expert for the stack: the next layer sees this write
         if shared and self.aggregate_write:
             a02, a1 = (g02, g1) if a02 is None else (a02 + g02, a1 + g1)
         else:
@@ -548,6 +563,9 @@ class PartitionedMemoryModel(nn.Module):
             self.shared_router_proj_weights = runners[0].shared_router_proj_weights
             for r in runners[1:]:
                 r.shared_router_proj_weights = self.shared_router_proj_weights
+        if runners[0].use_shared_expert and not runners[0].shared_expert_is_per_layer:
+            raise NotImplementedError("one always-on expert for all pools is not built for the partitioned stack (the "
+                                      "groups run one after the other); use shared_expert_per_layer=True")
         if runners[0].use_shared_expert:
             for name in ("shared_expert_w0_list", "shared_expert_w1_list", "shared_expert_w2_list"):
                 setattr(self, name, nn.ParameterList([p for r in runners for p in getattr(r, name)]))
