@@ -504,7 +504,7 @@ def test_resume_from_a_checkpoint_in_the_reference_format(tmp_path):
                 "lr_scheduler": sched.state_dict(), "fwdbwd_pass_step": 3, "param_update_step": 3}, path)
     t = NVSTrainer(cfg, device=torch.device("cpu"), load=path)
     assert (t.fwdbwd_step, t.update_step, t.schedule.step_count, t.trainer.step_count) == (3, 3, 3, 3)
-    ours = t.optimizer.state_dict()["state"]
+    ours = t.trainer.optimizer_state_dict()["state"]
     theirs = opt.state_dict()["state"]
     order = [n for n, p in named if p.dim() >= 2] + [n for n, p in named if p.dim() < 2]
     assert set(ours) == set(order)
@@ -514,6 +514,25 @@ def test_resume_from_a_checkpoint_in_the_reference_format(tmp_path):
         torch.testing.assert_close(ours[name]["master"], dict(named)[name].detach(), msg=name)     # fp32, not re-rounded
     t.fit(max_passes=1)
     assert t.fwdbwd_step == 4
+    # and back: what this trainer writes loads into torch's AdamW / LambdaLR the way the reference's resume does it
+    blob = torch.load(t.save(), weights_only=False)
+    assert blob["optimizer"]["param_groups"][0]["lr"] > 0 and blob["fwdbwd_pass_step"] == 4
+    assert all(v.dtype == torch.float32 for k, v in blob["model"].items() if v.is_floating_point())
+    dst = LVSMModel(cfg)
+    assert not dst.load_state_dict(blob["model"], strict=True).missing_keys
+    named2 = list(dst.named_parameters())
+    opt2 = torch.optim.AdamW([{"params": [p for _, p in named2 if p.dim() >= 2], "weight_decay": 0.05},
+                              {"params": [p for _, p in named2 if p.dim() < 2], "weight_decay": 0.0}], lr=1e-3)
+    sched2 = torch.optim.lr_scheduler.LambdaLR(opt2, lambda k: 1.0)
+    opt2.load_state_dict(blob["optimizer"])
+    sched2.load_state_dict(blob["lr_scheduler"])
+    assert sched2.last_epoch == 4 and opt2.param_groups[1]["weight_decay"] == 0.0
+    inner = t.trainer.optimizer_state_dict()["state"]
+    for idx, name in enumerate(order):
+        st = opt2.state[dict(named2)[name]]
+        assert float(st["step"]) == 4.0
+        torch.testing.assert_close(st["exp_avg"], inner[name]["exp_avg"], msg=name)
+        torch.testing.assert_close(dict(named2)[name].detach(), inner[name]["master"], msg=name)
     # a state that does not fit this model is skipped with a warning; weights and counters still load
     other = _cfg(num_experts=8)
     other["training"].update(out_dir=str(tmp_path / "other"), max_fwdbwd_passes=8)

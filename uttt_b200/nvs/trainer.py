@@ -213,8 +213,34 @@ class _OptimizerView:
         self.trainer, self.model = trainer, model
         self.loaded = False          # True once fp32 masters and moments came from a checkpoint
 
+    def _groups(self):
+        named = [(n, p) for n, p in self.model.named_parameters() if p.requires_grad]
+        return [[n for n, p in named if p.dim() >= 2], [n for n, p in named if p.dim() < 2]]
+
     def state_dict(self):
-        return self.trainer.optimizer_state_dict()
+        """The moments in ``torch.optim.AdamW``'s layout (what the reference's trainer writes and reads), so that a
+        run can move between the two implementations in either direction.  ``self.masters`` afterwards holds the
+        fp32 weights by name: the checkpoint stores those as the model's values."""
+        own = self.trainer.optimizer_state_dict()
+        cfg = self.trainer.opt
+        self.masters = {n: st["master"] for n, st in own["state"].items() if "master" in st}
+        if self.model is None:
+            return own
+        state, groups, idx = {}, [], 0
+        step = torch.tensor(float(own["step"]))
+        for names, decay in zip(self._groups(), (float(cfg.weight_decay), 0.0)):
+            ids = []
+            for name in names:
+                st = own["state"].get(name)
+                if st is not None and "exp_avg" in st:
+                    state[idx] = {"step": step.clone(), "exp_avg": st["exp_avg"], "exp_avg_sq": st["exp_avg_sq"]}
+                ids.append(idx)
+                idx += 1
+            groups.append({"lr": float(getattr(self, "last_lr", cfg.lr)), "initial_lr": float(cfg.lr),
+                           "betas": (float(cfg.beta1), float(cfg.beta2)), "eps": float(cfg.eps), "weight_decay": decay,
+                           "amsgrad": False, "maximize": False, "foreach": None, "capturable": False,
+                           "differentiable": False, "fused": None, "params": ids})
+        return {"state": state, "param_groups": groups, "skipped_steps": own.get("skipped_steps", 0)}
 
     def _from_torch_adamw(self, sd, model_state):
         named = [(n, p) for n, p in self.model.named_parameters() if p.requires_grad]
@@ -235,7 +261,7 @@ class _OptimizerView:
                 if model_state is not None and name in model_state:
                     state[name]["master"] = model_state[name].float()
                 step = max(step, int(entry["step"]))
-        return {"step": step, "skipped_steps": 0, "state": state}
+        return {"step": step, "skipped_steps": int(sd.get("skipped_steps", 0)), "state": state}
 
     def load_state_dict(self, sd, model_state=None):
         if "param_groups" in sd:
@@ -245,11 +271,15 @@ class _OptimizerView:
 
 
 class _Schedule:
-    def __init__(self):
-        self.step_count = 0
+    """Counter of optimizer steps, stored with the keys of a ``torch.optim.lr_scheduler.LambdaLR`` state."""
+
+    def __init__(self, base_lr: float = 0.0):
+        self.step_count, self.base_lr, self.last_lr = 0, base_lr, base_lr
 
     def state_dict(self):
-        return {"step_count": self.step_count}
+        return {"base_lrs": [self.base_lr, self.base_lr], "last_epoch": self.step_count,
+                "_step_count": self.step_count + 1, "_last_lr": [self.last_lr, self.last_lr],
+                "_get_lr_called_within_step": False, "lr_lambdas": [None, None], "step_count": self.step_count}
 
     def load_state_dict(self, sd):
         self.step_count = int(sd.get("step_count", sd.get("last_epoch", 0)))
@@ -274,7 +304,7 @@ class NVSTrainer:
         units = [(f"transformer_blocks.blocks.{i}", b) for i, b in
                  enumerate(getattr(self.model.transformer_blocks, "blocks", []))]
         self.trainer = ShardedTrainer(self.model, units, opt, no_decay=lambda n, p: p.dim() < 2)
-        self.optimizer, self.schedule = _OptimizerView(self.trainer, self.model), _Schedule()
+        self.optimizer, self.schedule = _OptimizerView(self.trainer, self.model), _Schedule(float(tr.get("lr", 4e-4)))
         self.out_dir = os.path.join(tr.get("out_dir", os.environ.get("UTTT_NVS_OUT_DIR", "experiments")),
                                     cfg.get("exp_name", "run"))
         self.fwdbwd_step = 0
@@ -373,6 +403,7 @@ class NVSTrainer:
             out = self.trainer.step(lr=lr, skip_above=skip_above)
             self.update_step += 1
             self.schedule.step_count = self.update_step
+            self.schedule.last_lr = self.optimizer.last_lr = lr
             stats.update(grad_norm=out["grad_norm"], skipped=out["skipped"], lr=lr)
         self.step_times.append(time.time() - t0)
         return stats
@@ -429,14 +460,24 @@ class NVSTrainer:
             torch.cuda.empty_cache()
 
     def save(self) -> Optional[str]:
+        """``ckpt_<pass:016>.pt`` in the reference's format: fp32 weights under the model's parameter names, the
+        moments as a ``torch.optim.AdamW`` state over (rank >= 2 | rest) groups, a ``LambdaLR``-style schedule state
+        and the two counters."""
         tr = self.cfg["training"]
         opt_sd = self.optimizer.state_dict()          # collective
+        masters = getattr(self.optimizer, "masters", {})
         path = None
         if self.rank == 0:
             class _Frozen:
                 def state_dict(_self):
                     return opt_sd
-            path = checkpoint_job(self.out_dir, self.model, _Frozen(), self.schedule, self.fwdbwd_step,
+
+            class _FullPrecision:
+                """The model's state with the optimizer's fp32 masters in place of the bf16 compute copies."""
+                def state_dict(_self):
+                    sd = self.model.state_dict()
+                    return {k: (masters[k].reshape(v.shape) if k in masters else v) for k, v in sd.items()}
+            path = checkpoint_job(self.out_dir, _FullPrecision(), _Frozen(), self.schedule, self.fwdbwd_step,
                                   self.update_step)
             delete_previous_job(self.out_dir, self.fwdbwd_step, int(tr.get("save_last_n_ckpts", 3)))
         if self.world > 1:
