@@ -620,3 +620,25 @@ def test_one_always_on_expert_for_the_whole_stack():
         LVSMModel(_cfg(use_shared_expert=True, aggregate_write=True))
     with pytest.raises(NotImplementedError):
         LVSMModel(_cfg("uttt_nvs.models.uttt_moe_partitioned.MemoryModel", num_shared_pools=2, **base))
+
+
+def test_overrides_aliases_and_command_line(tmp_path, monkeypatch):
+    from uttt_b200.nvs.trainer import apply_overrides, main
+    cfg = {"model": {"block_config": [{"params": {"a": 1}}, {"params": {}}]}, "training": {}}
+    apply_overrides(cfg, [["block1.num_experts", "8"], ["block0.a", "2"], ["training.lr", "3e-4"],
+                          ["training.tags", "['x', 'y']"], ["exp_name", "name"]])
+    assert cfg["model"]["block_config"][1]["params"]["num_experts"] == 8 and cfg["model"]["block_config"][0]["params"]["a"] == 2
+    assert cfg["training"] == {"lr": 3e-4, "tags": ["x", "y"]} and cfg["exp_name"] == "name"
+    import yaml
+    run = _cfg()
+    run["training"].update(out_dir=str(tmp_path / "from_file"), max_fwdbwd_passes=5, eval_every=2)
+    path = tmp_path / "run.yaml"
+    path.write_text(yaml.safe_dump(run))
+    monkeypatch.setenv("UTTT_NVS_OUT_DIR", str(tmp_path / "from_env"))          # wins over training.out_dir
+    main([str(path), "--debug", "--seed", "7", "-s", "block.num_experts", "2", "-s", "block.num_active_experts", "1"])
+    out = tmp_path / "from_env" / "t"
+    assert sorted(p for p in os.listdir(out) if p.startswith(("ckpt", "eval"))) == ["ckpt_0000000000000001.pt",
+                                                                                  "eval_00000001"]
+    assert not (tmp_path / "from_file").exists()
+    blob = torch.load(out / "ckpt_0000000000000001.pt", weights_only=False)
+    assert blob["model"]["transformer_blocks.pool_w0"].shape[1] == 2

@@ -39,7 +39,8 @@ from .checkpoint import checkpoint_job, delete_previous_job, resume_job, select_
 from .data import NVSDataset, ResumableDistributedSampler, SyntheticScenes
 from .model import LVSMModel, get_obj_by_name
 
-ALIASES = {"block.": "model.block_config.params."}
+ALIASES = {"block.": "model.block_config.params.", "block0.": "model.block_config.0.params.",
+           "block1.": "model.block_config.1.params.", "block2.": "model.block_config.2.params."}
 
 
 def apply_overrides(cfg: Dict[str, Any], pairs: List[List[str]]) -> Dict[str, Any]:
@@ -52,9 +53,11 @@ def apply_overrides(cfg: Dict[str, Any], pairs: List[List[str]]) -> Dict[str, An
         except (ValueError, SyntaxError):
             value = raw
         node = cfg
-        parts = key.split(".")
+        parts = [int(p) if p.lstrip("-").isdigit() else p for p in key.split(".")]     # integers index lists
         for p in parts[:-1]:
-            node = node.setdefault(p, {})
+            if isinstance(node, dict) and p not in node:
+                node[p] = {}
+            node = node[p]
         node[parts[-1]] = value
     return cfg
 
@@ -295,9 +298,12 @@ class NVSTrainer:
         if cfg["model"].get("act_ckpt"):
             raise NotImplementedError("model.act_ckpt is not supported: gradient checkpointing is already applied "
                                       "inside the blocks. Remove `act_ckpt: true` from the config.")
-        torch.manual_seed(int(tr.get("seed", 0)))
+        torch.manual_seed(int(tr.get("seed", 0)))                  # the same initial weights on every rank
         model_cls = LVSMModel if "class_name" not in cfg["model"] else LVSMModel
         self.model = model_cls(cfg).to(self.device)
+        import random as _random                                   # from here on every process draws its own stream
+        _random.seed(int(tr.get("seed", 0)) + self.rank)
+        torch.manual_seed(int(tr.get("seed", 0)) + self.rank)
         opt = AdamWConfig(lr=float(tr.get("lr", 4e-4)), beta1=float(tr.get("beta1", 0.9)),
                           beta2=float(tr.get("beta2", 0.95)), eps=1e-8, weight_decay=float(tr.get("weight_decay", 0.05)),
                           max_norm=float(tr.get("grad_clip_norm", 1.0)), skip_nan_inf=True)
@@ -305,7 +311,8 @@ class NVSTrainer:
                  enumerate(getattr(self.model.transformer_blocks, "blocks", []))]
         self.trainer = ShardedTrainer(self.model, units, opt, no_decay=lambda n, p: p.dim() < 2)
         self.optimizer, self.schedule = _OptimizerView(self.trainer, self.model), _Schedule(float(tr.get("lr", 4e-4)))
-        self.out_dir = os.path.join(tr.get("out_dir", os.environ.get("UTTT_NVS_OUT_DIR", "experiments")),
+        # the environment variable wins over the file, so one exported path redirects every configuration
+        self.out_dir = os.path.join(os.environ.get("UTTT_NVS_OUT_DIR") or tr.get("out_dir", "experiments"),
                                     cfg.get("exp_name", "run"))
         self.fwdbwd_step = 0
         self.update_step = 0
@@ -625,14 +632,33 @@ class NVSTrainer:
 
 
 def main(argv: Optional[List[str]] = None) -> None:
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--config", required=True)
+    ap = argparse.ArgumentParser(description="View-synthesis trainer")
+    ap.add_argument("config_file", nargs="?", default=None, help="YAML configuration (also --config)")
+    ap.add_argument("--config", default=None)
     ap.add_argument("-s", "--set", nargs=2, action="append", default=[], metavar=("KEY", "VALUE"))
-    ap.add_argument("--load", default="")
+    ap.add_argument("--load", default="", help="load weights from another run or file")
+    ap.add_argument("--seed", type=int, default=None, help="base seed (rank is added); default training.seed or 9595")
+    ap.add_argument("--debug", action="store_true", help="one pass, one evaluation batch, then stop")
+    ap.add_argument("--wandb_project", default=None)
     ap.add_argument("--max-passes", type=int, default=None)
     args = ap.parse_args(argv)
-    cfg = load_config(args.config, args.set)
-    NVSTrainer(cfg, load=args.load).fit(args.max_passes)
+    path = args.config or args.config_file
+    if not path:
+        ap.error("a configuration file is required")
+    if args.wandb_project:
+        os.environ["WANDB_PROJECT"] = args.wandb_project
+    cfg = load_config(path, args.set)
+    if args.seed is not None:
+        cfg["training"]["seed"] = args.seed
+    cfg["training"].setdefault("seed", 9595)
+    trainer = NVSTrainer(cfg, load=args.load)
+    if args.debug:
+        if trainer._eval_data is None and int(cfg["training"].get("eval_every", 2000)) > 0:
+            fresh, _ = trainer._build_eval()
+            trainer._eval_data = (fresh, 1)
+        trainer.fit(1)
+    else:
+        trainer.fit(args.max_passes)
     if dist.is_available() and dist.is_initialized():
         dist.destroy_process_group()
 
