@@ -147,8 +147,7 @@ class MetricsLog:
         self.path, self.run = None, None
         if not enabled:
             return
-        os.makedirs(out_dir, exist_ok=True)
-        self.path = os.path.join(out_dir, "metrics.jsonl")
+        self.path = os.path.join(out_dir, "metrics.jsonl")           # the folder is made by the first line written
         tr = cfg.get("training", {})
         key = os.environ.get("WANDB_API_KEY", "")
         key_file = tr.get("api_key_path")
@@ -165,6 +164,7 @@ class MetricsLog:
         os.environ.setdefault("WANDB_API_KEY", key)
         if tr.get("wandb_offline", False):
             os.environ["WANDB_MODE"] = "offline"
+        os.makedirs(out_dir, exist_ok=True)
         id_file = os.path.join(out_dir, "wandb_id.txt")
         run_id = open(id_file).read().strip() if os.path.exists(id_file) else None
         self.run = wandb.init(project=os.environ.get("WANDB_PROJECT", "uttt-nvs"), name=cfg.get("exp_name", "run"),
@@ -178,6 +178,7 @@ class MetricsLog:
         if self.path is None:
             return
         import json
+        os.makedirs(os.path.dirname(self.path), exist_ok=True)
         with open(self.path, "a") as fh:
             fh.write(json.dumps({"step": step, **payload}) + "\n")
         if self.run is not None:
