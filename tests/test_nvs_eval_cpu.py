@@ -298,3 +298,9 @@ def test_fingerprint_and_perceptual_modules():
     assert val.item() > 0 and a.grad.abs().sum() > 0 and float(loss(b, b)) == 0.0
     d = LPIPSVGG(allow_random=True)
     assert d(b, b).abs().max() == 0 and d(a.detach(), b).shape == (2,)
+    # the VGG-16 trunk with the lpips package's key names for the heads; a term of the training loss, so differentiable
+    names = [k for k in d.vgg.features.state_dict() if k.endswith(".weight")]
+    assert len(names) == 13 and not any(p.requires_grad for p in d.parameters())
+    a.grad = None
+    d(a, b).sum().backward()
+    assert a.grad is not None and a.grad.abs().sum() > 0

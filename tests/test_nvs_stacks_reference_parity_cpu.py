@@ -269,3 +269,49 @@ def test_whole_model_matches_the_reference(rel, shrink, monkeypatch):
     g_r = ref.image_token_decoder[1].weight.grad.flatten().float()
     g_o = ours.image_token_decoder[1].weight.grad.flatten().float()
     assert torch.nn.functional.cosine_similarity(g_o, g_r, dim=0) > 0.999
+
+
+def _synthetic_matconvnet_vgg19(path, seed=0):
+    """A file in the layout of ``imagenet-vgg-verydeep-19.mat`` with random filters: ``layers`` is a 1 x 37 cell of
+    1 x 1 structs (name, type, weights), ``weights`` a 1 x 2 cell (filters [h, w, in, out], bias)."""
+    import numpy as np
+    import scipy.io
+    rng = np.random.default_rng(seed)
+    channels = [64, 64, 128, 128, 256, 256, 256, 256, 512, 512, 512, 512, 512, 512, 512, 512]
+    conv_at = (0, 2, 5, 7, 10, 12, 14, 16, 19, 21, 23, 25, 28, 30, 32, 34)
+    layers = np.empty((1, 37), dtype=object)
+    c_in, k = 3, 0
+    for i in range(37):
+        if i in conv_at:
+            c_out = channels[k]
+            cell = np.empty((1, 2), dtype=object)
+            cell[0, 0] = (rng.standard_normal((3, 3, c_in, c_out)) * (2.0 / (9 * c_in)) ** 0.5).astype(np.float32)
+            cell[0, 1] = (rng.standard_normal((c_out, 1)) * 0.1).astype(np.float32)
+            layers[0, i] = {"name": f"conv{k}", "type": "conv", "weights": cell}
+            c_in, k = c_out, k + 1
+        else:
+            layers[0, i] = {"name": f"other{i}", "type": "relu", "weights": np.empty((1, 0), dtype=object)}
+    scipy.io.savemat(path, {"layers": layers})
+
+
+def test_perceptual_loss_matches_the_reference(tmp_path, monkeypatch):
+    """The VGG-19 perceptual loss against the reference's module, both reading the same MatConvNet-layout file
+    (random filters: the real file cannot be downloaded here): value and gradient with respect to the prediction."""
+    _reference("ttt_dense_block")
+    mat = str(tmp_path / "imagenet-vgg-verydeep-19.mat")
+    _synthetic_matconvnet_vgg19(mat)
+    monkeypatch.setenv("VGG19_MAT_PATH", mat)
+    from uttt_nvs.models.perceptual_loss import PerceptualLoss as Theirs
+    from uttt_b200.nvs.perceptual import PerceptualLoss as Ours
+    theirs, ours = Theirs(), Ours()
+    assert not list(p for p in ours.parameters() if p.requires_grad)
+    torch.manual_seed(0)
+    pred = torch.rand(2, 3, 64, 64)
+    target = torch.rand(2, 3, 64, 64)
+    pr, po = pred.clone().requires_grad_(), pred.clone().requires_grad_()
+    lr_, lo = theirs(pr, target), ours(po, target)
+    torch.testing.assert_close(lo, lr_, rtol=1e-5, atol=1e-6)
+    lr_.backward()
+    lo.backward()
+    torch.testing.assert_close(po.grad, pr.grad, rtol=1e-4, atol=1e-7)
+    assert float(ours(target, target)) == 0.0
