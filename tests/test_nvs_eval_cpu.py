@@ -304,3 +304,25 @@ def test_fingerprint_and_perceptual_modules():
     a.grad = None
     d(a, b).sum().backward()
     assert a.grad is not None and a.grad.abs().sum() > 0
+
+
+def test_output_folder_fingerprint():
+    import hashlib
+    from uttt_b200.nvs.eval.fingerprint import (NATURAL_OUTPUT_IDENTITY_ASSET_KEYS,
+                                                natural_output_source_fingerprint_sha256 as fp)
+    assets = {k: f"{i:064x}" for i, k in enumerate(NATURAL_OUTPUT_IDENTITY_ASSET_KEYS)}
+    base = dict(experiment_id="gso_x", protocol_version="nvs-eval-v2", run_signature="s" * 64, identity_assets=assets,
+                runtime_sha256="r" * 64, scene_count=2, scene_file_sha256={"a.pt": "1" * 64, "b.pt": "2" * 64})
+    digest = fp(**base)
+    # the published canonical form: sorted keys, compact separators, UTF-8
+    payload = {"experiment_id": "gso_x", "protocol_version": "nvs-eval-v2", "run_signature": "s" * 64,
+               "runtime_sha256": "r" * 64, "identity_assets": assets, "scene_count": 2,
+               "scene_file_sha256": base["scene_file_sha256"]}
+    want = hashlib.sha256(json.dumps(payload, ensure_ascii=False, sort_keys=True, separators=(",", ":")).encode()).hexdigest()
+    assert digest == want and fp(**{**base, "scene_file_sha256": {"b.pt": "2" * 64, "a.pt": "1" * 64}}) == digest
+    assert fp(**{**base, "experiment_id": "gso_y"}) != digest
+    for broken in (dict(experiment_id=""), dict(scene_count=3), dict(scene_count=True),
+                   dict(identity_assets={**assets, "extra": "x"}), dict(identity_assets={**assets, "code_commit": ""}),
+                   dict(scene_file_sha256={"dir/a.pt": "1" * 64, "b.pt": "2" * 64})):
+        with pytest.raises(ValueError):
+            fp(**{**base, **broken})

@@ -207,3 +207,38 @@ def validate_runtime_fingerprint(payload: Mapping[str, Any], require_cuda: bool 
             raise ValueError("formal CUDA runtime lacks NVIDIA driver")
     elif payload["gpu_model"] is not None and not isinstance(payload["gpu_model"], str):
         raise ValueError("GPU model must be a string or null")
+
+
+NATURAL_OUTPUT_IDENTITY_ASSET_KEYS = ("registry_sha256", "checkpoint_sha256", "config_sha256", "dataset_manifest_sha256",
+                                      "view_manifest_sha256", "code_commit", "redundancy_code_sha256")
+
+
+def natural_output_source_fingerprint_sha256(*, experiment_id: str, protocol_version: str, run_signature: str,
+                                             identity_assets: Mapping[str, Any], runtime_sha256: str,
+                                             scene_count: int, scene_file_sha256: Mapping[str, str]) -> str:
+    """Path-independent identity of a folder of per-scene model outputs (uttt_nvs/eval/common.py:277-360): which
+    experiment under which protocol and run signature produced it, from which assets (exactly the seven keys of
+    ``NATURAL_OUTPUT_IDENTITY_ASSET_KEYS``), on which runtime, and the digest of every scene file by base name.
+    Any malformed part is an error, so two folders hash alike only when all of it agrees."""
+    scalars = {"experiment_id": experiment_id, "protocol_version": protocol_version, "run_signature": run_signature,
+               "runtime_sha256": runtime_sha256}
+    bad = [k for k, v in scalars.items() if not isinstance(v, str) or not v]
+    if bad:
+        raise ValueError(f"natural-output fingerprint has invalid fields {bad}")
+    if not isinstance(identity_assets, Mapping):
+        raise ValueError("natural-output identity_assets must be an object")
+    if set(identity_assets) != set(NATURAL_OUTPUT_IDENTITY_ASSET_KEYS):
+        raise ValueError(f"natural-output identity_assets must contain exactly {sorted(NATURAL_OUTPUT_IDENTITY_ASSET_KEYS)}")
+    if any(not isinstance(identity_assets[k], str) or not identity_assets[k] for k in NATURAL_OUTPUT_IDENTITY_ASSET_KEYS):
+        raise ValueError("natural-output identity asset values must be non-empty strings")
+    if isinstance(scene_count, bool) or not isinstance(scene_count, int) or scene_count <= 0:
+        raise ValueError("natural-output scene_count must be a positive integer")
+    if not isinstance(scene_file_sha256, Mapping) or len(scene_file_sha256) != scene_count:
+        raise ValueError("natural-output scene_file_sha256 must contain exactly scene_count entries")
+    for name, digest in scene_file_sha256.items():
+        if not isinstance(name, str) or not name or os.path.basename(name) != name or not isinstance(digest, str) \
+                or not digest:
+            raise ValueError("natural-output scene hashes require basename keys and non-empty strings")
+    return canonical_json_sha256({**scalars,
+                                  "identity_assets": {k: identity_assets[k] for k in NATURAL_OUTPUT_IDENTITY_ASSET_KEYS},
+                                  "scene_count": scene_count, "scene_file_sha256": dict(scene_file_sha256)})
