@@ -642,3 +642,34 @@ def test_overrides_aliases_and_command_line(tmp_path, monkeypatch):
     assert not (tmp_path / "from_file").exists()
     blob = torch.load(out / "ckpt_0000000000000001.pt", weights_only=False)
     assert blob["model"]["transformer_blocks.pool_w0"].shape[1] == 2
+
+
+def test_group_after_group_equals_the_layer_interleaved_walk():
+    """The partitioned stack runs its groups one after the other over the whole schedule.  With one layer per group it
+    must give what per-block pools give, which walk the layers chunk by chunk: same weights, same renderings, same
+    gradients."""
+    torch.manual_seed(0)
+    common = dict(aggregate_write=False, num_experts=2, num_active_experts=1)
+    part = LVSMModel(_cfg("uttt_nvs.models.uttt_moe_partitioned.MemoryModel", num_shared_pools=2,
+                          router_share_mode="share_pool", **{**common, "num_experts": 4}))
+    per_block = LVSMModel(_cfg(pool_mode="per_block", router_share_mode="per_layer", **common))
+    rename = {"pool_w0_list": "block_w0_list", "pool_w1_list": "block_w1_list", "pool_w2_list": "block_w2_list",
+              "pool_router_proj_weights_list": "router_proj_weights_list"}
+    sd = {}
+    for k, v in part.state_dict().items():
+        for old, new in rename.items():
+            k = k.replace(f".{old}.", f".{new}.")
+        sd[k] = v
+    per_block.load_state_dict(sd)
+    batch = _batch()
+    out_p, out_b = part(batch), per_block(batch)
+    torch.testing.assert_close(out_p["rendering"], out_b["rendering"], rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(out_p["loss_metrics"]["loss"], out_b["loss_metrics"]["loss"], rtol=1e-5, atol=1e-7)
+    out_p["loss_metrics"]["loss"].backward()
+    out_b["loss_metrics"]["loss"].backward()
+    grads_b = {n: p.grad for n, p in per_block.named_parameters()}
+    for n, p in part.named_parameters():
+        m = n
+        for old, new in rename.items():
+            m = m.replace(f".{old}.", f".{new}.")
+        torch.testing.assert_close(p.grad, grads_b[m], rtol=1e-4, atol=1e-7, msg=n)
