@@ -673,3 +673,21 @@ def test_group_after_group_equals_the_layer_interleaved_walk():
         for old, new in rename.items():
             m = m.replace(f".{old}.", f".{new}.")
         torch.testing.assert_close(p.grad, grads_b[m], rtol=1e-4, atol=1e-7, msg=n)
+
+
+def test_routing_statistics_definitions():
+    from uttt_b200.nvs.blocks import routing_statistics
+    reads = torch.tensor([[[6.0, 2.0], [4.0, 4.0]], [[8.0, 0.0], [1.0, 7.0]]])       # [layers, scenes, experts]
+    writes = torch.tensor([[[2.0, 2.0], [3.0, 1.0]], [[2.0, 2.0], [0.0, 4.0]]])
+    s = routing_statistics(reads, writes, shared_pool=True)
+    assert float(s["apply_max_violation_rate"]) == pytest.approx((0.5 + 0.0 + 1.0 + 0.75) / 4)
+    assert float(s["apply_min_violation_rate"]) == pytest.approx((0.5 + 0.0 + 1.0 + 0.75) / 4)
+    assert float(s["update_max_violation_rate"]) == pytest.approx((0.0 + 0.5 + 0.0 + 1.0) / 4)
+    total = reads + writes                                                            # expert shares over the whole pool
+    share = total.sum(dim=(0, 1)) / total.sum()
+    assert float(s["moe_freq_max"]) == pytest.approx(float(share.max()))
+    per_layer = routing_statistics(reads, writes, shared_pool=False)
+    flat = total.sum(dim=1).flatten() / total.sum()
+    assert float(per_layer["moe_freq_min"]) == pytest.approx(float(flat.min()))
+    out = LVSMModel(_cfg())(_batch())
+    assert {"apply_min_violation_rate", "update_max_violation_rate", "moe_freq_min"} <= set(out["loss_metrics"])

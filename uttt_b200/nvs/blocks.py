@@ -219,6 +219,28 @@ def apply_unit_update(a02, a1, state: fw.PoolState, use_muon: bool, dtype) -> fw
                         n02, n1, None, None)
 
 
+@torch.no_grad()
+def routing_statistics(read_counts: torch.Tensor, write_counts: torch.Tensor, shared_pool: bool) -> Dict[str, torch.Tensor]:
+    """Balance figures from the per-(layer, scene, expert) selection counts of the reads and the writes
+    (uttt_moe_block.py:1468-1506).  Violation rates: per layer and scene, the largest share of an expert times E minus
+    one, and the distance of the smallest share times E from one, averaged.  Frequency extrema: shares of the experts
+    over reads and writes together, pooled over the layers of a shared pool (per (layer, expert) otherwise)."""
+    e = read_counts.shape[-1]
+
+    def violation(counts):
+        share = counts.float() / counts.float().sum(dim=-1, keepdim=True)
+        return (share.max(dim=-1).values * e - 1.0).mean(), (share.min(dim=-1).values * e - 1.0).abs().mean()
+
+    read_max, read_min = violation(read_counts)
+    write_max, write_min = violation(write_counts)
+    freq = (read_counts + write_counts).float().sum(dim=1)
+    freq = freq.sum(dim=0) if shared_pool else freq.flatten()
+    freq = freq / freq.sum().clamp_min(1e-12)
+    return {"apply_max_violation_rate": read_max, "apply_min_violation_rate": read_min,
+            "update_max_violation_rate": write_max, "update_min_violation_rate": write_min,
+            "moe_freq_max": freq.max(), "moe_freq_min": freq.min()}
+
+
 class MemoryModel(nn.Module):
     def __init__(self, layers: int, dim: int, v_gap: Optional[int] = None, load_balancing_loss_alpha: float = 0.01,
                  num_experts: int = 2, fw_head_dim: Optional[int] = None, fw_inter_multi: float = 1,
@@ -406,9 +428,7 @@ class MemoryModel(nn.Module):
         stats: Dict[str, Any] = {}
         if e > 1:
             lb = (fw.lb_loss_for_scope(ap, ac, "layer", e) + fw.lb_loss_for_scope(up, uc, "layer", e)) * self.lb_alpha
-            freq = ac.sum(1) / ac.sum(1).sum(1, keepdim=True).clamp_min(1)
-            stats = {"moe_freq_max": freq.max().detach(), "moe_freq_min": freq.min().detach(),
-                     "apply_max_violation_rate": (freq.max(1).values * e - 1).mean().detach()}
+            stats = routing_statistics(ac.detach(), uc.detach(), shared)
         return out, lb, [stats]
 
     def _write(self, states, mem_ins, pre_vs, keep, dt, se_states=None):
