@@ -44,6 +44,15 @@ def check_lm_json(path: str) -> List[str]:
     e, k = getattr(cfg, "memory_num_experts", 1), getattr(cfg, "memory_num_active_experts", 1)
     if k > e:
         errs.append(f"{path}: more active experts than experts")
+    if not errs:
+        # a registration that resolves but a constructor that rejects the file only shows when the model is built
+        import torch
+        from ..models import build_model
+        try:
+            with torch.device("meta"):
+                build_model(cfg)
+        except Exception as exc:
+            errs.append(f"{path}: the model cannot be built: {type(exc).__name__}: {exc}")
     return errs
 
 

@@ -303,6 +303,22 @@ def main() -> None:
     with open(os.path.join(ROOT, "lm", "exp", "eval_ptl.toml"), "w") as fh:
         fh.write('[job]\ndump_folder = "runs/eval"\n\n[training]\nbatch_size = 1\nseq_len = 32768\ndataset = "synthetic"\n\n'
                  '[eval]\nptl_start = 30000\nmax_batches = 64\n')
+    # the LaCT baseline's own published shapes (24 layers; window and chunk 2048; w0 / w2 low rank 32), with and
+    # without Newton-Schulz, and the fp32-state variant of the 760M model
+    lact = dict(lm_shapes("760M")["lact"], window_size=2048, chunk_size=2048, lact_chunk_size=2048)
+    for name, extra in {
+        "760M_lact_swiglu_nh4_fwlow_rank_momentum": dict(use_muon=False),
+        "760M_lact_swiglu_nh4_fwlow_rank_momentum_muon": dict(use_muon=True),
+        "760M_lact_swiglu_nh4_fwlow_rank_momentum_fused_kernel": dict(use_muon=False, use_fused_kernel=True,
+                                                                      fp32_states=True, no_v_silu=True),
+        "3B_lact_swiglu_nh4_fwlow_rank_momentum": dict(use_muon=False, hidden_size=3072, num_heads=24, num_attn_heads=24),
+        "3B_lact_swiglu_nh4_fwlow_rank_momentum_muon": dict(use_muon=True, hidden_size=3072, num_heads=24,
+                                                            num_attn_heads=24),
+    }.items():
+        path = os.path.join(ROOT, "lm", "lact", f"{name}.json")
+        os.makedirs(os.path.dirname(path), exist_ok=True)
+        with open(path, "w") as fh:
+            fh.write(config_from_dict(dict(lact, **extra)).to_json_string())
     os.makedirs(os.path.join(ROOT, "lm", "named"), exist_ok=True)
     for name in ("760M-uttt-moe", "124M-uttt-moe", "124M-uttt-dense", "tiny-uttt-moe"):
         with open(os.path.join(ROOT, "lm", "named", f"{name}.json"), "w") as fh:
