@@ -242,8 +242,24 @@ def test_sharded_evaluation_merge_aggregate_and_grids(toy):
                                      allow_missing_checkpoint=True)
     assert len(files) == 2 and all(os.path.getsize(f) > 0 for f in files)
     from PIL import Image
-    w, h = Image.open(files[0]).size
-    assert (w, h) == (3 * 34 + 2, 3 * 34 + 2)
+    assert Image.open(files[0]).size == (32 * 4, render_comparison.HEADER + (32 + render_comparison.CAPTION) * 3)
+    index = json.loads((toy["root"] / "grids" / "toy" / "index.json").read_text())
+    assert index["view_indices"] == [1, 3, 5] and index["models"] == ["A-small", "B-small"]
+    assert len(index["scene_ids"]) == 2 and index["files"] == files
+    folder = os.path.dirname(files[0])
+    assert os.path.basename(folder) == render_comparison.safe_name(index["scene_ids"][0])
+    names = set(os.listdir(folder))
+    assert {"input_view_00.png", "comparison.png", "ground_truth_view_01.png", "ground_truth_view_05.png",
+            "A-small_view_01.png", "B-small_view_03.png"} <= names and len(names) == 2 + 3 * 3
+    per_view = index["metrics"]["A-small"][index["scene_ids"][0]]["3"]
+    assert set(per_view) == {"psnr", "ssim", "lpips"} and per_view["psnr"] > 0
+    named = render_comparison.render(reg_path, "toy", ["toy_a"], toy["root"] / "grids_named",
+                                     scene_ids=[index["scene_ids"][1]], view_indices=(2,), device="cpu",
+                                     amp_dtype="fp32", allow_missing_checkpoint=True)
+    assert len(named) == 1 and render_comparison.safe_name(index["scene_ids"][1]) in named[0]
+    with pytest.raises(KeyError):
+        render_comparison.render(reg_path, "toy", ["toy_a"], toy["root"] / "grids_named", scene_ids=["nope"],
+                                 device="cpu", amp_dtype="fp32", allow_missing_checkpoint=True)
 
 
 def test_smoke_runs_stay_out_of_the_full_results(toy):
