@@ -101,6 +101,27 @@ def test_toy_dataset_uses_the_reference_layout(tmp_path):
                       "decoded_images": True, "errors": []}
     with pytest.raises(ValueError):
         make_toy_dataset(str(tmp_path / "x"), num_scenes=0)
+    for field, flag in (("num_scenes", "scenes"), ("num_frames", "views"), ("image_size", "size"), ("repeat", "repeat")):
+        kw = dict(num_scenes=1, num_frames=2, image_size=8, repeat=1)
+        kw[field] = 0
+        with pytest.raises(ValueError, match=flag):
+            make_toy_dataset(str(tmp_path / "absent"), **kw)
+    assert not (tmp_path / "absent").exists()
+
+
+def test_toy_cli_defaults_give_enough_views_for_the_fixed_view_evaluation(tmp_path, capsys):
+    from uttt_b200.nvs import data as nvs_data
+    nvs_data.main(["make-toy", "--out", str(tmp_path), "--scenes", "1", "--size", "8", "--repeat", "1"])
+    man = capsys.readouterr().out.strip().splitlines()[-1]
+    assert man == str(tmp_path / "manifest.txt")
+    assert not manifests.validate_manifest(man, min_views=24)["errors"]
+    with pytest.raises(SystemExit) as err:
+        nvs_data.main(["build-manifest", "--root", str(tmp_path), "--out", str(tmp_path / "m2.txt"), "--limit", "-1"])
+    assert err.value.code == 2 and not (tmp_path / "m2.txt").exists()
+    w2c = np.asarray(json.load(open(tmp_path / "scene_000" / "opencv_cameras.json"))["frames"][0]["w2c"])
+    rot = w2c[:3, :3]                                     # right-handed OpenCV camera that sees the origin in front
+    np.testing.assert_allclose(rot @ rot.T, np.eye(3), atol=1e-5)
+    assert np.linalg.det(rot) == pytest.approx(1.0, abs=1e-5) and w2c[2, 3] > 0
 
 
 def test_checker_reports_each_kind_of_damage(tmp_path):

@@ -99,10 +99,10 @@ def make_toy_dataset(out_dir: str, num_scenes: int = 4, num_frames: int = 16, im
     ``repeat`` times each (a manifest line is a sample, so a few scenes can fill a large global batch).
     Returns the manifest path."""
     from PIL import Image
-    for name, value in (("num_scenes", num_scenes), ("num_frames", num_frames), ("image_size", image_size),
-                        ("repeat", repeat)):
+    for name, flag, value in (("num_scenes", "scenes", num_scenes), ("num_frames", "views", num_frames),
+                              ("image_size", "size", image_size), ("repeat", "repeat", repeat)):
         if type(value) is not int or value < 1:
-            raise ValueError(f"{name} must be a positive integer")
+            raise ValueError(f"{name} (--{flag}) must be a positive integer")
     out_dir = os.path.abspath(os.path.expanduser(out_dir))
     rng = np.random.default_rng(seed)
     manifest = []
@@ -253,8 +253,9 @@ class ResumableDistributedSampler(DistributedSampler):
 
 
 def main(argv=None):
-    """``python -m uttt_b200.nvs.data make-toy --output DIR [--num-scenes 4] [--num-frames 16] [--image-size 64]
-    [--repeat 1]``; ``check-manifest MANIFEST [--min-views N] [--check-images]``; ``build-manifest --root DIR
+    """``python -m uttt_b200.nvs.data make-toy --output DIR [--num-scenes 16] [--num-frames 24] [--image-size 256]
+    [--repeat 16] [--seed 9595]`` (the defaults of uttt_nvs/data/make_toy_dataset.py:99-110: 24 frames per scene are
+    what the fixed-view evaluation needs); ``check-manifest MANIFEST [--min-views N] [--check-images]``; ``build-manifest --root DIR
     --output manifest.txt [--pattern "opencv_cameras*.json"] [--limit N]`` (the last two are also
     ``python -m uttt_b200.nvs.manifests check | build``)."""
     import argparse
@@ -263,11 +264,11 @@ def main(argv=None):
     sub = ap.add_subparsers(dest="cmd", required=True)
     a = sub.add_parser("make-toy")
     a.add_argument("--output", "--out", dest="output", required=True)
-    a.add_argument("--num-scenes", "--scenes", dest="num_scenes", type=int, default=4)
-    a.add_argument("--num-frames", "--views", dest="num_frames", type=int, default=16)
-    a.add_argument("--image-size", "--size", dest="image_size", type=int, default=64)
-    a.add_argument("--repeat", type=int, default=1)
-    a.add_argument("--seed", type=int, default=0)
+    a.add_argument("--num-scenes", "--scenes", dest="num_scenes", type=int, default=16)
+    a.add_argument("--num-frames", "--views", dest="num_frames", type=int, default=24)
+    a.add_argument("--image-size", "--size", dest="image_size", type=int, default=256)
+    a.add_argument("--repeat", type=int, default=16)
+    a.add_argument("--seed", type=int, default=9595)
     b = sub.add_parser("check-manifest")
     b.add_argument("manifest")
     b.add_argument("--min-views", type=int, default=1)
@@ -279,8 +280,11 @@ def main(argv=None):
     c.add_argument("--limit", type=int, default=0)
     args = ap.parse_args(argv)
     if args.cmd == "make-toy":
-        print(make_toy_dataset(args.output, args.num_scenes, args.num_frames, args.image_size, args.seed,
-                               args.repeat))
+        try:
+            print(make_toy_dataset(args.output, args.num_scenes, args.num_frames, args.image_size, args.seed,
+                                   args.repeat))
+        except ValueError as exc:
+            ap.error(str(exc))
     elif args.cmd == "check-manifest":
         sys.exit(manifests.main(["check", args.manifest, "--min-views", str(args.min_views)]
                                 + (["--check-images"] if args.check_images else [])))

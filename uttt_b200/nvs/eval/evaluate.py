@@ -36,7 +36,7 @@ import torch
 import yaml
 
 from .. import metrics as M
-from ..model import LVSMModel
+from ..model import resolve_model_class
 from ..trainer import apply_overrides
 from . import stats
 from .fingerprint import (canonical_json_sha256, deterministic_runtime_fingerprint, evaluation_code_sha256, file_sha256,
@@ -69,7 +69,7 @@ def load_model(exp: Experiment, device, allow_missing_checkpoint: bool = False, 
     """The model of the entry's configuration with the entry's checkpoint loaded strictly: a missing or an
     unexpected tensor is an error (wrapper prefixes of DDP / activation checkpointing / compilation are stripped)."""
     cfg = cfg or load_config(exp)
-    model = LVSMModel(cfg)
+    model = resolve_model_class(cfg["model"].get("class_name"))(cfg)
     info: Dict[str, Any] = {"fwdbwd_pass_step": None, "param_update_step": None}
     if exp.checkpoint is not None and exp.checkpoint.is_file():
         ckpt = torch.load(exp.checkpoint, map_location="cpu", weights_only=False)

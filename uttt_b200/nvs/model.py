@@ -57,6 +57,16 @@ def get_obj_by_name(path: str):
     return getattr(importlib.import_module(module), name)
 
 
+def resolve_model_class(path: Optional[str] = None):
+    """The class that ``model.class_name`` names.  This package has one view-synthesis model, so the reference's
+    ``uttt_nvs.models.lvsm_moe.Images2latent3D`` and this module's ``LVSMModel`` both resolve to it; any other name
+    is an error rather than a silent substitution."""
+    if not path or path in ("uttt_nvs.models.lvsm_moe.Images2latent3D", f"{__name__}.LVSMModel"):
+        return LVSMModel
+    raise ValueError(f"model.class_name {path!r} is not defined (known: uttt_nvs.models.lvsm_moe.Images2latent3D, "
+                     f"{__name__}.LVSMModel)")
+
+
 class Patchify(nn.Module):
     def __init__(self, patch: int):
         super().__init__()

@@ -37,7 +37,7 @@ from ..parallel.fsdp import AdamWConfig, ShardedTrainer
 from ..train.engine import init_distributed
 from .checkpoint import checkpoint_job, delete_previous_job, resume_job, select_resume_path
 from .data import NVSDataset, ResumableDistributedSampler, SyntheticScenes
-from .model import LVSMModel, get_obj_by_name
+from .model import LVSMModel, get_obj_by_name, resolve_model_class
 
 ALIASES = {"block.": "model.block_config.params.", "block0.": "model.block_config.0.params.",
            "block1.": "model.block_config.1.params.", "block2.": "model.block_config.2.params."}
@@ -300,7 +300,7 @@ class NVSTrainer:
             raise NotImplementedError("model.act_ckpt is not supported: gradient checkpointing is already applied "
                                       "inside the blocks. Remove `act_ckpt: true` from the config.")
         torch.manual_seed(int(tr.get("seed", 0)))                  # the same initial weights on every rank
-        model_cls = LVSMModel if "class_name" not in cfg["model"] else LVSMModel
+        model_cls = resolve_model_class(cfg["model"].get("class_name"))
         self.model = model_cls(cfg).to(self.device)
         import random as _random                                   # from here on every process draws its own stream
         _random.seed(int(tr.get("seed", 0)) + self.rank)

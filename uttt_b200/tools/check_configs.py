@@ -67,11 +67,15 @@ def check_job_toml(path: str) -> List[str]:
 
 
 def check_nvs_yaml(path: str) -> List[str]:
-    from ..nvs.model import get_obj_by_name
+    from ..nvs.model import get_obj_by_name, resolve_model_class
     errs = []
     with open(path) as fh:
         cfg = yaml.safe_load(fh)
     m, tr = cfg["model"], cfg["training"]
+    try:
+        resolve_model_class(m.get("class_name"))
+    except ValueError as exc:
+        errs.append(f"{path}: {exc}")
     try:
         get_obj_by_name(m["block_config"]["type"])
     except Exception as exc:
@@ -86,14 +90,18 @@ def check_nvs_yaml(path: str) -> List[str]:
         errs.append(f"{path}: dim not divisible by fw_head_dim")
     if p.get("num_active_experts", 1) > p.get("num_experts", 1):
         errs.append(f"{path}: more active experts than experts")
-    if tr["total_batch_size"] % (tr["batch_size_per_gpu"] * tr.get("grad_accum_steps", 1)):
-        errs.append(f"{path}: total_batch_size is not reachable with batch_size_per_gpu x grad_accum_steps")
     if not isinstance(cfg.get("exp_name"), str) or not cfg["exp_name"]:
         errs.append(f"{path}: exp_name must be a non-empty string")
-    for key in ("total_batch_size", "batch_size_per_gpu", "num_views", "eval_num_views", "max_fwdbwd_passes",
-                "checkpoint_every"):
+    counts_ok = True
+    for key in ("total_batch_size", "batch_size_per_gpu", "grad_accum_steps", "num_views", "eval_num_views",
+                "max_fwdbwd_passes", "checkpoint_every"):
         if key in tr and (type(tr[key]) is not int or tr[key] < 1):
             errs.append(f"{path}: training.{key} must be a positive integer, got {tr[key]!r}")
+            counts_ok = False
+    if counts_ok and tr["total_batch_size"] % (tr["batch_size_per_gpu"] * tr.get("grad_accum_steps", 1)):
+        errs.append(f"{path}: total_batch_size is not reachable with batch_size_per_gpu x grad_accum_steps")
+    if type(p.get("num_experts", 1)) is not int or p.get("num_experts", 1) < 1:
+        errs.append(f"{path}: num_experts must be a positive integer")
     if p.get("aggregate_write") and p.get("pool_mode", "shared") != "shared":
         errs.append(f"{path}: aggregate_write requires a shared pool")
     if not errs:
