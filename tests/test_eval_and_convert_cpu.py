@@ -146,3 +146,81 @@ def test_ptl_job_file_interface_and_summary_tool(tmp_path, capsys):
         ptl.load_positions(tmp_path / "bad.json")
     (tmp_path / "obj.json").write_text(json.dumps({"per_position_loss": [1.0, None], "count": [2, 0]}))
     assert ptl.load_positions(tmp_path / "obj.json")[0] == 1.0
+
+
+class _ByteTokenizer:
+    eos_token_id = 0
+
+    def encode(self, text):
+        return [b + 1 for b in text.encode("utf-8")]
+
+    def decode(self, ids):
+        return bytes(max(i - 1, 0) % 256 for i in ids).decode("latin-1")
+
+
+def test_harness_adapter_requests_and_shard_bookkeeping(tmp_path):
+    """The three request kinds of the evaluation harness on a tiny model, without the harness package."""
+    import json
+    from types import SimpleNamespace
+    from uttt_b200.eval import harness
+    from uttt_b200.models.generation import generate
+    torch.manual_seed(0)
+    model = build_model(named_config("tiny-uttt-moe", memory_lb_loss_alpha=0.0)).eval()
+    tok = _ByteTokenizer()
+    adapter = harness.TextAdapter(model, tok, max_length=96, device="cpu")
+    prompt = "needle 42 is hidden here. " * 3
+    # greedy continuation equals the package's own generate()
+    ids = torch.tensor([tok.encode(prompt)])
+    want = generate(model, ids, max_new_tokens=6)[0, ids.shape[1]:].tolist()
+    if 0 in want:
+        want = want[:want.index(0)]
+    got = adapter.generate_until([SimpleNamespace(args=(prompt, {"until": [], "max_gen_toks": 6}))])
+    assert got == [tok.decode(want)]
+    # a stop string ends the text before it
+    full = tok.decode(want)
+    if len(full) >= 3:
+        stop = full[2]
+        cut = adapter.generate_until([(prompt, {"until": [stop], "max_gen_toks": 6})])[0]
+        assert cut == full[:full.find(stop)]
+    assert harness.first_stop("abc\n\ndef", ["\n\n", "f"]) == "abc" and harness.first_stop("abc", []) == "abc"
+    # log-likelihood equals the sum of next-token log-probabilities of a plain forward
+    cont = " 42"
+    (ll, greedy), = adapter.loglikelihood([(prompt, cont)])
+    seq = tok.encode(prompt) + tok.encode(cont)
+    with torch.no_grad():
+        logits = model(input_ids=torch.tensor([seq[:-1]])).logits[0].float()
+    logp = torch.log_softmax(logits, -1)
+    n = len(tok.encode(cont))
+    ref = sum(float(logp[len(seq) - 1 - n + j, seq[len(seq) - n + j]]) for j in range(n))
+    assert ll == pytest.approx(ref, abs=1e-3) and isinstance(greedy, bool)
+    rolling = adapter.loglikelihood_rolling([(prompt,)])[0]
+    assert math.isfinite(rolling) and rolling < 0
+    # strided shards and their manifest
+    none, off = harness.strided_samples({"niah": 10}, 0, 1)
+    assert none is None and off["enabled"] is False
+    picks, manifest = harness.strided_samples({"niah": 10, "vt": 3}, 1, 4)
+    assert picks == {"niah": [1, 5, 9], "vt": [1]}
+    assert manifest["tasks"]["niah"] == {"total_samples": 10, "shard_samples": 3, "first_index": 1, "last_index": 9}
+    with pytest.raises(ValueError):
+        harness.strided_samples({"niah": 10}, 4, 4)
+    with pytest.raises(ValueError):
+        harness.strided_samples({"niah": 2}, 3, 4)
+    # shard results pooled by sample count
+    for r, (score, count) in enumerate(((1.0, 3), (0.0, 1))):
+        folder = tmp_path / "shards" / f"shard_{r}"
+        folder.mkdir(parents=True)
+        (folder / "results.json").write_text(json.dumps({
+            "results": {"niah": {"4096,none": score, "4096_stderr,none": 0.1, "alias": "niah"}},
+            "sample_shard": {"enabled": True, "rank": r, "world_size": 2,
+                             "tasks": {"niah": {"shard_samples": count}}}}))
+    assert harness.main(["merge", "--shards-dir", str(tmp_path / "shards"), "--output-dir", str(tmp_path / "merged"),
+                         "--expected-shards", "2"]) == 0
+    merged = json.loads((tmp_path / "merged" / "results.json").read_text())
+    assert merged["results"]["niah"] == {"4096,none": 0.75} and merged["samples_per_task"] == {"niah": 4.0}
+    assert harness.main(["merge", "--shards-dir", str(tmp_path / "shards"), "--output-dir", str(tmp_path / "m2"),
+                         "--expected-shards", "3"]) == 1
+    assert harness.write_samples({"a/b": [{"x": 1}]}, tmp_path) == ["samples/a_b.jsonl"]
+    try:
+        import lm_eval  # noqa: F401
+    except ImportError:                                   # the command says what to run instead
+        assert harness.main(["--model-dir", str(tmp_path), "--output", str(tmp_path / "r.json")]) == 2
