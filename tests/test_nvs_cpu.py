@@ -451,6 +451,10 @@ def test_trainer_refuses_what_the_reference_refuses(tmp_path):
     t = NVSTrainer(cfg, device=torch.device("cpu"))
     t.fit()
     assert os.path.isdir(os.path.join(t.out_dir, "eval_00000002")) and t.fwdbwd_step == 2
+    small = make_toy_dataset(str(tmp_path / "small"), num_scenes=1, num_frames=6, image_size=32, repeat=1)
+    cfg["training"].update(dataset_path=small, out_dir=str(tmp_path / "third"))
+    with pytest.raises(ValueError, match="zero complete batches"):   # one entry, two samples per batch
+        NVSTrainer(cfg, device=torch.device("cpu")).fit()
 
 
 def test_learning_rate_schedule_values():

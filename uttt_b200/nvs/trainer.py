@@ -364,6 +364,10 @@ class NVSTrainer:
         self.num_train_samples = len(ds)
         sampler = ResumableDistributedSampler(ds, num_replicas=self.world, rank=self.rank, shuffle=True, seed=0,
                                               drop_last=True)
+        if len(sampler) < int(tr["batch_size_per_gpu"]):
+            raise ValueError(f"zero complete batches: {len(ds)} manifest entries over {self.world} process(es) give "
+                             f"{len(sampler)} samples per process, fewer than batch_size_per_gpu="
+                             f"{tr['batch_size_per_gpu']}; repeat the manifest entries or lower the batch size")
         per_epoch = max(len(sampler) // int(tr["batch_size_per_gpu"]), 1)
         sampler.set_epoch(self.fwdbwd_step // per_epoch)
         sampler.set_resume_offset((self.fwdbwd_step % per_epoch) * int(tr["batch_size_per_gpu"]))
